@@ -1,0 +1,349 @@
+#!/usr/bin/env python
+"""Benchmark of the fp8 fully-connected + attention path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+Prints ONE JSON line (rank 0).  A "step" is one pass of the hot path over one batch of seeded
+synthetic input.  Workloads:
+
+  quant   per-tensor amax + fp32->e4m3 quantise + dequantise round trip of one 2^30-element tensor
+          (values ~N(0,1) with 0.1 % of positions replaced by 100*N(0,1) outliers), GB/s of
+          algorithmic traffic (14 bytes per element)
+
+`value` is measured with inputs resident in HBM; `e2e` is the same work through the C-ABI with
+pinned HOST buffers, host<->device copies inside the timed region.  `--impl reference` times the
+CPU oracle (a port of the upstream project's host-side math; upstream has no CPU implementation
+of its own) on the host cores, on a bounded sample of the same workload.
+
+Under torchrun (N > 1) every rank runs the same per-GPU work (weak scaling, no data-path
+collective); timing is CUDA events, max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+
+def _peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------------
+# workloads
+# ---------------------------------------------------------------------------------------------
+
+class QuantWorkload:
+    """amax + quantise(e4m3) + dequantise of one fp32 tensor, all through the C-ABI."""
+
+    name = "quant"
+    metric = "fp8 quantise+dequantise round-trip GB/s"
+    unit = "GB/s"
+    dtype = "f32->e4m3->f32"
+    bytes_per_elem = 14  # 4 (amax read) + 4 (re-read) + 1 (codes) + 1 (codes read) + 4 (fp32 write)
+    kernels_per_step = 3
+    memsets_per_step = 1
+
+    def __init__(self, log2n: int = 30, seed: int = 1):
+        self.n = 1 << log2n
+        self.log2n = log2n
+        self.seed = seed
+
+    def config(self, n_gpus):
+        return {"workload": f"quantise/dequantise round trip, 2^{self.log2n} fp32 elements per GPU, e4m3, "
+                            "N(0,1) + 0.1% outliers x100, seed 1",
+                "elements_per_gpu": self.n, "l2_policy": "inputs (4 GiB) larger than L2",
+                "parallelism": f"independent tensor per GPU x{n_gpus}"}
+
+    def units_per_step(self):  # GB of algorithmic traffic per GPU per step
+        return self.n * self.bytes_per_elem / 1e9
+
+    def setup(self, torch, df8, dev, rank):
+        self.torch, self.df8 = torch, df8
+        g = torch.Generator(device=dev)
+        g.manual_seed(self.seed + rank)
+        self.x = torch.randn(self.n, device=dev, generator=g)
+        k = self.n // 1000
+        idx = torch.randint(0, self.n, (k,), device=dev, generator=g)
+        self.x[idx] = 100.0 * torch.randn(k, device=dev, generator=g)
+        self.amax = torch.zeros(1, device=dev)
+        self.scale = torch.zeros(2, device=dev)
+        self.codes = torch.empty(self.n, dtype=torch.uint8, device=dev)
+        self.y = torch.empty(self.n, device=dev)
+
+    def step(self):
+        d = self.df8
+        d.amax_f32(self.x, self.amax)
+        d.quantize_f32(self.x, d.E4M3, self.amax, self.codes, self.scale)
+        d.dequantize_f32(self.codes, d.E4M3, self.scale, self.y)
+
+    # dominant kernel, timed on its own for the roofline entry
+    def roofline(self, torch, peaks, iters=10):
+        d = self.df8
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        d.amax_f32(self.x, self.amax)
+        torch.cuda.synchronize()
+        ev[0].record()
+        for _ in range(iters):
+            d.quantize_f32(self.x, d.E4M3, self.amax, self.codes, self.scale)
+        ev[1].record()
+        torch.cuda.synchronize()
+        ms = ev[0].elapsed_time(ev[1]) / iters
+        achieved = self.n * 5 / 1e9 / (ms / 1e3)
+        return {"kernel": "quantize_f32_kernel<e4m3>", "bound": "hbm", "achieved": round(achieved, 1),
+                "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
+                "frac": round(achieved / peaks["hbm_gbs"], 4), "ms_per_launch": round(ms, 4),
+                "algorithmic_bytes_per_launch": self.n * 5, "traffic": None}
+
+    def e2e_setup(self, torch, dev):
+        # a 2^28-element slice of the workload keeps the pinned allocations modest (1 GiB in)
+        self.e2e_n = min(self.n, 1 << 28)
+        self.hx = torch.empty(self.e2e_n, dtype=torch.float32, pin_memory=True)
+        self.hx.copy_(self.x[: self.e2e_n])
+        self.hy = torch.empty(self.e2e_n, dtype=torch.float32, pin_memory=True)
+        self.hcodes = torch.empty(self.e2e_n, dtype=torch.uint8, pin_memory=True)
+
+    def e2e_step(self):
+        d, n = self.df8, self.e2e_n
+        x, codes, y = self.x[:n], self.codes[:n], self.y[:n]
+        x.copy_(self.hx, non_blocking=True)
+        d.amax_f32(x, self.amax)
+        d.quantize_f32(x, d.E4M3, self.amax, codes, self.scale)
+        d.dequantize_f32(codes, d.E4M3, self.scale, y)
+        self.hcodes.copy_(codes, non_blocking=True)
+        self.hy.copy_(y, non_blocking=True)
+
+    def e2e_units_per_step(self):
+        return self.e2e_n * self.bytes_per_elem / 1e9
+
+    def e2e_bytes(self):
+        return self.e2e_n * 4, self.e2e_n * 5
+
+    # CPU oracle on a bounded sample
+    def cpu_sample(self, orc, log2n=25):
+        n = 1 << log2n
+        x = orc.fill_normal_outliers(n, seed=self.seed)
+        t0 = time.perf_counter()
+        a = orc.amax(x)
+        codes, s = orc.quantize(x, orc.E4M3, amax_v=a)
+        orc.dequantize(codes, orc.E4M3, s[1])
+        dt = time.perf_counter() - t0
+        return n * self.bytes_per_elem / 1e9, dt, f"2^{log2n} elements of the same distribution"
+
+
+WORKLOADS = {"quant": QuantWorkload}
+DEFAULT_WORKLOAD = "quant"
+
+
+# ---------------------------------------------------------------------------------------------
+
+def run_reference(args, rank, world):
+    """CPU arm: the oracle port of the upstream host-side math on all host threads (rank 0 only)."""
+    if rank != 0:
+        return
+    import oracle as orc
+
+    orc.build()
+    wl = WORKLOADS[args.workload]()
+    cores = orc.get_threads()
+    for _ in range(max(args.warmup, 1)):
+        wl.cpu_sample(orc, log2n=22)
+    units, secs, sample = 0.0, 0.0, ""
+    for _ in range(args.steps):
+        u, dt, sample = wl.cpu_sample(orc)
+        units += u
+        secs += dt
+    value = units / secs
+    line = {
+        "impl": "reference", "metric": wl.metric, "value": round(value, 3), "unit": wl.unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 * secs / args.steps, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+        "config": wl.config(args.gpus),
+        "cpu_baseline": {"value": round(value, 3), "unit": wl.unit, "cores": cores, "kind": "port",
+                         "sample": sample + " per step; upstream has no CPU implementation of this path, "
+                                            "the oracle port of its host-side math is timed"},
+        "e2e": {"value": round(value, 3), "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    import deepfuse_b200 as df8
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    df8.lib()
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+        torch.cuda.synchronize()
+
+    peaks = _peaks()
+    wl = WORKLOADS[args.workload]()
+    wl.setup(torch, df8, dev, rank)
+
+    for _ in range(args.warmup):
+        wl.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for _ in range(args.steps):
+        wl.step()
+    end.record()
+    barrier()
+    ms_total = start.elapsed_time(end)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # end-to-end: host buffers, copies inside the timed region
+    wl.e2e_setup(torch, dev)
+    for _ in range(2):
+        wl.e2e_step()
+    barrier()
+    e_steps = max(2, min(args.steps, 5))
+    start.record()
+    for _ in range(e_steps):
+        wl.e2e_step()
+    end.record()
+    barrier()
+    e2e_ms_total = start.elapsed_time(end)
+
+    if world > 1:
+        t = torch.tensor([ms_total, e2e_ms_total], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, e2e_ms_total = t.tolist()
+
+    if rank == 0:
+        value = wl.units_per_step() * world * args.steps / (ms_total / 1e3)
+        e2e_value = wl.e2e_units_per_step() * world * e_steps / (e2e_ms_total / 1e3)
+        h2d, d2h = wl.e2e_bytes()
+        roofline = wl.roofline(torch, peaks)
+        import oracle as orc
+
+        orc.build()
+        units, secs, sample = wl.cpu_sample(orc)
+        line = {
+            "metric": wl.metric, "value": round(value, 2), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_total / args.steps, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+            "config": wl.config(world), "clocks": clocks,
+            "e2e": {"value": round(e2e_value, 2), "unit": wl.unit, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "steps": e_steps},
+            "gpu_launches": (wl.kernels_per_step) * args.steps,
+            "roofline": roofline,
+            "cpu_baseline": {"value": round(units / secs, 3), "unit": wl.unit, "cores": orc.get_threads(),
+                             "kind": "port", "sample": sample},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world == 1 and args.gpus > 1 and args.impl == "ours":
+        # convenience: relaunch under torchrun, one rank per GPU
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29531"),
+               str(Path(__file__).resolve()), *sys.argv[1:]]
+        raise SystemExit(subprocess.call(cmd))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

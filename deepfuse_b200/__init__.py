@@ -1,0 +1,103 @@
+"""deepfuse_b200 — Python loader for the B200 fp8 kernel library (``libdf8.so``).
+
+The product is the native code: CUDA kernels behind the C-ABI of ``include/df8.h`` and the C++17
+``dnn::`` classes above it.  This module only loads the shared libraries with ``ctypes`` and gives the
+tests and ``bench.py`` typed access to the entry points.  PyTorch is used by callers for device memory
+and streams only; tensors are passed as raw device pointers.
+
+There is no CPU fallback: if the library has not been built, or an entry point fails, an exception
+is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+__all__ = ["lib", "dnn_lib", "check", "Df8Error", "E4M3", "E5M2", "LIB_DIR", "ptr", "stream_ptr"]
+
+LIB_DIR = Path(__file__).resolve().parent / "lib"
+
+E4M3, E5M2 = 0, 1
+FP8_MAX = {E4M3: 448.0, E5M2: 57344.0}
+
+# GEMM epilogue flags (include/df8.h)
+GELU, RESIDUAL, AMAX = 1, 2, 4
+# attention mask modes
+MASK_NONE, MASK_CAUSAL, MASK_ADDITIVE = 0, 1, 2
+
+
+class Df8Error(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+
+_lib = None
+_dnn = None
+
+_vp, _sz, _i, _f = C.c_void_p, C.c_size_t, C.c_int, C.c_float
+
+# name -> argtypes; every entry returns df8_status (int) unless listed in _RESTYPES
+_SIGNATURES = {
+    "df8_amax_f32": [_vp, _sz, _vp, _vp],
+    "df8_quantize_f32": [_vp, _sz, _i, _vp, _vp, _vp, _vp],
+    "df8_dequantize_f32": [_vp, _sz, _i, _vp, _vp, _vp],
+}
+_RESTYPES = {"df8_last_error": C.c_char_p, "df8_version": C.c_char_p}
+
+
+def lib() -> C.CDLL:
+    """The C-ABI kernel library. Raises if it has not been built (python -m deepfuse_b200.build)."""
+    global _lib
+    if _lib is None:
+        path = LIB_DIR / "libdf8.so"
+        if not path.exists():
+            raise Df8Error(f"{path} is missing: build it with `python -m deepfuse_b200.build` "
+                           "(there is no CPU or PyTorch fallback)")
+        handle = C.CDLL(str(path), mode=C.RTLD_GLOBAL)
+        for name, rt in _RESTYPES.items():
+            fn = getattr(handle, name)
+            fn.restype = rt
+            fn.argtypes = []
+        for name, args in _SIGNATURES.items():
+            fn = getattr(handle, name, None)
+            if fn is None:
+                raise Df8Error(f"libdf8.so does not export {name}")
+            fn.argtypes = args
+            fn.restype = C.c_int
+        _lib = handle
+    return _lib
+
+
+def check(status: int, what: str = "") -> None:
+    """Raise Df8Error carrying df8_last_error() if `status` is non-zero."""
+    if status != 0:
+        msg = lib().df8_last_error().decode("utf-8", "replace")
+        raise Df8Error(f"{what or 'df8 call'} failed (status {status}): {msg}")
+
+
+def ptr(t) -> int:
+    """Device pointer of a torch tensor (or None)."""
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(stream=None) -> int:
+    """cudaStream_t of a torch stream (default: torch's current stream)."""
+    import torch
+
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return s.cuda_stream
+
+
+# ---- thin typed wrappers over torch tensors (used by tests and bench.py) -----------------------
+
+def amax_f32(x, amax_out, stream=None) -> None:
+    check(lib().df8_amax_f32(ptr(x), x.numel(), ptr(amax_out), stream_ptr(stream)), "df8_amax_f32")
+
+
+def quantize_f32(x, kind: int, amax_in, codes_out, scale_out, stream=None) -> None:
+    check(lib().df8_quantize_f32(ptr(x), x.numel(), kind, ptr(amax_in), ptr(codes_out), ptr(scale_out),
+                                 stream_ptr(stream)), "df8_quantize_f32")
+
+
+def dequantize_f32(codes, kind: int, scale, y_out, stream=None) -> None:
+    check(lib().df8_dequantize_f32(ptr(codes), codes.numel(), kind, ptr(scale), ptr(y_out), stream_ptr(stream)),
+          "df8_dequantize_f32")

@@ -1,0 +1,130 @@
+// Internal helpers shared by the kernel translation units of libdf8 (not part of the C-ABI).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "df8.h"
+
+namespace df8 {
+
+// Records a printf-style message as the calling thread's last error and returns `code`.
+df8_status fail(df8_status code, const char* fmt, ...);
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+#define DF8_CUDA_TRY(expr)                                                                  \
+    do {                                                                                    \
+        cudaError_t err__ = (expr);                                                         \
+        if (err__ != cudaSuccess)                                                           \
+            return ::df8::fail(DF8_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                \
+                               cudaGetErrorString(err__), __FILE__, __LINE__);              \
+    } while (0)
+
+#define DF8_LAUNCH_CHECK(what)                                                              \
+    do {                                                                                    \
+        cudaError_t err__ = cudaGetLastError();                                             \
+        if (err__ != cudaSuccess)                                                           \
+            return ::df8::fail(DF8_ERR_CUDA, "launch of %s failed: %s", what,               \
+                               cudaGetErrorString(err__));                                  \
+    } while (0)
+
+#define DF8_REQUIRE(cond, ...)                                                              \
+    do {                                                                                    \
+        if (!(cond)) return ::df8::fail(DF8_ERR_INVALID, __VA_ARGS__);                      \
+    } while (0)
+
+inline cudaStream_t as_stream(df8_stream s) { return reinterpret_cast<cudaStream_t>(s); }
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+__host__ __device__ constexpr float fp8_max(int kind) { return kind == DF8_E4M3 ? 448.0f : 57344.0f; }
+
+// ---- device helpers ---------------------------------------------------------------------
+
+// Two fp32 -> two fp8 codes, round-to-nearest-even, saturating to the largest finite value.
+// The low byte of the result holds `lo`, the high byte `hi`.
+template <int KIND>
+__device__ __forceinline__ uint16_t cvt_f32x2_to_fp8x2(float lo, float hi) {
+    uint16_t r;
+    if constexpr (KIND == DF8_E4M3) {
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    } else {
+        asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    }
+    return r;
+}
+
+// Four fp32 -> four packed fp8 codes (byte i holds v[i]).
+template <int KIND>
+__device__ __forceinline__ uint32_t cvt_f32x4_to_fp8x4(float a, float b, float c, float d) {
+    return uint32_t(cvt_f32x2_to_fp8x2<KIND>(a, b)) | (uint32_t(cvt_f32x2_to_fp8x2<KIND>(c, d)) << 16);
+}
+
+// Two fp8 codes (low byte = first) -> two fp32 values; exact widening via f16.
+template <int KIND>
+__device__ __forceinline__ float2 cvt_fp8x2_to_f32x2(uint16_t codes) {
+    uint32_t h2;
+    if constexpr (KIND == DF8_E4M3) {
+        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(codes));
+    } else {
+        asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(h2) : "h"(codes));
+    }
+    float lo, hi;
+    asm("{.reg .f16 l, h; mov.b32 {l, h}, %2; cvt.f32.f16 %0, l; cvt.f32.f16 %1, h;}"
+        : "=f"(lo), "=f"(hi)
+        : "r"(h2));
+    return make_float2(lo, hi);
+}
+
+// q = FP8_MAX / amax and dq = amax / FP8_MAX, each one IEEE fp32 division; both 1 when amax is 0.
+__device__ __forceinline__ float2 scales_from_amax(float amax, float fmax) {
+    if (!(amax > 0.0f)) return make_float2(1.0f, 1.0f);
+    return make_float2(__fdiv_rn(fmax, amax), __fdiv_rn(amax, fmax));
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// atomic max for non-negative floats (their bit patterns order like unsigned integers).
+__device__ __forceinline__ void atomic_max_nonneg(float* addr, float v) {
+    atomicMax(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
+}
+
+// 128-bit streaming global accesses (data touched once: keep it out of L1).
+__device__ __forceinline__ float4 ld_stream_f4(const float4* p) {
+    float4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ld_stream_u4(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void st_stream_f4(float4* p, float4 v) {
+    asm volatile("st.global.cs.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ void st_stream_u4(uint4* p, uint4 v) {
+    asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+}  // namespace df8

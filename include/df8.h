@@ -1,0 +1,81 @@
+/*
+ * df8.h — C-ABI of the B200 (sm_100a) fp8 fully-connected + attention kernel library.
+ *
+ * This is the boundary the C++ `dnn::` layer classes (dnn/core, dnn/layers, dnn/models) sit on.
+ * The upstream project has no FFI of its own: its layers launch their kernels directly from the
+ * class bodies.  Each entry point below therefore names the upstream launch site (or the
+ * host-side helper) it replaces, by that project's file:line.
+ *
+ * Conventions
+ *  - every function returns a df8_status (0 = ok); the text of the last failure on the calling
+ *    thread is returned by df8_last_error();
+ *  - all pointers are DEVICE pointers unless the parameter name ends in `_h`;
+ *  - every launch is enqueued on the `stream` argument; nothing synchronises the device and
+ *    nothing allocates device memory, except the calls documented as doing so
+ *    (df8_streamer_create, df8_comm_*);
+ *  - scales are passed as device pointers so that a chain of kernels runs without a host
+ *    round trip:  `scale` is a pair of floats {q, dq} with q = FP8_MAX/amax (1 if amax==0)
+ *    and dq = amax/FP8_MAX (1 if amax==0);  FP8_MAX = 448 for e4m3 and 57344 for e5m2;
+ *  - fp8 values travel as raw codes in uint8_t buffers (the upstream tensor type for them is
+ *    dnn::tensor<uint8_t>, dnn/core/tensor.cuh:149).
+ */
+#ifndef DF8_H_
+#define DF8_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int df8_status;
+enum {
+    DF8_OK = 0,
+    DF8_ERR_INVALID = 1,     /* bad argument (null pointer, bad size, bad enum, misalignment) */
+    DF8_ERR_CUDA = 2,        /* a CUDA runtime / driver call failed */
+    DF8_ERR_UNSUPPORTED = 3, /* shape outside what the kernels cover */
+    DF8_ERR_TIMEOUT = 4,     /* a bounded device-side wait gave up (see df8_status_word_read) */
+    DF8_ERR_COMM = 5         /* an NCCL call failed */
+};
+
+/* fp8 element kinds.  Upstream names only the storage types (__nv_fp8x4_e4m3 / __nv_fp8x4_e5m2,
+ * dnn/core/tensor.cu:489-498); conversion semantics are those of the CUDA toolkit's cuda_fp8.h:
+ * round-to-nearest-even, saturate to the largest finite value. */
+typedef enum { DF8_E4M3 = 0, DF8_E5M2 = 1 } df8_kind;
+
+/* stream handle: a cudaStream_t passed as an opaque pointer (NULL = legacy default stream,
+ * which is what dnn::Cuda::stream() returns when no stream is set, dnn/core/cuda.cu:85-87). */
+typedef void* df8_stream;
+
+/* ---- library ---------------------------------------------------------------------------- */
+
+/* Text of the last error recorded on the calling thread ("" if none). Never NULL. */
+const char* df8_last_error(void);
+
+/* Library version string. */
+const char* df8_version(void);
+
+/* ---- per-tensor amax / quantise / dequantise ---------------------------------------------
+ * No upstream kernel exists for these (the fp8 tensor instantiations at dnn/core/tensor.cu:489-498
+ * are never compiled); they implement the per-tensor quantiser:
+ *     amax = max_i |x_i|;  q = FP8_MAX / amax;  code_i = cvt_rn_satfinite(x_i * q);
+ *     y_i = float(code_i) * (amax / FP8_MAX).
+ */
+
+/* amax_out[0] = max_i |x[i]| over n fp32 values (NaNs are ignored; n == 0 gives 0).
+ * The kernel clears amax_out itself. */
+df8_status df8_amax_f32(const float* x, size_t n, float* amax_out, df8_stream stream);
+
+/* codes_out[i] = fp8(x[i] * q) with q derived from amax_in[0]; writes scale_out = {q, dq}. */
+df8_status df8_quantize_f32(const float* x, size_t n, df8_kind kind, const float* amax_in,
+                            uint8_t* codes_out, float* scale_out, df8_stream stream);
+
+/* y_out[i] = float(codes[i]) * scale[1]. */
+df8_status df8_dequantize_f32(const uint8_t* codes, size_t n, df8_kind kind, const float* scale,
+                              float* y_out, df8_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DF8_H_ */

@@ -162,7 +162,10 @@ class QuantWorkload:
         return {"kernel": "quantize_f32_kernel<e4m3>", "bound": "hbm", "achieved": round(achieved, 1),
                 "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
                 "frac": round(achieved / peaks["hbm_gbs"], 4), "ms_per_launch": round(ms, 4),
-                "algorithmic_bytes_per_launch": self.n * 5, "traffic": None}
+                "algorithmic_bytes_per_launch": self.n * 5,
+                # ncu dram read+write bytes of one 2^27-element launch (619.17 MB,
+                # profiles/quantize_f32_kernel_quant_2p27.md), scaled by the element count
+                "traffic": round(619.17e6 * self.n / (1 << 27))}
 
     def e2e_setup(self, torch, dev):
         # a 2^28-element slice of the workload keeps the pinned allocations modest (1 GiB in)
@@ -204,6 +207,12 @@ WORKLOADS = {"quant": QuantWorkload}
 DEFAULT_WORKLOAD = "quant"
 
 
+def make_workload(args):
+    if args.workload == "quant" and args.log2n:
+        return QuantWorkload(log2n=args.log2n)
+    return WORKLOADS[args.workload]()
+
+
 # ---------------------------------------------------------------------------------------------
 
 def run_reference(args, rank, world):
@@ -213,7 +222,7 @@ def run_reference(args, rank, world):
     import oracle as orc
 
     orc.build()
-    wl = WORKLOADS[args.workload]()
+    wl = make_workload(args)
     cores = orc.get_threads()
     for _ in range(max(args.warmup, 1)):
         wl.cpu_sample(orc, log2n=22)
@@ -257,7 +266,7 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.synchronize()
 
     peaks = _peaks()
-    wl = WORKLOADS[args.workload]()
+    wl = make_workload(args)
     wl.setup(torch, df8, dev, rank)
 
     for _ in range(args.warmup):
@@ -327,6 +336,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--log2n", type=int, default=None, help="quant workload: tensor size override (profiling)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

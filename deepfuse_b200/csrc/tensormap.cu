@@ -1,0 +1,48 @@
+#include "tensormap.cuh"
+
+#include <cudaTypedefs.h>
+#include <mutex>
+
+namespace df8 {
+
+namespace {
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(p);
+    });
+    return fn;
+}
+}  // namespace
+
+df8_status make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
+                           uint32_t box_rows, uint32_t box_cols, bool swizzle128) {
+    EncodeFn fn = encode_fn();
+    if (!fn) return fail(DF8_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) || (pitch_bytes & 15u))
+        return fail(DF8_ERR_INVALID, "TMA operand must be 16-byte aligned with a row pitch that is a multiple of 16 "
+                                     "(base %p, pitch %llu)", base, (unsigned long long)pitch_bytes);
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(DF8_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rows %llu cols %llu pitch %llu box %ux%u)",
+                    int(r), (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)pitch_bytes,
+                    box_rows, box_cols);
+    return DF8_OK;
+}
+
+}  // namespace df8

@@ -40,6 +40,9 @@ _SIGNATURES = {
     "df8_amax_f32": [_vp, _sz, _vp, _vp],
     "df8_quantize_f32": [_vp, _sz, _i, _vp, _vp, _vp, _vp],
     "df8_dequantize_f32": [_vp, _sz, _i, _vp, _vp, _vp],
+    "df8_gemm_fp8_tn": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp],
+    "df8_status_word_read": [_vp, _vp],
+    "df8_status_word_reset": [],
 }
 _RESTYPES = {"df8_last_error": C.c_char_p, "df8_version": C.c_char_p}
 
@@ -101,3 +104,21 @@ def quantize_f32(x, kind: int, amax_in, codes_out, scale_out, stream=None) -> No
 def dequantize_f32(codes, kind: int, scale, y_out, stream=None) -> None:
     check(lib().df8_dequantize_f32(ptr(codes), codes.numel(), kind, ptr(scale), ptr(y_out), stream_ptr(stream)),
           "df8_dequantize_f32")
+
+
+def gemm_fp8_tn(a_codes, kind_a, scale_a, w_codes, kind_w, scale_w, bias, residual, M, N, K, flags, out,
+                out_amax=None, stream=None) -> None:
+    check(lib().df8_gemm_fp8_tn(ptr(a_codes), kind_a, ptr(scale_a), ptr(w_codes), kind_w, ptr(scale_w), ptr(bias),
+                                ptr(residual), M, N, K, flags, ptr(out), ptr(out_amax), stream_ptr(stream)),
+          "df8_gemm_fp8_tn")
+
+
+def status_word() -> tuple[int, int]:
+    """(first timeout code, number of timeouts) recorded by bounded device-side waits; (0, 0) when clean."""
+    code, count = C.c_uint(0), C.c_uint(0)
+    check(lib().df8_status_word_read(C.byref(code), C.byref(count)), "df8_status_word_read")
+    return code.value, count.value
+
+
+def status_word_reset() -> None:
+    check(lib().df8_status_word_reset(), "df8_status_word_reset")

@@ -75,6 +75,33 @@ df8_status df8_quantize_f32(const float* x, size_t n, df8_kind kind, const float
 df8_status df8_dequantize_f32(const uint8_t* codes, size_t n, df8_kind kind, const float* scale,
                               float* y_out, df8_stream stream);
 
+/* ---- fp8 GEMM (fully connected) ----------------------------------------------------------
+ * Replaces the launch of fully_connected_forward_kernel (dnn/layers/fully_connected_layer.cu:15-41,
+ * launched at :199-208):  Y[M,N] = X[M,K] . W[N,K]^T + b,  W stored [out,in] row-major.
+ * Here X and W arrive as fp8 codes with their per-tensor scales and the contraction runs on the
+ * tcgen05 tensor cores with fp32 accumulation:
+ *     out[m,n] = epi( acc[m,n] * (scale_a[1] * scale_w[1]) + bias[n] )
+ * epi, selected by `flags`:
+ *     DF8_EPI_GELU      x*0.5*(1+tanh(0.7978845608*(x+0.044715x^3)))   (dnn/layers/activation_layer.cu:9-20)
+ *     DF8_EPI_RESIDUAL  + residual[m,n]      (replaces the separate add kernel, dnn/core/tensor.cu:383-415)
+ *     DF8_EPI_AMAX      also reduce max|out| into out_amax[0] (cleared by the call), so the next
+ *                       quantise needs no separate amax pass
+ * K must be a multiple of 16; A and W must be 16-byte aligned.  bias may be NULL. */
+enum { DF8_EPI_GELU = 1, DF8_EPI_RESIDUAL = 2, DF8_EPI_AMAX = 4 };
+
+df8_status df8_gemm_fp8_tn(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a,
+                           const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
+                           const float* bias, const float* residual, int M, int N, int K, int flags,
+                           float* out, float* out_amax, df8_stream stream);
+
+/* ---- bounded-wait status word --------------------------------------------------------------
+ * Every device-side wait (mbarrier polls in the GEMM and attention pipelines) gives up after a
+ * time limit instead of hanging the GPU; the first such event stores a non-zero code.  Upstream
+ * has no counterpart (its kernels do not wait on one another).  Both calls synchronise with the
+ * device (they copy from / to a device symbol); code_h / count_h are HOST pointers. */
+df8_status df8_status_word_read(unsigned int* code_h, unsigned int* count_h);
+df8_status df8_status_word_reset(void);
+
 #ifdef __cplusplus
 }
 #endif

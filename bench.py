@@ -64,6 +64,11 @@ class ClockSampler:
             return
         self.thread = threading.Thread(target=self._pump, daemon=True)
         self.thread.start()
+        # nvidia-smi stalls kernel launches while it attaches to the driver: let it produce its first
+        # sample before the timed region begins
+        t0 = time.time()
+        while not self.lines and time.time() - t0 < 5.0:
+            time.sleep(0.02)
 
     def _pump(self):
         for line in self.proc.stdout:
@@ -203,13 +208,124 @@ class QuantWorkload:
         return n * self.bytes_per_elem / 1e9, dt, f"2^{log2n} elements of the same distribution"
 
 
-WORKLOADS = {"quant": QuantWorkload}
+
+class GemmWorkload:
+    """The fp8 projections of one GPT-2 layer at M tokens (QKV, out, FC1+GELU, FC2+residual) plus the
+    vocabulary head, each one df8_gemm_fp8_tn call on pre-quantised e4m3 operands."""
+
+    name = "gemm"
+    metric = "fp8 GEMM TFLOP/s"
+    unit = "TFLOP/s"
+    dtype = "e4m3 x e4m3 -> f32"
+
+    def __init__(self, M=8192, E=768, F=3072, V=50257, only=None):
+        self.M, self.E, self.F, self.V = M, E, F, V
+        shapes = [("qkv", 3 * E, E, 4), ("out", E, E, 2), ("fc1", F, E, 1 | 4), ("fc2", E, F, 2), ("head", V, E, 0)]
+        self.shapes = [s for s in shapes if only is None or s[0] in only]
+        self.kernels_per_step = len(self.shapes)
+
+    def config(self, n_gpus):
+        return {"workload": f"GPT-2 small projection set at M={self.M} tokens: "
+                            + ", ".join(f"{n}[{self.M}x{N}x{K}]" for n, N, K, _ in self.shapes),
+                "l2_policy": "L2 flushed by a 256 MiB write between steps", "parallelism": f"replicated x{n_gpus}"}
+
+    def flops(self):
+        return sum(2.0 * self.M * N * K for _, N, K, _ in self.shapes)
+
+    def units_per_step(self):
+        return self.flops() / 1e12
+
+    def setup(self, torch, df8, dev, rank):
+        self.torch, self.df8 = torch, df8
+        g = torch.Generator(device=dev)
+        g.manual_seed(5 + rank)
+        self.ops = []
+        one = torch.tensor([1.0, 1.0 / 64], device=dev)
+        for name, N, K, flags in self.shapes:
+            a = torch.randint(0, 0x78, (self.M, K), dtype=torch.uint8, device=dev, generator=g)
+            w = torch.randint(0, 0x60, (N, K), dtype=torch.uint8, device=dev, generator=g)
+            sign = torch.randint(0, 2, (N, K), dtype=torch.uint8, device=dev, generator=g) * 0x80
+            w = w | sign
+            bias = torch.zeros(N, device=dev)
+            res = torch.randn(self.M, N, device=dev, generator=g) if flags & 2 else None
+            out = torch.empty(self.M, N, device=dev)
+            amax = torch.zeros(1, device=dev)
+            self.ops.append((a, w, bias, res, out, amax, N, K, flags))
+        self.one = one
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step(self):
+        d = self.df8
+        self.flush.zero_()
+        for a, w, bias, res, out, amax, N, K, flags in self.ops:
+            d.gemm_fp8_tn(a, d.E4M3, self.one, w, d.E4M3, self.one, bias, res, self.M, N, K, flags, out, amax)
+
+    def roofline(self, torch, peaks, iters=20):
+        d = self.df8
+        per = {}
+        best = None
+        for (name, _, _, _), (a, w, bias, res, out, amax, N, K, flags) in zip(self.shapes, self.ops):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            for _ in range(3):
+                d.gemm_fp8_tn(a, d.E4M3, self.one, w, d.E4M3, self.one, bias, res, self.M, N, K, flags, out, amax)
+            torch.cuda.synchronize()
+            ev[0].record()
+            for _ in range(iters):
+                d.gemm_fp8_tn(a, d.E4M3, self.one, w, d.E4M3, self.one, bias, res, self.M, N, K, flags, out, amax)
+            ev[1].record()
+            torch.cuda.synchronize()
+            ms = ev[0].elapsed_time(ev[1]) / iters
+            tf = 2.0 * self.M * N * K / 1e12 / (ms / 1e3)
+            per[name] = {"ms": round(ms, 4), "tflops": round(tf, 1)}
+            if best is None or 2.0 * self.M * N * K > best[0]:
+                best = (2.0 * self.M * N * K, name, ms, tf)
+        peak = 2.0 * peaks["bf16_tflops"]
+        return {"kernel": f"gemm_fp8_tn_kernel ({best[1]})", "bound": "tensor", "achieved": round(best[3], 1),
+                "peak": peak, "peak_source": peaks["source"] + " bf16 burst x2 (fp8 dense)", "unit": "TFLOP/s",
+                "frac": round(best[3] / peak, 4), "ms_per_launch": round(best[2], 4),
+                "algorithmic_flops_per_launch": best[0], "traffic": None, "per_shape": per}
+
+    def e2e_setup(self, torch, dev):
+        a = self.ops[0][0]
+        self.h_a = torch.empty(a.shape, dtype=torch.uint8, pin_memory=True)
+        self.h_a.copy_(a)
+        self.h_out = torch.empty(self.M, dtype=torch.float32, pin_memory=True)
+
+    def e2e_step(self):
+        self.ops[0][0].copy_(self.h_a, non_blocking=True)
+        self.step()
+        self.h_out.copy_(self.ops[-1][4][:, 0], non_blocking=True)
+
+    def e2e_units_per_step(self):
+        return self.units_per_step()
+
+    def e2e_bytes(self):
+        return self.h_a.numel(), self.h_out.numel() * 4
+
+    def cpu_sample(self, orc, rows=16):
+        import numpy as np
+
+        units, secs = 0.0, 0.0
+        rng = np.random.default_rng(0)
+        for name, N, K, flags in self.shapes:
+            Nc = min(N, 4096)
+            xc = rng.integers(0, 0x78, (rows, K), dtype=np.uint8)
+            wc = rng.integers(0, 0x60, (Nc, K), dtype=np.uint8)
+            t0 = time.perf_counter()
+            orc.fc_forward_fp8(xc, orc.E4M3, 1.0, wc, orc.E4M3, 1.0)
+            secs += time.perf_counter() - t0
+            units += 2.0 * rows * Nc * K / 1e12
+        return units, secs, f"{rows} token rows (and at most 4096 output columns) of each projection"
+
+WORKLOADS = {"quant": QuantWorkload, "gemm": GemmWorkload}
 DEFAULT_WORKLOAD = "quant"
 
 
 def make_workload(args):
     if args.workload == "quant" and args.log2n:
         return QuantWorkload(log2n=args.log2n)
+    if args.workload == "gemm" and args.only:
+        return GemmWorkload(only=args.only.split(","))
     return WORKLOADS[args.workload]()
 
 
@@ -319,7 +435,7 @@ def run_ours(args, rank, world, local_rank):
             "config": wl.config(world), "clocks": clocks,
             "e2e": {"value": round(e2e_value, 2), "unit": wl.unit, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e_steps},
-            "gpu_launches": (wl.kernels_per_step) * args.steps,
+            "gpu_launches": wl.kernels_per_step * args.steps,
             "roofline": roofline,
             "cpu_baseline": {"value": round(units / secs, 3), "unit": wl.unit, "cores": orc.get_threads(),
                              "kind": "port", "sample": sample},
@@ -336,6 +452,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default=None, help="gemm workload: comma list of projections (profiling)")
     ap.add_argument("--log2n", type=int, default=None, help="quant workload: tensor size override (profiling)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":

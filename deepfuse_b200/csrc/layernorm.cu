@@ -1,0 +1,221 @@
+// Row-wise LayerNorm over the last dimension, plain and fused with the per-tensor fp8 quantiser.
+//
+// Math (upstream dnn/layers/layer_norm_layer.cu:40-62): mean = sum(x)/C; var = sum((x-mean)^2)/C
+// (biased, second pass); y = (x-mean) * rsqrt(var+eps) * gamma + beta.  Upstream computes both sums
+// serially in thread 0 and only handles 2-D [rows, C<=1024] inputs (:70-79); here a row is reduced by a
+// whole CTA with warp shuffles, any C, and [B,T,E] inputs are rows = B*T.
+//
+// Because the LayerNorm output always feeds a GEMM, the fused entry point never writes the fp32
+// result: pass 1 keeps each row's (mean, rstd) in a small scratch array and reduces max|y| over the
+// tensor, pass 2 re-reads x, normalises and emits fp8 codes.  9 bytes of HBM traffic per element
+// instead of 13 for LayerNorm -> amax -> quantise as separate kernels.
+#include "df8_internal.cuh"
+
+namespace df8 {
+namespace {
+
+constexpr int kLnThreads = 256;
+constexpr int kMaxV4 = 4;  // float4 per thread kept in registers: C <= 4096 on the fast path
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();  // protect `red` from the previous reduction's readers
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = lane < nw ? red[lane] : 0.f;
+    return warp_sum(t);  // every warp computes the same total
+}
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+    v = warp_max(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = lane < nw ? red[lane] : 0.f;
+    return warp_max(t);
+}
+
+// MODE 0: write fp32 y (+ optional amax).  MODE 1: stats pass (row stats + amax, no y).
+// MODE 2: quantise pass (reads row stats and the scale derived from amax, writes codes).
+template <int MODE, int KIND, bool FAST>
+__global__ void __launch_bounds__(kLnThreads)
+layernorm_kernel(const float* __restrict__ x, int rows, int C, const float* __restrict__ gamma,
+                 const float* __restrict__ beta, float eps, float* __restrict__ y, float* __restrict__ amax_out,
+                 float2* __restrict__ row_stats, const float* __restrict__ amax_in, uint8_t* __restrict__ codes,
+                 float* __restrict__ scale_out) {
+    __shared__ float red[kLnThreads / 32];
+    float q = 1.f;
+    if constexpr (MODE == 2) {
+        const float2 s = scales_from_amax(*amax_in, fp8_max(KIND));
+        q = s.x;
+        if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) {
+            scale_out[0] = s.x;
+            scale_out[1] = s.y;
+        }
+    }
+    float tile_amax = 0.f;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float* xr = x + size_t(row) * C;
+        float mean, rstd;
+        if constexpr (FAST) {
+            // C % 4 == 0 and C <= 4 * kMaxV4 * blockDim: the row lives in registers
+            const int c4 = C >> 2;
+            float4 v[kMaxV4];
+#pragma unroll
+            for (int j = 0; j < kMaxV4; ++j) {
+                const int i = threadIdx.x + j * kLnThreads;
+                v[j] = i < c4 ? reinterpret_cast<const float4*>(xr)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            if constexpr (MODE == 2) {
+                const float2 st = row_stats[row];
+                mean = st.x;
+                rstd = st.y;
+            } else {
+                float s = 0.f;
+#pragma unroll
+                for (int j = 0; j < kMaxV4; ++j) s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+                mean = block_sum(s, red) / float(C);
+                float sq = 0.f;
+#pragma unroll
+                for (int j = 0; j < kMaxV4; ++j) {
+                    const int i = threadIdx.x + j * kLnThreads;
+                    if (i < c4) {
+                        const float a = v[j].x - mean, b = v[j].y - mean, c = v[j].z - mean, d = v[j].w - mean;
+                        sq += (a * a + b * b) + (c * c + d * d);
+                    }
+                }
+                rstd = rsqrtf(block_sum(sq, red) / float(C) + eps);
+                if constexpr (MODE == 1)
+                    if (threadIdx.x == 0) row_stats[row] = make_float2(mean, rstd);
+            }
+#pragma unroll
+            for (int j = 0; j < kMaxV4; ++j) {
+                const int i = threadIdx.x + j * kLnThreads;
+                if (i < c4) {
+                    float4 g = make_float4(1.f, 1.f, 1.f, 1.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (gamma) g = reinterpret_cast<const float4*>(gamma)[i];
+                    if (beta) b = reinterpret_cast<const float4*>(beta)[i];
+                    float4 o;
+                    o.x = fmaf((v[j].x - mean) * rstd, g.x, b.x);
+                    o.y = fmaf((v[j].y - mean) * rstd, g.y, b.y);
+                    o.z = fmaf((v[j].z - mean) * rstd, g.z, b.z);
+                    o.w = fmaf((v[j].w - mean) * rstd, g.w, b.w);
+                    if constexpr (MODE == 2) {
+                        reinterpret_cast<uint32_t*>(codes + size_t(row) * C)[i] = cvt_f32x4_to_fp8x4<KIND>(
+                            __fmul_rn(o.x, q), __fmul_rn(o.y, q), __fmul_rn(o.z, q), __fmul_rn(o.w, q));
+                    } else {
+                        tile_amax = fmaxf(tile_amax, fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w))));
+                        if constexpr (MODE == 0) reinterpret_cast<float4*>(y + size_t(row) * C)[i] = o;
+                    }
+                }
+            }
+        } else {
+            // any C: three passes over the row (it stays in L1/L2)
+            if constexpr (MODE == 2) {
+                const float2 st = row_stats[row];
+                mean = st.x;
+                rstd = st.y;
+            } else {
+                float s = 0.f;
+                for (int i = threadIdx.x; i < C; i += blockDim.x) s += xr[i];
+                mean = block_sum(s, red) / float(C);
+                float sq = 0.f;
+                for (int i = threadIdx.x; i < C; i += blockDim.x) {
+                    const float d = xr[i] - mean;
+                    sq += d * d;
+                }
+                rstd = rsqrtf(block_sum(sq, red) / float(C) + eps);
+                if constexpr (MODE == 1)
+                    if (threadIdx.x == 0) row_stats[row] = make_float2(mean, rstd);
+            }
+            for (int i = threadIdx.x; i < C; i += blockDim.x) {
+                const float o = fmaf((xr[i] - mean) * rstd, gamma ? gamma[i] : 1.f, beta ? beta[i] : 0.f);
+                if constexpr (MODE == 2) {
+                    codes[size_t(row) * C + i] = uint8_t(cvt_f32x2_to_fp8x2<KIND>(__fmul_rn(o, q), 0.f) & 0xff);
+                } else {
+                    tile_amax = fmaxf(tile_amax, fabsf(o));
+                    if constexpr (MODE == 0) y[size_t(row) * C + i] = o;
+                }
+            }
+        }
+    }
+    if constexpr (MODE != 2) {
+        if (amax_out) {
+            const float m = block_max(tile_amax, red);
+            if (threadIdx.x == 0 && m > 0.f) atomic_max_nonneg(amax_out, m);
+        }
+    }
+}
+
+bool fast_ok(int C, const void* a, const void* b, const void* c, const void* d) {
+    return (C % 4 == 0) && C <= 4 * kMaxV4 * kLnThreads && aligned16(a) && aligned16(b) && aligned16(c) &&
+           aligned16(d);
+}
+
+int ln_grid(int rows) {
+    const int cap = sm_count() * 8;
+    return rows < cap ? (rows > 0 ? rows : 1) : cap;
+}
+
+}  // namespace
+}  // namespace df8
+
+using namespace df8;
+
+extern "C" df8_status df8_layernorm_f32(const float* x, int rows, int cols, const float* gamma, const float* beta,
+                                        float eps, float* y, float* amax_out, df8_stream stream) {
+    DF8_REQUIRE(rows >= 0 && cols > 0, "df8_layernorm_f32: bad shape rows=%d cols=%d", rows, cols);
+    cudaStream_t st = as_stream(stream);
+    if (amax_out) DF8_CUDA_TRY(cudaMemsetAsync(amax_out, 0, sizeof(float), st));
+    if (rows == 0) return DF8_OK;
+    DF8_REQUIRE(x && y, "df8_layernorm_f32: null buffer");
+    if (fast_ok(cols, x, y, gamma, beta))
+        layernorm_kernel<0, 0, true><<<ln_grid(rows), kLnThreads, 0, st>>>(x, rows, cols, gamma, beta, eps, y, amax_out,
+                                                                          nullptr, nullptr, nullptr, nullptr);
+    else
+        layernorm_kernel<0, 0, false><<<ln_grid(rows), kLnThreads, 0, st>>>(x, rows, cols, gamma, beta, eps, y,
+                                                                           amax_out, nullptr, nullptr, nullptr, nullptr);
+    DF8_LAUNCH_CHECK("layernorm_kernel");
+    return DF8_OK;
+}
+
+namespace {
+template <int KIND>
+df8_status launch_ln_quant(const float* x, int rows, int cols, const float* gamma, const float* beta, float eps,
+                           uint8_t* codes, float* scale_out, float* amax_out, float2* row_stats, cudaStream_t st) {
+    const int grid = ln_grid(rows);
+    if (fast_ok(cols, x, gamma, beta, nullptr) && (reinterpret_cast<uintptr_t>(codes) & 3u) == 0) {
+        layernorm_kernel<1, KIND, true><<<grid, kLnThreads, 0, st>>>(x, rows, cols, gamma, beta, eps, nullptr, amax_out,
+                                                                    row_stats, nullptr, nullptr, nullptr);
+        layernorm_kernel<2, KIND, true><<<grid, kLnThreads, 0, st>>>(x, rows, cols, gamma, beta, eps, nullptr, nullptr,
+                                                                    row_stats, amax_out, codes, scale_out);
+    } else {
+        layernorm_kernel<1, KIND, false><<<grid, kLnThreads, 0, st>>>(x, rows, cols, gamma, beta, eps, nullptr, amax_out,
+                                                                     row_stats, nullptr, nullptr, nullptr);
+        layernorm_kernel<2, KIND, false><<<grid, kLnThreads, 0, st>>>(x, rows, cols, gamma, beta, eps, nullptr, nullptr,
+                                                                     row_stats, amax_out, codes, scale_out);
+    }
+    DF8_LAUNCH_CHECK("layernorm_kernel (fused quantise)");
+    return DF8_OK;
+}
+}  // namespace
+
+extern "C" df8_status df8_layernorm_quantize_f32(const float* x, int rows, int cols, const float* gamma,
+                                                 const float* beta, float eps, df8_kind kind, uint8_t* codes_out,
+                                                 float* scale_out, float* amax_out, float* row_stats_scratch,
+                                                 df8_stream stream) {
+    DF8_REQUIRE(kind == DF8_E4M3 || kind == DF8_E5M2, "df8_layernorm_quantize_f32: unknown fp8 kind %d", int(kind));
+    DF8_REQUIRE(rows >= 0 && cols > 0, "df8_layernorm_quantize_f32: bad shape rows=%d cols=%d", rows, cols);
+    DF8_REQUIRE(amax_out && scale_out, "df8_layernorm_quantize_f32: amax_out and scale_out are required");
+    cudaStream_t st = as_stream(stream);
+    DF8_CUDA_TRY(cudaMemsetAsync(amax_out, 0, sizeof(float), st));
+    DF8_REQUIRE(rows == 0 || (x && codes_out && row_stats_scratch), "df8_layernorm_quantize_f32: null buffer");
+    DF8_REQUIRE((reinterpret_cast<uintptr_t>(row_stats_scratch) & 7u) == 0,
+                "df8_layernorm_quantize_f32: row_stats_scratch must be 8-byte aligned");
+    float2* stats = reinterpret_cast<float2*>(row_stats_scratch);
+    return kind == DF8_E4M3
+               ? launch_ln_quant<DF8_E4M3>(x, rows, cols, gamma, beta, eps, codes_out, scale_out, amax_out, stats, st)
+               : launch_ln_quant<DF8_E5M2>(x, rows, cols, gamma, beta, eps, codes_out, scale_out, amax_out, stats, st);
+}

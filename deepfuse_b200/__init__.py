@@ -41,6 +41,11 @@ _SIGNATURES = {
     "df8_quantize_f32": [_vp, _sz, _i, _vp, _vp, _vp, _vp],
     "df8_dequantize_f32": [_vp, _sz, _i, _vp, _vp, _vp],
     "df8_gemm_fp8_tn": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp],
+    "df8_layernorm_f32": [_vp, _i, _i, _vp, _vp, _f, _vp, _vp, _vp],
+    "df8_layernorm_quantize_f32": [_vp, _i, _i, _vp, _vp, _f, _i, _vp, _vp, _vp, _vp, _vp],
+    "df8_embed_pe_f32": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
+    "df8_attention_fp8": [_vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp, _vp],
+    "df8_softmax_masked_f32": [_vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "df8_status_word_read": [_vp, _vp],
     "df8_status_word_reset": [],
 }
@@ -122,3 +127,32 @@ def status_word() -> tuple[int, int]:
 
 def status_word_reset() -> None:
     check(lib().df8_status_word_reset(), "df8_status_word_reset")
+
+
+def layernorm_f32(x, rows, cols, gamma, beta, eps, y, amax_out=None, stream=None) -> None:
+    check(lib().df8_layernorm_f32(ptr(x), rows, cols, ptr(gamma), ptr(beta), eps, ptr(y), ptr(amax_out),
+                                  stream_ptr(stream)), "df8_layernorm_f32")
+
+
+def layernorm_quantize_f32(x, rows, cols, gamma, beta, eps, kind, codes_out, scale_out, amax_out, row_stats,
+                           stream=None) -> None:
+    check(lib().df8_layernorm_quantize_f32(ptr(x), rows, cols, ptr(gamma), ptr(beta), eps, kind, ptr(codes_out),
+                                           ptr(scale_out), ptr(amax_out), ptr(row_stats), stream_ptr(stream)),
+          "df8_layernorm_quantize_f32")
+
+
+def embed_pe_f32(ids, B, T, E, V, table, bias, pe, out, bad_ids=None, stream=None) -> None:
+    check(lib().df8_embed_pe_f32(ptr(ids), B, T, E, V, ptr(table), ptr(bias), ptr(pe), ptr(out), ptr(bad_ids),
+                                 stream_ptr(stream)), "df8_embed_pe_f32")
+
+
+def attention_fp8(qkv_codes, kind, scale, B, T, H, D, mask_mode, mask, out, out_amax=None, stream=None) -> None:
+    mask_b = 0 if mask is None else mask.shape[0]
+    check(lib().df8_attention_fp8(ptr(qkv_codes), kind, ptr(scale), B, T, H, D, mask_mode, ptr(mask), mask_b,
+                                  ptr(out), ptr(out_amax), stream_ptr(stream)), "df8_attention_fp8")
+
+
+def softmax_masked_f32(x, mask, B, H, T, out, stream=None) -> None:
+    mask_b = 0 if mask is None else mask.shape[0]
+    check(lib().df8_softmax_masked_f32(ptr(x), ptr(mask), mask_b, B, H, T, ptr(out), stream_ptr(stream)),
+          "df8_softmax_masked_f32")

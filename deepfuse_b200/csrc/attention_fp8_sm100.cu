@@ -1,0 +1,401 @@
+// fp8 multi-head attention for sm_100a: QK^T, online softmax and PV in one kernel, on tcgen05.
+//
+// Input is the fused QKV projection output as fp8 codes, [B*T, 3E] row-major with Q = columns [0,E),
+// K = [E,2E), V = [2E,3E) and head h = columns [hD,(h+1)D) of each — the layout upstream's
+// MultiHeadAttentionLayer builds with three slice copies and three head-split kernels
+// (dnn/layers/multi_head_attention.cu:225-260); here TMA reads every head tile in place.
+// It replaces upstream's matmul_kernel launches (:266-270, :283-287), SoftmaxLayer::forward
+// (dnn/layers/softmax_layer.cu:26-81) and the head-merge kernel (:292-294), with the intended
+// semantics (all batch-heads, scores = Q.K^T / sqrt(D)), not the launch bugs noted at :262-271.
+//
+// Softmax follows upstream exactly in form: p = exp(s + mask - rowmax) / (sum + 1e-6), and p = 0
+// where mask < -1e8.  It is evaluated blockwise (online): per 128-key block the running row maximum
+// and sum are updated and the block's probabilities multiply V on the tensor cores; the [T,T] score
+// matrix never exists in memory.  A probability (scaled by 256) is handed to the tensor core as the sum
+// of two e4m3 numbers, its rounding and the rounding of what is left, i.e. with about 7 mantissa bits:
+// a single e4m3 rounding (3 bits) leaves ~2 % error on flat attention rows, outside the 1e-2 bound.
+//
+// One CTA = one (batch, head, 128-query block).
+//   warp 0     TMA producer: Q tile once, then K/V tiles through a 2-stage ring
+//   warp 1     MMA issuer:   S = Q.K^T (M=128, N=128, K=D) and O_blk = P.V (M=128, N=D, K=128),
+//                            V consumed as an N-major operand straight from its [keys, D] tile
+//   warps 2-5  softmax:      thread = query row; tcgen05.ld of S, exp2, P -> swizzled smem as the
+//                            A operand of the PV product, running O in registers
+// All mbarrier waits are bounded (status word, see df8_status_word_read).
+#include "df8_internal.cuh"
+#include "sm100_ptx.cuh"
+#include "tensormap.cuh"
+
+namespace df8 {
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kAttnThreads = 192;
+constexpr int BQ = 128;
+constexpr int BKV = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct AttnArgs {
+    const float* scale;  // {q, dq} of the QKV codes
+    const float* mask;   // additive mask [mask_b,1,T,T] fp32 or null
+    float* out;          // [B*T, E] fp32
+    float* out_amax;     // 1 float or null
+    int B, T, H, E;
+    int mask_mode;       // 0 none, 1 causal, 2 additive tensor
+    int mask_b;
+    uint32_t idesc_qk, idesc_pv;
+    unsigned int* status;
+};
+
+template <int D>
+struct AttnCfg {
+    static constexpr int kQBytes = BQ * D;
+    static constexpr int kKBytes = BKV * D;
+    static constexpr int kStageBytes = 2 * kKBytes;  // K then V
+    static constexpr int kStages = 2;
+    static constexpr int kPBytes = 2 * BQ * BKV;  // probabilities as two e4m3 tiles: leading part + remainder
+    static constexpr int kBarBytes = 128;
+    static constexpr int kUsedBytes = kQBytes + kStages * kStageBytes + kPBytes + kBarBytes + 1024;
+    // pad the request so that at most two CTAs share an SM: each allocates 256 of the 512 TMEM columns
+    static constexpr int kSmemBytes = kUsedBytes < 100 * 1024 ? 100 * 1024 : kUsedBytes;
+    static constexpr int kTmemCols = 256;  // S: columns [0,128), O_blk: [128, 128+D)
+};
+
+__device__ __forceinline__ void record_timeout(unsigned int* status, unsigned int code) {
+    if (status) {
+        atomicCAS(status, 0u, code);
+        atomicAdd(status + 1, 1u);
+    }
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads, (D == 64 ? 2 : 1))
+attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs args) {
+    using Cfg = AttnCfg<D>;
+    constexpr int SW = D;  // swizzle width of the Q/K/V tiles = their row length in bytes
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sQ = smem;
+    uint8_t* sKV = sQ + Cfg::kQBytes;
+    uint8_t* sP = sKV + Cfg::kStages * Cfg::kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + Cfg::kPBytes);
+    uint64_t* q_full = bars;
+    uint64_t* kv_full = bars + 1;   // [2]
+    uint64_t* kv_empty = bars + 3;  // [2]
+    uint64_t* s_full = bars + 5;
+    uint64_t* s_empty = bars + 6;
+    uint64_t* p_full = bars + 7;
+    uint64_t* o_full = bars + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int qblk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int T = args.T, E = args.E;
+    const int q0 = qblk * BQ;
+    const int row_base = b * T;
+    int n_kv = (T + BKV - 1) / BKV;
+    if (args.mask_mode == 1 && qblk + 1 < n_kv) n_kv = qblk + 1;  // causal: blocks above the diagonal vanish
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(q_full), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(kv_full + s), 1);
+            mbar_init(smem_u32(kv_empty + s), 1);
+        }
+        mbar_init(smem_u32(s_full), 1);
+        mbar_init(smem_u32(s_empty), 4);
+        mbar_init(smem_u32(p_full), 4);
+        mbar_init(smem_u32(o_full), 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s = tmem_base;
+    const uint32_t tmem_o = tmem_base + 128;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            prefetch_tensormap(&tma_qkv);
+            mbar_arrive_expect_tx(smem_u32(q_full), Cfg::kQBytes);
+            tma_load_2d(smem_u32(sQ), &tma_qkv, smem_u32(q_full), h * D, row_base + q0);
+            for (int j = 0; j < n_kv; ++j) {
+                const int s = j & 1;
+                if (!mbar_wait_bounded(smem_u32(kv_empty + s), ((j >> 1) & 1) ^ 1)) {
+                    record_timeout(args.status, 0x1100u + s);
+                    break;
+                }
+                uint8_t* st = sKV + s * Cfg::kStageBytes;
+                const uint32_t fb = smem_u32(kv_full + s);
+                mbar_arrive_expect_tx(fb, Cfg::kStageBytes);
+                tma_load_2d(smem_u32(st), &tma_qkv, fb, E + h * D, row_base + j * BKV);
+                tma_load_2d(smem_u32(st + Cfg::kKBytes), &tma_qkv, fb, 2 * E + h * D, row_base + j * BKV);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            auto issue_qk = [&](int stage) {
+                const uint32_t qa = smem_u32(sQ);
+                const uint32_t ka = smem_u32(sKV + stage * Cfg::kStageBytes);
+#pragma unroll
+                for (int k = 0; k < D / 32; ++k)
+                    tc_mma_f8(tmem_s, make_desc_kmajor<SW>(qa + k * 32), make_desc_kmajor<SW>(ka + k * 32),
+                              args.idesc_qk, k != 0);
+                tc_commit(smem_u32(s_full));
+            };
+            bool ok = mbar_wait_bounded(smem_u32(q_full), 0) && mbar_wait_bounded(smem_u32(kv_full + 0), 0);
+            if (!ok) record_timeout(args.status, 0x1200u);
+            if (ok) {
+                tc_fence_after_sync();
+                issue_qk(0);
+            }
+            for (int j = 0; j < n_kv && ok; ++j) {
+                if (j + 1 < n_kv) {
+                    const int s1 = (j + 1) & 1;
+                    if (!mbar_wait_bounded(smem_u32(kv_full + s1), ((j + 1) >> 1) & 1) ||
+                        !mbar_wait_bounded(smem_u32(s_empty), j & 1)) {
+                        record_timeout(args.status, 0x1300u + s1);
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    issue_qk(s1);
+                }
+                if (!mbar_wait_bounded(smem_u32(p_full), j & 1)) {
+                    record_timeout(args.status, 0x1400u);
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t va = smem_u32(sKV + (j & 1) * Cfg::kStageBytes + Cfg::kKBytes);
+#pragma unroll
+                for (int part = 0; part < 2; ++part) {
+                    const uint32_t pa = smem_u32(sP + part * BQ * BKV);
+#pragma unroll
+                    for (int k = 0; k < BKV / 32; ++k)
+                        tc_mma_f8(tmem_o, make_desc_kmajor<128>(pa + k * 32),
+                                  make_desc_mnmajor<SW>(va + k * 32 * D, 8 * SW), args.idesc_pv, (part | k) != 0);
+                }
+                tc_commit(smem_u32(o_full));
+                tc_commit(smem_u32(kv_empty + (j & 1)));
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const int qi = q0 + row;
+        const float dq = args.scale[1];
+        const float cs = dq * dq * rsqrtf(float(D)) * kLog2e;  // raw score -> log2 domain
+        const uint32_t lane_addr = uint32_t(q * 32) << 16;
+        const float* mrow = nullptr;
+        if (args.mask_mode == 2 && qi < T)
+            mrow = args.mask + (size_t(args.mask_b > 1 ? b : 0) * T + qi) * T;
+
+        float m = -INFINITY;  // running max (log2 domain)
+        float l = 0.f;        // running sum of 256 * p
+        float acc[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) acc[d] = 0.f;
+        bool ok = true;
+
+        for (int j = 0; j < n_kv; ++j) {
+            const int k0 = j * BKV;
+            if (!mbar_wait_bounded(smem_u32(s_full), j & 1)) {
+                if (lane == 0) record_timeout(args.status, 0x1500u);
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+            const bool edge = (k0 + BKV > T) || (args.mask_mode == 1 && k0 + BKV - 1 > q0) || (args.mask_mode == 2);
+
+            auto score = [&](uint32_t raw, int kj) -> float {
+                float t = __uint_as_float(raw) * cs;
+                if (edge) {
+                    if (kj >= T) return -INFINITY;
+                    if (args.mask_mode == 1 && kj > qi) return -INFINITY;
+                    if (mrow) {
+                        const float mv = mrow[kj];
+                        if (mv < -1e8f) return -INFINITY;
+                        t = fmaf(mv, kLog2e, t);
+                    }
+                }
+                return t;
+            };
+
+            // pass 1: block row maximum
+            float mb = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < BKV / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mb = fmaxf(mb, score(r[i], k0 + c * 32 + i));
+            }
+            const float m_new = fmaxf(m, mb);
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+            const float alpha = ex2(m - m_use);  // 0 when m is still -inf
+            const float shift = m_use - 8.0f;    // p' = 256 * exp2(t - m_use)
+
+            // pass 2: probabilities -> e4m3 -> swizzled smem (A operand of the PV product)
+            float psum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < BKV / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
+                tmem_ld_wait();
+                uint32_t w[8], wl[8];
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    float p[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        p[i] = ex2(score(r[4 * g + i], k0 + c * 32 + 4 * g + i) - shift);
+                        psum += p[i];
+                    }
+                    w[g] = cvt_f32x4_to_fp8x4<DF8_E4M3>(p[0], p[1], p[2], p[3]);
+                    const float2 h01 = cvt_fp8x2_to_f32x2<DF8_E4M3>(uint16_t(w[g] & 0xffff));
+                    const float2 h23 = cvt_fp8x2_to_f32x2<DF8_E4M3>(uint16_t(w[g] >> 16));
+                    wl[g] = cvt_f32x4_to_fp8x4<DF8_E4M3>(p[0] - h01.x, p[1] - h01.y, p[2] - h23.x, p[3] - h23.y);
+                }
+                uint8_t* prow = sP + row * 128;
+                const int o0 = ((2 * c) ^ (row & 7)) << 4, o1 = ((2 * c + 1) ^ (row & 7)) << 4;
+                *reinterpret_cast<uint4*>(prow + o0) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(prow + o1) = make_uint4(w[4], w[5], w[6], w[7]);
+                *reinterpret_cast<uint4*>(prow + BQ * BKV + o0) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+                *reinterpret_cast<uint4*>(prow + BQ * BKV + o1) = make_uint4(wl[4], wl[5], wl[6], wl[7]);
+            }
+            l = fmaf(l, alpha, psum);
+            m = m_new;
+
+            // S consumed: the issuer may overwrite it with the next block's scores
+            tc_fence_before_sync();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P visible to the tensor core
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(smem_u32(s_empty));
+                mbar_arrive(smem_u32(p_full));
+            }
+
+            if (!mbar_wait_bounded(smem_u32(o_full), j & 1)) {
+                if (lane == 0) record_timeout(args.status, 0x1600u);
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_o + lane_addr + c * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(r[i]));
+            }
+            tc_fence_before_sync();
+        }
+
+        if (ok) {
+            // out = O * dq / (sum + 1e-6); O and sum both carry the factor 256
+            const float inv = dq / (l + 256.0f * 1e-6f);
+            float amax = 0.f;
+            if (qi < T) {
+                float* o = args.out + (size_t(row_base) + qi) * E + h * D;
+#pragma unroll
+                for (int d = 0; d < D; d += 4) {
+                    float4 v = make_float4(acc[d] * inv, acc[d + 1] * inv, acc[d + 2] * inv, acc[d + 3] * inv);
+                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                    *reinterpret_cast<float4*>(o + d) = v;
+                }
+            }
+            if (args.out_amax) {
+                amax = warp_max(amax);
+                if (lane == 0 && amax > 0.f) atomic_max_nonneg(args.out_amax, amax);
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+template <int D>
+df8_status launch_attention(const CUtensorMap& tm, const AttnArgs& args, dim3 grid, cudaStream_t st) {
+    using Cfg = AttnCfg<D>;
+    auto kern = attention_fp8_kernel<D>;
+    static bool configured[64] = {};
+    int dev = 0;
+    DF8_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        DF8_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        configured[dev] = true;
+    }
+    kern<<<grid, kAttnThreads, Cfg::kSmemBytes, st>>>(tm, args);
+    DF8_LAUNCH_CHECK("attention_fp8_kernel");
+    return DF8_OK;
+}
+
+}  // namespace
+}  // namespace df8
+
+using namespace df8;
+
+extern "C" df8_status df8_attention_fp8(const uint8_t* qkv_codes, df8_kind kind, const float* scale, int B, int T,
+                                        int H, int D, int mask_mode, const float* mask, int mask_b, float* out,
+                                        float* out_amax, df8_stream stream) {
+    DF8_REQUIRE(kind == DF8_E4M3 || kind == DF8_E5M2, "df8_attention_fp8: unknown fp8 kind %d", int(kind));
+    DF8_REQUIRE(B >= 0 && T >= 0 && H > 0, "df8_attention_fp8: bad shape B=%d T=%d H=%d", B, T, H);
+    DF8_REQUIRE(mask_mode >= 0 && mask_mode <= 2, "df8_attention_fp8: unknown mask mode %d", mask_mode);
+    DF8_REQUIRE(mask_mode != 2 || (mask != nullptr && (mask_b == 1 || mask_b == B)),
+                "df8_attention_fp8: additive mask must be [B,1,T,T] or [1,1,T,T]");
+    if (D != 64 && D != 128)
+        return fail(DF8_ERR_UNSUPPORTED, "df8_attention_fp8: head dimension %d not supported (64 or 128)", D);
+    cudaStream_t st = as_stream(stream);
+    if (out_amax) DF8_CUDA_TRY(cudaMemsetAsync(out_amax, 0, sizeof(float), st));
+    if (B == 0 || T == 0) return DF8_OK;
+    DF8_REQUIRE(qkv_codes && scale && out, "df8_attention_fp8: null buffer");
+    DF8_REQUIRE(aligned16(out), "df8_attention_fp8: out must be 16-byte aligned");
+    const int E = H * D;
+    const long rows = long(B) * T;
+    DF8_REQUIRE(rows < (1l << 31), "df8_attention_fp8: too many tokens");
+
+    unsigned int* status_ptr = nullptr;
+    df8_status src = status_word_device_ptr(&status_ptr);
+    if (src != DF8_OK) return src;
+
+    CUtensorMap tm;
+    df8_status rc = make_tmap_2d_u8(&tm, qkv_codes, uint64_t(rows), uint64_t(3 * E), uint64_t(3 * E), BQ, uint32_t(D), D);
+    if (rc != DF8_OK) return rc;
+
+    AttnArgs a;
+    a.scale = scale;
+    a.mask = mask;
+    a.out = out;
+    a.out_amax = out_amax;
+    a.B = B;
+    a.T = T;
+    a.H = H;
+    a.E = E;
+    a.mask_mode = mask_mode;
+    a.mask_b = mask_b;
+    a.idesc_qk = ptx::make_idesc_f8(BQ, BKV, int(kind), int(kind));
+    a.idesc_pv = ptx::make_idesc_f8(BQ, D, DF8_E4M3, int(kind), 0, 1);
+    a.status = status_ptr;
+    dim3 grid((T + BQ - 1) / BQ, H, B);
+    return D == 64 ? launch_attention<64>(tm, a, grid, st) : launch_attention<128>(tm, a, grid, st);
+}

@@ -16,6 +16,10 @@ df8_status fail(df8_status code, const char* fmt, ...);
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Device address, on the current device, of the status word that bounded device-side waits write
+// when they give up ([0] first code, [1] count).
+df8_status status_word_device_ptr(unsigned int** out);
+
 #define DF8_CUDA_TRY(expr)                                                                  \
     do {                                                                                    \
         cudaError_t err__ = (expr);                                                         \

@@ -22,8 +22,6 @@
 
 namespace df8 {
 
-__device__ unsigned int g_status_word[4];  // [0] first timeout code, [1] count
-
 namespace {
 
 using namespace ptx;
@@ -337,11 +335,9 @@ extern "C" df8_status df8_gemm_fp8_tn(const uint8_t* a_codes, df8_kind kind_a, c
     if (K % 16 != 0)
         return fail(DF8_ERR_UNSUPPORTED, "df8_gemm_fp8_tn: K=%d must be a multiple of 16 (TMA row pitch)", K);
 
-    static unsigned int* status_ptr[64] = {};
-    int dev = 0;
-    DF8_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !status_ptr[dev])
-        DF8_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status_ptr[dev]), g_status_word));
+    unsigned int* status_ptr = nullptr;
+    df8_status src = status_word_device_ptr(&status_ptr);
+    if (src != DF8_OK) return src;
 
     const int sms = sm_count();
     // tile width: the one that fills whole waves of the persistent grid best (wider tiles reuse A more)
@@ -356,9 +352,9 @@ extern "C" df8_status df8_gemm_fp8_tn(const uint8_t* a_codes, df8_kind kind_a, c
     const int grid = int(tiles < sms ? tiles : sms);
 
     CUtensorMap ta, tw;
-    df8_status rc = make_tmap_2d_u8(&ta, a_codes, uint64_t(M), uint64_t(K), uint64_t(K), BM, BK, true);
+    df8_status rc = make_tmap_2d_u8(&ta, a_codes, uint64_t(M), uint64_t(K), uint64_t(K), BM, BK, 128);
     if (rc != DF8_OK) return rc;
-    rc = make_tmap_2d_u8(&tw, w_codes, uint64_t(N), uint64_t(K), uint64_t(K), uint32_t(bn), BK, true);
+    rc = make_tmap_2d_u8(&tw, w_codes, uint64_t(N), uint64_t(K), uint64_t(K), uint32_t(bn), BK, 128);
     if (rc != DF8_OK) return rc;
 
     GemmArgs args;
@@ -373,7 +369,7 @@ extern "C" df8_status df8_gemm_fp8_tn(const uint8_t* a_codes, df8_kind kind_a, c
     args.K = K;
     args.flags = flags;
     args.idesc = ptx::make_idesc_f8(BM, bn, int(kind_a), int(kind_w));
-    args.status = (dev >= 0 && dev < 64) ? status_ptr[dev] : nullptr;
+    args.status = status_ptr;
 
     const bool vec4 = (N % 4 == 0) && aligned16(out) && (!bias || aligned16(bias)) &&
                       (!(flags & DF8_EPI_RESIDUAL) || aligned16(residual));
@@ -382,18 +378,4 @@ extern "C" df8_status df8_gemm_fp8_tn(const uint8_t* a_codes, df8_kind kind_a, c
                     : launch_gemm<256, 4, false>(ta, tw, args, grid, st);
     return vec4 ? launch_gemm<128, 6, true>(ta, tw, args, grid, st)
                 : launch_gemm<128, 6, false>(ta, tw, args, grid, st);
-}
-
-extern "C" df8_status df8_status_word_read(unsigned int* code_h, unsigned int* count_h) {
-    unsigned int w[4] = {0, 0, 0, 0};
-    DF8_CUDA_TRY(cudaMemcpyFromSymbol(w, g_status_word, sizeof(w)));
-    if (code_h) *code_h = w[0];
-    if (count_h) *count_h = w[1];
-    return DF8_OK;
-}
-
-extern "C" df8_status df8_status_word_reset(void) {
-    unsigned int w[4] = {0, 0, 0, 0};
-    DF8_CUDA_TRY(cudaMemcpyToSymbol(g_status_word, w, sizeof(w)));
-    return DF8_OK;
 }

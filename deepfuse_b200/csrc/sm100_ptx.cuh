@@ -126,17 +126,33 @@ __device__ __forceinline__ uint64_t make_desc_kmajor_sw128(uint32_t smem_addr) {
     return d;
 }
 
-// Shared-memory matrix descriptor for an MN-major operand tile with the 128-byte swizzle:
-// 128 contiguous bytes run along M/N, 8 such rows (consecutive k) form a 1024-byte atom.
-// `lbo_bytes` is the distance between atoms along M/N, `sbo_bytes` between 8-k groups.
-__device__ __forceinline__ uint64_t make_desc_mnmajor_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                            uint32_t sbo_bytes) {
+// Same K-major tile with rows of `SW` bytes (SW = 64 or 128) and the SW-byte swizzle: groups of
+// 8 rows are 8*SW bytes apart.
+template <int SW>
+__device__ __forceinline__ uint64_t make_desc_kmajor(uint32_t smem_addr) {
+    static_assert(SW == 64 || SW == 128, "swizzle width");
     uint64_t d = 0;
     d |= uint64_t((smem_addr & 0x3FFFFu) >> 4);
-    d |= uint64_t((lbo_bytes >> 4) & 0x3FFF) << 16;
-    d |= uint64_t((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= uint64_t(1) << 16;
+    d |= uint64_t((8 * SW) >> 4) << 32;
     d |= uint64_t(1) << 46;
-    d |= uint64_t(2) << 61;
+    d |= uint64_t(SW == 128 ? 2 : 4) << 61;  // layout type: 128-byte / 64-byte swizzle
+    return d;
+}
+
+// Shared-memory matrix descriptor for an MN-major operand tile with the SW-byte swizzle
+// (SW = 64 or 128): SW contiguous bytes run along M/N, 8 such rows (consecutive k) form an atom of
+// 8*SW bytes.  The stride field is the distance between 8-k groups; the leading field is the
+// distance between atoms along M/N (only used when the tile is wider than SW elements).
+template <int SW>
+__device__ __forceinline__ uint64_t make_desc_mnmajor(uint32_t smem_addr, uint32_t mn_atom_stride_bytes) {
+    static_assert(SW == 64 || SW == 128, "swizzle width");
+    uint64_t d = 0;
+    d |= uint64_t((smem_addr & 0x3FFFFu) >> 4);
+    d |= uint64_t((mn_atom_stride_bytes >> 4) & 0x3FFF) << 16;
+    d |= uint64_t((8 * SW) >> 4) << 32;
+    d |= uint64_t(1) << 46;
+    d |= uint64_t(SW == 128 ? 2 : 4) << 61;
     return d;
 }
 

@@ -25,7 +25,7 @@ EncodeFn encode_fn() {
 }  // namespace
 
 df8_status make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
-                           uint32_t box_rows, uint32_t box_cols, bool swizzle128) {
+                           uint32_t box_rows, uint32_t box_cols, int swizzle_bytes) {
     EncodeFn fn = encode_fn();
     if (!fn) return fail(DF8_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     if ((reinterpret_cast<uintptr_t>(base) & 15u) || (pitch_bytes & 15u))
@@ -35,8 +35,13 @@ df8_status make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, ui
     cuuint64_t strides[1] = {pitch_bytes};
     cuuint32_t box[2] = {box_cols, box_rows};
     cuuint32_t estr[2] = {1, 1};
+    CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_NONE;
+    if (swizzle_bytes == 32) sw = CU_TENSOR_MAP_SWIZZLE_32B;
+    else if (swizzle_bytes == 64) sw = CU_TENSOR_MAP_SWIZZLE_64B;
+    else if (swizzle_bytes == 128) sw = CU_TENSOR_MAP_SWIZZLE_128B;
+    else if (swizzle_bytes != 0) return fail(DF8_ERR_INVALID, "unsupported TMA swizzle of %d bytes", swizzle_bytes);
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(DF8_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rows %llu cols %llu pitch %llu box %ux%u)",

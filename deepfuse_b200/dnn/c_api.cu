@@ -1,0 +1,336 @@
+// C harness over the dnn:: classes (declared in include/df8_dnn.h).  Every function builds and calls
+// the C++ objects through their public members and converts exceptions into a return code.
+#include "df8_dnn.h"
+
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "dnn/core/cuda.cuh"
+#include "dnn/core/fp8.cuh"
+#include "dnn/layers/fully_connected_layer.cuh"
+#include "dnn/layers/layer_norm_layer.cuh"
+#include "dnn/layers/multi_head_attention.cuh"
+#include "dnn/layers/softmax_layer.cuh"
+#include "dnn/layers/transformer_block.cuh"
+#include "dnn/models/gpt2.cuh"
+#include "dnn/tokens/positional_encoding.cuh"
+#include "dnn/tokens/token_embedding.cuh"
+
+namespace {
+
+thread_local std::string t_error;
+thread_local std::unique_ptr<dnn::Cuda> t_context;
+
+template <typename F>
+int guarded(F&& body) {
+    try {
+        body();
+        return 0;
+    } catch (const std::invalid_argument& e) {
+        t_error = std::string("invalid_argument: ") + e.what();
+        return 2;
+    } catch (const std::out_of_range& e) {
+        t_error = std::string("out_of_range: ") + e.what();
+        return 3;
+    } catch (const std::exception& e) {
+        t_error = std::string("runtime_error: ") + e.what();
+        return 1;
+    }
+}
+
+void sync_stream() { dnn::utils::CHECK_CUDA_EX(cudaStreamSynchronize(dnn::Cuda::stream())); }
+
+struct NamedParam {
+    std::string name;
+    dnn::tensor<float>* t;
+};
+
+}  // namespace
+
+struct dnn_gpt2 {
+    std::unique_ptr<dnn::Gpt2<float>> model;
+    std::vector<NamedParam> params;
+    std::unique_ptr<dnn::tensor<float>> last;  // result of the last forward, kept alive for the caller
+    std::unique_ptr<dnn::tensor<int>> ids;
+
+    void index_params() {
+        params.clear();
+        auto add = [this](const std::string& prefix, dnn::tensor<float>* w, dnn::tensor<float>* b,
+                          const char* wn = "weight", const char* bn = "bias") {
+            params.push_back({prefix + "." + wn, w});
+            params.push_back({prefix + "." + bn, b});
+        };
+        add("embedding", model->token_embedding().weights(), model->token_embedding().bias());
+        for (int i = 0; i < model->num_layers(); ++i) {
+            auto& blk = model->block(i);
+            const std::string p = "block" + std::to_string(i);
+            auto n1 = blk.norm1().parameters();
+            auto n2 = blk.norm2().parameters();
+            add(p + ".ln1", n1[0], n1[1], "gamma", "beta");
+            add(p + ".ln2", n2[0], n2[1], "gamma", "beta");
+            add(p + ".qkv", blk.attention().qkv_projection().weights(), blk.attention().qkv_projection().bias());
+            add(p + ".out", blk.attention().out_projection().weights(), blk.attention().out_projection().bias());
+            add(p + ".fc1", blk.mlp_fc1().weights(), blk.mlp_fc1().bias());
+            add(p + ".fc2", blk.mlp_fc2().weights(), blk.mlp_fc2().bias());
+        }
+        add("final_fc", model->final_fc().weights(), model->final_fc().bias());
+    }
+};
+
+extern "C" const char* dnn_last_error(void) { return t_error.c_str(); }
+
+extern "C" int dnn_init(int device) {
+    return guarded([&] {
+        if (!t_context || t_context->id() != device) {
+            t_context.reset();
+            t_context = std::make_unique<dnn::Cuda>(device);
+        }
+    });
+}
+
+extern "C" int dnn_set_stream(void* stream) {
+    return guarded([&] { dnn::Cuda::set_stream(reinterpret_cast<cudaStream_t>(stream)); });
+}
+
+extern "C" int dnn_set_fp8_policy(int weight_kind, int activation_kind) {
+    return guarded([&] {
+        if ((weight_kind != 0 && weight_kind != 1) || (activation_kind != 0 && activation_kind != 1))
+            throw std::invalid_argument("fp8 kind must be 0 (e4m3) or 1 (e5m2)");
+        dnn::fp8::policy().weight_kind = df8_kind(weight_kind);
+        dnn::fp8::policy().activation_kind = df8_kind(activation_kind);
+    });
+}
+
+// ---- Gpt2 -------------------------------------------------------------------------------------
+
+extern "C" dnn_gpt2* dnn_gpt2_create(int vocab, int max_seq_len, int layers, int heads, int hidden, int ffn) {
+    dnn_gpt2* h = nullptr;
+    int rc = guarded([&] {
+        auto handle = std::make_unique<dnn_gpt2>();
+        handle->model = std::make_unique<dnn::Gpt2<float>>(nullptr, vocab, max_seq_len, layers, heads, hidden, ffn);
+        handle->index_params();
+        h = handle.release();
+    });
+    return rc == 0 ? h : nullptr;
+}
+
+extern "C" void dnn_gpt2_destroy(dnn_gpt2* m) {
+    guarded([&] {
+        if (m) sync_stream();
+        delete m;
+    });
+}
+
+extern "C" int dnn_gpt2_set_options(dnn_gpt2* m, int mlp_gelu, int causal) {
+    return guarded([&] {
+        m->model->set_mlp_gelu(mlp_gelu != 0);
+        m->model->set_causal(causal != 0);
+    });
+}
+
+extern "C" int dnn_gpt2_num_params(dnn_gpt2* m) { return m ? int(m->params.size()) : -1; }
+
+extern "C" int dnn_gpt2_param_info(dnn_gpt2* m, int index, char* name_h, int name_cap, int* shape_h, int* ndim_h) {
+    return guarded([&] {
+        const NamedParam& p = m->params.at(size_t(index));
+        if (name_h && name_cap > 0) std::snprintf(name_h, size_t(name_cap), "%s", p.name.c_str());
+        const auto& s = p.t->shape();
+        if (ndim_h) *ndim_h = int(s.size());
+        if (shape_h)
+            for (size_t i = 0; i < s.size() && i < 8; ++i) shape_h[i] = s[i];
+    });
+}
+
+extern "C" int dnn_gpt2_param_upload(dnn_gpt2* m, int index, const float* data_h) {
+    return guarded([&] {
+        m->params.at(size_t(index)).t->upload(data_h);
+        sync_stream();
+    });
+}
+
+extern "C" int dnn_gpt2_param_download(dnn_gpt2* m, int index, float* data_h) {
+    return guarded([&] { m->params.at(size_t(index)).t->download(data_h); });
+}
+
+extern "C" int dnn_gpt2_prepare(dnn_gpt2* m) {
+    return guarded([&] {
+        for (int i = 0; i < m->model->num_layers(); ++i) {
+            auto& blk = m->model->block(i);
+            blk.attention().qkv_projection().quantized_weights();
+            blk.attention().out_projection().quantized_weights();
+            blk.mlp_fc1().quantized_weights();
+            blk.mlp_fc2().quantized_weights();
+        }
+        m->model->final_fc().quantized_weights();
+        sync_stream();
+    });
+}
+
+namespace {
+void stage_ids(dnn_gpt2* m, const int32_t* src, int B, int T, cudaMemcpyKind kind) {
+    if (!m->ids || m->ids->shape() != std::vector<int>{B, T}) m->ids = std::make_unique<dnn::tensor<int>>(std::vector<int>{B, T});
+    dnn::utils::CHECK_CUDA_EX(cudaMemcpyAsync(m->ids->data(), src, sizeof(int32_t) * size_t(B) * size_t(T), kind,
+                                              dnn::Cuda::stream()));
+}
+}  // namespace
+
+extern "C" int dnn_gpt2_forward_logits(dnn_gpt2* m, const int32_t* ids_d, int B, int T, int check_ids,
+                                       float** logits_d) {
+    return guarded([&] {
+        stage_ids(m, ids_d, B, T, cudaMemcpyDeviceToDevice);
+        m->last.reset();  // return the previous result to the pool before allocating the next one
+        m->last = std::make_unique<dnn::tensor<float>>(m->model->forward_logits(*m->ids, check_ids != 0));
+        *logits_d = m->last->data();
+    });
+}
+
+extern "C" int dnn_gpt2_forward_logits_host(dnn_gpt2* m, const int32_t* ids_h, int B, int T, float** logits_d) {
+    return guarded([&] {
+        stage_ids(m, ids_h, B, T, cudaMemcpyHostToDevice);
+        m->last.reset();
+        m->last = std::make_unique<dnn::tensor<float>>(m->model->forward_logits(*m->ids, false));
+        *logits_d = m->last->data();
+    });
+}
+
+extern "C" int dnn_gpt2_forward_hidden(dnn_gpt2* m, const int32_t* ids_d, int B, int T, float** hidden_d) {
+    return guarded([&] {
+        stage_ids(m, ids_d, B, T, cudaMemcpyDeviceToDevice);
+        m->last.reset();
+        m->last = std::make_unique<dnn::tensor<float>>(m->model->forward_hidden(*m->ids, true));
+        *hidden_d = m->last->data();
+    });
+}
+
+extern "C" int dnn_gpt2_forward_ids(dnn_gpt2* m, const int32_t* ids_h, int T, float* hidden_h) {
+    return guarded([&] {
+        std::vector<int> ids(ids_h, ids_h + T);
+        dnn::tensor<float> hidden = m->model->forward(ids);
+        hidden.download(hidden_h);
+    });
+}
+
+extern "C" int dnn_gpt2_save(dnn_gpt2* m, const char* path) {
+    return guarded([&] { m->model->save(path); });
+}
+
+extern "C" dnn_gpt2* dnn_gpt2_load(const char* path) {
+    dnn_gpt2* h = nullptr;
+    int rc = guarded([&] {
+        auto handle = std::make_unique<dnn_gpt2>();
+        handle->model = dnn::Gpt2<float>::load(path, false);
+        handle->index_params();
+        h = handle.release();
+    });
+    return rc == 0 ? h : nullptr;
+}
+
+// ---- single layers through their public forward() ------------------------------------------------
+
+extern "C" int dnn_fc_forward(int in_features, int out_features, const float* w_h, const float* b_h,
+                              const float* x_h, int M, float* y_h) {
+    return guarded([&] {
+        dnn::FullyConnectedLayer<float> layer(in_features, out_features);
+        auto params = layer.parameters();
+        if (w_h) params[0]->upload(w_h);
+        if (b_h) params[1]->upload(b_h);
+        dnn::tensor<float> x({M, in_features});
+        x.upload(x_h);
+        dnn::tensor<float> y = layer.forward(x);
+        y.download(y_h);
+    });
+}
+
+extern "C" int dnn_layernorm_forward(int rows, int cols, const float* gamma_h, const float* beta_h, float eps,
+                                     const float* x_h, float* y_h) {
+    return guarded([&] {
+        dnn::LayerNormLayer<float> layer(cols, eps, gamma_h != nullptr);
+        if (gamma_h) {
+            auto p = layer.parameters();
+            p[0]->upload(gamma_h);
+            if (beta_h) p[1]->upload(beta_h);
+        }
+        dnn::tensor<float> x({rows, cols});
+        x.upload(x_h);
+        dnn::tensor<float> y = layer.forward(x);
+        y.download(y_h);
+    });
+}
+
+extern "C" int dnn_softmax_forward(int B, int H, int T, const float* x_h, const float* mask_h, int mask_b,
+                                   float* y_h) {
+    return guarded([&] {
+        dnn::SoftmaxLayer<float> layer;
+        dnn::tensor<float> x({B, H, T, T});
+        x.upload(x_h);
+        std::unique_ptr<dnn::tensor<float>> mask;
+        if (mask_h) {
+            mask = std::make_unique<dnn::tensor<float>>(std::vector<int>{mask_b, 1, T, T});
+            mask->upload(mask_h);
+            layer.set_mask(mask.get());
+        }
+        dnn::tensor<float> y = layer.forward(x);
+        y.download(y_h);
+    });
+}
+
+extern "C" int dnn_mha_forward(int B, int T, int E, int H, const float* wqkv_h, const float* bqkv_h,
+                               const float* wo_h, const float* bo_h, const float* x_h, int mask_mode,
+                               const float* mask_h, int mask_b, float* y_h) {
+    return guarded([&] {
+        dnn::MultiHeadAttentionLayer<float> layer(E, H);
+        layer.qkv_projection().weights()->upload(wqkv_h);
+        layer.qkv_projection().bias()->upload(bqkv_h);
+        layer.out_projection().weights()->upload(wo_h);
+        layer.out_projection().bias()->upload(bo_h);
+        std::unique_ptr<dnn::tensor<float>> mask;
+        if (mask_mode == 1) layer.set_causal(true);
+        if (mask_mode == 2) {
+            mask = std::make_unique<dnn::tensor<float>>(std::vector<int>{mask_b, 1, T, T});
+            mask->upload(mask_h);
+            layer.set_mask(mask.get());
+        }
+        dnn::tensor<float> x({B, T, E});
+        x.upload(x_h);
+        dnn::tensor<float> y = layer.forward(x);
+        y.download(y_h);
+    });
+}
+
+extern "C" int dnn_embedding_forward(int V, int E, int max_len, const float* table_h, const float* bias_h,
+                                     const int32_t* ids_h, int B, int T, int add_positions, float* y_h) {
+    return guarded([&] {
+        dnn::TokenEmbedding<float> emb(V, E, max_len);
+        if (table_h) emb.weights()->upload(table_h);
+        if (bias_h) emb.bias()->upload(bias_h);
+        dnn::tensor<int> ids({B, T});
+        ids.upload(ids_h);
+        dnn::tensor<float> x = emb.forward(ids);
+        if (add_positions) {
+            dnn::PositionalEncoding<float> pe(E, max_len);
+            x = pe.forward(x);
+        }
+        x.download(y_h);
+    });
+}
+
+// One TransformerBlock through its public forward(); params in the order of TransformerBlock::parameters()
+// (ln1 g,b; ln2 g,b; qkv W,b; out W,b; fc1 W,b; fc2 W,b), each a host array.
+extern "C" int dnn_block_forward(int B, int T, int E, int H, int F, const float* const* params_h, int n_params,
+                                 int mlp_gelu, int causal, const float* x_h, float* y_h) {
+    return guarded([&] {
+        dnn::TransformerBlock<float> block(E, H, F);
+        auto params = block.parameters();
+        if (int(params.size()) != n_params) throw std::invalid_argument("dnn_block_forward: expected 12 parameter arrays");
+        for (int i = 0; i < n_params; ++i) params[size_t(i)]->upload(params_h[i]);
+        block.set_mlp_gelu(mlp_gelu != 0);
+        block.set_causal(causal != 0);
+        dnn::tensor<float> x({B, T, E});
+        x.upload(x_h);
+        dnn::tensor<float> y = block.forward(x);
+        y.download(y_h);
+    });
+}

@@ -1,0 +1,48 @@
+// fp8 execution policy and small helpers shared by the dnn:: layers.
+//
+// Upstream names the fp8 element kinds only as tensor storage types (dnn/core/tensor.cu:489-498) and has
+// no quantised layer; this header is where the new build states how the fp32 layer API maps onto the
+// 8-bit kernels: every fully-connected layer keeps its fp32 weights (the API-visible tensors) and a
+// cached per-tensor-quantised copy; activations are quantised per tensor right before each GEMM /
+// attention call.
+#pragma once
+
+#include <cstdint>
+#include <vector>
+
+#include "df8.h"
+#include "dnn/core/cuda.cuh"
+#include "dnn/core/tensor.cuh"
+#include "dnn/utils/common.cuh"
+
+namespace dnn {
+namespace fp8 {
+
+struct Policy {
+    df8_kind weight_kind = DF8_E4M3;
+    df8_kind activation_kind = DF8_E4M3;
+};
+
+// Process-wide policy read by layers at forward time.
+Policy& policy();
+
+// Codes + {q, dq} scale + amax of one per-tensor-quantised activation or weight.
+struct Quantized {
+    tensor<uint8_t> codes;
+    tensor<float> scale;  // {q, dq}
+    tensor<float> amax;   // 1 element
+    df8_kind kind = DF8_E4M3;
+    explicit Quantized(size_t n = 0)
+        : codes({int(n)}), scale({2}), amax({1}) {}
+};
+
+inline df8_stream stream() { return reinterpret_cast<df8_stream>(Cuda::stream()); }
+
+// q <- per-tensor quantisation of n fp32 values at x (amax pass + quantise pass).
+void quantize(const float* x, size_t n, df8_kind kind, Quantized& q);
+
+// Same, when max|x| is already known on the device (a fused epilogue produced it).
+void quantize_with_amax(const float* x, size_t n, df8_kind kind, const float* amax, Quantized& q);
+
+}  // namespace fp8
+}  // namespace dnn

@@ -1,0 +1,109 @@
+#include "dnn/layers/fully_connected_layer.cuh"
+
+#include <cmath>
+#include <random>
+#include <stdexcept>
+#include <vector>
+
+namespace dnn {
+
+template <typename TT>
+FullyConnectedLayer<TT>::FullyConnectedLayer(int in_features, int out_features, bool training_enabled)
+    : LayerWeightBias<TT>(tensor<TT>({out_features, in_features}), tensor<TT>({1, out_features, 1, 1}),
+                          tensor<TT>({out_features, in_features}), tensor<TT>({1, out_features, 1, 1}),
+                          training_enabled),
+      in_features_(in_features),
+      out_features_(out_features) {
+    if (in_features <= 0 || out_features <= 0)
+        throw std::invalid_argument("FullyConnectedLayer: feature counts must be positive");
+    initialize_weights();
+    this->grad_weights_.zero();
+    this->grad_bias_.zero();
+}
+
+template <typename TT>
+FullyConnectedLayer<TT>::~FullyConnectedLayer() = default;
+
+// Xavier-uniform weights in [-sqrt(6/(in+out)), +sqrt(6/(in+out))], zero bias — the distribution
+// upstream draws (fully_connected_layer.cu:359-385), from a fixed-seed generator instead of
+// std::random_device so that a run is reproducible.
+template <typename TT>
+void FullyConnectedLayer<TT>::initialize_weights() {
+    const float limit = std::sqrt(6.0f / float(in_features_ + out_features_));
+    std::mt19937 gen(0x5EED0000u + unsigned(in_features_) * 31u + unsigned(out_features_));
+    std::uniform_real_distribution<float> dist(-limit, limit);
+    std::vector<TT> host(this->weights_.numel());
+    for (auto& v : host) v = static_cast<TT>(dist(gen));
+    this->weights_.upload(host.data());
+    utils::CHECK_CUDA_EX(cudaStreamSynchronize(Cuda::stream()));
+    this->bias_.zero();
+}
+
+template <typename TT>
+const fp8::Quantized& FullyConnectedLayer<TT>::quantized_weights() {
+    if (wq_version_ != this->weights_.version()) {
+        fp8::quantize(this->weights_.data(), this->weights_.numel(), fp8::policy().weight_kind, wq_);
+        wq_version_ = this->weights_.version();
+    }
+    return wq_;
+}
+
+template <typename TT>
+void FullyConnectedLayer<TT>::forward_codes(const uint8_t* a_codes, df8_kind a_kind, const float* a_scale, int M,
+                                            int flags, const float* residual, float* out, float* out_amax) {
+    const fp8::Quantized& w = quantized_weights();
+    utils::CHECK_DF8(df8_gemm_fp8_tn(a_codes, a_kind, a_scale, w.codes.data(), w.kind, w.scale.data(),
+                                     this->bias_.data(), residual, M, out_features_, in_features_, flags, out,
+                                     out_amax, fp8::stream()));
+}
+
+template <typename TT>
+tensor<TT> FullyConnectedLayer<TT>::forward(const tensor<TT>& input) {
+    const auto& shape = input.shape();
+    if (shape.empty() || input.numel() % size_t(in_features_) != 0 || shape.back() != in_features_)
+        throw std::runtime_error("FullyConnectedLayer::forward: input's last dimension must be in_features");
+    if (this->training_enabled_) input_cache_ = input.clone();
+    const int M = int(input.numel() / size_t(in_features_));
+    std::vector<int> out_shape(shape.begin(), shape.end() - 1);
+    out_shape.push_back(out_features_);
+    tensor<TT> output(out_shape);
+    fp8::quantize(input.data(), input.numel(), fp8::policy().activation_kind, xq_);
+    forward_codes(xq_.codes.data(), xq_.kind, xq_.scale.data(), M, 0, nullptr, output.data(), nullptr);
+    return output;
+}
+
+// The backward pass (upstream fc_backward_* kernels, fully_connected_layer.cu:43-107) is training-side
+// and outside this build; the error upstream raises when no forward input was cached is kept.
+template <typename TT>
+tensor<TT> FullyConnectedLayer<TT>::backward(const tensor<TT>& /*grad_output*/) {
+    if (!input_cache_.has_value())
+        throw std::runtime_error("FullyConnectedLayer::backward: no cached input (training disabled or forward not run)");
+    throw std::runtime_error("FullyConnectedLayer::backward: the fp8 inference build has no backward pass");
+}
+
+// Stream layout shared with upstream (fully_connected_layer.cu:387-401): in, out, weights, bias.
+template <typename TT>
+void FullyConnectedLayer<TT>::save(std::ostream& out) const {
+    out.write(reinterpret_cast<const char*>(&in_features_), sizeof(in_features_));
+    out.write(reinterpret_cast<const char*>(&out_features_), sizeof(out_features_));
+    this->weights_.save(out);
+    this->bias_.save(out);
+}
+
+template <typename TT>
+void FullyConnectedLayer<TT>::load(std::istream& in) {
+    int in_f = 0, out_f = 0;
+    in.read(reinterpret_cast<char*>(&in_f), sizeof(in_f));
+    in.read(reinterpret_cast<char*>(&out_f), sizeof(out_f));
+    if (!in || in_f <= 0 || out_f <= 0) throw std::runtime_error("FullyConnectedLayer::load: bad header");
+    in_features_ = in_f;
+    out_features_ = out_f;
+    this->weights_.load(in);
+    this->bias_.load(in);
+    this->grad_weights_ = tensor<TT>({out_f, in_f});
+    this->grad_bias_ = tensor<TT>({1, out_f, 1, 1});
+}
+
+template class FullyConnectedLayer<float>;
+
+}  // namespace dnn

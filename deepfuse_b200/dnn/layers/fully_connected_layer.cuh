@@ -1,0 +1,57 @@
+// FullyConnectedLayer<TT>: Y[N,out] = X[N,in] . W[out,in]^T + b, on the fp8 tensor-core GEMM.
+//
+// Public surface of upstream dnn/layers/fully_connected_layer.cuh:22-52 (constructor
+// (in_features, out_features, training_enabled), forward, backward, name() == "FullyConnected",
+// initialize_weights, save, load, plus weights()/bias()/parameters() from LayerWeightBias), weights
+// [out,in] row-major and bias shaped {1,out,1,1} as upstream allocates them
+// (dnn/layers/fully_connected_layer.cu:110-151).
+//
+// forward() quantises the fp32 input per tensor (policy().activation_kind), multiplies it with the
+// cached per-tensor e4m3 copy of the weights in df8_gemm_fp8_tn and returns fp32 — in place of
+// upstream's one-thread-per-output fp32 kernel (fully_connected_layer.cu:15-41, :199-208).
+// The cached weight codes are refreshed whenever the fp32 weight tensor's version() changes.
+#pragma once
+
+#include <iostream>
+#include <optional>
+#include <string>
+
+#include "dnn/core/fp8.cuh"
+#include "dnn/core/layer.cuh"
+#include "dnn/core/tensor.cuh"
+
+namespace dnn {
+
+template <typename TT>
+class FullyConnectedLayer : public LayerWeightBias<TT> {
+public:
+    FullyConnectedLayer(int in_features, int out_features, bool training_enabled = false);
+    ~FullyConnectedLayer() override;
+
+    tensor<TT> forward(const tensor<TT>& input) override;
+    tensor<TT> backward(const tensor<TT>& grad_output) override;
+    std::string name() const override { return "FullyConnected"; }
+    void initialize_weights() override;
+    void save(std::ostream& out) const override;
+    void load(std::istream& in) override;
+
+    int in_features() const { return in_features_; }
+    int out_features() const { return out_features_; }
+
+    // ---- fp8 path (additions; upstream has no counterpart) ----
+    // Per-tensor quantised weights, refreshed if the fp32 weights changed since the last call.
+    const fp8::Quantized& quantized_weights();
+    // out[M,out] = epilogue(codes . Wq^T); `flags` are DF8_EPI_* bits; out_amax may be null.
+    void forward_codes(const uint8_t* a_codes, df8_kind a_kind, const float* a_scale, int M, int flags,
+                       const float* residual, float* out, float* out_amax);
+
+private:
+    int in_features_;
+    int out_features_;
+    std::optional<tensor<TT>> input_cache_;
+    fp8::Quantized wq_;
+    uint64_t wq_version_ = ~0ull;
+    fp8::Quantized xq_;  // reused activation buffer
+};
+
+}  // namespace dnn

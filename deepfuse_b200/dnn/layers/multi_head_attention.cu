@@ -1,0 +1,116 @@
+#include "dnn/layers/multi_head_attention.cuh"
+
+#include <stdexcept>
+
+namespace dnn {
+
+template <typename TT>
+MultiHeadAttentionLayer<TT>::MultiHeadAttentionLayer(int embed_dim, int num_heads, bool training_enabled)
+    : Layer<TT>(training_enabled),
+      embed_dim_(embed_dim),
+      num_heads_(num_heads),
+      head_dim_(num_heads > 0 ? embed_dim / num_heads : 0),
+      use_mask_(false),
+      qkv_proj_(embed_dim > 0 ? embed_dim : 1, embed_dim > 0 ? 3 * embed_dim : 1, training_enabled),
+      out_proj_(embed_dim > 0 ? embed_dim : 1, embed_dim > 0 ? embed_dim : 1, training_enabled),
+      softmax_(training_enabled),
+      last_q_({1, 1}),
+      last_attn_({1, 1}),
+      qkv_f32_({1}),
+      attn_f32_({1}),
+      amax_({1}) {
+    if (embed_dim <= 0 || num_heads <= 0) throw std::runtime_error("embed_dim and num_heads must be positive");
+    if (embed_dim % num_heads != 0) throw std::runtime_error("embed_dim must be divisible by num_heads");
+}
+
+template <typename TT>
+MultiHeadAttentionLayer<TT>::~MultiHeadAttentionLayer() = default;
+
+template <typename TT>
+void MultiHeadAttentionLayer<TT>::set_mask(tensor<TT>* mask) {
+    if (mask && (mask->shape().size() != 4 || mask->shape()[1] != 1))
+        throw std::runtime_error("Mask must be 4D tensor with shape [B, 1, T, T]");
+    softmax_.set_mask(mask);
+    use_mask_ = mask != nullptr;
+}
+
+template <typename TT>
+void MultiHeadAttentionLayer<TT>::initialize_weights() {
+    qkv_proj_.initialize_weights();
+    out_proj_.initialize_weights();
+}
+
+template <typename TT>
+void MultiHeadAttentionLayer<TT>::forward_quantized(const fp8::Quantized& xq, int B, int T, const float* residual,
+                                                    float* out) {
+    const int M = B * T, E = embed_dim_;
+    const df8_kind act = fp8::policy().activation_kind;
+    if (qkv_f32_.numel() != size_t(M) * 3 * E) qkv_f32_ = tensor<float>({M, 3 * E});
+    if (attn_f32_.numel() != size_t(M) * E) attn_f32_ = tensor<float>({M, E});
+
+    // QKV projection, its max|.| reduced in the GEMM epilogue, then one quantise pass
+    qkv_proj_.forward_codes(xq.codes.data(), xq.kind, xq.scale.data(), M, DF8_EPI_AMAX, nullptr, qkv_f32_.data(),
+                            amax_.data());
+    fp8::quantize_with_amax(qkv_f32_.data(), qkv_f32_.numel(), act, amax_.data(), qkvq_);
+
+    int mode = causal_ ? DF8_MASK_CAUSAL : DF8_MASK_NONE;
+    const float* mask_ptr = nullptr;
+    int mask_b = 0;
+    if (tensor<TT>* m = softmax_.mask()) {
+        const auto& ms = m->shape();
+        if (ms[2] != T || ms[3] != T || (ms[0] != B && ms[0] != 1))
+            throw std::runtime_error("Mask must be 4D tensor with shape [B, 1, T, T]");
+        mode = DF8_MASK_ADDITIVE;
+        mask_ptr = m->data();
+        mask_b = ms[0];
+    }
+    utils::CHECK_DF8(df8_attention_fp8(qkvq_.codes.data(), qkvq_.kind, qkvq_.scale.data(), B, T, num_heads_, head_dim_,
+                                       mode, mask_ptr, mask_b, attn_f32_.data(), amax_.data(), fp8::stream()));
+    fp8::quantize_with_amax(attn_f32_.data(), attn_f32_.numel(), act, amax_.data(), attnq_);
+    out_proj_.forward_codes(attnq_.codes.data(), attnq_.kind, attnq_.scale.data(), M,
+                            residual ? DF8_EPI_RESIDUAL : 0, residual, out, nullptr);
+}
+
+template <typename TT>
+tensor<TT> MultiHeadAttentionLayer<TT>::forward(const tensor<TT>& input) {
+    const auto& shape = input.shape();
+    if (shape.size() != 3) throw std::runtime_error("Input tensor must be 3D [B, T, E]");
+    if (shape[2] != embed_dim_) throw std::runtime_error("Input tensor's last dimension must equal embed_dim");
+    if (this->training_enabled_) input_cache_ = input.clone();
+    const int B = shape[0], T = shape[1];
+    fp8::quantize(input.data(), input.numel(), fp8::policy().activation_kind, xq_);
+    tensor<TT> out(shape);
+    forward_quantized(xq_, B, T, nullptr, out.data());
+    return out;
+}
+
+// Upstream's backward is an identity stub (multi_head_attention.cu:310-319); kept.
+template <typename TT>
+tensor<TT> MultiHeadAttentionLayer<TT>::backward(const tensor<TT>& grad_output) {
+    return grad_output.clone();
+}
+
+template <typename TT>
+void MultiHeadAttentionLayer<TT>::save(std::ostream& out) const {
+    out.write(reinterpret_cast<const char*>(&embed_dim_), sizeof(embed_dim_));
+    out.write(reinterpret_cast<const char*>(&num_heads_), sizeof(num_heads_));
+    qkv_proj_.save(out);
+    out_proj_.save(out);
+}
+
+template <typename TT>
+void MultiHeadAttentionLayer<TT>::load(std::istream& in) {
+    int e = 0, h = 0;
+    in.read(reinterpret_cast<char*>(&e), sizeof(e));
+    in.read(reinterpret_cast<char*>(&h), sizeof(h));
+    if (!in || e <= 0 || h <= 0 || e % h != 0) throw std::runtime_error("MultiHeadAttentionLayer::load: bad header");
+    embed_dim_ = e;
+    num_heads_ = h;
+    head_dim_ = e / h;
+    qkv_proj_.load(in);
+    out_proj_.load(in);
+}
+
+template class MultiHeadAttentionLayer<float>;
+
+}  // namespace dnn

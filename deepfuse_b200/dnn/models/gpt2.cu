@@ -1,0 +1,149 @@
+#include "dnn/models/gpt2.cuh"
+
+#include <fstream>
+#include <random>
+
+namespace dnn {
+
+template <typename T>
+Gpt2<T>::Gpt2(std::shared_ptr<Tokenizer> tokenizer, int vocab_size, int max_seq_len, int num_layers, int num_heads,
+              int hidden_dim, int intermediate_dim, T /*learning_rate*/, T /*beta1*/, T /*beta2*/, T /*epsilon*/,
+              bool training_enabled)
+    : NaturalLanguageModel<T>(std::move(tokenizer), max_seq_len, training_enabled),
+      vocab_size_(vocab_size),
+      max_seq_len_(max_seq_len),
+      hidden_dim_(hidden_dim) {
+    token_embedding_ = std::make_unique<TokenEmbedding<T>>(vocab_size, hidden_dim, max_seq_len, training_enabled);
+    initialize_weights(token_embedding_->weights(), static_cast<T>(0.02f));
+    positional_encoding_ = std::make_unique<PositionalEncoding<T>>(hidden_dim, max_seq_len, training_enabled);
+    for (int i = 0; i < num_layers; ++i) {
+        auto block = std::make_unique<TransformerBlock<T>>(hidden_dim, num_heads, intermediate_dim, training_enabled);
+        block->set_mlp_gelu(true);
+        transformer_blocks_.push_back(std::move(block));
+    }
+    final_fc_ = std::make_unique<FullyConnectedLayer<T>>(hidden_dim, vocab_size, training_enabled);
+    initialize_weights(final_fc_->weights(), static_cast<T>(0.02f));
+}
+
+template <typename T>
+std::string Gpt2<T>::name() const {
+    return "Gpt2";
+}
+
+// N(0, scale) from a fixed-seed generator (upstream draws from std::random_device, gpt2.cu:204-214).
+template <typename T>
+void Gpt2<T>::initialize_weights(tensor<T>* weights, T scale) {
+    std::mt19937 gen(0x69D72000u + unsigned(weights->numel() % 0xFFFFu));
+    std::normal_distribution<float> dist(0.0f, float(scale));
+    std::vector<T> host(weights->numel());
+    for (auto& v : host) v = static_cast<T>(dist(gen));
+    weights->upload(host.data());
+    utils::CHECK_CUDA_EX(cudaStreamSynchronize(Cuda::stream()));
+}
+
+template <typename T>
+void Gpt2<T>::train_step(const tensor<T>&, const tensor<T>&) {
+    throw std::runtime_error("Use token-based train_step for NLP models.");
+}
+
+template <typename T>
+void Gpt2<T>::train_step(const std::vector<int>&, const std::vector<int>&) {
+    throw std::runtime_error("Gpt2::train_step: training (loss, backward, optimiser) is outside the fp8 inference build");
+}
+
+template <typename T>
+tensor<T> Gpt2<T>::forward(const tensor<T>&) {
+    throw std::runtime_error("Use token-based forward for NLP models.");
+}
+
+template <typename T>
+tensor<T> Gpt2<T>::forward(const std::vector<int>& input_token_ids) {
+    tensor<int> ids({1, int(input_token_ids.size())});
+    ids.upload(input_token_ids.data());
+    return forward_hidden(ids);
+}
+
+template <typename T>
+tensor<T> Gpt2<T>::forward_hidden(const tensor<int>& ids, bool check_ids) {
+    const auto& s = ids.shape();
+    if (s.size() != 2) throw std::runtime_error("Gpt2 expects token ids shaped [B, T]");
+    const int B = s[0], T_len = s[1];
+    if (T_len > positional_encoding_->max_seq_len())
+        throw std::runtime_error("Input sequence length exceeds maximum allowed length");
+    tensor<T> x = token_embedding_->forward_with_positions(ids, positional_encoding_->table().data(), check_ids);
+    for (auto& block : transformer_blocks_) block->forward_inplace(x.data(), B, T_len);
+    return x;
+}
+
+template <typename T>
+tensor<T> Gpt2<T>::forward_logits(const tensor<int>& ids, bool check_ids) {
+    tensor<T> x = forward_hidden(ids, check_ids);
+    const int M = int(x.numel() / size_t(hidden_dim_));
+    fp8::quantize(x.data(), x.numel(), fp8::policy().activation_kind, head_q_);
+    tensor<T> logits({M, vocab_size_});
+    final_fc_->forward_codes(head_q_.codes.data(), head_q_.kind, head_q_.scale.data(), M, 0, nullptr, logits.data(),
+                             nullptr);
+    return logits;
+}
+
+template <typename T>
+void Gpt2<T>::set_mlp_gelu(bool on) {
+    for (auto& b : transformer_blocks_) b->set_mlp_gelu(on);
+}
+
+template <typename T>
+void Gpt2<T>::set_causal(bool causal) {
+    for (auto& b : transformer_blocks_) b->set_causal(causal);
+}
+
+template <typename T>
+std::vector<BaseLayer*> Gpt2<T>::layers() {
+    std::vector<BaseLayer*> all;
+    all.push_back(token_embedding_.get());
+    all.push_back(positional_encoding_.get());
+    for (auto& b : transformer_blocks_) all.push_back(b.get());
+    all.push_back(final_fc_.get());
+    return all;
+}
+
+// Container written here: the four header ints upstream writes (vocab, max_seq_len, layer count, hidden
+// dim; gpt2.cu:148-152) followed by the heads and MLP width upstream's loader hard-codes (:179), then each
+// layer's own save() stream in execution order.  Upstream's file additionally interleaves the tokenizer
+// state and raw layer-name bytes that its own loader cannot read back (:153-187).
+template <typename T>
+void Gpt2<T>::save(const std::string& path) const {
+    std::ofstream out(path, std::ios::binary);
+    if (!out) throw std::runtime_error("Failed to open file for saving Gpt2");
+    const int num_layers = int(transformer_blocks_.size());
+    out.write(reinterpret_cast<const char*>(&vocab_size_), sizeof(int));
+    out.write(reinterpret_cast<const char*>(&max_seq_len_), sizeof(int));
+    out.write(reinterpret_cast<const char*>(&num_layers), sizeof(int));
+    out.write(reinterpret_cast<const char*>(&hidden_dim_), sizeof(int));
+    const int heads = transformer_blocks_.empty() ? 0 : transformer_blocks_[0]->attention().num_heads();
+    const int ffn = transformer_blocks_.empty() ? 0 : transformer_blocks_[0]->mlp_fc1().out_features();
+    out.write(reinterpret_cast<const char*>(&heads), sizeof(int));
+    out.write(reinterpret_cast<const char*>(&ffn), sizeof(int));
+    token_embedding_->save(out);
+    for (const auto& b : transformer_blocks_) b->save(out);
+    final_fc_->save(out);
+}
+
+template <typename T>
+std::unique_ptr<Gpt2<T>> Gpt2<T>::load(const std::string& path, bool training_enabled) {
+    std::ifstream in(path, std::ios::binary);
+    if (!in) throw std::runtime_error("Failed to open file for loading Gpt2");
+    int v = 0, t = 0, l = 0, e = 0, h = 0, f = 0;
+    for (int* p : {&v, &t, &l, &e, &h, &f}) in.read(reinterpret_cast<char*>(p), sizeof(int));
+    if (!in || v <= 0 || t <= 0 || l < 0 || e <= 0 || h <= 0 || f <= 0)
+        throw std::runtime_error("Gpt2::load: bad header");
+    auto model = std::make_unique<Gpt2<T>>(nullptr, v, t, l, h, e, f, static_cast<T>(1e-4), static_cast<T>(0.9),
+                                           static_cast<T>(0.98), static_cast<T>(1e-8), training_enabled);
+    model->token_embedding_->load(in);
+    for (auto& b : model->transformer_blocks_) b->load(in);
+    model->final_fc_->load(in);
+    return model;
+}
+
+template class Gpt2<float>;
+
+}  // namespace dnn

@@ -1,0 +1,82 @@
+// Gpt2<T>: token embedding -> sinusoidal positions -> N pre-LayerNorm transformer blocks -> vocabulary head.
+//
+// Public surface of upstream dnn/models/gpt2.cuh:20-58: the constructor (tokenizer, vocab_size,
+// max_seq_len, num_layers, num_heads, hidden_dim, intermediate_dim, learning_rate, beta1, beta2, epsilon,
+// training_enabled) with upstream's defaults, name() == "Gpt2", forward(token ids) returning the hidden
+// states [1,T,E] of a single sequence (dnn/models/gpt2.cu:126-142), forward(tensor)/train_step(tensor,
+// tensor) throwing "Use token-based ..." (:52-55, :121-124), layers() (:194-202), save/load.
+// Wiring as upstream: no final LayerNorm, no mask handed to the blocks.
+//
+// Additions for batched fp8 inference (upstream's forward is batch-1 and stops before the head; its
+// train_step composes the same pieces up to the logits, :66-83):
+//   forward_logits(ids [B,T])   -> fp32 logits [B*T, V]   (embedding -> PE -> blocks -> final_fc)
+//   forward_hidden(ids [B,T])   -> hidden states [B,T,E]
+//   set_mlp_gelu / set_causal   forwarded to every block (GELU is ON by default for this model: GPT-2's MLP
+//                               uses it, although upstream's block has no activation)
+//   enable_layer_streaming(...) block weights live as fp8 codes in pinned host memory and are uploaded
+//                               layer by layer on a side stream while the previous layers compute
+#pragma once
+
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "dnn/layers/fully_connected_layer.cuh"
+#include "dnn/layers/transformer_block.cuh"
+#include "dnn/models/natural_language_model.cuh"
+#include "dnn/tokens/positional_encoding.cuh"
+#include "dnn/tokens/token_embedding.cuh"
+#include "dnn/tokens/tokenizer.cuh"
+
+namespace dnn {
+
+template <typename T>
+class Gpt2 : public NaturalLanguageModel<T> {
+public:
+    Gpt2(std::shared_ptr<Tokenizer> tokenizer, int vocab_size = 50257, int max_seq_len = 1024, int num_layers = 12,
+         int num_heads = 12, int hidden_dim = 768, int intermediate_dim = 3072, T learning_rate = static_cast<T>(1e-4),
+         T beta1 = static_cast<T>(0.9), T beta2 = static_cast<T>(0.98), T epsilon = static_cast<T>(1e-8),
+         bool training_enabled = false);
+
+    std::string name() const override;
+
+    void train_step(const tensor<T>& input, const tensor<T>& target) override;
+    void train_step(const std::vector<int>& input_token_ids, const std::vector<int>& target_token_ids);
+
+    tensor<T> forward(const tensor<T>& input) override;
+    tensor<T> forward(const std::vector<int>& input_token_ids);
+
+    void save(const std::string& path) const override;
+    static std::unique_ptr<Gpt2<T>> load(const std::string& path, bool training_enabled);
+
+    std::vector<BaseLayer*> layers() override;
+
+    // ---- batched fp8 inference ----
+    tensor<T> forward_hidden(const tensor<int>& ids, bool check_ids = true);
+    tensor<T> forward_logits(const tensor<int>& ids, bool check_ids = true);
+    void set_mlp_gelu(bool on);
+    void set_causal(bool causal);
+
+    int vocab_size() const { return vocab_size_; }
+    int hidden_dim() const { return hidden_dim_; }
+    int num_layers() const { return int(transformer_blocks_.size()); }
+    TokenEmbedding<T>& token_embedding() { return *token_embedding_; }
+    PositionalEncoding<T>& positional_encoding() { return *positional_encoding_; }
+    TransformerBlock<T>& block(int i) { return *transformer_blocks_.at(size_t(i)); }
+    FullyConnectedLayer<T>& final_fc() { return *final_fc_; }
+
+private:
+    void initialize_weights(tensor<T>* weights, T scale);
+
+    int vocab_size_;
+    int max_seq_len_;
+    int hidden_dim_;
+    std::unique_ptr<TokenEmbedding<T>> token_embedding_;
+    std::unique_ptr<PositionalEncoding<T>> positional_encoding_;
+    std::vector<std::unique_ptr<TransformerBlock<T>>> transformer_blocks_;
+    std::unique_ptr<FullyConnectedLayer<T>> final_fc_;
+    fp8::Quantized head_q_;
+};
+
+}  // namespace dnn

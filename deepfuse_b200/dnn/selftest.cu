@@ -1,0 +1,374 @@
+// Self tests of the dnn:: class API, written in C++ because they exercise C++-only behaviour (move
+// semantics, exception types, thread-local contexts).  They restate, with fixed inputs, the cases of the
+// upstream project's own unit tests: tests/core/tensor_test.cu:22-414, tests/core/cuda_test.cu:45-172 and
+// the EXPECT_THROW cases of tests/layers/*_test.cu and tests/tokens/*_test.cu.  Each function returns the
+// number of failed checks and writes a line per failure into the report buffer.
+#include "df8_dnn.h"
+
+#include <cmath>
+#include <cstdio>
+#include <functional>
+#include <sstream>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "dnn/core/cuda.cuh"
+#include "dnn/layers/fully_connected_layer.cuh"
+#include "dnn/layers/layer_norm_layer.cuh"
+#include "dnn/layers/multi_head_attention.cuh"
+#include "dnn/layers/softmax_layer.cuh"
+#include "dnn/layers/transformer_block.cuh"
+#include "dnn/models/gpt2.cuh"
+#include "dnn/tokens/positional_encoding.cuh"
+#include "dnn/tokens/token_embedding.cuh"
+
+namespace {
+
+struct Report {
+    int failures = 0;
+    int checks = 0;
+    std::ostringstream text;
+    void check(bool ok, const char* what, int line) {
+        ++checks;
+        if (!ok) {
+            ++failures;
+            text << "FAILED line " << line << ": " << what << "\n";
+        }
+    }
+    int finish(char* out, int cap) {
+        text << checks << " checks, " << failures << " failed\n";
+        if (out && cap > 0) std::snprintf(out, size_t(cap), "%s", text.str().c_str());
+        return failures;
+    }
+};
+
+#define CHECK(r, cond) (r).check((cond), #cond, __LINE__)
+
+template <typename E>
+bool throws(const std::function<void()>& f) {
+    try {
+        f();
+    } catch (const E&) {
+        return true;
+    } catch (...) {
+        return false;
+    }
+    return false;
+}
+
+std::vector<float> iota_f(size_t n, float start = 0.f) {
+    std::vector<float> v(n);
+    for (size_t i = 0; i < n; ++i) v[i] = start + float(i);
+    return v;
+}
+
+template <typename T>
+std::vector<T> to_host(const dnn::tensor<T>& t) {
+    std::vector<T> h(t.numel());
+    t.download(h.data());
+    return h;
+}
+
+void ensure_context(std::unique_ptr<dnn::Cuda>& holder) {
+    try {
+        dnn::Cuda::current();
+    } catch (const std::runtime_error&) {
+        holder = std::make_unique<dnn::Cuda>(0);
+    }
+}
+
+}  // namespace
+
+extern "C" int dnn_selftest_tensor(char* report_h, int cap) {
+    Report r;
+    std::unique_ptr<dnn::Cuda> ctx;
+    try {
+        ensure_context(ctx);
+        using dnn::tensor;
+        // construction, shape, size (tensor_test.cu: constructor / shape cases)
+        tensor<float> a({2, 3, 4});
+        CHECK(r, a.size() == 24 && a.shape().size() == 3 && a.size(0) == 2 && a.size(2) == 4);
+        CHECK(r, throws<std::out_of_range>([&] { a.size(3); }));
+        CHECK(r, throws<std::out_of_range>([&] { a.size(-1); }));
+        // upload / download round trip
+        auto src = iota_f(24);
+        a.upload(src.data());
+        CHECK(r, to_host(a) == src);
+        // fill / zero
+        tensor<float> f({5});
+        f.fill(2.5f);
+        CHECK(r, to_host(f) == std::vector<float>(5, 2.5f));
+        f.zero();
+        CHECK(r, to_host(f) == std::vector<float>(5, 0.f));
+        // reshape keeps data, rejects a different element count with both shapes in the text
+        a.reshape({6, 4});
+        CHECK(r, a.shape() == std::vector<int>({6, 4}) && to_host(a) == src);
+        bool msg_ok = false;
+        try {
+            a.reshape({5, 5});
+        } catch (const std::runtime_error& e) {
+            const std::string m = e.what();
+            msg_ok = m.find("[6, 4]") != std::string::npos && m.find("[5, 5]") != std::string::npos;
+        }
+        CHECK(r, msg_ok);
+        // move construction / assignment leave the source empty
+        tensor<float> b(std::move(a));
+        CHECK(r, b.size() == 24 && a.size() == 0 && a.data() == nullptr);
+        tensor<float> c({1});
+        c = std::move(b);
+        CHECK(r, c.size() == 24 && b.data() == nullptr && to_host(c) == src);
+        // clone is deep
+        tensor<float> d = c.clone();
+        d.fill(1.f);
+        CHECK(r, to_host(c) == src);
+        // operator+ and += ; mismatched shapes throw runtime_error
+        tensor<float> x({2, 2}), y({2, 2});
+        std::vector<float> xv{1, 2, 3, 4}, yv{10, 20, 30, 40};
+        x.upload(xv.data());
+        y.upload(yv.data());
+        tensor<float> z = x + y;
+        CHECK(r, to_host(z) == std::vector<float>({11, 22, 33, 44}));
+        x += y;
+        CHECK(r, to_host(x) == std::vector<float>({11, 22, 33, 44}));
+        tensor<float> w({4});
+        CHECK(r, throws<std::runtime_error>([&] { x += w; }));
+        CHECK(r, throws<std::runtime_error>([&] { tensor<float> q = x + w; }));
+        // equals / approx_equal / operator==
+        CHECK(r, x.equals(z));
+        y.upload(std::vector<float>({11, 22, 33, 44.00001f}).data());
+        CHECK(r, !x.equals(y) && x.approx_equal(y, 1e-3f) && !x.approx_equal(y, 1e-7f));
+        auto mask = to_host(x == y);
+        CHECK(r, mask == std::vector<uint8_t>({1, 1, 1, 0}));
+        CHECK(r, !x.equals(w));
+        // narrow / slice along each dim
+        tensor<float> n({2, 3, 4});
+        n.upload(src.data());
+        tensor<float> n1 = n.clone();
+        n1.narrow(1, 1, 2);
+        CHECK(r, n1.shape() == std::vector<int>({2, 2, 4}));
+        CHECK(r, to_host(n1) == std::vector<float>({4, 5, 6, 7, 8, 9, 10, 11, 16, 17, 18, 19, 20, 21, 22, 23}));
+        tensor<float> n2 = n.clone();
+        n2.slice(2, 1, 3);
+        CHECK(r, n2.shape() == std::vector<int>({2, 3, 2}) && to_host(n2)[0] == 1.f && to_host(n2)[11] == 22.f);
+        CHECK(r, throws<std::invalid_argument>([&] { n.clone().narrow(3, 0, 1); }));
+        CHECK(r, throws<std::invalid_argument>([&] { n.clone().narrow(1, 2, 2); }));
+        CHECK(r, throws<std::invalid_argument>([&] { n.clone().slice(0, 1, 1); }));
+        // the Q/K/V split of a [B,T,3,E] projection as upstream's attention does it (slice along dim 2)
+        tensor<float> qkv({1, 2, 3, 2});
+        qkv.upload(iota_f(12).data());
+        tensor<float> kpart = qkv.clone();
+        kpart.slice(2, 1, 2).reshape({1, 2, 2});
+        CHECK(r, to_host(kpart) == std::vector<float>({2, 3, 8, 9}));
+        // transpose (2-D), permute (general), bad permutations
+        tensor<float> t2({2, 3});
+        t2.upload(iota_f(6).data());
+        t2.transpose();
+        CHECK(r, t2.shape() == std::vector<int>({3, 2}) && to_host(t2) == std::vector<float>({0, 3, 1, 4, 2, 5}));
+        tensor<float> p({2, 3, 4});
+        p.upload(src.data());
+        p.permute({2, 0, 1});
+        auto ph = to_host(p);
+        bool perm_ok = p.shape() == std::vector<int>({4, 2, 3});
+        for (int i = 0; i < 4 && perm_ok; ++i)
+            for (int j = 0; j < 2; ++j)
+                for (int k = 0; k < 3; ++k) perm_ok &= ph[size_t((i * 2 + j) * 3 + k)] == src[size_t((j * 3 + k) * 4 + i)];
+        CHECK(r, perm_ok);
+        tensor<float> nchw({1, 2, 2, 2});
+        nchw.upload(iota_f(8).data());
+        nchw.transpose();  // channel-first -> channel-last, batch kept in front
+        CHECK(r, nchw.shape() == std::vector<int>({1, 2, 2, 2}) &&
+                     to_host(nchw) == std::vector<float>({0, 4, 1, 5, 2, 6, 3, 7}));
+        CHECK(r, throws<std::invalid_argument>([&] { p.permute({0, 1}); }));
+        CHECK(r, throws<std::invalid_argument>([&] { p.permute({0, 0, 1}); }));
+        // save / load round trip in the upstream stream layout: int ndim, int shape[], raw data
+        std::stringstream ss;
+        c.save(ss);
+        CHECK(r, ss.str().size() == sizeof(int) * 4 + sizeof(float) * 24);
+        tensor<float> l({1});
+        l.load(ss);
+        CHECK(r, l.shape() == c.shape() && l.equals(c));
+        // other element types
+        tensor<int> ti({3});
+        std::vector<int> iv{7, -1, 3};
+        ti.upload(iv.data());
+        CHECK(r, to_host(ti) == iv);
+        tensor<uint8_t> tu({4});
+        tu.fill(0x7E);
+        CHECK(r, to_host(tu) == std::vector<uint8_t>(4, 0x7E));
+        tensor<__half> th({2});
+        th.fill(__float2half(1.5f));
+        CHECK(r, __half2float(to_host(th)[1]) == 1.5f);
+        // version() moves on every content change (what the fp8 weight cache keys on)
+        const uint64_t v0 = c.version();
+        c.fill(0.f);
+        CHECK(r, c.version() != v0);
+        // empty tensor
+        tensor<float> e({0, 4});
+        CHECK(r, e.size() == 0 && e.clone().size() == 0);
+        CHECK(r, !c.to_string().empty());
+    } catch (const std::exception& e) {
+        r.check(false, e.what(), __LINE__);
+    }
+    return r.finish(report_h, cap);
+}
+
+// Context and stream semantics (upstream tests/core/cuda_test.cu:45-172).
+extern "C" int dnn_selftest_context(char* report_h, int cap) {
+    Report r;
+    try {
+        using dnn::Cuda;
+        // a fresh thread has no current instance; constructing one makes it current; nesting restores
+        std::thread([&r] {
+            CHECK(r, throws<std::runtime_error>([] { Cuda::current(); }));
+            {
+                Cuda outer(0);
+                CHECK(r, &Cuda::current() == &outer && outer.id() == 0);
+                {
+                    Cuda inner(0);
+                    CHECK(r, &Cuda::current() == &inner);
+                }
+                CHECK(r, &Cuda::current() == &outer);
+            }
+            CHECK(r, throws<std::runtime_error>([] { Cuda::current(); }));
+            CHECK(r, throws<std::runtime_error>([] { Cuda bad(9999); }));
+            CHECK(r, throws<std::runtime_error>([] { Cuda bad(-1); }));
+        }).join();
+        // per-thread contexts are independent
+        Cuda* seen[2] = {nullptr, nullptr};
+        std::thread t0([&] {
+            Cuda c(0);
+            seen[0] = &Cuda::current();
+        });
+        std::thread t1([&] {
+            Cuda c(0);
+            seen[1] = &Cuda::current();
+        });
+        t0.join();
+        t1.join();
+        CHECK(r, seen[0] != nullptr && seen[1] != nullptr && seen[0] != seen[1]);
+        CHECK(r, !Cuda::get_devices().empty() && Cuda::get_devices()[0].architecture() == "Blackwell");
+        // stream TLS + StreamGuard
+        std::thread([&r] {
+            Cuda c(0);
+            CHECK(r, Cuda::stream() == cudaStreamLegacy);
+            cudaStream_t s1 = nullptr, s2 = nullptr;
+            cudaStreamCreate(&s1);
+            cudaStreamCreate(&s2);
+            Cuda::set_stream(s1);
+            CHECK(r, Cuda::stream() == s1);
+            {
+                dnn::StreamGuard g(s2);
+                CHECK(r, Cuda::stream() == s2);
+                // work issued inside the guard runs on s2
+                dnn::tensor<float> t({1024});
+                t.fill(3.f);
+                std::vector<float> h(1024);
+                t.download(h.data());
+                CHECK(r, h[1023] == 3.f);
+            }
+            CHECK(r, Cuda::stream() == s1);
+            std::thread([&r] { CHECK(r, Cuda::stream() == cudaStreamLegacy); }).join();  // TLS: not inherited
+            Cuda::set_stream(cudaStreamLegacy);
+            cudaStreamDestroy(s1);
+            cudaStreamDestroy(s2);
+            std::ostringstream os;
+            c.dump_info(os);
+            CHECK(r, os.str().find("Device 0") != std::string::npos);
+        }).join();
+    } catch (const std::exception& e) {
+        r.check(false, e.what(), __LINE__);
+    }
+    return r.finish(report_h, cap);
+}
+
+// Error behaviour of the layers (the EXPECT_THROW cases of upstream's layer, token and model tests).
+extern "C" int dnn_selftest_errors(char* report_h, int cap) {
+    Report r;
+    std::unique_ptr<dnn::Cuda> ctx;
+    try {
+        ensure_context(ctx);
+        using namespace dnn;
+        // MultiHeadAttention: constructor checks (multi_head_attention_test.cu:101) and input rank / mask shape
+        CHECK(r, throws<std::runtime_error>([] { MultiHeadAttentionLayer<float> m(10, 3); }));
+        CHECK(r, throws<std::runtime_error>([] { MultiHeadAttentionLayer<float> m(0, 1); }));
+        CHECK(r, throws<std::runtime_error>([] { MultiHeadAttentionLayer<float> m(64, -1); }));
+        {
+            MultiHeadAttentionLayer<float> m(64, 1);
+            CHECK(r, m.embed_dim() == 64 && m.num_heads() == 1 && m.head_dim() == 64 && m.name() == "MultiHeadAttention");
+            tensor<float> bad({4, 64});
+            CHECK(r, throws<std::runtime_error>([&] { m.forward(bad); }));
+            tensor<float> mask3({1, 4, 4});
+            CHECK(r, throws<std::runtime_error>([&] { m.set_mask(&mask3); }));
+            tensor<float> mask_h2({1, 2, 4, 4});
+            CHECK(r, throws<std::runtime_error>([&] { m.set_mask(&mask_h2); }));
+            CHECK(r, m.get_q_weights()->shape() == std::vector<int>({192, 64}));
+        }
+        // TransformerBlock: input rank -> runtime_error, mask shape -> invalid_argument
+        {
+            TransformerBlock<float> b(64, 1, 128);
+            tensor<float> bad({4, 64});
+            CHECK(r, throws<std::runtime_error>([&] { b.forward(bad); }));
+            tensor<float> mask3({1, 4, 4});
+            CHECK(r, throws<std::invalid_argument>([&] { b.set_mask(&mask3); }));
+            CHECK(r, b.name() == "TransformerBlock" && b.parameters().size() == 12);
+        }
+        // Softmax: non-4-D input (softmax_layer_test.cu:267-280)
+        {
+            SoftmaxLayer<float> s;
+            tensor<float> bad({2, 4, 8});
+            CHECK(r, throws<std::runtime_error>([&] { s.forward(bad); }));
+            CHECK(r, s.name() == "Softmax");
+        }
+        // FullyConnected: shapes of parameters (fully_connected_layer_test.cu:84-104), backward without cache
+        {
+            FullyConnectedLayer<float> fc(4, 3, true);
+            auto p = fc.parameters();
+            CHECK(r, p.size() == 2 && p[0]->shape() == std::vector<int>({3, 4}) && p[1]->shape()[1] == 3);
+            CHECK(r, fc.name() == "FullyConnected");
+            tensor<float> g({1, 3});
+            CHECK(r, throws<std::runtime_error>([&] { fc.backward(g); }));
+            tensor<float> bad({2, 5});
+            CHECK(r, throws<std::runtime_error>([&] { fc.forward(bad); }));
+        }
+        // TokenEmbedding / PositionalEncoding constructor arguments and id / length checks
+        CHECK(r, throws<std::invalid_argument>([] { TokenEmbedding<float> e(0, 8); }));
+        CHECK(r, throws<std::invalid_argument>([] { TokenEmbedding<float> e(8, -1); }));
+        CHECK(r, throws<std::invalid_argument>([] { TokenEmbedding<float> e(8, 8, 0); }));
+        CHECK(r, throws<std::invalid_argument>([] { PositionalEncoding<float> p(0, 8); }));
+        CHECK(r, throws<std::invalid_argument>([] { PositionalEncoding<float> p(8, 0); }));
+        {
+            TokenEmbedding<float> e(10, 8, 4);
+            tensor<int> ids({1, 3});
+            std::vector<int> good{0, 9, 5}, bad_hi{0, 10, 5}, bad_lo{-1, 2, 3};
+            ids.upload(good.data());
+            tensor<float> out = e.forward(ids);
+            CHECK(r, out.shape() == std::vector<int>({1, 3, 8}));
+            ids.upload(bad_hi.data());
+            CHECK(r, throws<std::runtime_error>([&] { e.forward(ids); }));
+            ids.upload(bad_lo.data());
+            CHECK(r, throws<std::runtime_error>([&] { e.forward(ids); }));
+            tensor<int> too_long({1, 5});
+            too_long.zero();
+            CHECK(r, throws<std::runtime_error>([&] { e.forward(too_long); }));
+            tensor<int> rank1({3});
+            CHECK(r, throws<std::runtime_error>([&] { e.forward(rank1); }));
+        }
+        // Gpt2: tensor-based entry points refuse (gpt2.cu:52-55, :121-124); token-based forward returns [1,T,E]
+        {
+            Gpt2<float> model(nullptr, 50, 16, 1, 1, 64, 128);
+            tensor<float> t({1, 4});
+            CHECK(r, throws<std::runtime_error>([&] { model.forward(t); }));
+            CHECK(r, throws<std::runtime_error>([&] { model.train_step(t, t); }));
+            CHECK(r, model.name() == "Gpt2" && model.layers().size() == 4);
+            tensor<float> hidden = model.forward(std::vector<int>{1, 2, 3, 4, 5, 6, 7, 8});
+            CHECK(r, hidden.shape() == std::vector<int>({1, 8, 64}));
+            CHECK(r, throws<std::runtime_error>([&] { model.forward(std::vector<int>{1, 99}); }));
+            CHECK(r, throws<std::runtime_error>([&] { model.forward(std::vector<int>(17, 1)); }));
+            CHECK(r, throws<std::runtime_error>([&] { Gpt2<float>::load("/nonexistent/model.bin", false); }));
+        }
+    } catch (const std::exception& e) {
+        r.check(false, e.what(), __LINE__);
+    }
+    return r.finish(report_h, cap);
+}

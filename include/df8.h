@@ -94,6 +94,60 @@ df8_status df8_gemm_fp8_tn(const uint8_t* a_codes, df8_kind kind_a, const float*
                            const float* bias, const float* residual, int M, int N, int K, int flags,
                            float* out, float* out_amax, df8_stream stream);
 
+/* ---- fp8 attention -------------------------------------------------------------------------
+ * Replaces, inside MultiHeadAttentionLayer::forward (dnn/layers/multi_head_attention.cu:204-308), the
+ * Q/K/V slice + head-split copies (:231-260), both matmul_kernel launches (:266-270, :283-287),
+ * SoftmaxLayer::forward (dnn/layers/softmax_layer.cu:141-171) and the head merge (:292-294).
+ *   qkv_codes  [B*T, 3E] fp8 codes of the fused QKV projection (E = H*D; Q | K | V column blocks,
+ *              head h at columns [hD,(h+1)D) of each), one per-tensor scale
+ *   out        [B*T, E] fp32:  softmax(Q.K^T / sqrt(D) + mask) . V, heads merged back
+ *   softmax    p = exp(s - rowmax) / (sum + 1e-6), and p = 0 where mask < -1e8 (softmax_layer.cu:26-81)
+ *   mask_mode  DF8_MASK_NONE, DF8_MASK_CAUSAL (the -1e9-above-the-diagonal mask upstream's tests build,
+ *              tests/layers/multi_head_attention_test.cu:50-70) or DF8_MASK_ADDITIVE with
+ *              mask = fp32 [mask_b,1,T,T], mask_b == B or 1 (what set_mask receives, :190-196)
+ *   out_amax   optional: max|out| (cleared by the call)
+ * D must be 64 or 128. */
+enum { DF8_MASK_NONE = 0, DF8_MASK_CAUSAL = 1, DF8_MASK_ADDITIVE = 2 };
+
+df8_status df8_attention_fp8(const uint8_t* qkv_codes, df8_kind kind, const float* scale, int B, int T,
+                             int H, int D, int mask_mode, const float* mask, int mask_b, float* out,
+                             float* out_amax, df8_stream stream);
+
+/* ---- stand-alone masked softmax ------------------------------------------------------------
+ * Replaces the launch of softmax_masked_kernel (dnn/layers/softmax_layer.cu:26-81, launched at
+ * :154-167) for SoftmaxLayer::forward: x [B,H,T,T] fp32, optional additive mask [mask_b,1,T,T]
+ * (mask_b == B or 1), out = exp(x+mask-rowmax)/(sum+1e-6), 0 where mask < -1e8. Any T. */
+df8_status df8_softmax_masked_f32(const float* x, const float* mask, int mask_b, int B, int H, int T,
+                                  float* out, df8_stream stream);
+
+/* ---- LayerNorm ---------------------------------------------------------------------------
+ * Replaces the launch of layer_norm_forward_kernel (dnn/layers/layer_norm_layer.cu:25-63, launched
+ * at :74-79): per row over the last dimension, mean, biased variance by a second pass,
+ * y = (x-mean)*rsqrt(var+eps)*gamma + beta.  gamma / beta may be NULL (no affine).
+ * amax_out (optional) receives max|y| over the whole tensor (cleared by the call). */
+df8_status df8_layernorm_f32(const float* x, int rows, int cols, const float* gamma, const float* beta,
+                             float eps, float* y, float* amax_out, df8_stream stream);
+
+/* LayerNorm fused with the per-tensor quantiser: codes_out = fp8(LN(x) * q), q from max|LN(x)|.
+ * The fp32 LayerNorm output is never written.  row_stats_scratch: 2*rows floats of scratch
+ * (8-byte aligned) for the per-row mean and rstd between the two passes.
+ * Writes amax_out[0] and scale_out = {q, dq}. */
+df8_status df8_layernorm_quantize_f32(const float* x, int rows, int cols, const float* gamma,
+                                      const float* beta, float eps, df8_kind kind, uint8_t* codes_out,
+                                      float* scale_out, float* amax_out, float* row_stats_scratch,
+                                      df8_stream stream);
+
+/* ---- token embedding + positional encoding -----------------------------------------------
+ * Replaces embedding_forward_kernel (dnn/tokens/token_embedding.cu:31-45, launched at :146-154) and
+ * add_positional_encodings_kernel (dnn/tokens/positional_encoding.cu:31-48, launched at :94-104):
+ *     out[b,t,:] = table[ids[b,t],:] + bias[:] + pe[t,:]
+ * ids [B,T] int32, table [V,E], bias [E] or NULL, pe [>=T,E] or NULL, out [B,T,E].
+ * An id outside [0,V) yields a zero row and increments bad_ids[0] (optional, cleared by the call);
+ * upstream throws for such ids (token_embedding.cu:131-138) and the C++ layer above does too. */
+df8_status df8_embed_pe_f32(const int32_t* ids, int B, int T, int E, int V, const float* table,
+                            const float* bias, const float* pe, float* out, int32_t* bad_ids,
+                            df8_stream stream);
+
 /* ---- bounded-wait status word --------------------------------------------------------------
  * Every device-side wait (mbarrier polls in the GEMM and attention pipelines) gives up after a
  * time limit instead of hanging the GPU; the first such event stores a non-zero code.  Upstream

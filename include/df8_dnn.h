@@ -1,0 +1,77 @@
+/*
+ * df8_dnn.h — C harness over the C++17 `dnn::` classes (libdf8_dnn.so).
+ *
+ * The product API for C++ callers is the class interface under deepfuse_b200/dnn (the same class and
+ * member names as the upstream project's dnn/core, dnn/layers, dnn/tokens, dnn/models).  This header
+ * exists so that a non-C++ host (the Python tests and bench.py) can drive those classes: every function
+ * constructs / calls the C++ objects and converts exceptions into a non-zero return code whose text is
+ * available from dnn_last_error().  Pointers ending in `_h` are HOST pointers, `_d` DEVICE pointers.
+ */
+#ifndef DF8_DNN_H_
+#define DF8_DNN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct dnn_gpt2 dnn_gpt2;
+
+const char* dnn_last_error(void);
+
+/* Creates the calling thread's dnn::Cuda context for `device` (dnn/core/cuda.cuh) if there is none. */
+int dnn_init(int device);
+/* dnn::Cuda::set_stream for the calling thread; stream is a cudaStream_t. */
+int dnn_set_stream(void* stream);
+/* fp8 kinds (0 = e4m3, 1 = e5m2) used for weights and for activations. */
+int dnn_set_fp8_policy(int weight_kind, int activation_kind);
+
+/* ---- dnn::Gpt2<float> ---- */
+dnn_gpt2* dnn_gpt2_create(int vocab, int max_seq_len, int layers, int heads, int hidden, int ffn);
+void dnn_gpt2_destroy(dnn_gpt2* m);
+int dnn_gpt2_set_options(dnn_gpt2* m, int mlp_gelu, int causal);
+/* Parameters in a fixed order: embedding {weights,bias}; per block {ln1 g,b; ln2 g,b; qkv W,b; out W,b;
+ * fc1 W,b; fc2 W,b}; final_fc {W,b}.  name_h receives e.g. "block3.fc1.weight". */
+int dnn_gpt2_num_params(dnn_gpt2* m);
+int dnn_gpt2_param_info(dnn_gpt2* m, int index, char* name_h, int name_cap, int* shape_h, int* ndim_h);
+int dnn_gpt2_param_upload(dnn_gpt2* m, int index, const float* data_h);
+int dnn_gpt2_param_download(dnn_gpt2* m, int index, float* data_h);
+/* Quantises every weight now (otherwise it happens lazily in the first forward). */
+int dnn_gpt2_prepare(dnn_gpt2* m);
+/* logits [B*T, vocab] fp32 stay on the device, owned by the handle until the next forward;
+ * ids are int32 on the device (ids_d) or on the host (ids_h, uploaded inside the call). */
+int dnn_gpt2_forward_logits(dnn_gpt2* m, const int32_t* ids_d, int B, int T, int check_ids, float** logits_d);
+int dnn_gpt2_forward_logits_host(dnn_gpt2* m, const int32_t* ids_h, int B, int T, float** logits_d);
+/* hidden states [B,T,E] of Gpt2::forward_hidden, device pointer owned by the handle */
+int dnn_gpt2_forward_hidden(dnn_gpt2* m, const int32_t* ids_d, int B, int T, float** hidden_d);
+/* the model's own public batch-1 entry point, Gpt2::forward(std::vector<int>): hidden [1,T,E] to host */
+int dnn_gpt2_forward_ids(dnn_gpt2* m, const int32_t* ids_h, int T, float* hidden_h);
+int dnn_gpt2_save(dnn_gpt2* m, const char* path);
+dnn_gpt2* dnn_gpt2_load(const char* path);
+
+/* ---- single layers through their public forward(), host buffers in and out ---- */
+int dnn_fc_forward(int in_features, int out_features, const float* w_h, const float* b_h, const float* x_h, int M,
+                   float* y_h);
+int dnn_layernorm_forward(int rows, int cols, const float* gamma_h, const float* beta_h, float eps, const float* x_h,
+                          float* y_h);
+int dnn_softmax_forward(int B, int H, int T, const float* x_h, const float* mask_h, int mask_b, float* y_h);
+/* params: qkv W [3E,E], b [3E]; out W [E,E], b [E]; mask_mode 0 none, 1 causal flag, 2 additive tensor */
+int dnn_mha_forward(int B, int T, int E, int H, const float* wqkv_h, const float* bqkv_h, const float* wo_h,
+                    const float* bo_h, const float* x_h, int mask_mode, const float* mask_h, int mask_b, float* y_h);
+/* one TransformerBlock; params_h: 12 host arrays in the order ln1 g,b; ln2 g,b; qkv W,b; out W,b; fc1 W,b; fc2 W,b */
+int dnn_block_forward(int B, int T, int E, int H, int F, const float* const* params_h, int n_params, int mlp_gelu,
+                      int causal, const float* x_h, float* y_h);
+int dnn_embedding_forward(int V, int E, int max_len, const float* table_h, const float* bias_h, const int32_t* ids_h,
+                          int B, int T, int add_positions, float* y_h);
+
+/* ---- self tests written in C++ against the class API (tensor, Cuda/StreamGuard, error behaviour);
+ * return the number of failed checks and write a report to report_h. ---- */
+int dnn_selftest_tensor(char* report_h, int cap);
+int dnn_selftest_context(char* report_h, int cap);
+int dnn_selftest_errors(char* report_h, int cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DF8_DNN_H_ */

@@ -1,0 +1,121 @@
+"""GPU parity of the fp8 attention kernel (df8_attention_fp8) against the CPU oracle.
+
+Tolerance: max |y - y_ref| / max |y_ref| <= 1e-2 per output tensor, y_ref = the oracle's attention on the
+dequantised Q, K, V with double accumulation and an unquantised softmax.  The kernel rounds the block
+probabilities to e4m3 before the PV product, which is where the difference comes from."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def rel_err(y, ref):
+    return float(np.abs(y.astype(np.float64) - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+def describe(y, ref):
+    d = np.abs(y.astype(np.float64) - ref) / max(np.abs(ref).max(), 1e-30)
+    bad = d > TOL
+    rows = np.where(bad.any(axis=1))[0]
+    cols = np.where(bad.any(axis=0))[0]
+    return (f"rel_err {d.max():.3e}; {bad.sum()}/{bad.size} bad; rows {rows[:10]}({rows.size}) cols {cols[:10]}"
+            f"({cols.size}); y[0,:4]={y[0, :4]} ref[0,:4]={ref[0, :4]} nan={np.isnan(y).sum()}")
+
+
+def run_attention(df8, oracle, dev, B, T, H, D, kind=0, mask_mode=0, mask=None, seed=0, std=1.0):
+    import torch
+
+    E = H * D
+    qkv = oracle.fill_normal(B * T * 3 * E, seed=seed, std=std).reshape(B * T, 3 * E)
+    codes, s = oracle.quantize(qkv, kind)
+    out = torch.full((B * T, E), float("nan"), device=dev)
+    amax = torch.full((1,), -1.0, device=dev)
+    md = None if mask is None else torch.from_numpy(mask).to(dev)
+    df8.attention_fp8(torch.from_numpy(codes).to(dev), kind, torch.from_numpy(s).to(dev), B, T, H, D, mask_mode, md,
+                      out, amax)
+    torch.cuda.synchronize()
+    ref = oracle.attention_fp8(codes, kind, s[1], B, T, H, D, mask_mode, mask)
+    return out.cpu().numpy(), ref, amax.item()
+
+
+@pytest.mark.parametrize("B,T,H,D", [(1, 128, 1, 64), (2, 256, 3, 64), (1, 128, 1, 128), (2, 384, 2, 128),
+                                     (1, 100, 2, 64), (3, 200, 1, 64), (1, 1, 1, 64), (1, 513, 2, 128)])
+def test_attention_unmasked(df8, oracle, cuda, B, T, H, D):
+    y, ref, amax = run_attention(df8, oracle, cuda, B, T, H, D, seed=B + T + H + D)
+    assert rel_err(y, ref) <= TOL, describe(y, ref)
+    assert amax == np.abs(y).max()
+    assert df8.status_word() == (0, 0)
+
+
+@pytest.mark.parametrize("B,T,H,D", [(2, 256, 2, 64), (1, 200, 1, 64), (1, 384, 2, 128)])
+def test_attention_causal(df8, oracle, cuda, B, T, H, D):
+    y, ref, _ = run_attention(df8, oracle, cuda, B, T, H, D, mask_mode=1, seed=5)
+    assert rel_err(y, ref) <= TOL, describe(y, ref)
+    # the first query of every sequence attends to itself only: out == V[0]
+    assert df8.status_word() == (0, 0)
+
+
+def test_attention_additive_mask_matches_causal_flag(df8, oracle, cuda):
+    """The additive -1e9 mask upstream's tests build (multi_head_attention_test.cu:50-70) must give what the
+    causal flag gives, both for a per-batch [B,1,T,T] and a broadcast [1,1,T,T] mask."""
+    B, T, H, D = 2, 160, 2, 64
+    i, j = np.meshgrid(np.arange(T), np.arange(T), indexing="ij")
+    m1 = np.where(j <= i, 0.0, -1e9).astype(np.float32)[None, None]
+    y_flag, ref, _ = run_attention(df8, oracle, cuda, B, T, H, D, mask_mode=1, seed=9)
+    y_b1, _, _ = run_attention(df8, oracle, cuda, B, T, H, D, mask_mode=2, mask=m1, seed=9)
+    y_bb, _, _ = run_attention(df8, oracle, cuda, B, T, H, D, mask_mode=2, mask=np.repeat(m1, B, axis=0), seed=9)
+    assert np.array_equal(y_flag, y_b1) and np.array_equal(y_flag, y_bb)
+    assert rel_err(y_flag, ref) <= TOL
+
+
+def test_attention_soft_additive_mask_and_fully_masked_rows(df8, oracle, cuda):
+    B, T, H, D = 1, 96, 1, 64
+    rng = np.random.default_rng(3)
+    mask = rng.standard_normal((1, 1, T, T)).astype(np.float32)
+    mask[0, 0, 5, :] = -1e9   # a fully masked query row -> zeros (softmax_layer.cu:75-80)
+    mask[0, 0, :, 7] = -1e9   # a key nobody may attend to
+    y, ref, _ = run_attention(df8, oracle, cuda, B, T, H, D, mask_mode=2, mask=mask, seed=13)
+    assert rel_err(y, ref) <= TOL, describe(y, ref)
+    assert not y[5].any()
+
+
+@pytest.mark.parametrize("kind", [0, 1])
+def test_attention_kinds_and_peaked_scores(df8, oracle, cuda, kind):
+    """Larger activations make the softmax peaked (few dominant keys): the hard case for e4m3 probabilities."""
+    y, ref, _ = run_attention(df8, oracle, cuda, 1, 256, 2, 64, kind=kind, seed=17, std=3.0)
+    assert rel_err(y, ref) <= (TOL if kind == 0 else 2.5e-2), describe(y, ref)
+
+
+def test_attention_gpt2_small_shape_sampled(df8, oracle, cuda):
+    """B=8, T=1024, H=12, D=64 (GPT-2 small): the full tensor against the oracle for two batch rows' worth of
+    heads would take minutes on CPU, so batch 0 is checked in full through a B=1 call on the same data and the
+    B=8 call must reproduce it bit for bit (sequences are independent)."""
+    import torch
+
+    B, T, H, D = 8, 1024, 12, 64
+    E = H * D
+    qkv = oracle.fill_normal(B * T * 3 * E, seed=23).reshape(B * T, 3 * E)
+    codes, s = oracle.quantize(qkv, 0)
+    cd, sd = torch.from_numpy(codes).to(cuda), torch.from_numpy(s).to(cuda)
+    out = torch.empty((B * T, E), device=cuda)
+    df8.attention_fp8(cd, 0, sd, B, T, H, D, 0, None, out)
+    out1 = torch.empty((T, E), device=cuda)
+    df8.attention_fp8(cd[3 * T:4 * T].contiguous(), 0, sd, 1, T, H, D, 0, None, out1)
+    assert torch.equal(out[3 * T:4 * T], out1)
+    ref = oracle.attention_fp8(codes[3 * T:4 * T], 0, s[1], 1, T, H, D)
+    y = out1.cpu().numpy()
+    assert rel_err(y, ref) <= TOL, describe(y, ref)
+    assert df8.status_word() == (0, 0)
+
+
+def test_attention_rejects_bad_arguments(df8, cuda):
+    import torch
+
+    c = torch.zeros(128 * 3 * 96, dtype=torch.uint8, device=cuda)
+    s = torch.ones(2, device=cuda)
+    out = torch.zeros(128 * 96, device=cuda)
+    with pytest.raises(df8.Df8Error, match="head dimension"):
+        df8.attention_fp8(c, 0, s, 1, 128, 3, 32, 0, None, out)
+    with pytest.raises(df8.Df8Error, match="mask"):
+        df8.attention_fp8(c, 0, s, 1, 128, 1, 64, 2, None, out)

@@ -6,6 +6,9 @@
 Prints ONE JSON line (rank 0).  A "step" is one pass of the hot path over one batch of seeded
 synthetic input.  Workloads:
 
+  gpt2s   (default) GPT-2 small fp8 forward, 12 layers, d_model 768, batch 8x1024 token ids per GPU -> fp32
+          logits through dnn::Gpt2; tokens/s.  gpt2m: GPT-2 medium, e5m2 activations, batch 32 sharded
+  gemm    the fp8 projections of one GPT-2 small layer + the vocabulary head at 8192 tokens; TFLOP/s
   quant   per-tensor amax + fp32->e4m3 quantise + dequantise round trip of one 2^30-element tensor
           (values ~N(0,1) with 0.1 % of positions replaced by 100*N(0,1) outliers), GB/s of
           algorithmic traffic (14 bytes per element)
@@ -317,8 +320,139 @@ class GemmWorkload:
             units += 2.0 * rows * Nc * K / 1e12
         return units, secs, f"{rows} token rows (and at most 4096 output columns) of each projection"
 
-WORKLOADS = {"quant": QuantWorkload, "gemm": GemmWorkload}
-DEFAULT_WORKLOAD = "quant"
+
+GPT2_CONFIGS = {
+    # name: (layers, hidden, heads, ffn, vocab, context, batch per GPU, activation kind)
+    "gpt2s": dict(layers=12, hidden=768, heads=12, ffn=3072, vocab=50257, ctx=1024, batch=8, act="e4m3"),
+    "gpt2m": dict(layers=24, hidden=1024, heads=16, ffn=4096, vocab=50257, ctx=1024, batch=32, act="e5m2"),
+}
+
+
+def gpt2_flops_per_token(c, T):
+    E, F, V, L = c["hidden"], c["ffn"], c["vocab"], c["layers"]
+    return L * (2 * (3 * E * E + E * E + 2 * E * F) + 4 * T * E) + 2 * E * V
+
+
+class Gpt2Workload:
+    """GPT-2 fp8 forward (token ids -> fp32 logits) through dnn::Gpt2<float>::forward_logits."""
+
+    unit = "tokens/s"
+
+    def __init__(self, name="gpt2s", n_gpus=1, batch=None, layers=None):
+        self.name = name
+        self.c = dict(GPT2_CONFIGS[name])
+        if layers:
+            self.c["layers"] = layers
+        self.n_gpus = n_gpus
+        # gpt2s: weak scaling, 8 sequences per GPU; gpt2m: the fixed batch of 32 sharded across the GPUs
+        self.strong = name == "gpt2m"
+        self.B = batch or (max(1, self.c["batch"] // n_gpus) if self.strong else self.c["batch"])
+        self.T = self.c["ctx"]
+        self.metric = "GPT-2 fp8 forward tokens/s"
+        self.dtype = f"{self.c['act']} activations x e4m3 weights -> f32 accumulate"
+        self.kernels_per_step = 1 + 13 * self.c["layers"] + 3
+
+    def config(self, n_gpus):
+        c = self.c
+        return {"workload": f"GPT-2 {'small' if self.name == 'gpt2s' else 'medium'} fp8 forward: {c['layers']} layers, "
+                            f"d_model {c['hidden']}, {c['heads']} heads, FFN {c['ffn']}, vocab {c['vocab']}, "
+                            f"batch {self.B}x{self.T} token ids per GPU, fp32 logits, random-init N(0,0.02) weights",
+                "global_batch": self.B * n_gpus, "seq_len": self.T,
+                "l2_policy": "working set per forward (1.65 GB of logits alone) larger than L2",
+                "parallelism": f"batch-sharded x{n_gpus}, weights replicated, no data-path collective"}
+
+    def units_per_step(self):
+        return self.B * self.T
+
+    def setup(self, torch, df8, dev, rank):
+        import oracle as orc
+        from oracle import gpt2_ref
+
+        self.torch, self.df8 = torch, df8
+        c = self.c
+        cfg = dict(vocab=c["vocab"], max_seq_len=c["ctx"], layers=c["layers"], heads=c["heads"], hidden=c["hidden"],
+                   ffn=c["ffn"])
+        df8.dnn_check(df8.dnn_lib().dnn_init(dev.index), "dnn_init")
+        df8.dnn_check(df8.dnn_lib().dnn_set_fp8_policy(0, 0 if c["act"] == "e4m3" else 1))
+        self.model = df8.Gpt2(**cfg, device=dev.index)
+        self.model.set_stream(torch.cuda.current_stream())
+        self.model.load_params(gpt2_ref.make_params(cfg, seed=2 if self.name == "gpt2s" else 3))
+        self.model.set_options(gelu=True, causal=False)
+        ids = orc.fill_token_ids(self.B * self.T, seed=100 + rank, vocab=c["vocab"]).reshape(self.B, self.T)
+        self.ids = torch.from_numpy(ids).to(dev)
+        self.ids_host = torch.from_numpy(ids).pin_memory()
+        self.last_logits = torch.empty((self.B, c["vocab"]), dtype=torch.float32, pin_memory=True)
+        self.dev = dev
+
+    def step(self):
+        self.logits_ptr = self.model.forward_logits(self.ids, check_ids=False)
+
+    def e2e_setup(self, torch, dev):
+        pass
+
+    def e2e_step(self):
+        torch, c = self.torch, self.c
+        ptr = self.model.forward_logits_host(self.ids_host)
+        logits = self.df8.device_view(torch, ptr, (self.B, self.T, c["vocab"]))
+        self.last_logits.copy_(logits[:, -1, :], non_blocking=True)  # the next-token logits of every sequence
+
+    def e2e_units_per_step(self):
+        return self.units_per_step()
+
+    def e2e_bytes(self):
+        return self.ids_host.numel() * 4, self.last_logits.numel() * 4
+
+    def roofline(self, torch, peaks, iters=10):
+        # dominant kernel: the vocabulary-head GEMM [B*T, V] x [V, E]
+        d, c = self.df8, self.c
+        M, N, K = self.B * self.T, c["vocab"], c["hidden"]
+        g = torch.Generator(device=self.dev)
+        g.manual_seed(1)
+        a = torch.randint(0, 0x70, (M, K), dtype=torch.uint8, device=self.dev, generator=g)
+        w = torch.randint(0, 0x70, (N, K), dtype=torch.uint8, device=self.dev, generator=g)
+        one = torch.tensor([1.0, 1.0 / 64], device=self.dev)
+        out = torch.empty((M, N), device=self.dev)
+        for _ in range(2):
+            d.gemm_fp8_tn(a, 0, one, w, 0, one, None, None, M, N, K, 0, out)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        torch.cuda.synchronize()
+        ev[0].record()
+        for _ in range(iters):
+            d.gemm_fp8_tn(a, 0, one, w, 0, one, None, None, M, N, K, 0, out)
+        ev[1].record()
+        torch.cuda.synchronize()
+        ms = ev[0].elapsed_time(ev[1]) / iters
+        flops = 2.0 * M * N * K
+        tf = flops / 1e12 / (ms / 1e3)
+        peak = 2.0 * peaks["bf16_tflops_sustained"]
+        return {"kernel": "gemm_fp8_tn_kernel (vocabulary head)", "bound": "tensor", "achieved": round(tf, 1),
+                "peak": peak, "peak_source": peaks["source"] + " bf16 sustained x2 (fp8 dense)", "unit": "TFLOP/s",
+                "frac": round(tf / peak, 4), "ms_per_launch": round(ms, 4), "algorithmic_flops_per_launch": flops,
+                "traffic": None, "model_flops_per_token": gpt2_flops_per_token(c, self.T)}
+
+    def cpu_sample(self, orc, tokens=128):
+        from oracle import gpt2_ref
+
+        c = self.c
+        E = c["hidden"]
+        cfg = dict(vocab=c["vocab"], max_seq_len=c["ctx"], layers=1, heads=c["heads"], hidden=E, ffn=c["ffn"])
+        prm = gpt2_ref.make_params(cfg, seed=2)
+        x = orc.fill_normal(tokens * E, seed=7).reshape(tokens, E)
+        act = orc.E4M3 if c["act"] == "e4m3" else orc.E5M2
+        t0 = time.perf_counter()
+        y = gpt2_ref.block_forward(prm, "block0", x, 1, tokens, c["heads"], act, orc.E4M3, True)
+        t_block = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        gpt2_ref._fc(y, prm["final_fc.weight"], prm["final_fc.bias"], act, orc.E4M3)
+        t_head = time.perf_counter() - t0
+        # one block at `tokens` context -> L blocks at the full context, scaled by the per-token block flops
+        blk = lambda T: 2 * (3 * E * E + E * E + 2 * E * c["ffn"]) + 4 * T * E
+        secs = t_block * GPT2_CONFIGS[self.name]["layers"] * blk(self.T) / blk(tokens) + t_head
+        return tokens, secs, (f"one transformer block + the vocabulary head on 1x{tokens} tokens, extrapolated "
+                              f"linearly in flops to {GPT2_CONFIGS[self.name]['layers']} blocks at context {self.T}")
+
+WORKLOADS = {"quant": QuantWorkload, "gemm": GemmWorkload, "gpt2s": Gpt2Workload, "gpt2m": Gpt2Workload}
+DEFAULT_WORKLOAD = "gpt2s"
 
 
 def make_workload(args):
@@ -326,6 +460,9 @@ def make_workload(args):
         return QuantWorkload(log2n=args.log2n)
     if args.workload == "gemm" and args.only:
         return GemmWorkload(only=args.only.split(","))
+    if args.workload in GPT2_CONFIGS:
+        return Gpt2Workload(args.workload, n_gpus=max(1, int(os.environ.get("WORLD_SIZE", args.gpus))),
+                            batch=args.batch, layers=args.layers)
     return WORKLOADS[args.workload]()
 
 
@@ -431,8 +568,8 @@ def run_ours(args, rank, world, local_rank):
         line = {
             "metric": wl.metric, "value": round(value, 2), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_total / args.steps, 4), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-            "config": wl.config(world), "clocks": clocks,
+            "scaling": "strong" if getattr(wl, "strong", False) else "weak", "vs_baseline": None,
+            "dtype": wl.dtype, "data": "synthetic", "config": wl.config(world), "clocks": clocks,
             "e2e": {"value": round(e2e_value, 2), "unit": wl.unit, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e_steps},
             "gpu_launches": wl.kernels_per_step * args.steps,
@@ -452,6 +589,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=None, help="gpt2 workloads: sequences per GPU (profiling)")
+    ap.add_argument("--layers", type=int, default=None, help="gpt2 workloads: layer count override (profiling)")
     ap.add_argument("--only", default=None, help="gemm workload: comma list of projections (profiling)")
     ap.add_argument("--log2n", type=int, default=None, help="quant workload: tensor size override (profiling)")
     args = ap.parse_args()

@@ -46,6 +46,7 @@ _SIGNATURES = {
     "df8_embed_pe_f32": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
     "df8_attention_fp8": [_vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp, _vp],
     "df8_softmax_masked_f32": [_vp, _vp, _i, _i, _i, _i, _vp, _vp],
+    "df8_gemm_fp8_tn_q": [_vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     "df8_status_word_read": [_vp, _vp],
     "df8_status_word_reset": [],
 }
@@ -118,6 +119,13 @@ def gemm_fp8_tn(a_codes, kind_a, scale_a, w_codes, kind_w, scale_w, bias, residu
           "df8_gemm_fp8_tn")
 
 
+def gemm_fp8_tn_q(a_codes, kind_a, scale_a, w_codes, kind_w, scale_w, bias, M, N, K, flags, out_kind, out_codes,
+                  out_scale, out_amax, stream=None) -> None:
+    check(lib().df8_gemm_fp8_tn_q(ptr(a_codes), kind_a, ptr(scale_a), ptr(w_codes), kind_w, ptr(scale_w), ptr(bias),
+                                  M, N, K, flags, out_kind, ptr(out_codes), ptr(out_scale), ptr(out_amax),
+                                  stream_ptr(stream)), "df8_gemm_fp8_tn_q")
+
+
 def status_word() -> tuple[int, int]:
     """(first timeout code, number of timeouts) recorded by bounded device-side waits; (0, 0) when clean."""
     code, count = C.c_uint(0), C.c_uint(0)
@@ -156,3 +164,153 @@ def softmax_masked_f32(x, mask, B, H, T, out, stream=None) -> None:
     mask_b = 0 if mask is None else mask.shape[0]
     check(lib().df8_softmax_masked_f32(ptr(x), ptr(mask), mask_b, B, H, T, ptr(out), stream_ptr(stream)),
           "df8_softmax_masked_f32")
+
+
+# ---- libdf8_dnn.so: the C++ dnn:: classes behind their C harness (include/df8_dnn.h) -----------------
+
+_DNN_SIGNATURES = {
+    "dnn_init": [_i],
+    "dnn_set_stream": [_vp],
+    "dnn_set_fp8_policy": [_i, _i],
+    "dnn_gpt2_destroy": [_vp],
+    "dnn_gpt2_set_options": [_vp, _i, _i],
+    "dnn_gpt2_num_params": [_vp],
+    "dnn_gpt2_param_info": [_vp, _i, _vp, _i, _vp, _vp],
+    "dnn_gpt2_param_upload": [_vp, _i, _vp],
+    "dnn_gpt2_param_download": [_vp, _i, _vp],
+    "dnn_gpt2_prepare": [_vp],
+    "dnn_gpt2_forward_logits": [_vp, _vp, _i, _i, _i, _vp],
+    "dnn_gpt2_forward_logits_host": [_vp, _vp, _i, _i, _vp],
+    "dnn_gpt2_forward_hidden": [_vp, _vp, _i, _i, _vp],
+    "dnn_gpt2_forward_ids": [_vp, _vp, _i, _vp],
+    "dnn_gpt2_save": [_vp, C.c_char_p],
+    "dnn_fc_forward": [_i, _i, _vp, _vp, _vp, _i, _vp],
+    "dnn_layernorm_forward": [_i, _i, _vp, _vp, _f, _vp, _vp],
+    "dnn_softmax_forward": [_i, _i, _i, _vp, _vp, _i, _vp],
+    "dnn_mha_forward": [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp],
+    "dnn_block_forward": [_i, _i, _i, _i, _i, _vp, _i, _i, _i, _vp, _vp],
+    "dnn_embedding_forward": [_i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "dnn_selftest_tensor": [_vp, _i],
+    "dnn_selftest_context": [_vp, _i],
+    "dnn_selftest_errors": [_vp, _i],
+}
+
+
+def dnn_lib() -> C.CDLL:
+    """The C++ dnn:: class library behind its C harness. Raises if it has not been built."""
+    global _dnn
+    if _dnn is None:
+        lib()  # libdf8.so first (RTLD_GLOBAL), libdf8_dnn.so links against it
+        path = LIB_DIR / "libdf8_dnn.so"
+        if not path.exists():
+            raise Df8Error(f"{path} is missing: build it with `python -m deepfuse_b200.build`")
+        handle = C.CDLL(str(path))
+        handle.dnn_last_error.restype = C.c_char_p
+        handle.dnn_last_error.argtypes = []
+        handle.dnn_gpt2_create.restype = C.c_void_p
+        handle.dnn_gpt2_create.argtypes = [_i] * 6
+        handle.dnn_gpt2_load.restype = C.c_void_p
+        handle.dnn_gpt2_load.argtypes = [C.c_char_p]
+        for name, args in _DNN_SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.argtypes = args
+            fn.restype = None if name == "dnn_gpt2_destroy" else C.c_int
+        _dnn = handle
+    return _dnn
+
+
+def dnn_check(rc: int, what: str = "dnn call") -> None:
+    if rc != 0:
+        raise Df8Error(f"{what} failed (code {rc}): {dnn_lib().dnn_last_error().decode('utf-8', 'replace')}")
+
+
+class Gpt2:
+    """dnn::Gpt2<float> driven through the C harness (tests and bench.py)."""
+
+    def __init__(self, vocab, max_seq_len, layers, heads, hidden, ffn, device: int = 0):
+        d = dnn_lib()
+        dnn_check(d.dnn_init(device), "dnn_init")
+        self.cfg = dict(vocab=vocab, max_seq_len=max_seq_len, layers=layers, heads=heads, hidden=hidden, ffn=ffn)
+        self.h = d.dnn_gpt2_create(vocab, max_seq_len, layers, heads, hidden, ffn)
+        if not self.h:
+            raise Df8Error("dnn_gpt2_create failed: " + d.dnn_last_error().decode())
+
+    def close(self):
+        if self.h:
+            dnn_lib().dnn_gpt2_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def param_names(self):
+        d = dnn_lib()
+        out = []
+        buf = C.create_string_buffer(128)
+        shape = (C.c_int * 8)()
+        ndim = C.c_int(0)
+        for i in range(d.dnn_gpt2_num_params(self.h)):
+            dnn_check(d.dnn_gpt2_param_info(self.h, i, buf, 128, shape, C.byref(ndim)), "dnn_gpt2_param_info")
+            out.append((buf.value.decode(), tuple(shape[k] for k in range(ndim.value))))
+        return out
+
+    def load_params(self, params: dict):
+        import numpy as np
+
+        d = dnn_lib()
+        for i, (name, shape) in enumerate(self.param_names()):
+            a = np.ascontiguousarray(params[name], dtype=np.float32)
+            n = 1
+            for s in shape:
+                n *= s
+            if a.size != n:
+                raise ValueError(f"{name}: expected {shape}, got {a.shape}")
+            dnn_check(d.dnn_gpt2_param_upload(self.h, i, a.ctypes.data_as(C.c_void_p)), "dnn_gpt2_param_upload")
+        dnn_check(d.dnn_gpt2_prepare(self.h), "dnn_gpt2_prepare")
+
+    def set_options(self, gelu=True, causal=False):
+        dnn_check(dnn_lib().dnn_gpt2_set_options(self.h, int(gelu), int(causal)), "dnn_gpt2_set_options")
+
+    def set_stream(self, stream=None):
+        dnn_check(dnn_lib().dnn_set_stream(stream_ptr(stream)), "dnn_set_stream")
+
+    def forward_logits(self, ids_dev, check_ids=True) -> int:
+        """ids_dev: torch int32 CUDA tensor [B,T]; returns the device pointer of fp32 logits [B*T, V]."""
+        out = C.c_void_p(0)
+        B, T = ids_dev.shape
+        dnn_check(dnn_lib().dnn_gpt2_forward_logits(self.h, ptr(ids_dev), B, T, int(check_ids), C.byref(out)),
+                  "dnn_gpt2_forward_logits")
+        return out.value
+
+    def forward_logits_host(self, ids_host) -> int:
+        """ids_host: pinned torch int32 CPU tensor [B,T]; the upload happens inside the call."""
+        out = C.c_void_p(0)
+        B, T = ids_host.shape
+        dnn_check(dnn_lib().dnn_gpt2_forward_logits_host(self.h, ids_host.data_ptr(), B, T, C.byref(out)),
+                  "dnn_gpt2_forward_logits_host")
+        return out.value
+
+    def forward_hidden(self, ids_dev) -> int:
+        out = C.c_void_p(0)
+        B, T = ids_dev.shape
+        dnn_check(dnn_lib().dnn_gpt2_forward_hidden(self.h, ptr(ids_dev), B, T, C.byref(out)),
+                  "dnn_gpt2_forward_hidden")
+        return out.value
+
+
+def device_view(torch, data_ptr: int, shape, dtype=None):
+    """A torch tensor viewing device memory owned by the native side (no copy)."""
+    import numpy as np
+
+    dtype = dtype or torch.float32
+    n = int(np.prod(shape))
+    itemsize = torch.empty((), dtype=dtype).element_size()
+
+    class _Holder:
+        __cuda_array_interface__ = {"shape": (n,), "typestr": {4: "<f4", 1: "|u1"}[itemsize] if dtype != torch.int32 else "<i4",
+                                    "data": (data_ptr, False), "version": 3}
+
+    return torch.as_tensor(_Holder(), device=f"cuda:{torch.cuda.current_device()}").view(*shape)

@@ -10,10 +10,19 @@
 //   warp 0     TMA producer: 128-byte-swizzled K-blocks of A and W into a STAGES-deep smem ring
 //   warp 1     MMA issuer:   tcgen05.mma kind::f8f6f4 (M=128, N=BN, K=32 per instruction),
 //                            fp32 accumulators in TMEM, double-buffered (2 x BN columns)
-//   warps 2-5  epilogue:     tcgen05.ld -> smem transpose -> coalesced global stores with the fused
-//                            dequant scale, bias, GELU (upstream activation_layer.cu:9-20 formula),
-//                            residual add (upstream tensor.cu:383-415) and |out| max reduction
+//   warps 2-9  epilogue:     two warps per TMEM lane quarter, each taking every other 32-column chunk:
+//                            tcgen05.ld (the next chunk's load in flight while this one is stored) with
+//                            the fused dequant scale, bias, GELU (upstream activation_layer.cu:9-20
+//                            formula), residual add (upstream tensor.cu:383-415) and |out| max reduction.
+//                            fp32 output goes through a per-warp smem transpose so that global stores are
+//                            coalesced along N; fp8 output (32 codes = one 32-byte sector per thread and
+//                            chunk) and the amax-only pass store straight from registers.
 // The epilogue of tile i overlaps the main loop of tile i+1 through the second TMEM buffer.
+//
+// Output modes: fp32 [M,N]; fp8 codes [M,N] quantised with a scale derived from a given max|out|;
+// or nothing but max|out|.  df8_gemm_fp8_tn_q chains the last two (the GEMM runs twice) to produce
+// per-tensor-quantised output without ever writing the fp32 tensor: at these K the second pass of
+// tensor-core work is cheaper than 4+4+1 bytes per element of HBM round trip.
 // All mbarrier waits are bounded; a wait that gives up records a code in the status word
 // (df8_status_word_read) and the CTA tears down normally.
 #include "df8_internal.cuh"
@@ -28,16 +37,27 @@ using namespace ptx;
 
 constexpr int BM = 128;
 constexpr int BK = 128;  // bytes == fp8 elements per K-block (one 128-byte swizzle row)
-constexpr int kGemmThreads = 192;
+constexpr int kEpiWarps = 8;
+constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 constexpr int kStagingFloatsPerWarp = 32 * 36;
+
+// epilogue / output modes (template parameter MODE)
+constexpr int kOutF32Vec = 0;   // fp32, N % 4 == 0 and 16-byte aligned pointers: 128-bit accesses
+constexpr int kOutF32 = 1;      // fp32, any N
+constexpr int kOutE4M3 = 2;     // fp8 codes, N % 16 == 0
+constexpr int kOutE5M2 = 3;
+constexpr int kOutNone = 4;     // max|out| only
 
 struct GemmArgs {
     const float* scale_a;   // {q, dq} of A
     const float* scale_w;   // {q, dq} of W
     const float* bias;      // [N] or null
     const float* residual;  // [M,N] or null
-    float* out;             // [M,N] fp32
+    float* out;             // [M,N] fp32 (fp32 modes)
     float* out_amax;        // 1 float or null
+    uint8_t* out_codes;     // [M,N] fp8 codes (fp8 modes)
+    const float* q_amax;    // max|out| the fp8 output scale is derived from (fp8 modes)
+    float* out_scale;       // {q, dq} of the fp8 output, written by CTA 0 (fp8 modes), or null
     int M, N, K;
     int flags;
     uint32_t idesc;
@@ -49,7 +69,7 @@ struct GemmCfg {
     static constexpr int kABytes = BM * BK;
     static constexpr int kBBytes = BN * BK;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStagingBytes = 4 * kStagingFloatsPerWarp * 4;
+    static constexpr int kStagingBytes = kEpiWarps * kStagingFloatsPerWarp * 4;
     static constexpr int kBarBytes = 256;
     static constexpr int kSmemBytes = STAGES * kStageBytes + kStagingBytes + kBarBytes + 1024;
     static constexpr int kTmemCols = 2 * BN;
@@ -72,57 +92,68 @@ __device__ __forceinline__ float gelu_tanh(float x) {
     return x * 0.5f * (1.0f + t);
 }
 
-// Epilogue for one 32-row x 32-column chunk held by one warp (thread = row, r[j] = column j).
-// Transposes through the warp's staging buffer so that global accesses are coalesced along N.
+// ---- fp32 output: transpose one 32-row x 32-column chunk through the warp's staging buffer -------
+
+// thread = row: park the chunk's accumulators in shared memory
 template <bool VEC4>
-__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], float* stg, int lane, int row0, int col0,
-                                               const GemmArgs& a, float alpha, float& amax) {
+__device__ __forceinline__ void stage_chunk(const uint32_t (&r)[32], float* stg, int lane) {
     if constexpr (VEC4) {
         float4* srow = reinterpret_cast<float4*>(stg + lane * 36);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
             srow[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-        __syncwarp();
+    } else {
+        float* srow = stg + lane * 33;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) srow[j] = __uint_as_float(r[j]);
+    }
+}
+
+// lanes run along N: apply the epilogue and store coalesced
+template <bool VEC4>
+__device__ __forceinline__ void store_chunk_f32(const float* stg, int lane, int row0, int col0, const GemmArgs& a,
+                                                float alpha, float& amax) {
+    if constexpr (VEC4) {
         const int cq = (lane & 7) * 4;
         const int gcol = col0 + cq;
         const bool col_ok = gcol < a.N;
         float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
         if (a.bias && col_ok) b4 = *reinterpret_cast<const float4*>(a.bias + gcol);
+        float4 v[8], rs[8];
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
             const int rl = it * 4 + (lane >> 3);
-            const int grow = row0 + rl;
-            float4 v = *reinterpret_cast<const float4*>(stg + rl * 36 + cq);
+            v[it] = *reinterpret_cast<const float4*>(stg + rl * 36 + cq);
+            if ((a.flags & 2) && row0 + rl < a.M && col_ok)
+                rs[it] = *reinterpret_cast<const float4*>(a.residual + size_t(row0 + rl) * a.N + gcol);
+            else
+                rs[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int grow = row0 + it * 4 + (lane >> 3);
+            float4 o = v[it];
+            o.x = fmaf(o.x, alpha, b4.x);
+            o.y = fmaf(o.y, alpha, b4.y);
+            o.z = fmaf(o.z, alpha, b4.z);
+            o.w = fmaf(o.w, alpha, b4.w);
+            if (a.flags & 1) {
+                o.x = gelu_tanh(o.x);
+                o.y = gelu_tanh(o.y);
+                o.z = gelu_tanh(o.z);
+                o.w = gelu_tanh(o.w);
+            }
+            o.x += rs[it].x;
+            o.y += rs[it].y;
+            o.z += rs[it].z;
+            o.w += rs[it].w;
             if (grow < a.M && col_ok) {
-                v.x = fmaf(v.x, alpha, b4.x);
-                v.y = fmaf(v.y, alpha, b4.y);
-                v.z = fmaf(v.z, alpha, b4.z);
-                v.w = fmaf(v.w, alpha, b4.w);
-                if (a.flags & 1) {
-                    v.x = gelu_tanh(v.x);
-                    v.y = gelu_tanh(v.y);
-                    v.z = gelu_tanh(v.z);
-                    v.w = gelu_tanh(v.w);
-                }
-                const size_t off = size_t(grow) * a.N + gcol;
-                if (a.flags & 2) {
-                    const float4 rs = *reinterpret_cast<const float4*>(a.residual + off);
-                    v.x += rs.x;
-                    v.y += rs.y;
-                    v.z += rs.z;
-                    v.w += rs.w;
-                }
-                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-                *reinterpret_cast<float4*>(a.out + off) = v;
+                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w))));
+                *reinterpret_cast<float4*>(a.out + size_t(grow) * a.N + gcol) = o;
             }
         }
-        __syncwarp();
     } else {
-        float* srow = stg + lane * 33;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) srow[j] = __uint_as_float(r[j]);
-        __syncwarp();
         const int gcol = col0 + lane;
         const bool col_ok = gcol < a.N;
         const float b = (a.bias && col_ok) ? a.bias[gcol] : 0.f;
@@ -139,11 +170,48 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], float* s
                 a.out[off] = v;
             }
         }
-        __syncwarp();
     }
 }
 
-template <int BN, int STAGES, bool VEC4>
+// ---- fp8 / amax-only output: thread = row, straight from registers ------------------------------
+
+// KIND: DF8_E4M3 / DF8_E5M2 to emit codes, -1 to only reduce max|out|.
+template <int KIND>
+__device__ __forceinline__ void direct_chunk(const uint32_t (&r)[32], int grow, int col0, const GemmArgs& a,
+                                             float alpha, float out_q, float& amax) {
+    const bool row_ok = grow < a.M;
+    uint32_t w[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (a.bias) b4 = __ldg(reinterpret_cast<const float4*>(a.bias + col0 + 4 * g));  // same address in every lane
+        float v0 = fmaf(__uint_as_float(r[4 * g]), alpha, b4.x);
+        float v1 = fmaf(__uint_as_float(r[4 * g + 1]), alpha, b4.y);
+        float v2 = fmaf(__uint_as_float(r[4 * g + 2]), alpha, b4.z);
+        float v3 = fmaf(__uint_as_float(r[4 * g + 3]), alpha, b4.w);
+        if (a.flags & 1) {
+            v0 = gelu_tanh(v0);
+            v1 = gelu_tanh(v1);
+            v2 = gelu_tanh(v2);
+            v3 = gelu_tanh(v3);
+        }
+        if constexpr (KIND < 0) {
+            if (row_ok) amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3))));
+        } else {
+            w[g] = cvt_f32x4_to_fp8x4<KIND>(__fmul_rn(v0, out_q), __fmul_rn(v1, out_q), __fmul_rn(v2, out_q),
+                                            __fmul_rn(v3, out_q));
+        }
+    }
+    if constexpr (KIND >= 0) {
+        if (row_ok) {
+            uint4* dst = reinterpret_cast<uint4*>(a.out_codes + size_t(grow) * a.N + col0);
+            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+    }
+}
+
+template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_w,
                    const GemmArgs args) {
@@ -168,7 +236,7 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(tfull + b), 1);
-            mbar_init(smem_u32(tempty + b), 4);
+            mbar_init(smem_u32(tempty + b), kEpiWarps);
         }
         mbar_fence_init();
     }
@@ -252,9 +320,22 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
             }
         }
     } else {
-        const int q = warp & 3;  // TMEM lane quarter this warp may read
-        float* stg = staging + (warp - 2) * kStagingFloatsPerWarp;
+        const int e = warp - 2;
+        const int q = warp & 3;    // TMEM lane quarter this warp may read
+        const int half = e >> 2;   // which of the quarter's two warps: takes chunks half, half+2, ...
+        constexpr int kChunks = BN / 64;  // 32-column chunks per warp and tile
+        float* stg = staging + e * kStagingFloatsPerWarp;
         const float alpha = args.scale_a[1] * args.scale_w[1];
+        float out_q = 1.f;
+        if constexpr (MODE == kOutE4M3 || MODE == kOutE5M2) {
+            const float2 sc = scales_from_amax(*args.q_amax, fp8_max(MODE == kOutE4M3 ? DF8_E4M3 : DF8_E5M2));
+            out_q = sc.x;
+            if (blockIdx.x == 0 && e == 0 && lane == 0 && args.out_scale) {
+                args.out_scale[0] = sc.x;
+                args.out_scale[1] = sc.y;
+            }
+        }
+        const uint32_t lane_addr = uint32_t(q * 32) << 16;
         uint32_t acc_it = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++acc_it) {
             const uint32_t buf = acc_it & 1;
@@ -268,17 +349,48 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
             tc_fence_after_sync();
             float amax = 0.f;
             const int row0 = m0 + q * 32;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                if (n0 + c * 32 >= args.N) break;  // uniform across the warp
+            const uint32_t taddr = tmem_base + buf * BN + lane_addr;
+            int nvalid = 0;  // chunks of this warp that start inside N (uniform across the warp)
+#pragma unroll
+            for (int j = 0; j < kChunks; ++j)
+                if (n0 + 32 * (half + 2 * j) < args.N) nvalid = j + 1;
+
+            if constexpr (MODE == kOutF32Vec || MODE == kOutF32) {
+                constexpr bool VEC4 = MODE == kOutF32Vec;
                 uint32_t r[32];
-                tmem_ld_32x32(tmem_base + buf * BN + c * 32 + (uint32_t(q * 32) << 16), r);
-                tmem_ld_wait();
-                epilogue_chunk<VEC4>(r, stg, lane, row0, n0 + c * 32, args, alpha, amax);
+                if (nvalid > 0) tmem_ld_32x32(taddr + 32 * half, r);
+                for (int j = 0; j < nvalid; ++j) {
+                    tmem_ld_wait();
+                    stage_chunk<VEC4>(r, stg, lane);
+                    __syncwarp();
+                    if (j + 1 < nvalid) {
+                        tmem_ld_32x32(taddr + 32 * (half + 2 * (j + 1)), r);  // in flight during the stores below
+                    } else {
+                        tc_fence_before_sync();  // last chunk is out of TMEM: hand the buffer back early
+                        if (lane == 0) mbar_arrive(smem_u32(tempty + buf));
+                    }
+                    store_chunk_f32<VEC4>(stg, lane, row0, n0 + 32 * (half + 2 * j), args, alpha, amax);
+                    __syncwarp();
+                }
+                if (nvalid == 0) {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(tempty + buf));
+                }
+            } else {
+                constexpr int KIND = MODE == kOutE4M3 ? int(DF8_E4M3) : (MODE == kOutE5M2 ? int(DF8_E5M2) : -1);
+                const int grow = row0 + lane;
+#pragma unroll 1
+                for (int j = 0; j < nvalid; ++j) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + 32 * (half + 2 * j), r);
+                    tmem_ld_wait();
+                    direct_chunk<KIND>(r, grow, n0 + 32 * (half + 2 * j), args, alpha, out_q, amax);
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(tempty + buf));
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(tempty + buf));
             if (args.flags & 4) {
                 amax = warp_max(amax);
                 if (lane == 0 && amax > 0.f) atomic_max_nonneg(args.out_amax, amax);
@@ -294,11 +406,11 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
     }
 }
 
-template <int BN, int STAGES, bool VEC4>
+template <int BN, int STAGES, int MODE>
 df8_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmArgs& args, int grid,
                        cudaStream_t st) {
     using Cfg = GemmCfg<BN, STAGES>;
-    auto kern = gemm_fp8_tn_kernel<BN, STAGES, VEC4>;
+    auto kern = gemm_fp8_tn_kernel<BN, STAGES, MODE>;
     static bool configured[64] = {};
     int dev = 0;
     DF8_CUDA_TRY(cudaGetDevice(&dev));
@@ -309,6 +421,47 @@ df8_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmA
     kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ta, tw, args);
     DF8_LAUNCH_CHECK("gemm_fp8_tn_kernel");
     return DF8_OK;
+}
+
+template <int MODE>
+df8_status launch_gemm_bn(bool wide, const CUtensorMap& ta, const CUtensorMap& tw, const GemmArgs& args, int grid,
+                          cudaStream_t st) {
+    return wide ? launch_gemm<256, 3, MODE>(ta, tw, args, grid, st) : launch_gemm<128, 5, MODE>(ta, tw, args, grid, st);
+}
+
+// Shared host path of the entry points: picks the tile width, encodes the tensor maps, launches `mode`.
+df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uint8_t* w_codes, df8_kind kind_w,
+                    GemmArgs args, cudaStream_t st) {
+    const int M = args.M, N = args.N, K = args.K;
+    df8_status src = status_word_device_ptr(&args.status);
+    if (src != DF8_OK) return src;
+
+    const int sms = sm_count();
+    // tile width: the one that fills whole waves of the persistent grid best (wider tiles reuse A more)
+    auto efficiency = [&](int bn, double weight) {
+        const long tiles = long((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+        const long waves = (tiles + sms - 1) / sms;
+        return weight * double(tiles) / double(waves * sms) * (double(N) / double(((N + bn - 1) / bn) * bn));
+    };
+    const bool wide = efficiency(256, 1.0) >= efficiency(128, 0.92);
+    const int bn = wide ? 256 : 128;
+    const long tiles = long((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+    const int grid = int(tiles < sms ? tiles : sms);
+
+    CUtensorMap ta, tw;
+    df8_status rc = make_tmap_2d_u8(&ta, a_codes, uint64_t(M), uint64_t(K), uint64_t(K), BM, BK, 128);
+    if (rc != DF8_OK) return rc;
+    rc = make_tmap_2d_u8(&tw, w_codes, uint64_t(N), uint64_t(K), uint64_t(K), uint32_t(bn), BK, 128);
+    if (rc != DF8_OK) return rc;
+    args.idesc = ptx::make_idesc_f8(BM, bn, int(kind_a), int(kind_w));
+
+    switch (mode) {
+        case kOutF32Vec: return launch_gemm_bn<kOutF32Vec>(wide, ta, tw, args, grid, st);
+        case kOutF32: return launch_gemm_bn<kOutF32>(wide, ta, tw, args, grid, st);
+        case kOutE4M3: return launch_gemm_bn<kOutE4M3>(wide, ta, tw, args, grid, st);
+        case kOutE5M2: return launch_gemm_bn<kOutE5M2>(wide, ta, tw, args, grid, st);
+        default: return launch_gemm_bn<kOutNone>(wide, ta, tw, args, grid, st);
+    }
 }
 
 }  // namespace
@@ -335,29 +488,7 @@ extern "C" df8_status df8_gemm_fp8_tn(const uint8_t* a_codes, df8_kind kind_a, c
     if (K % 16 != 0)
         return fail(DF8_ERR_UNSUPPORTED, "df8_gemm_fp8_tn: K=%d must be a multiple of 16 (TMA row pitch)", K);
 
-    unsigned int* status_ptr = nullptr;
-    df8_status src = status_word_device_ptr(&status_ptr);
-    if (src != DF8_OK) return src;
-
-    const int sms = sm_count();
-    // tile width: the one that fills whole waves of the persistent grid best (wider tiles reuse A more)
-    auto efficiency = [&](int bn, double weight) {
-        const long tiles = long((M + BM - 1) / BM) * ((N + bn - 1) / bn);
-        const long waves = (tiles + sms - 1) / sms;
-        return weight * double(tiles) / double(waves * sms) * (double(N) / double(((N + bn - 1) / bn) * bn));
-    };
-    const bool wide = efficiency(256, 1.0) >= efficiency(128, 0.92);
-    const int bn = wide ? 256 : 128;
-    const long tiles = long((M + BM - 1) / BM) * ((N + bn - 1) / bn);
-    const int grid = int(tiles < sms ? tiles : sms);
-
-    CUtensorMap ta, tw;
-    df8_status rc = make_tmap_2d_u8(&ta, a_codes, uint64_t(M), uint64_t(K), uint64_t(K), BM, BK, 128);
-    if (rc != DF8_OK) return rc;
-    rc = make_tmap_2d_u8(&tw, w_codes, uint64_t(N), uint64_t(K), uint64_t(K), uint32_t(bn), BK, 128);
-    if (rc != DF8_OK) return rc;
-
-    GemmArgs args;
+    GemmArgs args{};
     args.scale_a = scale_a;
     args.scale_w = scale_w;
     args.bias = bias;
@@ -368,14 +499,49 @@ extern "C" df8_status df8_gemm_fp8_tn(const uint8_t* a_codes, df8_kind kind_a, c
     args.N = N;
     args.K = K;
     args.flags = flags;
-    args.idesc = ptx::make_idesc_f8(BM, bn, int(kind_a), int(kind_w));
-    args.status = status_ptr;
-
     const bool vec4 = (N % 4 == 0) && aligned16(out) && (!bias || aligned16(bias)) &&
                       (!(flags & DF8_EPI_RESIDUAL) || aligned16(residual));
-    if (wide)
-        return vec4 ? launch_gemm<256, 4, true>(ta, tw, args, grid, st)
-                    : launch_gemm<256, 4, false>(ta, tw, args, grid, st);
-    return vec4 ? launch_gemm<128, 6, true>(ta, tw, args, grid, st)
-                : launch_gemm<128, 6, false>(ta, tw, args, grid, st);
+    return run_gemm(vec4 ? kOutF32Vec : kOutF32, a_codes, kind_a, w_codes, kind_w, args, st);
+}
+
+extern "C" df8_status df8_gemm_fp8_tn_q(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a,
+                                        const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
+                                        const float* bias, int M, int N, int K, int flags, df8_kind out_kind,
+                                        uint8_t* out_codes, float* out_scale, float* out_amax, df8_stream stream) {
+    DF8_REQUIRE((kind_a == DF8_E4M3 || kind_a == DF8_E5M2) && (kind_w == DF8_E4M3 || kind_w == DF8_E5M2) &&
+                    (out_kind == DF8_E4M3 || out_kind == DF8_E5M2),
+                "df8_gemm_fp8_tn_q: unknown fp8 kind");
+    DF8_REQUIRE(M >= 0 && N >= 0 && K > 0, "df8_gemm_fp8_tn_q: bad shape M=%d N=%d K=%d", M, N, K);
+    DF8_REQUIRE((flags & ~DF8_EPI_GELU) == 0, "df8_gemm_fp8_tn_q: only DF8_EPI_GELU is accepted, got 0x%x", flags);
+    DF8_REQUIRE(out_amax && out_scale, "df8_gemm_fp8_tn_q: out_amax and out_scale are required");
+    cudaStream_t st = as_stream(stream);
+    DF8_CUDA_TRY(cudaMemsetAsync(out_amax, 0, sizeof(float), st));
+    if (K % 16 != 0 || N % 32 != 0)
+        return fail(DF8_ERR_UNSUPPORTED, "df8_gemm_fp8_tn_q: needs K %% 16 == 0 and N %% 32 == 0 (K=%d N=%d)", K, N);
+    DF8_REQUIRE(M == 0 || N == 0 || (a_codes && w_codes && scale_a && scale_w && out_codes),
+                "df8_gemm_fp8_tn_q: null buffer");
+    DF8_REQUIRE(aligned16(out_codes) && (!bias || aligned16(bias)), "df8_gemm_fp8_tn_q: out_codes and bias must be 16-byte aligned");
+
+    GemmArgs args{};
+    args.scale_a = scale_a;
+    args.scale_w = scale_w;
+    args.bias = bias;
+    args.out_amax = out_amax;
+    args.M = M;
+    args.N = N;
+    args.K = K;
+    args.out_codes = out_codes;
+    args.q_amax = out_amax;
+    args.out_scale = out_scale;
+    if (M == 0 || N == 0) {  // still publish the scale of an empty tensor: {1, 1}
+        const float one[2] = {1.f, 1.f};
+        DF8_CUDA_TRY(cudaMemcpyAsync(out_scale, one, sizeof(one), cudaMemcpyHostToDevice, st));
+        return DF8_OK;
+    }
+    // pass 1: max|out| only;  pass 2: the same product again, quantised with the scale that max gives
+    args.flags = flags | DF8_EPI_AMAX;
+    df8_status rc = run_gemm(kOutNone, a_codes, kind_a, w_codes, kind_w, args, st);
+    if (rc != DF8_OK) return rc;
+    args.flags = flags;
+    return run_gemm(out_kind == DF8_E4M3 ? kOutE4M3 : kOutE5M2, a_codes, kind_a, w_codes, kind_w, args, st);
 }

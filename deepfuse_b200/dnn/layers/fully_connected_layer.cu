@@ -39,10 +39,31 @@ void FullyConnectedLayer<TT>::initialize_weights() {
     this->bias_.zero();
 }
 
+namespace {
+// rows x cols fp32 -> rows x cols_padded, the new columns zero (zero is the fp8 code 0x00 as well)
+tensor<float> pad_columns(const float* src, int rows, int cols, int cols_padded) {
+    tensor<float> out({rows, cols_padded});
+    out.zero();
+    if (rows > 0)
+        utils::CHECK_CUDA_EX(cudaMemcpy2DAsync(out.data(), size_t(cols_padded) * sizeof(float), src,
+                                               size_t(cols) * sizeof(float), size_t(cols) * sizeof(float), size_t(rows),
+                                               cudaMemcpyDeviceToDevice, Cuda::stream()));
+    return out;
+}
+}  // namespace
+
+// The GEMM's TMA loads need a row pitch that is a multiple of 16 bytes, so a layer whose in_features is
+// not a multiple of 16 keeps its codes (and quantises its inputs) with the K dimension zero-padded.
 template <typename TT>
 const fp8::Quantized& FullyConnectedLayer<TT>::quantized_weights() {
     if (wq_version_ != this->weights_.version()) {
-        fp8::quantize(this->weights_.data(), this->weights_.numel(), fp8::policy().weight_kind, wq_);
+        const int kp = padded_in();
+        if (kp == in_features_) {
+            fp8::quantize(this->weights_.data(), this->weights_.numel(), fp8::policy().weight_kind, wq_);
+        } else {
+            tensor<float> padded = pad_columns(this->weights_.data(), out_features_, in_features_, kp);
+            fp8::quantize(padded.data(), padded.numel(), fp8::policy().weight_kind, wq_);
+        }
         wq_version_ = this->weights_.version();
     }
     return wq_;
@@ -53,8 +74,26 @@ void FullyConnectedLayer<TT>::forward_codes(const uint8_t* a_codes, df8_kind a_k
                                             int flags, const float* residual, float* out, float* out_amax) {
     const fp8::Quantized& w = quantized_weights();
     utils::CHECK_DF8(df8_gemm_fp8_tn(a_codes, a_kind, a_scale, w.codes.data(), w.kind, w.scale.data(),
-                                     this->bias_.data(), residual, M, out_features_, in_features_, flags, out,
+                                     this->bias_.data(), residual, M, out_features_, padded_in(), flags, out,
                                      out_amax, fp8::stream()));
+}
+
+template <typename TT>
+void FullyConnectedLayer<TT>::forward_codes_quantized(const uint8_t* a_codes, df8_kind a_kind, const float* a_scale,
+                                                      int M, int flags, df8_kind out_kind, fp8::Quantized& q) {
+    const size_t n = size_t(M) * size_t(out_features_);
+    if (q.codes.numel() != n) q.codes = tensor<uint8_t>({int(n)});
+    q.kind = out_kind;
+    const fp8::Quantized& w = quantized_weights();
+    if (out_features_ % 32 == 0) {
+        utils::CHECK_DF8(df8_gemm_fp8_tn_q(a_codes, a_kind, a_scale, w.codes.data(), w.kind, w.scale.data(),
+                                           this->bias_.data(), M, out_features_, padded_in(), flags, out_kind,
+                                           q.codes.data(), q.scale.data(), q.amax.data(), fp8::stream()));
+        return;
+    }
+    tensor<float> f32({M, out_features_});
+    forward_codes(a_codes, a_kind, a_scale, M, flags | DF8_EPI_AMAX, nullptr, f32.data(), q.amax.data());
+    fp8::quantize_with_amax(f32.data(), n, out_kind, q.amax.data(), q);
 }
 
 template <typename TT>
@@ -67,7 +106,12 @@ tensor<TT> FullyConnectedLayer<TT>::forward(const tensor<TT>& input) {
     std::vector<int> out_shape(shape.begin(), shape.end() - 1);
     out_shape.push_back(out_features_);
     tensor<TT> output(out_shape);
-    fp8::quantize(input.data(), input.numel(), fp8::policy().activation_kind, xq_);
+    if (padded_in() == in_features_) {
+        fp8::quantize(input.data(), input.numel(), fp8::policy().activation_kind, xq_);
+    } else {
+        tensor<float> padded = pad_columns(input.data(), M, in_features_, padded_in());
+        fp8::quantize(padded.data(), padded.numel(), fp8::policy().activation_kind, xq_);
+    }
     forward_codes(xq_.codes.data(), xq_.kind, xq_.scale.data(), M, 0, nullptr, output.data(), nullptr);
     return output;
 }

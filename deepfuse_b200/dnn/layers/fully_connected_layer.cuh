@@ -37,13 +37,21 @@ public:
 
     int in_features() const { return in_features_; }
     int out_features() const { return out_features_; }
+    // K extent of the fp8 codes: in_features rounded up to a multiple of 16 (zero-padded)
+    int padded_in() const { return (in_features_ + 15) / 16 * 16; }
 
     // ---- fp8 path (additions; upstream has no counterpart) ----
     // Per-tensor quantised weights, refreshed if the fp32 weights changed since the last call.
     const fp8::Quantized& quantized_weights();
-    // out[M,out] = epilogue(codes . Wq^T); `flags` are DF8_EPI_* bits; out_amax may be null.
+    // out[M,out] = epilogue(codes . Wq^T); a_codes is [M, padded_in()]; `flags` are DF8_EPI_* bits;
+    // out_amax may be null.
     void forward_codes(const uint8_t* a_codes, df8_kind a_kind, const float* a_scale, int M, int flags,
                        const float* residual, float* out, float* out_amax);
+
+    // q <- per-tensor quantisation (kind out_kind) of epilogue(codes . Wq^T), `flags` = 0 or DF8_EPI_GELU.
+    // Uses the two-pass GEMM that never writes the fp32 result when out_features % 32 == 0.
+    void forward_codes_quantized(const uint8_t* a_codes, df8_kind a_kind, const float* a_scale, int M, int flags,
+                                 df8_kind out_kind, fp8::Quantized& q);
 
 private:
     int in_features_;

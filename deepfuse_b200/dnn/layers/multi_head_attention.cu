@@ -16,7 +16,6 @@ MultiHeadAttentionLayer<TT>::MultiHeadAttentionLayer(int embed_dim, int num_head
       softmax_(training_enabled),
       last_q_({1, 1}),
       last_attn_({1, 1}),
-      qkv_f32_({1}),
       attn_f32_({1}),
       amax_({1}) {
     if (embed_dim <= 0 || num_heads <= 0) throw std::runtime_error("embed_dim and num_heads must be positive");
@@ -45,13 +44,10 @@ void MultiHeadAttentionLayer<TT>::forward_quantized(const fp8::Quantized& xq, in
                                                     float* out) {
     const int M = B * T, E = embed_dim_;
     const df8_kind act = fp8::policy().activation_kind;
-    if (qkv_f32_.numel() != size_t(M) * 3 * E) qkv_f32_ = tensor<float>({M, 3 * E});
     if (attn_f32_.numel() != size_t(M) * E) attn_f32_ = tensor<float>({M, E});
 
-    // QKV projection, its max|.| reduced in the GEMM epilogue, then one quantise pass
-    qkv_proj_.forward_codes(xq.codes.data(), xq.kind, xq.scale.data(), M, DF8_EPI_AMAX, nullptr, qkv_f32_.data(),
-                            amax_.data());
-    fp8::quantize_with_amax(qkv_f32_.data(), qkv_f32_.numel(), act, amax_.data(), qkvq_);
+    // QKV projection straight to per-tensor-quantised codes (the fp32 [M,3E] tensor is never written)
+    qkv_proj_.forward_codes_quantized(xq.codes.data(), xq.kind, xq.scale.data(), M, 0, act, qkvq_);
 
     int mode = causal_ ? DF8_MASK_CAUSAL : DF8_MASK_NONE;
     const float* mask_ptr = nullptr;

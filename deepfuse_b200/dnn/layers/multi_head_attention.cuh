@@ -70,7 +70,7 @@ private:
     tensor<TT> last_q_, last_attn_;
     std::optional<tensor<TT>> input_cache_;
     // reused work buffers
-    tensor<float> qkv_f32_, attn_f32_;
+    tensor<float> attn_f32_;
     tensor<float> amax_;
     fp8::Quantized xq_, qkvq_, attnq_;
 };

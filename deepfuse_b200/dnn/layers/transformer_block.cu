@@ -15,9 +15,7 @@ TransformerBlock<T>::TransformerBlock(int embed_dim, int num_heads, int mlp_hidd
       attn_(embed_dim, num_heads, training_enabled),
       mlp_fc1_(embed_dim, mlp_hidden_dim, training_enabled),
       mlp_fc2_(mlp_hidden_dim, embed_dim, training_enabled),
-      x1_({1}),
-      hidden_f32_({1}),
-      amax_({1}) {}
+      x1_({1}) {}
 
 template <typename T>
 TransformerBlock<T>::~TransformerBlock() = default;
@@ -33,8 +31,9 @@ template <typename T>
 void TransformerBlock<T>::forward_inplace(float* x, int B, int T_len) {
     const int M = B * T_len, E = embed_dim_, F = mlp_hidden_dim_;
     const df8_kind act = fp8::policy().activation_kind;
+    if (E % 16 != 0 || F % 16 != 0)
+        throw std::runtime_error("TransformerBlock: embed_dim and mlp_hidden_dim must be multiples of 16 on the fp8 path");
     if (x1_.numel() != size_t(M) * E) x1_ = tensor<float>({M, E});
-    if (hidden_f32_.numel() != size_t(M) * F) hidden_f32_ = tensor<float>({M, F});
 
     // x1 = x + MHA(LN1(x))
     norm1_.forward_quantized(x, M, act, ln_q_);
@@ -42,9 +41,8 @@ void TransformerBlock<T>::forward_inplace(float* x, int B, int T_len) {
 
     // y = x1 + FC2(act(FC1(LN2(x1))))
     norm2_.forward_quantized(x1_.data(), M, act, ln_q_);
-    mlp_fc1_.forward_codes(ln_q_.codes.data(), ln_q_.kind, ln_q_.scale.data(), M,
-                           DF8_EPI_AMAX | (mlp_gelu_ ? DF8_EPI_GELU : 0), nullptr, hidden_f32_.data(), amax_.data());
-    fp8::quantize_with_amax(hidden_f32_.data(), hidden_f32_.numel(), act, amax_.data(), hidden_q_);
+    mlp_fc1_.forward_codes_quantized(ln_q_.codes.data(), ln_q_.kind, ln_q_.scale.data(), M,
+                                     mlp_gelu_ ? DF8_EPI_GELU : 0, act, hidden_q_);
     mlp_fc2_.forward_codes(hidden_q_.codes.data(), hidden_q_.kind, hidden_q_.scale.data(), M, DF8_EPI_RESIDUAL,
                            x1_.data(), x, nullptr);
 }

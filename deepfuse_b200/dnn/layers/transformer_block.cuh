@@ -9,7 +9,7 @@
 //
 // forward() runs the fused fp8 path: LayerNorm emits fp8 codes directly, both residual additions
 // happen inside GEMM epilogues (upstream: separate add kernels, transformer_block.cu:69,86), the QKV
-// and FC1 outputs are re-quantised with the max|.| their GEMM epilogues reduce, and none of the seven
+// and FC1 GEMMs emit per-tensor-quantised fp8 codes themselves, and none of the seven
 // activation clones upstream keeps (:60-83) is made unless training is enabled.
 #pragma once
 
@@ -72,7 +72,7 @@ private:
     std::optional<tensor<T>> input_cache_;
     // reused work buffers
     fp8::Quantized ln_q_, hidden_q_;
-    tensor<float> x1_, hidden_f32_, amax_;
+    tensor<float> x1_;
 };
 
 }  // namespace dnn

@@ -94,6 +94,17 @@ df8_status df8_gemm_fp8_tn(const uint8_t* a_codes, df8_kind kind_a, const float*
                            const float* bias, const float* residual, int M, int N, int K, int flags,
                            float* out, float* out_amax, df8_stream stream);
 
+/* Same product with per-tensor-quantised fp8 OUTPUT and no fp32 intermediate in memory:
+ *     out_codes[m,n] = fp8_out_kind( epi(acc*dq_a*dq_w + bias[n]) * q ),  q = FP8_MAX / max|epi(...)|
+ * The kernel runs twice — a first pass that only reduces max|.| into out_amax, a second that
+ * recomputes the tile and quantises it in the epilogue — which is bit-identical to df8_gemm_fp8_tn
+ * (+DF8_EPI_AMAX) followed by df8_quantize_f32, without the 4+4+1 bytes per element of HBM traffic.
+ * flags: 0 or DF8_EPI_GELU.  Needs K % 16 == 0 and N % 32 == 0.  Writes out_scale = {q, dq}. */
+df8_status df8_gemm_fp8_tn_q(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a,
+                             const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
+                             const float* bias, int M, int N, int K, int flags, df8_kind out_kind,
+                             uint8_t* out_codes, float* out_scale, float* out_amax, df8_stream stream);
+
 /* ---- fp8 attention -------------------------------------------------------------------------
  * Replaces, inside MultiHeadAttentionLayer::forward (dnn/layers/multi_head_attention.cu:204-308), the
  * Q/K/V slice + head-split copies (:231-260), both matmul_kernel launches (:266-270, :283-287),

@@ -1,0 +1,113 @@
+"""CPU oracle of the fp8 GPT-2 forward pipeline.  TEST INFRASTRUCTURE ONLY.
+
+Composes the per-kernel oracle functions (oracle/df8_oracle.cpp) in the order the upstream project wires
+its model: embedding + bias (dnn/tokens/token_embedding.cu:37-44), sinusoidal positions
+(dnn/tokens/positional_encoding.cu:20-27,44-47), pre-LayerNorm blocks (dnn/layers/transformer_block.cu:59-86:
+x1 = x + MHA(LN1(x)); y = x1 + FC2(act(FC1(LN2(x1))))), vocabulary head without a final LayerNorm
+(dnn/models/gpt2.cu:66-83).  Where the 8-bit path quantises, this does too, at the same places: every
+tensor that feeds a GEMM or the attention is quantised per tensor (scale = FP8_MAX / amax); weights are
+quantised once.  `gelu=False` reproduces upstream's block, which applies no activation (:79-81).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+import oracle as O
+
+
+def make_params(cfg: dict, seed: int, std: float = 0.02) -> dict:
+    """Seeded N(0, std) weights, zero biases, LayerNorm gamma 1 / beta 0, in the naming of
+    dnn_gpt2_param_info (include/df8_dnn.h)."""
+    V, E, F, L = cfg["vocab"], cfg["hidden"], cfg["ffn"], cfg["layers"]
+    p = {}
+    k = [seed * 1000]
+
+    def normal(shape):
+        k[0] += 1
+        return O.fill_normal(int(np.prod(shape)), seed=k[0], std=std).reshape(shape)
+
+    p["embedding.weight"] = normal((V, E))
+    p["embedding.bias"] = np.zeros(E, np.float32)
+    for i in range(L):
+        b = f"block{i}"
+        p[f"{b}.ln1.gamma"] = np.ones(E, np.float32)
+        p[f"{b}.ln1.beta"] = np.zeros(E, np.float32)
+        p[f"{b}.ln2.gamma"] = np.ones(E, np.float32)
+        p[f"{b}.ln2.beta"] = np.zeros(E, np.float32)
+        p[f"{b}.qkv.weight"] = normal((3 * E, E))
+        p[f"{b}.qkv.bias"] = np.zeros(3 * E, np.float32)
+        p[f"{b}.out.weight"] = normal((E, E))
+        p[f"{b}.out.bias"] = np.zeros(E, np.float32)
+        p[f"{b}.fc1.weight"] = normal((F, E))
+        p[f"{b}.fc1.bias"] = np.zeros(F, np.float32)
+        p[f"{b}.fc2.weight"] = normal((E, F))
+        p[f"{b}.fc2.bias"] = np.zeros(E, np.float32)
+    p["final_fc.weight"] = normal((V, E))
+    p["final_fc.bias"] = np.zeros(V, np.float32)
+    return p
+
+
+def _fc(x_f32, w, b, act_kind, w_kind, residual=None, gelu=False):
+    if act_kind is None:  # unquantised fp32 layer (upstream's FullyConnectedLayer math), for error budgets
+        y = O.fc_forward_f32(x_f32, w, b)
+        if gelu:
+            y = O.gelu(y)
+        return y + residual if residual is not None else y
+    xc, xs = O.quantize(x_f32, act_kind)
+    wc, ws = O.quantize(w, w_kind)
+    flags = (O.GELU if gelu else 0) | (O.RESIDUAL if residual is not None else 0)
+    return O.fc_forward_fp8(xc, act_kind, xs[1], wc, w_kind, ws[1], b, residual, flags)
+
+
+def _attention(qkv, B, T, heads, act_kind, mask_mode, mask):
+    E = qkv.shape[1] // 3
+    D = E // heads
+    if act_kind is not None:
+        qc, qs = O.quantize(qkv, act_kind)
+        return O.attention_fp8(qc, act_kind, qs[1], B, T, heads, D, mask_mode, mask)
+    # fp32 attention with the upstream softmax (softmax_layer.cu:26-81), numpy matmuls in float64
+    v = qkv.astype(np.float64).reshape(B, T, 3, heads, D)
+    q, k, val = (v[:, :, n].transpose(0, 2, 1, 3) for n in range(3))
+    scores = (q @ k.transpose(0, 1, 3, 2) / np.sqrt(D)).astype(np.float32)
+    if mask_mode == O.MASK_CAUSAL:
+        i, j = np.meshgrid(np.arange(T), np.arange(T), indexing="ij")
+        mask = np.where(j <= i, 0.0, -1e9).astype(np.float32)[None, None]
+    prob = O.softmax_masked(scores, mask if mask_mode != O.MASK_NONE else None).astype(np.float64)
+    return (prob @ val).transpose(0, 2, 1, 3).reshape(B * T, E).astype(np.float32)
+
+
+def block_forward(p: dict, prefix: str, x: np.ndarray, B: int, T: int, heads: int, act_kind: int, w_kind: int,
+                  gelu: bool, mask_mode: int = O.MASK_NONE, mask=None) -> np.ndarray:
+    """x [B*T, E] fp32 -> block output [B*T, E]."""
+    E = x.shape[1]
+    h = O.layernorm(x, p[f"{prefix}.ln1.gamma"], p[f"{prefix}.ln1.beta"], 1e-5)
+    qkv = _fc(h, p[f"{prefix}.qkv.weight"], p[f"{prefix}.qkv.bias"], act_kind, w_kind)
+    a = _attention(qkv, B, T, heads, act_kind, mask_mode, mask)
+    x1 = _fc(a, p[f"{prefix}.out.weight"], p[f"{prefix}.out.bias"], act_kind, w_kind, residual=x)
+    h2 = O.layernorm(x1, p[f"{prefix}.ln2.gamma"], p[f"{prefix}.ln2.beta"], 1e-5)
+    f = _fc(h2, p[f"{prefix}.fc1.weight"], p[f"{prefix}.fc1.bias"], act_kind, w_kind, gelu=gelu)
+    return _fc(f, p[f"{prefix}.fc2.weight"], p[f"{prefix}.fc2.bias"], act_kind, w_kind, residual=x1)
+
+
+def mha_forward(p: dict, prefix: str, x: np.ndarray, B: int, T: int, heads: int, act_kind: int, w_kind: int,
+                mask_mode: int = O.MASK_NONE, mask=None) -> np.ndarray:
+    """MultiHeadAttentionLayer::forward on x [B*T, E]: QKV projection, attention, output projection."""
+    qkv = _fc(x, p[f"{prefix}.qkv.weight"], p[f"{prefix}.qkv.bias"], act_kind, w_kind)
+    a = _attention(qkv, B, T, heads, act_kind, mask_mode, mask)
+    return _fc(a, p[f"{prefix}.out.weight"], p[f"{prefix}.out.bias"], act_kind, w_kind)
+
+
+def gpt2_forward(p: dict, ids: np.ndarray, cfg: dict, act_kind: int = O.E4M3, w_kind: int = O.E4M3, gelu: bool = True,
+                 causal: bool = False, return_hidden: bool = False) -> np.ndarray:
+    """ids [B,T] int32 -> logits [B*T, V] (or hidden states [B*T, E]).  act_kind=None runs the same wiring
+    in unquantised fp32 (the model the 8-bit path approximates)."""
+    B, T = ids.shape
+    E = cfg["hidden"]
+    pe = O.pe_table(cfg["max_seq_len"], E)
+    x = O.embed_pe(ids, p["embedding.weight"], p["embedding.bias"], pe).reshape(B * T, E)
+    mode = O.MASK_CAUSAL if causal else O.MASK_NONE
+    for i in range(cfg["layers"]):
+        x = block_forward(p, f"block{i}", x, B, T, cfg["heads"], act_kind, w_kind, gelu, mode)
+    if return_hidden:
+        return x
+    return _fc(x, p["final_fc.weight"], p["final_fc.bias"], act_kind, w_kind)

@@ -149,3 +149,50 @@ def test_gemm_rejects_bad_arguments(df8, cuda):
         df8.gemm_fp8_tn(a, 5, s, a, 0, s, None, None, 64, 64, 16, 0, out)
     with pytest.raises(df8.Df8Error, match="residual"):
         df8.gemm_fp8_tn(a, 0, s, a, 0, s, None, None, 64, 64, 16, 2, out)
+
+
+@pytest.mark.parametrize("out_kind", [0, 1])
+@pytest.mark.parametrize("M,N,K,flags", [(300, 768, 256, 0), (1024, 2304, 768, 0), (512, 3072, 768, 1), (64, 96, 48, 1)])
+def test_gemm_quantised_output_is_the_two_step_chain(df8, oracle, cuda, out_kind, M, N, K, flags):
+    """df8_gemm_fp8_tn_q (two tensor-core passes, no fp32 intermediate) must give, bit for bit, the codes and
+    scale of df8_gemm_fp8_tn + DF8_EPI_AMAX followed by df8_quantize_f32; and agree with the oracle chain."""
+    import torch
+
+    x = oracle.fill_normal(M * K, seed=31).reshape(M, K)
+    w = oracle.fill_normal(N * K, seed=32, std=0.05).reshape(N, K)
+    b = oracle.fill_normal(N, seed=33, std=0.1)
+    xc, sx = oracle.quantize(x, 0)
+    wc, sw = oracle.quantize(w, 0)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+    xcd, wcd, sxd, swd, bd = t(xc), t(wc), t(sx), t(sw), t(b)
+    # two-step chain
+    f32 = torch.empty((M, N), device=cuda)
+    amax = torch.zeros(1, device=cuda)
+    df8.gemm_fp8_tn(xcd, 0, sxd, wcd, 0, swd, bd, None, M, N, K, flags | 4, f32, amax)
+    codes_ref = torch.empty((M, N), dtype=torch.uint8, device=cuda)
+    scale_ref = torch.zeros(2, device=cuda)
+    df8.quantize_f32(f32, out_kind, amax, codes_ref, scale_ref)
+    # fused
+    codes = torch.full((M, N), 0xAA, dtype=torch.uint8, device=cuda)
+    scale = torch.zeros(2, device=cuda)
+    amax2 = torch.full((1,), -1.0, device=cuda)
+    df8.gemm_fp8_tn_q(xcd, 0, sxd, wcd, 0, swd, bd, M, N, K, flags, out_kind, codes, scale, amax2)
+    assert amax2.item() == amax.item()
+    assert torch.equal(scale, scale_ref)
+    assert torch.equal(codes, codes_ref), f"{(codes != codes_ref).sum().item()} code mismatches"
+    # oracle chain: fp8 GEMM -> per-tensor quantise (codes may differ where the fp32 sums differ in the last bit)
+    y = oracle.fc_forward_fp8(xc, 0, sx[1], wc, 0, sw[1], b, None, flags)
+    oc, osc = oracle.quantize(y, out_kind)
+    got = oracle.dequantize(codes.cpu().numpy(), out_kind, float(scale[1].item()))
+    assert rel_err(got, oracle.dequantize(oc, out_kind, osc[1])) <= (2 ** -3 if out_kind == 0 else 2 ** -2)
+    assert (codes.cpu().numpy() != oc).mean() < (0.02 if flags == 0 else 0.05)
+    assert df8.status_word() == (0, 0)
+
+
+def test_gemm_quantised_output_rejects_odd_n(df8, cuda):
+    import torch
+
+    a = torch.zeros(64 * 32, dtype=torch.uint8, device=cuda)
+    s = torch.ones(2, device=cuda)
+    with pytest.raises(df8.Df8Error, match="N % 32"):
+        df8.gemm_fp8_tn_q(a, 0, s, a, 0, s, None, 64, 40, 32, 0, 0, a, s, s)

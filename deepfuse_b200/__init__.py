@@ -47,6 +47,13 @@ _SIGNATURES = {
     "df8_attention_fp8": [_vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp, _vp],
     "df8_softmax_masked_f32": [_vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "df8_gemm_fp8_tn_q": [_vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
+    "df8_streamer_create": [_sz, _i, _i, _vp],
+    "df8_streamer_destroy": [_vp],
+    "df8_streamer_host_ptr": [_vp, _i, _vp],
+    "df8_streamer_prefetch": [_vp, _i],
+    "df8_streamer_acquire": [_vp, _i, _vp, _vp],
+    "df8_streamer_release": [_vp, _i, _vp],
+    "df8_streamer_stats": [_vp, _vp, _vp, _vp],
     "df8_status_word_read": [_vp, _vp],
     "df8_status_word_reset": [],
 }
@@ -184,6 +191,8 @@ _DNN_SIGNATURES = {
     "dnn_gpt2_forward_hidden": [_vp, _vp, _i, _i, _vp],
     "dnn_gpt2_forward_ids": [_vp, _vp, _i, _vp],
     "dnn_gpt2_save": [_vp, C.c_char_p],
+    "dnn_gpt2_enable_streaming": [_vp, _i, _i],
+    "dnn_gpt2_disable_streaming": [_vp],
     "dnn_fc_forward": [_i, _i, _vp, _vp, _vp, _i, _vp],
     "dnn_layernorm_forward": [_i, _i, _vp, _vp, _f, _vp, _vp],
     "dnn_softmax_forward": [_i, _i, _i, _vp, _vp, _i, _vp],
@@ -209,6 +218,8 @@ def dnn_lib() -> C.CDLL:
         handle.dnn_last_error.argtypes = []
         handle.dnn_gpt2_create.restype = C.c_void_p
         handle.dnn_gpt2_create.argtypes = [_i] * 6
+        handle.dnn_gpt2_streamed_bytes.restype = C.c_ulonglong
+        handle.dnn_gpt2_streamed_bytes.argtypes = [_vp]
         handle.dnn_gpt2_load.restype = C.c_void_p
         handle.dnn_gpt2_load.argtypes = [C.c_char_p]
         for name, args in _DNN_SIGNATURES.items():
@@ -273,6 +284,15 @@ class Gpt2:
 
     def set_options(self, gelu=True, causal=False):
         dnn_check(dnn_lib().dnn_gpt2_set_options(self.h, int(gelu), int(causal)), "dnn_gpt2_set_options")
+
+    def enable_streaming(self, slots=2, release_fp32=False):
+        dnn_check(dnn_lib().dnn_gpt2_enable_streaming(self.h, slots, int(release_fp32)), "dnn_gpt2_enable_streaming")
+
+    def disable_streaming(self):
+        dnn_check(dnn_lib().dnn_gpt2_disable_streaming(self.h), "dnn_gpt2_disable_streaming")
+
+    def streamed_bytes(self) -> int:
+        return int(dnn_lib().dnn_gpt2_streamed_bytes(self.h))
 
     def set_stream(self, stream=None):
         dnn_check(dnn_lib().dnn_set_stream(stream_ptr(stream)), "dnn_set_stream")

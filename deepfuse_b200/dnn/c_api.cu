@@ -334,3 +334,18 @@ extern "C" int dnn_block_forward(int B, int T, int E, int H, int F, const float*
         y.download(y_h);
     });
 }
+
+// ---- layer streaming ---------------------------------------------------------------------------
+
+extern "C" int dnn_gpt2_enable_streaming(dnn_gpt2* m, int slots, int release_fp32) {
+    return guarded([&] {
+        m->model->enable_layer_streaming(slots, release_fp32 != 0);
+        sync_stream();
+    });
+}
+
+extern "C" int dnn_gpt2_disable_streaming(dnn_gpt2* m) {
+    return guarded([&] { m->model->disable_layer_streaming(); });
+}
+
+extern "C" unsigned long long dnn_gpt2_streamed_bytes(dnn_gpt2* m) { return m ? m->model->streamed_bytes() : 0ull; }

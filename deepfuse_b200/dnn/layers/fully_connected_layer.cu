@@ -70,10 +70,24 @@ const fp8::Quantized& FullyConnectedLayer<TT>::quantized_weights() {
 }
 
 template <typename TT>
+void FullyConnectedLayer<TT>::export_weight_codes(uint8_t* dst_h) {
+    const fp8::Quantized& w = quantized_weights();
+    utils::CHECK_CUDA_EX(cudaMemcpyAsync(dst_h, w.codes.data(), weight_code_bytes(), cudaMemcpyDeviceToHost, Cuda::stream()));
+    utils::CHECK_CUDA_EX(cudaStreamSynchronize(Cuda::stream()));
+}
+
+template <typename TT>
+void FullyConnectedLayer<TT>::drop_cached_codes() {
+    quantized_weights();  // make sure the scale is current before the codes go away
+    wq_.codes = tensor<uint8_t>({0});
+}
+
+template <typename TT>
 void FullyConnectedLayer<TT>::forward_codes(const uint8_t* a_codes, df8_kind a_kind, const float* a_scale, int M,
                                             int flags, const float* residual, float* out, float* out_amax) {
     const fp8::Quantized& w = quantized_weights();
-    utils::CHECK_DF8(df8_gemm_fp8_tn(a_codes, a_kind, a_scale, w.codes.data(), w.kind, w.scale.data(),
+    const uint8_t* w_codes = external_codes_ ? external_codes_ : w.codes.data();
+    utils::CHECK_DF8(df8_gemm_fp8_tn(a_codes, a_kind, a_scale, w_codes, w.kind, w.scale.data(),
                                      this->bias_.data(), residual, M, out_features_, padded_in(), flags, out,
                                      out_amax, fp8::stream()));
 }
@@ -85,8 +99,9 @@ void FullyConnectedLayer<TT>::forward_codes_quantized(const uint8_t* a_codes, df
     if (q.codes.numel() != n) q.codes = tensor<uint8_t>({int(n)});
     q.kind = out_kind;
     const fp8::Quantized& w = quantized_weights();
+    const uint8_t* w_codes = external_codes_ ? external_codes_ : w.codes.data();
     if (out_features_ % 32 == 0) {
-        utils::CHECK_DF8(df8_gemm_fp8_tn_q(a_codes, a_kind, a_scale, w.codes.data(), w.kind, w.scale.data(),
+        utils::CHECK_DF8(df8_gemm_fp8_tn_q(a_codes, a_kind, a_scale, w_codes, w.kind, w.scale.data(),
                                            this->bias_.data(), M, out_features_, padded_in(), flags, out_kind,
                                            q.codes.data(), q.scale.data(), q.amax.data(), fp8::stream()));
         return;

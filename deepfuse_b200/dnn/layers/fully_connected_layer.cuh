@@ -53,7 +53,21 @@ public:
     void forward_codes_quantized(const uint8_t* a_codes, df8_kind a_kind, const float* a_scale, int M, int flags,
                                  df8_kind out_kind, fp8::Quantized& q);
 
+    // Layer streaming: when set, the GEMMs read the weight codes from `codes` (a device slot filled by
+    // the streamer) instead of the layer's own cached copy, which may then be dropped; the scale stays
+    // resident.  nullptr returns to the cached copy.
+    void use_external_codes(const uint8_t* codes) { external_codes_ = codes; }
+    // Size in bytes of this layer's weight codes, and a copy of them into HOST memory (synchronises).
+    size_t weight_code_bytes() const { return size_t(out_features_) * size_t(padded_in()); }
+    void export_weight_codes(uint8_t* dst_h);
+    // Frees the device copy of the weight codes (streaming mode keeps them in pinned host memory).
+    void drop_cached_codes();
+    // Declares the cached scale current for the present weights tensor / forces a re-quantisation.
+    void mark_weights_quantized() { wq_version_ = this->weights_.version(); }
+    void invalidate_quantized_weights() { wq_version_ = ~0ull; }
+
 private:
+    const uint8_t* external_codes_ = nullptr;
     int in_features_;
     int out_features_;
     std::optional<tensor<TT>> input_cache_;

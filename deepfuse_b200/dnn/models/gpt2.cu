@@ -71,7 +71,26 @@ tensor<T> Gpt2<T>::forward_hidden(const tensor<int>& ids, bool check_ids) {
     if (T_len > positional_encoding_->max_seq_len())
         throw std::runtime_error("Input sequence length exceeds maximum allowed length");
     tensor<T> x = token_embedding_->forward_with_positions(ids, positional_encoding_->table().data(), check_ids);
-    for (auto& block : transformer_blocks_) block->forward_inplace(x.data(), B, T_len);
+    if (!streamer_) {
+        for (auto& block : transformer_blocks_) block->forward_inplace(x.data(), B, T_len);
+        return x;
+    }
+    const int L = int(transformer_blocks_.size());
+    for (int l = 0; l < L; ++l) {
+        TransformerBlock<T>& blk = *transformer_blocks_[size_t(l)];
+        void* slot = nullptr;
+        utils::CHECK_DF8(df8_streamer_acquire(streamer_, l, fp8::stream(), &slot));
+        const uint8_t* p = static_cast<const uint8_t*>(slot);
+        FullyConnectedLayer<T>* fcs[4] = {&blk.attention().qkv_projection(), &blk.attention().out_projection(),
+                                          &blk.mlp_fc1(), &blk.mlp_fc2()};
+        for (FullyConnectedLayer<T>* fc : fcs) {
+            fc->use_external_codes(p);
+            p += (fc->weight_code_bytes() + 255) & ~size_t(255);
+        }
+        blk.forward_inplace(x.data(), B, T_len);
+        utils::CHECK_DF8(df8_streamer_release(streamer_, l, fp8::stream()));
+        utils::CHECK_DF8(df8_streamer_prefetch(streamer_, (l + stream_slots_) % L));
+    }
     return x;
 }
 
@@ -84,6 +103,66 @@ tensor<T> Gpt2<T>::forward_logits(const tensor<int>& ids, bool check_ids) {
     final_fc_->forward_codes(head_q_.codes.data(), head_q_.kind, head_q_.scale.data(), M, 0, nullptr, logits.data(),
                              nullptr);
     return logits;
+}
+
+template <typename T>
+Gpt2<T>::~Gpt2() {
+    if (streamer_) df8_streamer_destroy(streamer_);
+}
+
+template <typename T>
+void Gpt2<T>::enable_layer_streaming(int slots, bool release_fp32) {
+    if (streamer_ || transformer_blocks_.empty()) return;
+    const int L = int(transformer_blocks_.size());
+    auto fcs_of = [](TransformerBlock<T>& blk) {
+        return std::vector<FullyConnectedLayer<T>*>{&blk.attention().qkv_projection(), &blk.attention().out_projection(),
+                                                    &blk.mlp_fc1(), &blk.mlp_fc2()};
+    };
+    size_t layer_bytes = 0;
+    for (FullyConnectedLayer<T>* fc : fcs_of(*transformer_blocks_[0])) layer_bytes += (fc->weight_code_bytes() + 255) & ~size_t(255);
+    utils::CHECK_DF8(df8_streamer_create(layer_bytes, slots, L, &streamer_));
+    int n_slots = 0;
+    utils::CHECK_DF8(df8_streamer_stats(streamer_, nullptr, nullptr, &n_slots));
+    stream_slots_ = n_slots;
+    for (int l = 0; l < L; ++l) {
+        void* host = nullptr;
+        utils::CHECK_DF8(df8_streamer_host_ptr(streamer_, l, &host));
+        uint8_t* p = static_cast<uint8_t*>(host);
+        for (FullyConnectedLayer<T>* fc : fcs_of(*transformer_blocks_[size_t(l)])) {
+            fc->export_weight_codes(p);
+            p += (fc->weight_code_bytes() + 255) & ~size_t(255);
+            fc->drop_cached_codes();
+            if (release_fp32) {
+                // keep version(): the cached scale must stay valid
+                *fc->weights() = tensor<T>({0, fc->in_features()});
+                fc->mark_weights_quantized();
+            }
+        }
+    }
+    for (int l = 0; l < stream_slots_; ++l) utils::CHECK_DF8(df8_streamer_prefetch(streamer_, l));
+}
+
+template <typename T>
+void Gpt2<T>::disable_layer_streaming() {
+    if (!streamer_) return;
+    utils::CHECK_CUDA_EX(cudaStreamSynchronize(Cuda::stream()));
+    for (auto& blk : transformer_blocks_) {
+        FullyConnectedLayer<T>* fcs[4] = {&blk->attention().qkv_projection(), &blk->attention().out_projection(),
+                                          &blk->mlp_fc1(), &blk->mlp_fc2()};
+        for (FullyConnectedLayer<T>* fc : fcs) {
+            fc->use_external_codes(nullptr);
+            fc->invalidate_quantized_weights();  // re-quantise from the fp32 weights on next use
+        }
+    }
+    df8_streamer_destroy(streamer_);
+    streamer_ = nullptr;
+}
+
+template <typename T>
+unsigned long long Gpt2<T>::streamed_bytes() const {
+    unsigned long long b = 0;
+    if (streamer_) df8_streamer_stats(streamer_, &b, nullptr, nullptr);
+    return b;
 }
 
 template <typename T>

@@ -58,6 +58,17 @@ public:
     void set_mlp_gelu(bool on);
     void set_causal(bool causal);
 
+    // Layer streaming (README.md:212-220 sketches `layer->load_weights_to_gpu()`; no such code exists
+    // upstream).  The e4m3 codes of every block's four weight matrices move to pinned host memory; the
+    // device keeps `slots` layer-sized buffers; during a forward the upload of layer l+slots runs on a side
+    // stream while layer l computes.  Scales, biases and LayerNorm parameters stay resident.
+    // release_fp32 also frees the blocks' fp32 master weights on the device (weights() then returns
+    // empty tensors; re-uploading them requires disabling streaming first).
+    void enable_layer_streaming(int slots = 2, bool release_fp32 = false);
+    void disable_layer_streaming();
+    bool layer_streaming() const { return streamer_ != nullptr; }
+    unsigned long long streamed_bytes() const;
+
     int vocab_size() const { return vocab_size_; }
     int hidden_dim() const { return hidden_dim_; }
     int num_layers() const { return int(transformer_blocks_.size()); }
@@ -77,6 +88,11 @@ private:
     std::vector<std::unique_ptr<TransformerBlock<T>>> transformer_blocks_;
     std::unique_ptr<FullyConnectedLayer<T>> final_fc_;
     fp8::Quantized head_q_;
+    df8_streamer* streamer_ = nullptr;
+    int stream_slots_ = 0;
+
+public:
+    ~Gpt2() override;
 };
 
 }  // namespace dnn

@@ -159,6 +159,27 @@ df8_status df8_embed_pe_f32(const int32_t* ids, int B, int T, int E, int V, cons
                             const float* bias, const float* pe, float* out, int32_t* bad_ids,
                             df8_stream stream);
 
+/* ---- layer-streaming weight upload -----------------------------------------------------------
+ * Pinned host arena holding one byte blob per layer + a ring of device slots + a copy stream, after
+ * the slot-ring loader of apps/host-multi/NVMeLoader_Linux.hpp:38-183 (pinned slots, per-slot stream,
+ * cudaMemcpyAsync, (pointer, size, stream) hand-off at :90-134).  Usage per layer l of a forward:
+ *     acquire(l, compute)  -> device pointer of the layer's bytes; compute stream waits for the upload
+ *     ... launch the layer's kernels on the compute stream ...
+ *     release(l, compute)  -> the slot may be overwritten once those kernels are done
+ *     prefetch((l + n_slots) % n_layers)   -> upload of a later layer overlaps the following compute
+ * create allocates (cudaHostAlloc, cudaMalloc, stream, events); destroy frees.  The other calls
+ * neither allocate nor synchronise.  Not thread-safe: one streamer per model per host thread. */
+typedef struct df8_streamer df8_streamer;
+df8_status df8_streamer_create(size_t slot_bytes, int n_slots, int n_layers, df8_streamer** out);
+df8_status df8_streamer_destroy(df8_streamer* s);
+/* host_ptr_h receives the pinned HOST address where layer `layer`'s slot_bytes bytes are kept */
+df8_status df8_streamer_host_ptr(df8_streamer* s, int layer, void** host_ptr_h);
+df8_status df8_streamer_prefetch(df8_streamer* s, int layer);
+df8_status df8_streamer_acquire(df8_streamer* s, int layer, df8_stream compute_stream, void** dev_ptr_h);
+df8_status df8_streamer_release(df8_streamer* s, int layer, df8_stream compute_stream);
+df8_status df8_streamer_stats(df8_streamer* s, unsigned long long* bytes_uploaded_h, size_t* slot_bytes_h,
+                              int* n_slots_h);
+
 /* ---- bounded-wait status word --------------------------------------------------------------
  * Every device-side wait (mbarrier polls in the GEMM and attention pipelines) gives up after a
  * time limit instead of hanging the GPU; the first such event stores a non-zero code.  Upstream

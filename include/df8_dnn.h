@@ -47,6 +47,11 @@ int dnn_gpt2_forward_logits_host(dnn_gpt2* m, const int32_t* ids_h, int B, int T
 int dnn_gpt2_forward_hidden(dnn_gpt2* m, const int32_t* ids_d, int B, int T, float** hidden_d);
 /* the model's own public batch-1 entry point, Gpt2::forward(std::vector<int>): hidden [1,T,E] to host */
 int dnn_gpt2_forward_ids(dnn_gpt2* m, const int32_t* ids_h, int T, float* hidden_h);
+/* Gpt2::enable_layer_streaming: block weight codes move to pinned host memory and are uploaded per layer
+ * through `slots` device buffers on a side stream; release_fp32 also frees the fp32 block weights. */
+int dnn_gpt2_enable_streaming(dnn_gpt2* m, int slots, int release_fp32);
+int dnn_gpt2_disable_streaming(dnn_gpt2* m);
+unsigned long long dnn_gpt2_streamed_bytes(dnn_gpt2* m);
 int dnn_gpt2_save(dnn_gpt2* m, const char* path);
 dnn_gpt2* dnn_gpt2_load(const char* path);
 

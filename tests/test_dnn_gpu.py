@@ -252,3 +252,35 @@ def test_gpt2_save_load_round_trip(df8, dnn, oracle, cuda, tmp_path):
     dnn.dnn_gpt2_destroy(h2)
     assert not dnn.dnn_gpt2_load(b"/nonexistent/file.bin")
     model.close()
+
+
+@pytest.mark.parametrize("slots,release", [(2, False), (3, True), (1, False)])
+def test_gpt2_layer_streaming_is_bit_identical(df8, dnn, oracle, cuda, slots, release):
+    """Weights streamed per layer from pinned host memory through a ring of device slots must give exactly
+    the logits of the resident-weights forward, on repeated forwards (ring wrap-around), on a side stream."""
+    import torch
+    from oracle import gpt2_ref
+
+    cfg = dict(vocab=300, max_seq_len=64, layers=5, heads=2, hidden=128, ffn=512)
+    prm = gpt2_ref.make_params(cfg, seed=11, std=0.05)
+    model = df8.Gpt2(**cfg)
+    model.load_params(prm)
+    ids = torch.from_numpy(oracle.fill_token_ids(3 * 64, seed=4, vocab=300).reshape(3, 64)).to(cuda)
+    want = df8.device_view(torch, model.forward_logits(ids), (3 * 64, 300)).clone()
+    model.enable_streaming(slots, release)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        model.set_stream(side)
+        for _ in range(3):
+            got = df8.device_view(torch, model.forward_logits(ids), (3 * 64, 300)).clone()
+            assert torch.equal(got, want)
+        side.synchronize()
+    model.set_stream(torch.cuda.current_stream())
+    layer_bytes = (3 * 128 * 128 + 128 * 128 + 2 * 128 * 512)
+    assert model.streamed_bytes() >= 3 * 5 * layer_bytes
+    if not release:
+        model.disable_streaming()
+        again = df8.device_view(torch, model.forward_logits(ids), (3 * 64, 300)).clone()
+        assert torch.equal(again, want)
+    assert df8.status_word() == (0, 0)
+    model.close()

@@ -358,6 +358,8 @@ class Gpt2Workload:
                             f"d_model {c['hidden']}, {c['heads']} heads, FFN {c['ffn']}, vocab {c['vocab']}, "
                             f"batch {self.B}x{self.T} token ids per GPU, fp32 logits, random-init N(0,0.02) weights",
                 "global_batch": self.B * n_gpus, "seq_len": self.T,
+                "weights": ("e4m3 codes of the block weights in pinned host memory, streamed per layer through 2 "
+                            "device slots on a side stream") if self.name == "gpt2m" else "resident e4m3 codes",
                 "l2_policy": "working set per forward (1.65 GB of logits alone) larger than L2",
                 "parallelism": f"batch-sharded x{n_gpus}, weights replicated, no data-path collective"}
 
@@ -378,6 +380,8 @@ class Gpt2Workload:
         self.model.set_stream(torch.cuda.current_stream())
         self.model.load_params(gpt2_ref.make_params(cfg, seed=2 if self.name == "gpt2s" else 3))
         self.model.set_options(gelu=True, causal=False)
+        if self.name == "gpt2m":  # e4m3 weights held in pinned host memory, streamed per layer
+            self.model.enable_streaming(slots=2, release_fp32=True)
         ids = orc.fill_token_ids(self.B * self.T, seed=100 + rank, vocab=c["vocab"]).reshape(self.B, self.T)
         self.ids = torch.from_numpy(ids).to(dev)
         self.ids_host = torch.from_numpy(ids).pin_memory()
@@ -451,7 +455,88 @@ class Gpt2Workload:
         return tokens, secs, (f"one transformer block + the vocabulary head on 1x{tokens} tokens, extrapolated "
                               f"linearly in flops to {GPT2_CONFIGS[self.name]['layers']} blocks at context {self.T}")
 
-WORKLOADS = {"quant": QuantWorkload, "gemm": GemmWorkload, "gpt2s": Gpt2Workload, "gpt2m": Gpt2Workload}
+
+class AttnWorkload:
+    """df8_attention_fp8 on a GPT-2 small sized QKV code buffer (B=8, T=1024, H=12, D=64), non-causal."""
+
+    name = "attn"
+    metric = "fp8 attention TFLOP/s"
+    unit = "TFLOP/s"
+    dtype = "e4m3 QKV -> f32"
+    kernels_per_step = 1
+
+    def __init__(self, B=8, T=1024, H=12, D=64):
+        self.B, self.T, self.H, self.D = B, T, H, D
+
+    def config(self, n_gpus):
+        return {"workload": f"attention B={self.B} T={self.T} H={self.H} D={self.D}, e4m3 codes, no mask",
+                "l2_policy": "L2 flushed by a 256 MiB write between steps", "parallelism": f"replicated x{n_gpus}"}
+
+    def units_per_step(self):
+        return 4.0 * self.B * self.H * self.T * self.T * self.D / 1e12
+
+    def setup(self, torch, df8, dev, rank):
+        self.torch, self.df8 = torch, df8
+        g = torch.Generator(device=dev)
+        g.manual_seed(3)
+        E = self.H * self.D
+        x = torch.randn(self.B * self.T, 3 * E, device=dev, generator=g)
+        self.codes = torch.empty(x.shape, dtype=torch.uint8, device=dev)
+        self.scale, amax = torch.zeros(2, device=dev), torch.zeros(1, device=dev)
+        df8.amax_f32(x, amax)
+        df8.quantize_f32(x, 0, amax, self.codes, self.scale)
+        self.out = torch.empty(self.B * self.T, E, device=dev)
+        self.amax = torch.zeros(1, device=dev)
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step(self):
+        self.flush.zero_()
+        self.df8.attention_fp8(self.codes, 0, self.scale, self.B, self.T, self.H, self.D, 0, None, self.out, self.amax)
+
+    def roofline(self, torch, peaks, iters=20):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        torch.cuda.synchronize()
+        ev[0].record()
+        for _ in range(iters):
+            self.df8.attention_fp8(self.codes, 0, self.scale, self.B, self.T, self.H, self.D, 0, None, self.out, self.amax)
+        ev[1].record()
+        torch.cuda.synchronize()
+        ms = ev[0].elapsed_time(ev[1]) / iters
+        tf = self.units_per_step() / (ms / 1e3)
+        peak = 2.0 * peaks["bf16_tflops"]
+        return {"kernel": "attention_fp8_kernel<64>", "bound": "tensor", "achieved": round(tf, 1), "peak": peak,
+                "peak_source": peaks["source"] + " bf16 burst x2 (fp8 dense)", "unit": "TFLOP/s",
+                "frac": round(tf / peak, 4), "ms_per_launch": round(ms, 4),
+                "algorithmic_flops_per_launch": self.units_per_step() * 1e12, "traffic": None}
+
+    def e2e_setup(self, torch, dev):
+        self.h_codes = torch.empty(self.codes.shape, dtype=torch.uint8, pin_memory=True)
+        self.h_codes.copy_(self.codes)
+        self.h_out = torch.empty(self.out.shape[0], dtype=torch.float32, pin_memory=True)
+
+    def e2e_step(self):
+        self.codes.copy_(self.h_codes, non_blocking=True)
+        self.step()
+        self.h_out.copy_(self.out[:, 0], non_blocking=True)
+
+    def e2e_units_per_step(self):
+        return self.units_per_step()
+
+    def e2e_bytes(self):
+        return self.h_codes.numel(), self.h_out.numel() * 4
+
+    def cpu_sample(self, orc, T=256):
+        import numpy as np
+
+        E = self.H * self.D
+        rng = np.random.default_rng(0)
+        codes = rng.integers(0, 0x70, (T, 3 * E), dtype=np.uint8)
+        t0 = time.perf_counter()
+        orc.attention_fp8(codes, orc.E4M3, 0.01, 1, T, self.H, self.D)
+        dt = time.perf_counter() - t0
+        return 4.0 * self.H * T * T * self.D / 1e12, dt, f"one sequence of {T} tokens, {self.H} heads"
+
+WORKLOADS = {"attn": AttnWorkload, "quant": QuantWorkload, "gemm": GemmWorkload, "gpt2s": Gpt2Workload, "gpt2m": Gpt2Workload}
 DEFAULT_WORKLOAD = "gpt2s"
 
 

@@ -54,6 +54,14 @@ _SIGNATURES = {
     "df8_streamer_acquire": [_vp, _i, _vp, _vp],
     "df8_streamer_release": [_vp, _i, _vp],
     "df8_streamer_stats": [_vp, _vp, _vp, _vp],
+    "df8_comm_available": [_vp],
+    "df8_comm_unique_id": [_vp],
+    "df8_comm_init_rank": [_vp, _i, _i, _vp],
+    "df8_comm_destroy": [_vp],
+    "df8_comm_abort": [_vp],
+    "df8_comm_rank": [_vp, _vp, _vp],
+    "df8_comm_allgather_u8": [_vp, _vp, _vp, _sz, _vp],
+    "df8_comm_allreduce_max_f32": [_vp, _vp, _sz, _vp],
     "df8_status_word_read": [_vp, _vp],
     "df8_status_word_reset": [],
 }

@@ -19,8 +19,9 @@
 //   warp 0     TMA producer: Q tile once, then K/V tiles through a 2-stage ring
 //   warp 1     MMA issuer:   S = Q.K^T (M=128, N=128, K=D) and O_blk = P.V (M=128, N=D, K=128),
 //                            V consumed as an N-major operand straight from its [keys, D] tile
-//   warps 2-5  softmax:      thread = query row; tcgen05.ld of S, exp2, P -> swizzled smem as the
-//                            A operand of the PV product, running O in registers
+//   warps 2-5  softmax:      thread = query row; tcgen05.ld of the whole score row, exp2, P -> swizzled smem
+//                            as the A operand of the PV product.  O accumulates in TMEM across key blocks and
+//                            is rescaled (tcgen05.ld/st) only when the row maximum has grown past a threshold
 // All mbarrier waits are bounded (status word, see df8_status_word_read).
 #include "df8_internal.cuh"
 #include "sm100_ptx.cuh"
@@ -165,6 +166,8 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
             }
             for (int j = 0; j < n_kv && ok; ++j) {
                 if (j + 1 < n_kv) {
+                    // the softmax warps release S as soon as they hold block j's scores in registers, so
+                    // the next block's Q.K^T runs underneath their exponentials
                     const int s1 = (j + 1) & 1;
                     if (!mbar_wait_bounded(smem_u32(kv_full + s1), ((j + 1) >> 1) & 1) ||
                         !mbar_wait_bounded(smem_u32(s_empty), j & 1)) {
@@ -179,6 +182,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                     break;
                 }
                 tc_fence_after_sync();
+                // O (+)= P.V, accumulated in TMEM over the key blocks; P = leading part + remainder
                 const uint32_t va = smem_u32(sKV + (j & 1) * Cfg::kStageBytes + Cfg::kKBytes);
 #pragma unroll
                 for (int part = 0; part < 2; ++part) {
@@ -186,9 +190,10 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
 #pragma unroll
                     for (int k = 0; k < BKV / 32; ++k)
                         tc_mma_f8(tmem_o, make_desc_kmajor<128>(pa + k * 32),
-                                  make_desc_mnmajor<SW>(va + k * 32 * D, 8 * SW), args.idesc_pv, (part | k) != 0);
+                                  make_desc_mnmajor<SW>(va + k * 32 * D, 8 * SW), args.idesc_pv,
+                                  (j | part | k) != 0);
                 }
-                tc_commit(smem_u32(o_full));
+                tc_commit(smem_u32(o_full));  // "P.V of block j done": P is free, O may be touched
                 tc_commit(smem_u32(kv_empty + (j & 1)));
             }
         }
@@ -203,12 +208,17 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
         if (args.mask_mode == 2 && qi < T)
             mrow = args.mask + (size_t(args.mask_b > 1 ? b : 0) * T + qi) * T;
 
-        float m = -INFINITY;  // running max (log2 domain)
-        float l = 0.f;        // running sum of 256 * p
-        float acc[D];
-#pragma unroll
-        for (int d = 0; d < D; ++d) acc[d] = 0.f;
+        // Probabilities are formed as p' = 2^kPShift * exp2(t - m) against a reference maximum m that is only
+        // moved (and O, l rescaled) when the true running maximum has grown by more than kLazy: then
+        // p' <= 2^(kPShift + kLazy) stays inside e4m3 (max 448), and the TMEM round trip that rescales O
+        // is rare after the first key blocks.
+        constexpr float kPShift = 6.0f;
+        constexpr float kLazy = 2.5f;
+        float m = -INFINITY;       // reference maximum of the exponentials (log2 domain)
+        float m_true = -INFINITY;  // true running maximum
+        float l = 0.f;             // running sum of p'
         bool ok = true;
+        int pv_waited = 0;         // number of "P.V done" phases this thread has observed
 
         for (int j = 0; j < n_kv; ++j) {
             const int k0 = j * BKV;
@@ -218,51 +228,105 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                 break;
             }
             tc_fence_after_sync();
-            const bool edge = (k0 + BKV > T) || (args.mask_mode == 1 && k0 + BKV - 1 > q0) || (args.mask_mode == 2);
-
-            auto score = [&](uint32_t raw, int kj) -> float {
-                float t = __uint_as_float(raw) * cs;
-                if (edge) {
-                    if (kj >= T) return -INFINITY;
-                    if (args.mask_mode == 1 && kj > qi) return -INFINITY;
-                    if (mrow) {
-                        const float mv = mrow[kj];
-                        if (mv < -1e8f) return -INFINITY;
-                        t = fmaf(mv, kLog2e, t);
-                    }
-                }
-                return t;
-            };
-
-            // pass 1: block row maximum
-            float mb = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < BKV / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
-                tmem_ld_wait();
+            // the whole 128-column score row into registers, then S is released at once
+            uint32_t r[BKV];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mb = fmaxf(mb, score(r[i], k0 + c * 32 + i));
-            }
-            const float m_new = fmaxf(m, mb);
-            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            const float alpha = ex2(m - m_use);  // 0 when m is still -inf
-            const float shift = m_use - 8.0f;    // p' = 256 * exp2(t - m_use)
+            for (int c = 0; c < BKV / 32; ++c)
+                tmem_ld_32x32(tmem_s + lane_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+            tmem_ld_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(s_empty));
 
-            // pass 2: probabilities -> e4m3 -> swizzled smem (A operand of the PV product)
+            const bool edge = (k0 + BKV > T) || (args.mask_mode == 1 && k0 + BKV - 1 > q0) || (args.mask_mode == 2);
+            float mb = -INFINITY;
+            if (!edge) {
+                float raw = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < BKV; ++i) raw = fmaxf(raw, __uint_as_float(r[i]));
+                mb = raw * cs;  // cs > 0: the maximum commutes with the scaling
+#pragma unroll
+                for (int i = 0; i < BKV; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * cs);
+            } else {
+#pragma unroll
+                for (int i = 0; i < BKV; ++i) {
+                    const int kj = k0 + i;
+                    float t = __uint_as_float(r[i]) * cs;
+                    if (kj >= T || (args.mask_mode == 1 && kj > qi)) {
+                        t = -INFINITY;
+                    } else if (mrow) {
+                        const float mv = mrow[kj];
+                        t = (mv < -1e8f) ? -INFINITY : fmaf(mv, kLog2e, t);
+                    }
+                    r[i] = __float_as_uint(t);
+                    mb = fmaxf(mb, t);
+                }
+            }
+            m_true = fmaxf(m_true, mb);
+
+            // move the reference maximum?  (always on the first block that has an unmasked key)
+            const bool move = m_true > m + kLazy;  // also true while m is -inf and m_true is finite
+            if (__any_sync(0xffffffffu, move)) {
+                float alpha = 1.f;
+                if (move) {
+                    alpha = ex2(m - m_true);  // 0 when m was -inf
+                    m = m_true;
+                    l *= alpha;
+                }
+                if (j > 0) {
+                    // O holds the products of blocks < j: wait until the last of them has landed, scale the row
+                    while (pv_waited < j) {
+                        if (!mbar_wait_bounded(smem_u32(o_full), pv_waited & 1)) {
+                            ok = false;
+                            break;
+                        }
+                        ++pv_waited;
+                    }
+                    if (!__all_sync(0xffffffffu, ok)) {
+                        if (lane == 0) record_timeout(args.status, 0x1600u);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t o[32];
+                        tmem_ld_32x32(tmem_o + lane_addr + c * 32, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st_32x32(tmem_o + lane_addr + c * 32, o);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            const float shift = ((m == -INFINITY) ? 0.f : m) - kPShift;
+
+            // P must not be overwritten before the previous block's P.V has read it
+            while (pv_waited < j) {
+                if (!mbar_wait_bounded(smem_u32(o_full), pv_waited & 1)) {
+                    ok = false;
+                    break;
+                }
+                ++pv_waited;
+            }
+            if (!__all_sync(0xffffffffu, ok)) {
+                if (lane == 0) record_timeout(args.status, 0x1700u);
+                ok = false;
+                break;
+            }
+
             float psum = 0.f;
-#pragma unroll 1
+            uint8_t* prow = sP + row * 128;
+#pragma unroll
             for (int c = 0; c < BKV / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
-                tmem_ld_wait();
                 uint32_t w[8], wl[8];
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
                     float p[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        p[i] = ex2(score(r[4 * g + i], k0 + c * 32 + 4 * g + i) - shift);
+                        p[i] = ex2(__uint_as_float(r[c * 32 + 4 * g + i]) - shift);
                         psum += p[i];
                     }
                     w[g] = cvt_f32x4_to_fp8x4<DF8_E4M3>(p[0], p[1], p[2], p[3]);
@@ -270,55 +334,55 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                     const float2 h23 = cvt_fp8x2_to_f32x2<DF8_E4M3>(uint16_t(w[g] >> 16));
                     wl[g] = cvt_f32x4_to_fp8x4<DF8_E4M3>(p[0] - h01.x, p[1] - h01.y, p[2] - h23.x, p[3] - h23.y);
                 }
-                uint8_t* prow = sP + row * 128;
                 const int o0 = ((2 * c) ^ (row & 7)) << 4, o1 = ((2 * c + 1) ^ (row & 7)) << 4;
                 *reinterpret_cast<uint4*>(prow + o0) = make_uint4(w[0], w[1], w[2], w[3]);
                 *reinterpret_cast<uint4*>(prow + o1) = make_uint4(w[4], w[5], w[6], w[7]);
                 *reinterpret_cast<uint4*>(prow + BQ * BKV + o0) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
                 *reinterpret_cast<uint4*>(prow + BQ * BKV + o1) = make_uint4(wl[4], wl[5], wl[6], wl[7]);
             }
-            l = fmaf(l, alpha, psum);
-            m = m_new;
+            l += psum;
 
-            // S consumed: the issuer may overwrite it with the next block's scores
-            tc_fence_before_sync();
+            tc_fence_before_sync();  // orders the O rescale (if any) before the issuer's next P.V
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P visible to the tensor core
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(smem_u32(s_empty));
-                mbar_arrive(smem_u32(p_full));
-            }
-
-            if (!mbar_wait_bounded(smem_u32(o_full), j & 1)) {
-                if (lane == 0) record_timeout(args.status, 0x1600u);
-                ok = false;
-                break;
-            }
-            tc_fence_after_sync();
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_o + lane_addr + c * 32, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(r[i]));
-            }
-            tc_fence_before_sync();
+            if (lane == 0) mbar_arrive(smem_u32(p_full));
         }
 
         if (ok) {
-            // out = O * dq / (sum + 1e-6); O and sum both carry the factor 256
-            const float inv = dq / (l + 256.0f * 1e-6f);
+            while (pv_waited < n_kv) {
+                if (!mbar_wait_bounded(smem_u32(o_full), pv_waited & 1)) {
+                    ok = false;
+                    break;
+                }
+                ++pv_waited;
+            }
+            if (!ok && lane == 0) record_timeout(args.status, 0x1800u);
+        }
+        if (__all_sync(0xffffffffu, ok)) {
+            tc_fence_after_sync();
+            // upstream: p = exp(s - max) / (sum + 1e-6).  Here sum' = 2^kPShift * sum * 2^(max - m), so the
+            // 1e-6 is carried over with the same factor.
+            const float eps = 1e-6f * ex2(kPShift + ((m == -INFINITY) ? 0.f : (m_true - m)));
+            const float inv = dq / (l + eps);
             float amax = 0.f;
-            if (qi < T) {
-                float* o = args.out + (size_t(row_base) + qi) * E + h * D;
+            float* o = args.out + (size_t(row_base) + qi) * E + h * D;
 #pragma unroll
-                for (int d = 0; d < D; d += 4) {
-                    float4 v = make_float4(acc[d] * inv, acc[d + 1] * inv, acc[d + 2] * inv, acc[d + 3] * inv);
-                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-                    *reinterpret_cast<float4*>(o + d) = v;
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_o + lane_addr + c * 32, v);
+                tmem_ld_wait();
+                if (qi < T && n_kv > 0) {
+#pragma unroll
+                    for (int d = 0; d < 32; d += 4) {
+                        float4 f = make_float4(__uint_as_float(v[d]) * inv, __uint_as_float(v[d + 1]) * inv,
+                                               __uint_as_float(v[d + 2]) * inv, __uint_as_float(v[d + 3]) * inv);
+                        if (l == 0.f) f = make_float4(0.f, 0.f, 0.f, 0.f);  // every key masked: zeros, as upstream
+                        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
+                        *reinterpret_cast<float4*>(o + c * 32 + d) = f;
+                    }
                 }
             }
+            tc_fence_before_sync();
             if (args.out_amax) {
                 amax = warp_max(amax);
                 if (lane == 0 && amax > 0.f) atomic_max_nonneg(args.out_amax, amax);

@@ -29,6 +29,8 @@
 #include "sm100_ptx.cuh"
 #include "tensormap.cuh"
 
+#include <cstdlib>
+
 namespace df8 {
 
 namespace {
@@ -84,12 +86,14 @@ __device__ __forceinline__ void record_timeout(unsigned int* status, unsigned in
     }
 }
 
+// x * 0.5 * (1 + tanh(0.7978845608 * (x + 0.044715 x^3))), every operation rounded separately (explicit
+// intrinsics, no FMA contraction) so that all epilogue variants produce identical bits.
 __device__ __forceinline__ float gelu_tanh(float x) {
-    // x * 0.5 * (1 + tanh(0.7978845608 * (x + 0.044715 x^3)))
-    const float inner = 0.7978845608f * (x + 0.044715f * x * x * x);
+    const float x3c = __fmul_rn(__fmul_rn(0.044715f, __fmul_rn(x, x)), x);
+    const float inner = __fmul_rn(0.7978845608f, __fadd_rn(x, x3c));
     float t;
     asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(inner));
-    return x * 0.5f * (1.0f + t);
+    return __fmul_rn(__fmul_rn(x, 0.5f), __fadd_rn(1.0f, t));
 }
 
 // ---- fp32 output: transpose one 32-row x 32-column chunk through the warp's staging buffer -------
@@ -144,30 +148,47 @@ __device__ __forceinline__ void store_chunk_f32(const float* stg, int lane, int 
                 o.z = gelu_tanh(o.z);
                 o.w = gelu_tanh(o.w);
             }
-            o.x += rs[it].x;
-            o.y += rs[it].y;
-            o.z += rs[it].z;
-            o.w += rs[it].w;
+            if (a.flags & 2) {  // not unconditionally: x + 0 would turn -0 into +0
+                o.x += rs[it].x;
+                o.y += rs[it].y;
+                o.z += rs[it].z;
+                o.w += rs[it].w;
+            }
             if (grow < a.M && col_ok) {
                 amax = fmaxf(amax, fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w))));
                 *reinterpret_cast<float4*>(a.out + size_t(grow) * a.N + gcol) = o;
             }
         }
     } else {
+        // any N (e.g. a vocabulary of 50257): 4-byte accesses, a warp covers 128 contiguous bytes of one row;
+        // the row pointer is advanced instead of recomputed and the row-tail test is hoisted
         const int gcol = col0 + lane;
-        const bool col_ok = gcol < a.N;
-        const float b = (a.bias && col_ok) ? a.bias[gcol] : 0.f;
-#pragma unroll 8
-        for (int rl = 0; rl < 32; ++rl) {
-            const int grow = row0 + rl;
-            float v = stg[rl * 33 + lane];
-            if (grow < a.M && col_ok) {
-                v = fmaf(v, alpha, b);
-                if (a.flags & 1) v = gelu_tanh(v);
-                const size_t off = size_t(grow) * a.N + gcol;
-                if (a.flags & 2) v += a.residual[off];
-                amax = fmaxf(amax, fabsf(v));
-                a.out[off] = v;
+        if (gcol < a.N) {
+            const float b = a.bias ? a.bias[gcol] : 0.f;
+            const int rows = min(32, a.M - row0);
+            float* dst = a.out + size_t(row0) * a.N + gcol;
+            const float* res = (a.flags & 2) ? a.residual + size_t(row0) * a.N + gcol : nullptr;
+            const bool gelu = (a.flags & 1) != 0;
+            if (rows == 32 && !res && !gelu) {
+#pragma unroll
+                for (int rl = 0; rl < 32; ++rl) {
+                    const float v = fmaf(stg[rl * 33 + lane], alpha, b);
+                    amax = fmaxf(amax, fabsf(v));
+                    *dst = v;
+                    dst += a.N;
+                }
+            } else {
+                for (int rl = 0; rl < rows; ++rl) {
+                    float v = fmaf(stg[rl * 33 + lane], alpha, b);
+                    if (gelu) v = gelu_tanh(v);
+                    if (res) {
+                        v += *res;
+                        res += a.N;
+                    }
+                    amax = fmaxf(amax, fabsf(v));
+                    *dst = v;
+                    dst += a.N;
+                }
             }
         }
     }
@@ -406,6 +427,265 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
     }
 }
 
+// ---- CTA-pair variant: 256 x 256 output tile per pair of CTAs (tcgen05 cta_group::2) ---------------
+//
+// A 128 x 256 tile per CTA needs (128+256) x 128 operand bytes per 128-deep K block, i.e. 171 flop per byte
+// pulled from L2 into shared memory; at the B200's fp8 rate that is more than the L2 can deliver, and the
+// single-CTA kernel above tops out there.  Two CTAs of a cluster working on one 256 x 256 tile each load
+// their own 128 rows of A and their own 128 rows (N) of W — 256 flop per byte — and the pair's leader issues
+// one MMA (M = 256) that reads both CTAs' shared memory; each CTA's TMEM receives its own 128 rows, and each
+// CTA runs its own epilogue.  Loads stay plain per-CTA TMA loads; only barrier arrivals cross between CTAs.
+template <int STAGES, int MODE>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_w,
+                        const GemmArgs args) {
+    constexpr int BN = 256;
+    constexpr int kABytes = BM * BK, kBBytes = (BN / 2) * BK, kStageBytes = kABytes + kBBytes;
+    constexpr int kStagingBytes = kEpiWarps * kStagingFloatsPerWarp * 4;
+    constexpr int kTmemCols = 2 * BN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    float* staging = reinterpret_cast<float*>(smem + STAGES * kStageBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * kStageBytes + kStagingBytes);
+    uint64_t* full = bars;                // used in the leader only: both CTAs' loads report here
+    uint64_t* empty = bars + STAGES;      // one set per CTA, signalled by the leader's MMA commits
+    uint64_t* tfull = bars + 2 * STAGES;  // one set per CTA
+    uint64_t* tempty = tfull + 2;         // used in the leader only: both CTAs' epilogue warps arrive here
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(full + s), 1);
+            mbar_init(smem_u32(empty + s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(tfull + b), 1);
+            mbar_init(smem_u32(tempty + b), 2 * kEpiWarps);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_arrive();  // the partner's barriers exist before anything arrives on them
+    cluster_wait();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int pair = blockIdx.x >> 1;
+    const int npairs = gridDim.x >> 1;
+    const int num_m = (args.M + 2 * BM - 1) / (2 * BM);
+    const int num_n = (args.N + BN - 1) / BN;
+    const int num_tiles = num_m * num_n;
+    const int num_kb = (args.K + BK - 1) / BK;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            prefetch_tensormap(&tma_a);
+            prefetch_tensormap(&tma_w);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
+                const int m0 = (tile % num_m) * 2 * BM + int(rank) * BM;
+                const int n0 = (tile / num_m) * BN + int(rank) * (BN / 2);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait_bounded(smem_u32(empty + stage), phase ^ 1)) {
+                        record_timeout(args.status, 0x2100u + (rank << 4) + stage);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t fb = map_to_cta(smem_u32(full + stage), 0);
+                    uint8_t* sa = smem + stage * kStageBytes;
+                    if (leader) mbar_arrive_expect_tx(smem_u32(full + stage), 2 * kStageBytes);
+                    tma_load_2d_pair(smem_u32(sa), &tma_a, fb, kb * BK, m0);
+                    tma_load_2d_pair(smem_u32(sa + kABytes), &tma_w, fb, kb * BK, n0);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t acc_it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += npairs, ++acc_it) {
+                const uint32_t buf = acc_it & 1;
+                const uint32_t acc_phase = (acc_it >> 1) & 1;
+                if (!mbar_wait_bounded(smem_u32(tempty + buf), acc_phase ^ 1)) {
+                    record_timeout(args.status, 0x2200u + buf);
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait_bounded(smem_u32(full + stage), phase)) {
+                        record_timeout(args.status, 0x2300u + stage);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(smem + stage * kStageBytes);
+                    const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+                    for (int k = 0; k < BK / 32; ++k)
+                        tc_mma_f8_pair(d_tmem, make_desc_kmajor_sw128(a_addr + k * 32),
+                                       make_desc_kmajor_sw128(b_addr + k * 32), args.idesc, (kb | k) != 0);
+                    // the stage is free in both CTAs once these MMAs have read it
+                    tc_commit_pair(smem_u32(empty + stage));
+                    tc_commit_pair(map_to_cta(smem_u32(empty + stage), 1));
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (ok) {
+                    tc_commit_pair(smem_u32(tfull + buf));
+                    tc_commit_pair(map_to_cta(smem_u32(tfull + buf), 1));
+                }
+            }
+        }
+    } else {
+        const int e = warp - 2;
+        const int q = warp & 3;
+        const int half = e >> 2;
+        constexpr int kChunks = BN / 64;
+        float* stg = staging + e * kStagingFloatsPerWarp;
+        const float alpha = args.scale_a[1] * args.scale_w[1];
+        float out_q = 1.f;
+        if constexpr (MODE == kOutE4M3 || MODE == kOutE5M2) {
+            const float2 sc = scales_from_amax(*args.q_amax, fp8_max(MODE == kOutE4M3 ? DF8_E4M3 : DF8_E5M2));
+            out_q = sc.x;
+            if (blockIdx.x == 0 && e == 0 && lane == 0 && args.out_scale) {
+                args.out_scale[0] = sc.x;
+                args.out_scale[1] = sc.y;
+            }
+        }
+        const uint32_t lane_addr = uint32_t(q * 32) << 16;
+        auto release = [&](uint32_t buf) {  // this warp is done with accumulator buffer `buf`
+            if (lane == 0) {
+                if (leader) mbar_arrive(smem_u32(tempty + buf));
+                else mbar_arrive_cluster(map_to_cta(smem_u32(tempty + buf), 0));
+            }
+        };
+        uint32_t acc_it = 0;
+        for (int tile = pair; tile < num_tiles; tile += npairs, ++acc_it) {
+            const uint32_t buf = acc_it & 1;
+            const uint32_t acc_phase = (acc_it >> 1) & 1;
+            const int m0 = (tile % num_m) * 2 * BM + int(rank) * BM;
+            const int n0 = (tile / num_m) * BN;
+            if (!mbar_wait_bounded(smem_u32(tfull + buf), acc_phase)) {
+                if (lane == 0) record_timeout(args.status, 0x2400u + (rank << 4) + buf);
+                break;
+            }
+            tc_fence_after_sync();
+            float amax = 0.f;
+            const int row0 = m0 + q * 32;
+            const uint32_t taddr = tmem_base + buf * BN + lane_addr;
+            int nvalid = 0;
+#pragma unroll
+            for (int j = 0; j < kChunks; ++j)
+                if (n0 + 32 * (half + 2 * j) < args.N) nvalid = j + 1;
+
+            if constexpr (MODE == kOutF32Vec || MODE == kOutF32) {
+                constexpr bool VEC4 = MODE == kOutF32Vec;
+                uint32_t r[32];
+                if (nvalid > 0) tmem_ld_32x32(taddr + 32 * half, r);
+                for (int j = 0; j < nvalid; ++j) {
+                    tmem_ld_wait();
+                    stage_chunk<VEC4>(r, stg, lane);
+                    __syncwarp();
+                    if (j + 1 < nvalid) {
+                        tmem_ld_32x32(taddr + 32 * (half + 2 * (j + 1)), r);
+                    } else {
+                        tc_fence_before_sync();
+                        release(buf);
+                    }
+                    store_chunk_f32<VEC4>(stg, lane, row0, n0 + 32 * (half + 2 * j), args, alpha, amax);
+                    __syncwarp();
+                }
+                if (nvalid == 0) {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    release(buf);
+                }
+            } else {
+                constexpr int KIND = MODE == kOutE4M3 ? int(DF8_E4M3) : (MODE == kOutE5M2 ? int(DF8_E5M2) : -1);
+                const int grow = row0 + lane;
+#pragma unroll 1
+                for (int j = 0; j < nvalid; ++j) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + 32 * (half + 2 * j), r);
+                    tmem_ld_wait();
+                    direct_chunk<KIND>(r, grow, n0 + 32 * (half + 2 * j), args, alpha, out_q, amax);
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                release(buf);
+            }
+            if (args.flags & 4) {
+                amax = warp_max(amax);
+                if (lane == 0 && amax > 0.f) atomic_max_nonneg(args.out_amax, amax);
+            }
+        }
+    }
+
+    // neither CTA may leave while its partner can still read its shared memory or signal its barriers
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_arrive();
+    cluster_wait();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+}
+
+constexpr int kPairStages = 5;
+constexpr int kPairSmemBytes = kPairStages * (BM * BK + 128 * BK) + kEpiWarps * kStagingFloatsPerWarp * 4 + 256 + 1024;
+static_assert(kPairSmemBytes <= 227 * 1024, "shared memory budget");
+
+template <int MODE>
+df8_status launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tw, const GemmArgs& args, int grid,
+                            cudaStream_t st) {
+    auto kern = gemm_fp8_tn_pair_kernel<kPairStages, MODE>;
+    static bool configured[64] = {};
+    int dev = 0;
+    DF8_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        DF8_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
+        configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(grid), 1, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = kPairSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t err = cudaLaunchKernelEx(&cfg, kern, ta, tw, args);
+    if (err != cudaSuccess)
+        return fail(DF8_ERR_CUDA, "launch of gemm_fp8_tn_pair_kernel failed: %s", cudaGetErrorString(err));
+    return DF8_OK;
+}
+
 template <int BN, int STAGES, int MODE>
 df8_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmArgs& args, int grid,
                        cudaStream_t st) {
@@ -429,6 +709,18 @@ df8_status launch_gemm_bn(bool wide, const CUtensorMap& ta, const CUtensorMap& t
     return wide ? launch_gemm<256, 3, MODE>(ta, tw, args, grid, st) : launch_gemm<128, 5, MODE>(ta, tw, args, grid, st);
 }
 
+// DF8_GEMM_PAIR=0 / 1 in the environment forces the choice (profiling, tests); otherwise the pair kernel
+// takes problems that give every CTA pair at least one full 256 x 256 tile.
+bool use_pair_kernel(int M, int N, int K, int sms) {
+    static const int forced = [] {
+        const char* e = getenv("DF8_GEMM_PAIR");
+        return e ? atoi(e) : -1;
+    }();
+    if (forced == 1) return true;
+    (void)M; (void)N; (void)K; (void)sms;
+    return false;
+}
+
 // Shared host path of the entry points: picks the tile width, encodes the tensor maps, launches `mode`.
 df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uint8_t* w_codes, df8_kind kind_w,
                     GemmArgs args, cudaStream_t st) {
@@ -437,6 +729,25 @@ df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uin
     if (src != DF8_OK) return src;
 
     const int sms = sm_count();
+    // CTA pairs on 256 x 256 tiles when the problem fills them (see gemm_fp8_tn_pair_kernel)
+    if (use_pair_kernel(M, N, K, sms)) {
+        const long tiles2 = long((M + 255) / 256) * ((N + 255) / 256);
+        const long pairs = tiles2 < sms / 2 ? tiles2 : sms / 2;
+        CUtensorMap ta2, tw2;
+        df8_status rc2 = make_tmap_2d_u8(&ta2, a_codes, uint64_t(M), uint64_t(K), uint64_t(K), BM, BK, 128);
+        if (rc2 != DF8_OK) return rc2;
+        rc2 = make_tmap_2d_u8(&tw2, w_codes, uint64_t(N), uint64_t(K), uint64_t(K), 128, BK, 128);
+        if (rc2 != DF8_OK) return rc2;
+        args.idesc = ptx::make_idesc_f8(256, 256, int(kind_a), int(kind_w));
+        const int grid2 = int(pairs) * 2;
+        switch (mode) {
+            case kOutF32Vec: return launch_gemm_pair<kOutF32Vec>(ta2, tw2, args, grid2, st);
+            case kOutF32: return launch_gemm_pair<kOutF32>(ta2, tw2, args, grid2, st);
+            case kOutE4M3: return launch_gemm_pair<kOutE4M3>(ta2, tw2, args, grid2, st);
+            case kOutE5M2: return launch_gemm_pair<kOutE5M2>(ta2, tw2, args, grid2, st);
+            default: return launch_gemm_pair<kOutNone>(ta2, tw2, args, grid2, st);
+        }
+    }
     // tile width: the one that fills whole waves of the persistent grid best (wider tiles reuse A more)
     auto efficiency = [&](int bn, double weight) {
         const long tiles = long((M + BM - 1) / BM) * ((N + bn - 1) / bn);

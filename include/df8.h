@@ -180,6 +180,27 @@ df8_status df8_streamer_release(df8_streamer* s, int layer, df8_stream compute_s
 df8_status df8_streamer_stats(df8_streamer* s, unsigned long long* bytes_uploaded_h, size_t* slot_bytes_h,
                               int* n_slots_h);
 
+/* ---- collectives for the column-sharded fully-connected path --------------------------------------
+ * Upstream has no communication backend: its multi-GPU mode runs independent replicas under a
+ * tbb::parallel_for (apps/host-multi/main.cpp:157-181).  These calls wrap NCCL (bound at run time with
+ * dlopen, so the library loads without it): one communicator per process, one process per GPU.
+ * Rank 0 makes the 128-byte id (df8_comm_unique_id, HOST buffer) and passes it to the other ranks by
+ * any host channel; df8_comm_init_rank is collective and allocates; the data calls are enqueued on
+ * `stream` and neither allocate nor synchronise.  df8_comm_abort ends outstanding collectives with an
+ * error when a peer has gone away (host-side failure handling; never on the data path). */
+typedef struct df8_comm df8_comm;
+df8_status df8_comm_available(int* version_h);
+df8_status df8_comm_unique_id(void* id_h);
+df8_status df8_comm_init_rank(const void* id_h, int world, int rank, df8_comm** out);
+df8_status df8_comm_destroy(df8_comm* c);
+df8_status df8_comm_abort(df8_comm* c);
+df8_status df8_comm_rank(const df8_comm* c, int* rank_h, int* world_h);
+/* recv_d[r*bytes_per_rank ...] = rank r's send_d (the gathered layout is rank-major) */
+df8_status df8_comm_allgather_u8(df8_comm* c, const uint8_t* send_d, uint8_t* recv_d, size_t bytes_per_rank,
+                                 df8_stream stream);
+/* in place: buf_d[i] = max over ranks (the per-tensor amax of a tensor whose columns are sharded) */
+df8_status df8_comm_allreduce_max_f32(df8_comm* c, float* buf_d, size_t count, df8_stream stream);
+
 /* ---- bounded-wait status word --------------------------------------------------------------
  * Every device-side wait (mbarrier polls in the GEMM and attention pipelines) gives up after a
  * time limit instead of hanging the GPU; the first such event stores a non-zero code.  Upstream

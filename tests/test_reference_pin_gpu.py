@@ -43,8 +43,11 @@ def test_fc_oracle_matches_upstream_kernel(ref, oracle, M, K, N):
 
 
 def test_softmax_oracle_matches_upstream_kernel(ref, oracle):
+    """Only rows of at most one warp (T <= 32): upstream's kernel overwrites the shared row with the exponentials
+    (softmax_layer.cu:62-64) without a barrier after every thread's max scan (:57-61), so with several warps per
+    row a fast warp corrupts the maximum a slow warp is still computing (observed: 1.5e-2 error at T = 1024)."""
     rng = np.random.default_rng(1)
-    for B, H, T in [(2, 4, 8), (1, 2, 128), (1, 1, 1024)]:
+    for B, H, T in [(2, 4, 8), (3, 2, 32), (1, 1, 17)]:
         x = rng.standard_normal((B, H, T, T)).astype(np.float32)
         y = np.zeros_like(x)
         ok(ref, ref.ref_softmax_forward(B, H, T, p(x), None, 0, p(y)))
@@ -61,7 +64,7 @@ def test_layernorm_oracle_matches_upstream_kernel(ref, oracle):
         g = oracle.fill_normal(cols, seed=1, mean=1.0, std=0.2)
         b = oracle.fill_normal(cols, seed=2, std=0.2)
         y = np.zeros_like(x)
-        ok(ref, ref.ref_layernorm_forward(rows, cols, p(g), p(b), 1e-5, p(x), p(y)))
+        ok(ref, ref.ref_layernorm_forward(rows, cols, p(g), p(b), C.c_float(1e-5), p(x), p(y)))
         assert np.abs(y - oracle.layernorm(x, g, b, 1e-5)).max() <= 2e-5
 
 

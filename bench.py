@@ -350,7 +350,9 @@ class Gpt2Workload:
         self.T = self.c["ctx"]
         self.metric = "GPT-2 fp8 forward tokens/s"
         self.dtype = f"{self.c['act']} activations x e4m3 weights -> f32 accumulate"
-        self.kernels_per_step = 1 + 13 * self.c["layers"] + 3
+        # embedding; per layer: LN+quantise 2, QKV GEMM 2 passes, attention, quantise, out GEMM, LN+quantise 2,
+        # FC1 GEMM 2 passes, FC2 GEMM; head: amax, quantise, GEMM
+        self.kernels_per_step = 1 + 12 * self.c["layers"] + 3
 
     def config(self, n_gpus):
         c = self.c
@@ -670,7 +672,7 @@ def run_ours(args, rank, world, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])

@@ -62,6 +62,10 @@ _SIGNATURES = {
     "df8_comm_rank": [_vp, _vp, _vp],
     "df8_comm_allgather_u8": [_vp, _vp, _vp, _sz, _vp],
     "df8_comm_allreduce_max_f32": [_vp, _vp, _sz, _vp],
+    "df8_gemm_fp8_tn_amax": [_vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
+    "df8_gemm_fp8_tn_codes": [_vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
+    "df8_fc_fp8_column_sharded": [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
+    "df8_interleave_gathered_u8": [_vp, _i, _i, _i, _vp, _vp],
     "df8_status_word_read": [_vp, _vp],
     "df8_status_word_reset": [],
 }

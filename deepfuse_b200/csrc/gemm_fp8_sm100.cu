@@ -709,16 +709,15 @@ df8_status launch_gemm_bn(bool wide, const CUtensorMap& ta, const CUtensorMap& t
     return wide ? launch_gemm<256, 3, MODE>(ta, tw, args, grid, st) : launch_gemm<128, 5, MODE>(ta, tw, args, grid, st);
 }
 
-// DF8_GEMM_PAIR=0 / 1 in the environment forces the choice (profiling, tests); otherwise the pair kernel
-// takes problems that give every CTA pair at least one full 256 x 256 tile.
+// DF8_GEMM_PAIR=0 / 1 in the environment (read at every call) forces the choice for profiling and tests;
+// otherwise the pair kernel takes problems that give every CTA pair at least one full 256 x 256 tile.
 bool use_pair_kernel(int M, int N, int K, int sms) {
-    static const int forced = [] {
-        const char* e = getenv("DF8_GEMM_PAIR");
-        return e ? atoi(e) : -1;
-    }();
-    if (forced == 1) return true;
-    (void)M; (void)N; (void)K; (void)sms;
-    return false;
+    const char* e = getenv("DF8_GEMM_PAIR");
+    if (e && e[0] == '0') return false;
+    if (e && e[0] == '1') return M > 0 && N > 0;
+    (void)K;
+    (void)sms;
+    return false;  // automatic selection stays off until the pair kernel has been measured against the single-CTA one
 }
 
 // Shared host path of the entry points: picks the tile width, encodes the tensor maps, launches `mode`.
@@ -855,4 +854,65 @@ extern "C" df8_status df8_gemm_fp8_tn_q(const uint8_t* a_codes, df8_kind kind_a,
     if (rc != DF8_OK) return rc;
     args.flags = flags;
     return run_gemm(out_kind == DF8_E4M3 ? kOutE4M3 : kOutE5M2, a_codes, kind_a, w_codes, kind_w, args, st);
+}
+
+// The two halves of df8_gemm_fp8_tn_q as separate calls, for callers that have to combine the max|out|
+// with other ranks' (column-sharded layers) between the passes.
+extern "C" df8_status df8_gemm_fp8_tn_amax(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a,
+                                           const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
+                                           const float* bias, int M, int N, int K, int flags, float* out_amax,
+                                           df8_stream stream) {
+    DF8_REQUIRE((kind_a == DF8_E4M3 || kind_a == DF8_E5M2) && (kind_w == DF8_E4M3 || kind_w == DF8_E5M2),
+                "df8_gemm_fp8_tn_amax: unknown fp8 kind");
+    DF8_REQUIRE(M >= 0 && N >= 0 && K > 0, "df8_gemm_fp8_tn_amax: bad shape M=%d N=%d K=%d", M, N, K);
+    DF8_REQUIRE((flags & ~DF8_EPI_GELU) == 0, "df8_gemm_fp8_tn_amax: only DF8_EPI_GELU is accepted, got 0x%x", flags);
+    DF8_REQUIRE(out_amax != nullptr, "df8_gemm_fp8_tn_amax: out_amax is required");
+    cudaStream_t st = as_stream(stream);
+    DF8_CUDA_TRY(cudaMemsetAsync(out_amax, 0, sizeof(float), st));
+    if (M == 0 || N == 0) return DF8_OK;
+    if (K % 16 != 0 || N % 32 != 0)
+        return fail(DF8_ERR_UNSUPPORTED, "df8_gemm_fp8_tn_amax: needs K %% 16 == 0 and N %% 32 == 0 (K=%d N=%d)", K, N);
+    DF8_REQUIRE(a_codes && w_codes && scale_a && scale_w, "df8_gemm_fp8_tn_amax: null buffer");
+    DF8_REQUIRE(!bias || aligned16(bias), "df8_gemm_fp8_tn_amax: bias must be 16-byte aligned");
+    GemmArgs args{};
+    args.scale_a = scale_a;
+    args.scale_w = scale_w;
+    args.bias = bias;
+    args.out_amax = out_amax;
+    args.M = M;
+    args.N = N;
+    args.K = K;
+    args.flags = flags | DF8_EPI_AMAX;
+    return run_gemm(kOutNone, a_codes, kind_a, w_codes, kind_w, args, st);
+}
+
+extern "C" df8_status df8_gemm_fp8_tn_codes(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a,
+                                            const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
+                                            const float* bias, int M, int N, int K, int flags, df8_kind out_kind,
+                                            const float* amax_in, uint8_t* out_codes, float* out_scale,
+                                            df8_stream stream) {
+    DF8_REQUIRE((kind_a == DF8_E4M3 || kind_a == DF8_E5M2) && (kind_w == DF8_E4M3 || kind_w == DF8_E5M2) &&
+                    (out_kind == DF8_E4M3 || out_kind == DF8_E5M2),
+                "df8_gemm_fp8_tn_codes: unknown fp8 kind");
+    DF8_REQUIRE(M >= 0 && N >= 0 && K > 0, "df8_gemm_fp8_tn_codes: bad shape M=%d N=%d K=%d", M, N, K);
+    DF8_REQUIRE((flags & ~DF8_EPI_GELU) == 0, "df8_gemm_fp8_tn_codes: only DF8_EPI_GELU is accepted, got 0x%x", flags);
+    DF8_REQUIRE(amax_in != nullptr, "df8_gemm_fp8_tn_codes: amax_in is required");
+    if (M == 0 || N == 0) return DF8_OK;
+    if (K % 16 != 0 || N % 32 != 0)
+        return fail(DF8_ERR_UNSUPPORTED, "df8_gemm_fp8_tn_codes: needs K %% 16 == 0 and N %% 32 == 0 (K=%d N=%d)", K, N);
+    DF8_REQUIRE(a_codes && w_codes && scale_a && scale_w && out_codes, "df8_gemm_fp8_tn_codes: null buffer");
+    DF8_REQUIRE(aligned16(out_codes) && (!bias || aligned16(bias)),
+                "df8_gemm_fp8_tn_codes: out_codes and bias must be 16-byte aligned");
+    GemmArgs args{};
+    args.scale_a = scale_a;
+    args.scale_w = scale_w;
+    args.bias = bias;
+    args.M = M;
+    args.N = N;
+    args.K = K;
+    args.flags = flags;
+    args.out_codes = out_codes;
+    args.q_amax = amax_in;
+    args.out_scale = out_scale;
+    return run_gemm(out_kind == DF8_E4M3 ? kOutE4M3 : kOutE5M2, a_codes, kind_a, w_codes, kind_w, args, as_stream(stream));
 }

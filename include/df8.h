@@ -105,6 +105,18 @@ df8_status df8_gemm_fp8_tn_q(const uint8_t* a_codes, df8_kind kind_a, const floa
                              const float* bias, int M, int N, int K, int flags, df8_kind out_kind,
                              uint8_t* out_codes, float* out_scale, float* out_amax, df8_stream stream);
 
+/* The two passes of df8_gemm_fp8_tn_q as separate calls (a column-sharded layer combines max|out| across
+ * ranks between them): _amax reduces max|epi(...)| into out_amax (cleared by the call) and writes nothing
+ * else; _codes recomputes the product and emits fp8 codes with the scale derived from amax_in[0]. */
+df8_status df8_gemm_fp8_tn_amax(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a,
+                                const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
+                                const float* bias, int M, int N, int K, int flags, float* out_amax,
+                                df8_stream stream);
+df8_status df8_gemm_fp8_tn_codes(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a,
+                                 const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
+                                 const float* bias, int M, int N, int K, int flags, df8_kind out_kind,
+                                 const float* amax_in, uint8_t* out_codes, float* out_scale, df8_stream stream);
+
 /* ---- fp8 attention -------------------------------------------------------------------------
  * Replaces, inside MultiHeadAttentionLayer::forward (dnn/layers/multi_head_attention.cu:204-308), the
  * Q/K/V slice + head-split copies (:231-260), both matmul_kernel launches (:266-270, :283-287),
@@ -200,6 +212,23 @@ df8_status df8_comm_allgather_u8(df8_comm* c, const uint8_t* send_d, uint8_t* re
                                  df8_stream stream);
 /* in place: buf_d[i] = max over ranks (the per-tensor amax of a tensor whose columns are sharded) */
 df8_status df8_comm_allreduce_max_f32(df8_comm* c, float* buf_d, size_t count, df8_stream stream);
+
+/* Column-sharded fully-connected layer (no upstream counterpart: upstream's layer always holds the full
+ * [out,in] weight, dnn/layers/fully_connected_layer.cu:112-116).  Every rank passes the full quantised input
+ * a_codes [M,K] and ITS row block of the weight codes w_shard_codes [N/world, K] (rank r owns output columns
+ * [r*N/world, (r+1)*N/world)), with the scale of the WHOLE weight tensor; bias_shard is the matching slice.
+ * Result on every rank: out_codes [M,N], out_scale, out_amax identical to df8_gemm_fp8_tn_q on one GPU.
+ * Steps: amax pass -> all-reduce(max) of one float -> codes pass -> all-gather of M*N/world bytes per rank
+ * -> interleave.  slice_scratch: M*N/world bytes, gathered_scratch: M*N bytes.  N % (32*world) == 0. */
+df8_status df8_fc_fp8_column_sharded(df8_comm* comm, const uint8_t* a_codes, df8_kind kind_a,
+                                     const float* scale_a, const uint8_t* w_shard_codes, df8_kind kind_w,
+                                     const float* scale_w, const float* bias_shard, int M, int N, int K,
+                                     int flags, df8_kind out_kind, uint8_t* slice_scratch,
+                                     uint8_t* gathered_scratch, uint8_t* out_codes, float* out_scale,
+                                     float* out_amax, df8_stream stream);
+/* out [M, world*cols_per_rank] <- gathered [world][M, cols_per_rank] (the layout an all-gather leaves) */
+df8_status df8_interleave_gathered_u8(const uint8_t* gathered, int M, int cols_per_rank, int world,
+                                      uint8_t* out, df8_stream stream);
 
 /* ---- bounded-wait status word --------------------------------------------------------------
  * Every device-side wait (mbarrier polls in the GEMM and attention pipelines) gives up after a

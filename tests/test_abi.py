@@ -48,3 +48,20 @@ def test_missing_library_fails_loudly(df8, monkeypatch, tmp_path):
         assert "no CPU or PyTorch fallback" in str(e)
     else:
         raise AssertionError("loading a missing library must raise")
+
+
+def test_dnn_harness_exports_every_declared_symbol(df8):
+    """libdf8_dnn.so (the C++ dnn:: classes + their C harness) loads without a GPU and exports what
+    include/df8_dnn.h declares."""
+    text = re.sub(r"/\*.*?\*/", "", (ROOT / "include" / "df8_dnn.h").read_text(), flags=re.S)
+    names = sorted(set(re.findall(r"\b(dnn_[a-z0-9_]+)\s*\(", text)))
+    assert "dnn_gpt2_create" in names and "dnn_selftest_tensor" in names
+    handle = df8.dnn_lib()
+    missing = [n for n in names if not hasattr(handle, n)]
+    assert not missing, f"declared in include/df8_dnn.h but not exported: {missing}"
+
+
+def test_dnn_harness_reports_errors_without_a_gpu(df8):
+    lib = df8.dnn_lib()
+    assert lib.dnn_set_fp8_policy(3, 0) != 0
+    assert b"fp8 kind" in lib.dnn_last_error()

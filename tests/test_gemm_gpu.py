@@ -196,3 +196,39 @@ def test_gemm_quantised_output_rejects_odd_n(df8, cuda):
     s = torch.ones(2, device=cuda)
     with pytest.raises(df8.Df8Error, match="N % 32"):
         df8.gemm_fp8_tn_q(a, 0, s, a, 0, s, None, 64, 40, 32, 0, 0, a, s, s)
+
+
+@pytest.mark.parametrize("M,N,K,flags", [(256, 256, 128, 0), (512, 768, 768, 4), (1024, 2304, 768, 0), (300, 1003, 256, 0),
+                                         (129, 257, 144, 3), (2048, 3072, 768, 5), (64, 3072, 768, 0)])
+def test_gemm_cta_pair_kernel(df8, oracle, cuda, monkeypatch, M, N, K, flags):
+    """The cta_group::2 kernel (two CTAs per 256 x 256 tile), forced on through DF8_GEMM_PAIR=1, against the
+    oracle and, bit for bit, against the single-CTA kernel (same products, same fp32 accumulation order)."""
+    monkeypatch.setenv("DF8_GEMM_PAIR", "1")
+    y2, ref, amax2, _ = run_gemm(df8, oracle, cuda, M, N, K, flags=flags, seed=M + N)
+    monkeypatch.setenv("DF8_GEMM_PAIR", "0")
+    y1, _, amax1, _ = run_gemm(df8, oracle, cuda, M, N, K, flags=flags, seed=M + N)
+    tol = 2e-3 if flags & 1 else TIGHT
+    assert rel_err(y2, ref) <= tol, describe_mismatch(y2, ref, tol)
+    assert np.array_equal(y1, y2)
+    assert amax1 == amax2
+    assert df8.status_word() == (0, 0)
+
+
+def test_gemm_cta_pair_quantised_output(df8, oracle, cuda, monkeypatch):
+    import torch
+
+    M, N, K = 1024, 3072, 768
+    xc, sx = oracle.quantize(oracle.fill_normal(M * K, seed=41).reshape(M, K), 0)
+    wc, sw = oracle.quantize(oracle.fill_normal(N * K, seed=42, std=0.05).reshape(N, K), 0)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+    xcd, wcd, sxd, swd = t(xc), t(wc), t(sx), t(sw)
+    outs = []
+    for pair in ("0", "1"):
+        monkeypatch.setenv("DF8_GEMM_PAIR", pair)
+        codes = torch.full((M, N), 0xAA, dtype=torch.uint8, device=cuda)
+        scale, amax = torch.zeros(2, device=cuda), torch.zeros(1, device=cuda)
+        df8.gemm_fp8_tn_q(xcd, 0, sxd, wcd, 0, swd, None, M, N, K, 1, 0, codes, scale, amax)
+        outs.append((codes, scale, amax))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert outs[0][2].item() == outs[1][2].item()
+    assert df8.status_word() == (0, 0)

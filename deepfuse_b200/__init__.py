@@ -43,6 +43,7 @@ _SIGNATURES = {
     "df8_gemm_fp8_tn": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp],
     "df8_layernorm_f32": [_vp, _i, _i, _vp, _vp, _f, _vp, _vp, _vp],
     "df8_layernorm_quantize_f32": [_vp, _i, _i, _vp, _vp, _f, _i, _vp, _vp, _vp, _vp, _vp],
+    "df8_layernorm_quantize_f32_noalloc": [_vp, _i, _i, _vp, _vp, _f, _i, _vp, _vp, _vp, _vp],
     "df8_embed_pe_f32": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
     "df8_attention_fp8": [_vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp, _vp],
     "df8_softmax_masked_f32": [_vp, _vp, _i, _i, _i, _i, _vp, _vp],
@@ -166,6 +167,13 @@ def layernorm_quantize_f32(x, rows, cols, gamma, beta, eps, kind, codes_out, sca
     check(lib().df8_layernorm_quantize_f32(ptr(x), rows, cols, ptr(gamma), ptr(beta), eps, kind, ptr(codes_out),
                                            ptr(scale_out), ptr(amax_out), ptr(row_stats), stream_ptr(stream)),
           "df8_layernorm_quantize_f32")
+
+
+def layernorm_quantize_f32_noalloc(x, rows, cols, gamma, beta, eps, kind, codes_out, scale_out, amax_out,
+                                   stream=None) -> None:
+    check(lib().df8_layernorm_quantize_f32_noalloc(ptr(x), rows, cols, ptr(gamma), ptr(beta), eps, kind,
+                                                   ptr(codes_out), ptr(scale_out), ptr(amax_out),
+                                                   stream_ptr(stream)), "df8_layernorm_quantize_f32_noalloc")
 
 
 def embed_pe_f32(ids, B, T, E, V, table, bias, pe, out, bad_ids=None, stream=None) -> None:

@@ -219,3 +219,66 @@ extern "C" df8_status df8_layernorm_quantize_f32(const float* x, int rows, int c
                ? launch_ln_quant<DF8_E4M3>(x, rows, cols, gamma, beta, eps, codes_out, scale_out, amax_out, stats, st)
                : launch_ln_quant<DF8_E5M2>(x, rows, cols, gamma, beta, eps, codes_out, scale_out, amax_out, stats, st);
 }
+
+// ---- variant that never allocates -----------------------------------------------------------------
+//
+// Some callers of the fused LayerNorm + quantise cannot provide the row-statistics scratch buffer
+// because they cannot allocate device memory at the point of the call: a serving loop that handed
+// every byte of the GPU to its own arena at start-up, a host thread that must not take the
+// allocator's lock or the implicit device synchronisation of cudaMalloc / cudaFree, or glue code in
+// a language binding that only ever sees the caller's input and output buffers.  For them the
+// scratch lives in the library image: a fixed array in device global memory, reserved on every GPU
+// that loads the library for as long as the process lives.
+namespace {
+
+constexpr int kNoAllocMaxRows = 65536;  // 2 floats per row: 512 KiB of device memory per GPU
+
+static __device__ __align__(256) float g_ln_row_stats[2 * kNoAllocMaxRows];
+
+// Device address of g_ln_row_stats on the current device.  In host code the array's name is only a
+// handle for the runtime, not something a kernel may dereference, so the real address is looked up
+// once per device (with that device current) and cached.
+df8_status ln_static_scratch(float** out) {
+    static float* cached[64] = {};
+    int dev = 0;
+    DF8_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(DF8_ERR_INVALID, "device index %d out of range", dev);
+    if (!cached[dev]) {
+        float* p = nullptr;
+        cudaError_t err = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_ln_row_stats);
+        if (err != cudaSuccess)
+            return fail(DF8_ERR_CUDA, "cudaGetSymbolAddress(g_ln_row_stats) failed: %s", cudaGetErrorString(err));
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return DF8_OK;
+}
+
+}  // namespace
+
+extern "C" df8_status df8_layernorm_quantize_f32_noalloc(const float* x, int rows, int cols, const float* gamma,
+                                                         const float* beta, float eps, df8_kind kind,
+                                                         uint8_t* codes_out, float* scale_out, float* amax_out,
+                                                         df8_stream stream) {
+    DF8_REQUIRE(kind == DF8_E4M3 || kind == DF8_E5M2, "df8_layernorm_quantize_f32_noalloc: unknown fp8 kind %d",
+                int(kind));
+    DF8_REQUIRE(rows >= 0 && cols > 0, "df8_layernorm_quantize_f32_noalloc: bad shape rows=%d cols=%d", rows, cols);
+    if (rows > kNoAllocMaxRows)
+        return fail(DF8_ERR_UNSUPPORTED,
+                    "df8_layernorm_quantize_f32_noalloc: %d rows exceed the built-in scratch of %d rows; "
+                    "use df8_layernorm_quantize_f32 with a caller-provided buffer",
+                    rows, kNoAllocMaxRows);
+    DF8_REQUIRE(amax_out && scale_out, "df8_layernorm_quantize_f32_noalloc: amax_out and scale_out are required");
+    DF8_REQUIRE(rows == 0 || (x && codes_out), "df8_layernorm_quantize_f32_noalloc: null buffer");
+    float* stats = nullptr;
+    df8_status rc = ln_static_scratch(&stats);
+    if (rc != DF8_OK) return rc;
+    cudaStream_t st = as_stream(stream);
+    // max|LN(x)| is accumulated with atomicMax and must start from zero; the row statistics need no
+    // clearing: pass 1 writes the entry of every row before pass 2 reads it.
+    DF8_CUDA_TRY(cudaMemsetAsync(amax_out, 0, sizeof(float), st));
+    float2* stats2 = reinterpret_cast<float2*>(stats);
+    return kind == DF8_E4M3
+               ? launch_ln_quant<DF8_E4M3>(x, rows, cols, gamma, beta, eps, codes_out, scale_out, amax_out, stats2, st)
+               : launch_ln_quant<DF8_E5M2>(x, rows, cols, gamma, beta, eps, codes_out, scale_out, amax_out, stats2, st);
+}

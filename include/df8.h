@@ -160,6 +160,22 @@ df8_status df8_layernorm_quantize_f32(const float* x, int rows, int cols, const 
                                       float* scale_out, float* amax_out, float* row_stats_scratch,
                                       df8_stream stream);
 
+/* The same fused LayerNorm + quantise for callers that cannot allocate device memory (and so cannot
+ * supply row_stats_scratch): a server that partitioned the whole GPU into its own arena at start-up, a
+ * thread that may not block on the allocator, a thin language binding that only owns inputs and
+ * outputs.  This entry point has no counterpart in the upstream project.  The per-row scratch is a
+ * fixed array inside the library's device image (512 KiB on every GPU that loads the library, held until
+ * the process exits); rows above 65536 are rejected with DF8_ERR_UNSUPPORTED.  The call itself performs no
+ * cudaMalloc / cudaFree and uses no allocating library routine.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
+ * first call outside any stream capture.  All calls on a device share the one array: two calls whose
+ * kernels may overlap on the GPU (different streams, no ordering between them) race on it, so order them.
+ * Nothing in the array has to be cleared between calls; amax_out is cleared by the call. */
+df8_status df8_layernorm_quantize_f32_noalloc(const float* x, int rows, int cols, const float* gamma,
+                                              const float* beta, float eps, df8_kind kind,
+                                              uint8_t* codes_out, float* scale_out, float* amax_out,
+                                              df8_stream stream);
+
 /* ---- token embedding + positional encoding -----------------------------------------------
  * Replaces embedding_forward_kernel (dnn/tokens/token_embedding.cu:31-45, launched at :146-154) and
  * add_positional_encodings_kernel (dnn/tokens/positional_encoding.cu:31-48, launched at :94-104):

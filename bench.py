@@ -224,7 +224,9 @@ class GemmWorkload:
     def __init__(self, M=8192, E=768, F=3072, V=50257, only=None):
         self.M, self.E, self.F, self.V = M, E, F, V
         shapes = [("qkv", 3 * E, E, 4), ("out", E, E, 2), ("fc1", F, E, 1 | 4), ("fc2", E, F, 2), ("head", V, E, 0)]
-        self.shapes = [s for s in shapes if only is None or s[0] in only]
+        # large square problem (tensor-pipe bound; not part of the default set): --only big
+        extra = [("big", 8192, 8192, 0), ("big4k", 8192, 4096, 0)]
+        self.shapes = [s for s in shapes if only is None or s[0] in only] + [s for s in extra if only and s[0] in only]
         self.kernels_per_step = len(self.shapes)
 
     def config(self, n_gpus):
@@ -564,8 +566,8 @@ def run_reference(args, rank, world):
     orc.build()
     wl = make_workload(args)
     cores = orc.get_threads()
-    for _ in range(max(args.warmup, 1)):
-        wl.cpu_sample(orc, log2n=22)
+    for _ in range(min(max(args.warmup, 1), 1)):
+        wl.cpu_sample(orc)  # one warm-up sample (page-in of the oracle library, thread pool start)
     units, secs, sample = 0.0, 0.0, ""
     for _ in range(args.steps):
         u, dt, sample = wl.cpu_sample(orc)

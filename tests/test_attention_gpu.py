@@ -65,7 +65,10 @@ def test_attention_additive_mask_matches_causal_flag(df8, oracle, cuda):
     y_flag, ref, _ = run_attention(df8, oracle, cuda, B, T, H, D, mask_mode=1, seed=9)
     y_b1, _, _ = run_attention(df8, oracle, cuda, B, T, H, D, mask_mode=2, mask=m1, seed=9)
     y_bb, _, _ = run_attention(df8, oracle, cuda, B, T, H, D, mask_mode=2, mask=np.repeat(m1, B, axis=0), seed=9)
-    assert np.array_equal(y_flag, y_b1) and np.array_equal(y_flag, y_bb)
+    # the per-batch and the broadcast mask take the same code path: identical; the causal flag skips the blocks
+    # above the diagonal and folds the score scaling into one fma on unmasked blocks: equal up to fp32 rounding
+    assert np.array_equal(y_b1, y_bb)
+    assert rel_err(y_flag, y_b1) <= 1e-5
     assert rel_err(y_flag, ref) <= TOL
 
 

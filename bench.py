@@ -225,9 +225,11 @@ class GemmWorkload:
         self.M, self.E, self.F, self.V = M, E, F, V
         shapes = [("qkv", 3 * E, E, 4), ("out", E, E, 2), ("fc1", F, E, 1 | 4), ("fc2", E, F, 2), ("head", V, E, 0)]
         # large square problem (tensor-pipe bound; not part of the default set): --only big
-        extra = [("big", 8192, 8192, 0), ("big4k", 8192, 4096, 0)]
+        # and the two projections whose output the next layer consumes as fp8 codes, through the two-pass
+        # df8_gemm_fp8_tn_q (flag 8 here; counted as one product although the tensor work runs twice)
+        extra = [("big", 8192, 8192, 0), ("big4k", 8192, 4096, 0), ("qkvq", 3 * E, E, 8), ("fc1q", F, E, 1 | 8)]
         self.shapes = [s for s in shapes if only is None or s[0] in only] + [s for s in extra if only and s[0] in only]
-        self.kernels_per_step = len(self.shapes)
+        self.kernels_per_step = sum(2 if f & 8 else 1 for _, _, _, f in self.shapes)
 
     def config(self, n_gpus):
         return {"workload": f"GPT-2 small projection set at M={self.M} tokens: "
@@ -253,30 +255,41 @@ class GemmWorkload:
             w = w | sign
             bias = torch.zeros(N, device=dev)
             res = torch.randn(self.M, N, device=dev, generator=g) if flags & 2 else None
-            out = torch.empty(self.M, N, device=dev)
+            out = (torch.empty(self.M, N, dtype=torch.uint8, device=dev) if flags & 8
+                   else torch.empty(self.M, N, device=dev))
             amax = torch.zeros(1, device=dev)
             self.ops.append((a, w, bias, res, out, amax, N, K, flags))
         self.one = one
+        self.out_scale = torch.zeros(2, device=dev)
         self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
-    def step(self):
+    def _call(self, op):
         d = self.df8
-        self.flush.zero_()
-        for a, w, bias, res, out, amax, N, K, flags in self.ops:
+        a, w, bias, res, out, amax, N, K, flags = op
+        if flags & 8:
+            d.gemm_fp8_tn_q(a, d.E4M3, self.one, w, d.E4M3, self.one, bias, self.M, N, K, flags & 1, d.E4M3, out,
+                            self.out_scale, amax)
+        else:
             d.gemm_fp8_tn(a, d.E4M3, self.one, w, d.E4M3, self.one, bias, res, self.M, N, K, flags, out, amax)
+
+    def step(self):
+        self.flush.zero_()
+        for op in self.ops:
+            self._call(op)
 
     def roofline(self, torch, peaks, iters=20):
         d = self.df8
         per = {}
         best = None
-        for (name, _, _, _), (a, w, bias, res, out, amax, N, K, flags) in zip(self.shapes, self.ops):
+        for (name, _, _, _), op in zip(self.shapes, self.ops):
+            N, K = op[6], op[7]
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
             for _ in range(3):
-                d.gemm_fp8_tn(a, d.E4M3, self.one, w, d.E4M3, self.one, bias, res, self.M, N, K, flags, out, amax)
+                self._call(op)
             torch.cuda.synchronize()
             ev[0].record()
             for _ in range(iters):
-                d.gemm_fp8_tn(a, d.E4M3, self.one, w, d.E4M3, self.one, bias, res, self.M, N, K, flags, out, amax)
+                self._call(op)
             ev[1].record()
             torch.cuda.synchronize()
             ms = ev[0].elapsed_time(ev[1]) / iters

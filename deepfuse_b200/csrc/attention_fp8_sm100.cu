@@ -11,9 +11,11 @@
 // Softmax follows upstream exactly in form: p = exp(s + mask - rowmax) / (sum + 1e-6), and p = 0
 // where mask < -1e8.  It is evaluated blockwise (online): per 128-key block the running row maximum
 // and sum are updated and the block's probabilities multiply V on the tensor cores; the [T,T] score
-// matrix never exists in memory.  A probability (scaled by 256) is handed to the tensor core as the sum
-// of two e4m3 numbers, its rounding and the rounding of what is left, i.e. with about 7 mantissa bits:
-// a single e4m3 rounding (3 bits) leaves ~2 % error on flat attention rows, outside the 1e-2 bound.
+// matrix never exists in memory.  A probability (scaled by a power of two) is handed to the tensor core as
+// the sum of two e4m3 numbers, its rounding and the rounding of what is left, i.e. with about 7 mantissa
+// bits: a single e4m3 rounding (3 bits) leaves ~2 % error on flat attention rows, outside the 1e-2 bound.
+// The exponentials and the split run on packed halves (two keys per instruction); the row sum is taken by
+// the tensor core as well (P times a tile of ones), so it is the sum of exactly the values that multiply V.
 //
 // One CTA = one (batch, head, 128-query block).
 //   warp 0     TMA producer: Q tile once, then K/V tiles through a 2-stage ring
@@ -22,8 +24,8 @@
 //   warps 2-9  softmax:      two threads per query row (warps w and w+4 share a TMEM lane quarter and take 64
 //                            of the block's 128 key columns each, exchanging the row maximum through smem);
 //                            tcgen05.ld of the scores, exp2, P -> swizzled smem as the A operand of the PV
-//                            product.  O accumulates in TMEM across key blocks and is rescaled (tcgen05.ld/st)
-//                            only when the row maximum has grown past a threshold
+//                            product.  O and the row sum accumulate in TMEM across key blocks and are
+//                            rescaled (tcgen05.ld/st) only when the row maximum has grown past a threshold
 // All mbarrier waits are bounded (status word, see df8_status_word_read).
 #include "df8_internal.cuh"
 #include "sm100_ptx.cuh"
@@ -49,7 +51,7 @@ struct AttnArgs {
     int B, T, H, E;
     int mask_mode;       // 0 none, 1 causal, 2 additive tensor
     int mask_b;
-    uint32_t idesc_qk, idesc_pv;
+    uint32_t idesc_qk, idesc_pv, idesc_sum;
     unsigned int* status;
 };
 
@@ -61,11 +63,13 @@ struct AttnCfg {
     static constexpr int kStageBytes = 2 * kKBytes;  // K then V
     static constexpr int kStages = 2;
     static constexpr int kPBytes = 2 * 2 * BQ * BKV;  // two buffers of {leading part, remainder} e4m3 tiles
+    static constexpr int kOnesBytes = 16 * 128;       // 16 x 128 tile of e4m3 ones: B operand of the row-sum product
     static constexpr int kBarBytes = 128 + 2 * 2 * BQ * 8;  // mbarriers + the tagged row-maximum exchange between warp pairs
-    static constexpr int kUsedBytes = kQBytes + kStages * kStageBytes + kPBytes + kBarBytes + 1024;
+    static constexpr int kUsedBytes = kQBytes + kStages * kStageBytes + kPBytes + kOnesBytes + kBarBytes + 1024;
     // pad the request so that at most two CTAs share an SM: each allocates 256 of the 512 TMEM columns
     static constexpr int kSmemBytes = kUsedBytes < 110 * 1024 ? 110 * 1024 : kUsedBytes;
-    static constexpr int kTmemCols = 256;  // S: columns [0,128), O_blk: [128, 128+D)
+    // S: columns [0,128), O: [128, 128+D), row sum: [128+D, 128+D+16) (sixteen identical copies)
+    static constexpr int kTmemCols = D == 64 ? 256 : 512;
 };
 
 __device__ __forceinline__ void record_timeout(unsigned int* status, unsigned int code) {
@@ -80,6 +84,37 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// packed-half helpers: element 0 lives in the low half
+__device__ __forceinline__ uint32_t pack_f16x2(float e0, float e1) {
+    uint32_t d;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(e1), "f"(e0));
+    return d;
+}
+__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
+    uint32_t d;
+    asm("ex2.approx.f16x2 %0, %1;" : "=r"(d) : "r"(x));
+    return d;
+}
+__device__ __forceinline__ uint32_t e4m3x2_of_f16x2(uint32_t x) {  // 16 significant bits
+    uint16_t d;
+    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(d) : "r"(x));
+    return d;
+}
+__device__ __forceinline__ uint32_t f16x2_of_e4m3x2(uint32_t x) {
+    uint32_t d;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(d) : "h"(static_cast<uint16_t>(x)));
+    return d;
+}
+__device__ __forceinline__ uint32_t sub_f16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
 
 template <int D>
 __global__ void __launch_bounds__(kAttnThreads, (D == 64 ? 2 : 1))
@@ -91,7 +126,8 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
     uint8_t* sQ = smem;
     uint8_t* sKV = sQ + Cfg::kQBytes;
     uint8_t* sP = sKV + Cfg::kStages * Cfg::kStageBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + Cfg::kPBytes);
+    uint8_t* sOnes = sP + Cfg::kPBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sOnes + Cfg::kOnesBytes);
     uint64_t* q_full = bars;
     uint64_t* kv_full = bars + 1;   // [2]
     uint64_t* kv_empty = bars + 3;  // [2]
@@ -124,6 +160,9 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
         mbar_fence_init();
     }
     for (int i = threadIdx.x; i < 2 * 2 * BQ; i += kAttnThreads) xch[i] = 0ull;
+    for (int i = threadIdx.x; i < Cfg::kOnesBytes / 4; i += kAttnThreads)
+        reinterpret_cast<uint32_t*>(sOnes)[i] = 0x38383838u;  // e4m3 1.0; every byte equal, so no swizzle to honour
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
         tmem_relinquish();
@@ -134,6 +173,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_s = tmem_base;
     const uint32_t tmem_o = tmem_base + 128;
+    const uint32_t tmem_l = tmem_base + 128 + D;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -155,23 +195,34 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            auto issue_qk = [&](int stage) {
-                const uint32_t qa = smem_u32(sQ);
-                const uint32_t ka = smem_u32(sKV + stage * Cfg::kStageBytes);
+            // The issuing thread's scalar instructions bound the MMA issue rate at these small shapes (about 5
+            // cycles per dependent instruction, ~18 MMAs per key block), so every descriptor is split into a
+            // constant high half and a low half that only needs 32-bit adds.
+            const uint64_t qd = make_desc_kmajor<SW>(smem_u32(sQ));
+            const uint64_t kd = make_desc_kmajor<SW>(smem_u32(sKV));
+            const uint64_t vd = make_desc_mnmajor<SW>(smem_u32(sKV + Cfg::kKBytes), 8 * SW);
+            const uint64_t pd = make_desc_kmajor<128>(smem_u32(sP));
+            const uint64_t od = make_desc_kmajor<128>(smem_u32(sOnes));
+            const uint32_t q_lo = desc_lo(qd), k_lo0 = desc_lo(kd), v_lo0 = desc_lo(vd), p_lo0 = desc_lo(pd), o_lo = desc_lo(od);
+            const uint32_t qk_hi = desc_hi(qd), v_hi = desc_hi(vd), p_hi = desc_hi(pd);
+            constexpr uint32_t kStageStep = Cfg::kStageBytes >> 4, kPBufStep = (2 * BQ * BKV) >> 4, kPPartStep = (BQ * BKV) >> 4;
+            const uint32_t idesc_qk = args.idesc_qk, idesc_pv = args.idesc_pv, idesc_sum = args.idesc_sum;
+            const uint32_t s_full_b = smem_u32(s_full), o_full_b = smem_u32(o_full);
+            auto issue_qk = [&](uint32_t k_lo) {
+                tc_mma_f8(tmem_s, desc_join(q_lo, qk_hi), desc_join(k_lo, qk_hi), idesc_qk, 0);
 #pragma unroll
-                for (int k = 0; k < D / 32; ++k)
-                    tc_mma_f8(tmem_s, make_desc_kmajor<SW>(qa + k * 32), make_desc_kmajor<SW>(ka + k * 32),
-                              args.idesc_qk, k != 0);
-                tc_commit(smem_u32(s_full));
+                for (int k = 1; k < D / 32; ++k)
+                    tc_mma_f8_acc(tmem_s, desc_join(q_lo + 2 * k, qk_hi), desc_join(k_lo + 2 * k, qk_hi), idesc_qk);
+                tc_commit(s_full_b);
             };
             bool ok = mbar_wait_bounded(smem_u32(q_full), 0) && mbar_wait_bounded(smem_u32(kv_full + 0), 0);
             if (!ok) record_timeout(args.status, 0x1200u);
             if (ok) {
                 tc_fence_after_sync();
-                issue_qk(0);
+                issue_qk(k_lo0);
             }
-            const uint64_t pdesc0 = make_desc_kmajor<128>(smem_u32(sP));  // descriptors advance by adding bytes/16
             for (int j = 0; j < n_kv && ok; ++j) {
+                const uint32_t sj = uint32_t(j & 1);
                 if (j + 1 < n_kv) {
                     // the softmax warps release S as soon as they hold block j's scores in registers, so
                     // the next block's Q.K^T runs underneath their exponentials
@@ -182,25 +233,32 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                         break;
                     }
                     tc_fence_after_sync();
-                    issue_qk(s1);
+                    issue_qk(k_lo0 + uint32_t(s1) * kStageStep);
                 }
                 if (!mbar_wait_bounded(smem_u32(p_full), j & 1)) {
                     record_timeout(args.status, 0x1400u);
                     break;
                 }
                 tc_fence_after_sync();
-                // O (+)= P.V, accumulated in TMEM over the key blocks; P = leading part + remainder
-                const uint64_t vdesc = make_desc_mnmajor<SW>(smem_u32(sKV + (j & 1) * Cfg::kStageBytes + Cfg::kKBytes), 8 * SW);
-                const uint64_t pdesc = pdesc0 + uint64_t(((j & 1) * 2 * BQ * BKV) >> 4);
-#pragma unroll
-                for (int part = 0; part < 2; ++part) {
-#pragma unroll
-                    for (int k = 0; k < BKV / 32; ++k)
-                        tc_mma_f8(tmem_o, pdesc + uint64_t((part * BQ * BKV + k * 32) >> 4),
-                                  vdesc + uint64_t((k * 32 * D) >> 4), args.idesc_pv, (j | part | k) != 0);
+                // O (+)= P.V and row sums (+)= P.1, accumulated in TMEM over the key blocks; P = leading part +
+                // remainder.  Per 32 keys: P advances 32 bytes inside its 128-byte rows, V advances 32 rows of D bytes.
+                const uint32_t v_lo = v_lo0 + sj * kStageStep, p_lo = p_lo0 + sj * kPBufStep;
+                if (j == 0) {
+                    tc_mma_f8(tmem_o, desc_join(p_lo, p_hi), desc_join(v_lo, v_hi), idesc_pv, 0);
+                    tc_mma_f8(tmem_l, desc_join(p_lo, p_hi), desc_join(o_lo, p_hi), idesc_sum, 0);
+                } else {
+                    tc_mma_f8_acc(tmem_o, desc_join(p_lo, p_hi), desc_join(v_lo, v_hi), idesc_pv);
+                    tc_mma_f8_acc(tmem_l, desc_join(p_lo, p_hi), desc_join(o_lo, p_hi), idesc_sum);
                 }
-                tc_commit(smem_u32(o_full));  // "P.V of block j done": P is free, O may be touched
-                tc_commit(smem_u32(kv_empty + (j & 1)));
+#pragma unroll
+                for (int i = 1; i < 2 * (BKV / 32); ++i) {
+                    const int part = i / (BKV / 32), k = i % (BKV / 32);
+                    const uint32_t pl = p_lo + part * kPPartStep + 2 * k;
+                    tc_mma_f8_acc(tmem_o, desc_join(pl, p_hi), desc_join(v_lo + ((k * 32 * D) >> 4), v_hi), idesc_pv);
+                    tc_mma_f8_acc(tmem_l, desc_join(pl, p_hi), desc_join(o_lo + 2 * k, p_hi), idesc_sum);
+                }
+                tc_commit(o_full_b);  // "P.V of block j done": P is free, O may be touched
+                tc_commit(smem_u32(kv_empty + sj));
             }
         }
     } else {
@@ -240,11 +298,12 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
         // moved (and O, l rescaled) when the true running maximum has grown by more than kLazy: then
         // p' <= 2^(kPShift + kLazy) stays inside e4m3 (max 448), and the TMEM round trip that rescales O
         // is rare after the first key blocks.
-        constexpr float kPShift = 6.0f;
+        // The exponent t - m + kPShift is rounded to half precision before exp2: its magnitude stays below 8
+        // for every key that matters, i.e. an absolute error of at most 2^-9 in the exponent (0.14 % of p).
+        constexpr float kPShift = 5.0f;
         constexpr float kLazy = 2.5f;
         float m = -INFINITY;       // reference maximum of the exponentials (log2 domain)
         float m_true = -INFINITY;  // true running maximum of the row
-        float l = 0.f;             // running sum of p' over this thread's columns
         bool ok = true;
         int pv_waited = 0;         // number of "P.V done" phases this thread has observed
 
@@ -269,10 +328,13 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
             const bool edge = (j * BKV + BKV > T) || (args.mask_mode == 1 && j * BKV + BKV - 1 > q0) || (args.mask_mode == 2);
             float mb = -INFINITY;
             if (!edge) {
-                float raw = -INFINITY;
+                float ra = -INFINITY, rb = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < HC; ++i) raw = fmaxf(raw, __uint_as_float(r[i]));
-                mb = raw * cs;  // cs > 0: the maximum commutes with the scaling; r stays unscaled (see below)
+                for (int i = 0; i < HC; i += 4) {
+                    ra = fmax3(ra, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                    rb = fmax3(rb, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                }
+                mb = fmaxf(ra, rb) * cs;  // cs > 0: the maximum commutes with the scaling; r stays unscaled (see below)
             } else {
 #pragma unroll
                 for (int i = 0; i < HC; ++i) {
@@ -308,7 +370,6 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                 if (move) {
                     alpha = ex2(m - m_true);  // 0 when m was -inf
                     m = m_true;
-                    l *= alpha;
                 }
                 if (j > 0) {
                     // O holds the products of blocks < j: wait until the last of them has landed, then scale
@@ -336,6 +397,12 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
                         tmem_st_32x32(oaddr, o);
                     }
+                    if (half == 0) {  // the row sum: only column 0 of its sixteen copies is ever read back
+                        const uint32_t laddr = tmem_l + lane_addr;
+                        const float lv = __uint_as_float(tmem_ld_32x1(laddr));
+                        tmem_ld_wait();
+                        tmem_st_32x1(laddr, __float_as_uint(lv * alpha));
+                    }
                     tmem_st_wait();
                 }
             }
@@ -356,27 +423,24 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                 break;
             }
 
-            float psum = 0.f;
             uint8_t* prow = sP + (j & 1) * 2 * BQ * BKV + row * 128;
+            const float nshift = -shift;
 #pragma unroll
             for (int c = 0; c < HC / 32; ++c) {
                 uint32_t w[8], wl[8];
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
-                    float p[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        p[i] = ex2(fmaf(__uint_as_float(r[c * 32 + 4 * g + i]), ecs, -shift));
-                        psum += p[i];
-                    }
-                    // leading part = p rounded to e4m3's 3 mantissa bits with integer arithmetic (the conversion
-                    // unit is this kernel's bottleneck: exp2 and the fp8 packs already saturate it), remainder exact
-                    float hi[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        hi[i] = __uint_as_float((__float_as_uint(p[i]) + 0x00080000u) & 0xFFF00000u);
-                    w[g] = cvt_f32x4_to_fp8x4<DF8_E4M3>(hi[0], hi[1], hi[2], hi[3]);
-                    wl[g] = cvt_f32x4_to_fp8x4<DF8_E4M3>(p[0] - hi[0], p[1] - hi[1], p[2] - hi[2], p[3] - hi[3]);
+                    const int i0 = c * 32 + 4 * g;
+                    // two keys per instruction from here on: exp2, leading e4m3 part, exact remainder, its e4m3
+                    const uint32_t pa = ex2_f16x2(pack_f16x2(fmaf(__uint_as_float(r[i0]), ecs, nshift),
+                                                             fmaf(__uint_as_float(r[i0 + 1]), ecs, nshift)));
+                    const uint32_t pb = ex2_f16x2(pack_f16x2(fmaf(__uint_as_float(r[i0 + 2]), ecs, nshift),
+                                                             fmaf(__uint_as_float(r[i0 + 3]), ecs, nshift)));
+                    const uint32_t ha = e4m3x2_of_f16x2(pa), hb = e4m3x2_of_f16x2(pb);
+                    const uint32_t la = e4m3x2_of_f16x2(sub_f16x2(pa, f16x2_of_e4m3x2(ha)));
+                    const uint32_t lb = e4m3x2_of_f16x2(sub_f16x2(pb, f16x2_of_e4m3x2(hb)));
+                    w[g] = ha | (hb << 16);
+                    wl[g] = la | (lb << 16);
                 }
                 const int cc = half * (HC / 16) + 2 * c;  // 16-byte chunk index inside the 128-byte row
                 const int o0 = (cc ^ (row & 7)) << 4, o1 = ((cc + 1) ^ (row & 7)) << 4;
@@ -385,7 +449,6 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                 *reinterpret_cast<uint4*>(prow + BQ * BKV + o0) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
                 *reinterpret_cast<uint4*>(prow + BQ * BKV + o1) = make_uint4(wl[4], wl[5], wl[6], wl[7]);
             }
-            l += psum;
             // catch up with the "P.V done" barrier before the issuer can complete another phase: a waiter must
             // never fall two phases behind a parity-tracked mbarrier (block j-1's product is long finished here)
             while (pv_waited < j) {
@@ -419,10 +482,12 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
         }
         if (__all_sync(0xffffffffu, ok)) {
             tc_fence_after_sync();
-            // the row sum is the sum of the two halves
-            float l_other = 0.f;
-            if (!swap_with_partner(n_kv, l, l_other) && lane == 0) record_timeout(args.status, 0x1a00u);
-            l += l_other;
+            // the row sum, accumulated by the tensor core next to O
+            float l = 0.f;
+            if (n_kv > 0) {
+                l = __uint_as_float(tmem_ld_32x1(tmem_l + lane_addr));
+                tmem_ld_wait();
+            }
             // upstream: p = exp(s - max) / (sum + 1e-6).  Here sum' = 2^kPShift * sum * 2^(max - m), so the
             // 1e-6 is carried over with the same factor.
             const float eps = 1e-6f * ex2(kPShift + ((m == -INFINITY) ? 0.f : (m_true - m)));
@@ -522,6 +587,7 @@ extern "C" df8_status df8_attention_fp8(const uint8_t* qkv_codes, df8_kind kind,
     a.mask_b = mask_b;
     a.idesc_qk = ptx::make_idesc_f8(BQ, BKV, int(kind), int(kind));
     a.idesc_pv = ptx::make_idesc_f8(BQ, D, DF8_E4M3, int(kind), 0, 1);
+    a.idesc_sum = ptx::make_idesc_f8(BQ, 16, DF8_E4M3, DF8_E4M3);
     a.status = status_ptr;
     dim3 grid((T + BQ - 1) / BQ, H, B);
     return D == 64 ? launch_attention<64>(tm, a, grid, st) : launch_attention<128>(tm, a, grid, st);

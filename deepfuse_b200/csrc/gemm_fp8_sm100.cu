@@ -10,13 +10,14 @@
 //   warp 0     TMA producer: 128-byte-swizzled K-blocks of A and W into a STAGES-deep smem ring
 //   warp 1     MMA issuer:   tcgen05.mma kind::f8f6f4 (M=128, N=BN, K=32 per instruction),
 //                            fp32 accumulators in TMEM, double-buffered (2 x BN columns)
-//   warps 2-9  epilogue:     two warps per TMEM lane quarter, each taking every other 32-column chunk:
-//                            tcgen05.ld (the next chunk's load in flight while this one is stored) with
-//                            the fused dequant scale, bias, GELU (upstream activation_layer.cu:9-20
-//                            formula), residual add (upstream tensor.cu:383-415) and |out| max reduction.
-//                            fp32 output goes through a per-warp smem transpose so that global stores are
-//                            coalesced along N; fp8 output (32 codes = one 32-byte sector per thread and
-//                            chunk) and the amax-only pass store straight from registers.
+//   warps 2..  epilogue:     fused dequant scale, bias, GELU (upstream activation_layer.cu:9-20 formula),
+//                            residual add (upstream tensor.cu:383-415) and |out| max reduction.
+//                            fp32 output: two warps per TMEM lane quarter, each taking every other 32-column
+//                            chunk (the next chunk's tcgen05.ld in flight while this one is stored), through
+//                            a per-warp smem transpose so that global stores are coalesced along N.
+//                            fp8 output (32 codes = one 32-byte sector per thread and chunk) and the
+//                            amax-only pass: four warps per quarter, all of a warp's chunks pulled into
+//                            registers at once and the TMEM buffer handed back before any arithmetic.
 // The epilogue of tile i overlaps the main loop of tile i+1 through the second TMEM buffer.
 //
 // Output modes: fp32 [M,N]; fp8 codes [M,N] quantised with a scale derived from a given max|out|;
@@ -40,7 +41,6 @@ using namespace ptx;
 constexpr int BM = 128;
 constexpr int BK = 128;  // bytes == fp8 elements per K-block (one 128-byte swizzle row)
 constexpr int kEpiWarps = 8;
-constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 constexpr int kStagingFloatsPerWarp = 32 * 36;
 
 // epilogue / output modes (template parameter MODE)
@@ -49,6 +49,13 @@ constexpr int kOutF32 = 1;      // fp32, any N
 constexpr int kOutE4M3 = 2;     // fp8 codes, N % 16 == 0
 constexpr int kOutE5M2 = 3;
 constexpr int kOutNone = 4;     // max|out| only
+
+// Epilogue warps of the single-CTA kernel.  The fp32 modes are bound by their global stores and run two
+// warps per TMEM lane quarter; the fp8 / amax-only modes are a chain of latencies (TMEM load, conversion,
+// GELU) with nothing to store or little, and run four per quarter so that each SM sub-partition has four
+// warps to interleave.
+__host__ __device__ constexpr int epi_warps(int mode) { return mode >= kOutE4M3 ? 16 : 8; }
+__host__ __device__ constexpr int gemm_threads(int mode) { return 64 + 32 * epi_warps(mode); }
 
 struct GemmArgs {
     const float* scale_a;   // {q, dq} of A
@@ -66,12 +73,13 @@ struct GemmArgs {
     unsigned int* status;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MODE>
 struct GemmCfg {
     static constexpr int kABytes = BM * BK;
     static constexpr int kBBytes = BN * BK;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStagingBytes = kEpiWarps * kStagingFloatsPerWarp * 4;
+    // fp32 modes: a transpose buffer per epilogue warp; fp8 / amax modes: only each warp's bias slice
+    static constexpr int kStagingBytes = MODE >= kOutE4M3 ? epi_warps(MODE) * 64 * 4 : kEpiWarps * kStagingFloatsPerWarp * 4;
     static constexpr int kBarBytes = 256;
     static constexpr int kSmemBytes = STAGES * kStageBytes + kStagingBytes + kBarBytes + 1024;
     static constexpr int kTmemCols = 2 * BN;
@@ -197,15 +205,17 @@ __device__ __forceinline__ void store_chunk_f32(const float* stg, int lane, int 
 // ---- fp8 / amax-only output: thread = row, straight from registers ------------------------------
 
 // KIND: DF8_E4M3 / DF8_E5M2 to emit codes, -1 to only reduce max|out|.
+// `sbias`: the chunk's 32 bias values in shared memory (zeros without a bias), or null to read a.bias.
 template <int KIND>
 __device__ __forceinline__ void direct_chunk(const uint32_t (&r)[32], int grow, int col0, const GemmArgs& a,
-                                             float alpha, float out_q, float& amax) {
+                                             float alpha, float out_q, float& amax, const float* sbias = nullptr) {
     const bool row_ok = grow < a.M;
     uint32_t w[8];
 #pragma unroll
     for (int g = 0; g < 8; ++g) {
         float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (a.bias) b4 = __ldg(reinterpret_cast<const float4*>(a.bias + col0 + 4 * g));  // same address in every lane
+        if (sbias) b4 = *reinterpret_cast<const float4*>(sbias + 4 * g);  // broadcast read
+        else if (a.bias) b4 = __ldg(reinterpret_cast<const float4*>(a.bias + col0 + 4 * g));  // same address in every lane
         float v0 = fmaf(__uint_as_float(r[4 * g]), alpha, b4.x);
         float v1 = fmaf(__uint_as_float(r[4 * g + 1]), alpha, b4.y);
         float v2 = fmaf(__uint_as_float(r[4 * g + 2]), alpha, b4.z);
@@ -233,10 +243,11 @@ __device__ __forceinline__ void direct_chunk(const uint32_t (&r)[32], int grow, 
 }
 
 template <int BN, int STAGES, int MODE>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(gemm_threads(MODE), 1)
 gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_w,
                    const GemmArgs args) {
-    using Cfg = GemmCfg<BN, STAGES>;
+    using Cfg = GemmCfg<BN, STAGES, MODE>;
+    constexpr int EW = epi_warps(MODE);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     float* staging = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes);
@@ -257,7 +268,7 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(tfull + b), 1);
-            mbar_init(smem_u32(tempty + b), kEpiWarps);
+            mbar_init(smem_u32(tempty + b), EW);
         }
         mbar_fence_init();
     }
@@ -305,8 +316,16 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
         }
     } else if (warp == 1) {
         if (lane == 0) {
+            // This thread's scalar instructions are the issue-rate limit at BN = 128 (a K block is consumed
+            // in 256 cycles), so the loop carries ready-made values: the descriptor of the stage's A tile as
+            // a 32-bit low half that steps with the ring, and the barrier addresses likewise.
+            const uint64_t desc0 = make_desc_kmajor_sw128(smem_u32(smem));
+            const uint32_t dhi = desc_hi(desc0), dlo0 = desc_lo(desc0);
+            constexpr uint32_t kStageStep = Cfg::kStageBytes >> 4, kBOff = Cfg::kABytes >> 4;
+            const uint32_t full0 = smem_u32(full), empty0 = smem_u32(empty);
+            const uint32_t idesc = args.idesc;
             int stage = 0;
-            uint32_t phase = 0;
+            uint32_t phase = 0, dlo = dlo0, fullb = full0, emptyb = empty0;
             uint32_t acc_it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++acc_it) {
@@ -319,22 +338,28 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait_bounded(smem_u32(full + stage), phase)) {
+                    if (!mbar_wait_bounded(fullb, phase)) {
                         record_timeout(args.status, 0x300u + stage);
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t a_addr = smem_u32(smem + stage * Cfg::kStageBytes);
-                    const uint32_t b_addr = a_addr + Cfg::kABytes;
+                    const uint32_t alo = dlo, blo = dlo + kBOff;
+                    if (kb == 0) tc_mma_f8(d_tmem, desc_join(alo, dhi), desc_join(blo, dhi), idesc, 0);
+                    else tc_mma_f8_acc(d_tmem, desc_join(alo, dhi), desc_join(blo, dhi), idesc);
 #pragma unroll
-                    for (int k = 0; k < BK / 32; ++k)
-                        tc_mma_f8(d_tmem, make_desc_kmajor_sw128(a_addr + k * 32),
-                                  make_desc_kmajor_sw128(b_addr + k * 32), args.idesc, (kb | k) != 0);
-                    tc_commit(smem_u32(empty + stage));
+                    for (int k = 1; k < BK / 32; ++k)  // 32 bytes of K = 2 descriptor address units
+                        tc_mma_f8_acc(d_tmem, desc_join(alo + 2 * k, dhi), desc_join(blo + 2 * k, dhi), idesc);
+                    tc_commit(emptyb);
+                    dlo += kStageStep;
+                    fullb += 8;
+                    emptyb += 8;
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1;
+                        dlo = dlo0;
+                        fullb = full0;
+                        emptyb = empty0;
                     }
                 }
                 if (ok) tc_commit(smem_u32(tfull + buf));
@@ -358,19 +383,56 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
         }
         const uint32_t lane_addr = uint32_t(q * 32) << 16;
         uint32_t acc_it = 0;
+        float amax = 0.f;  // max|out| over all of this warp's tiles: one atomic per warp at the end
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++acc_it) {
             const uint32_t buf = acc_it & 1;
             const uint32_t acc_phase = (acc_it >> 1) & 1;
             const int m0 = (tile % num_m) * BM;
             const int n0 = (tile / num_m) * BN;
+            const int row0 = m0 + q * 32;
+            const uint32_t taddr = tmem_base + buf * BN + lane_addr;
+            if constexpr (MODE >= kOutE4M3) {
+                // Four warps per lane quarter; warp `part` takes the 32-column chunks part, part + 4, ...
+                // Its bias slice goes to shared memory before the accumulators are waited for; the chunks
+                // are pulled into registers in one go and the TMEM buffer is handed back before any math.
+                constexpr int KIND = MODE == kOutE4M3 ? int(DF8_E4M3) : (MODE == kOutE5M2 ? int(DF8_E5M2) : -1);
+                constexpr int kParts = EW / 4;
+                constexpr int kCh = BN / (32 * kParts);
+                const int part = e >> 2;
+                float* sb = staging + e * (32 * kCh);
+#pragma unroll
+                for (int j = 0; j < kCh; ++j) {
+                    const int col = n0 + 32 * (part + kParts * j) + lane;
+                    sb[j * 32 + lane] = (args.bias && col < args.N) ? __ldg(args.bias + col) : 0.f;
+                }
+                __syncwarp();
+                if (!mbar_wait_bounded(smem_u32(tfull + buf), acc_phase)) {
+                    if (lane == 0) record_timeout(args.status, 0x400u + buf);
+                    break;
+                }
+                tc_fence_after_sync();
+                uint32_t r[kCh][32];
+#pragma unroll
+                for (int j = 0; j < kCh; ++j)
+                    if (n0 + 32 * (part + kParts * j) < args.N) tmem_ld_32x32(taddr + 32 * (part + kParts * j), r[j]);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(tempty + buf));
+                const int grow = row0 + lane;
+#pragma unroll
+                for (int j = 0; j < kCh; ++j) {
+                    const int col0 = n0 + 32 * (part + kParts * j);
+                    if (col0 < args.N) direct_chunk<KIND>(r[j], grow, col0, args, alpha, out_q, amax, sb + j * 32);
+                }
+                __syncwarp();  // every lane is done with the bias slice before the next tile overwrites it
+                continue;
+            }
             if (!mbar_wait_bounded(smem_u32(tfull + buf), acc_phase)) {
                 if (lane == 0) record_timeout(args.status, 0x400u + buf);
                 break;
             }
             tc_fence_after_sync();
-            float amax = 0.f;
-            const int row0 = m0 + q * 32;
-            const uint32_t taddr = tmem_base + buf * BN + lane_addr;
             int nvalid = 0;  // chunks of this warp that start inside N (uniform across the warp)
 #pragma unroll
             for (int j = 0; j < kChunks; ++j)
@@ -398,24 +460,11 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(tempty + buf));
                 }
-            } else {
-                constexpr int KIND = MODE == kOutE4M3 ? int(DF8_E4M3) : (MODE == kOutE5M2 ? int(DF8_E5M2) : -1);
-                const int grow = row0 + lane;
-#pragma unroll 1
-                for (int j = 0; j < nvalid; ++j) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(taddr + 32 * (half + 2 * j), r);
-                    tmem_ld_wait();
-                    direct_chunk<KIND>(r, grow, n0 + 32 * (half + 2 * j), args, alpha, out_q, amax);
-                }
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(tempty + buf));
             }
-            if (args.flags & 4) {
-                amax = warp_max(amax);
-                if (lane == 0 && amax > 0.f) atomic_max_nonneg(args.out_amax, amax);
-            }
+        }
+        if (args.flags & 4) {
+            amax = warp_max(amax);
+            if (lane == 0 && amax > 0.f) atomic_max_nonneg(args.out_amax, amax);
         }
     }
 
@@ -436,12 +485,13 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
 // one MMA (M = 256) that reads both CTAs' shared memory; each CTA's TMEM receives its own 128 rows, and each
 // CTA runs its own epilogue.  Loads stay plain per-CTA TMA loads; only barrier arrivals cross between CTAs.
 template <int STAGES, int MODE>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(gemm_threads(MODE), 1)
 gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_w,
                         const GemmArgs args) {
     constexpr int BN = 256;
     constexpr int kABytes = BM * BK, kBBytes = (BN / 2) * BK, kStageBytes = kABytes + kBBytes;
-    constexpr int kStagingBytes = kEpiWarps * kStagingFloatsPerWarp * 4;
+    constexpr int EW = epi_warps(MODE);
+    constexpr int kStagingBytes = kEpiWarps * kStagingFloatsPerWarp * 4;  // fp8 / amax modes use 4 KB of it (bias slices)
     constexpr int kTmemCols = 2 * BN;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -465,7 +515,7 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(tfull + b), 1);
-            mbar_init(smem_u32(tempty + b), 2 * kEpiWarps);
+            mbar_init(smem_u32(tempty + b), 2 * EW);
         }
         mbar_fence_init();
     }
@@ -517,6 +567,8 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
         }
     } else if (warp == 1) {
         if (lane == 0 && leader) {
+            const uint64_t desc0 = make_desc_kmajor_sw128(smem_u32(smem));
+            const uint32_t dhi = desc_hi(desc0), dlo0 = desc_lo(desc0);
             int stage = 0;
             uint32_t phase = 0;
             uint32_t acc_it = 0;
@@ -537,12 +589,12 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t a_addr = smem_u32(smem + stage * kStageBytes);
-                    const uint32_t b_addr = a_addr + kABytes;
+                    const uint32_t alo = dlo0 + uint32_t(stage) * (kStageBytes >> 4), blo = alo + (kABytes >> 4);
+                    if (kb == 0) tc_mma_f8_pair(d_tmem, desc_join(alo, dhi), desc_join(blo, dhi), args.idesc, 0);
+                    else tc_mma_f8_pair_acc(d_tmem, desc_join(alo, dhi), desc_join(blo, dhi), args.idesc);
 #pragma unroll
-                    for (int k = 0; k < BK / 32; ++k)
-                        tc_mma_f8_pair(d_tmem, make_desc_kmajor_sw128(a_addr + k * 32),
-                                       make_desc_kmajor_sw128(b_addr + k * 32), args.idesc, (kb | k) != 0);
+                    for (int k = 1; k < BK / 32; ++k)
+                        tc_mma_f8_pair_acc(d_tmem, desc_join(alo + 2 * k, dhi), desc_join(blo + 2 * k, dhi), args.idesc);
                     // the stage is free in both CTAs once these MMAs have read it
                     tc_commit_pair(smem_u32(empty + stage));
                     tc_commit_pair(map_to_cta(smem_u32(empty + stage), 1));
@@ -581,19 +633,53 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
             }
         };
         uint32_t acc_it = 0;
+        float amax = 0.f;
         for (int tile = pair; tile < num_tiles; tile += npairs, ++acc_it) {
             const uint32_t buf = acc_it & 1;
             const uint32_t acc_phase = (acc_it >> 1) & 1;
             const int m0 = (tile % num_m) * 2 * BM + int(rank) * BM;
             const int n0 = (tile / num_m) * BN;
+            const int row0 = m0 + q * 32;
+            const uint32_t taddr = tmem_base + buf * BN + lane_addr;
+            if constexpr (MODE >= kOutE4M3) {  // as in the single-CTA kernel
+                constexpr int KIND = MODE == kOutE4M3 ? int(DF8_E4M3) : (MODE == kOutE5M2 ? int(DF8_E5M2) : -1);
+                constexpr int kParts = EW / 4;
+                constexpr int kCh = BN / (32 * kParts);
+                const int part = e >> 2;
+                float* sb = staging + e * (32 * kCh);
+#pragma unroll
+                for (int j = 0; j < kCh; ++j) {
+                    const int col = n0 + 32 * (part + kParts * j) + lane;
+                    sb[j * 32 + lane] = (args.bias && col < args.N) ? __ldg(args.bias + col) : 0.f;
+                }
+                __syncwarp();
+                if (!mbar_wait_bounded(smem_u32(tfull + buf), acc_phase)) {
+                    if (lane == 0) record_timeout(args.status, 0x2400u + (rank << 4) + buf);
+                    break;
+                }
+                tc_fence_after_sync();
+                uint32_t r[kCh][32];
+#pragma unroll
+                for (int j = 0; j < kCh; ++j)
+                    if (n0 + 32 * (part + kParts * j) < args.N) tmem_ld_32x32(taddr + 32 * (part + kParts * j), r[j]);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                release(buf);
+                const int grow = row0 + lane;
+#pragma unroll
+                for (int j = 0; j < kCh; ++j) {
+                    const int col0 = n0 + 32 * (part + kParts * j);
+                    if (col0 < args.N) direct_chunk<KIND>(r[j], grow, col0, args, alpha, out_q, amax, sb + j * 32);
+                }
+                __syncwarp();
+                continue;
+            }
             if (!mbar_wait_bounded(smem_u32(tfull + buf), acc_phase)) {
                 if (lane == 0) record_timeout(args.status, 0x2400u + (rank << 4) + buf);
                 break;
             }
             tc_fence_after_sync();
-            float amax = 0.f;
-            const int row0 = m0 + q * 32;
-            const uint32_t taddr = tmem_base + buf * BN + lane_addr;
             int nvalid = 0;
 #pragma unroll
             for (int j = 0; j < kChunks; ++j)
@@ -621,24 +707,11 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
                     __syncwarp();
                     release(buf);
                 }
-            } else {
-                constexpr int KIND = MODE == kOutE4M3 ? int(DF8_E4M3) : (MODE == kOutE5M2 ? int(DF8_E5M2) : -1);
-                const int grow = row0 + lane;
-#pragma unroll 1
-                for (int j = 0; j < nvalid; ++j) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(taddr + 32 * (half + 2 * j), r);
-                    tmem_ld_wait();
-                    direct_chunk<KIND>(r, grow, n0 + 32 * (half + 2 * j), args, alpha, out_q, amax);
-                }
-                tc_fence_before_sync();
-                __syncwarp();
-                release(buf);
             }
-            if (args.flags & 4) {
-                amax = warp_max(amax);
-                if (lane == 0 && amax > 0.f) atomic_max_nonneg(args.out_amax, amax);
-            }
+        }
+        if (args.flags & 4) {
+            amax = warp_max(amax);
+            if (lane == 0 && amax > 0.f) atomic_max_nonneg(args.out_amax, amax);
         }
     }
 
@@ -670,7 +743,7 @@ df8_status launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tw, const 
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(grid), 1, 1);
-    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.blockDim = dim3(gemm_threads(MODE), 1, 1);
     cfg.dynamicSmemBytes = kPairSmemBytes;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -689,7 +762,7 @@ df8_status launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tw, const 
 template <int BN, int STAGES, int MODE>
 df8_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmArgs& args, int grid,
                        cudaStream_t st) {
-    using Cfg = GemmCfg<BN, STAGES>;
+    using Cfg = GemmCfg<BN, STAGES, MODE>;
     auto kern = gemm_fp8_tn_kernel<BN, STAGES, MODE>;
     static bool configured[64] = {};
     int dev = 0;
@@ -698,7 +771,7 @@ df8_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmA
         DF8_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         configured[dev] = true;
     }
-    kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ta, tw, args);
+    kern<<<grid, gemm_threads(MODE), Cfg::kSmemBytes, st>>>(ta, tw, args);
     DF8_LAUNCH_CHECK("gemm_fp8_tn_kernel");
     return DF8_OK;
 }
@@ -706,7 +779,13 @@ df8_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmA
 template <int MODE>
 df8_status launch_gemm_bn(bool wide, const CUtensorMap& ta, const CUtensorMap& tw, const GemmArgs& args, int grid,
                           cudaStream_t st) {
-    return wide ? launch_gemm<256, 3, MODE>(ta, tw, args, grid, st) : launch_gemm<128, 5, MODE>(ta, tw, args, grid, st);
+    // ring depth: whatever fits beside the epilogue's staging.  One K block of operands takes ~1300 cycles to
+    // arrive from L2 and ~512 (256 at BN = 128) to consume, so three 48 KB stages leave the tensor core waiting;
+    // the fp8 / amax modes need no transpose buffer and get a deeper ring.
+    if constexpr (MODE >= kOutE4M3)
+        return wide ? launch_gemm<256, 4, MODE>(ta, tw, args, grid, st) : launch_gemm<128, 6, MODE>(ta, tw, args, grid, st);
+    else
+        return wide ? launch_gemm<256, 3, MODE>(ta, tw, args, grid, st) : launch_gemm<128, 5, MODE>(ta, tw, args, grid, st);
 }
 
 // DF8_GEMM_PAIR=0 / 1 in the environment (read at every call) forces the choice for profiling and tests;
@@ -748,13 +827,15 @@ df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uin
             default: return launch_gemm_pair<kOutNone>(ta2, tw2, args, grid2, st);
         }
     }
-    // tile width: the one that fills whole waves of the persistent grid best (wider tiles reuse A more)
-    auto efficiency = [&](int bn, double weight) {
+    // Tile width.  A TMA tiled load costs the SM's copy engine ~250 cycles whatever its size, and L2 delivers
+    // ~85 bytes per cycle to an SM: a 128 x 128 K block (two loads, 32 KB) therefore takes ~530 cycles although
+    // its MMAs need 256, about as long as a 128 x 256 one (48 KB, MMAs 512).  So narrow tiles only pay when
+    // they save whole rounds of the persistent grid.
+    auto rounds = [&](int bn) {
         const long tiles = long((M + BM - 1) / BM) * ((N + bn - 1) / bn);
-        const long waves = (tiles + sms - 1) / sms;
-        return weight * double(tiles) / double(waves * sms) * (double(N) / double(((N + bn - 1) / bn) * bn));
+        return double((tiles + sms - 1) / sms);
     };
-    const bool wide = efficiency(256, 1.0) >= efficiency(128, 0.92);
+    const bool wide = N > 128 && rounds(256) * 1.0 <= rounds(128) * 0.94;
     const int bn = wide ? 256 : 128;
     const long tiles = long((M + BM - 1) / BM) * ((N + bn - 1) / bn);
     const int grid = int(tiles < sms ? tiles : sms);

@@ -223,9 +223,16 @@ layernorm_rows_kernel(const float* __restrict__ x, int rows, int C, const float*
         }
     }
     if constexpr (MODE != 2) {
-        if (amax_out) {
+        if (amax_out) {  // uniform across the block: one atomic per block, not one per warp
+            __shared__ float block_amax[kLnThreads / 32];
             const float mx = warp_max(warp_amax);
-            if (lane == 0 && mx > 0.f) atomic_max_nonneg(amax_out, mx);
+            if (lane == 0) block_amax[threadIdx.x >> 5] = mx;
+            __syncthreads();
+            if (threadIdx.x < 32) {
+                float m = threadIdx.x < kLnThreads / 32 ? block_amax[threadIdx.x] : 0.f;
+                m = warp_max(m);
+                if (threadIdx.x == 0 && m > 0.f) atomic_max_nonneg(amax_out, m);
+            }
         }
     }
 }

@@ -17,15 +17,20 @@
 // The exponentials and the split run on packed halves (two keys per instruction); the row sum is taken by
 // the tensor core as well (P times a tile of ones), so it is the sum of exactly the values that multiply V.
 //
-// One CTA = one (batch, head, 128-query block).
-//   warp 0     TMA producer: Q tile once, then K/V tiles through a 2-stage ring
+// Work item = one (batch, head, 128-query block).  The grid is persistent: as many CTAs as fit on the GPU
+// at once (two per SM at D = 64), each walking the items blockIdx.x, blockIdx.x + gridDim.x, ... with its
+// barriers, TMEM and shared memory set up once; every barrier parity follows a running block counter.
+// (Launched as one CTA per item, the block scheduler left the slot of a finished CTA empty for many
+// microseconds: the kernel took 1.7x the sum of its CTA times.)
+//   warp 0     TMA producer: an item's Q tile, then its K/V tiles through a 2-stage ring
 //   warp 1     MMA issuer:   S = Q.K^T (M=128, N=128, K=D) and O_blk = P.V (M=128, N=D, K=128),
 //                            V consumed as an N-major operand straight from its [keys, D] tile
-//   warps 2-9  softmax:      two threads per query row (warps w and w+4 share a TMEM lane quarter and take 64
-//                            of the block's 128 key columns each, exchanging the row maximum through smem);
-//                            tcgen05.ld of the scores, exp2, P -> swizzled smem as the A operand of the PV
-//                            product.  O and the row sum accumulate in TMEM across key blocks and are
-//                            rescaled (tcgen05.ld/st) only when the row maximum has grown past a threshold
+//   warps 2-5  softmax:      one thread per query row with the block's 128 scores in registers (tcgen05.ld),
+//                            row maximum, exp2 on packed halves, P -> swizzled smem as the A operand of the
+//                            PV product.  O and the row sum accumulate in TMEM across key blocks and are
+//                            rescaled (tcgen05.ld/st) only when the row maximum has grown past a threshold.
+//                            (Two threads per row with 64 scores each spilled at the 96 registers two CTAs
+//                            per SM allow with 320 threads, and paid ~700 cycles per block to swap maxima.)
 // All mbarrier waits are bounded (status word, see df8_status_word_read).
 #include "df8_internal.cuh"
 #include "sm100_ptx.cuh"
@@ -37,7 +42,7 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kSoftmaxWarps = 8;  // two per TMEM lane quarter: each takes half of the block's 128 key columns
+constexpr int kSoftmaxWarps = 4;  // one per TMEM lane quarter
 constexpr int kAttnThreads = 64 + 32 * kSoftmaxWarps;
 constexpr int BQ = 128;
 constexpr int BKV = 128;
@@ -49,6 +54,7 @@ struct AttnArgs {
     float* out;          // [B*T, E] fp32
     float* out_amax;     // 1 float or null
     int B, T, H, E;
+    int n_qblk, n_items;
     int mask_mode;       // 0 none, 1 causal, 2 additive tensor
     int mask_b;
     uint32_t idesc_qk, idesc_pv, idesc_sum;
@@ -64,7 +70,7 @@ struct AttnCfg {
     static constexpr int kStages = 2;
     static constexpr int kPBytes = 2 * 2 * BQ * BKV;  // two buffers of {leading part, remainder} e4m3 tiles
     static constexpr int kOnesBytes = 16 * 128;       // 16 x 128 tile of e4m3 ones: B operand of the row-sum product
-    static constexpr int kBarBytes = 128 + 2 * 2 * BQ * 8;  // mbarriers + the tagged row-maximum exchange between warp pairs
+    static constexpr int kBarBytes = 128;  // mbarriers and the TMEM base slot
     static constexpr int kUsedBytes = kQBytes + kStages * kStageBytes + kPBytes + kOnesBytes + kBarBytes + 1024;
     // pad the request so that at most two CTAs share an SM: each allocates 256 of the 512 TMEM columns
     static constexpr int kSmemBytes = kUsedBytes < 110 * 1024 ? 110 * 1024 : kUsedBytes;
@@ -135,17 +141,30 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
     uint64_t* s_empty = bars + 6;
     uint64_t* p_full = bars + 7;
     uint64_t* o_full = bars + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
-    unsigned long long* xch = reinterpret_cast<unsigned long long*>(bars + 16);  // [2 buffers][2 halves][128 rows] of (tag, float)
+    uint64_t* q_empty = bars + 9;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int qblk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int T = args.T, E = args.E;
-    const int q0 = qblk * BQ;
-    const int row_base = b * T;
-    int n_kv = (T + BKV - 1) / BKV;
-    if (args.mask_mode == 1 && qblk + 1 < n_kv) n_kv = qblk + 1;  // causal: blocks above the diagonal vanish
+    const int n_items = args.n_items;
+    const int n_kv_all = (T + BKV - 1) / BKV;
+    // item -> (query block, head, batch).  Under the causal mask the query blocks are walked from the last
+    // (longest key range) to the first, so that the short items fill the end of the schedule.
+    struct Item {
+        int qblk, h, b, n_kv;
+    };
+    auto decode = [&](int item) {
+        Item it;
+        const int hb = args.H * args.B;
+        const int qr = item / hb, bh = item - qr * hb;
+        it.qblk = args.mask_mode == 1 ? args.n_qblk - 1 - qr : qr;
+        it.b = bh / args.H;
+        it.h = bh - it.b * args.H;
+        it.n_kv = n_kv_all;
+        if (args.mask_mode == 1 && it.qblk + 1 < n_kv_all) it.n_kv = it.qblk + 1;  // blocks above the diagonal vanish
+        return it;
+    };
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(q_full), 1);
@@ -157,9 +176,9 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
         mbar_init(smem_u32(s_empty), kSoftmaxWarps);
         mbar_init(smem_u32(p_full), kSoftmaxWarps);
         mbar_init(smem_u32(o_full), 1);
+        mbar_init(smem_u32(q_empty), 1);
         mbar_fence_init();
     }
-    for (int i = threadIdx.x; i < 2 * 2 * BQ; i += kAttnThreads) xch[i] = 0ull;
     for (int i = threadIdx.x; i < Cfg::kOnesBytes / 4; i += kAttnThreads)
         reinterpret_cast<uint32_t*>(sOnes)[i] = 0x38383838u;  // e4m3 1.0; every byte equal, so no swizzle to honour
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -178,19 +197,31 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
     if (warp == 0) {
         if (lane == 0) {
             prefetch_tensormap(&tma_qkv);
-            mbar_arrive_expect_tx(smem_u32(q_full), Cfg::kQBytes);
-            tma_load_2d(smem_u32(sQ), &tma_qkv, smem_u32(q_full), h * D, row_base + q0);
-            for (int j = 0; j < n_kv; ++j) {
-                const int s = j & 1;
-                if (!mbar_wait_bounded(smem_u32(kv_empty + s), ((j >> 1) & 1) ^ 1)) {
-                    record_timeout(args.status, 0x1100u + s);
+            uint32_t kv_it = 0, item_it = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++item_it) {
+                const Item w = decode(item);
+                const int row_base = w.b * T;
+                // Q is single-buffered: the previous item's last Q.K^T must have read it
+                if (item_it > 0 && !mbar_wait_bounded(smem_u32(q_empty), (item_it - 1) & 1)) {
+                    record_timeout(args.status, 0x1000u);
                     break;
                 }
-                uint8_t* st = sKV + s * Cfg::kStageBytes;
-                const uint32_t fb = smem_u32(kv_full + s);
-                mbar_arrive_expect_tx(fb, Cfg::kStageBytes);
-                tma_load_2d(smem_u32(st), &tma_qkv, fb, E + h * D, row_base + j * BKV);
-                tma_load_2d(smem_u32(st + Cfg::kKBytes), &tma_qkv, fb, 2 * E + h * D, row_base + j * BKV);
+                mbar_arrive_expect_tx(smem_u32(q_full), Cfg::kQBytes);
+                tma_load_2d(smem_u32(sQ), &tma_qkv, smem_u32(q_full), w.h * D, row_base + w.qblk * BQ);
+                for (int j = 0; j < w.n_kv; ++j, ++kv_it) {
+                    const int s = kv_it & 1;
+                    if (!mbar_wait_bounded(smem_u32(kv_empty + s), ((kv_it >> 1) & 1) ^ 1)) {
+                        record_timeout(args.status, 0x1100u + s);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* st = sKV + s * Cfg::kStageBytes;
+                    const uint32_t fb = smem_u32(kv_full + s);
+                    mbar_arrive_expect_tx(fb, Cfg::kStageBytes);
+                    tma_load_2d(smem_u32(st), &tma_qkv, fb, E + w.h * D, row_base + j * BKV);
+                    tma_load_2d(smem_u32(st + Cfg::kKBytes), &tma_qkv, fb, 2 * E + w.h * D, row_base + j * BKV);
+                }
             }
         }
     } else if (warp == 1) {
@@ -208,91 +239,76 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
             constexpr uint32_t kStageStep = Cfg::kStageBytes >> 4, kPBufStep = (2 * BQ * BKV) >> 4, kPPartStep = (BQ * BKV) >> 4;
             const uint32_t idesc_qk = args.idesc_qk, idesc_pv = args.idesc_pv, idesc_sum = args.idesc_sum;
             const uint32_t s_full_b = smem_u32(s_full), o_full_b = smem_u32(o_full);
-            auto issue_qk = [&](uint32_t k_lo) {
+            const uint32_t q_empty_b = smem_u32(q_empty);
+            // S = Q.K^T of the block with running index x (its K/V stage is x & 1); `last`: the item's final
+            // one, after which Q may be overwritten
+            auto issue_qk = [&](uint32_t x, bool last) -> bool {
+                if (!mbar_wait_bounded(smem_u32(kv_full + (x & 1)), (x >> 1) & 1)) return false;
+                // the softmax warps release S as soon as they hold the previous block's scores in registers
+                if (x > 0 && !mbar_wait_bounded(smem_u32(s_empty), (x - 1) & 1)) return false;
+                tc_fence_after_sync();
+                const uint32_t k_lo = k_lo0 + (x & 1) * kStageStep;
                 tc_mma_f8(tmem_s, desc_join(q_lo, qk_hi), desc_join(k_lo, qk_hi), idesc_qk, 0);
 #pragma unroll
                 for (int k = 1; k < D / 32; ++k)
                     tc_mma_f8_acc(tmem_s, desc_join(q_lo + 2 * k, qk_hi), desc_join(k_lo + 2 * k, qk_hi), idesc_qk);
                 tc_commit(s_full_b);
+                if (last) tc_commit(q_empty_b);
+                return true;
             };
-            bool ok = mbar_wait_bounded(smem_u32(q_full), 0) && mbar_wait_bounded(smem_u32(kv_full + 0), 0);
-            if (!ok) record_timeout(args.status, 0x1200u);
-            if (ok) {
-                tc_fence_after_sync();
-                issue_qk(k_lo0);
-            }
-            for (int j = 0; j < n_kv && ok; ++j) {
-                const uint32_t sj = uint32_t(j & 1);
-                if (j + 1 < n_kv) {
-                    // the softmax warps release S as soon as they hold block j's scores in registers, so
-                    // the next block's Q.K^T runs underneath their exponentials
-                    const int s1 = (j + 1) & 1;
-                    if (!mbar_wait_bounded(smem_u32(kv_full + s1), ((j + 1) >> 1) & 1) ||
-                        !mbar_wait_bounded(smem_u32(s_empty), j & 1)) {
-                        record_timeout(args.status, 0x1300u + s1);
+            uint32_t g = 0, item_it = 0;  // g: running key-block counter over this CTA's items
+            bool ok = true;
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++item_it) {
+                const Item w = decode(item);
+                if (!mbar_wait_bounded(smem_u32(q_full), item_it & 1) || !issue_qk(g, w.n_kv == 1)) {
+                    record_timeout(args.status, 0x1200u);
+                    break;
+                }
+                for (int j = 0; j < w.n_kv; ++j) {
+                    const uint32_t x = g + uint32_t(j), sj = x & 1;
+                    // the next block's Q.K^T runs underneath this block's exponentials
+                    if (j + 1 < w.n_kv && !issue_qk(x + 1, j + 2 == w.n_kv)) {
+                        record_timeout(args.status, 0x1300u + (sj ^ 1));
+                        ok = false;
+                        break;
+                    }
+                    if (!mbar_wait_bounded(smem_u32(p_full), x & 1)) {
+                        record_timeout(args.status, 0x1400u);
+                        ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    issue_qk(k_lo0 + uint32_t(s1) * kStageStep);
-                }
-                if (!mbar_wait_bounded(smem_u32(p_full), j & 1)) {
-                    record_timeout(args.status, 0x1400u);
-                    break;
-                }
-                tc_fence_after_sync();
-                // O (+)= P.V and row sums (+)= P.1, accumulated in TMEM over the key blocks; P = leading part +
-                // remainder.  Per 32 keys: P advances 32 bytes inside its 128-byte rows, V advances 32 rows of D bytes.
-                const uint32_t v_lo = v_lo0 + sj * kStageStep, p_lo = p_lo0 + sj * kPBufStep;
-                if (j == 0) {
-                    tc_mma_f8(tmem_o, desc_join(p_lo, p_hi), desc_join(v_lo, v_hi), idesc_pv, 0);
-                    tc_mma_f8(tmem_l, desc_join(p_lo, p_hi), desc_join(o_lo, p_hi), idesc_sum, 0);
-                } else {
-                    tc_mma_f8_acc(tmem_o, desc_join(p_lo, p_hi), desc_join(v_lo, v_hi), idesc_pv);
-                    tc_mma_f8_acc(tmem_l, desc_join(p_lo, p_hi), desc_join(o_lo, p_hi), idesc_sum);
-                }
+                    // O (+)= P.V and row sums (+)= P.1, accumulated in TMEM over the item's key blocks; P = leading
+                    // part + remainder.  Per 32 keys: P advances 32 bytes inside its 128-byte rows, V advances 32
+                    // rows of D bytes.
+                    const uint32_t v_lo = v_lo0 + sj * kStageStep, p_lo = p_lo0 + sj * kPBufStep;
+                    if (j == 0) {
+                        tc_mma_f8(tmem_o, desc_join(p_lo, p_hi), desc_join(v_lo, v_hi), idesc_pv, 0);
+                        tc_mma_f8(tmem_l, desc_join(p_lo, p_hi), desc_join(o_lo, p_hi), idesc_sum, 0);
+                    } else {
+                        tc_mma_f8_acc(tmem_o, desc_join(p_lo, p_hi), desc_join(v_lo, v_hi), idesc_pv);
+                        tc_mma_f8_acc(tmem_l, desc_join(p_lo, p_hi), desc_join(o_lo, p_hi), idesc_sum);
+                    }
 #pragma unroll
-                for (int i = 1; i < 2 * (BKV / 32); ++i) {
-                    const int part = i / (BKV / 32), k = i % (BKV / 32);
-                    const uint32_t pl = p_lo + part * kPPartStep + 2 * k;
-                    tc_mma_f8_acc(tmem_o, desc_join(pl, p_hi), desc_join(v_lo + ((k * 32 * D) >> 4), v_hi), idesc_pv);
-                    tc_mma_f8_acc(tmem_l, desc_join(pl, p_hi), desc_join(o_lo + 2 * k, p_hi), idesc_sum);
+                    for (int i = 1; i < 2 * (BKV / 32); ++i) {
+                        const int part = i / (BKV / 32), k = i % (BKV / 32);
+                        const uint32_t pl = p_lo + part * kPPartStep + 2 * k;
+                        tc_mma_f8_acc(tmem_o, desc_join(pl, p_hi), desc_join(v_lo + ((k * 32 * D) >> 4), v_hi), idesc_pv);
+                        tc_mma_f8_acc(tmem_l, desc_join(pl, p_hi), desc_join(o_lo + 2 * k, p_hi), idesc_sum);
+                    }
+                    tc_commit(o_full_b);  // "P.V of block x done": P is free, O may be touched
+                    tc_commit(smem_u32(kv_empty + sj));
                 }
-                tc_commit(o_full_b);  // "P.V of block j done": P is free, O may be touched
-                tc_commit(smem_u32(kv_empty + sj));
+                g += uint32_t(w.n_kv);
             }
         }
     } else {
         const int q = warp & 3;            // TMEM lane quarter (warps w and w+4 share it)
-        const int half = (warp - 2) >> 2;  // which 64 of the block's 128 key columns this thread takes
-        constexpr int HC = BKV / 2;        // columns per thread and block
+        constexpr int HC = BKV;            // score columns per thread and block: the whole row
         const int row = q * 32 + lane;
-        const int qi = q0 + row;
         const float dq = args.scale[1];
         const float cs = dq * dq * rsqrtf(float(D)) * kLog2e;  // raw score -> log2 domain
         const uint32_t lane_addr = uint32_t(q * 32) << 16;
-        const float* mrow = nullptr;
-        if (args.mask_mode == 2 && qi < T)
-            mrow = args.mask + (size_t(args.mask_b > 1 ? b : 0) * T + qi) * T;
-        // The two threads of a row swap one float per key block through shared memory.  Each slot carries a
-        // sequence tag, so the reader simply polls (bounded) until its partner's value for this step is there;
-        // slots alternate between two buffers, and a slot can only be rewritten after the partner has consumed
-        // the step in between.
-        auto swap_with_partner = [&](int step, float mine, float& theirs) -> bool {
-            volatile unsigned long long* base = xch + size_t(step & 1) * 2 * BQ;
-            base[half * BQ + row] = (static_cast<unsigned long long>(step + 1) << 32) | __float_as_uint(mine);
-            volatile unsigned long long* other = base + (half ^ 1) * BQ + row;
-            const uint64_t t0 = globaltimer_ns();
-            for (;;) {
-                for (int it = 0; it < 1024; ++it) {
-                    const unsigned long long v = *other;
-                    if (uint32_t(v >> 32) == uint32_t(step + 1)) {
-                        theirs = __uint_as_float(uint32_t(v));
-                        return true;
-                    }
-                }
-                if (globaltimer_ns() - t0 > 2000000000ull) return false;
-            }
-        };
 
         // Probabilities are formed as p' = 2^kPShift * exp2(t - m) against a reference maximum m that is only
         // moved (and O, l rescaled) when the true running maximum has grown by more than kLazy: then
@@ -302,24 +318,36 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
         // for every key that matters, i.e. an absolute error of at most 2^-9 in the exponent (0.14 % of p).
         constexpr float kPShift = 5.0f;
         constexpr float kLazy = 2.5f;
+        bool ok = true;
+        int pv_waited = 0;  // number of "P.V done" phases this thread has observed (over all items)
+        int g = 0;          // running key-block counter over this CTA's items
+        float amax = 0.f;   // max|out| over this thread's outputs of all items
+
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+        const Item w = decode(item);
+        const int n_kv = w.n_kv, h = w.h, b = w.b;
+        const int q0 = w.qblk * BQ, row_base = b * T;
+        const int qi = q0 + row;
+        const float* mrow = nullptr;
+        if (args.mask_mode == 2 && qi < T)
+            mrow = args.mask + (size_t(args.mask_b > 1 ? b : 0) * T + qi) * T;
         float m = -INFINITY;       // reference maximum of the exponentials (log2 domain)
         float m_true = -INFINITY;  // true running maximum of the row
-        bool ok = true;
-        int pv_waited = 0;         // number of "P.V done" phases this thread has observed
 
         for (int j = 0; j < n_kv; ++j) {
-            const int k0 = j * BKV + half * HC;
-            if (!mbar_wait_bounded(smem_u32(s_full), j & 1)) {
+            const int gj = g + j;
+            const int k0 = j * BKV;
+            if (!mbar_wait_bounded(smem_u32(s_full), gj & 1)) {
                 if (lane == 0) record_timeout(args.status, 0x1500u);
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-            // this thread's 64 score columns into registers, then S is released at once
+            // this row's 128 scores into registers, then S is released at once
             uint32_t r[HC];
 #pragma unroll
             for (int c = 0; c < HC / 32; ++c)
-                tmem_ld_32x32(tmem_s + lane_addr + half * HC + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+                tmem_ld_32x32(tmem_s + lane_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
             tmem_ld_wait();
             tc_fence_before_sync();
             __syncwarp();
@@ -328,13 +356,15 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
             const bool edge = (j * BKV + BKV > T) || (args.mask_mode == 1 && j * BKV + BKV - 1 > q0) || (args.mask_mode == 2);
             float mb = -INFINITY;
             if (!edge) {
-                float ra = -INFINITY, rb = -INFINITY;
+                float ra = -INFINITY, rb = -INFINITY, rc = -INFINITY, rd = -INFINITY;  // four dependency chains
 #pragma unroll
-                for (int i = 0; i < HC; i += 4) {
+                for (int i = 0; i < HC; i += 8) {
                     ra = fmax3(ra, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
                     rb = fmax3(rb, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                    rc = fmax3(rc, __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+                    rd = fmax3(rd, __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
                 }
-                mb = fmaxf(ra, rb) * cs;  // cs > 0: the maximum commutes with the scaling; r stays unscaled (see below)
+                mb = fmaxf(fmaxf(ra, rb), fmaxf(rc, rd)) * cs;  // cs > 0: the maximum commutes with the scaling; r stays unscaled (see below)
             } else {
 #pragma unroll
                 for (int i = 0; i < HC; ++i) {
@@ -350,17 +380,6 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                     mb = fmaxf(mb, t);
                 }
             }
-            // the row's block maximum = max over both halves
-            {
-                float theirs = -INFINITY;
-                const bool got = swap_with_partner(j, mb, theirs);
-                if (!__all_sync(0xffffffffu, got)) {
-                    if (lane == 0) record_timeout(args.status, 0x1900u);
-                    ok = false;
-                    break;
-                }
-                mb = fmaxf(mb, theirs);
-            }
             m_true = fmaxf(m_true, mb);
 
             // move the reference maximum?  (always on the first block that has an unmasked key)
@@ -373,8 +392,8 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                 }
                 if (j > 0) {
                     // O holds the products of blocks < j: wait until the last of them has landed, then scale
-                    // this thread's half of the row
-                    while (pv_waited < j) {
+                    // this row
+                    while (pv_waited < gj) {
                         if (!mbar_wait_bounded(smem_u32(o_full), pv_waited & 1)) {
                             ok = false;
                             break;
@@ -387,17 +406,17 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                         break;
                     }
                     tc_fence_after_sync();
-#pragma unroll
-                    for (int c = 0; c < D / 64; ++c) {
-                        uint32_t o[32];
-                        const uint32_t oaddr = tmem_o + lane_addr + half * (D / 2) + c * 32;
-                        tmem_ld_32x32(oaddr, o);
+#pragma unroll 1
+                    for (int c = 0; c < D / 16; ++c) {  // small pieces: the row's 128 scores stay in registers meanwhile
+                        uint32_t o[16];
+                        const uint32_t oaddr = tmem_o + lane_addr + c * 16;
+                        tmem_ld_32x16(oaddr, o);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st_32x32(oaddr, o);
+                        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st_32x16(oaddr, o);
                     }
-                    if (half == 0) {  // the row sum: only column 0 of its sixteen copies is ever read back
+                    {  // the row sum: only column 0 of its sixteen copies is ever read back
                         const uint32_t laddr = tmem_l + lane_addr;
                         const float lv = __uint_as_float(tmem_ld_32x1(laddr));
                         tmem_ld_wait();
@@ -410,7 +429,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
             const float ecs = edge ? 1.f : cs;  // masked blocks hold scores already scaled (and masked) in r
 
             // P is double-buffered: this block's buffer was last read by the P.V of block j-2
-            while (pv_waited < j - 1) {
+            while (pv_waited < gj - 1) {
                 if (!mbar_wait_bounded(smem_u32(o_full), pv_waited & 1)) {
                     ok = false;
                     break;
@@ -423,7 +442,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                 break;
             }
 
-            uint8_t* prow = sP + (j & 1) * 2 * BQ * BKV + row * 128;
+            uint8_t* prow = sP + (gj & 1) * 2 * BQ * BKV + row * 128;
             const float nshift = -shift;
 #pragma unroll
             for (int c = 0; c < HC / 32; ++c) {
@@ -442,7 +461,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                     w[g] = ha | (hb << 16);
                     wl[g] = la | (lb << 16);
                 }
-                const int cc = half * (HC / 16) + 2 * c;  // 16-byte chunk index inside the 128-byte row
+                const int cc = 2 * c;  // 16-byte chunk index inside the 128-byte row
                 const int o0 = (cc ^ (row & 7)) << 4, o1 = ((cc + 1) ^ (row & 7)) << 4;
                 *reinterpret_cast<uint4*>(prow + o0) = make_uint4(w[0], w[1], w[2], w[3]);
                 *reinterpret_cast<uint4*>(prow + o1) = make_uint4(w[4], w[5], w[6], w[7]);
@@ -451,7 +470,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
             }
             // catch up with the "P.V done" barrier before the issuer can complete another phase: a waiter must
             // never fall two phases behind a parity-tracked mbarrier (block j-1's product is long finished here)
-            while (pv_waited < j) {
+            while (pv_waited < gj) {
                 if (!mbar_wait_bounded(smem_u32(o_full), pv_waited & 1)) {
                     ok = false;
                     break;
@@ -471,7 +490,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
         }
 
         if (ok) {
-            while (pv_waited < n_kv) {
+            while (pv_waited < g + n_kv) {
                 if (!mbar_wait_bounded(smem_u32(o_full), pv_waited & 1)) {
                     ok = false;
                     break;
@@ -480,7 +499,8 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
             }
             if (!ok && lane == 0) record_timeout(args.status, 0x1800u);
         }
-        if (__all_sync(0xffffffffu, ok)) {
+        if (!__all_sync(0xffffffffu, ok)) break;
+        {
             tc_fence_after_sync();
             // the row sum, accumulated by the tensor core next to O
             float l = 0.f;
@@ -492,29 +512,40 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
             // 1e-6 is carried over with the same factor.
             const float eps = 1e-6f * ex2(kPShift + ((m == -INFINITY) ? 0.f : (m_true - m)));
             const float inv = dq / (l + eps);
-            float amax = 0.f;
-            float* o = args.out + (size_t(row_base) + qi) * E + h * D + half * (D / 2);
+            // Rows leave through shared memory so that global stores are whole 128-byte row segments: the
+            // staging area is this warp's own 32 rows of the first P buffer, idle once the item's last P.V is done
+            // and not touched by the other warps (they only ever write their own rows).
+            uint8_t* stg = sP + q * 32 * 128;
+            float* obase = args.out + (size_t(row_base) + q0 + q * 32) * E + h * D;
 #pragma unroll
-            for (int c = 0; c < D / 64; ++c) {
+            for (int c = 0; c < D / 32; ++c) {
                 uint32_t v[32];
-                tmem_ld_32x32(tmem_o + lane_addr + half * (D / 2) + c * 32, v);
+                tmem_ld_32x32(tmem_o + lane_addr + c * 32, v);
                 tmem_ld_wait();
-                if (qi < T && n_kv > 0) {
 #pragma unroll
-                    for (int d = 0; d < 32; d += 4) {
-                        float4 f = make_float4(__uint_as_float(v[d]) * inv, __uint_as_float(v[d + 1]) * inv,
-                                               __uint_as_float(v[d + 2]) * inv, __uint_as_float(v[d + 3]) * inv);
-                        if (l == 0.f) f = make_float4(0.f, 0.f, 0.f, 0.f);  // every key masked: zeros, as upstream
-                        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
-                        *reinterpret_cast<float4*>(o + c * 32 + d) = f;
-                    }
+                for (int d = 0; d < 32; d += 4) {
+                    float4 f = make_float4(__uint_as_float(v[d]) * inv, __uint_as_float(v[d + 1]) * inv,
+                                           __uint_as_float(v[d + 2]) * inv, __uint_as_float(v[d + 3]) * inv);
+                    if (l == 0.f) f = make_float4(0.f, 0.f, 0.f, 0.f);  // every key masked: zeros, as upstream
+                    if (qi < T) amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
+                    *reinterpret_cast<float4*>(stg + lane * 128 + (((d >> 2) ^ (lane & 7)) << 4)) = f;
                 }
+                __syncwarp();
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const int rr = it * 4 + (lane >> 3), k = lane & 7;
+                    const float4 f = *reinterpret_cast<const float4*>(stg + rr * 128 + ((k ^ (rr & 7)) << 4));
+                    if (q0 + q * 32 + rr < T) *reinterpret_cast<float4*>(obase + size_t(rr) * E + c * 32 + k * 4) = f;
+                }
+                __syncwarp();
             }
-            tc_fence_before_sync();
-            if (args.out_amax) {
-                amax = warp_max(amax);
-                if (lane == 0 && amax > 0.f) atomic_max_nonneg(args.out_amax, amax);
-            }
+            tc_fence_before_sync();  // O and the row sum are in registers before this warp's next p_full arrival
+        }
+        g += n_kv;
+        }  // items
+        if (args.out_amax) {
+            amax = warp_max(amax);
+            if (lane == 0 && amax > 0.f) atomic_max_nonneg(args.out_amax, amax);
         }
     }
 
@@ -589,7 +620,12 @@ extern "C" df8_status df8_attention_fp8(const uint8_t* qkv_codes, df8_kind kind,
     a.idesc_pv = ptx::make_idesc_f8(BQ, D, DF8_E4M3, int(kind), 0, 1);
     a.idesc_sum = ptx::make_idesc_f8(BQ, 16, DF8_E4M3, DF8_E4M3);
     a.status = status_ptr;
-    dim3 grid((T + BQ - 1) / BQ, H, B);
+    a.n_qblk = (T + BQ - 1) / BQ;
+    const long items = long(a.n_qblk) * H * B;
+    DF8_REQUIRE(items < (1l << 31), "df8_attention_fp8: too many query blocks");
+    a.n_items = int(items);
+    const long slots = long(sm_count()) * (D == 64 ? 2 : 1);  // CTAs resident at once
+    dim3 grid(unsigned(items < slots ? items : slots), 1, 1);
     return D == 64 ? launch_attention<64>(tm, a, grid, st) : launch_attention<128>(tm, a, grid, st);
 }
 

@@ -69,6 +69,7 @@ _SIGNATURES = {
     "df8_interleave_gathered_u8": [_vp, _i, _i, _i, _vp, _vp],
     "df8_status_word_read": [_vp, _vp],
     "df8_status_word_reset": [],
+    "df8_set_amax_preclear": [C.c_int],
 }
 _RESTYPES = {"df8_last_error": C.c_char_p, "df8_version": C.c_char_p}
 

@@ -146,6 +146,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    griddep_launch_dependents();
     const int T = args.T, E = args.E;
     const int n_items = args.n_items;
     const int n_kv_all = (T + BKV - 1) / BKV;
@@ -190,6 +191,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    griddep_wait();  // set-up above overlaps the previous kernel's tail; global memory is touched below
     const uint32_t tmem_s = tmem_base;
     const uint32_t tmem_o = tmem_base + 128;
     const uint32_t tmem_l = tmem_base + 128 + D;
@@ -568,8 +570,8 @@ df8_status launch_attention(const CUtensorMap& tm, const AttnArgs& args, dim3 gr
         DF8_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         configured[dev] = true;
     }
-    kern<<<grid, kAttnThreads, Cfg::kSmemBytes, st>>>(tm, args);
-    DF8_LAUNCH_CHECK("attention_fp8_kernel");
+    cudaError_t err = launch_kernel(kern, grid, dim3(kAttnThreads), Cfg::kSmemBytes, st, tm, args);
+    if (err != cudaSuccess) return fail(DF8_ERR_CUDA, "launch of attention_fp8_kernel failed: %s", cudaGetErrorString(err));
     return DF8_OK;
 }
 
@@ -589,7 +591,7 @@ extern "C" df8_status df8_attention_fp8(const uint8_t* qkv_codes, df8_kind kind,
     if (D != 64 && D != 128)
         return fail(DF8_ERR_UNSUPPORTED, "df8_attention_fp8: head dimension %d not supported (64 or 128)", D);
     cudaStream_t st = as_stream(stream);
-    if (out_amax) DF8_CUDA_TRY(cudaMemsetAsync(out_amax, 0, sizeof(float), st));
+    DF8_CLEAR_AMAX(out_amax, st);
     if (B == 0 || T == 0) return DF8_OK;
     DF8_REQUIRE(qkv_codes && scale && out, "df8_attention_fp8: null buffer");
     DF8_REQUIRE(aligned16(out), "df8_attention_fp8: out must be 16-byte aligned");

@@ -6,6 +6,7 @@
 // above turn a non-zero status back into the exception types upstream throws.
 #include "df8_internal.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace df8 {
@@ -20,6 +21,19 @@ df8_status fail(df8_status code, const char* fmt, ...) {
     vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
     va_end(ap);
     return code;
+}
+
+namespace {
+thread_local bool g_amax_preclear = true;
+}
+bool amax_preclear() { return g_amax_preclear; }
+
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("DF8_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
 }
 
 int sm_count() {
@@ -41,5 +55,11 @@ int sm_count() {
 }  // namespace df8
 
 extern "C" const char* df8_last_error(void) { return df8::g_last_error; }
+
+extern "C" int df8_set_amax_preclear(int enabled) {
+    const int before = df8::g_amax_preclear ? 1 : 0;
+    df8::g_amax_preclear = enabled != 0;
+    return before;
+}
 
 extern "C" const char* df8_version(void) { return "df8 0.1 (sm_100a)"; }

@@ -36,6 +36,23 @@ df8_status status_word_device_ptr(unsigned int** out);
                                cudaGetErrorString(err__));                                  \
     } while (0)
 
+// Launch through launch_kernel() (programmatic dependent launch allowed); a kernel name with template commas goes
+// in parentheses.
+#define DF8_LAUNCH(what, kern, grid, block, smem, st, ...)                                  \
+    do {                                                                                    \
+        cudaError_t err__ = ::df8::launch_kernel(kern, grid, block, smem, st, __VA_ARGS__); \
+        if (err__ != cudaSuccess)                                                           \
+            return ::df8::fail(DF8_ERR_CUDA, "launch of %s failed: %s", what,               \
+                               cudaGetErrorString(err__));                                  \
+    } while (0)
+
+// Clears *amax_out on the stream unless the calling thread turned that off (df8_set_amax_preclear).
+#define DF8_CLEAR_AMAX(ptr, st)                                                             \
+    do {                                                                                    \
+        if ((ptr) != nullptr && ::df8::amax_preclear())                                     \
+            DF8_CUDA_TRY(cudaMemsetAsync((ptr), 0, sizeof(float), (st)));                   \
+    } while (0)
+
 #define DF8_REQUIRE(cond, ...)                                                              \
     do {                                                                                    \
         if (!(cond)) return ::df8::fail(DF8_ERR_INVALID, __VA_ARGS__);                      \
@@ -43,11 +60,40 @@ df8_status status_word_device_ptr(unsigned int** out);
 
 inline cudaStream_t as_stream(df8_stream s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// Programmatic dependent launch.  Kernels of this library are short (10-100 us) and run back to back on one
+// stream, so the gap between two of them (grid drain, launch latency, the next kernel's set-up) is a visible part
+// of a forward pass.  Every kernel calls griddep_launch_dependents() on entry and griddep_wait() before its
+// first access to global memory; launched through launch_kernel() it may then be scheduled, and run its
+// set-up, while the previous kernel of the stream is still finishing.  After an operation that is not such a
+// kernel (a memset, a copy, another library's kernel) the attribute has no effect.  DF8_PDL=0 in the
+// environment turns the attribute off.
+bool pdl_enabled();
+bool amax_preclear();
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 __host__ __device__ constexpr float fp8_max(int kind) { return kind == DF8_E4M3 ? 448.0f : 57344.0f; }
 
 // ---- device helpers ---------------------------------------------------------------------
+
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 
 // Two fp32 -> two fp8 codes, round-to-nearest-even, saturating to the largest finite value.
 // The low byte of the result holds `lo`, the high byte `hi`.

@@ -19,6 +19,8 @@ __global__ void __launch_bounds__(kEmbThreads)
 embed_pe_kernel(const int* __restrict__ ids, int rows, int T, int E, int V, const float* __restrict__ table,
                 const float* __restrict__ bias, const float* __restrict__ pe, float* __restrict__ out,
                 int* __restrict__ bad_ids) {
+    griddep_launch_dependents();
+    griddep_wait();
     const int warps_per_block = kEmbThreads / 32;
     const int lane = threadIdx.x & 31;
     for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
@@ -76,9 +78,10 @@ extern "C" df8_status df8_embed_pe_f32(const int32_t* ids, int B, int T, int E, 
     if (blocks > cap) blocks = cap;
     const bool vec4 = (E % 4 == 0) && aligned16(table) && aligned16(out) && aligned16(bias) && aligned16(pe);
     if (vec4)
-        embed_pe_kernel<true><<<int(blocks), kEmbThreads, 0, st>>>(ids, int(rows), T, E, V, table, bias, pe, out, bad_ids);
+        DF8_LAUNCH("embed_pe_kernel", embed_pe_kernel<true>, dim3(unsigned(blocks)), dim3(kEmbThreads), 0, st, ids, int(rows), T,
+                   E, V, table, bias, pe, out, bad_ids);
     else
-        embed_pe_kernel<false><<<int(blocks), kEmbThreads, 0, st>>>(ids, int(rows), T, E, V, table, bias, pe, out, bad_ids);
-    DF8_LAUNCH_CHECK("embed_pe_kernel");
+        DF8_LAUNCH("embed_pe_kernel", embed_pe_kernel<false>, dim3(unsigned(blocks)), dim3(kEmbThreads), 0, st, ids, int(rows), T,
+                   E, V, table, bias, pe, out, bad_ids);
     return DF8_OK;
 }

@@ -260,6 +260,7 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    griddep_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -280,6 +281,7 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    griddep_wait();  // everything above overlaps the previous kernel's tail; global memory is touched below
 
     const int num_m = (args.M + BM - 1) / BM;
     const int num_n = (args.N + BN - 1) / BN;
@@ -507,6 +509,7 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
     const int lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
+    griddep_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -529,6 +532,7 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
     cluster_wait();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    griddep_wait();
 
     const int pair = blockIdx.x >> 1;
     const int npairs = gridDim.x >> 1;
@@ -746,13 +750,15 @@ df8_status launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tw, const 
     cfg.blockDim = dim3(gemm_threads(MODE), 1, 1);
     cfg.dynamicSmemBytes = kPairSmemBytes;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
     cudaError_t err = cudaLaunchKernelEx(&cfg, kern, ta, tw, args);
     if (err != cudaSuccess)
         return fail(DF8_ERR_CUDA, "launch of gemm_fp8_tn_pair_kernel failed: %s", cudaGetErrorString(err));
@@ -771,8 +777,8 @@ df8_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmA
         DF8_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         configured[dev] = true;
     }
-    kern<<<grid, gemm_threads(MODE), Cfg::kSmemBytes, st>>>(ta, tw, args);
-    DF8_LAUNCH_CHECK("gemm_fp8_tn_kernel");
+    cudaError_t err = launch_kernel(kern, dim3(unsigned(grid)), dim3(gemm_threads(MODE)), Cfg::kSmemBytes, st, ta, tw, args);
+    if (err != cudaSuccess) return fail(DF8_ERR_CUDA, "launch of gemm_fp8_tn_kernel failed: %s", cudaGetErrorString(err));
     return DF8_OK;
 }
 
@@ -872,7 +878,7 @@ extern "C" df8_status df8_gemm_fp8_tn(const uint8_t* a_codes, df8_kind kind_a, c
     cudaStream_t st = as_stream(stream);
     if (flags & DF8_EPI_AMAX) {
         DF8_REQUIRE(out_amax != nullptr, "df8_gemm_fp8_tn: DF8_EPI_AMAX needs out_amax");
-        DF8_CUDA_TRY(cudaMemsetAsync(out_amax, 0, sizeof(float), st));
+        DF8_CLEAR_AMAX(out_amax, st);
     }
     if (M == 0 || N == 0) return DF8_OK;
     DF8_REQUIRE(a_codes && w_codes && scale_a && scale_w && out, "df8_gemm_fp8_tn: null buffer");
@@ -907,7 +913,7 @@ extern "C" df8_status df8_gemm_fp8_tn_q(const uint8_t* a_codes, df8_kind kind_a,
     DF8_REQUIRE((flags & ~DF8_EPI_GELU) == 0, "df8_gemm_fp8_tn_q: only DF8_EPI_GELU is accepted, got 0x%x", flags);
     DF8_REQUIRE(out_amax && out_scale, "df8_gemm_fp8_tn_q: out_amax and out_scale are required");
     cudaStream_t st = as_stream(stream);
-    DF8_CUDA_TRY(cudaMemsetAsync(out_amax, 0, sizeof(float), st));
+    DF8_CLEAR_AMAX(out_amax, st);
     if (K % 16 != 0 || N % 32 != 0)
         return fail(DF8_ERR_UNSUPPORTED, "df8_gemm_fp8_tn_q: needs K %% 16 == 0 and N %% 32 == 0 (K=%d N=%d)", K, N);
     DF8_REQUIRE(M == 0 || N == 0 || (a_codes && w_codes && scale_a && scale_w && out_codes),
@@ -950,7 +956,7 @@ extern "C" df8_status df8_gemm_fp8_tn_amax(const uint8_t* a_codes, df8_kind kind
     DF8_REQUIRE((flags & ~DF8_EPI_GELU) == 0, "df8_gemm_fp8_tn_amax: only DF8_EPI_GELU is accepted, got 0x%x", flags);
     DF8_REQUIRE(out_amax != nullptr, "df8_gemm_fp8_tn_amax: out_amax is required");
     cudaStream_t st = as_stream(stream);
-    DF8_CUDA_TRY(cudaMemsetAsync(out_amax, 0, sizeof(float), st));
+    DF8_CLEAR_AMAX(out_amax, st);
     if (M == 0 || N == 0) return DF8_OK;
     if (K % 16 != 0 || N % 32 != 0)
         return fail(DF8_ERR_UNSUPPORTED, "df8_gemm_fp8_tn_amax: needs K %% 16 == 0 and N %% 32 == 0 (K=%d N=%d)", K, N);

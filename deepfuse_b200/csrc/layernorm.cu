@@ -45,6 +45,8 @@ layernorm_kernel(const float* __restrict__ x, int rows, int C, const float* __re
                  const float* __restrict__ beta, float eps, float* __restrict__ y, float* __restrict__ amax_out,
                  float2* __restrict__ row_stats, const float* __restrict__ amax_in, uint8_t* __restrict__ codes,
                  float* __restrict__ scale_out) {
+    griddep_launch_dependents();
+    griddep_wait();
     __shared__ float red[kLnThreads / 32];
     float q = 1.f;
     if constexpr (MODE == 2) {
@@ -157,6 +159,8 @@ layernorm_rows_kernel(const float* __restrict__ x, int rows, int C, const float*
                       const float* __restrict__ beta, float eps, float* __restrict__ y, float* __restrict__ amax_out,
                       float2* __restrict__ row_stats, const float* __restrict__ amax_in, uint8_t* __restrict__ codes,
                       float* __restrict__ scale_out) {
+    griddep_launch_dependents();
+    griddep_wait();
     const int lane = threadIdx.x & 31;
     const int wpb = kLnThreads / 32;
     const int c4 = C >> 2;
@@ -248,8 +252,8 @@ bool launch_rows_kernel(const float* x, int rows, int C, const float* gamma, con
     if (blocks < 1) blocks = 1;
     const int grid = int(blocks);
 #define DF8_LN_ROWS(V4)                                                                                           \
-    layernorm_rows_kernel<MODE, KIND, V4><<<grid, kLnThreads, 0, st>>>(x, rows, C, gamma, beta, eps, y, amax_out,   \
-                                                                      row_stats, amax_in, codes, scale_out)
+    (void)launch_kernel((layernorm_rows_kernel<MODE, KIND, V4>), dim3(unsigned(grid)), dim3(kLnThreads), 0, st, x, rows, C,  \
+                        gamma, beta, eps, y, amax_out, row_stats, amax_in, codes, scale_out)
     if (C <= 256) DF8_LN_ROWS(2);
     else if (C <= 512) DF8_LN_ROWS(4);
     else if (C <= 768) DF8_LN_ROWS(6);
@@ -280,16 +284,16 @@ extern "C" df8_status df8_layernorm_f32(const float* x, int rows, int cols, cons
                                         float eps, float* y, float* amax_out, df8_stream stream) {
     DF8_REQUIRE(rows >= 0 && cols > 0, "df8_layernorm_f32: bad shape rows=%d cols=%d", rows, cols);
     cudaStream_t st = as_stream(stream);
-    if (amax_out) DF8_CUDA_TRY(cudaMemsetAsync(amax_out, 0, sizeof(float), st));
+    DF8_CLEAR_AMAX(amax_out, st);
     if (rows == 0) return DF8_OK;
     DF8_REQUIRE(x && y, "df8_layernorm_f32: null buffer");
     if (fast_ok(cols, x, y, gamma, beta) &&
         launch_rows_kernel<0, 0>(x, rows, cols, gamma, beta, eps, y, amax_out, nullptr, nullptr, nullptr, nullptr, st)) {
     } else if (fast_ok(cols, x, y, gamma, beta))
-        layernorm_kernel<0, 0, true><<<ln_grid(rows), kLnThreads, 0, st>>>(x, rows, cols, gamma, beta, eps, y, amax_out,
+        (void)launch_kernel((layernorm_kernel<0, 0, true>), dim3(unsigned(ln_grid(rows))), dim3(kLnThreads), 0, st, x, rows, cols, gamma, beta, eps, y, amax_out,
                                                                           nullptr, nullptr, nullptr, nullptr);
     else
-        layernorm_kernel<0, 0, false><<<ln_grid(rows), kLnThreads, 0, st>>>(x, rows, cols, gamma, beta, eps, y,
+        (void)launch_kernel((layernorm_kernel<0, 0, false>), dim3(unsigned(ln_grid(rows))), dim3(kLnThreads), 0, st, x, rows, cols, gamma, beta, eps, y,
                                                                            amax_out, nullptr, nullptr, nullptr, nullptr);
     DF8_LAUNCH_CHECK("layernorm_kernel");
     return DF8_OK;
@@ -307,14 +311,14 @@ df8_status launch_ln_quant(const float* x, int rows, int cols, const float* gamm
         launch_rows_kernel<2, KIND>(x, rows, cols, gamma, beta, eps, nullptr, nullptr, row_stats, amax_out, codes,
                                     scale_out, st);
     } else if (fast) {
-        layernorm_kernel<1, KIND, true><<<grid, kLnThreads, 0, st>>>(x, rows, cols, gamma, beta, eps, nullptr, amax_out,
+        (void)launch_kernel((layernorm_kernel<1, KIND, true>), dim3(unsigned(grid)), dim3(kLnThreads), 0, st, x, rows, cols, gamma, beta, eps, nullptr, amax_out,
                                                                     row_stats, nullptr, nullptr, nullptr);
-        layernorm_kernel<2, KIND, true><<<grid, kLnThreads, 0, st>>>(x, rows, cols, gamma, beta, eps, nullptr, nullptr,
+        (void)launch_kernel((layernorm_kernel<2, KIND, true>), dim3(unsigned(grid)), dim3(kLnThreads), 0, st, x, rows, cols, gamma, beta, eps, nullptr, nullptr,
                                                                     row_stats, amax_out, codes, scale_out);
     } else {
-        layernorm_kernel<1, KIND, false><<<grid, kLnThreads, 0, st>>>(x, rows, cols, gamma, beta, eps, nullptr, amax_out,
+        (void)launch_kernel((layernorm_kernel<1, KIND, false>), dim3(unsigned(grid)), dim3(kLnThreads), 0, st, x, rows, cols, gamma, beta, eps, nullptr, amax_out,
                                                                      row_stats, nullptr, nullptr, nullptr);
-        layernorm_kernel<2, KIND, false><<<grid, kLnThreads, 0, st>>>(x, rows, cols, gamma, beta, eps, nullptr, nullptr,
+        (void)launch_kernel((layernorm_kernel<2, KIND, false>), dim3(unsigned(grid)), dim3(kLnThreads), 0, st, x, rows, cols, gamma, beta, eps, nullptr, nullptr,
                                                                      row_stats, amax_out, codes, scale_out);
     }
     DF8_LAUNCH_CHECK("layernorm_kernel (fused quantise)");
@@ -330,7 +334,7 @@ extern "C" df8_status df8_layernorm_quantize_f32(const float* x, int rows, int c
     DF8_REQUIRE(rows >= 0 && cols > 0, "df8_layernorm_quantize_f32: bad shape rows=%d cols=%d", rows, cols);
     DF8_REQUIRE(amax_out && scale_out, "df8_layernorm_quantize_f32: amax_out and scale_out are required");
     cudaStream_t st = as_stream(stream);
-    DF8_CUDA_TRY(cudaMemsetAsync(amax_out, 0, sizeof(float), st));
+    DF8_CLEAR_AMAX(amax_out, st);
     DF8_REQUIRE(rows == 0 || (x && codes_out && row_stats_scratch), "df8_layernorm_quantize_f32: null buffer");
     DF8_REQUIRE((reinterpret_cast<uintptr_t>(row_stats_scratch) & 7u) == 0,
                 "df8_layernorm_quantize_f32: row_stats_scratch must be 8-byte aligned");
@@ -396,7 +400,7 @@ extern "C" df8_status df8_layernorm_quantize_f32_noalloc(const float* x, int row
     cudaStream_t st = as_stream(stream);
     // max|LN(x)| is accumulated with atomicMax and must start from zero; the row statistics need no
     // clearing: pass 1 writes the entry of every row before pass 2 reads it.
-    DF8_CUDA_TRY(cudaMemsetAsync(amax_out, 0, sizeof(float), st));
+    DF8_CLEAR_AMAX(amax_out, st);
     float2* stats2 = reinterpret_cast<float2*>(stats);
     return kind == DF8_E4M3
                ? launch_ln_quant<DF8_E4M3>(x, rows, cols, gamma, beta, eps, codes_out, scale_out, amax_out, stats2, st)

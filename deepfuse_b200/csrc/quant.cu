@@ -22,6 +22,8 @@ constexpr int kCtasPerSm = 8;
 // Grid-stride over float4 chunks, 4 chunks (64 B) in flight per thread per iteration.
 __global__ void __launch_bounds__(kThreads) amax_f32_kernel(const float* __restrict__ x, size_t n,
                                                             float* __restrict__ amax_out) {
+    griddep_launch_dependents();
+    griddep_wait();
     const size_t n4 = n >> 2;
     const float4* x4 = reinterpret_cast<const float4*>(x);
     const size_t stride = size_t(gridDim.x) * kThreads;
@@ -64,6 +66,8 @@ __global__ void __launch_bounds__(kThreads) quantize_f32_kernel(const float* __r
                                                                 const float* __restrict__ amax_in,
                                                                 uint8_t* __restrict__ codes,
                                                                 float* __restrict__ scale_out) {
+    griddep_launch_dependents();
+    griddep_wait();
     const float2 s = scales_from_amax(*amax_in, fp8_max(KIND));
     if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) {
         scale_out[0] = s.x;
@@ -119,6 +123,8 @@ template <int KIND>
 __global__ void __launch_bounds__(kThreads) dequantize_f32_kernel(const uint8_t* __restrict__ codes, size_t n,
                                                                   const float* __restrict__ scale,
                                                                   float* __restrict__ y) {
+    griddep_launch_dependents();
+    griddep_wait();
     const float dq = scale[1];
     const size_t n4 = n >> 2;
     const uint32_t* c4 = reinterpret_cast<const uint32_t*>(codes);
@@ -160,10 +166,9 @@ extern "C" df8_status df8_amax_f32(const float* x, size_t n, float* amax_out, df
     DF8_REQUIRE(n == 0 || x != nullptr, "df8_amax_f32: x is null");
     DF8_REQUIRE(aligned16(x), "df8_amax_f32: x must be 16-byte aligned");
     cudaStream_t st = as_stream(stream);
-    DF8_CUDA_TRY(cudaMemsetAsync(amax_out, 0, sizeof(float), st));
+    DF8_CLEAR_AMAX(amax_out, st);
     if (n == 0) return DF8_OK;
-    amax_f32_kernel<<<grid_for(n / 16 + 1), kThreads, 0, st>>>(x, n, amax_out);
-    DF8_LAUNCH_CHECK("amax_f32_kernel");
+    DF8_LAUNCH("amax_f32_kernel", amax_f32_kernel, dim3(unsigned(grid_for(n / 16 + 1))), dim3(kThreads), 0, st, x, n, amax_out);
     return DF8_OK;
 }
 
@@ -176,10 +181,11 @@ extern "C" df8_status df8_quantize_f32(const float* x, size_t n, df8_kind kind, 
     cudaStream_t st = as_stream(stream);
     const int grid = grid_for(n / 16 + 1);
     if (kind == DF8_E4M3)
-        quantize_f32_kernel<DF8_E4M3><<<grid, kThreads, 0, st>>>(x, n, amax_in, codes_out, scale_out);
+        DF8_LAUNCH("quantize_f32_kernel", quantize_f32_kernel<DF8_E4M3>, dim3(unsigned(grid)), dim3(kThreads), 0, st, x, n, amax_in,
+                   codes_out, scale_out);
     else
-        quantize_f32_kernel<DF8_E5M2><<<grid, kThreads, 0, st>>>(x, n, amax_in, codes_out, scale_out);
-    DF8_LAUNCH_CHECK("quantize_f32_kernel");
+        DF8_LAUNCH("quantize_f32_kernel", quantize_f32_kernel<DF8_E5M2>, dim3(unsigned(grid)), dim3(kThreads), 0, st, x, n, amax_in,
+                   codes_out, scale_out);
     return DF8_OK;
 }
 
@@ -193,9 +199,10 @@ extern "C" df8_status df8_dequantize_f32(const uint8_t* codes, size_t n, df8_kin
     cudaStream_t st = as_stream(stream);
     const int grid = grid_for(n / 16 + 1);
     if (kind == DF8_E4M3)
-        dequantize_f32_kernel<DF8_E4M3><<<grid, kThreads, 0, st>>>(codes, n, scale, y_out);
+        DF8_LAUNCH("dequantize_f32_kernel", dequantize_f32_kernel<DF8_E4M3>, dim3(unsigned(grid)), dim3(kThreads), 0, st, codes, n,
+                   scale, y_out);
     else
-        dequantize_f32_kernel<DF8_E5M2><<<grid, kThreads, 0, st>>>(codes, n, scale, y_out);
-    DF8_LAUNCH_CHECK("dequantize_f32_kernel");
+        DF8_LAUNCH("dequantize_f32_kernel", dequantize_f32_kernel<DF8_E5M2>, dim3(unsigned(grid)), dim3(kThreads), 0, st, codes, n,
+                   scale, y_out);
     return DF8_OK;
 }

@@ -8,11 +8,57 @@ Policy& policy() {
     return p;
 }
 
+namespace {
+constexpr int kPoolFloats = 4096;
+struct PassState {
+    int depth = 0;
+    int next = 0;
+    int prev_preclear = 1;
+    float* pool = nullptr;  // of the device the scope was opened on; never freed (16 KB per device and thread)
+};
+thread_local PassState g_pass;
+thread_local float* g_pools[64] = {};
+
+void clear_pool() {
+    utils::CHECK_CUDA_EX(cudaMemsetAsync(g_pass.pool, 0, kPoolFloats * sizeof(float), Cuda::stream()));
+    g_pass.next = 0;
+}
+}  // namespace
+
+PassScope::PassScope() {
+    if (g_pass.depth++ > 0) return;
+    int dev = 0;
+    utils::CHECK_CUDA_EX(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {  // no pool for such a device: behave as if no scope were open
+        g_pass.pool = nullptr;
+        return;
+    }
+    if (!g_pools[dev]) utils::CHECK_CUDA_EX(cudaMalloc(&g_pools[dev], kPoolFloats * sizeof(float)));
+    g_pass.pool = g_pools[dev];
+    clear_pool();
+    g_pass.prev_preclear = df8_set_amax_preclear(0);
+}
+
+PassScope::~PassScope() {
+    if (--g_pass.depth > 0) return;
+    if (g_pass.pool) df8_set_amax_preclear(g_pass.prev_preclear);
+    g_pass.pool = nullptr;
+}
+
+float* amax_slot(float* own) {
+    if (g_pass.depth == 0 || !g_pass.pool) return own;
+    // every slot handed out so far has been consumed by kernels already on the stream, so a full pool is
+    // simply cleared again
+    if (g_pass.next == kPoolFloats) clear_pool();
+    return g_pass.pool + g_pass.next++;
+}
+
 void quantize(const float* x, size_t n, df8_kind kind, Quantized& q) {
     if (q.codes.numel() != n) q.codes = tensor<uint8_t>({int(n)});
     q.kind = kind;
-    utils::CHECK_DF8(df8_amax_f32(x, n, q.amax.data(), stream()));
-    utils::CHECK_DF8(df8_quantize_f32(x, n, kind, q.amax.data(), q.codes.data(), q.scale.data(), stream()));
+    float* am = amax_slot(q.amax.data());
+    utils::CHECK_DF8(df8_amax_f32(x, n, am, stream()));
+    utils::CHECK_DF8(df8_quantize_f32(x, n, kind, am, q.codes.data(), q.scale.data(), stream()));
 }
 
 void quantize_with_amax(const float* x, size_t n, df8_kind kind, const float* amax, Quantized& q) {

@@ -38,6 +38,23 @@ struct Quantized {
 
 inline df8_stream stream() { return reinterpret_cast<df8_stream>(Cuda::stream()); }
 
+// Amax slots of one forward pass.  Every producer of a per-tensor maximum needs its output float cleared
+// first; done call by call that is a memset node in front of five kernels per transformer block.  While a
+// PassScope is alive on the thread, amax_slot() hands out consecutive floats of one device array that the
+// scope cleared with a single memset, and the kernels library's own per-call clearing is switched off
+// (df8_set_amax_preclear).  Scopes nest; only the outermost one does anything.
+class PassScope {
+public:
+    PassScope();
+    ~PassScope();
+    PassScope(const PassScope&) = delete;
+    PassScope& operator=(const PassScope&) = delete;
+};
+
+// The float a producer should write max|out| to: a fresh pre-cleared slot inside a PassScope, otherwise
+// `own` (the caller's private buffer, cleared by the library call itself).
+float* amax_slot(float* own);
+
 // q <- per-tensor quantisation of n fp32 values at x (amax pass + quantise pass).
 void quantize(const float* x, size_t n, df8_kind kind, Quantized& q);
 

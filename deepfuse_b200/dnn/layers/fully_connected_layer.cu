@@ -103,12 +103,14 @@ void FullyConnectedLayer<TT>::forward_codes_quantized(const uint8_t* a_codes, df
     if (out_features_ % 32 == 0) {
         utils::CHECK_DF8(df8_gemm_fp8_tn_q(a_codes, a_kind, a_scale, w_codes, w.kind, w.scale.data(),
                                            this->bias_.data(), M, out_features_, padded_in(), flags, out_kind,
-                                           q.codes.data(), q.scale.data(), q.amax.data(), fp8::stream()));
+                                           q.codes.data(), q.scale.data(), fp8::amax_slot(q.amax.data()),
+                                           fp8::stream()));
         return;
     }
     tensor<float> f32({M, out_features_});
-    forward_codes(a_codes, a_kind, a_scale, M, flags | DF8_EPI_AMAX, nullptr, f32.data(), q.amax.data());
-    fp8::quantize_with_amax(f32.data(), n, out_kind, q.amax.data(), q);
+    float* am = fp8::amax_slot(q.amax.data());
+    forward_codes(a_codes, a_kind, a_scale, M, flags | DF8_EPI_AMAX, nullptr, f32.data(), am);
+    fp8::quantize_with_amax(f32.data(), n, out_kind, am, q);
 }
 
 template <typename TT>

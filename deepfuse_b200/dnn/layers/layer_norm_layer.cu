@@ -43,7 +43,8 @@ void LayerNormLayer<T>::forward_quantized(const float* x, int rows, df8_kind kin
     q.kind = kind;
     utils::CHECK_DF8(df8_layernorm_quantize_f32(x, rows, norm_size_, affine_ ? gamma_.data() : nullptr,
                                                 affine_ ? beta_.data() : nullptr, epsilon_, kind, q.codes.data(),
-                                                q.scale.data(), q.amax.data(), row_stats_.data(), fp8::stream()));
+                                                q.scale.data(), fp8::amax_slot(q.amax.data()), row_stats_.data(),
+                                                fp8::stream()));
 }
 
 // Upstream's backward returns the incoming gradient unchanged (layer_norm_layer.cu:83-91); kept.

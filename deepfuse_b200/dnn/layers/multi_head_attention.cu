@@ -60,9 +60,10 @@ void MultiHeadAttentionLayer<TT>::forward_quantized(const fp8::Quantized& xq, in
         mask_ptr = m->data();
         mask_b = ms[0];
     }
+    float* am = fp8::amax_slot(amax_.data());
     utils::CHECK_DF8(df8_attention_fp8(qkvq_.codes.data(), qkvq_.kind, qkvq_.scale.data(), B, T, num_heads_, head_dim_,
-                                       mode, mask_ptr, mask_b, attn_f32_.data(), amax_.data(), fp8::stream()));
-    fp8::quantize_with_amax(attn_f32_.data(), attn_f32_.numel(), act, amax_.data(), attnq_);
+                                       mode, mask_ptr, mask_b, attn_f32_.data(), am, fp8::stream()));
+    fp8::quantize_with_amax(attn_f32_.data(), attn_f32_.numel(), act, am, attnq_);
     out_proj_.forward_codes(attnq_.codes.data(), attnq_.kind, attnq_.scale.data(), M,
                             residual ? DF8_EPI_RESIDUAL : 0, residual, out, nullptr);
 }

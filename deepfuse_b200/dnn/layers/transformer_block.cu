@@ -34,6 +34,7 @@ void TransformerBlock<T>::forward_inplace(float* x, int B, int T_len) {
     if (E % 16 != 0 || F % 16 != 0)
         throw std::runtime_error("TransformerBlock: embed_dim and mlp_hidden_dim must be multiples of 16 on the fp8 path");
     if (x1_.numel() != size_t(M) * E) x1_ = tensor<float>({M, E});
+    fp8::PassScope amax_slots;
 
     // x1 = x + MHA(LN1(x))
     norm1_.forward_quantized(x, M, act, ln_q_);

@@ -70,6 +70,7 @@ tensor<T> Gpt2<T>::forward_hidden(const tensor<int>& ids, bool check_ids) {
     const int B = s[0], T_len = s[1];
     if (T_len > positional_encoding_->max_seq_len())
         throw std::runtime_error("Input sequence length exceeds maximum allowed length");
+    fp8::PassScope amax_slots;  // one memset for all the pass's amax outputs
     tensor<T> x = token_embedding_->forward_with_positions(ids, positional_encoding_->table().data(), check_ids);
     if (!streamer_) {
         for (auto& block : transformer_blocks_) block->forward_inplace(x.data(), B, T_len);
@@ -96,6 +97,7 @@ tensor<T> Gpt2<T>::forward_hidden(const tensor<int>& ids, bool check_ids) {
 
 template <typename T>
 tensor<T> Gpt2<T>::forward_logits(const tensor<int>& ids, bool check_ids) {
+    fp8::PassScope amax_slots;
     tensor<T> x = forward_hidden(ids, check_ids);
     const int M = int(x.numel() / size_t(hidden_dim_));
     fp8::quantize(x.data(), x.numel(), fp8::policy().activation_kind, head_q_);

@@ -56,6 +56,13 @@ const char* df8_last_error(void);
 /* Library version string. */
 const char* df8_version(void);
 
+/* Every entry point that returns max|out| through an `amax_out` / `out_amax` pointer first clears that float on
+ * the stream (one memset node per call).  A caller that keeps its amax slots in one array and clears the whole
+ * array once per forward pass turns the per-call clearing off for the calling thread with enabled = 0; it then
+ * guarantees that a slot is zero when the kernels of the call that fills it run.  Returns the previous setting.
+ * No upstream counterpart: the reference has no quantiser (see below). */
+int df8_set_amax_preclear(int enabled);
+
 /* ---- per-tensor amax / quantise / dequantise ---------------------------------------------
  * No upstream kernel exists for these (the fp8 tensor instantiations at dnn/core/tensor.cu:489-498
  * are never compiled); they implement the per-tensor quantiser:

@@ -94,6 +94,30 @@ def test_amax_ignores_nan_and_zero_tensor(df8, cuda):
     assert amax.item() == 0.0 and scale.tolist() == [1.0, 1.0] and not codes.any().item()
 
 
+def test_amax_preclear_switch(df8, cuda):
+    """With the per-call clearing off the caller owns the zeroing: a slot keeps accumulating the maximum
+    until the caller clears it; the switch is per thread and returns the previous setting."""
+    import torch
+
+    a = torch.tensor([1.0, -2.0, 0.5, 0.25], device=cuda)
+    b = torch.tensor([0.5, 0.25, -1.5, 1.0], device=cuda)
+    slot = torch.zeros(1, device=cuda)
+    lib = df8.lib()
+    assert lib.df8_set_amax_preclear(0) == 1
+    try:
+        df8.amax_f32(a, slot)
+        df8.amax_f32(b, slot)
+        assert slot.item() == 2.0  # not cleared in between
+        slot.zero_()
+        df8.amax_f32(b, slot)
+        assert slot.item() == 1.5
+    finally:
+        assert lib.df8_set_amax_preclear(1) == 0
+    df8.amax_f32(b, slot)
+    df8.amax_f32(torch.zeros(4, device=cuda), slot)
+    assert slot.item() == 0.0  # cleared by the call again
+
+
 @pytest.mark.parametrize("kind", [0, 1])
 def test_large_tensor_properties(df8, oracle, cuda, kind):
     """2^28 elements: amax equals torch's, the round trip is idempotent, and a strided sample of the

@@ -122,25 +122,36 @@ __device__ __forceinline__ void stage_chunk(const uint32_t (&r)[32], float* stg,
     }
 }
 
-// lanes run along N: apply the epilogue and store coalesced
+// The residual values a lane will add in store_chunk_f32<true> for the chunk at (row0, col0).  They do not depend
+// on the accumulators, so the epilogue issues these loads one chunk ahead (for a tile's first chunk: before it
+// waits for the MMAs) and their global-memory latency stays off the per-chunk chain.
+__device__ __forceinline__ void load_residual_vec4(float4 (&rs)[8], int lane, int row0, int col0, const GemmArgs& a) {
+    const int gcol = col0 + (lane & 7) * 4;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const int rl = it * 4 + (lane >> 3);
+        if ((a.flags & 2) && row0 + rl < a.M && gcol < a.N)
+            rs[it] = *reinterpret_cast<const float4*>(a.residual + size_t(row0 + rl) * a.N + gcol);
+        else
+            rs[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+}
+
+// lanes run along N: apply the epilogue and store coalesced.  `rs`: load_residual_vec4 of this chunk (VEC4 only).
 template <bool VEC4>
 __device__ __forceinline__ void store_chunk_f32(const float* stg, int lane, int row0, int col0, const GemmArgs& a,
-                                                float alpha, float& amax) {
+                                                float alpha, float& amax, const float4 (&rs)[8]) {
     if constexpr (VEC4) {
         const int cq = (lane & 7) * 4;
         const int gcol = col0 + cq;
         const bool col_ok = gcol < a.N;
         float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
         if (a.bias && col_ok) b4 = *reinterpret_cast<const float4*>(a.bias + gcol);
-        float4 v[8], rs[8];
+        float4 v[8];
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
             const int rl = it * 4 + (lane >> 3);
             v[it] = *reinterpret_cast<const float4*>(stg + rl * 36 + cq);
-            if ((a.flags & 2) && row0 + rl < a.M && col_ok)
-                rs[it] = *reinterpret_cast<const float4*>(a.residual + size_t(row0 + rl) * a.N + gcol);
-            else
-                rs[it] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
@@ -430,6 +441,8 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
                 __syncwarp();  // every lane is done with the bias slice before the next tile overwrites it
                 continue;
             }
+            float4 rs[8];  // residual of the chunk about to be stored, loaded one chunk ahead
+            if constexpr (MODE == kOutF32Vec) load_residual_vec4(rs, lane, row0, n0 + 32 * half, args);
             if (!mbar_wait_bounded(smem_u32(tfull + buf), acc_phase)) {
                 if (lane == 0) record_timeout(args.status, 0x400u + buf);
                 break;
@@ -454,7 +467,12 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
                         tc_fence_before_sync();  // last chunk is out of TMEM: hand the buffer back early
                         if (lane == 0) mbar_arrive(smem_u32(tempty + buf));
                     }
-                    store_chunk_f32<VEC4>(stg, lane, row0, n0 + 32 * (half + 2 * j), args, alpha, amax);
+                    float4 rs_cur[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) rs_cur[i] = rs[i];
+                    if constexpr (VEC4)
+                        if (j + 1 < nvalid) load_residual_vec4(rs, lane, row0, n0 + 32 * (half + 2 * (j + 1)), args);
+                    store_chunk_f32<VEC4>(stg, lane, row0, n0 + 32 * (half + 2 * j), args, alpha, amax, rs_cur);
                     __syncwarp();
                 }
                 if (nvalid == 0) {
@@ -679,6 +697,8 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
                 __syncwarp();
                 continue;
             }
+            float4 rs[8];
+            if constexpr (MODE == kOutF32Vec) load_residual_vec4(rs, lane, row0, n0 + 32 * half, args);
             if (!mbar_wait_bounded(smem_u32(tfull + buf), acc_phase)) {
                 if (lane == 0) record_timeout(args.status, 0x2400u + (rank << 4) + buf);
                 break;
@@ -703,7 +723,12 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
                         tc_fence_before_sync();
                         release(buf);
                     }
-                    store_chunk_f32<VEC4>(stg, lane, row0, n0 + 32 * (half + 2 * j), args, alpha, amax);
+                    float4 rs_cur[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) rs_cur[i] = rs[i];
+                    if constexpr (VEC4)
+                        if (j + 1 < nvalid) load_residual_vec4(rs, lane, row0, n0 + 32 * (half + 2 * (j + 1)), args);
+                    store_chunk_f32<VEC4>(stg, lane, row0, n0 + 32 * (half + 2 * j), args, alpha, amax, rs_cur);
                     __syncwarp();
                 }
                 if (nvalid == 0) {

@@ -94,14 +94,16 @@ __device__ __forceinline__ void record_timeout(unsigned int* status, unsigned in
     }
 }
 
-// x * 0.5 * (1 + tanh(0.7978845608 * (x + 0.044715 x^3))), every operation rounded separately (explicit
-// intrinsics, no FMA contraction) so that all epilogue variants produce identical bits.
+// x * 0.5 * (1 + tanh(0.7978845608 * (x + 0.044715 x^3))), evaluated as
+//     u = x * fma(x*x, 0.7978845608*0.044715, 0.7978845608);   hx = 0.5 x;   gelu = fma(hx, tanh(u), hx)
+// with explicit intrinsics (no compiler-chosen contraction), so that every epilogue variant produces identical
+// bits; five arithmetic instructions and one tanh.approx per element (the fc1 epilogue is issue-bound).
 __device__ __forceinline__ float gelu_tanh(float x) {
-    const float x3c = __fmul_rn(__fmul_rn(0.044715f, __fmul_rn(x, x)), x);
-    const float inner = __fmul_rn(0.7978845608f, __fadd_rn(x, x3c));
+    const float u = __fmul_rn(x, __fmaf_rn(__fmul_rn(x, x), 0.7978845608f * 0.044715f, 0.7978845608f));
     float t;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(inner));
-    return __fmul_rn(__fmul_rn(x, 0.5f), __fadd_rn(1.0f, t));
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+    const float hx = __fmul_rn(x, 0.5f);
+    return __fmaf_rn(hx, t, hx);
 }
 
 // ---- fp32 output: transpose one 32-row x 32-column chunk through the warp's staging buffer -------

@@ -223,6 +223,16 @@ _DNN_SIGNATURES = {
     "dnn_selftest_tensor": [_vp, _i],
     "dnn_selftest_context": [_vp, _i],
     "dnn_selftest_errors": [_vp, _i],
+    "dnn_gpt2cs_destroy": [_vp],
+    "dnn_gpt2cs_set_options": [_vp, _i, _i],
+    "dnn_gpt2cs_vocab_range": [_vp, _vp, _vp],
+    "dnn_gpt2cs_num_params": [_vp],
+    "dnn_gpt2cs_param_info": [_vp, _i, _vp, _i, _vp, _vp],
+    "dnn_gpt2cs_param_upload": [_vp, _i, _vp],
+    "dnn_gpt2cs_initialize_on_device": [_vp, C.c_ulonglong],
+    "dnn_gpt2cs_prepare": [_vp],
+    "dnn_gpt2cs_forward_logits_shard": [_vp, _vp, _i, _i, _i, _vp],
+    "dnn_gpt2cs_forward_logits_shard_host": [_vp, _vp, _i, _i, _vp],
 }
 
 
@@ -243,10 +253,12 @@ def dnn_lib() -> C.CDLL:
         handle.dnn_gpt2_streamed_bytes.argtypes = [_vp]
         handle.dnn_gpt2_load.restype = C.c_void_p
         handle.dnn_gpt2_load.argtypes = [C.c_char_p]
+        handle.dnn_gpt2cs_create.restype = C.c_void_p
+        handle.dnn_gpt2cs_create.argtypes = [_vp] + [_i] * 6
         for name, args in _DNN_SIGNATURES.items():
             fn = getattr(handle, name)
             fn.argtypes = args
-            fn.restype = None if name == "dnn_gpt2_destroy" else C.c_int
+            fn.restype = None if name in ("dnn_gpt2_destroy", "dnn_gpt2cs_destroy") else C.c_int
         _dnn = handle
     return _dnn
 
@@ -339,6 +351,141 @@ class Gpt2:
         B, T = ids_dev.shape
         dnn_check(dnn_lib().dnn_gpt2_forward_hidden(self.h, ptr(ids_dev), B, T, C.byref(out)),
                   "dnn_gpt2_forward_hidden")
+        return out.value
+
+
+class Comm:
+    """One df8_comm (NCCL communicator, one process per GPU).  The 128-byte id made on rank 0 reaches the other ranks
+    through torch.distributed when a process group exists, otherwise through the file `id_path`."""
+
+    def __init__(self, rank: int, world: int, id_path: str | None = None):
+        import os
+        import time
+
+        l = lib()
+        buf = C.create_string_buffer(128)
+        self.h = C.c_void_p(0)
+        self.rank, self.world = rank, world
+        if world == 1:
+            return  # a single rank needs no communicator: the sharded model takes NULL
+        use_dist = False
+        try:
+            import torch.distributed as dist
+
+            use_dist = dist.is_available() and dist.is_initialized() and id_path is None
+        except Exception:
+            pass
+        if use_dist:
+            import torch
+
+            if rank == 0:
+                check(l.df8_comm_unique_id(buf), "df8_comm_unique_id")
+            dev = "cuda" if dist.get_backend() == "nccl" else "cpu"
+            t = torch.tensor(list(buf.raw), dtype=torch.uint8, device=dev)
+            dist.broadcast(t, src=0)
+            buf.raw = bytes(t.cpu().tolist())
+        else:
+            if id_path is None:
+                raise Df8Error("Comm needs an initialised torch.distributed group or an id_path")
+            if rank == 0:
+                check(l.df8_comm_unique_id(buf), "df8_comm_unique_id")
+                with open(id_path + ".tmp", "wb") as f:
+                    f.write(buf.raw)
+                os.replace(id_path + ".tmp", id_path)
+            else:
+                for _ in range(1200):
+                    if os.path.exists(id_path):
+                        break
+                    time.sleep(0.05)
+                buf.raw = open(id_path, "rb").read()
+        check(l.df8_comm_init_rank(buf, world, rank, C.byref(self.h)), "df8_comm_init_rank")
+
+    def close(self):
+        if self.h:
+            check(lib().df8_comm_destroy(self.h), "df8_comm_destroy")
+            self.h = C.c_void_p(0)
+
+
+class Gpt2ColumnSharded:
+    """dnn::Gpt2ColumnSharded<float> through the C harness: this rank's shard of a GPT-2 whose fully-connected
+    weights are split by output columns over the ranks of `comm`."""
+
+    def __init__(self, comm: Comm, vocab, max_seq_len, layers, heads, hidden, ffn, device: int = 0):
+        d = dnn_lib()
+        dnn_check(d.dnn_init(device), "dnn_init")
+        self.comm = comm
+        self.cfg = dict(vocab=vocab, max_seq_len=max_seq_len, layers=layers, heads=heads, hidden=hidden, ffn=ffn)
+        self.h = d.dnn_gpt2cs_create(comm.h, vocab, max_seq_len, layers, heads, hidden, ffn)
+        if not self.h:
+            raise Df8Error("dnn_gpt2cs_create failed: " + d.dnn_last_error().decode())
+        b, n = C.c_int(0), C.c_int(0)
+        dnn_check(d.dnn_gpt2cs_vocab_range(self.h, C.byref(b), C.byref(n)), "dnn_gpt2cs_vocab_range")
+        self.vocab_begin, self.vocab_rows = b.value, n.value
+
+    def close(self):
+        if self.h:
+            dnn_lib().dnn_gpt2cs_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def param_names(self):
+        d = dnn_lib()
+        out = []
+        buf = C.create_string_buffer(128)
+        shape = (C.c_int * 8)()
+        ndim = C.c_int(0)
+        for i in range(d.dnn_gpt2cs_num_params(self.h)):
+            dnn_check(d.dnn_gpt2cs_param_info(self.h, i, buf, 128, shape, C.byref(ndim)), "dnn_gpt2cs_param_info")
+            out.append((buf.value.decode(), tuple(shape[k] for k in range(ndim.value))))
+        return out
+
+    def load_full_params(self, params: dict):
+        """Slices this rank's shards out of a full parameter dictionary and uploads them (collective)."""
+        import numpy as np
+
+        from .sharding import shard_gpt2_params
+
+        d = dnn_lib()
+        mine = shard_gpt2_params(params, self.cfg, self.comm.world, self.comm.rank)
+        for i, (name, shape) in enumerate(self.param_names()):
+            a = np.ascontiguousarray(mine[name], dtype=np.float32)
+            n = 1
+            for s in shape:
+                n *= s
+            if a.size != n:
+                raise ValueError(f"{name}: expected {shape}, got {a.shape}")
+            dnn_check(d.dnn_gpt2cs_param_upload(self.h, i, a.ctypes.data_as(C.c_void_p)), "dnn_gpt2cs_param_upload")
+        dnn_check(d.dnn_gpt2cs_prepare(self.h), "dnn_gpt2cs_prepare")
+
+    def initialize_on_device(self, seed: int):
+        dnn_check(dnn_lib().dnn_gpt2cs_initialize_on_device(self.h, seed), "dnn_gpt2cs_initialize_on_device")
+        dnn_check(dnn_lib().dnn_gpt2cs_prepare(self.h), "dnn_gpt2cs_prepare")
+
+    def set_options(self, gelu=True, causal=False):
+        dnn_check(dnn_lib().dnn_gpt2cs_set_options(self.h, int(gelu), int(causal)), "dnn_gpt2cs_set_options")
+
+    def set_stream(self, stream=None):
+        dnn_check(dnn_lib().dnn_set_stream(stream_ptr(stream)), "dnn_set_stream")
+
+    def forward_logits_shard(self, ids_dev, check_ids=True) -> int:
+        """ids_dev: torch int32 CUDA tensor [B,T] (the same on every rank); returns the device pointer of this rank's
+        fp32 logits [B*T, vocab_rows]."""
+        out = C.c_void_p(0)
+        B, T = ids_dev.shape
+        dnn_check(dnn_lib().dnn_gpt2cs_forward_logits_shard(self.h, ptr(ids_dev), B, T, int(check_ids), C.byref(out)),
+                  "dnn_gpt2cs_forward_logits_shard")
+        return out.value
+
+    def forward_logits_shard_host(self, ids_host) -> int:
+        out = C.c_void_p(0)
+        B, T = ids_host.shape
+        dnn_check(dnn_lib().dnn_gpt2cs_forward_logits_shard_host(self.h, ids_host.data_ptr(), B, T, C.byref(out)),
+                  "dnn_gpt2cs_forward_logits_shard_host")
         return out.value
 
 

@@ -16,6 +16,7 @@
 #include "dnn/layers/softmax_layer.cuh"
 #include "dnn/layers/transformer_block.cuh"
 #include "dnn/models/gpt2.cuh"
+#include "dnn/models/gpt2_column_sharded.cuh"
 #include "dnn/tokens/positional_encoding.cuh"
 #include "dnn/tokens/token_embedding.cuh"
 
@@ -349,3 +350,136 @@ extern "C" int dnn_gpt2_disable_streaming(dnn_gpt2* m) {
 }
 
 extern "C" unsigned long long dnn_gpt2_streamed_bytes(dnn_gpt2* m) { return m ? m->model->streamed_bytes() : 0ull; }
+
+
+// ---- Gpt2ColumnSharded ---------------------------------------------------------------------------
+
+struct dnn_gpt2cs {
+    std::unique_ptr<dnn::Gpt2ColumnSharded<float>> model;
+    std::vector<NamedParam> params;
+    std::unique_ptr<dnn::tensor<float>> last;
+    std::unique_ptr<dnn::tensor<int>> ids;
+
+    void index_params() {
+        params.clear();
+        auto add = [this](const std::string& prefix, dnn::tensor<float>* w, dnn::tensor<float>* b,
+                          const char* wn = "weight", const char* bn = "bias") {
+            params.push_back({prefix + "." + wn, w});
+            params.push_back({prefix + "." + bn, b});
+        };
+        add("embedding", model->token_embedding().weights(), model->token_embedding().bias());
+        for (int i = 0; i < model->num_layers(); ++i) {
+            auto& blk = model->block(i);
+            const std::string p = "block" + std::to_string(i);
+            auto n1 = blk.norm1.parameters();
+            auto n2 = blk.norm2.parameters();
+            add(p + ".ln1", n1[0], n1[1], "gamma", "beta");
+            add(p + ".ln2", n2[0], n2[1], "gamma", "beta");
+            add(p + ".qkv", blk.qkv.weights(), blk.qkv.bias());
+            add(p + ".out", blk.out.weights(), blk.out.bias());
+            add(p + ".fc1", blk.fc1.weights(), blk.fc1.bias());
+            add(p + ".fc2", blk.fc2.weights(), blk.fc2.bias());
+        }
+        add("final_fc", model->final_fc().weights(), model->final_fc().bias());
+    }
+    void stage_ids(const int32_t* src, int B, int T, cudaMemcpyKind kind) {
+        if (!ids || ids->shape() != std::vector<int>{B, T}) ids = std::make_unique<dnn::tensor<int>>(std::vector<int>{B, T});
+        dnn::utils::CHECK_CUDA_EX(cudaMemcpyAsync(ids->data(), src, sizeof(int32_t) * size_t(B) * size_t(T), kind,
+                                                  dnn::Cuda::stream()));
+    }
+};
+
+extern "C" dnn_gpt2cs* dnn_gpt2cs_create(void* comm, int vocab, int max_seq_len, int layers, int heads, int hidden,
+                                         int ffn) {
+    dnn_gpt2cs* h = nullptr;
+    int rc = guarded([&] {
+        auto handle = std::make_unique<dnn_gpt2cs>();
+        handle->model = std::make_unique<dnn::Gpt2ColumnSharded<float>>(static_cast<df8_comm*>(comm), vocab, max_seq_len,
+                                                                        layers, heads, hidden, ffn);
+        handle->index_params();
+        h = handle.release();
+    });
+    return rc == 0 ? h : nullptr;
+}
+
+extern "C" void dnn_gpt2cs_destroy(dnn_gpt2cs* m) {
+    guarded([&] {
+        if (m) sync_stream();
+        delete m;
+    });
+}
+
+extern "C" int dnn_gpt2cs_set_options(dnn_gpt2cs* m, int mlp_gelu, int causal) {
+    return guarded([&] {
+        m->model->set_mlp_gelu(mlp_gelu != 0);
+        m->model->set_causal(causal != 0);
+    });
+}
+
+extern "C" int dnn_gpt2cs_vocab_range(dnn_gpt2cs* m, int* begin_h, int* rows_h) {
+    return guarded([&] {
+        if (begin_h) *begin_h = m->model->vocab_begin();
+        if (rows_h) *rows_h = m->model->vocab_rows();
+    });
+}
+
+extern "C" int dnn_gpt2cs_num_params(dnn_gpt2cs* m) { return m ? int(m->params.size()) : -1; }
+
+extern "C" int dnn_gpt2cs_param_info(dnn_gpt2cs* m, int index, char* name_h, int name_cap, int* shape_h, int* ndim_h) {
+    return guarded([&] {
+        const NamedParam& p = m->params.at(size_t(index));
+        if (name_h && name_cap > 0) std::snprintf(name_h, size_t(name_cap), "%s", p.name.c_str());
+        const auto& s = p.t->shape();
+        if (ndim_h) *ndim_h = int(s.size());
+        if (shape_h)
+            for (size_t i = 0; i < s.size() && i < 8; ++i) shape_h[i] = s[i];
+    });
+}
+
+extern "C" int dnn_gpt2cs_param_upload(dnn_gpt2cs* m, int index, const float* data_h) {
+    return guarded([&] {
+        m->params.at(size_t(index)).t->upload(data_h);
+        sync_stream();
+    });
+}
+
+extern "C" int dnn_gpt2cs_initialize_on_device(dnn_gpt2cs* m, unsigned long long seed) {
+    return guarded([&] {
+        m->model->initialize_on_device(seed);
+        sync_stream();
+    });
+}
+
+extern "C" int dnn_gpt2cs_prepare(dnn_gpt2cs* m) {
+    return guarded([&] {
+        for (int i = 0; i < m->model->num_layers(); ++i) {
+            auto& blk = m->model->block(i);
+            blk.qkv.quantized_weights();
+            blk.out.quantized_weights();
+            blk.fc1.quantized_weights();
+            blk.fc2.quantized_weights();
+        }
+        m->model->final_fc().quantized_weights();
+        sync_stream();
+    });
+}
+
+extern "C" int dnn_gpt2cs_forward_logits_shard(dnn_gpt2cs* m, const int32_t* ids_d, int B, int T, int check_ids,
+                                               float** logits_d) {
+    return guarded([&] {
+        m->stage_ids(ids_d, B, T, cudaMemcpyDeviceToDevice);
+        m->last.reset();
+        m->last = std::make_unique<dnn::tensor<float>>(m->model->forward_logits_shard(*m->ids, check_ids != 0));
+        *logits_d = m->last->data();
+    });
+}
+
+extern "C" int dnn_gpt2cs_forward_logits_shard_host(dnn_gpt2cs* m, const int32_t* ids_h, int B, int T,
+                                                    float** logits_d) {
+    return guarded([&] {
+        m->stage_ids(ids_h, B, T, cudaMemcpyHostToDevice);
+        m->last.reset();
+        m->last = std::make_unique<dnn::tensor<float>>(m->model->forward_logits_shard(*m->ids, false));
+        *logits_d = m->last->data();
+    });
+}

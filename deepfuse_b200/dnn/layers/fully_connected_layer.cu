@@ -3,6 +3,7 @@
 #include <cmath>
 #include <random>
 #include <stdexcept>
+#include <type_traits>
 #include <vector>
 
 namespace dnn {
@@ -40,6 +41,35 @@ void FullyConnectedLayer<TT>::initialize_weights() {
 }
 
 namespace {
+// splitmix64 of (seed, index) -> uniform in (-limit, limit)
+__global__ void init_uniform_kernel(float* w, size_t n, float limit, uint64_t seed, uint64_t offset) {
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
+        uint64_t z = seed * 0x9E3779B97F4A7C15ull + (i + offset + 1) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        z ^= z >> 31;
+        const float u = float(uint32_t(z >> 40)) * (1.0f / 16777216.0f);  // [0, 1)
+        w[i] = (2.0f * u - 1.0f) * limit;
+    }
+}
+}  // namespace
+
+template <typename TT>
+void FullyConnectedLayer<TT>::initialize_weights_on_device(float limit, uint64_t seed, uint64_t index_offset) {
+    if constexpr (std::is_same<TT, float>::value) {
+        const size_t n = this->weights_.numel();
+        if (n) {
+            init_uniform_kernel<<<1184, 256, 0, Cuda::stream()>>>(this->weights_.data(), n, limit, seed, index_offset);
+            utils::CHECK_CUDA_EX(cudaGetLastError());
+        }
+        this->weights_.bump_version();
+        this->bias_.zero();
+    } else {
+        throw std::runtime_error("initialize_weights_on_device: float layers only");
+    }
+}
+
+namespace {
 // rows x cols fp32 -> rows x cols_padded, the new columns zero (zero is the fp8 code 0x00 as well)
 tensor<float> pad_columns(const float* src, int rows, int cols, int cols_padded) {
     tensor<float> out({rows, cols_padded});
@@ -58,11 +88,20 @@ template <typename TT>
 const fp8::Quantized& FullyConnectedLayer<TT>::quantized_weights() {
     if (wq_version_ != this->weights_.version()) {
         const int kp = padded_in();
-        if (kp == in_features_) {
-            fp8::quantize(this->weights_.data(), this->weights_.numel(), fp8::policy().weight_kind, wq_);
-        } else {
-            tensor<float> padded = pad_columns(this->weights_.data(), out_features_, in_features_, kp);
-            fp8::quantize(padded.data(), padded.numel(), fp8::policy().weight_kind, wq_);
+        std::optional<tensor<float>> padded;
+        const float* src = this->weights_.data();
+        size_t n = this->weights_.numel();
+        if (kp != in_features_) {
+            padded = pad_columns(this->weights_.data(), out_features_, in_features_, kp);
+            src = padded->data();
+            n = padded->numel();
+        }
+        if (!shard_comm_) {
+            fp8::quantize(src, n, fp8::policy().weight_kind, wq_);
+        } else {  // the scale of the whole (sharded) tensor
+            utils::CHECK_DF8(df8_amax_f32(src, n, wq_.amax.data(), fp8::stream()));
+            utils::CHECK_DF8(df8_comm_allreduce_max_f32(shard_comm_, wq_.amax.data(), 1, fp8::stream()));
+            fp8::quantize_with_amax(src, n, fp8::policy().weight_kind, wq_.amax.data(), wq_);
         }
         wq_version_ = this->weights_.version();
     }

@@ -65,9 +65,20 @@ public:
     // Declares the cached scale current for the present weights tensor / forces a re-quantisation.
     void mark_weights_quantized() { wq_version_ = this->weights_.version(); }
     void invalidate_quantized_weights() { wq_version_ = ~0ull; }
+    // Column sharding: this layer holds a row block of a larger weight matrix whose other blocks live on the
+    // other ranks of `comm`.  The per-tensor scale must then come from the maximum over ALL blocks, so
+    // quantized_weights() all-reduces the local max|w| first (a collective: every rank must quantise).
+    void set_shard_comm(df8_comm* comm) {
+        shard_comm_ = comm;
+        invalidate_quantized_weights();
+    }
+    // Replaces the weights by uniform values in (-limit, +limit) generated on the device from a counter hash
+    // of (seed, element index + index_offset); for models too large to initialise through the host.
+    void initialize_weights_on_device(float limit, uint64_t seed, uint64_t index_offset = 0);
 
 private:
     const uint8_t* external_codes_ = nullptr;
+    df8_comm* shard_comm_ = nullptr;
     int in_features_;
     int out_features_;
     std::optional<tensor<TT>> input_cache_;

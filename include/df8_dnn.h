@@ -55,6 +55,28 @@ unsigned long long dnn_gpt2_streamed_bytes(dnn_gpt2* m);
 int dnn_gpt2_save(dnn_gpt2* m, const char* path);
 dnn_gpt2* dnn_gpt2_load(const char* path);
 
+/* ---- dnn::Gpt2ColumnSharded<float>: fully-connected weights split by output columns over the ranks of a
+ * df8_comm (include/df8.h; NULL = a single rank).  Parameters are this rank's SHARDS, named as above:
+ * blockN.qkv.weight is [3E/g, E] = the rows {Q, K, V} x (this rank's heads) of the fused weight, blockN.out /
+ * fc1 / fc2 .weight are row blocks [E/g,E], [F/g,E], [E/g,F] (biases likewise), final_fc.weight is rows
+ * [vocab_begin, vocab_begin + vocab_rows) of the head; embedding and LayerNorm parameters are replicated. ---- */
+typedef struct dnn_gpt2cs dnn_gpt2cs;
+dnn_gpt2cs* dnn_gpt2cs_create(void* comm, int vocab, int max_seq_len, int layers, int heads, int hidden, int ffn);
+void dnn_gpt2cs_destroy(dnn_gpt2cs* m);
+int dnn_gpt2cs_set_options(dnn_gpt2cs* m, int mlp_gelu, int causal);
+int dnn_gpt2cs_vocab_range(dnn_gpt2cs* m, int* begin_h, int* rows_h);
+int dnn_gpt2cs_num_params(dnn_gpt2cs* m);
+int dnn_gpt2cs_param_info(dnn_gpt2cs* m, int index, char* name_h, int name_cap, int* shape_h, int* ndim_h);
+int dnn_gpt2cs_param_upload(dnn_gpt2cs* m, int index, const float* data_h);
+/* uniform random shards generated on the device (for shapes too large to initialise through the host) */
+int dnn_gpt2cs_initialize_on_device(dnn_gpt2cs* m, unsigned long long seed);
+/* collective: quantises every shard with the scale of its whole (sharded) tensor */
+int dnn_gpt2cs_prepare(dnn_gpt2cs* m);
+/* collective: logits of this rank's vocabulary rows [B*T, vocab_rows] fp32, owned by the handle */
+int dnn_gpt2cs_forward_logits_shard(dnn_gpt2cs* m, const int32_t* ids_d, int B, int T, int check_ids,
+                                    float** logits_d);
+int dnn_gpt2cs_forward_logits_shard_host(dnn_gpt2cs* m, const int32_t* ids_h, int B, int T, float** logits_d);
+
 /* ---- single layers through their public forward(), host buffers in and out ---- */
 int dnn_fc_forward(int in_features, int out_features, const float* w_h, const float* b_h, const float* x_h, int M,
                    float* y_h);

@@ -78,3 +78,55 @@ def test_two_rank_gloo_run(tmp_path):
         assert got[0] == 11.0            # max over ranks of 10 + rank
         assert got[1] == 1.0             # column-sharded FC reassembled by all-gather
         assert got[2:].tolist() == [0, 16, 16, 16]
+
+
+def test_vocab_shard_covers_the_vocabulary():
+    from deepfuse_b200.sharding import vocab_shard
+
+    for vocab, world in [(50257, 8), (50257, 2), (1000, 4), (7, 8), (16, 1)]:
+        rows = []
+        for r in range(world):
+            b, n = vocab_shard(vocab, world, r)
+            assert b == min(r * -(-vocab // world), vocab) and n >= 0
+            rows.extend(range(b, b + n))
+        assert rows == list(range(vocab))
+
+
+def test_shard_gpt2_params_reassembles_to_the_full_tensors():
+    import numpy as np
+
+    from deepfuse_b200.sharding import shard_gpt2_params, vocab_shard
+
+    cfg = dict(vocab=37, hidden=16, ffn=32, heads=4)
+    E, F, V = cfg["hidden"], cfg["ffn"], cfg["vocab"]
+    rng = np.random.default_rng(0)
+    full = {"embedding.weight": rng.normal(size=(V, E)), "embedding.bias": rng.normal(size=(1, E, 1, 1)),
+            "block0.ln1.gamma": rng.normal(size=(E,)), "block0.ln1.beta": rng.normal(size=(E,)),
+            "block0.qkv.weight": rng.normal(size=(3 * E, E)), "block0.qkv.bias": rng.normal(size=(1, 3 * E, 1, 1)),
+            "block0.out.weight": rng.normal(size=(E, E)), "block0.out.bias": rng.normal(size=(1, E, 1, 1)),
+            "block0.fc1.weight": rng.normal(size=(F, E)), "block0.fc1.bias": rng.normal(size=(1, F, 1, 1)),
+            "block0.fc2.weight": rng.normal(size=(E, F)), "block0.fc2.bias": rng.normal(size=(1, E, 1, 1)),
+            "final_fc.weight": rng.normal(size=(V, E)), "final_fc.bias": rng.normal(size=(1, V, 1, 1))}
+    for world in (1, 2, 4):
+        shards = [shard_gpt2_params(full, cfg, world, r) for r in range(world)]
+        eg = E // world
+        # QKV: rank r holds [Q_r; K_r; V_r]
+        qkv = np.empty((3 * E, E))
+        qb = np.empty(3 * E)
+        for r, s in enumerate(shards):
+            for part in range(3):
+                qkv[part * E + r * eg:part * E + (r + 1) * eg] = s["block0.qkv.weight"][part * eg:(part + 1) * eg]
+                qb[part * E + r * eg:part * E + (r + 1) * eg] = s["block0.qkv.bias"].reshape(-1)[part * eg:(part + 1) * eg]
+        assert np.array_equal(qkv, full["block0.qkv.weight"]) and np.array_equal(qb, full["block0.qkv.bias"].reshape(-1))
+        for name in ("block0.out", "block0.fc1", "block0.fc2", "final_fc"):
+            w = np.concatenate([s[name + ".weight"] for s in shards])
+            b = np.concatenate([s[name + ".bias"].reshape(-1) for s in shards])
+            assert np.array_equal(w, full[name + ".weight"]) and np.array_equal(b, full[name + ".bias"].reshape(-1))
+        for r, s in enumerate(shards):
+            assert s["final_fc.weight"].shape[0] == vocab_shard(V, world, r)[1]
+            assert np.array_equal(s["embedding.weight"], full["embedding.weight"])
+            assert np.array_equal(s["block0.ln1.gamma"], full["block0.ln1.gamma"])
+    import pytest
+
+    with pytest.raises(ValueError):
+        shard_gpt2_params(full, cfg, 3, 0)

@@ -468,9 +468,9 @@ class Gpt2Workload:
         t_head = time.perf_counter() - t0
         # one block at `tokens` context -> L blocks at the full context, scaled by the per-token block flops
         blk = lambda T: 2 * (3 * E * E + E * E + 2 * E * c["ffn"]) + 4 * T * E
-        secs = t_block * GPT2_CONFIGS[self.name]["layers"] * blk(self.T) / blk(tokens) + t_head
+        secs = t_block * c["layers"] * blk(self.T) / blk(tokens) + t_head
         return tokens, secs, (f"one transformer block + the vocabulary head on 1x{tokens} tokens, extrapolated "
-                              f"linearly in flops to {GPT2_CONFIGS[self.name]['layers']} blocks at context {self.T}")
+                              f"linearly in flops to {c['layers']} blocks at context {self.T}")
 
 
 class AttnWorkload:
@@ -553,7 +553,112 @@ class AttnWorkload:
         dt = time.perf_counter() - t0
         return 4.0 * self.H * T * T * self.D / 1e12, dt, f"one sequence of {T} tokens, {self.H} heads"
 
-WORKLOADS = {"attn": AttnWorkload, "quant": QuantWorkload, "gemm": GemmWorkload, "gpt2s": Gpt2Workload, "gpt2m": Gpt2Workload}
+class Gpt2ShardedWorkload(Gpt2Workload):
+    """BASELINE configs[4]: the 6.7B-shape GPT-2 forward (32 layers, d_model 4096, 32 heads, FFN 16384, context 2048,
+    batch 16 x 2048 token ids, the same on every rank) with the fully-connected weights column-sharded over the
+    GPUs and NCCL all-gathers between the layers (dnn::Gpt2ColumnSharded).  Total work is fixed: strong scaling.
+    Weights are uniform with the standard deviation of N(0, 0.02), generated on the device."""
+
+    CFG = dict(layers=32, hidden=4096, heads=32, ffn=16384, vocab=50257, ctx=2048, batch=16, act="e4m3")
+
+    def __init__(self, n_gpus=1, batch=None, layers=None):
+        self.name = "gpt67"
+        self.c = dict(self.CFG)
+        if layers:
+            self.c["layers"] = layers
+        self.n_gpus = n_gpus
+        self.strong = True
+        self.B = batch or self.c["batch"]
+        self.T = self.c["ctx"]
+        self.metric = "GPT-2 fp8 forward tokens/s"
+        self.dtype = "e4m3 activations x e4m3 weights -> f32 accumulate"
+        # embedding; per layer: 2 x (LayerNorm 2), QKV 2 passes, attention, quantise, gather + interleave, out GEMM,
+        # gather + interleave, add, FC1 2 passes, gather + interleave, FC2, gather + interleave, add; head 3
+        per_layer = 15 + (8 if n_gpus > 1 else 4)
+        self.kernels_per_step = 1 + per_layer * self.c["layers"] + 3
+
+    def config(self, n_gpus):
+        c = self.c
+        return {"workload": f"GPT-2 6.7B-shape fp8 forward: {c['layers']} layers, d_model {c['hidden']}, {c['heads']} "
+                            f"heads, FFN {c['ffn']}, vocab {c['vocab']}, batch {self.B}x{self.T} token ids (the same "
+                            f"on every rank), fp32 logits sharded by vocabulary rows, random-init weights",
+                "global_batch": self.B, "seq_len": self.T, "weights": "resident e4m3 codes, 1/N of every matrix per GPU",
+                "l2_policy": "working set per forward far larger than L2",
+                "parallelism": f"fully-connected weights column-sharded x{n_gpus}, attention by heads, NCCL all-reduce(max) "
+                               f"of per-tensor maxima and all-gather of fp8 codes / fp32 residual updates"}
+
+    def units_per_step(self):
+        return self.B * self.T / self.n_gpus  # every rank works on all tokens: count each token once
+
+    def setup(self, torch, df8, dev, rank):
+        import oracle as orc
+
+        self.torch, self.df8, self.dev = torch, df8, dev
+        c = self.c
+        d = df8.dnn_lib()
+        df8.dnn_check(d.dnn_init(dev.index), "dnn_init")
+        df8.dnn_check(d.dnn_set_fp8_policy(0, 0))
+        df8.dnn_check(d.dnn_set_host_init(0))
+        self.comm = df8.Comm(rank, self.n_gpus)
+        self.model = df8.Gpt2ColumnSharded(self.comm, vocab=c["vocab"], max_seq_len=c["ctx"], layers=c["layers"],
+                                           heads=c["heads"], hidden=c["hidden"], ffn=c["ffn"], device=dev.index)
+        df8.dnn_check(d.dnn_set_host_init(1))
+        self.model.set_stream(torch.cuda.current_stream())
+        self.model.initialize_on_device(4)
+        self.model.set_options(gelu=True, causal=False)
+        ids = orc.fill_token_ids(self.B * self.T, seed=4, vocab=c["vocab"]).reshape(self.B, self.T)
+        self.ids = torch.from_numpy(ids).to(dev)
+        self.ids_host = torch.from_numpy(ids).pin_memory()
+        self.last_logits = torch.empty((self.B, self.model.vocab_rows), dtype=torch.float32, pin_memory=True)
+
+    def step(self):
+        self.logits_ptr = self.model.forward_logits_shard(self.ids, check_ids=False)
+
+    def e2e_step(self):
+        torch = self.torch
+        ptr = self.model.forward_logits_shard_host(self.ids_host)
+        logits = self.df8.device_view(torch, ptr, (self.B, self.T, self.model.vocab_rows))
+        self.last_logits.copy_(logits[:, -1, :], non_blocking=True)
+
+    def e2e_units_per_step(self):
+        return self.units_per_step()
+
+    def roofline(self, torch, peaks, iters=5):
+        # dominant kernel: this rank's FC1 product [B*T, F/N] x [F/N, E], one fp8-codes pass
+        d, c = self.df8, self.c
+        M, N, K = self.B * self.T, c["ffn"] // self.n_gpus, c["hidden"]
+        g = torch.Generator(device=self.dev)
+        g.manual_seed(1)
+        a = torch.randint(0, 0x70, (M, K), dtype=torch.uint8, device=self.dev, generator=g)
+        w = torch.randint(0, 0x70, (N, K), dtype=torch.uint8, device=self.dev, generator=g)
+        one = torch.tensor([1.0, 1.0 / 64], device=self.dev)
+        out = torch.empty((M, N), dtype=torch.uint8, device=self.dev)
+        amax, osc = torch.zeros(1, device=self.dev), torch.zeros(2, device=self.dev)
+        for _ in range(2):
+            d.gemm_fp8_tn_q(a, 0, one, w, 0, one, None, M, N, K, 1, 0, out, osc, amax)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        torch.cuda.synchronize()
+        ev[0].record()
+        for _ in range(iters):
+            d.gemm_fp8_tn_q(a, 0, one, w, 0, one, None, M, N, K, 1, 0, out, osc, amax)
+        ev[1].record()
+        torch.cuda.synchronize()
+        ms = ev[0].elapsed_time(ev[1]) / iters / 2  # two passes per call
+        flops = 2.0 * M * N * K
+        tf = flops / 1e12 / (ms / 1e3)
+        peak = 2.0 * peaks["bf16_tflops_sustained"]
+        return {"kernel": "gemm_fp8_tn_pair_kernel (FC1 shard, average of its two passes)", "bound": "tensor",
+                "achieved": round(tf, 1), "peak": peak, "peak_source": peaks["source"] + " bf16 sustained x2 (fp8 dense)",
+                "unit": "TFLOP/s", "frac": round(tf / peak, 4), "ms_per_launch": round(ms, 4),
+                "algorithmic_flops_per_launch": flops, "traffic": None,
+                "model_flops_per_token": gpt2_flops_per_token(c, self.T)}
+
+    def cpu_sample(self, orc, tokens=32):
+        return super().cpu_sample(orc, tokens=tokens)
+
+
+WORKLOADS = {"attn": AttnWorkload, "quant": QuantWorkload, "gemm": GemmWorkload, "gpt2s": Gpt2Workload, "gpt2m": Gpt2Workload,
+             "gpt67": Gpt2ShardedWorkload}
 DEFAULT_WORKLOAD = "gpt2s"
 
 
@@ -562,6 +667,9 @@ def make_workload(args):
         return QuantWorkload(log2n=args.log2n)
     if args.workload == "gemm" and args.only:
         return GemmWorkload(only=args.only.split(","))
+    if args.workload == "gpt67":
+        return Gpt2ShardedWorkload(n_gpus=max(1, int(os.environ.get("WORLD_SIZE", args.gpus))), batch=args.batch,
+                                   layers=args.layers)
     if args.workload in GPT2_CONFIGS:
         return Gpt2Workload(args.workload, n_gpus=max(1, int(os.environ.get("WORLD_SIZE", args.gpus))),
                             batch=args.batch, layers=args.layers)

@@ -223,6 +223,7 @@ _DNN_SIGNATURES = {
     "dnn_selftest_tensor": [_vp, _i],
     "dnn_selftest_context": [_vp, _i],
     "dnn_selftest_errors": [_vp, _i],
+    "dnn_set_host_init": [_i],
     "dnn_gpt2cs_destroy": [_vp],
     "dnn_gpt2cs_set_options": [_vp, _i, _i],
     "dnn_gpt2cs_vocab_range": [_vp, _vp, _vp],

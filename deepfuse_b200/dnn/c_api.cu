@@ -105,6 +105,10 @@ extern "C" int dnn_set_fp8_policy(int weight_kind, int activation_kind) {
     });
 }
 
+extern "C" int dnn_set_host_init(int enabled) {
+    return guarded([&] { dnn::fp8::policy().host_init = enabled != 0; });
+}
+
 // ---- Gpt2 -------------------------------------------------------------------------------------
 
 extern "C" dnn_gpt2* dnn_gpt2_create(int vocab, int max_seq_len, int layers, int heads, int hidden, int ffn) {

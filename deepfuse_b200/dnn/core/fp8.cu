@@ -9,6 +9,26 @@ Policy& policy() {
 }
 
 namespace {
+// splitmix64 of (seed, index) -> uniform in (-limit, limit)
+__global__ void fill_uniform_kernel(float* w, size_t n, float limit, uint64_t seed, uint64_t offset) {
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
+        uint64_t z = seed * 0x9E3779B97F4A7C15ull + (i + offset + 1) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        z ^= z >> 31;
+        const float u = float(uint32_t(z >> 40)) * (1.0f / 16777216.0f);  // [0, 1)
+        w[i] = (2.0f * u - 1.0f) * limit;
+    }
+}
+}  // namespace
+
+void fill_uniform(float* p, size_t n, float limit, uint64_t seed, uint64_t index_offset) {
+    if (n == 0) return;
+    fill_uniform_kernel<<<1184, 256, 0, Cuda::stream()>>>(p, n, limit, seed, index_offset);
+    utils::CHECK_CUDA_EX(cudaGetLastError());
+}
+
+namespace {
 constexpr int kPoolFloats = 4096;
 struct PassState {
     int depth = 0;

@@ -21,7 +21,13 @@ namespace fp8 {
 struct Policy {
     df8_kind weight_kind = DF8_E4M3;
     df8_kind activation_kind = DF8_E4M3;
+    // false: layer constructors leave their weights zero instead of drawing them on the host (for models of
+    // billions of parameters that are then filled on the device or loaded)
+    bool host_init = true;
 };
+
+// p[i] = uniform in (-limit, limit) from a counter hash of (seed, i + index_offset), generated on the device
+void fill_uniform(float* p, size_t n, float limit, uint64_t seed, uint64_t index_offset = 0);
 
 // Process-wide policy read by layers at forward time.
 Policy& policy();

@@ -11,13 +11,21 @@ namespace dnn {
 template <typename TT>
 FullyConnectedLayer<TT>::FullyConnectedLayer(int in_features, int out_features, bool training_enabled)
     : LayerWeightBias<TT>(tensor<TT>({out_features, in_features}), tensor<TT>({1, out_features, 1, 1}),
-                          tensor<TT>({out_features, in_features}), tensor<TT>({1, out_features, 1, 1}),
-                          training_enabled),
+                          // gradient buffers: not kept for inference-only layers of models built without host
+                          // initialisation (billions of parameters)
+                          (training_enabled || fp8::policy().host_init) ? tensor<TT>({out_features, in_features})
+                                                                        : tensor<TT>({0}),
+                          tensor<TT>({1, out_features, 1, 1}), training_enabled),
       in_features_(in_features),
       out_features_(out_features) {
     if (in_features <= 0 || out_features <= 0)
         throw std::invalid_argument("FullyConnectedLayer: feature counts must be positive");
-    initialize_weights();
+    if (fp8::policy().host_init) {
+        initialize_weights();
+    } else {
+        this->weights_.zero();
+        this->bias_.zero();
+    }
     this->grad_weights_.zero();
     this->grad_bias_.zero();
 }
@@ -40,28 +48,10 @@ void FullyConnectedLayer<TT>::initialize_weights() {
     this->bias_.zero();
 }
 
-namespace {
-// splitmix64 of (seed, index) -> uniform in (-limit, limit)
-__global__ void init_uniform_kernel(float* w, size_t n, float limit, uint64_t seed, uint64_t offset) {
-    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
-        uint64_t z = seed * 0x9E3779B97F4A7C15ull + (i + offset + 1) * 0xBF58476D1CE4E5B9ull;
-        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
-        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
-        z ^= z >> 31;
-        const float u = float(uint32_t(z >> 40)) * (1.0f / 16777216.0f);  // [0, 1)
-        w[i] = (2.0f * u - 1.0f) * limit;
-    }
-}
-}  // namespace
-
 template <typename TT>
 void FullyConnectedLayer<TT>::initialize_weights_on_device(float limit, uint64_t seed, uint64_t index_offset) {
     if constexpr (std::is_same<TT, float>::value) {
-        const size_t n = this->weights_.numel();
-        if (n) {
-            init_uniform_kernel<<<1184, 256, 0, Cuda::stream()>>>(this->weights_.data(), n, limit, seed, index_offset);
-            utils::CHECK_CUDA_EX(cudaGetLastError());
-        }
+        fp8::fill_uniform(this->weights_.data(), this->weights_.numel(), limit, seed, index_offset);
         this->weights_.bump_version();
         this->bias_.zero();
     } else {

@@ -87,6 +87,9 @@ void Gpt2ColumnSharded<T>::initialize_on_device(uint64_t seed) {
             fc->initialize_weights_on_device(limit, ++tag, uint64_t(rank_) * fc->weights()->numel());
     }
     final_fc_->initialize_weights_on_device(limit, ++tag, uint64_t(vocab_begin_) * uint64_t(hidden_dim_));
+    // the (replicated) embedding table: the same values on every rank
+    fp8::fill_uniform(token_embedding_->weights()->data(), token_embedding_->weights()->numel(), limit, ++tag, 0);
+    token_embedding_->weights()->bump_version();
 }
 
 template <typename T>

@@ -24,7 +24,12 @@ TokenEmbedding<T>::TokenEmbedding(int vocab_size, int embedding_dim, int max_seq
       embedding_dim_(embedding_dim),
       max_seq_len_(checked_positive(max_seq_len, "Maximum sequence length")),
       bad_ids_({1}) {
-    initialize_weights();
+    if (fp8::policy().host_init) {
+        initialize_weights();
+    } else {
+        this->weights_.zero();
+        this->bias_.zero();
+    }
     this->grad_weights_.zero();
     this->grad_bias_.zero();
 }

@@ -26,6 +26,9 @@ int dnn_init(int device);
 int dnn_set_stream(void* stream);
 /* fp8 kinds (0 = e4m3, 1 = e5m2) used for weights and for activations. */
 int dnn_set_fp8_policy(int weight_kind, int activation_kind);
+/* 0: constructors of layers leave weights zero instead of drawing them on the host (then fill on the device or
+ * upload); 1 (default): upstream's behaviour. */
+int dnn_set_host_init(int enabled);
 
 /* ---- dnn::Gpt2<float> ---- */
 dnn_gpt2* dnn_gpt2_create(int vocab, int max_seq_len, int layers, int heads, int hidden, int ffn);

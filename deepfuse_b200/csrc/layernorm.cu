@@ -9,7 +9,15 @@
 // result: pass 1 keeps each row's (mean, rstd) in a small scratch array and reduces max|y| over the
 // tensor, pass 2 re-reads x, normalises and emits fp8 codes.  9 bytes of HBM traffic per element
 // instead of 13 for LayerNorm -> amax -> quantise as separate kernels.
+//
+// When the whole activation fits in the GPU's shared memory (rows * C * 4 bytes <= SMs x 200 KB, e.g. 8192 x 768),
+// the fused entry point runs ONE co-resident kernel instead: every CTA normalises its rows into shared memory,
+// the CTAs meet at a grid-wide barrier once max|y| is complete, and the codes are produced from shared memory.
+// x is read once and nothing but the codes is written: 5 bytes per element, one launch.
 #include "df8_internal.cuh"
+
+#include <atomic>
+#include <cstdlib>
 
 namespace df8 {
 namespace {
@@ -265,6 +273,168 @@ bool launch_rows_kernel(const float* x, int rows, int C, const float* gamma, con
     return true;
 }
 
+// ---- shared-memory-resident fused LayerNorm + quantise (one launch, grid-wide barrier) ----------------
+
+constexpr int kResThreads = 1024;
+constexpr int kResSmemCap = 200 * 1024;
+// Arrival counters of the grid barrier.  Every launch uses the same grid (one CTA per SM), so a counter stays a
+// multiple of it between launches; consecutive launches take consecutive counters, so launches that overlap on
+// a GPU (different streams) do not see each other's arrivals.
+constexpr int kResCounters = 64;
+__device__ unsigned int g_ln_grid_counter[kResCounters] = {};
+
+template <int KIND, int V4>
+__global__ void __launch_bounds__(kResThreads, 1)
+layernorm_quantize_resident_kernel(const float* __restrict__ x, int rows, int C, const float* __restrict__ gamma,
+                                   const float* __restrict__ beta, float eps, float* amax, uint8_t* __restrict__ codes,
+                                   float* __restrict__ scale_out, int rows_per_cta, int counter_slot,
+                                   unsigned int* status) {
+    extern __shared__ float4 ybuf[];  // [rows_per_cta][C / 4]: the normalised rows of this CTA
+    __shared__ float block_amax[kResThreads / 32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int nw = kResThreads / 32;
+    const int c4 = C >> 2;
+    const int r0 = blockIdx.x * rows_per_cta;
+    const int nrows = min(rows_per_cta, rows - r0);  // may be <= 0: such a CTA only takes part in the barrier
+    float warp_amax = 0.f;
+    for (int lr = warp; lr < nrows; lr += nw) {
+        const float4* xr = reinterpret_cast<const float4*>(x + size_t(r0 + lr) * C);
+        float4 v[V4];
+#pragma unroll
+        for (int j = 0; j < V4; ++j) {
+            const int i = lane + 32 * j;
+            v[j] = i < c4 ? ld_stream_f4(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        // the same operations in the same order as layernorm_rows_kernel: the two paths agree bit for bit
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < V4; ++j) sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+        const float mean = warp_sum(sum) / float(C);
+        float sq = 0.f;
+#pragma unroll
+        for (int j = 0; j < V4; ++j) {
+            if (lane + 32 * j < c4) {
+                const float a = v[j].x - mean, b = v[j].y - mean, c = v[j].z - mean, d = v[j].w - mean;
+                sq += (a * a + b * b) + (c * c + d * d);
+            }
+        }
+        const float rstd = rsqrtf(warp_sum(sq) / float(C) + eps);
+#pragma unroll
+        for (int j = 0; j < V4; ++j) {
+            const int i = lane + 32 * j;
+            if (i < c4) {
+                float4 g = make_float4(1.f, 1.f, 1.f, 1.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (gamma) g = __ldg(reinterpret_cast<const float4*>(gamma) + i);
+                if (beta) b = __ldg(reinterpret_cast<const float4*>(beta) + i);
+                float4 o;
+                o.x = fmaf((v[j].x - mean) * rstd, g.x, b.x);
+                o.y = fmaf((v[j].y - mean) * rstd, g.y, b.y);
+                o.z = fmaf((v[j].z - mean) * rstd, g.z, b.z);
+                o.w = fmaf((v[j].w - mean) * rstd, g.w, b.w);
+                warp_amax = fmaxf(warp_amax, fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w))));
+                ybuf[size_t(lr) * c4 + i] = o;
+            }
+        }
+    }
+    {
+        const float mx = warp_max(warp_amax);
+        if (lane == 0) block_amax[warp] = mx;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            float m = block_amax[threadIdx.x];
+            m = warp_max(m);
+            if (threadIdx.x == 0 && m > 0.f) atomic_max_nonneg(amax, m);
+        }
+    }
+    // ---- grid-wide barrier: max|y| is complete once every CTA has arrived (bounded wait) ----
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned int ticket = atomicAdd(&g_ln_grid_counter[counter_slot], 1u);
+        const unsigned int target = (ticket / gridDim.x + 1u) * gridDim.x;
+        volatile unsigned int* cnt = &g_ln_grid_counter[counter_slot];
+        unsigned long long t0 = 0;
+        for (unsigned int spins = 0; int(*cnt - target) < 0; ++spins) {
+            __nanosleep(64);
+            if ((spins & 1023u) == 1023u) {
+                unsigned long long now;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (t0 == 0) t0 = now;
+                if (now - t0 > 2000000000ull) {  // a CTA never came: give up, flag it, and finish
+                    if (status) {
+                        atomicCAS(status, 0u, 0x3000u);
+                        atomicAdd(status + 1, 1u);
+                    }
+                    break;
+                }
+            }
+        }
+        __threadfence();
+    }
+    __syncthreads();
+    const float2 sc = scales_from_amax(*reinterpret_cast<volatile float*>(amax), fp8_max(KIND));
+    if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) {
+        scale_out[0] = sc.x;
+        scale_out[1] = sc.y;
+    }
+    const float q = sc.x;
+    for (int lr = warp; lr < nrows; lr += nw) {
+        uint32_t* crow = reinterpret_cast<uint32_t*>(codes + size_t(r0 + lr) * C);
+#pragma unroll
+        for (int j = 0; j < V4; ++j) {
+            const int i = lane + 32 * j;
+            if (i < c4) {
+                const float4 o = ybuf[size_t(lr) * c4 + i];
+                crow[i] = cvt_f32x4_to_fp8x4<KIND>(__fmul_rn(o.x, q), __fmul_rn(o.y, q), __fmul_rn(o.z, q),
+                                                   __fmul_rn(o.w, q));
+            }
+        }
+    }
+}
+
+// Launches the resident kernel if the problem qualifies; returns false (nothing launched) otherwise.
+template <int KIND>
+bool launch_resident(const float* x, int rows, int C, const float* gamma, const float* beta, float eps, uint8_t* codes,
+                     float* scale_out, float* amax, cudaStream_t st) {
+    if (const char* e = getenv("DF8_LN_RESIDENT"))
+        if (e[0] == '0') return false;
+    if (C > 1024 || rows < 1024) return false;
+    const int sms = sm_count();
+    const int rows_per_cta = (rows + sms - 1) / sms;
+    const size_t smem = size_t(rows_per_cta) * size_t(C) * sizeof(float);
+    if (smem > size_t(kResSmemCap)) return false;
+    unsigned int* status = nullptr;
+    if (status_word_device_ptr(&status) != DF8_OK) return false;
+    static std::atomic<unsigned int> next_slot{0};
+    const int counter_slot = int(next_slot.fetch_add(1u) % unsigned(kResCounters));
+    auto launch = [&](auto kern) -> bool {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kResSmemCap) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(unsigned(sms));
+        cfg.blockDim = dim3(kResThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeCooperative;  // the grid barrier needs every CTA resident
+        attr[0].val.cooperative = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, kern, x, rows, C, gamma, beta, eps, amax, codes, scale_out, rows_per_cta,
+                               counter_slot, status) != cudaSuccess) {
+            (void)cudaGetLastError();  // e.g. not co-schedulable: the two-kernel path takes over
+            return false;
+        }
+        return true;
+    };
+    if (C <= 256) return launch(layernorm_quantize_resident_kernel<KIND, 2>);
+    if (C <= 512) return launch(layernorm_quantize_resident_kernel<KIND, 4>);
+    if (C <= 768) return launch(layernorm_quantize_resident_kernel<KIND, 6>);
+    return launch(layernorm_quantize_resident_kernel<KIND, 8>);
+}
+
 bool fast_ok(int C, const void* a, const void* b, const void* c, const void* d) {
     return (C % 4 == 0) && C <= 4 * kMaxV4 * kLnThreads && aligned16(a) && aligned16(b) && aligned16(c) &&
            aligned16(d);
@@ -305,6 +475,7 @@ df8_status launch_ln_quant(const float* x, int rows, int cols, const float* gamm
                            uint8_t* codes, float* scale_out, float* amax_out, float2* row_stats, cudaStream_t st) {
     const int grid = ln_grid(rows);
     const bool fast = fast_ok(cols, x, gamma, beta, nullptr) && (reinterpret_cast<uintptr_t>(codes) & 3u) == 0;
+    if (fast && launch_resident<KIND>(x, rows, cols, gamma, beta, eps, codes, scale_out, amax_out, st)) return DF8_OK;
     if (fast && cols <= 4096) {
         launch_rows_kernel<1, KIND>(x, rows, cols, gamma, beta, eps, nullptr, amax_out, row_stats, nullptr, nullptr,
                                     nullptr, st);

@@ -63,6 +63,38 @@ def test_layernorm_quantize_vs_oracle(df8, oracle, cuda, kind, rows, cols):
     assert np.all(np.abs(got - want) <= step * np.maximum(np.abs(want), 1e-3) + 1e-6)
 
 
+@pytest.mark.parametrize("kind", [0, 1])
+@pytest.mark.parametrize("rows,cols,affine", [(8192, 768, True), (4096, 1024, False), (1500, 256, True), (1024, 520, True)])
+def test_layernorm_quantize_resident_path_equals_two_kernel_path(df8, oracle, cuda, monkeypatch, kind, rows, cols, affine):
+    """Activations that fit the GPU's shared memory take the one-launch kernel (rows normalised into shared memory,
+    grid-wide barrier, codes from shared memory); it must give the codes, scale and amax of the two-kernel path bit
+    for bit, repeatedly (the barrier counters are reused) and without touching the status word."""
+    import torch
+
+    x = oracle.fill_normal(rows * cols, seed=rows + cols, std=2.0).reshape(rows, cols)
+    g = oracle.fill_normal(cols, seed=4, mean=1.0, std=0.1) if affine else None
+    b = oracle.fill_normal(cols, seed=5, std=0.1) if affine else None
+    xd = _t(torch, x, cuda)
+    gd = _t(torch, g, cuda) if affine else None
+    bd = _t(torch, b, cuda) if affine else None
+
+    def run():
+        codes = torch.full((rows, cols), 0xAA, dtype=torch.uint8, device=cuda)
+        scale, amax = torch.zeros(2, device=cuda), torch.zeros(1, device=cuda)
+        stats = torch.zeros(2 * rows, device=cuda)
+        df8.layernorm_quantize_f32(xd, rows, cols, gd, bd, 1e-5, kind, codes, scale, amax, stats)
+        torch.cuda.synchronize()
+        return codes, scale, amax
+
+    monkeypatch.setenv("DF8_LN_RESIDENT", "0")
+    c0, s0, a0 = run()
+    monkeypatch.delenv("DF8_LN_RESIDENT")
+    for _ in range(3):
+        c1, s1, a1 = run()
+        assert a1.item() == a0.item() and torch.equal(s1, s0) and torch.equal(c1, c0)
+    assert df8.status_word() == (0, 0)
+
+
 @pytest.mark.parametrize("B,T,E,V", [(2, 5, 8, 11), (8, 64, 768, 50257), (1, 7, 30, 100)])
 def test_embed_pe_vs_oracle(df8, oracle, cuda, B, T, E, V):
     import torch

@@ -449,7 +449,10 @@ class Gpt2Workload:
         return {"kernel": "gemm_fp8_tn_kernel (vocabulary head)", "bound": "tensor", "achieved": round(tf, 1),
                 "peak": peak, "peak_source": peaks["source"] + " bf16 sustained x2 (fp8 dense)", "unit": "TFLOP/s",
                 "frac": round(tf / peak, 4), "ms_per_launch": round(ms, 4), "algorithmic_flops_per_launch": flops,
-                "traffic": None, "model_flops_per_token": gpt2_flops_per_token(c, self.T)}
+                # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this launch at batch 8 x 1024
+                # (profiles/gemm_fp8_tn_kernel_head_8192x50257x768.md: 68.0 MB + 1.605 GB), scaled by the rows
+                "traffic": round((68.0e6 + 1.605e9) * M / 8192) if c["hidden"] == 768 else None,
+                "model_flops_per_token": gpt2_flops_per_token(c, self.T)}
 
     def cpu_sample(self, orc, tokens=128):
         from oracle import gpt2_ref
@@ -524,7 +527,10 @@ class AttnWorkload:
         return {"kernel": "attention_fp8_kernel<64>", "bound": "tensor", "achieved": round(tf, 1), "peak": peak,
                 "peak_source": peaks["source"] + " bf16 burst x2 (fp8 dense)", "unit": "TFLOP/s",
                 "frac": round(tf / peak, 4), "ms_per_launch": round(ms, 4),
-                "algorithmic_flops_per_launch": self.units_per_step() * 1e12, "traffic": None}
+                "algorithmic_flops_per_launch": self.units_per_step() * 1e12,
+                # one ncu capture of this launch (profiles/attention_fp8_kernel_b8_t1024_h12_d64.md): 19.2 MB read
+                # + 67.3 MB written (25.2 MB of output; the rest is write-back of the bench's L2 flush buffer)
+                "traffic": round(19.15e6 + 67.33e6) if (self.B, self.T, self.H, self.D) == (8, 1024, 12, 64) else None}
 
     def e2e_setup(self, torch, dev):
         self.h_codes = torch.empty(self.codes.shape, dtype=torch.uint8, pin_memory=True)

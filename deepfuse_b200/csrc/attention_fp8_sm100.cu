@@ -11,11 +11,12 @@
 // Softmax follows upstream exactly in form: p = exp(s + mask - rowmax) / (sum + 1e-6), and p = 0
 // where mask < -1e8.  It is evaluated blockwise (online): per 128-key block the running row maximum
 // and sum are updated and the block's probabilities multiply V on the tensor cores; the [T,T] score
-// matrix never exists in memory.  A probability (scaled by a power of two) is handed to the tensor core as
-// the sum of two e4m3 numbers, its rounding and the rounding of what is left, i.e. with about 7 mantissa
-// bits: a single e4m3 rounding (3 bits) leaves ~2 % error on flat attention rows, outside the 1e-2 bound.
-// The exponentials and the split run on packed halves (two keys per instruction); the row sum is taken by
-// the tensor core as well (P times a tile of ones), so it is the sum of exactly the values that multiply V.
+// matrix never exists in memory.  The probabilities (scaled by a power of two) go to the tensor core as
+// half-precision numbers — a single e4m3 rounding (3 mantissa bits) leaves ~2 % error on flat attention rows,
+// outside the 1e-2 bound — so O += P.V is a kind::f16 product and each V tile is widened from its fp8 codes to
+// halves (exactly) on its way: the exponentials run on packed halves (ex2.approx.f16x2, two keys per
+// instruction) whose results are stored as they are, with no conversion.  The row sum is taken by the tensor
+// core as well (P times a tile of ones), so it is the sum of exactly the values that multiply V.
 //
 // Work item = one (batch, head, 128-query block).  The grid is persistent: as many CTAs as fit on the GPU
 // at once (two per SM at D = 64), each walking the items blockIdx.x, blockIdx.x + gridDim.x, ... with its
@@ -23,14 +24,19 @@
 // (Launched as one CTA per item, the block scheduler left the slot of a finished CTA empty for many
 // microseconds: the kernel took 1.7x the sum of its CTA times.)
 //   warp 0     TMA producer: an item's Q tile, then its K/V tiles through a 2-stage ring
-//   warp 1     MMA issuer:   S = Q.K^T (M=128, N=128, K=D) and O_blk = P.V (M=128, N=D, K=128),
-//                            V consumed as an N-major operand straight from its [keys, D] tile
+//   warp 1     MMA issuer:   S = Q.K^T (kind::f8f6f4, M=128, N=128, K=D), O += P.V and row sums += P.1
+//                            (kind::f16, M=128, N=D / 16, K=128)
 //   warps 2-5  softmax:      one thread per query row with the block's 128 scores in registers (tcgen05.ld),
-//                            row maximum, exp2 on packed halves, P -> swizzled smem as the A operand of the
-//                            PV product.  O and the row sum accumulate in TMEM across key blocks and are
-//                            rescaled (tcgen05.ld/st) only when the row maximum has grown past a threshold.
-//                            (Two threads per row with 64 scores each spilled at the 96 registers two CTAs
-//                            per SM allow with 320 threads, and paid ~700 cycles per block to swap maxima.)
+//                            row maximum, exp2 on packed halves stored straight into the swizzled fp16 A operand of
+//                            the PV product; the same thread widens key row `row` of the block's V tile from fp8
+//                            codes to the N-major fp16 B operand.  O and the row sum accumulate in TMEM across key
+//                            blocks and are rescaled (tcgen05.ld/st) only when the row maximum has grown past a
+//                            threshold.
+//                            (Two threads per row with 64 scores each spilled at the 96 registers two CTAs per SM
+//                            allow with 320 threads, and paid ~700 cycles per block to swap maxima; probabilities
+//                            as the sum of two e4m3 numbers kept the PV product in fp8 but cost two fp8 packs per
+//                            key on the conversion unit, which the exponentials already saturate: 94 us against
+//                            82 us for this form at B=8 T=1024 H=12 D=64.)
 // All mbarrier waits are bounded (status word, see df8_status_word_read).
 #include "df8_internal.cuh"
 #include "sm100_ptx.cuh"
@@ -57,6 +63,7 @@ struct AttnArgs {
     int n_qblk, n_items;
     int mask_mode;       // 0 none, 1 causal, 2 additive tensor
     int mask_b;
+    int v_kind;          // fp8 kind of the QKV codes (how V widens to fp16)
     uint32_t idesc_qk, idesc_pv, idesc_sum;
     unsigned int* status;
 };
@@ -68,10 +75,11 @@ struct AttnCfg {
     static constexpr int kKBytes = BKV * D;
     static constexpr int kStageBytes = 2 * kKBytes;  // K then V
     static constexpr int kStages = 2;
-    static constexpr int kPBytes = 2 * 2 * BQ * BKV;  // two buffers of {leading part, remainder} e4m3 tiles
-    static constexpr int kOnesBytes = 16 * 128;       // 16 x 128 tile of e4m3 ones: B operand of the row-sum product
+    static constexpr int kPBytes = 2 * BQ * 128;      // fp16 P [128 queries][128 keys]: two K atoms of 64 keys (128 B rows)
+    static constexpr int kV16Bytes = BKV * D * 2;     // the block's V widened to fp16: [keys][D], D/64 atoms of 128 B rows
+    static constexpr int kOnesBytes = 2 * 16 * 128;   // 16 x 128 tile of fp16 ones: B operand of the row-sum product
     static constexpr int kBarBytes = 128;  // mbarriers and the TMEM base slot
-    static constexpr int kUsedBytes = kQBytes + kStages * kStageBytes + kPBytes + kOnesBytes + kBarBytes + 1024;
+    static constexpr int kUsedBytes = kQBytes + kStages * kStageBytes + kPBytes + kV16Bytes + kOnesBytes + kBarBytes + 1024;
     // pad the request so that at most two CTAs share an SM: each allocates 256 of the 512 TMEM columns
     static constexpr int kSmemBytes = kUsedBytes < 110 * 1024 ? 110 * 1024 : kUsedBytes;
     // S: columns [0,128), O: [128, 128+D), row sum: [128+D, 128+D+16) (sixteen identical copies)
@@ -106,19 +114,14 @@ __device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
     asm("ex2.approx.f16x2 %0, %1;" : "=r"(d) : "r"(x));
     return d;
 }
-__device__ __forceinline__ uint32_t e4m3x2_of_f16x2(uint32_t x) {  // 16 significant bits
-    uint16_t d;
-    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(d) : "r"(x));
-    return d;
-}
 __device__ __forceinline__ uint32_t f16x2_of_e4m3x2(uint32_t x) {
     uint32_t d;
     asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(d) : "h"(static_cast<uint16_t>(x)));
     return d;
 }
-__device__ __forceinline__ uint32_t sub_f16x2(uint32_t a, uint32_t b) {
+__device__ __forceinline__ uint32_t f16x2_of_e5m2x2(uint32_t x) {
     uint32_t d;
-    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(d) : "h"(static_cast<uint16_t>(x)));
     return d;
 }
 
@@ -132,7 +135,8 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
     uint8_t* sQ = smem;
     uint8_t* sKV = sQ + Cfg::kQBytes;
     uint8_t* sP = sKV + Cfg::kStages * Cfg::kStageBytes;
-    uint8_t* sOnes = sP + Cfg::kPBytes;
+    uint8_t* sV16 = sP + Cfg::kPBytes;
+    uint8_t* sOnes = sV16 + Cfg::kV16Bytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sOnes + Cfg::kOnesBytes);
     uint64_t* q_full = bars;
     uint64_t* kv_full = bars + 1;   // [2]
@@ -181,7 +185,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
         mbar_fence_init();
     }
     for (int i = threadIdx.x; i < Cfg::kOnesBytes / 4; i += kAttnThreads)
-        reinterpret_cast<uint32_t*>(sOnes)[i] = 0x38383838u;  // e4m3 1.0; every byte equal, so no swizzle to honour
+        reinterpret_cast<uint32_t*>(sOnes)[i] = 0x3C003C00u;  // fp16 1.0; every element equal, so no swizzle to honour
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
@@ -233,12 +237,13 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
             // constant high half and a low half that only needs 32-bit adds.
             const uint64_t qd = make_desc_kmajor<SW>(smem_u32(sQ));
             const uint64_t kd = make_desc_kmajor<SW>(smem_u32(sKV));
-            const uint64_t vd = make_desc_mnmajor<SW>(smem_u32(sKV + Cfg::kKBytes), 8 * SW);
+            // V16: N-major, 128-byte rows (64 halves of D) per key; a second N atom (D = 128) lies kV16Bytes / 2 further
+            const uint64_t vd = make_desc_mnmajor<128>(smem_u32(sV16), Cfg::kV16Bytes / 2);
             const uint64_t pd = make_desc_kmajor<128>(smem_u32(sP));
             const uint64_t od = make_desc_kmajor<128>(smem_u32(sOnes));
             const uint32_t q_lo = desc_lo(qd), k_lo0 = desc_lo(kd), v_lo0 = desc_lo(vd), p_lo0 = desc_lo(pd), o_lo = desc_lo(od);
             const uint32_t qk_hi = desc_hi(qd), v_hi = desc_hi(vd), p_hi = desc_hi(pd);
-            constexpr uint32_t kStageStep = Cfg::kStageBytes >> 4, kPBufStep = (2 * BQ * BKV) >> 4, kPPartStep = (BQ * BKV) >> 4;
+            constexpr uint32_t kStageStep = Cfg::kStageBytes >> 4, kPAtomStep = (BQ * 128) >> 4, kOnesAtomStep = (16 * 128) >> 4;
             const uint32_t idesc_qk = args.idesc_qk, idesc_pv = args.idesc_pv, idesc_sum = args.idesc_sum;
             const uint32_t s_full_b = smem_u32(s_full), o_full_b = smem_u32(o_full);
             const uint32_t q_empty_b = smem_u32(q_empty);
@@ -283,20 +288,21 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                     // O (+)= P.V and row sums (+)= P.1, accumulated in TMEM over the item's key blocks; P = leading
                     // part + remainder.  Per 32 keys: P advances 32 bytes inside its 128-byte rows, V advances 32
                     // rows of D bytes.
-                    const uint32_t v_lo = v_lo0 + sj * kStageStep, p_lo = p_lo0 + sj * kPBufStep;
+                    // 16 keys per instruction: P advances 32 bytes inside its 128-byte rows (next K atom after four),
+                    // V16 advances 16 rows of 128 bytes, the ones tile like P
                     if (j == 0) {
-                        tc_mma_f8(tmem_o, desc_join(p_lo, p_hi), desc_join(v_lo, v_hi), idesc_pv, 0);
-                        tc_mma_f8(tmem_l, desc_join(p_lo, p_hi), desc_join(o_lo, p_hi), idesc_sum, 0);
+                        tc_mma_f16(tmem_o, desc_join(p_lo0, p_hi), desc_join(v_lo0, v_hi), idesc_pv, 0);
+                        tc_mma_f16(tmem_l, desc_join(p_lo0, p_hi), desc_join(o_lo, p_hi), idesc_sum, 0);
                     } else {
-                        tc_mma_f8_acc(tmem_o, desc_join(p_lo, p_hi), desc_join(v_lo, v_hi), idesc_pv);
-                        tc_mma_f8_acc(tmem_l, desc_join(p_lo, p_hi), desc_join(o_lo, p_hi), idesc_sum);
+                        tc_mma_f16_acc(tmem_o, desc_join(p_lo0, p_hi), desc_join(v_lo0, v_hi), idesc_pv);
+                        tc_mma_f16_acc(tmem_l, desc_join(p_lo0, p_hi), desc_join(o_lo, p_hi), idesc_sum);
                     }
 #pragma unroll
-                    for (int i = 1; i < 2 * (BKV / 32); ++i) {
-                        const int part = i / (BKV / 32), k = i % (BKV / 32);
-                        const uint32_t pl = p_lo + part * kPPartStep + 2 * k;
-                        tc_mma_f8_acc(tmem_o, desc_join(pl, p_hi), desc_join(v_lo + ((k * 32 * D) >> 4), v_hi), idesc_pv);
-                        tc_mma_f8_acc(tmem_l, desc_join(pl, p_hi), desc_join(o_lo + 2 * k, p_hi), idesc_sum);
+                    for (int k = 1; k < BKV / 16; ++k) {
+                        const uint32_t pl = p_lo0 + (k / 4) * kPAtomStep + 2 * (k % 4);
+                        tc_mma_f16_acc(tmem_o, desc_join(pl, p_hi), desc_join(v_lo0 + ((k * 16 * 128) >> 4), v_hi), idesc_pv);
+                        tc_mma_f16_acc(tmem_l, desc_join(pl, p_hi),
+                                       desc_join(o_lo + (k / 4) * kOnesAtomStep + 2 * (k % 4), p_hi), idesc_sum);
                     }
                     tc_commit(o_full_b);  // "P.V of block x done": P is free, O may be touched
                     tc_commit(smem_u32(kv_empty + sj));
@@ -430,48 +436,8 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
             const float shift = ((m == -INFINITY) ? 0.f : m) - kPShift;
             const float ecs = edge ? 1.f : cs;  // masked blocks hold scores already scaled (and masked) in r
 
-            // P is double-buffered: this block's buffer was last read by the P.V of block j-2
-            while (pv_waited < gj - 1) {
-                if (!mbar_wait_bounded(smem_u32(o_full), pv_waited & 1)) {
-                    ok = false;
-                    break;
-                }
-                ++pv_waited;
-            }
-            if (!__all_sync(0xffffffffu, ok)) {
-                if (lane == 0) record_timeout(args.status, 0x1700u);
-                ok = false;
-                break;
-            }
-
-            uint8_t* prow = sP + (gj & 1) * 2 * BQ * BKV + row * 128;
-            const float nshift = -shift;
-#pragma unroll
-            for (int c = 0; c < HC / 32; ++c) {
-                uint32_t w[8], wl[8];
-#pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    const int i0 = c * 32 + 4 * g;
-                    // two keys per instruction from here on: exp2, leading e4m3 part, exact remainder, its e4m3
-                    const uint32_t pa = ex2_f16x2(pack_f16x2(fmaf(__uint_as_float(r[i0]), ecs, nshift),
-                                                             fmaf(__uint_as_float(r[i0 + 1]), ecs, nshift)));
-                    const uint32_t pb = ex2_f16x2(pack_f16x2(fmaf(__uint_as_float(r[i0 + 2]), ecs, nshift),
-                                                             fmaf(__uint_as_float(r[i0 + 3]), ecs, nshift)));
-                    const uint32_t ha = e4m3x2_of_f16x2(pa), hb = e4m3x2_of_f16x2(pb);
-                    const uint32_t la = e4m3x2_of_f16x2(sub_f16x2(pa, f16x2_of_e4m3x2(ha)));
-                    const uint32_t lb = e4m3x2_of_f16x2(sub_f16x2(pb, f16x2_of_e4m3x2(hb)));
-                    w[g] = ha | (hb << 16);
-                    wl[g] = la | (lb << 16);
-                }
-                const int cc = 2 * c;  // 16-byte chunk index inside the 128-byte row
-                const int o0 = (cc ^ (row & 7)) << 4, o1 = ((cc + 1) ^ (row & 7)) << 4;
-                *reinterpret_cast<uint4*>(prow + o0) = make_uint4(w[0], w[1], w[2], w[3]);
-                *reinterpret_cast<uint4*>(prow + o1) = make_uint4(w[4], w[5], w[6], w[7]);
-                *reinterpret_cast<uint4*>(prow + BQ * BKV + o0) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
-                *reinterpret_cast<uint4*>(prow + BQ * BKV + o1) = make_uint4(wl[4], wl[5], wl[6], wl[7]);
-            }
-            // catch up with the "P.V done" barrier before the issuer can complete another phase: a waiter must
-            // never fall two phases behind a parity-tracked mbarrier (block j-1's product is long finished here)
+            // P and V16 are single buffers: the P.V of the previous block must have read them.  (It was issued at
+            // the end of that block's softmax and has had this block's score load and row maximum to finish.)
             while (pv_waited < gj) {
                 if (!mbar_wait_bounded(smem_u32(o_full), pv_waited & 1)) {
                     ok = false;
@@ -479,10 +445,54 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                 }
                 ++pv_waited;
             }
+            // this block's V tile has landed (the MMA thread waited for the same barrier before Q.K^T)
+            if (ok && !mbar_wait_bounded(smem_u32(kv_full + (gj & 1)), (gj >> 1) & 1)) ok = false;
             if (!__all_sync(0xffffffffu, ok)) {
-                if (lane == 0) record_timeout(args.status, 0x1b00u);
+                if (lane == 0) record_timeout(args.status, 0x1700u);
                 ok = false;
                 break;
+            }
+
+            // ---- V: fp8 codes -> halves (exact), key `row` of the block per thread, into the N-major fp16 tile ----
+            {
+                const uint8_t* vsrc = sKV + (gj & 1) * Cfg::kStageBytes + Cfg::kKBytes + row * D;
+                const int sw_in = (D == 64) ? ((row >> 1) & 3) : (row & 7);  // TMA swizzle of the D-byte source rows
+#pragma unroll
+                for (int c = 0; c < D / 16; ++c) {
+                    const uint4 in = *reinterpret_cast<const uint4*>(vsrc + ((c ^ sw_in) << 4));
+                    const uint32_t wds[4] = {in.x, in.y, in.z, in.w};
+                    uint32_t h[8];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        h[2 * k] = (args.v_kind == DF8_E4M3) ? f16x2_of_e4m3x2(wds[k] & 0xFFFFu) : f16x2_of_e5m2x2(wds[k] & 0xFFFFu);
+                        h[2 * k + 1] = (args.v_kind == DF8_E4M3) ? f16x2_of_e4m3x2(wds[k] >> 16) : f16x2_of_e5m2x2(wds[k] >> 16);
+                    }
+                    // 16 codes -> 32 bytes = chunks 2c, 2c+1 of the key's 128-byte rows (one row per 64 values of D)
+                    uint8_t* vrow = sV16 + ((2 * c) >> 3) * (Cfg::kV16Bytes / 2) + row * 128;
+                    const int k0c = (2 * c) & 7;
+                    *reinterpret_cast<uint4*>(vrow + ((k0c ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4*>(vrow + (((k0c + 1) ^ (row & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+                }
+            }
+
+            // ---- P = 2^(t - m + kPShift) as halves, 64 keys (128 bytes) per K atom ----
+            uint8_t* prow = sP + row * 128;
+            const float nshift = -shift;
+#pragma unroll
+            for (int c = 0; c < HC / 32; ++c) {
+                uint32_t w[16];
+#pragma unroll
+                for (int g = 0; g < 16; ++g) {
+                    const int i0 = c * 32 + 2 * g;
+                    w[g] = ex2_f16x2(pack_f16x2(fmaf(__uint_as_float(r[i0]), ecs, nshift),
+                                                fmaf(__uint_as_float(r[i0 + 1]), ecs, nshift)));
+                }
+                uint8_t* patom = prow + (c >> 1) * (BQ * 128);
+                const int cb = (c & 1) * 4;  // 32 keys = 64 bytes = four 16-byte chunks
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    *reinterpret_cast<uint4*>(patom + (((cb + k) ^ (row & 7)) << 4)) =
+                        make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
             }
 
             tc_fence_before_sync();  // orders the O rescale (if any) before the issuer's next P.V
@@ -619,8 +629,9 @@ extern "C" df8_status df8_attention_fp8(const uint8_t* qkv_codes, df8_kind kind,
     a.mask_mode = mask_mode;
     a.mask_b = mask_b;
     a.idesc_qk = ptx::make_idesc_f8(BQ, BKV, int(kind), int(kind));
-    a.idesc_pv = ptx::make_idesc_f8(BQ, D, DF8_E4M3, int(kind), 0, 1);
-    a.idesc_sum = ptx::make_idesc_f8(BQ, 16, DF8_E4M3, DF8_E4M3);
+    a.v_kind = int(kind);
+    a.idesc_pv = ptx::make_idesc_f16(BQ, D, 0, 1);
+    a.idesc_sum = ptx::make_idesc_f16(BQ, 16);
     a.status = status_ptr;
     a.n_qblk = (T + BQ - 1) / BQ;
     const long items = long(a.n_qblk) * H * B;

@@ -128,6 +128,25 @@ __device__ __forceinline__ void tc_mma_f8_acc(uint32_t tmem_d, uint64_t desc_a, 
         : "memory");
 }
 
+// The same for 16-bit float operands (K = 16 per instruction).
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16_acc(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.eq.u32 p, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc)
+        : "memory");
+}
+
 // A shared-memory descriptor as two 32-bit halves.  Walking a tile or a stage ring only changes the start
 // address in the low half (16-byte units, no carry out of its 14-bit field), so issue loops keep the high
 // half in a register and do 32-bit adds on the low one.
@@ -260,6 +279,12 @@ __host__ __device__ constexpr uint32_t make_idesc_f8(int m, int n, int kind_a, i
            | (uint32_t(b_mn_major) << 16)  // B major
            | (uint32_t(n >> 3) << 17)      // N / 8
            | (uint32_t(m >> 4) << 24);     // M / 16
+}
+
+// Instruction descriptor for kind::f16 with fp16 operands (format code 0) and fp32 accumulation.
+__host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n, int a_mn_major = 0, int b_mn_major = 0) {
+    return (1u << 4) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) | (uint32_t(n >> 3) << 17) |
+           (uint32_t(m >> 4) << 24);
 }
 
 // 32 lanes x 32 columns of 32-bit TMEM data: thread i of the warp receives lane (base_lane + i),

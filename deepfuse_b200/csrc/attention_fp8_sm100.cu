@@ -76,10 +76,10 @@ struct AttnCfg {
     static constexpr int kStageBytes = 2 * kKBytes;  // K then V
     static constexpr int kStages = 2;
     static constexpr int kPBytes = 2 * BQ * 128;      // fp16 P [128 queries][128 keys]: two K atoms of 64 keys (128 B rows)
-    static constexpr int kV16Bytes = BKV * D * 2;     // the block's V widened to fp16: [keys][D], D/64 atoms of 128 B rows
+    static constexpr int kV16Bytes = BKV * D * 2;     // a block's V widened to fp16: [keys][D], D/64 atoms of 128 B rows
     static constexpr int kOnesBytes = 2 * 16 * 128;   // 16 x 128 tile of fp16 ones: B operand of the row-sum product
     static constexpr int kBarBytes = 128;  // mbarriers and the TMEM base slot
-    static constexpr int kUsedBytes = kQBytes + kStages * kStageBytes + kPBytes + kV16Bytes + kOnesBytes + kBarBytes + 1024;
+    static constexpr int kUsedBytes = kQBytes + kStages * kStageBytes + kPBytes + 2 * kV16Bytes + kOnesBytes + kBarBytes + 1024;
     // pad the request so that at most two CTAs share an SM: each allocates 256 of the 512 TMEM columns
     static constexpr int kSmemBytes = kUsedBytes < 110 * 1024 ? 110 * 1024 : kUsedBytes;
     // S: columns [0,128), O: [128, 128+D), row sum: [128+D, 128+D+16) (sixteen identical copies)
@@ -136,7 +136,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
     uint8_t* sKV = sQ + Cfg::kQBytes;
     uint8_t* sP = sKV + Cfg::kStages * Cfg::kStageBytes;
     uint8_t* sV16 = sP + Cfg::kPBytes;
-    uint8_t* sOnes = sV16 + Cfg::kV16Bytes;
+    uint8_t* sOnes = sV16 + 2 * Cfg::kV16Bytes;  // two V16 buffers: block x uses buffer x & 1
     uint64_t* bars = reinterpret_cast<uint64_t*>(sOnes + Cfg::kOnesBytes);
     uint64_t* q_full = bars;
     uint64_t* kv_full = bars + 1;   // [2]
@@ -244,6 +244,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
             const uint32_t q_lo = desc_lo(qd), k_lo0 = desc_lo(kd), v_lo0 = desc_lo(vd), p_lo0 = desc_lo(pd), o_lo = desc_lo(od);
             const uint32_t qk_hi = desc_hi(qd), v_hi = desc_hi(vd), p_hi = desc_hi(pd);
             constexpr uint32_t kStageStep = Cfg::kStageBytes >> 4, kPAtomStep = (BQ * 128) >> 4, kOnesAtomStep = (16 * 128) >> 4;
+            constexpr uint32_t kV16Step = Cfg::kV16Bytes >> 4;
             const uint32_t idesc_qk = args.idesc_qk, idesc_pv = args.idesc_pv, idesc_sum = args.idesc_sum;
             const uint32_t s_full_b = smem_u32(s_full), o_full_b = smem_u32(o_full);
             const uint32_t q_empty_b = smem_u32(q_empty);
@@ -290,17 +291,18 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                     // rows of D bytes.
                     // 16 keys per instruction: P advances 32 bytes inside its 128-byte rows (next K atom after four),
                     // V16 advances 16 rows of 128 bytes, the ones tile like P
+                    const uint32_t v_lo = v_lo0 + sj * kV16Step;
                     if (j == 0) {
-                        tc_mma_f16(tmem_o, desc_join(p_lo0, p_hi), desc_join(v_lo0, v_hi), idesc_pv, 0);
+                        tc_mma_f16(tmem_o, desc_join(p_lo0, p_hi), desc_join(v_lo, v_hi), idesc_pv, 0);
                         tc_mma_f16(tmem_l, desc_join(p_lo0, p_hi), desc_join(o_lo, p_hi), idesc_sum, 0);
                     } else {
-                        tc_mma_f16_acc(tmem_o, desc_join(p_lo0, p_hi), desc_join(v_lo0, v_hi), idesc_pv);
+                        tc_mma_f16_acc(tmem_o, desc_join(p_lo0, p_hi), desc_join(v_lo, v_hi), idesc_pv);
                         tc_mma_f16_acc(tmem_l, desc_join(p_lo0, p_hi), desc_join(o_lo, p_hi), idesc_sum);
                     }
 #pragma unroll
                     for (int k = 1; k < BKV / 16; ++k) {
                         const uint32_t pl = p_lo0 + (k / 4) * kPAtomStep + 2 * (k % 4);
-                        tc_mma_f16_acc(tmem_o, desc_join(pl, p_hi), desc_join(v_lo0 + ((k * 16 * 128) >> 4), v_hi), idesc_pv);
+                        tc_mma_f16_acc(tmem_o, desc_join(pl, p_hi), desc_join(v_lo + ((k * 16 * 128) >> 4), v_hi), idesc_pv);
                         tc_mma_f16_acc(tmem_l, desc_join(pl, p_hi),
                                        desc_join(o_lo + (k / 4) * kOnesAtomStep + 2 * (k % 4), p_hi), idesc_sum);
                     }
@@ -345,6 +347,44 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
         for (int j = 0; j < n_kv; ++j) {
             const int gj = g + j;
             const int k0 = j * BKV;
+            // ---- V: fp8 codes -> halves (exact), key `row` of the block per thread, into the N-major fp16 tile.
+            // Done first: the V tile lands with the K tile, before S can be ready, and V16 buffer gj & 1 was last read
+            // by the P.V of block gj - 2, which the previous block's wait (before its P stores) has seen complete ----
+            if (!mbar_wait_bounded(smem_u32(kv_full + (gj & 1)), (gj >> 1) & 1)) {
+                if (lane == 0) record_timeout(args.status, 0x1c00u);
+                ok = false;
+                break;
+            }
+            {
+                const uint8_t* vsrc = sKV + (gj & 1) * Cfg::kStageBytes + Cfg::kKBytes + row * D;
+                uint8_t* vdst = sV16 + (gj & 1) * Cfg::kV16Bytes + row * 128;
+                const int sw_in = (D == 64) ? ((row >> 1) & 3) : (row & 7);  // TMA swizzle of the D-byte source rows
+                const bool e4m3 = args.v_kind == DF8_E4M3;
+#pragma unroll
+                for (int c = 0; c < D / 16; ++c) {
+                    const uint4 in = *reinterpret_cast<const uint4*>(vsrc + ((c ^ sw_in) << 4));
+                    const uint32_t wds[4] = {in.x, in.y, in.z, in.w};
+                    uint32_t h[8];
+                    if (e4m3) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            h[2 * k] = f16x2_of_e4m3x2(wds[k] & 0xFFFFu);
+                            h[2 * k + 1] = f16x2_of_e4m3x2(wds[k] >> 16);
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            h[2 * k] = f16x2_of_e5m2x2(wds[k] & 0xFFFFu);
+                            h[2 * k + 1] = f16x2_of_e5m2x2(wds[k] >> 16);
+                        }
+                    }
+                    // 16 codes -> 32 bytes = chunks 2c, 2c+1 of the key's 128-byte rows (one row per 64 values of D)
+                    uint8_t* vrow = vdst + ((2 * c) >> 3) * (Cfg::kV16Bytes / 2);
+                    const int k0c = (2 * c) & 7;
+                    *reinterpret_cast<uint4*>(vrow + ((k0c ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4*>(vrow + (((k0c + 1) ^ (row & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+                }
+            }
             if (!mbar_wait_bounded(smem_u32(s_full), gj & 1)) {
                 if (lane == 0) record_timeout(args.status, 0x1500u);
                 ok = false;
@@ -436,8 +476,15 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
             const float shift = ((m == -INFINITY) ? 0.f : m) - kPShift;
             const float ecs = edge ? 1.f : cs;  // masked blocks hold scores already scaled (and masked) in r
 
-            // P and V16 are single buffers: the P.V of the previous block must have read them.  (It was issued at
-            // the end of that block's softmax and has had this block's score load and row maximum to finish.)
+            // ---- P = 2^(t - m + kPShift) as halves: all 64 packed results first, the stores after the wait below ----
+            const float nshift = -shift;
+            uint32_t w[HC / 2];
+#pragma unroll
+            for (int g = 0; g < HC / 2; ++g)
+                w[g] = ex2_f16x2(pack_f16x2(fmaf(__uint_as_float(r[2 * g]), ecs, nshift),
+                                            fmaf(__uint_as_float(r[2 * g + 1]), ecs, nshift)));
+            // P is a single buffer: the P.V of the previous block must have read it.  That product was issued at
+            // the end of the previous block's softmax and has had this whole block's arithmetic to finish.
             while (pv_waited < gj) {
                 if (!mbar_wait_bounded(smem_u32(o_full), pv_waited & 1)) {
                     ok = false;
@@ -445,54 +492,21 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
                 }
                 ++pv_waited;
             }
-            // this block's V tile has landed (the MMA thread waited for the same barrier before Q.K^T)
-            if (ok && !mbar_wait_bounded(smem_u32(kv_full + (gj & 1)), (gj >> 1) & 1)) ok = false;
             if (!__all_sync(0xffffffffu, ok)) {
                 if (lane == 0) record_timeout(args.status, 0x1700u);
                 ok = false;
                 break;
             }
-
-            // ---- V: fp8 codes -> halves (exact), key `row` of the block per thread, into the N-major fp16 tile ----
-            {
-                const uint8_t* vsrc = sKV + (gj & 1) * Cfg::kStageBytes + Cfg::kKBytes + row * D;
-                const int sw_in = (D == 64) ? ((row >> 1) & 3) : (row & 7);  // TMA swizzle of the D-byte source rows
-#pragma unroll
-                for (int c = 0; c < D / 16; ++c) {
-                    const uint4 in = *reinterpret_cast<const uint4*>(vsrc + ((c ^ sw_in) << 4));
-                    const uint32_t wds[4] = {in.x, in.y, in.z, in.w};
-                    uint32_t h[8];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        h[2 * k] = (args.v_kind == DF8_E4M3) ? f16x2_of_e4m3x2(wds[k] & 0xFFFFu) : f16x2_of_e5m2x2(wds[k] & 0xFFFFu);
-                        h[2 * k + 1] = (args.v_kind == DF8_E4M3) ? f16x2_of_e4m3x2(wds[k] >> 16) : f16x2_of_e5m2x2(wds[k] >> 16);
-                    }
-                    // 16 codes -> 32 bytes = chunks 2c, 2c+1 of the key's 128-byte rows (one row per 64 values of D)
-                    uint8_t* vrow = sV16 + ((2 * c) >> 3) * (Cfg::kV16Bytes / 2) + row * 128;
-                    const int k0c = (2 * c) & 7;
-                    *reinterpret_cast<uint4*>(vrow + ((k0c ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
-                    *reinterpret_cast<uint4*>(vrow + (((k0c + 1) ^ (row & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
-                }
-            }
-
-            // ---- P = 2^(t - m + kPShift) as halves, 64 keys (128 bytes) per K atom ----
+            // 64 keys (128 bytes) per K atom; 32 keys = 64 bytes = four 16-byte chunks
             uint8_t* prow = sP + row * 128;
-            const float nshift = -shift;
 #pragma unroll
             for (int c = 0; c < HC / 32; ++c) {
-                uint32_t w[16];
-#pragma unroll
-                for (int g = 0; g < 16; ++g) {
-                    const int i0 = c * 32 + 2 * g;
-                    w[g] = ex2_f16x2(pack_f16x2(fmaf(__uint_as_float(r[i0]), ecs, nshift),
-                                                fmaf(__uint_as_float(r[i0 + 1]), ecs, nshift)));
-                }
                 uint8_t* patom = prow + (c >> 1) * (BQ * 128);
-                const int cb = (c & 1) * 4;  // 32 keys = 64 bytes = four 16-byte chunks
+                const int cb = (c & 1) * 4;
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
                     *reinterpret_cast<uint4*>(patom + (((cb + k) ^ (row & 7)) << 4)) =
-                        make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+                        make_uint4(w[16 * c + 4 * k], w[16 * c + 4 * k + 1], w[16 * c + 4 * k + 2], w[16 * c + 4 * k + 3]);
             }
 
             tc_fence_before_sync();  // orders the O rescale (if any) before the issuer's next P.V

@@ -55,6 +55,8 @@ constexpr int kOutNone = 4;     // max|out| only
 // GELU) with nothing to store or little, and run four per quarter so that each SM sub-partition has four
 // warps to interleave.
 __host__ __device__ constexpr int epi_warps(int mode) { return mode >= kOutE4M3 ? 16 : 8; }
+// per-warp staging bytes of the fp8 / amax modes: the bias slice (64 floats) and, for fp8 output, the codes tile
+__host__ __device__ constexpr int direct_staging_bytes(int mode) { return mode == kOutNone ? 256 : 256 + 2048; }
 __host__ __device__ constexpr int gemm_threads(int mode) { return 64 + 32 * epi_warps(mode); }
 
 struct GemmArgs {
@@ -79,7 +81,8 @@ struct GemmCfg {
     static constexpr int kBBytes = BN * BK;
     static constexpr int kStageBytes = kABytes + kBBytes;
     // fp32 modes: a transpose buffer per epilogue warp; fp8 / amax modes: only each warp's bias slice
-    static constexpr int kStagingBytes = MODE >= kOutE4M3 ? epi_warps(MODE) * 64 * 4 : kEpiWarps * kStagingFloatsPerWarp * 4;
+    static constexpr int kStagingBytes =
+        MODE >= kOutE4M3 ? epi_warps(MODE) * direct_staging_bytes(MODE) : kEpiWarps * kStagingFloatsPerWarp * 4;
     static constexpr int kBarBytes = 256;
     static constexpr int kSmemBytes = STAGES * kStageBytes + kStagingBytes + kBarBytes + 1024;
     static constexpr int kTmemCols = 2 * BN;
@@ -219,9 +222,14 @@ __device__ __forceinline__ void store_chunk_f32(const float* stg, int lane, int 
 
 // KIND: DF8_E4M3 / DF8_E5M2 to emit codes, -1 to only reduce max|out|.
 // `sbias`: the chunk's 32 bias values in shared memory (zeros without a bias), or null to read a.bias.
-template <int KIND>
+// Codes: the thread's 32 bytes (one row of the chunk) are parked as pieces 2j, 2j+1 of its row in the warp's
+// staging tile `stg` ([32 rows][PP pieces of 16 bytes], pieces XOR-swizzled so that neither these writes nor the
+// row-segment reads of store_staged_codes conflict); storing them from here, 16 bytes per row and instruction,
+// cost 6-10 us per pass (measured): the stores must leave as whole row segments.
+template <int KIND, int PP = 2>
 __device__ __forceinline__ void direct_chunk(const uint32_t (&r)[32], int grow, int col0, const GemmArgs& a,
-                                             float alpha, float out_q, float& amax, const float* sbias = nullptr) {
+                                             float alpha, float out_q, float& amax, const float* sbias = nullptr,
+                                             uint8_t* stg = nullptr, int j = 0) {
     const bool row_ok = grow < a.M;
     uint32_t w[8];
 #pragma unroll
@@ -247,11 +255,28 @@ __device__ __forceinline__ void direct_chunk(const uint32_t (&r)[32], int grow, 
         }
     }
     if constexpr (KIND >= 0) {
-        if (row_ok) {
-            uint4* dst = reinterpret_cast<uint4*>(a.out_codes + size_t(grow) * a.N + col0);
-            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-        }
+        const int lane = threadIdx.x & 31;
+        const int sw = PP == 4 ? ((lane >> 1) & 3) : ((lane >> 2) & 1);
+        uint8_t* srow = stg + lane * (PP * 16);
+        *reinterpret_cast<uint4*>(srow + (((2 * j) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(srow + (((2 * j + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    (void)row_ok;
+}
+
+// The warp's staged codes ([32 rows][PP x 16 bytes], columns col0 .. col0 + 16 PP) to global memory: PP lanes cover
+// one row's contiguous PP x 16 bytes, 32 / PP rows per instruction.
+template <int PP>
+__device__ __forceinline__ void store_staged_codes(const uint8_t* stg, int lane, int row0, int col0, const GemmArgs& a) {
+    constexpr int kRowsPerInstr = 32 / PP;
+    const int p = lane % PP;
+#pragma unroll
+    for (int it = 0; it < PP; ++it) {
+        const int rr = it * kRowsPerInstr + lane / PP;
+        const int sw = PP == 4 ? ((rr >> 1) & 3) : ((rr >> 2) & 1);
+        const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * (PP * 16) + ((p ^ sw) << 4));
+        if (row0 + rr < a.M && col0 + 16 * p < a.N)
+            *reinterpret_cast<uint4*>(a.out_codes + size_t(row0 + rr) * a.N + col0 + 16 * p) = v;
     }
 }
 
@@ -414,10 +439,14 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
                 constexpr int kParts = EW / 4;
                 constexpr int kCh = BN / (32 * kParts);
                 const int part = e >> 2;
-                float* sb = staging + e * (32 * kCh);
+                // this warp's columns: kCh adjacent chunks, so that its codes of a row are one contiguous segment
+                const int colw = n0 + 32 * kCh * part;
+                uint8_t* wst = reinterpret_cast<uint8_t*>(staging) + e * direct_staging_bytes(MODE);
+                float* sb = reinterpret_cast<float*>(wst);
+                uint8_t* codes_tile = wst + 256;
 #pragma unroll
                 for (int j = 0; j < kCh; ++j) {
-                    const int col = n0 + 32 * (part + kParts * j) + lane;
+                    const int col = colw + 32 * j + lane;
                     sb[j * 32 + lane] = (args.bias && col < args.N) ? __ldg(args.bias + col) : 0.f;
                 }
                 __syncwarp();
@@ -429,7 +458,7 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
                 uint32_t r[kCh][32];
 #pragma unroll
                 for (int j = 0; j < kCh; ++j)
-                    if (n0 + 32 * (part + kParts * j) < args.N) tmem_ld_32x32(taddr + 32 * (part + kParts * j), r[j]);
+                    if (colw + 32 * j < args.N) tmem_ld_32x32(taddr + 32 * (kCh * part + j), r[j]);
                 tmem_ld_wait();
                 tc_fence_before_sync();
                 __syncwarp();
@@ -437,10 +466,15 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
                 const int grow = row0 + lane;
 #pragma unroll
                 for (int j = 0; j < kCh; ++j) {
-                    const int col0 = n0 + 32 * (part + kParts * j);
-                    if (col0 < args.N) direct_chunk<KIND>(r[j], grow, col0, args, alpha, out_q, amax, sb + j * 32);
+                    const int col0 = colw + 32 * j;
+                    if (col0 < args.N)
+                        direct_chunk<KIND, 2 * kCh>(r[j], grow, col0, args, alpha, out_q, amax, sb + j * 32, codes_tile, j);
                 }
-                __syncwarp();  // every lane is done with the bias slice before the next tile overwrites it
+                __syncwarp();  // the codes tile is complete (and every lane is done with the bias slice)
+                if constexpr (KIND >= 0) {
+                    store_staged_codes<2 * kCh>(codes_tile, lane, row0, colw, args);
+                    __syncwarp();  // before the next tile overwrites the staging
+                }
                 continue;
             }
             float4 rs[8];  // residual of the chunk about to be stored, loaded one chunk ahead
@@ -670,10 +704,14 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
                 constexpr int kParts = EW / 4;
                 constexpr int kCh = BN / (32 * kParts);
                 const int part = e >> 2;
-                float* sb = staging + e * (32 * kCh);
+                // this warp's columns: kCh adjacent chunks, so that its codes of a row are one contiguous segment
+                const int colw = n0 + 32 * kCh * part;
+                uint8_t* wst = reinterpret_cast<uint8_t*>(staging) + e * direct_staging_bytes(MODE);
+                float* sb = reinterpret_cast<float*>(wst);
+                uint8_t* codes_tile = wst + 256;
 #pragma unroll
                 for (int j = 0; j < kCh; ++j) {
-                    const int col = n0 + 32 * (part + kParts * j) + lane;
+                    const int col = colw + 32 * j + lane;
                     sb[j * 32 + lane] = (args.bias && col < args.N) ? __ldg(args.bias + col) : 0.f;
                 }
                 __syncwarp();
@@ -685,7 +723,7 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
                 uint32_t r[kCh][32];
 #pragma unroll
                 for (int j = 0; j < kCh; ++j)
-                    if (n0 + 32 * (part + kParts * j) < args.N) tmem_ld_32x32(taddr + 32 * (part + kParts * j), r[j]);
+                    if (colw + 32 * j < args.N) tmem_ld_32x32(taddr + 32 * (kCh * part + j), r[j]);
                 tmem_ld_wait();
                 tc_fence_before_sync();
                 __syncwarp();
@@ -693,10 +731,15 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
                 const int grow = row0 + lane;
 #pragma unroll
                 for (int j = 0; j < kCh; ++j) {
-                    const int col0 = n0 + 32 * (part + kParts * j);
-                    if (col0 < args.N) direct_chunk<KIND>(r[j], grow, col0, args, alpha, out_q, amax, sb + j * 32);
+                    const int col0 = colw + 32 * j;
+                    if (col0 < args.N)
+                        direct_chunk<KIND, 2 * kCh>(r[j], grow, col0, args, alpha, out_q, amax, sb + j * 32, codes_tile, j);
                 }
                 __syncwarp();
+                if constexpr (KIND >= 0) {
+                    store_staged_codes<2 * kCh>(codes_tile, lane, row0, colw, args);
+                    __syncwarp();
+                }
                 continue;
             }
             float4 rs[8];
@@ -815,7 +858,7 @@ df8_status launch_gemm_bn(bool wide, const CUtensorMap& ta, const CUtensorMap& t
     // ring depth: whatever fits beside the epilogue's staging.  One K block of operands takes ~1300 cycles to
     // arrive from L2 and ~512 (256 at BN = 128) to consume, so three 48 KB stages leave the tensor core waiting;
     // the fp8 / amax modes need no transpose buffer and get a deeper ring.
-    if constexpr (MODE >= kOutE4M3)
+    if constexpr (MODE == kOutNone)
         return wide ? launch_gemm<256, 4, MODE>(ta, tw, args, grid, st) : launch_gemm<128, 6, MODE>(ta, tw, args, grid, st);
     else
         return wide ? launch_gemm<256, 3, MODE>(ta, tw, args, grid, st) : launch_gemm<128, 5, MODE>(ta, tw, args, grid, st);

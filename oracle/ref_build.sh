@@ -1,6 +1,6 @@
 #!/usr/bin/env bash
-# Compiles the upstream project's own fp32 layers for sm_100a, from its sources under $REF (default
-# /root/reference), into oracle/_ref/libdnn_ref.so.  Only this wrapper (ref_wrap.cu) is ours; no upstream source
+# Compiles the upstream project's own fp32 layers for sm_100a, from its sources under $REF (the checkout of the
+# upstream project), into oracle/_ref/libdnn_ref.so.  Only this wrapper (ref_wrap.cu) is ours; no upstream source
 # is copied into the repository and upstream's CMake build is not used (it needs network access for GoogleTest,
 # and TBB for one app).  Output goes to oracle/_ref/ only, which is git-ignored.
 set -euo pipefail

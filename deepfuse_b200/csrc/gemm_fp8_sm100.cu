@@ -907,11 +907,19 @@ df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uin
     // ~85 bytes per cycle to an SM: a 128 x 128 K block (two loads, 32 KB) therefore takes ~530 cycles although
     // its MMAs need 256, about as long as a 128 x 256 one (48 KB, MMAs 512).  So narrow tiles only pay when
     // they save whole rounds of the persistent grid.
+    // The fp32 modes add their epilogue to the picture: a 32 x 32 chunk takes a warp ~2000 cycles to stage and
+    // store (measured), i.e. ~31 cycles per tile column with eight warps, which exceeds the main loop at small K.
     auto rounds = [&](int bn) {
         const long tiles = long((M + BM - 1) / BM) * ((N + bn - 1) / bn);
         return double((tiles + sms - 1) / sms);
     };
-    const bool wide = N > 128 && rounds(256) * 1.0 <= rounds(128) * 0.94;
+    const double kloop = double((K + BK - 1) / BK) * 540.0;
+    auto tile_cycles = [&](int bn) {
+        const double main_loop = bn == 256 ? kloop : 0.94 * kloop;
+        const double epilogue = (mode == kOutF32Vec || mode == kOutF32) ? 31.0 * bn : 0.0;
+        return main_loop > epilogue ? main_loop : epilogue;
+    };
+    const bool wide = N > 128 && rounds(256) * tile_cycles(256) <= rounds(128) * tile_cycles(128);
     const int bn = wide ? 256 : 128;
     const long tiles = long((M + BM - 1) / BM) * ((N + bn - 1) / bn);
     const int grid = int(tiles < sms ? tiles : sms);

@@ -365,9 +365,12 @@ class Gpt2Workload:
         self.T = self.c["ctx"]
         self.metric = "GPT-2 fp8 forward tokens/s"
         self.dtype = f"{self.c['act']} activations x e4m3 weights -> f32 accumulate"
-        # embedding; per layer: LN+quantise 2, QKV GEMM 2 passes, attention, quantise, out GEMM, LN+quantise 2,
-        # FC1 GEMM 2 passes, FC2 GEMM; head: amax, quantise, GEMM
-        self.kernels_per_step = 1 + 12 * self.c["layers"] + 3
+        # embedding; per layer: LN+quantise (one cooperative kernel when the activation fits the GPU's shared
+        # memory, else two), QKV GEMM 2 passes, attention, quantise, out GEMM, LN+quantise, FC1 GEMM 2 passes,
+        # FC2 GEMM; head: amax, quantise, GEMM
+        rows, C = self.B * self.T, self.c["hidden"]
+        ln = 1 if (C <= 1024 and rows >= 1024 and rows * C * 4 <= 148 * 200 * 1024) else 2
+        self.kernels_per_step = 1 + (8 + 2 * ln) * self.c["layers"] + 3
 
     def config(self, n_gpus):
         c = self.c

@@ -540,15 +540,19 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
 // their own 128 rows of A and their own 128 rows (N) of W — 256 flop per byte — and the pair's leader issues
 // one MMA (M = 256) that reads both CTAs' shared memory; each CTA's TMEM receives its own 128 rows, and each
 // CTA runs its own epilogue.  Loads stay plain per-CTA TMA loads; only barrier arrivals cross between CTAs.
-template <int STAGES, int MODE>
+//
+// BN = 256, or 192 in the fp32 modes: with N = 768 (the residual projections of a 768-wide model) 256-column
+// tiles give 1.3 tiles per pair, i.e. two rounds of which the second is nearly empty; 192-column tiles give 1.73
+// tiles per pair in two shorter rounds with a shorter epilogue at the end.
+template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(gemm_threads(MODE), 1)
 gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_w,
                         const GemmArgs args) {
-    constexpr int BN = 256;
+    static_assert(BN == 256 || (BN == 192 && MODE < kOutE4M3), "192-column pair tiles exist for the fp32 modes only");
     constexpr int kABytes = BM * BK, kBBytes = (BN / 2) * BK, kStageBytes = kABytes + kBBytes;
     constexpr int EW = epi_warps(MODE);
     constexpr int kStagingBytes = kEpiWarps * kStagingFloatsPerWarp * 4;  // fp8 / amax modes use 4 KB of it (bias slices)
-    constexpr int kTmemCols = 2 * BN;
+    constexpr int kTmemCols = 512;  // two accumulator buffers of BN columns; allocations are powers of two
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     float* staging = reinterpret_cast<float*>(smem + STAGES * kStageBytes);
@@ -800,14 +804,19 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
     }
 }
 
-constexpr int kPairStages = 5;
-constexpr int kPairSmemBytes = kPairStages * (BM * BK + 128 * BK) + kEpiWarps * kStagingFloatsPerWarp * 4 + 256 + 1024;
-static_assert(kPairSmemBytes <= 227 * 1024, "shared memory budget");
+template <int BN>
+struct PairCfg {
+    static constexpr int kStages = BN == 256 ? 5 : 6;
+    static constexpr int kSmemBytes =
+        kStages * (BM * BK + (BN / 2) * BK) + kEpiWarps * kStagingFloatsPerWarp * 4 + 256 + 1024;
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+};
 
-template <int MODE>
+template <int BN, int MODE>
 df8_status launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tw, const GemmArgs& args, int grid,
                             cudaStream_t st) {
-    auto kern = gemm_fp8_tn_pair_kernel<kPairStages, MODE>;
+    constexpr int kPairSmemBytes = PairCfg<BN>::kSmemBytes;
+    auto kern = gemm_fp8_tn_pair_kernel<BN, PairCfg<BN>::kStages, MODE>;
     static bool configured[64] = {};
     int dev = 0;
     DF8_CUDA_TRY(cudaGetDevice(&dev));
@@ -886,21 +895,41 @@ df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uin
     const int sms = sm_count();
     // CTA pairs on 256 x 256 tiles when the problem fills them (see gemm_fp8_tn_pair_kernel)
     if (use_pair_kernel(M, N, K, sms)) {
-        const long tiles2 = long((M + 255) / 256) * ((N + 255) / 256);
+        // Tile width of the fp32 modes, by the measured per-K-block and per-chunk costs (cycles): a K block is
+        // bound by the tensor core (2 BN) or by the CTA's operand bytes arriving at ~50 bytes per cycle while the
+        // previous tile's stores are in flight; a 32-column chunk of the epilogue takes a warp ~2500 cycles and
+        // the last tile's epilogue overlaps nothing.
+        auto pair_cost = [&](int bn) {
+            const long tiles = long((M + 255) / 256) * ((N + bn - 1) / bn);
+            const double rounds = double((tiles + sms / 2 - 1) / (sms / 2));
+            const double mma = 2.0 * bn, loads = (BM * BK + bn / 2 * BK) / 50.0;
+            return rounds * double((K + BK - 1) / BK) * (mma > loads ? mma : loads) + 2500.0 * (bn / 64);
+        };
+        const bool fp32_mode = mode == kOutF32Vec || mode == kOutF32;
+        int bn2 = fp32_mode && pair_cost(192) < pair_cost(256) ? 192 : 256;
+        if (const char* e = getenv("DF8_GEMM_PAIR_BN")) {  // profiling and tests
+            if (fp32_mode && atoi(e) == 192) bn2 = 192;
+            if (atoi(e) == 256) bn2 = 256;
+        }
+        const long tiles2 = long((M + 255) / 256) * ((N + bn2 - 1) / bn2);
         const long pairs = tiles2 < sms / 2 ? tiles2 : sms / 2;
         CUtensorMap ta2, tw2;
         df8_status rc2 = make_tmap_2d_u8(&ta2, a_codes, uint64_t(M), uint64_t(K), uint64_t(K), BM, BK, 128);
         if (rc2 != DF8_OK) return rc2;
-        rc2 = make_tmap_2d_u8(&tw2, w_codes, uint64_t(N), uint64_t(K), uint64_t(K), 128, BK, 128);
+        rc2 = make_tmap_2d_u8(&tw2, w_codes, uint64_t(N), uint64_t(K), uint64_t(K), uint32_t(bn2 / 2), BK, 128);
         if (rc2 != DF8_OK) return rc2;
-        args.idesc = ptx::make_idesc_f8(256, 256, int(kind_a), int(kind_w));
+        args.idesc = ptx::make_idesc_f8(256, bn2, int(kind_a), int(kind_w));
         const int grid2 = int(pairs) * 2;
         switch (mode) {
-            case kOutF32Vec: return launch_gemm_pair<kOutF32Vec>(ta2, tw2, args, grid2, st);
-            case kOutF32: return launch_gemm_pair<kOutF32>(ta2, tw2, args, grid2, st);
-            case kOutE4M3: return launch_gemm_pair<kOutE4M3>(ta2, tw2, args, grid2, st);
-            case kOutE5M2: return launch_gemm_pair<kOutE5M2>(ta2, tw2, args, grid2, st);
-            default: return launch_gemm_pair<kOutNone>(ta2, tw2, args, grid2, st);
+            case kOutF32Vec:
+                return bn2 == 192 ? launch_gemm_pair<192, kOutF32Vec>(ta2, tw2, args, grid2, st)
+                                  : launch_gemm_pair<256, kOutF32Vec>(ta2, tw2, args, grid2, st);
+            case kOutF32:
+                return bn2 == 192 ? launch_gemm_pair<192, kOutF32>(ta2, tw2, args, grid2, st)
+                                  : launch_gemm_pair<256, kOutF32>(ta2, tw2, args, grid2, st);
+            case kOutE4M3: return launch_gemm_pair<256, kOutE4M3>(ta2, tw2, args, grid2, st);
+            case kOutE5M2: return launch_gemm_pair<256, kOutE5M2>(ta2, tw2, args, grid2, st);
+            default: return launch_gemm_pair<256, kOutNone>(ta2, tw2, args, grid2, st);
         }
     }
     // Tile width.  A TMA tiled load costs the SM's copy engine ~250 cycles whatever its size, and L2 delivers

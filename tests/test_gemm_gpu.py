@@ -94,6 +94,32 @@ def test_gemm_shapes_vs_oracle(df8, oracle, cuda, M, N, K):
     assert df8.status_word() == (0, 0)
 
 
+@pytest.mark.parametrize("N", [1001, 1002, 1003, 2049, 95])
+@pytest.mark.parametrize("bias", [True, False])
+def test_gemm_rows_not_16_byte_aligned(df8, oracle, cuda, N, bias):
+    """Rows of N % 4 != 0 floats (the 4-byte-store epilogue): every row alignment, a ragged last row block, a
+    last column chunk that ends inside a tile, the max|out| output and the canary bytes after the buffer."""
+    import torch
+
+    M, K = 203, 256
+    x = oracle.fill_normal(M * K, seed=N).reshape(M, K)
+    w = oracle.fill_normal(N * K, seed=N + 1, std=0.05).reshape(N, K)
+    b = oracle.fill_normal(N, seed=N + 2, std=0.1) if bias else None
+    xc, sx = oracle.quantize(x, 0)
+    wc, sw = oracle.quantize(w, 0)
+    t = lambda a: None if a is None else torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+    buf = torch.full((M * N + 64,), 777.0, device=cuda)
+    amax = torch.zeros(1, device=cuda)
+    df8.gemm_fp8_tn(t(xc), 0, t(sx), t(wc), 0, t(sw), t(b), None, M, N, K, 4, buf, amax)
+    torch.cuda.synchronize()
+    y = buf[: M * N].cpu().numpy().reshape(M, N)
+    ref = oracle.fc_forward_fp8(xc, 0, sx[1], wc, 0, sw[1], b, None, 0)
+    assert rel_err(y, ref) <= TIGHT, describe_mismatch(y, ref, TIGHT)
+    assert np.all(buf[M * N:].cpu().numpy() == 777.0)
+    assert amax.item() == np.abs(y).max()
+    assert df8.status_word() == (0, 0)
+
+
 @pytest.mark.parametrize("kind_a,kind_w", [(0, 0), (1, 0), (0, 1), (1, 1)])
 def test_gemm_kinds(df8, oracle, cuda, kind_a, kind_w):
     y, ref, _, _ = run_gemm(df8, oracle, cuda, 256, 384, 512, kind_a=kind_a, kind_w=kind_w, seed=7)
@@ -211,6 +237,26 @@ def test_gemm_cta_pair_kernel(df8, oracle, cuda, monkeypatch, M, N, K, flags):
     assert rel_err(y2, ref) <= tol, describe_mismatch(y2, ref, tol)
     assert np.array_equal(y1, y2)
     assert amax1 == amax2
+    assert df8.status_word() == (0, 0)
+
+
+@pytest.mark.parametrize("M,N,K,flags", [(512, 768, 1024, 2), (1024, 768, 3072, 6), (300, 1003, 256, 0), (256, 192, 128, 3),
+                                         (384, 1000, 384, 2)])
+def test_gemm_cta_pair_kernel_192_column_tiles(df8, oracle, cuda, monkeypatch, M, N, K, flags):
+    """The pair kernel's 256 x 192 tiles (fp32 output; chosen by itself for N = 768 at K >= 1024), forced on
+    here: against the oracle and bit for bit against the 256-column pair tiles and the single-CTA kernel,
+    residual, GELU and ragged edges included."""
+    monkeypatch.setenv("DF8_GEMM_PAIR", "1")
+    monkeypatch.setenv("DF8_GEMM_PAIR_BN", "192")
+    y2, ref, amax2, _ = run_gemm(df8, oracle, cuda, M, N, K, flags=flags, seed=M + N + 1)
+    monkeypatch.setenv("DF8_GEMM_PAIR_BN", "256")
+    y3, _, amax3, _ = run_gemm(df8, oracle, cuda, M, N, K, flags=flags, seed=M + N + 1)
+    monkeypatch.setenv("DF8_GEMM_PAIR", "0")
+    y1, _, amax1, _ = run_gemm(df8, oracle, cuda, M, N, K, flags=flags, seed=M + N + 1)
+    tol = 2e-3 if flags & 1 else TIGHT
+    assert rel_err(y2, ref) <= tol, describe_mismatch(y2, ref, tol)
+    assert np.array_equal(y1, y2) and np.array_equal(y1, y3)
+    assert amax1 == amax2 == amax3
     assert df8.status_word() == (0, 0)
 
 

@@ -112,6 +112,31 @@ def test_attention_gpt2_small_shape_sampled(df8, oracle, cuda):
     assert df8.status_word() == (0, 0)
 
 
+@pytest.mark.parametrize("B,T,H,mask_mode,kind", [(2, 256, 3, 0, 0), (1, 512, 2, 1, 0), (2, 768, 1, 1, 0), (1, 256, 2, 2, 0),
+                                                  (5, 512, 7, 0, 0), (1, 512, 1, 0, 1)])
+def test_attention_two_tile_kernel(df8, oracle, cuda, monkeypatch, B, T, H, mask_mode, kind):
+    """D = 64 with T a multiple of 256 takes the kernel with two query tiles per CTA (two threads per query row,
+    row sums from the ones columns of the V operand): against the oracle, and against the one-tile kernel
+    (DF8_ATTN_WIDE=0), which forms the same probabilities from the same maxima; more items than SMs included
+    (B = 5, H = 7: every CTA walks several items)."""
+    mask = None
+    if mask_mode == 2:
+        rng = np.random.default_rng(T)
+        mask = rng.standard_normal((1, 1, T, T)).astype(np.float32)
+        mask[0, 0, 9, :] = -1e9
+        mask[0, 0, :, 130] = -1e9
+    y2, ref, amax2 = run_attention(df8, oracle, cuda, B, T, H, 64, kind=kind, mask_mode=mask_mode, mask=mask, seed=T + H)
+    monkeypatch.setenv("DF8_ATTN_WIDE", "0")
+    y1, _, amax1 = run_attention(df8, oracle, cuda, B, T, H, 64, kind=kind, mask_mode=mask_mode, mask=mask, seed=T + H)
+    tol = TOL if kind == 0 else 2.5e-2
+    assert rel_err(y2, ref) <= tol, describe(y2, ref)
+    assert rel_err(y2, y1) <= 1e-5, describe(y2, y1)
+    assert amax2 == np.abs(y2).max()
+    if mask_mode == 2:
+        assert not y2[9].any()
+    assert df8.status_word() == (0, 0)
+
+
 def test_attention_rejects_bad_arguments(df8, cuda):
     import torch
 

@@ -116,11 +116,11 @@ __device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
     asm("ex2.approx.f16x2 %0, %1;" : "=r"(d) : "r"(x));
     return d;
 }
-// the same, pinned in program order between the barrier operations around it
-__device__ __forceinline__ uint32_t ex2_f16x2_ordered(uint32_t x) {
-    uint32_t d;
-    asm volatile("ex2.approx.f16x2 %0, %1;" : "=r"(d) : "r"(x));
-    return d;
+// ex2 pinned in program order between the barrier operations around it
+__device__ __forceinline__ float ex2_ordered(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 __device__ __forceinline__ uint32_t f16x2_of_e4m3x2(uint32_t x) {
     uint32_t d;
@@ -606,9 +606,11 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
 //     one loop) and their softmax warps — the two on a scheduler hold the same lane quarter of the two tiles — hit
 //     the special-function unit together: 2.25 k cycles for a block's exponentials instead of 1.25 k, with the
 //     unit idle for the rest of the block.  One mbarrier per tile and lane quarter orders them: tile 1 starts the
-//     exponentials of block x when tile 0 has issued those of block x, tile 0 those of block x + 1 when tile 1
-//     has issued those of block x; everything else (TMEM loads, maxima, P stores, waits) overlaps the other
-//     tile's turn.
+//     exponentials of block x when tile 0 has issued half of those of block x, tile 0 those of block x + 1 when
+//     tile 1 has issued half of those of block x; everything else (TMEM loads, maxima, P stores, waits) overlaps
+//     the other tile's turn.  (One warp alone does not fill the unit, hence the hand-over at half.)
+//   * exp2 is evaluated in fp32 and the results packed to halves: as fast here as ex2 on packed halves, and the
+//     exponent is not rounded to half precision first.
 // (Two threads per query row — sixteen softmax warps with 64 scores each — was measured as well: the halves of
 // a row must agree on the reference maximum every key block, and that exchange (~700 cycles per block through
 // shared memory and an mbarrier) cost more than the shorter phases saved: 91 us against 79 us.)
@@ -909,6 +911,7 @@ attention_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_qkv, const Att
         constexpr float kPShift = 5.0f;
         constexpr float kLazy = 2.5f;
         constexpr int HC = BKV;  // score columns per thread and block: the whole row
+        constexpr int kTurnAt = HC / 4;  // pairs of exponentials issued when the other tile may start its own
         bool ok = true;
         uint32_t pv_waited = 0;  // "P_t.V done" phases this thread has observed
         uint32_t gt = 0;         // running key-block counter of this thread's tile
@@ -1029,10 +1032,11 @@ attention_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_qkv, const Att
                 }
                 uint32_t pw[HC / 2];
 #pragma unroll
-                for (int i = 0; i < HC / 2; ++i)
-                    pw[i] = ex2_f16x2_ordered(pack_f16x2(fmaf(__uint_as_float(r[2 * i]), ecs, nshift),
-                                                         fmaf(__uint_as_float(r[2 * i + 1]), ecs, nshift)));
-                if (lane == 0) mbar_arrive(other_turn);
+                for (int i = 0; i < HC / 2; ++i) {
+                    pw[i] = pack_f16x2(ex2_ordered(fmaf(__uint_as_float(r[2 * i]), ecs, nshift)),
+                                       ex2_ordered(fmaf(__uint_as_float(r[2 * i + 1]), ecs, nshift)));
+                    if (i == kTurnAt - 1 && lane == 0) mbar_arrive(other_turn);
+                }
                 // P_t is a single buffer: the tile's previous P.V must have read it
                 while (pv_waited < gj) {
                     if (!mbar_wait_bounded(smem_u32(o_full + t), pv_waited & 1)) {

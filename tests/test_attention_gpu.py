@@ -117,7 +117,8 @@ def test_attention_gpt2_small_shape_sampled(df8, oracle, cuda):
 def test_attention_two_tile_kernel(df8, oracle, cuda, monkeypatch, B, T, H, mask_mode, kind):
     """D = 64 with T a multiple of 256 takes the kernel with two query tiles per CTA (two threads per query row,
     row sums from the ones columns of the V operand): against the oracle, and against the one-tile kernel
-    (DF8_ATTN_WIDE=0), which forms the same probabilities from the same maxima; more items than SMs included
+    (DF8_ATTN_WIDE=0), which rounds the exponent to half precision before exp2 where this one evaluates exp2 in
+    fp32 — they agree to 3e-3 of max|y|, both inside the bound against the oracle; more items than SMs included
     (B = 5, H = 7: every CTA walks several items)."""
     mask = None
     if mask_mode == 2:
@@ -130,7 +131,7 @@ def test_attention_two_tile_kernel(df8, oracle, cuda, monkeypatch, B, T, H, mask
     y1, _, amax1 = run_attention(df8, oracle, cuda, B, T, H, 64, kind=kind, mask_mode=mask_mode, mask=mask, seed=T + H)
     tol = TOL if kind == 0 else 2.5e-2
     assert rel_err(y2, ref) <= tol, describe(y2, ref)
-    assert rel_err(y2, y1) <= 1e-5, describe(y2, y1)
+    assert rel_err(y2, y1) <= 3e-3, describe(y2, y1)
     assert amax2 == np.abs(y2).max()
     if mask_mode == 2:
         assert not y2[9].any()

@@ -75,6 +75,10 @@ struct GemmArgs {
     unsigned int* status;
 };
 
+__host__ __device__ constexpr int pair_staging_bytes(int mode) {
+    return mode >= kOutE4M3 ? epi_warps(mode) * direct_staging_bytes(mode) : kEpiWarps * kStagingFloatsPerWarp * 4;
+}
+
 template <int BN, int STAGES, int MODE>
 struct GemmCfg {
     static constexpr int kABytes = BM * BK;
@@ -551,7 +555,8 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
     static_assert(BN == 256 || (BN == 192 && MODE < kOutE4M3), "192-column pair tiles exist for the fp32 modes only");
     constexpr int kABytes = BM * BK, kBBytes = (BN / 2) * BK, kStageBytes = kABytes + kBBytes;
     constexpr int EW = epi_warps(MODE);
-    constexpr int kStagingBytes = kEpiWarps * kStagingFloatsPerWarp * 4;  // fp8 / amax modes use 4 KB of it (bias slices)
+    // fp32 modes: a transpose buffer per warp; fp8 codes: bias slice + codes tile per warp; max|out| only: bias slices
+    constexpr int kStagingBytes = pair_staging_bytes(MODE);
     constexpr int kTmemCols = 512;  // two accumulator buffers of BN columns; allocations are powers of two
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -804,19 +809,20 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
     }
 }
 
-template <int BN>
+template <int BN, int MODE>
 struct PairCfg {
-    static constexpr int kStages = BN == 256 ? 5 : 6;
-    static constexpr int kSmemBytes =
-        kStages * (BM * BK + (BN / 2) * BK) + kEpiWarps * kStagingFloatsPerWarp * 4 + 256 + 1024;
+    // ring depth: the operand loads are latency-bound (~2.4 k cycles from issue to arrival with every SM loading),
+    // so as many stages as fit beside the epilogue's staging
+    static constexpr int kStages = (BN == 192 || MODE == kOutNone) ? 6 : 5;
+    static constexpr int kSmemBytes = kStages * (BM * BK + (BN / 2) * BK) + pair_staging_bytes(MODE) + 256 + 1024;
     static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
 
 template <int BN, int MODE>
 df8_status launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tw, const GemmArgs& args, int grid,
                             cudaStream_t st) {
-    constexpr int kPairSmemBytes = PairCfg<BN>::kSmemBytes;
-    auto kern = gemm_fp8_tn_pair_kernel<BN, PairCfg<BN>::kStages, MODE>;
+    constexpr int kPairSmemBytes = PairCfg<BN, MODE>::kSmemBytes;
+    auto kern = gemm_fp8_tn_pair_kernel<BN, PairCfg<BN, MODE>::kStages, MODE>;
     static bool configured[64] = {};
     int dev = 0;
     DF8_CUDA_TRY(cudaGetDevice(&dev));

@@ -296,6 +296,10 @@ layernorm_quantize_resident_kernel(const float* __restrict__ x, int rows, int C,
     const int c4 = C >> 2;
     const int r0 = blockIdx.x * rows_per_cta;
     const int nrows = min(rows_per_cta, rows - r0);  // may be <= 0: such a CTA only takes part in the barrier
+    // launched under the previous kernel's tail (when the launch carries the programmatic attribute): CTAs that
+    // become resident early wait here, and later at the grid barrier, for the rest of the grid
+    griddep_launch_dependents();
+    griddep_wait();
     float warp_amax = 0.f;
     for (int lr = warp; lr < nrows; lr += nw) {
         const float4* xr = reinterpret_cast<const float4*>(x + size_t(r0 + lr) * C);
@@ -417,13 +421,24 @@ bool launch_resident(const float* x, int rows, int C, const float* gamma, const 
         cfg.blockDim = dim3(kResThreads);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = st;
-        cudaLaunchAttribute attr[1];
+        cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeCooperative;  // the grid barrier needs every CTA resident
         attr[0].val.cooperative = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        if (cudaLaunchKernelEx(&cfg, kern, x, rows, C, gamma, beta, eps, amax, codes, scale_out, rows_per_cta,
-                               counter_slot, status) != cudaSuccess) {
+        static std::atomic<bool> pdl_refused{false};  // a driver that rejects the combination: plain cooperative launches
+        cfg.numAttrs = (pdl_enabled() && !pdl_refused.load()) ? 2 : 1;
+        cudaError_t err = cudaLaunchKernelEx(&cfg, kern, x, rows, C, gamma, beta, eps, amax, codes, scale_out,
+                                             rows_per_cta, counter_slot, status);
+        if (err != cudaSuccess && cfg.numAttrs == 2) {
+            (void)cudaGetLastError();
+            pdl_refused.store(true);
+            cfg.numAttrs = 1;
+            err = cudaLaunchKernelEx(&cfg, kern, x, rows, C, gamma, beta, eps, amax, codes, scale_out, rows_per_cta,
+                                     counter_slot, status);
+        }
+        if (err != cudaSuccess) {
             (void)cudaGetLastError();  // e.g. not co-schedulable: the two-kernel path takes over
             return false;
         }

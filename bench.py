@@ -527,13 +527,18 @@ class AttnWorkload:
         ms = ev[0].elapsed_time(ev[1]) / iters
         tf = self.units_per_step() / (ms / 1e3)
         peak = 2.0 * peaks["bf16_tflops"]
-        return {"kernel": "attention_fp8_kernel<64>", "bound": "tensor", "achieved": round(tf, 1), "peak": peak,
+        wide = self.D == 64 and self.T % 256 == 0 and os.environ.get("DF8_ATTN_WIDE", "1")[:1] != "0"
+        # one ncu capture of this launch each: the two-tile kernel read 19.0 MB and wrote nothing back inside the
+        # capture (profiles/attention_fp8_wide_kernel_b8_t1024_h12_d64.md: the 25.2 MB of output stay in L2); the
+        # one-tile kernel 19.2 MB read + 67.3 MB written (output plus write-back of the bench's L2 flush buffer)
+        traffic = None
+        if (self.B, self.T, self.H, self.D) == (8, 1024, 12, 64):
+            traffic = round(19.0e6 + 9.7e3) if wide else round(19.15e6 + 67.33e6)
+        return {"kernel": "attention_fp8_wide_kernel" if wide else f"attention_fp8_kernel<{self.D}>",
+                "bound": "tensor", "achieved": round(tf, 1), "peak": peak,
                 "peak_source": peaks["source"] + " bf16 burst x2 (fp8 dense)", "unit": "TFLOP/s",
                 "frac": round(tf / peak, 4), "ms_per_launch": round(ms, 4),
-                "algorithmic_flops_per_launch": self.units_per_step() * 1e12,
-                # one ncu capture of this launch (profiles/attention_fp8_kernel_b8_t1024_h12_d64.md): 19.2 MB read
-                # + 67.3 MB written (25.2 MB of output; the rest is write-back of the bench's L2 flush buffer)
-                "traffic": round(19.15e6 + 67.33e6) if (self.B, self.T, self.H, self.D) == (8, 1024, 12, 64) else None}
+                "algorithmic_flops_per_launch": self.units_per_step() * 1e12, "traffic": traffic}
 
     def e2e_setup(self, torch, dev):
         self.h_codes = torch.empty(self.codes.shape, dtype=torch.uint8, pin_memory=True)

@@ -30,6 +30,7 @@
 #include "sm100_ptx.cuh"
 #include "tensormap.cuh"
 
+#include <atomic>
 #include <cstdlib>
 
 namespace df8 {
@@ -73,7 +74,14 @@ struct GemmArgs {
     int flags;
     uint32_t idesc;
     unsigned int* status;
+    unsigned int* grid_counter;  // fused max|out| + codes launch: arrival counter of the grid-wide barrier, else null
 };
+
+// Arrival counters of the fused launches' grid-wide barrier: each counts up for ever (a launch waits for the next
+// multiple of its grid size), one of them per launch in turn so that launches that overlap in time do not mix.
+// Every launch that uses them has one CTA per SM.
+constexpr int kFusedCounters = 64;
+__device__ unsigned int g_gemm_grid_counter[kFusedCounters] = {};
 
 __host__ __device__ constexpr int pair_staging_bytes(int mode) {
     return mode >= kOutE4M3 ? epi_warps(mode) * direct_staging_bytes(mode) : kEpiWarps * kStagingFloatsPerWarp * 4;
@@ -329,6 +337,14 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
     const int num_n = (args.N + BN - 1) / BN;
     const int num_tiles = num_m * num_n;
     const int num_kb = (args.K + BK - 1) / BK;
+    // This CTA's tiles: blockIdx.x + k * gridDim.x, k < n_mine.  A fused launch (max|out|, grid-wide barrier, codes;
+    // fp8 modes only) walks them twice, except that the accumulators of its last n_keep tiles stay in TMEM over the
+    // barrier and are not computed again: the sequence is k = 0 .. n_mine-1, then 0 .. n_mine-n_keep-1.
+    const bool fused = args.grid_counter != nullptr;
+    const int n_mine = int(blockIdx.x) < num_tiles ? (num_tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x) : 0;
+    const int n_keep = fused ? (n_mine < 2 ? n_mine : 2) : 0;
+    const int seq_len = fused ? 2 * n_mine - n_keep : n_mine;
+    auto seq_tile = [&](int i) { return int(blockIdx.x) + (i < n_mine ? i : i - n_mine) * int(gridDim.x); };
 
     if (warp == 0) {
         if (lane == 0) {
@@ -337,7 +353,8 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int i = 0; i < seq_len && ok; ++i) {
+                const int tile = seq_tile(i);
                 const int m0 = (tile % num_m) * BM;
                 const int n0 = (tile / num_m) * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
@@ -372,9 +389,10 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
             uint32_t phase = 0, dlo = dlo0, fullb = full0, emptyb = empty0;
             uint32_t acc_it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++acc_it) {
+            for (int i = 0; i < seq_len && ok; ++i, ++acc_it) {
                 const uint32_t buf = acc_it & 1;
                 const uint32_t acc_phase = (acc_it >> 1) & 1;
+                // (fused: the buffers of the kept tiles come back in the second phase, after their codes are out)
                 if (!mbar_wait_bounded(smem_u32(tempty + buf), acc_phase ^ 1)) {
                     record_timeout(args.status, 0x200u + buf);
                     break;
@@ -418,17 +436,118 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
         const float alpha = args.scale_a[1] * args.scale_w[1];
         float out_q = 1.f;
         if constexpr (MODE == kOutE4M3 || MODE == kOutE5M2) {
-            const float2 sc = scales_from_amax(*args.q_amax, fp8_max(MODE == kOutE4M3 ? DF8_E4M3 : DF8_E5M2));
-            out_q = sc.x;
-            if (blockIdx.x == 0 && e == 0 && lane == 0 && args.out_scale) {
-                args.out_scale[0] = sc.x;
-                args.out_scale[1] = sc.y;
+            if (!fused) {
+                const float2 sc = scales_from_amax(*args.q_amax, fp8_max(MODE == kOutE4M3 ? DF8_E4M3 : DF8_E5M2));
+                out_q = sc.x;
+                if (blockIdx.x == 0 && e == 0 && lane == 0 && args.out_scale) {
+                    args.out_scale[0] = sc.x;
+                    args.out_scale[1] = sc.y;
+                }
             }
         }
         const uint32_t lane_addr = uint32_t(q * 32) << 16;
         uint32_t acc_it = 0;
         float amax = 0.f;  // max|out| over all of this warp's tiles: one atomic per warp at the end
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++acc_it) {
+        if constexpr (MODE == kOutE4M3 || MODE == kOutE5M2) {
+            if (fused) {
+                constexpr int KIND = MODE == kOutE4M3 ? int(DF8_E4M3) : int(DF8_E5M2);
+                constexpr int kParts = EW / 4;
+                constexpr int kCh = BN / (32 * kParts);
+                const int part = e >> 2;
+                uint8_t* wst = reinterpret_cast<uint8_t*>(staging) + e * direct_staging_bytes(MODE);
+                float* sb = reinterpret_cast<float*>(wst);
+                uint8_t* codes_tile = wst + 256;
+                bool ok = true;
+                // One tile of the sequence: accumulators into registers (after waiting for the MMAs unless they were
+                // kept from the first phase), TMEM handed back unless the tile is kept, then max|out| or codes.
+                auto do_tile = [&](int k, uint32_t it, bool wait_full, bool release, bool codes) {
+                    const int tile = int(blockIdx.x) + k * int(gridDim.x);
+                    const uint32_t buf = it & 1;
+                    const int m0 = (tile % num_m) * BM, n0 = (tile / num_m) * BN;
+                    const int row0 = m0 + q * 32;
+                    const uint32_t taddr = tmem_base + buf * BN + lane_addr;
+                    const int colw = n0 + 32 * kCh * part;
+#pragma unroll
+                    for (int j = 0; j < kCh; ++j) {
+                        const int col = colw + 32 * j + lane;
+                        sb[j * 32 + lane] = (args.bias && col < args.N) ? __ldg(args.bias + col) : 0.f;
+                    }
+                    __syncwarp();
+                    if (wait_full && ok && !mbar_wait_bounded(smem_u32(tfull + buf), (it >> 1) & 1)) {
+                        if (lane == 0) record_timeout(args.status, 0x400u + buf);
+                        ok = false;  // keep walking (the barriers below need every warp), without touching TMEM
+                    }
+                    uint32_t r[kCh][32];
+                    if (ok) {
+                        tc_fence_after_sync();
+#pragma unroll
+                        for (int j = 0; j < kCh; ++j)
+                            if (colw + 32 * j < args.N) tmem_ld_32x32(taddr + 32 * (kCh * part + j), r[j]);
+                        tmem_ld_wait();
+                        tc_fence_before_sync();
+                    }
+                    __syncwarp();
+                    if (release && lane == 0) mbar_arrive(smem_u32(tempty + buf));
+                    if (ok) {
+                        const int grow = row0 + lane;
+#pragma unroll
+                        for (int j = 0; j < kCh; ++j) {
+                            const int col0 = colw + 32 * j;
+                            if (col0 < args.N) {
+                                if (codes) direct_chunk<KIND, 2 * kCh>(r[j], grow, col0, args, alpha, out_q, amax, sb + j * 32, codes_tile, j);
+                                else direct_chunk<-1>(r[j], grow, col0, args, alpha, 1.f, amax, sb + j * 32);
+                            }
+                        }
+                        __syncwarp();
+                        if (codes) {
+                            store_staged_codes<2 * kCh>(codes_tile, lane, row0, colw, args);
+                            __syncwarp();
+                        }
+                    }
+                };
+                // phase 1: max|out| over every tile; the last n_keep tiles stay in TMEM
+                for (int k = 0; k < n_mine; ++k) do_tile(k, uint32_t(k), true, k < n_mine - n_keep, false);
+                amax = warp_max(amax);
+                if (lane == 0 && amax > 0.f) atomic_max_nonneg(args.out_amax, amax);
+                // grid-wide barrier (bounded): every CTA's maxima are in before anyone reads the result
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory");
+                if (e == 0 && lane == 0) {
+                    __threadfence();
+                    const unsigned int ticket = atomicAdd(args.grid_counter, 1u);
+                    const unsigned int target = (ticket / gridDim.x + 1u) * gridDim.x;
+                    volatile unsigned int* cnt = args.grid_counter;
+                    unsigned long long t0 = 0;
+                    for (unsigned int spins = 0; int(*cnt - target) < 0; ++spins) {
+                        __nanosleep(32);
+                        if ((spins & 1023u) == 1023u) {
+                            const unsigned long long now = globaltimer_ns();
+                            if (t0 == 0) t0 = now;
+                            if (now - t0 > 2000000000ull) {  // a CTA never came: flag it and finish
+                                record_timeout(args.status, 0x4800u);
+                                break;
+                            }
+                        }
+                    }
+                    __threadfence();
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory");
+                {
+                    const float2 sc = scales_from_amax(*reinterpret_cast<const volatile float*>(args.out_amax),
+                                                       fp8_max(MODE == kOutE4M3 ? DF8_E4M3 : DF8_E5M2));
+                    out_q = sc.x;
+                    if (blockIdx.x == 0 && e == 0 && lane == 0 && args.out_scale) {
+                        args.out_scale[0] = sc.x;
+                        args.out_scale[1] = sc.y;
+                    }
+                }
+                amax = 0.f;
+                // phase 2: codes; first the kept tiles straight from TMEM, then the others as the MMAs redo them
+                for (int k = n_mine - n_keep; k < n_mine; ++k) do_tile(k, uint32_t(k), false, true, true);
+                for (int k = 0; k < n_mine - n_keep; ++k) do_tile(k, uint32_t(n_mine + k), true, true, true);
+                acc_it = uint32_t(seq_len);
+            }
+        }
+        for (int tile = blockIdx.x; tile < num_tiles && !fused; tile += gridDim.x, ++acc_it) {
             const uint32_t buf = acc_it & 1;
             const uint32_t acc_phase = (acc_it >> 1) & 1;
             const int m0 = (tile % num_m) * BM;
@@ -522,7 +641,7 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
                 }
             }
         }
-        if (args.flags & 4) {
+        if ((args.flags & 4) && !fused) {
             amax = warp_max(amax);
             if (lane == 0 && amax > 0.f) atomic_max_nonneg(args.out_amax, amax);
         }
@@ -862,6 +981,27 @@ df8_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmA
         DF8_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         configured[dev] = true;
     }
+    if (args.grid_counter != nullptr) {
+        // fused launch: its grid-wide barrier needs every CTA resident, i.e. a cooperative launch
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(unsigned(grid));
+        cfg.blockDim = dim3(gemm_threads(MODE));
+        cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeCooperative;
+        attr[0].val.cooperative = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl_enabled() ? 2 : 1;
+        cudaError_t err = cudaLaunchKernelEx(&cfg, kern, ta, tw, args);
+        if (err != cudaSuccess) {
+            (void)cudaGetLastError();
+            return DF8_ERR_UNSUPPORTED;  // not co-schedulable here: the caller falls back to two launches
+        }
+        return DF8_OK;
+    }
     cudaError_t err = launch_kernel(kern, dim3(unsigned(grid)), dim3(gemm_threads(MODE)), Cfg::kSmemBytes, st, ta, tw, args);
     if (err != cudaSuccess) return fail(DF8_ERR_CUDA, "launch of gemm_fp8_tn_kernel failed: %s", cudaGetErrorString(err));
     return DF8_OK;
@@ -892,15 +1032,21 @@ bool use_pair_kernel(int M, int N, int K, int sms) {
 }
 
 // Shared host path of the entry points: picks the tile width, encodes the tensor maps, launches `mode`.
+// `fused`: in: try the one-launch max|out| + codes form (fp8 modes); out: whether that is what was launched.  When
+// it cannot be (CTA-pair shapes, fewer tiles than SMs, no cooperative launch) nothing is launched and the caller
+// runs the two passes.
 df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uint8_t* w_codes, df8_kind kind_w,
-                    GemmArgs args, cudaStream_t st) {
+                    GemmArgs args, cudaStream_t st, bool* fused = nullptr) {
     const int M = args.M, N = args.N, K = args.K;
     df8_status src = status_word_device_ptr(&args.status);
     if (src != DF8_OK) return src;
+    const bool want_fused = fused != nullptr && *fused;
+    if (fused) *fused = false;
 
     const int sms = sm_count();
     // CTA pairs on 256 x 256 tiles when the problem fills them (see gemm_fp8_tn_pair_kernel)
     if (use_pair_kernel(M, N, K, sms)) {
+        if (want_fused) return DF8_OK;
         // Tile width of the fp32 modes, by the measured per-K-block and per-chunk costs (cycles): a K block is
         // bound by the tensor core (2 BN) or by the CTA's operand bytes arriving at ~50 bytes per cycle while the
         // previous tile's stores are in flight; a 32-column chunk of the epilogue takes a warp ~2500 cycles and
@@ -965,6 +1111,21 @@ df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uin
     rc = make_tmap_2d_u8(&tw, w_codes, uint64_t(N), uint64_t(K), uint64_t(K), uint32_t(bn), BK, 128);
     if (rc != DF8_OK) return rc;
     args.idesc = ptx::make_idesc_f8(BM, bn, int(kind_a), int(kind_w));
+    if (want_fused) {
+        if (grid != sms || (mode != kOutE4M3 && mode != kOutE5M2)) return DF8_OK;  // nothing launched, *fused stays false
+        static std::atomic<unsigned int> next_slot{0};
+        unsigned int* counters = nullptr;
+        if (cudaGetSymbolAddress(reinterpret_cast<void**>(&counters), g_gemm_grid_counter) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return DF8_OK;
+        }
+        args.grid_counter = counters + next_slot.fetch_add(1u) % unsigned(kFusedCounters);
+        const df8_status rc = mode == kOutE4M3 ? launch_gemm_bn<kOutE4M3>(wide, ta, tw, args, grid, st)
+                                               : launch_gemm_bn<kOutE5M2>(wide, ta, tw, args, grid, st);
+        if (rc == DF8_ERR_UNSUPPORTED) return DF8_OK;  // no cooperative launch here: two passes
+        if (rc == DF8_OK) *fused = true;
+        return rc;
+    }
 
     switch (mode) {
         case kOutF32Vec: return launch_gemm_bn<kOutF32Vec>(wide, ta, tw, args, grid, st);
@@ -1048,6 +1209,19 @@ extern "C" df8_status df8_gemm_fp8_tn_q(const uint8_t* a_codes, df8_kind kind_a,
         const float one[2] = {1.f, 1.f};
         DF8_CUDA_TRY(cudaMemcpyAsync(out_scale, one, sizeof(one), cudaMemcpyHostToDevice, st));
         return DF8_OK;
+    }
+    // One launch when the problem qualifies (single-CTA tiles, at least one tile per SM): max|out| over all tiles,
+    // a grid-wide barrier, then the codes, with each CTA's last two accumulator tiles kept in TMEM across the
+    // barrier instead of being computed twice.  DF8_GEMM_FUSED_Q=0 in the environment keeps the two launches.
+    {
+        const char* e = getenv("DF8_GEMM_FUSED_Q");
+        bool fused = !(e && e[0] == '0');
+        if (fused) {
+            args.flags = flags;
+            df8_status rcf = run_gemm(out_kind == DF8_E4M3 ? kOutE4M3 : kOutE5M2, a_codes, kind_a, w_codes, kind_w, args, st, &fused);
+            if (rcf != DF8_OK) return rcf;
+            if (fused) return DF8_OK;
+        }
     }
     // pass 1: max|out| only;  pass 2: the same product again, quantised with the scale that max gives
     args.flags = flags | DF8_EPI_AMAX;

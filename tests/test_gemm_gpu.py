@@ -178,10 +178,13 @@ def test_gemm_rejects_bad_arguments(df8, cuda):
 
 
 @pytest.mark.parametrize("out_kind", [0, 1])
-@pytest.mark.parametrize("M,N,K,flags", [(300, 768, 256, 0), (1024, 2304, 768, 0), (512, 3072, 768, 1), (64, 96, 48, 1)])
+@pytest.mark.parametrize("M,N,K,flags", [(300, 768, 256, 0), (1024, 2304, 768, 0), (512, 3072, 768, 1), (64, 96, 48, 1),
+                                         (2432, 2304, 768, 0), (4100, 2304, 256, 1), (8192, 2304, 768, 0)])
 def test_gemm_quantised_output_is_the_two_step_chain(df8, oracle, cuda, out_kind, M, N, K, flags):
     """df8_gemm_fp8_tn_q (two tensor-core passes, no fp32 intermediate) must give, bit for bit, the codes and
-    scale of df8_gemm_fp8_tn + DF8_EPI_AMAX followed by df8_quantize_f32; and agree with the oracle chain."""
+    scale of df8_gemm_fp8_tn + DF8_EPI_AMAX followed by df8_quantize_f32; and agree with the oracle chain.
+    The last three shapes have at least one tile per SM and take the one-launch form (max|out|, grid-wide barrier,
+    codes, with accumulator tiles kept in TMEM across the barrier): one or two tiles per CTA, two or three, four."""
     import torch
 
     x = oracle.fill_normal(M * K, seed=31).reshape(M, K)
@@ -212,6 +215,37 @@ def test_gemm_quantised_output_is_the_two_step_chain(df8, oracle, cuda, out_kind
     got = oracle.dequantize(codes.cpu().numpy(), out_kind, float(scale[1].item()))
     assert rel_err(got, oracle.dequantize(oc, out_kind, osc[1])) <= (2 ** -3 if out_kind == 0 else 2 ** -2)
     assert (codes.cpu().numpy() != oc).mean() < (0.02 if flags == 0 else 0.05)
+    assert df8.status_word() == (0, 0)
+
+
+@pytest.mark.parametrize("M,N,K,flags,out_kind", [(8192, 3072, 768, 1, 0), (8192, 2304, 768, 0, 1), (3000, 4096, 512, 0, 0)])
+def test_gemm_quantised_output_one_launch_equals_two_launches(df8, oracle, cuda, monkeypatch, M, N, K, flags, out_kind):
+    """The one-launch form of df8_gemm_fp8_tn_q against the two launches it replaces (DF8_GEMM_FUSED_Q=0): codes,
+    scale and max|out| identical, repeatedly (the barrier's arrival counters are reused), status word clean."""
+    import torch
+
+    g = torch.Generator(device=cuda)
+    g.manual_seed(M + N)
+    a = torch.randint(0, 0x78, (M, K), dtype=torch.uint8, device=cuda, generator=g)
+    w = torch.randint(0, 0x60, (N, K), dtype=torch.uint8, device=cuda, generator=g)
+    w = w | (torch.randint(0, 2, (N, K), dtype=torch.uint8, device=cuda, generator=g) * 0x80)
+    bias = torch.randn(N, device=cuda, generator=g)
+    sa = torch.tensor([64.0, 1.0 / 64], device=cuda)
+    sw = torch.tensor([512.0, 1.0 / 512], device=cuda)
+
+    def run():
+        codes = torch.full((M, N), 0xAA, dtype=torch.uint8, device=cuda)
+        scale, amax = torch.zeros(2, device=cuda), torch.full((1,), -1.0, device=cuda)
+        df8.gemm_fp8_tn_q(a, 0, sa, w, 0, sw, bias, M, N, K, flags, out_kind, codes, scale, amax)
+        return codes, scale, amax
+
+    monkeypatch.setenv("DF8_GEMM_FUSED_Q", "0")
+    ref = run()
+    monkeypatch.delenv("DF8_GEMM_FUSED_Q")
+    for _ in range(3):
+        got = run()
+        assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1]) and got[2].item() == ref[2].item()
+    assert ref[2].item() > 0
     assert df8.status_word() == (0, 0)
 
 

@@ -370,10 +370,10 @@ class Gpt2Workload:
         # FC2 GEMM; head: amax, quantise, GEMM
         rows, C = self.B * self.T, self.c["hidden"]
         ln = 1 if (C <= 1024 and rows >= 1024 and rows * C * 4 <= 148 * 200 * 1024) else 2
-        # the two GEMM passes of QKV and FC1 are one cooperative launch where the single-CTA kernel runs (K < 1024)
-        # with at least one 128 x 256 tile per SM
+        # with DF8_GEMM_FUSED_Q=1 the two GEMM passes of QKV and FC1 are one cooperative launch where the single-CTA
+        # kernel runs (K < 1024) with at least one 128 x 256 tile per SM
         one_launch = (C < 1024 and -(-rows // 128) * -(-3 * C // 256) >= 148
-                      and os.environ.get("DF8_GEMM_FUSED_Q", "1")[:1] != "0")
+                      and os.environ.get("DF8_GEMM_FUSED_Q", "0")[:1] == "1")
         gq = 1 if one_launch else 2
         self.kernels_per_step = 1 + (4 + 2 * gq + 2 * ln) * self.c["layers"] + 3
 

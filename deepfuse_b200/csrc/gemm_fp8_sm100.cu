@@ -292,10 +292,13 @@ __device__ __forceinline__ void store_staged_codes(const uint8_t* stg, int lane,
     }
 }
 
-template <int BN, int STAGES, int MODE>
+// FUSED (fp8 modes only): the one-launch max|out| + codes form, an instantiation of its own so that the plain
+// kernels carry none of its code or registers.
+template <int BN, int STAGES, int MODE, bool FUSED = false>
 __global__ void __launch_bounds__(gemm_threads(MODE), 1)
 gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_w,
                    const GemmArgs args) {
+    static_assert(!FUSED || MODE == kOutE4M3 || MODE == kOutE5M2, "the fused form emits fp8 codes");
     using Cfg = GemmCfg<BN, STAGES, MODE>;
     constexpr int EW = epi_warps(MODE);
     extern __shared__ uint8_t smem_raw[];
@@ -340,7 +343,7 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
     // This CTA's tiles: blockIdx.x + k * gridDim.x, k < n_mine.  A fused launch (max|out|, grid-wide barrier, codes;
     // fp8 modes only) walks them twice, except that the accumulators of its last n_keep tiles stay in TMEM over the
     // barrier and are not computed again: the sequence is k = 0 .. n_mine-1, then 0 .. n_mine-n_keep-1.
-    const bool fused = args.grid_counter != nullptr;
+    constexpr bool fused = FUSED;
     const int n_mine = int(blockIdx.x) < num_tiles ? (num_tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x) : 0;
     const int n_keep = fused ? (n_mine < 2 ? n_mine : 2) : 0;
     const int seq_len = fused ? 2 * n_mine - n_keep : n_mine;
@@ -517,8 +520,11 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
                     const unsigned int target = (ticket / gridDim.x + 1u) * gridDim.x;
                     volatile unsigned int* cnt = args.grid_counter;
                     unsigned long long t0 = 0;
+                    // (one poller per CTA, a quarter of a microsecond apart: 148 CTAs polling one address every few
+                    // tens of nanoseconds would load its L2 slice with a few billion reads per second while the
+                    // slower CTAs still stream operands)
                     for (unsigned int spins = 0; int(*cnt - target) < 0; ++spins) {
-                        __nanosleep(32);
+                        __nanosleep(256);
                         if ((spins & 1023u) == 1023u) {
                             const unsigned long long now = globaltimer_ns();
                             if (t0 == 0) t0 = now;
@@ -979,9 +985,14 @@ df8_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmA
     DF8_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !configured[dev]) {
         DF8_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        if constexpr (MODE == kOutE4M3 || MODE == kOutE5M2)
+            DF8_CUDA_TRY(cudaFuncSetAttribute(gemm_fp8_tn_kernel<BN, STAGES, MODE, true>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         configured[dev] = true;
     }
     if (args.grid_counter != nullptr) {
+        if constexpr (MODE == kOutE4M3 || MODE == kOutE5M2) {
+        auto fkern = gemm_fp8_tn_kernel<BN, STAGES, MODE, true>;
         // fused launch: its grid-wide barrier needs every CTA resident, i.e. a cooperative launch
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(unsigned(grid));
@@ -995,12 +1006,15 @@ df8_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmA
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = pdl_enabled() ? 2 : 1;
-        cudaError_t err = cudaLaunchKernelEx(&cfg, kern, ta, tw, args);
+        cudaError_t err = cudaLaunchKernelEx(&cfg, fkern, ta, tw, args);
         if (err != cudaSuccess) {
             (void)cudaGetLastError();
             return DF8_ERR_UNSUPPORTED;  // not co-schedulable here: the caller falls back to two launches
         }
         return DF8_OK;
+        } else {
+            return fail(DF8_ERR_INVALID, "the one-launch form exists for the fp8 output modes only");
+        }
     }
     cudaError_t err = launch_kernel(kern, dim3(unsigned(grid)), dim3(gemm_threads(MODE)), Cfg::kSmemBytes, st, ta, tw, args);
     if (err != cudaSuccess) return fail(DF8_ERR_CUDA, "launch of gemm_fp8_tn_kernel failed: %s", cudaGetErrorString(err));
@@ -1210,12 +1224,15 @@ extern "C" df8_status df8_gemm_fp8_tn_q(const uint8_t* a_codes, df8_kind kind_a,
         DF8_CUDA_TRY(cudaMemcpyAsync(out_scale, one, sizeof(one), cudaMemcpyHostToDevice, st));
         return DF8_OK;
     }
-    // One launch when the problem qualifies (single-CTA tiles, at least one tile per SM): max|out| over all tiles,
-    // a grid-wide barrier, then the codes, with each CTA's last two accumulator tiles kept in TMEM across the
-    // barrier instead of being computed twice.  DF8_GEMM_FUSED_Q=0 in the environment keeps the two launches.
+    // With DF8_GEMM_FUSED_Q=1 in the environment, one launch when the problem qualifies (single-CTA tiles, at least
+    // one tile per SM): max|out| over all tiles, a grid-wide barrier, then the codes, with each CTA's last two
+    // accumulator tiles kept in TMEM across the barrier instead of being computed twice.  Not the default: inside a
+    // GPT-2 small forward it is 45 us faster in most processes (3.56 against 3.60 ms) but in about one process in
+    // three 0.1-0.4 ms slower, for the whole process, where the two launches are steady to 0.1 % (the barrier makes
+    // every launch wait for its slowest CTA).
     {
         const char* e = getenv("DF8_GEMM_FUSED_Q");
-        bool fused = !(e && e[0] == '0');
+        bool fused = e && e[0] == '1';
         if (fused) {
             args.flags = flags;
             df8_status rcf = run_gemm(out_kind == DF8_E4M3 ? kOutE4M3 : kOutE5M2, a_codes, kind_a, w_codes, kind_w, args, st, &fused);

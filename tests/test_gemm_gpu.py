@@ -180,12 +180,16 @@ def test_gemm_rejects_bad_arguments(df8, cuda):
 @pytest.mark.parametrize("out_kind", [0, 1])
 @pytest.mark.parametrize("M,N,K,flags", [(300, 768, 256, 0), (1024, 2304, 768, 0), (512, 3072, 768, 1), (64, 96, 48, 1),
                                          (2432, 2304, 768, 0), (4100, 2304, 256, 1), (8192, 2304, 768, 0)])
-def test_gemm_quantised_output_is_the_two_step_chain(df8, oracle, cuda, out_kind, M, N, K, flags):
+def test_gemm_quantised_output_is_the_two_step_chain(df8, oracle, cuda, monkeypatch, out_kind, M, N, K, flags):
     """df8_gemm_fp8_tn_q (two tensor-core passes, no fp32 intermediate) must give, bit for bit, the codes and
     scale of df8_gemm_fp8_tn + DF8_EPI_AMAX followed by df8_quantize_f32; and agree with the oracle chain.
-    The last three shapes have at least one tile per SM and take the one-launch form (max|out|, grid-wide barrier,
-    codes, with accumulator tiles kept in TMEM across the barrier): one or two tiles per CTA, two or three, four."""
+    The last three shapes have at least one tile per SM and, with DF8_GEMM_FUSED_Q=1, take the one-launch form
+    (max|out|, grid-wide barrier, codes, with accumulator tiles kept in TMEM across the barrier): one or two tiles per
+    CTA, two or three, four."""
     import torch
+
+    if M >= 2432:
+        monkeypatch.setenv("DF8_GEMM_FUSED_Q", "1")
 
     x = oracle.fill_normal(M * K, seed=31).reshape(M, K)
     w = oracle.fill_normal(N * K, seed=32, std=0.05).reshape(N, K)
@@ -220,7 +224,7 @@ def test_gemm_quantised_output_is_the_two_step_chain(df8, oracle, cuda, out_kind
 
 @pytest.mark.parametrize("M,N,K,flags,out_kind", [(8192, 3072, 768, 1, 0), (8192, 2304, 768, 0, 1), (3000, 4096, 512, 0, 0)])
 def test_gemm_quantised_output_one_launch_equals_two_launches(df8, oracle, cuda, monkeypatch, M, N, K, flags, out_kind):
-    """The one-launch form of df8_gemm_fp8_tn_q against the two launches it replaces (DF8_GEMM_FUSED_Q=0): codes,
+    """The one-launch form of df8_gemm_fp8_tn_q (DF8_GEMM_FUSED_Q=1) against the two launches it replaces: codes,
     scale and max|out| identical, repeatedly (the barrier's arrival counters are reused), status word clean."""
     import torch
 
@@ -241,7 +245,7 @@ def test_gemm_quantised_output_one_launch_equals_two_launches(df8, oracle, cuda,
 
     monkeypatch.setenv("DF8_GEMM_FUSED_Q", "0")
     ref = run()
-    monkeypatch.delenv("DF8_GEMM_FUSED_Q")
+    monkeypatch.setenv("DF8_GEMM_FUSED_Q", "1")
     for _ in range(3):
         got = run()
         assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1]) and got[2].item() == ref[2].item()

@@ -1226,10 +1226,11 @@ extern "C" df8_status df8_gemm_fp8_tn_q(const uint8_t* a_codes, df8_kind kind_a,
     }
     // With DF8_GEMM_FUSED_Q=1 in the environment, one launch when the problem qualifies (single-CTA tiles, at least
     // one tile per SM): max|out| over all tiles, a grid-wide barrier, then the codes, with each CTA's last two
-    // accumulator tiles kept in TMEM across the barrier instead of being computed twice.  Not the default: inside a
-    // GPT-2 small forward it is 45 us faster in most processes (3.56 against 3.60 ms) but in about one process in
-    // three 0.1-0.4 ms slower, for the whole process, where the two launches are steady to 0.1 % (the barrier makes
-    // every launch wait for its slowest CTA).
+    // accumulator tiles kept in TMEM across the barrier instead of being computed twice.  Not the default: back to
+    // back it saves 2-4 us per product (34.0 against 35.7 us at 8192 x 2304 x 768), but inside a GPT-2 small forward
+    // the cooperative launches and the wait of every launch for its slowest CTA cost more than that (3.56 against
+    // 3.52 ms per forward), and about one process in three ran another 0.1-0.4 ms slower for its whole life where
+    // the two launches are steady to 0.1 %.
     {
         const char* e = getenv("DF8_GEMM_FUSED_Q");
         bool fused = e && e[0] == '1';

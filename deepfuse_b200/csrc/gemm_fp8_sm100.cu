@@ -27,6 +27,10 @@
 // All mbarrier waits are bounded; a wait that gives up records a code in the status word
 // (df8_status_word_read) and the CTA tears down normally.
 #include "df8_internal.cuh"
+// mbarrier waits of the GEMM kernels sleep up to 1 ms per try (measured: 3.534 -> 3.510 ms per GPT-2 small forward,
+// three runs each on one GPU; the attention kernels, whose waits are short and many, ran 1 % slower with it and
+// keep the default)
+#define DF8_MBAR_SUSPEND_NS 1000000
 #include "sm100_ptx.cuh"
 #include "tensormap.cuh"
 

@@ -69,6 +69,7 @@ _SIGNATURES = {
     "df8_interleave_gathered_u8": [_vp, _i, _i, _i, _vp, _vp],
     "df8_status_word_read": [_vp, _vp],
     "df8_status_word_reset": [],
+    "df8_status_word_check": [],
     "df8_set_amax_preclear": [C.c_int],
 }
 _RESTYPES = {"df8_last_error": C.c_char_p, "df8_version": C.c_char_p}
@@ -223,6 +224,7 @@ _DNN_SIGNATURES = {
     "dnn_selftest_tensor": [_vp, _i],
     "dnn_selftest_context": [_vp, _i],
     "dnn_selftest_errors": [_vp, _i],
+    "dnn_selftest_bounded_wait": [_vp, _i],
     "dnn_set_host_init": [_i],
     "dnn_gpt2cs_destroy": [_vp],
     "dnn_gpt2cs_set_options": [_vp, _i, _i],

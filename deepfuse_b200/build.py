@@ -7,7 +7,7 @@ Produces, under ``deepfuse_b200/lib/``:
 
 * ``libdf8.so``      the C-ABI kernel library declared in ``include/df8.h``
 * ``libdf8_dnn.so``  the C++17 ``dnn::`` classes built on it, plus the small C harness
-                     (``include/df8_dnn_c.h``) that the Python tests and ``bench.py`` drive
+                     (``include/df8_dnn.h``) that the Python tests and ``bench.py`` drive
 
 nvcc cross-compiles for sm_100a without a GPU, so this runs anywhere the CUDA toolkit is installed.
 """

@@ -42,6 +42,7 @@
 #include "sm100_ptx.cuh"
 #include "tensormap.cuh"
 
+#include <atomic>
 #include <cstdlib>
 
 namespace df8 {
@@ -1133,7 +1134,7 @@ attention_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_qkv, const Att
 
 df8_status launch_attention_wide(const CUtensorMap& tm, const AttnArgs& args, dim3 grid, cudaStream_t st) {
     auto kern = attention_fp8_wide_kernel;
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64] = {};
     int dev = 0;
     DF8_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !configured[dev]) {
@@ -1149,7 +1150,7 @@ template <int D>
 df8_status launch_attention(const CUtensorMap& tm, const AttnArgs& args, dim3 grid, cudaStream_t st) {
     using Cfg = AttnCfg<D>;
     auto kern = attention_fp8_kernel<D>;
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64] = {};
     int dev = 0;
     DF8_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !configured[dev]) {

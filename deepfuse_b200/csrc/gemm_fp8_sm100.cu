@@ -952,7 +952,7 @@ df8_status launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tw, const 
                             cudaStream_t st) {
     constexpr int kPairSmemBytes = PairCfg<BN, MODE>::kSmemBytes;
     auto kern = gemm_fp8_tn_pair_kernel<BN, PairCfg<BN, MODE>::kStages, MODE>;
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64] = {};
     int dev = 0;
     DF8_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !configured[dev]) {
@@ -984,7 +984,7 @@ df8_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmA
                        cudaStream_t st) {
     using Cfg = GemmCfg<BN, STAGES, MODE>;
     auto kern = gemm_fp8_tn_kernel<BN, STAGES, MODE>;
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64] = {};
     int dev = 0;
     DF8_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !configured[dev]) {

@@ -412,9 +412,16 @@ bool launch_resident(const float* x, int rows, int C, const float* gamma, const 
     static std::atomic<unsigned int> next_slot{0};
     const int counter_slot = int(next_slot.fetch_add(1u) % unsigned(kResCounters));
     auto launch = [&](auto kern) -> bool {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kResSmemCap) != cudaSuccess) {
-            (void)cudaGetLastError();
-            return false;
+        // once per device and kernel instantiation (this lambda's body is instantiated per kernel type)
+        static std::atomic<bool> configured[64] = {};
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+        if (!configured[dev].load(std::memory_order_acquire)) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kResSmemCap) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return false;
+            }
+            configured[dev].store(true, std::memory_order_release);
         }
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(unsigned(sms));
@@ -549,18 +556,20 @@ static __device__ __align__(256) float g_ln_row_stats[2 * kNoAllocMaxRows];
 // handle for the runtime, not something a kernel may dereference, so the real address is looked up
 // once per device (with that device current) and cached.
 df8_status ln_static_scratch(float** out) {
-    static float* cached[64] = {};
+    // (host threads that make their first call on a device at the same time all look the address up and store
+    // the same value; the atomic only makes that formally race-free)
+    static std::atomic<float*> cached[64] = {};
     int dev = 0;
     DF8_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return fail(DF8_ERR_INVALID, "device index %d out of range", dev);
-    if (!cached[dev]) {
-        float* p = nullptr;
+    float* p = cached[dev].load(std::memory_order_acquire);
+    if (!p) {
         cudaError_t err = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_ln_row_stats);
         if (err != cudaSuccess)
             return fail(DF8_ERR_CUDA, "cudaGetSymbolAddress(g_ln_row_stats) failed: %s", cudaGetErrorString(err));
-        cached[dev] = p;
+        cached[dev].store(p, std::memory_order_release);
     }
-    *out = cached[dev];
+    *out = p;
     return DF8_OK;
 }
 

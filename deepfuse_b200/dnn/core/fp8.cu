@@ -73,6 +73,8 @@ float* amax_slot(float* own) {
     return g_pass.pool + g_pass.next++;
 }
 
+void check_device_status() { utils::CHECK_DF8(df8_status_word_check()); }
+
 void quantize(const float* x, size_t n, df8_kind kind, Quantized& q) {
     if (q.codes.numel() != n) q.codes = tensor<uint8_t>({int(n)});
     q.kind = kind;

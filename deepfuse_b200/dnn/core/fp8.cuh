@@ -38,8 +38,10 @@ struct Quantized {
     tensor<float> scale;  // {q, dq}
     tensor<float> amax;   // 1 element
     df8_kind kind = DF8_E4M3;
+    // amax starts at zero: producers take a running maximum into it, and some callers clear it themselves only
+    // when no PassScope is open
     explicit Quantized(size_t n = 0)
-        : codes({int(n)}), scale({2}), amax({1}) {}
+        : codes({int(n)}), scale({2}), amax({1}) { amax.zero(); }
 };
 
 inline df8_stream stream() { return reinterpret_cast<df8_stream>(Cuda::stream()); }
@@ -60,6 +62,11 @@ public:
 // The float a producer should write max|out| to: a fresh pre-cleared slot inside a PassScope, otherwise
 // `own` (the caller's private buffer, cleared by the library call itself).
 float* amax_slot(float* own);
+
+// Throws std::runtime_error if a bounded device-side wait of the kernel library has given up since the status
+// word was last reset (df8_status_word_check); waits for the device, so callers use it where they synchronise
+// anyway (before handing results to the host).
+void check_device_status();
 
 // q <- per-tensor quantisation of n fp32 values at x (amax pass + quantise pass).
 void quantize(const float* x, size_t n, df8_kind kind, Quantized& q);

@@ -178,6 +178,9 @@ void tensor<TT>::download(TT* host_data) const {
         utils::CHECK_CUDA_EX(
             cudaMemcpyAsync(host_data, data_, total_size_ * sizeof(TT), cudaMemcpyDeviceToHost, Cuda::stream()));
     utils::CHECK_CUDA_EX(cudaStreamSynchronize(Cuda::stream()));
+    // results reach the host here: if a bounded device-side wait of the kernel library gave up on the way, the
+    // data is incomplete, and the caller gets the exception a failed CUDA call would raise
+    utils::CHECK_DF8(df8_status_word_check());
 }
 
 template <typename TT>

@@ -37,7 +37,7 @@ protected:
     uint64_t version_ = 0;
 
 public:
-    explicit tensor(const std::vector<int>& shape);
+    tensor(const std::vector<int>& shape);  // implicit, as upstream's (core/tensor.cuh:34)
     virtual ~tensor();
 
     tensor(const tensor&) = delete;

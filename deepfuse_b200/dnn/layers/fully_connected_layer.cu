@@ -89,6 +89,10 @@ const fp8::Quantized& FullyConnectedLayer<TT>::quantized_weights() {
         if (!shard_comm_) {
             fp8::quantize(src, n, fp8::policy().weight_kind, wq_);
         } else {  // the scale of the whole (sharded) tensor
+            // wq_.amax is the layer's own float, not a pre-cleared slot of a PassScope, and inside a scope the
+            // library does not clear it either: without this memset a lazy re-quantisation during a forward
+            // would take the maximum with whatever the float held (garbage, or the previous weights' maximum)
+            utils::CHECK_CUDA_EX(cudaMemsetAsync(wq_.amax.data(), 0, sizeof(float), Cuda::stream()));
             utils::CHECK_DF8(df8_amax_f32(src, n, wq_.amax.data(), fp8::stream()));
             utils::CHECK_DF8(df8_comm_allreduce_max_f32(shard_comm_, wq_.amax.data(), 1, fp8::stream()));
             fp8::quantize_with_amax(src, n, fp8::policy().weight_kind, wq_.amax.data(), wq_);

@@ -22,8 +22,30 @@
 #include "dnn/models/gpt2.cuh"
 #include "dnn/tokens/positional_encoding.cuh"
 #include "dnn/tokens/token_embedding.cuh"
+#include "df8_internal.cuh"
+#include "sm100_ptx.cuh"
 
 namespace {
+
+// Harness-only kernel: one thread waits, with a limit of `limit_ns`, on an mbarrier that nobody ever arrives at.
+// The wait must come back by itself, record `code` in the library's status word exactly as the GEMM and
+// attention pipelines do when one of their waits gives up, and the kernel must return normally.
+__global__ void wait_that_runs_out_kernel(unsigned int* status, unsigned int code, unsigned long long limit_ns,
+                                          unsigned long long* waited_ns) {
+    __shared__ uint64_t bar;
+    using namespace df8::ptx;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        mbar_fence_init();
+        const uint64_t t0 = globaltimer_ns();
+        const bool completed = mbar_wait_bounded(smem_u32(&bar), 0, limit_ns);
+        *waited_ns = globaltimer_ns() - t0;
+        if (!completed) {
+            atomicCAS(status, 0u, code);
+            atomicAdd(status + 1, 1u);
+        }
+    }
+}
 
 struct Report {
     int failures = 0;
@@ -368,6 +390,72 @@ extern "C" int dnn_selftest_errors(char* report_h, int cap) {
             CHECK(r, throws<std::runtime_error>([&] { Gpt2<float>::load("/nonexistent/model.bin", false); }));
         }
     } catch (const std::exception& e) {
+        r.check(false, e.what(), __LINE__);
+    }
+    return r.finish(report_h, cap);
+}
+
+// The failure path of the bounded device-side waits, made on purpose and without faulting anything: a wait with a
+// 1 ms limit on a barrier nobody arrives at runs out, the status word carries its code, the class layer raises
+// std::runtime_error where results would reach the host (tensor::download), and after a reset the same context
+// computes normally.
+extern "C" int dnn_selftest_bounded_wait(char* report_h, int cap) {
+    Report r;
+    std::unique_ptr<dnn::Cuda> ctx;
+    try {
+        ensure_context(ctx);
+        using namespace dnn;
+        CHECK(r, df8_status_word_reset() == DF8_OK);
+        CHECK(r, df8_status_word_check() == DF8_OK);
+        unsigned int* status = nullptr;
+        CHECK(r, df8::status_word_device_ptr(&status) == DF8_OK && status != nullptr);
+        tensor<float> x({2, 16});
+        x.fill(1.0f);
+        std::vector<float> host(32, 0.f);
+        x.download(host.data());  // clean status word: no exception
+        CHECK(r, host[31] == 1.0f);
+
+        unsigned long long* waited_d = nullptr;
+        utils::CHECK_CUDA_EX(cudaMalloc(&waited_d, sizeof(unsigned long long)));
+        const unsigned int code = 0x7E57u;
+        wait_that_runs_out_kernel<<<1, 32, 0, Cuda::stream()>>>(status, code, 1000000ull, waited_d);
+        utils::CHECK_CUDA_EX(cudaGetLastError());
+        utils::CHECK_CUDA_EX(cudaStreamSynchronize(Cuda::stream()));  // the kernel returned by itself
+        unsigned long long waited = 0;
+        utils::CHECK_CUDA_EX(cudaMemcpy(&waited, waited_d, sizeof(waited), cudaMemcpyDeviceToHost));
+        utils::CHECK_CUDA_EX(cudaFree(waited_d));
+        CHECK(r, waited >= 1000000ull && waited < 500000000ull);  // gave up after the limit, not much later
+
+        unsigned int got_code = 0, count = 0;
+        CHECK(r, df8_status_word_read(&got_code, &count) == DF8_OK);
+        CHECK(r, got_code == code && count == 1);
+        CHECK(r, df8_status_word_check() == DF8_ERR_TIMEOUT);
+        CHECK(r, std::string(df8_last_error()).find("0x7e57") != std::string::npos);
+        // the class layer: the same condition is a std::runtime_error where data would reach the host
+        CHECK(r, throws<std::runtime_error>([&] { x.download(host.data()); }));
+        CHECK(r, throws<std::runtime_error>([&] { fp8::check_device_status(); }));
+        {
+            Gpt2<float> model(nullptr, 50, 16, 1, 1, 64, 128);
+            CHECK(r, throws<std::runtime_error>([&] { model.forward(std::vector<int>{1, 2, 3}); }));
+        }
+        // reset, then the context works as before
+        CHECK(r, df8_status_word_reset() == DF8_OK);
+        CHECK(r, df8_status_word_check() == DF8_OK);
+        {
+            FullyConnectedLayer<float> fc(64, 32);
+            tensor<float> in({4, 64});
+            in.fill(0.5f);
+            tensor<float> out = fc.forward(in);
+            std::vector<float> y(4 * 32, NAN);
+            out.download(y.data());
+            bool finite = true;
+            for (float v : y) finite = finite && std::isfinite(v);
+            CHECK(r, finite);
+            for (int j = 0; j < 32; ++j) CHECK(r, y[size_t(j)] == y[size_t(32 + j)]);  // equal input rows, equal outputs
+        }
+        CHECK(r, df8_status_word_read(&got_code, &count) == DF8_OK && got_code == 0 && count == 0);
+    } catch (const std::exception& e) {
+        df8_status_word_reset();
         r.check(false, e.what(), __LINE__);
     }
     return r.finish(report_h, cap);

@@ -260,6 +260,11 @@ df8_status df8_interleave_gathered_u8(const uint8_t* gathered, int M, int cols_p
  * device (they copy from / to a device symbol); code_h / count_h are HOST pointers. */
 df8_status df8_status_word_read(unsigned int* code_h, unsigned int* count_h);
 df8_status df8_status_word_reset(void);
+/* DF8_OK while the word is clean; DF8_ERR_TIMEOUT (with the first code and the count in df8_last_error()) once a
+ * wait has given up, until df8_status_word_reset().  Results produced after such an event are not to be trusted:
+ * a kernel that gave up left part of its output unwritten.  Synchronises like df8_status_word_read.  The C++
+ * layer turns it into the std::runtime_error upstream raises for a failed CUDA call (dnn/utils/common.cuh:20-35). */
+df8_status df8_status_word_check(void);
 
 #ifdef __cplusplus
 }

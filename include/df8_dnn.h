@@ -100,6 +100,9 @@ int dnn_embedding_forward(int V, int E, int max_len, const float* table_h, const
 int dnn_selftest_tensor(char* report_h, int cap);
 int dnn_selftest_context(char* report_h, int cap);
 int dnn_selftest_errors(char* report_h, int cap);
+/* makes a bounded device-side wait run out (a 1 ms limit on a barrier nobody arrives at; nothing faults or hangs)
+ * and follows the failure to the caller: status word, DF8_ERR_TIMEOUT, std::runtime_error, reset, normal work */
+int dnn_selftest_bounded_wait(char* report_h, int cap);
 
 #ifdef __cplusplus
 }

@@ -89,6 +89,38 @@ def block_forward(p: dict, prefix: str, x: np.ndarray, B: int, T: int, heads: in
     return _fc(f, p[f"{prefix}.fc2.weight"], p[f"{prefix}.fc2.bias"], act_kind, w_kind, residual=x1)
 
 
+def block_trace(p: dict, prefix: str, x: np.ndarray, B: int, T: int, heads: int, act_kind: int, w_kind: int,
+                gelu: bool, mask_mode: int = O.MASK_NONE, mask=None) -> dict:
+    """block_forward with every intermediate kept, so that a test can feed the ORACLE's input into one GPU
+    kernel at a time (a code that flips in one kernel then cannot compound through the chain).  Keys:
+    ln1 / qkv / attn / x1 / ln2 / h / y are fp32 tensors; `<name>_q` = (codes, scale {q, dq}) of the tensors the
+    8-bit path quantises (ln1, qkv, attn, ln2, h); w_<layer> = (codes, scale) of the four weight matrices."""
+    t = {"x": x}
+    qz = lambda a: O.quantize(a, act_kind)
+    for name in ("qkv", "out", "fc1", "fc2"):
+        t[f"w_{name}"] = O.quantize(p[f"{prefix}.{name}.weight"], w_kind)
+
+    def fc(aq, name, residual=None, flags=0):
+        wc, ws = t[f"w_{name}"]
+        return O.fc_forward_fp8(aq[0], act_kind, aq[1][1], wc, w_kind, ws[1], p[f"{prefix}.{name}.bias"], residual,
+                                flags | (O.RESIDUAL if residual is not None else 0))
+
+    t["ln1"] = O.layernorm(x, p[f"{prefix}.ln1.gamma"], p[f"{prefix}.ln1.beta"], 1e-5)
+    t["ln1_q"] = qz(t["ln1"])
+    t["qkv"] = fc(t["ln1_q"], "qkv")
+    t["qkv_q"] = qz(t["qkv"])
+    E = x.shape[1]
+    t["attn"] = O.attention_fp8(t["qkv_q"][0], act_kind, t["qkv_q"][1][1], B, T, heads, E // heads, mask_mode, mask)
+    t["attn_q"] = qz(t["attn"])
+    t["x1"] = fc(t["attn_q"], "out", residual=x)
+    t["ln2"] = O.layernorm(t["x1"], p[f"{prefix}.ln2.gamma"], p[f"{prefix}.ln2.beta"], 1e-5)
+    t["ln2_q"] = qz(t["ln2"])
+    t["h"] = fc(t["ln2_q"], "fc1", flags=O.GELU if gelu else 0)
+    t["h_q"] = qz(t["h"])
+    t["y"] = fc(t["h_q"], "fc2", residual=t["x1"])
+    return t
+
+
 def mha_forward(p: dict, prefix: str, x: np.ndarray, B: int, T: int, heads: int, act_kind: int, w_kind: int,
                 mask_mode: int = O.MASK_NONE, mask=None) -> np.ndarray:
     """MultiHeadAttentionLayer::forward on x [B*T, E]: QKV projection, attention, output projection."""

@@ -1,11 +1,12 @@
 #!/usr/bin/env bash
-# Compiles the upstream project's own fp32 layers for sm_100a, from its sources under $REF (the checkout of the
+# Compiles the upstream project's own fp32 layers for sm_100a, from its sources under $DF8_REFERENCE_DIR (the checkout of the
 # upstream project), into oracle/_ref/libdnn_ref.so.  Only this wrapper (ref_wrap.cu) is ours; no upstream source
 # is copied into the repository and upstream's CMake build is not used (it needs network access for GoogleTest,
 # and TBB for one app).  Output goes to oracle/_ref/ only, which is git-ignored.
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-REF="${REF:-/root/reference}"
+# the upstream checkout: $DF8_REFERENCE_DIR, else a directory named "reference" beside this repository
+REF="${DF8_REFERENCE_DIR:-${REF:-$HERE/../../reference}}"
 OUT="$HERE/_ref"
 NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"
 if [ ! -d "$REF/dnn" ]; then

@@ -32,7 +32,7 @@ def dnn(df8, cuda):
     return lib
 
 
-@pytest.mark.parametrize("which", ["tensor", "context", "errors"])
+@pytest.mark.parametrize("which", ["tensor", "context", "errors", "bounded_wait"])
 def test_cpp_selftests(df8, dnn, which):
     buf = C.create_string_buffer(1 << 14)
     failures = getattr(dnn, f"dnn_selftest_{which}")(buf, len(buf))

@@ -43,8 +43,13 @@ def test_noalloc_matches_scratch_variant_twice_in_a_row(df8, oracle, cuda, kind)
         assert torch.equal(c0, c1), f"call {call}: {(c0 != c1).sum().item()} codes differ"
 
 
-def test_noalloc_rejects_more_rows_than_the_builtin_scratch(df8, cuda):
+def test_noalloc_rejects_more_rows_than_the_builtin_scratch(df8, cuda, monkeypatch):
     import torch
+
+    # 65536 rows of 4 columns would qualify for the one-launch kernel that keeps the rows in shared memory and
+    # needs no row scratch at all; switch it off (the variable is read at every call) so that both entry points
+    # take the two-kernel path and the built-in array is written and read over its whole extent
+    monkeypatch.setenv("DF8_LN_RESIDENT", "0")
 
     x = torch.zeros(16, device=cuda)
     codes = torch.zeros(16, dtype=torch.uint8, device=cuda)

@@ -54,12 +54,16 @@ constexpr int kOutF32 = 1;      // fp32, any N
 constexpr int kOutE4M3 = 2;     // fp8 codes, N % 16 == 0
 constexpr int kOutE5M2 = 3;
 constexpr int kOutNone = 4;     // max|out| only
+constexpr int kOutF32Tma = 5;   // fp32 through TMA stores: row pitch a multiple of 4 floats, no residual, 256-column tiles
+
+// the modes whose epilogue works thread = row straight from registers (fp8 codes, max|out| only)
+__host__ __device__ constexpr bool is_direct(int mode) { return mode == kOutE4M3 || mode == kOutE5M2 || mode == kOutNone; }
 
 // Epilogue warps of the single-CTA kernel.  The fp32 modes are bound by their global stores and run two
 // warps per TMEM lane quarter; the fp8 / amax-only modes are a chain of latencies (TMEM load, conversion,
 // GELU) with nothing to store or little, and run four per quarter so that each SM sub-partition has four
 // warps to interleave.
-__host__ __device__ constexpr int epi_warps(int mode) { return mode >= kOutE4M3 ? 16 : 8; }
+__host__ __device__ constexpr int epi_warps(int mode) { return is_direct(mode) ? 16 : 8; }
 // per-warp staging bytes of the fp8 / amax modes: the bias slice (64 floats) and, for fp8 output, the codes tile
 __host__ __device__ constexpr int direct_staging_bytes(int mode) { return mode == kOutNone ? 256 : 256 + 2048; }
 __host__ __device__ constexpr int gemm_threads(int mode) { return 64 + 32 * epi_warps(mode); }
@@ -75,6 +79,8 @@ struct GemmArgs {
     const float* q_amax;    // max|out| the fp8 output scale is derived from (fp8 modes)
     float* out_scale;       // {q, dq} of the fp8 output, written by CTA 0 (fp8 modes), or null
     int M, N, K;
+    int ldc;                // row pitch, in floats, of `out` and `residual` (fp32 modes)
+    int a_slab_cols;        // A is stored as K / a_slab_cols row-major [M, a_slab_cols] slabs (K when it is one matrix)
     int flags;
     uint32_t idesc;
     unsigned int* status;
@@ -87,8 +93,16 @@ struct GemmArgs {
 constexpr int kFusedCounters = 64;
 __device__ unsigned int g_gemm_grid_counter[kFusedCounters] = {};
 
+// TMA-store mode: two 32 x 32 fp32 boxes (4 KB each, 1024-byte aligned) per epilogue warp, then each warp's bias
+// slice (its four chunks of a 256-column tile)
+constexpr int kTmaBoxBytes = 32 * 32 * 4;
+constexpr int kTmaBiasFloatsPerWarp = 128;
+__host__ __device__ constexpr int tma_staging_bytes() { return kEpiWarps * (2 * kTmaBoxBytes + kTmaBiasFloatsPerWarp * 4); }
+
 __host__ __device__ constexpr int pair_staging_bytes(int mode) {
-    return mode >= kOutE4M3 ? epi_warps(mode) * direct_staging_bytes(mode) : kEpiWarps * kStagingFloatsPerWarp * 4;
+    return mode == kOutF32Tma ? tma_staging_bytes()
+           : is_direct(mode)  ? epi_warps(mode) * direct_staging_bytes(mode)
+                              : kEpiWarps * kStagingFloatsPerWarp * 4;
 }
 
 template <int BN, int STAGES, int MODE>
@@ -97,8 +111,7 @@ struct GemmCfg {
     static constexpr int kBBytes = BN * BK;
     static constexpr int kStageBytes = kABytes + kBBytes;
     // fp32 modes: a transpose buffer per epilogue warp; fp8 / amax modes: only each warp's bias slice
-    static constexpr int kStagingBytes =
-        MODE >= kOutE4M3 ? epi_warps(MODE) * direct_staging_bytes(MODE) : kEpiWarps * kStagingFloatsPerWarp * 4;
+    static constexpr int kStagingBytes = pair_staging_bytes(MODE);
     static constexpr int kBarBytes = 256;
     static constexpr int kSmemBytes = STAGES * kStageBytes + kStagingBytes + kBarBytes + 1024;
     static constexpr int kTmemCols = 2 * BN;
@@ -152,7 +165,7 @@ __device__ __forceinline__ void load_residual_vec4(float4 (&rs)[8], int lane, in
     for (int it = 0; it < 8; ++it) {
         const int rl = it * 4 + (lane >> 3);
         if ((a.flags & 2) && row0 + rl < a.M && gcol < a.N)
-            rs[it] = *reinterpret_cast<const float4*>(a.residual + size_t(row0 + rl) * a.N + gcol);
+            rs[it] = *reinterpret_cast<const float4*>(a.residual + size_t(row0 + rl) * a.ldc + gcol);
         else
             rs[it] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
@@ -166,8 +179,19 @@ __device__ __forceinline__ void store_chunk_f32(const float* stg, int lane, int 
         const int cq = (lane & 7) * 4;
         const int gcol = col0 + cq;
         const bool col_ok = gcol < a.N;
+        // N need not be a multiple of 4 when the row pitch is: the last group of a row then hangs over N by up to
+        // three columns, which land in the pitch padding; only the bias read and the maximum must stop at N
+        const bool whole = gcol + 4 <= a.N;
         float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (a.bias && col_ok) b4 = *reinterpret_cast<const float4*>(a.bias + gcol);
+        if (a.bias && col_ok) {
+            if (whole) {
+                b4 = *reinterpret_cast<const float4*>(a.bias + gcol);
+            } else {
+                b4.x = a.bias[gcol];
+                if (gcol + 1 < a.N) b4.y = a.bias[gcol + 1];
+                if (gcol + 2 < a.N) b4.z = a.bias[gcol + 2];
+            }
+        }
         float4 v[8];
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
@@ -195,8 +219,14 @@ __device__ __forceinline__ void store_chunk_f32(const float* stg, int lane, int 
                 o.w += rs[it].w;
             }
             if (grow < a.M && col_ok) {
-                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w))));
-                *reinterpret_cast<float4*>(a.out + size_t(grow) * a.N + gcol) = o;
+                if (whole) {
+                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w))));
+                } else {
+                    amax = fmaxf(amax, fabsf(o.x));
+                    if (gcol + 1 < a.N) amax = fmaxf(amax, fabsf(o.y));
+                    if (gcol + 2 < a.N) amax = fmaxf(amax, fabsf(o.z));
+                }
+                *reinterpret_cast<float4*>(a.out + size_t(grow) * a.ldc + gcol) = o;
             }
         }
     } else {
@@ -206,8 +236,8 @@ __device__ __forceinline__ void store_chunk_f32(const float* stg, int lane, int 
         if (gcol < a.N) {
             const float b = a.bias ? a.bias[gcol] : 0.f;
             const int rows = min(32, a.M - row0);
-            float* dst = a.out + size_t(row0) * a.N + gcol;
-            const float* res = (a.flags & 2) ? a.residual + size_t(row0) * a.N + gcol : nullptr;
+            float* dst = a.out + size_t(row0) * a.ldc + gcol;
+            const float* res = (a.flags & 2) ? a.residual + size_t(row0) * a.ldc + gcol : nullptr;
             const bool gelu = (a.flags & 1) != 0;
             if (rows == 32 && !res && !gelu) {
 #pragma unroll
@@ -215,7 +245,7 @@ __device__ __forceinline__ void store_chunk_f32(const float* stg, int lane, int 
                     const float v = fmaf(stg[rl * 33 + lane], alpha, b);
                     amax = fmaxf(amax, fabsf(v));
                     *dst = v;
-                    dst += a.N;
+                    dst += a.ldc;
                 }
             } else {
                 for (int rl = 0; rl < rows; ++rl) {
@@ -223,11 +253,11 @@ __device__ __forceinline__ void store_chunk_f32(const float* stg, int lane, int 
                     if (gelu) v = gelu_tanh(v);
                     if (res) {
                         v += *res;
-                        res += a.N;
+                        res += a.ldc;
                     }
                     amax = fmaxf(amax, fabsf(v));
                     *dst = v;
-                    dst += a.N;
+                    dst += a.ldc;
                 }
             }
         }
@@ -294,6 +324,98 @@ __device__ __forceinline__ void store_staged_codes(const uint8_t* stg, int lane,
         if (row0 + rr < a.M && col0 + 16 * p < a.N)
             *reinterpret_cast<uint4*>(a.out_codes + size_t(row0 + rr) * a.N + col0 + 16 * p) = v;
     }
+}
+
+// ---- fp32 output through TMA stores (kOutF32Tma) ----------------------------------------------------
+//
+// thread = row.  A 32 x 32 chunk is scaled, biased (and GELU'd) in registers and parked in one of the warp's two
+// 4 KB boxes in the 128-byte-swizzled layout of the output tensor map (16-byte piece c of row r at piece c ^ (r & 7):
+// neither these writes nor the copy engine's reads conflict); one cp.async.bulk.tensor store then takes the box
+// to global memory while the warp works on the next chunk.  The store clips rows >= M and columns >= N itself,
+// so edge tiles need no predication and the pitch padding of a row is never written.  Against the transpose
+// through shared memory + 128-bit st.global of the other fp32 modes this takes the global stores (and the
+// second pass over shared memory) off the warps: the vocabulary head, whose 1.6 GB of logits make the epilogue
+// the longest phase of a tile, is the case it is for.
+// `box_it` counts the warp's stores over the whole kernel (box box_it & 1 is the next one to fill).  Returns
+// false when the wait for the accumulators gave up.
+template <int BN, typename ReleaseFn>
+__device__ __forceinline__ bool epilogue_tile_f32_tma(const CUtensorMap* tma_out, const GemmArgs& args, uint8_t* boxes,
+                                                      float* sbias, uint32_t tfull_bar, uint32_t acc_phase,
+                                                      uint32_t taddr, int row0, int n0, int half, int lane,
+                                                      float alpha, float& amax, uint32_t& box_it, ReleaseFn release) {
+    constexpr int kChunks = BN / 64;
+    static_assert(kChunks * 32 <= kTmaBiasFloatsPerWarp, "bias slice");
+#pragma unroll
+    for (int j = 0; j < kChunks; ++j) {
+        const int col = n0 + 32 * (half + 2 * j) + lane;
+        sbias[j * 32 + lane] = (args.bias && col < args.N) ? __ldg(args.bias + col) : 0.f;
+    }
+    __syncwarp();
+    if (!mbar_wait_bounded(tfull_bar, acc_phase)) return false;
+    tc_fence_after_sync();
+    int nvalid = 0;
+#pragma unroll
+    for (int j = 0; j < kChunks; ++j)
+        if (n0 + 32 * (half + 2 * j) < args.N) nvalid = j + 1;
+    uint32_t r[32];
+    if (nvalid > 0) tmem_ld_32x32(taddr + 32 * half, r);
+    const bool row_ok = row0 + lane < args.M;
+    for (int j = 0; j < nvalid; ++j) {
+        const int col0 = n0 + 32 * (half + 2 * j);
+        uint8_t* box = boxes + (box_it & 1u) * kTmaBoxBytes;
+        // the store that last read this box (two stores ago) must be done reading it
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        tmem_ld_wait();
+        const float* sb = sbias + j * 32;
+        const bool full = col0 + 32 <= args.N;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            const float4 b4 = *reinterpret_cast<const float4*>(sb + 4 * g);  // broadcast read
+            float4 o;
+            o.x = fmaf(__uint_as_float(r[4 * g]), alpha, b4.x);
+            o.y = fmaf(__uint_as_float(r[4 * g + 1]), alpha, b4.y);
+            o.z = fmaf(__uint_as_float(r[4 * g + 2]), alpha, b4.z);
+            o.w = fmaf(__uint_as_float(r[4 * g + 3]), alpha, b4.w);
+            if (args.flags & 1) {
+                o.x = gelu_tanh(o.x);
+                o.y = gelu_tanh(o.y);
+                o.z = gelu_tanh(o.z);
+                o.w = gelu_tanh(o.w);
+            }
+            if ((args.flags & 4) && row_ok) {
+                if (full) {
+                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w))));
+                } else {
+                    const int c = col0 + 4 * g;
+                    if (c < args.N) amax = fmaxf(amax, fabsf(o.x));
+                    if (c + 1 < args.N) amax = fmaxf(amax, fabsf(o.y));
+                    if (c + 2 < args.N) amax = fmaxf(amax, fabsf(o.z));
+                    if (c + 3 < args.N) amax = fmaxf(amax, fabsf(o.w));
+                }
+            }
+            *reinterpret_cast<float4*>(box + lane * 128 + ((g ^ (lane & 7)) << 4)) = o;
+        }
+        fence_proxy_async_smem();  // each lane's writes become visible to the copy engine
+        __syncwarp();
+        if (j + 1 < nvalid) {
+            tmem_ld_32x32(taddr + 32 * (half + 2 * (j + 1)), r);  // in flight while the store is issued
+        } else {
+            tc_fence_before_sync();  // the tile's last chunk is out of TMEM: hand the buffer back
+            release();
+        }
+        if (lane == 0) {
+            tma_store_2d(tma_out, smem_u32(box), col0, row0);
+            tma_store_commit();
+        }
+        ++box_it;
+    }
+    if (nvalid == 0) {
+        tc_fence_before_sync();
+        __syncwarp();
+        release();
+    }
+    return true;
 }
 
 // FUSED (fp8 modes only): the one-launch max|out| + codes form, an instantiation of its own so that the plain

@@ -1,8 +1,9 @@
 """GPU parity of the fp8 attention kernel (df8_attention_fp8) against the CPU oracle.
 
-Tolerance: max |y - y_ref| / max |y_ref| <= 1e-2 per output tensor, y_ref = the oracle's attention on the
-dequantised Q, K, V with double accumulation and an unquantised softmax.  The kernel rounds the block
-probabilities to e4m3 before the PV product, which is where the difference comes from."""
+Tolerance: max |y - y_ref| / max |y_ref| <= 1e-2 per output tensor, for e4m3 and for e5m2 codes alike; y_ref =
+the oracle's attention on the dequantised Q, K, V with double accumulation and an unquantised softmax.  The
+kernel keeps the block probabilities as half-precision numbers for the PV product (V widened exactly from its
+codes) and evaluates exp2 with the hardware approximation; measured differences are below 1e-3."""
 import numpy as np
 import pytest
 
@@ -87,7 +88,7 @@ def test_attention_soft_additive_mask_and_fully_masked_rows(df8, oracle, cuda):
 def test_attention_kinds_and_peaked_scores(df8, oracle, cuda, kind):
     """Larger activations make the softmax peaked (few dominant keys): the hard case for e4m3 probabilities."""
     y, ref, _ = run_attention(df8, oracle, cuda, 1, 256, 2, 64, kind=kind, seed=17, std=3.0)
-    assert rel_err(y, ref) <= (TOL if kind == 0 else 2.5e-2), describe(y, ref)
+    assert rel_err(y, ref) <= TOL, describe(y, ref)
 
 
 def test_attention_gpt2_small_shape_sampled(df8, oracle, cuda):
@@ -129,8 +130,7 @@ def test_attention_two_tile_kernel(df8, oracle, cuda, monkeypatch, B, T, H, mask
     y2, ref, amax2 = run_attention(df8, oracle, cuda, B, T, H, 64, kind=kind, mask_mode=mask_mode, mask=mask, seed=T + H)
     monkeypatch.setenv("DF8_ATTN_WIDE", "0")
     y1, _, amax1 = run_attention(df8, oracle, cuda, B, T, H, 64, kind=kind, mask_mode=mask_mode, mask=mask, seed=T + H)
-    tol = TOL if kind == 0 else 2.5e-2
-    assert rel_err(y2, ref) <= tol, describe(y2, ref)
+    assert rel_err(y2, ref) <= TOL, describe(y2, ref)
     assert rel_err(y2, y1) <= 3e-3, describe(y2, y1)
     assert amax2 == np.abs(y2).max()
     if mask_mode == 2:

@@ -41,6 +41,9 @@ _SIGNATURES = {
     "df8_quantize_f32": [_vp, _sz, _i, _vp, _vp, _vp, _vp],
     "df8_dequantize_f32": [_vp, _sz, _i, _vp, _vp, _vp],
     "df8_gemm_fp8_tn": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp],
+    "df8_gemm_fp8_tn_ex": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp],
+    "df8_gemm_fp8_tn_amax_ex": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
+    "df8_gemm_fp8_tn_codes_ex": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     "df8_layernorm_f32": [_vp, _i, _i, _vp, _vp, _f, _vp, _vp, _vp],
     "df8_layernorm_quantize_f32": [_vp, _i, _i, _vp, _vp, _f, _i, _vp, _vp, _vp, _vp, _vp],
     "df8_layernorm_quantize_f32_noalloc": [_vp, _i, _i, _vp, _vp, _f, _i, _vp, _vp, _vp, _vp],
@@ -141,6 +144,13 @@ def gemm_fp8_tn(a_codes, kind_a, scale_a, w_codes, kind_w, scale_w, bias, residu
           "df8_gemm_fp8_tn")
 
 
+def gemm_fp8_tn_ex(a_codes, kind_a, scale_a, a_slabs, w_codes, kind_w, scale_w, bias, residual, M, N, K, flags, out, ldc,
+                   out_amax=None, stream=None) -> None:
+    check(lib().df8_gemm_fp8_tn_ex(ptr(a_codes), kind_a, ptr(scale_a), a_slabs, ptr(w_codes), kind_w, ptr(scale_w),
+                                   ptr(bias), ptr(residual), M, N, K, flags, ptr(out), ldc, ptr(out_amax),
+                                   stream_ptr(stream)), "df8_gemm_fp8_tn_ex")
+
+
 def gemm_fp8_tn_q(a_codes, kind_a, scale_a, w_codes, kind_w, scale_w, bias, M, N, K, flags, out_kind, out_codes,
                   out_scale, out_amax, stream=None) -> None:
     check(lib().df8_gemm_fp8_tn_q(ptr(a_codes), kind_a, ptr(scale_a), ptr(w_codes), kind_w, ptr(scale_w), ptr(bias),
@@ -211,6 +221,8 @@ _DNN_SIGNATURES = {
     "dnn_gpt2_forward_logits": [_vp, _vp, _i, _i, _i, _vp],
     "dnn_gpt2_forward_logits_host": [_vp, _vp, _i, _i, _vp],
     "dnn_gpt2_forward_hidden": [_vp, _vp, _i, _i, _vp],
+    "dnn_gpt2_forward_logits_pitched": [_vp, _vp, _i, _i, _i, _i, _vp, _vp],
+    "dnn_gpt2_copy_logits_host": [_vp, _vp],
     "dnn_gpt2_forward_ids": [_vp, _vp, _i, _vp],
     "dnn_gpt2_save": [_vp, C.c_char_p],
     "dnn_gpt2_enable_streaming": [_vp, _i, _i],
@@ -348,6 +360,21 @@ class Gpt2:
         dnn_check(dnn_lib().dnn_gpt2_forward_logits_host(self.h, ids_host.data_ptr(), B, T, C.byref(out)),
                   "dnn_gpt2_forward_logits_host")
         return out.value
+
+    def forward_logits_pitched(self, ids, check_ids=True) -> tuple[int, int]:
+        """ids: torch int32 tensor [B,T] on the device, or pinned on the host (uploaded inside the call).  Returns
+        (device pointer, pitch): fp32 logits [B*T, pitch] whose first `vocab` columns of every row are valid."""
+        out, pitch = C.c_void_p(0), C.c_int(0)
+        B, T = ids.shape
+        on_host = 0 if ids.is_cuda else 1
+        dnn_check(dnn_lib().dnn_gpt2_forward_logits_pitched(self.h, ids.data_ptr(), on_host, B, T, int(check_ids),
+                                                            C.byref(out), C.byref(pitch)),
+                  "dnn_gpt2_forward_logits_pitched")
+        return out.value, pitch.value
+
+    def copy_logits_host(self, dst_host) -> None:
+        """Enqueues the copy of the last logits into the dense (pinned) host tensor [B*T, vocab]."""
+        dnn_check(dnn_lib().dnn_gpt2_copy_logits_host(self.h, dst_host.data_ptr()), "dnn_gpt2_copy_logits_host")
 
     def forward_hidden(self, ids_dev) -> int:
         out = C.c_void_p(0)

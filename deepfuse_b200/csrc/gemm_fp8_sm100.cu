@@ -423,7 +423,7 @@ __device__ __forceinline__ bool epilogue_tile_f32_tma(const CUtensorMap* tma_out
 template <int BN, int STAGES, int MODE, bool FUSED = false>
 __global__ void __launch_bounds__(gemm_threads(MODE), 1)
 gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_w,
-                   const GemmArgs args) {
+                   const __grid_constant__ CUtensorMap tma_out, const GemmArgs args) {
     static_assert(!FUSED || MODE == kOutE4M3 || MODE == kOutE5M2, "the fused form emits fp8 codes");
     using Cfg = GemmCfg<BN, STAGES, MODE>;
     constexpr int EW = epi_warps(MODE);
@@ -482,10 +482,12 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            if constexpr (MODE == kOutF32Tma) prefetch_tensormap(&tma_out);
             for (int i = 0; i < seq_len && ok; ++i) {
                 const int tile = seq_tile(i);
                 const int m0 = (tile % num_m) * BM;
                 const int n0 = (tile / num_m) * BN;
+                int ax = 0, aslab = 0;  // A's K coordinate: column inside its slab, slab index
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait_bounded(smem_u32(empty + stage), phase ^ 1)) {
                         record_timeout(args.status, 0x100u + stage);
@@ -495,8 +497,13 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
                     const uint32_t fb = smem_u32(full + stage);
                     uint8_t* sa = smem + stage * Cfg::kStageBytes;
                     mbar_arrive_expect_tx(fb, Cfg::kStageBytes);
-                    tma_load_2d(smem_u32(sa), &tma_a, fb, kb * BK, m0);
+                    tma_load_3d(smem_u32(sa), &tma_a, fb, ax, m0, aslab);
                     tma_load_2d(smem_u32(sa + Cfg::kABytes), &tma_w, fb, kb * BK, n0);
+                    ax += BK;
+                    if (ax >= args.a_slab_cols) {
+                        ax = 0;
+                        ++aslab;
+                    }
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1;
@@ -576,6 +583,7 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
         }
         const uint32_t lane_addr = uint32_t(q * 32) << 16;
         uint32_t acc_it = 0;
+        uint32_t box_it = 0;  // TMA-store mode: running count of this warp's stores (alternates its two boxes)
         float amax = 0.f;  // max|out| over all of this warp's tiles: one atomic per warp at the end
         if constexpr (MODE == kOutE4M3 || MODE == kOutE5M2) {
             if (fused) {
@@ -686,7 +694,21 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
             const int n0 = (tile / num_m) * BN;
             const int row0 = m0 + q * 32;
             const uint32_t taddr = tmem_base + buf * BN + lane_addr;
-            if constexpr (MODE >= kOutE4M3) {
+            if constexpr (MODE == kOutF32Tma) {
+                uint8_t* boxes = reinterpret_cast<uint8_t*>(staging) + e * (2 * kTmaBoxBytes);
+                float* sbias = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(staging) + kEpiWarps * 2 * kTmaBoxBytes) +
+                               e * kTmaBiasFloatsPerWarp;
+                auto release = [&] {
+                    if (lane == 0) mbar_arrive(smem_u32(tempty + buf));
+                };
+                if (!epilogue_tile_f32_tma<BN>(&tma_out, args, boxes, sbias, smem_u32(tfull + buf), acc_phase, taddr, row0,
+                                               n0, half, lane, alpha, amax, box_it, release)) {
+                    if (lane == 0) record_timeout(args.status, 0x400u + buf);
+                    break;
+                }
+                continue;
+            }
+            if constexpr (is_direct(MODE)) {
                 // Four warps per lane quarter; warp `part` takes the 32-column chunks part, part + 4, ...
                 // Its bias slice goes to shared memory before the accumulators are waited for; the chunks
                 // are pulled into registers in one go and the TMEM buffer is handed back before any math.
@@ -777,6 +799,10 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
             amax = warp_max(amax);
             if (lane == 0 && amax > 0.f) atomic_max_nonneg(args.out_amax, amax);
         }
+        if constexpr (MODE == kOutF32Tma) {
+            if (lane == 0) tma_store_wait_all();  // this thread's stores are complete before the CTA goes away
+        }
+        (void)box_it;
     }
 
     tc_fence_before_sync();
@@ -802,8 +828,9 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(gemm_threads(MODE), 1)
 gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_w,
-                        const GemmArgs args) {
-    static_assert(BN == 256 || (BN == 192 && MODE < kOutE4M3), "192-column pair tiles exist for the fp32 modes only");
+                        const __grid_constant__ CUtensorMap tma_out, const GemmArgs args) {
+    static_assert(BN == 256 || (BN == 192 && (MODE == kOutF32Vec || MODE == kOutF32)),
+                  "192-column pair tiles exist for the st.global fp32 modes only");
     constexpr int kABytes = BM * BK, kBBytes = (BN / 2) * BK, kStageBytes = kABytes + kBBytes;
     constexpr int EW = epi_warps(MODE);
     // fp32 modes: a transpose buffer per warp; fp8 codes: bias slice + codes tile per warp; max|out| only: bias slices
@@ -862,9 +889,11 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            if constexpr (MODE == kOutF32Tma) prefetch_tensormap(&tma_out);
             for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
                 const int m0 = (tile % num_m) * 2 * BM + int(rank) * BM;
                 const int n0 = (tile / num_m) * BN + int(rank) * (BN / 2);
+                int ax = 0, aslab = 0;  // A's K coordinate: column inside its slab, slab index
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait_bounded(smem_u32(empty + stage), phase ^ 1)) {
                         record_timeout(args.status, 0x2100u + (rank << 4) + stage);
@@ -874,8 +903,13 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
                     const uint32_t fb = map_to_cta(smem_u32(full + stage), 0);
                     uint8_t* sa = smem + stage * kStageBytes;
                     if (leader) mbar_arrive_expect_tx(smem_u32(full + stage), 2 * kStageBytes);
-                    tma_load_2d_pair(smem_u32(sa), &tma_a, fb, kb * BK, m0);
+                    tma_load_3d_pair(smem_u32(sa), &tma_a, fb, ax, m0, aslab);
                     tma_load_2d_pair(smem_u32(sa + kABytes), &tma_w, fb, kb * BK, n0);
+                    ax += BK;
+                    if (ax >= args.a_slab_cols) {
+                        ax = 0;
+                        ++aslab;
+                    }
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1;
@@ -951,6 +985,7 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
             }
         };
         uint32_t acc_it = 0;
+        uint32_t box_it = 0;
         float amax = 0.f;
         for (int tile = pair; tile < num_tiles; tile += npairs, ++acc_it) {
             const uint32_t buf = acc_it & 1;
@@ -959,7 +994,19 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
             const int n0 = (tile / num_m) * BN;
             const int row0 = m0 + q * 32;
             const uint32_t taddr = tmem_base + buf * BN + lane_addr;
-            if constexpr (MODE >= kOutE4M3) {  // as in the single-CTA kernel
+            if constexpr (MODE == kOutF32Tma) {  // as in the single-CTA kernel
+                uint8_t* boxes = reinterpret_cast<uint8_t*>(staging) + e * (2 * kTmaBoxBytes);
+                float* sbias = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(staging) + kEpiWarps * 2 * kTmaBoxBytes) +
+                               e * kTmaBiasFloatsPerWarp;
+                auto release_buf = [&] { release(buf); };
+                if (!epilogue_tile_f32_tma<BN>(&tma_out, args, boxes, sbias, smem_u32(tfull + buf), acc_phase, taddr, row0,
+                                               n0, half, lane, alpha, amax, box_it, release_buf)) {
+                    if (lane == 0) record_timeout(args.status, 0x2400u + (rank << 4) + buf);
+                    break;
+                }
+                continue;
+            }
+            if constexpr (is_direct(MODE)) {  // as in the single-CTA kernel
                 constexpr int KIND = MODE == kOutE4M3 ? int(DF8_E4M3) : (MODE == kOutE5M2 ? int(DF8_E5M2) : -1);
                 constexpr int kParts = EW / 4;
                 constexpr int kCh = BN / (32 * kParts);
@@ -1047,6 +1094,10 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
             amax = warp_max(amax);
             if (lane == 0 && amax > 0.f) atomic_max_nonneg(args.out_amax, amax);
         }
+        if constexpr (MODE == kOutF32Tma) {
+            if (lane == 0) tma_store_wait_all();
+        }
+        (void)box_it;
     }
 
     // neither CTA may leave while its partner can still read its shared memory or signal its barriers
@@ -1064,14 +1115,14 @@ template <int BN, int MODE>
 struct PairCfg {
     // ring depth: the operand loads are latency-bound (~2.4 k cycles from issue to arrival with every SM loading),
     // so as many stages as fit beside the epilogue's staging
-    static constexpr int kStages = (BN == 192 || MODE == kOutNone) ? 6 : 5;
+    static constexpr int kStages = MODE == kOutF32Tma ? 4 : ((BN == 192 || MODE == kOutNone) ? 6 : 5);
     static constexpr int kSmemBytes = kStages * (BM * BK + (BN / 2) * BK) + pair_staging_bytes(MODE) + 256 + 1024;
     static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
 
 template <int BN, int MODE>
-df8_status launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tw, const GemmArgs& args, int grid,
-                            cudaStream_t st) {
+df8_status launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& to, const GemmArgs& args,
+                            int grid, cudaStream_t st) {
     constexpr int kPairSmemBytes = PairCfg<BN, MODE>::kSmemBytes;
     auto kern = gemm_fp8_tn_pair_kernel<BN, PairCfg<BN, MODE>::kStages, MODE>;
     static std::atomic<bool> configured[64] = {};
@@ -1095,15 +1146,15 @@ df8_status launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tw, const 
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    cudaError_t err = cudaLaunchKernelEx(&cfg, kern, ta, tw, args);
+    cudaError_t err = cudaLaunchKernelEx(&cfg, kern, ta, tw, to, args);
     if (err != cudaSuccess)
         return fail(DF8_ERR_CUDA, "launch of gemm_fp8_tn_pair_kernel failed: %s", cudaGetErrorString(err));
     return DF8_OK;
 }
 
 template <int BN, int STAGES, int MODE>
-df8_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmArgs& args, int grid,
-                       cudaStream_t st) {
+df8_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& to, const GemmArgs& args,
+                       int grid, cudaStream_t st) {
     using Cfg = GemmCfg<BN, STAGES, MODE>;
     auto kern = gemm_fp8_tn_kernel<BN, STAGES, MODE>;
     static std::atomic<bool> configured[64] = {};
@@ -1132,7 +1183,7 @@ df8_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmA
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = pdl_enabled() ? 2 : 1;
-        cudaError_t err = cudaLaunchKernelEx(&cfg, fkern, ta, tw, args);
+        cudaError_t err = cudaLaunchKernelEx(&cfg, fkern, ta, tw, to, args);
         if (err != cudaSuccess) {
             (void)cudaGetLastError();
             return DF8_ERR_UNSUPPORTED;  // not co-schedulable here: the caller falls back to two launches
@@ -1142,21 +1193,23 @@ df8_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmA
             return fail(DF8_ERR_INVALID, "the one-launch form exists for the fp8 output modes only");
         }
     }
-    cudaError_t err = launch_kernel(kern, dim3(unsigned(grid)), dim3(gemm_threads(MODE)), Cfg::kSmemBytes, st, ta, tw, args);
+    cudaError_t err = launch_kernel(kern, dim3(unsigned(grid)), dim3(gemm_threads(MODE)), Cfg::kSmemBytes, st, ta, tw, to, args);
     if (err != cudaSuccess) return fail(DF8_ERR_CUDA, "launch of gemm_fp8_tn_kernel failed: %s", cudaGetErrorString(err));
     return DF8_OK;
 }
 
 template <int MODE>
-df8_status launch_gemm_bn(bool wide, const CUtensorMap& ta, const CUtensorMap& tw, const GemmArgs& args, int grid,
-                          cudaStream_t st) {
+df8_status launch_gemm_bn(bool wide, const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& to,
+                          const GemmArgs& args, int grid, cudaStream_t st) {
     // ring depth: whatever fits beside the epilogue's staging.  One K block of operands takes ~1300 cycles to
     // arrive from L2 and ~512 (256 at BN = 128) to consume, so three 48 KB stages leave the tensor core waiting;
     // the fp8 / amax modes need no transpose buffer and get a deeper ring.
     if constexpr (MODE == kOutNone)
-        return wide ? launch_gemm<256, 4, MODE>(ta, tw, args, grid, st) : launch_gemm<128, 6, MODE>(ta, tw, args, grid, st);
+        return wide ? launch_gemm<256, 4, MODE>(ta, tw, to, args, grid, st) : launch_gemm<128, 6, MODE>(ta, tw, to, args, grid, st);
+    else if constexpr (MODE == kOutF32Tma)  // 256-column tiles only (run_gemm falls back to the st.global modes otherwise)
+        return launch_gemm<256, 3, MODE>(ta, tw, to, args, grid, st);
     else
-        return wide ? launch_gemm<256, 3, MODE>(ta, tw, args, grid, st) : launch_gemm<128, 5, MODE>(ta, tw, args, grid, st);
+        return wide ? launch_gemm<256, 3, MODE>(ta, tw, to, args, grid, st) : launch_gemm<128, 5, MODE>(ta, tw, to, args, grid, st);
 }
 
 // DF8_GEMM_PAIR=0 / 1 in the environment (read at every call) forces the choice for profiling and tests;
@@ -1172,18 +1225,38 @@ bool use_pair_kernel(int M, int N, int K, int sms) {
 }
 
 // Shared host path of the entry points: picks the tile width, encodes the tensor maps, launches `mode`.
+// `a_slabs`: A's K dimension is stored as that many row-major [M, K / a_slabs] slabs, M * K / a_slabs bytes apart
+// (what an all-gather of per-rank column slices leaves); 1 = an ordinary [M, K] matrix.
+// `tma_fallback`: the st.global fp32 mode to use where the TMA-store mode does not apply (narrow tiles).
 // `fused`: in: try the one-launch max|out| + codes form (fp8 modes); out: whether that is what was launched.  When
 // it cannot be (CTA-pair shapes, fewer tiles than SMs, no cooperative launch) nothing is launched and the caller
 // runs the two passes.
 df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uint8_t* w_codes, df8_kind kind_w,
-                    GemmArgs args, cudaStream_t st, bool* fused = nullptr) {
+                    GemmArgs args, cudaStream_t st, bool* fused = nullptr, int a_slabs = 1,
+                    int tma_fallback = kOutF32) {
     const int M = args.M, N = args.N, K = args.K;
     df8_status src = status_word_device_ptr(&args.status);
     if (src != DF8_OK) return src;
     const bool want_fused = fused != nullptr && *fused;
     if (fused) *fused = false;
+    if (a_slabs < 1 || K % a_slabs != 0 || (a_slabs > 1 && (K / a_slabs) % BK != 0))
+        return fail(DF8_ERR_UNSUPPORTED, "fp8 GEMM: K=%d cannot be read as %d slabs (a slab must be a multiple of %d columns)",
+                    K, a_slabs, BK);
+    const int slab_cols = K / a_slabs;
+    args.a_slab_cols = slab_cols;
+    if (args.ldc == 0) args.ldc = N;
+    if (const char* e = getenv("DF8_GEMM_TMA_STORE"))  // profiling and tests: 0 keeps the st.global epilogues
+        if (e[0] == '0' && mode == kOutF32Tma) mode = tma_fallback;
 
     const int sms = sm_count();
+    // A: coordinates (column inside the slab, row, slab)
+    CUtensorMap ta, tw, to = {};
+    df8_status rc = make_tmap_3d_u8(&ta, a_codes, uint64_t(M), uint64_t(slab_cols), uint64_t(a_slabs), uint64_t(slab_cols),
+                                    uint64_t(M) * uint64_t(slab_cols), BM, BK, 128);
+    if (rc != DF8_OK) return rc;
+    auto make_out_map = [&]() {
+        return make_tmap_2d_f32(&to, args.out, uint64_t(M), uint64_t(N), uint64_t(args.ldc) * sizeof(float), 32, 32, 128);
+    };
     // CTA pairs on 256 x 256 tiles when the problem fills them (see gemm_fp8_tn_pair_kernel)
     if (use_pair_kernel(M, N, K, sms)) {
         if (want_fused) return DF8_OK;
@@ -1205,51 +1278,51 @@ df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uin
         }
         const long tiles2 = long((M + 255) / 256) * ((N + bn2 - 1) / bn2);
         const long pairs = tiles2 < sms / 2 ? tiles2 : sms / 2;
-        CUtensorMap ta2, tw2;
-        df8_status rc2 = make_tmap_2d_u8(&ta2, a_codes, uint64_t(M), uint64_t(K), uint64_t(K), BM, BK, 128);
-        if (rc2 != DF8_OK) return rc2;
-        rc2 = make_tmap_2d_u8(&tw2, w_codes, uint64_t(N), uint64_t(K), uint64_t(K), uint32_t(bn2 / 2), BK, 128);
-        if (rc2 != DF8_OK) return rc2;
+        rc = make_tmap_2d_u8(&tw, w_codes, uint64_t(N), uint64_t(K), uint64_t(K), uint32_t(bn2 / 2), BK, 128);
+        if (rc != DF8_OK) return rc;
+        if (mode == kOutF32Tma && (rc = make_out_map()) != DF8_OK) return rc;
         args.idesc = ptx::make_idesc_f8(256, bn2, int(kind_a), int(kind_w));
         const int grid2 = int(pairs) * 2;
         switch (mode) {
             case kOutF32Vec:
-                return bn2 == 192 ? launch_gemm_pair<192, kOutF32Vec>(ta2, tw2, args, grid2, st)
-                                  : launch_gemm_pair<256, kOutF32Vec>(ta2, tw2, args, grid2, st);
+                return bn2 == 192 ? launch_gemm_pair<192, kOutF32Vec>(ta, tw, to, args, grid2, st)
+                                  : launch_gemm_pair<256, kOutF32Vec>(ta, tw, to, args, grid2, st);
             case kOutF32:
-                return bn2 == 192 ? launch_gemm_pair<192, kOutF32>(ta2, tw2, args, grid2, st)
-                                  : launch_gemm_pair<256, kOutF32>(ta2, tw2, args, grid2, st);
-            case kOutE4M3: return launch_gemm_pair<256, kOutE4M3>(ta2, tw2, args, grid2, st);
-            case kOutE5M2: return launch_gemm_pair<256, kOutE5M2>(ta2, tw2, args, grid2, st);
-            default: return launch_gemm_pair<256, kOutNone>(ta2, tw2, args, grid2, st);
+                return bn2 == 192 ? launch_gemm_pair<192, kOutF32>(ta, tw, to, args, grid2, st)
+                                  : launch_gemm_pair<256, kOutF32>(ta, tw, to, args, grid2, st);
+            case kOutF32Tma: return launch_gemm_pair<256, kOutF32Tma>(ta, tw, to, args, grid2, st);
+            case kOutE4M3: return launch_gemm_pair<256, kOutE4M3>(ta, tw, to, args, grid2, st);
+            case kOutE5M2: return launch_gemm_pair<256, kOutE5M2>(ta, tw, to, args, grid2, st);
+            default: return launch_gemm_pair<256, kOutNone>(ta, tw, to, args, grid2, st);
         }
     }
     // Tile width.  A TMA tiled load costs the SM's copy engine ~250 cycles whatever its size, and L2 delivers
     // ~85 bytes per cycle to an SM: a 128 x 128 K block (two loads, 32 KB) therefore takes ~530 cycles although
     // its MMAs need 256, about as long as a 128 x 256 one (48 KB, MMAs 512).  So narrow tiles only pay when
     // they save whole rounds of the persistent grid.
-    // The fp32 modes add their epilogue to the picture: a 32 x 32 chunk takes a warp ~2000 cycles to stage and
-    // store (measured), i.e. ~31 cycles per tile column with eight warps, which exceeds the main loop at small K.
+    // The st.global fp32 modes add their epilogue to the picture: a 32 x 32 chunk takes a warp ~2000 cycles to
+    // stage and store (measured), i.e. ~31 cycles per tile column with eight warps, which exceeds the main loop at
+    // small K.
     auto rounds = [&](int bn) {
         const long tiles = long((M + BM - 1) / BM) * ((N + bn - 1) / bn);
         return double((tiles + sms - 1) / sms);
     };
     const double kloop = double((K + BK - 1) / BK) * 540.0;
+    const int cost_mode = mode == kOutF32Tma ? tma_fallback : mode;
     auto tile_cycles = [&](int bn) {
         const double main_loop = bn == 256 ? kloop : 0.94 * kloop;
-        const double epilogue = (mode == kOutF32Vec || mode == kOutF32) ? 31.0 * bn : 0.0;
+        const double epilogue = (cost_mode == kOutF32Vec || cost_mode == kOutF32) ? 31.0 * bn : 0.0;
         return main_loop > epilogue ? main_loop : epilogue;
     };
     const bool wide = N > 128 && rounds(256) * tile_cycles(256) <= rounds(128) * tile_cycles(128);
+    if (mode == kOutF32Tma && !wide) mode = tma_fallback;  // the TMA-store epilogue exists for 256-column tiles
     const int bn = wide ? 256 : 128;
     const long tiles = long((M + BM - 1) / BM) * ((N + bn - 1) / bn);
     const int grid = int(tiles < sms ? tiles : sms);
 
-    CUtensorMap ta, tw;
-    df8_status rc = make_tmap_2d_u8(&ta, a_codes, uint64_t(M), uint64_t(K), uint64_t(K), BM, BK, 128);
-    if (rc != DF8_OK) return rc;
     rc = make_tmap_2d_u8(&tw, w_codes, uint64_t(N), uint64_t(K), uint64_t(K), uint32_t(bn), BK, 128);
     if (rc != DF8_OK) return rc;
+    if (mode == kOutF32Tma && (rc = make_out_map()) != DF8_OK) return rc;
     args.idesc = ptx::make_idesc_f8(BM, bn, int(kind_a), int(kind_w));
     if (want_fused) {
         if (grid != sms || (mode != kOutE4M3 && mode != kOutE5M2)) return DF8_OK;  // nothing launched, *fused stays false
@@ -1260,19 +1333,20 @@ df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uin
             return DF8_OK;
         }
         args.grid_counter = counters + next_slot.fetch_add(1u) % unsigned(kFusedCounters);
-        const df8_status rc = mode == kOutE4M3 ? launch_gemm_bn<kOutE4M3>(wide, ta, tw, args, grid, st)
-                                               : launch_gemm_bn<kOutE5M2>(wide, ta, tw, args, grid, st);
-        if (rc == DF8_ERR_UNSUPPORTED) return DF8_OK;  // no cooperative launch here: two passes
-        if (rc == DF8_OK) *fused = true;
-        return rc;
+        const df8_status rcf = mode == kOutE4M3 ? launch_gemm_bn<kOutE4M3>(wide, ta, tw, to, args, grid, st)
+                                                : launch_gemm_bn<kOutE5M2>(wide, ta, tw, to, args, grid, st);
+        if (rcf == DF8_ERR_UNSUPPORTED) return DF8_OK;  // no cooperative launch here: two passes
+        if (rcf == DF8_OK) *fused = true;
+        return rcf;
     }
 
     switch (mode) {
-        case kOutF32Vec: return launch_gemm_bn<kOutF32Vec>(wide, ta, tw, args, grid, st);
-        case kOutF32: return launch_gemm_bn<kOutF32>(wide, ta, tw, args, grid, st);
-        case kOutE4M3: return launch_gemm_bn<kOutE4M3>(wide, ta, tw, args, grid, st);
-        case kOutE5M2: return launch_gemm_bn<kOutE5M2>(wide, ta, tw, args, grid, st);
-        default: return launch_gemm_bn<kOutNone>(wide, ta, tw, args, grid, st);
+        case kOutF32Vec: return launch_gemm_bn<kOutF32Vec>(wide, ta, tw, to, args, grid, st);
+        case kOutF32: return launch_gemm_bn<kOutF32>(wide, ta, tw, to, args, grid, st);
+        case kOutF32Tma: return launch_gemm_bn<kOutF32Tma>(wide, ta, tw, to, args, grid, st);
+        case kOutE4M3: return launch_gemm_bn<kOutE4M3>(wide, ta, tw, to, args, grid, st);
+        case kOutE5M2: return launch_gemm_bn<kOutE5M2>(wide, ta, tw, to, args, grid, st);
+        default: return launch_gemm_bn<kOutNone>(wide, ta, tw, to, args, grid, st);
     }
 }
 
@@ -1285,8 +1359,17 @@ extern "C" df8_status df8_gemm_fp8_tn(const uint8_t* a_codes, df8_kind kind_a, c
                                       const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
                                       const float* bias, const float* residual, int M, int N, int K, int flags,
                                       float* out, float* out_amax, df8_stream stream) {
+    return df8_gemm_fp8_tn_ex(a_codes, kind_a, scale_a, 1, w_codes, kind_w, scale_w, bias, residual, M, N, K, flags, out,
+                              N, out_amax, stream);
+}
+
+extern "C" df8_status df8_gemm_fp8_tn_ex(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a, int a_slabs,
+                                         const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
+                                         const float* bias, const float* residual, int M, int N, int K, int flags,
+                                         float* out, int ldc, float* out_amax, df8_stream stream) {
     DF8_REQUIRE((kind_a == DF8_E4M3 || kind_a == DF8_E5M2) && (kind_w == DF8_E4M3 || kind_w == DF8_E5M2),
                 "df8_gemm_fp8_tn: unknown fp8 kind");
+    DF8_REQUIRE(ldc >= N, "df8_gemm_fp8_tn: ldc=%d is smaller than N=%d", ldc, N);
     DF8_REQUIRE(M >= 0 && N >= 0 && K > 0, "df8_gemm_fp8_tn: bad shape M=%d N=%d K=%d", M, N, K);
     DF8_REQUIRE((flags & ~7) == 0, "df8_gemm_fp8_tn: unknown flags 0x%x", flags);
     cudaStream_t st = as_stream(stream);
@@ -1310,10 +1393,17 @@ extern "C" df8_status df8_gemm_fp8_tn(const uint8_t* a_codes, df8_kind kind_a, c
     args.M = M;
     args.N = N;
     args.K = K;
+    args.ldc = ldc;
     args.flags = flags;
-    const bool vec4 = (N % 4 == 0) && aligned16(out) && (!bias || aligned16(bias)) &&
+    // 128-bit accesses need rows that start on 16-byte boundaries (a pitch that is a multiple of 4 floats; N itself
+    // may be anything: the last group of a row then reaches into the pitch padding)
+    const bool pitch4 = ldc % 4 == 0 && ldc >= (N + 3) / 4 * 4;
+    const bool vec4 = pitch4 && aligned16(out) && (!bias || aligned16(bias)) &&
                       (!(flags & DF8_EPI_RESIDUAL) || aligned16(residual));
-    return run_gemm(vec4 ? kOutF32Vec : kOutF32, a_codes, kind_a, w_codes, kind_w, args, st);
+    const int st_mode = vec4 ? kOutF32Vec : kOutF32;
+    // without a residual to read, rows that start on 16-byte boundaries leave through TMA stores
+    const bool tma = pitch4 && aligned16(out) && !(flags & DF8_EPI_RESIDUAL);
+    return run_gemm(tma ? kOutF32Tma : st_mode, a_codes, kind_a, w_codes, kind_w, args, st, nullptr, a_slabs, st_mode);
 }
 
 extern "C" df8_status df8_gemm_fp8_tn_q(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a,
@@ -1381,6 +1471,14 @@ extern "C" df8_status df8_gemm_fp8_tn_amax(const uint8_t* a_codes, df8_kind kind
                                            const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
                                            const float* bias, int M, int N, int K, int flags, float* out_amax,
                                            df8_stream stream) {
+    return df8_gemm_fp8_tn_amax_ex(a_codes, kind_a, scale_a, 1, w_codes, kind_w, scale_w, bias, M, N, K, flags, out_amax,
+                                   stream);
+}
+
+extern "C" df8_status df8_gemm_fp8_tn_amax_ex(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a, int a_slabs,
+                                              const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
+                                              const float* bias, int M, int N, int K, int flags, float* out_amax,
+                                              df8_stream stream) {
     DF8_REQUIRE((kind_a == DF8_E4M3 || kind_a == DF8_E5M2) && (kind_w == DF8_E4M3 || kind_w == DF8_E5M2),
                 "df8_gemm_fp8_tn_amax: unknown fp8 kind");
     DF8_REQUIRE(M >= 0 && N >= 0 && K > 0, "df8_gemm_fp8_tn_amax: bad shape M=%d N=%d K=%d", M, N, K);
@@ -1402,7 +1500,7 @@ extern "C" df8_status df8_gemm_fp8_tn_amax(const uint8_t* a_codes, df8_kind kind
     args.N = N;
     args.K = K;
     args.flags = flags | DF8_EPI_AMAX;
-    return run_gemm(kOutNone, a_codes, kind_a, w_codes, kind_w, args, st);
+    return run_gemm(kOutNone, a_codes, kind_a, w_codes, kind_w, args, st, nullptr, a_slabs);
 }
 
 extern "C" df8_status df8_gemm_fp8_tn_codes(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a,
@@ -1410,6 +1508,15 @@ extern "C" df8_status df8_gemm_fp8_tn_codes(const uint8_t* a_codes, df8_kind kin
                                             const float* bias, int M, int N, int K, int flags, df8_kind out_kind,
                                             const float* amax_in, uint8_t* out_codes, float* out_scale,
                                             df8_stream stream) {
+    return df8_gemm_fp8_tn_codes_ex(a_codes, kind_a, scale_a, 1, w_codes, kind_w, scale_w, bias, M, N, K, flags, out_kind,
+                                    amax_in, out_codes, out_scale, stream);
+}
+
+extern "C" df8_status df8_gemm_fp8_tn_codes_ex(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a, int a_slabs,
+                                               const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
+                                               const float* bias, int M, int N, int K, int flags, df8_kind out_kind,
+                                               const float* amax_in, uint8_t* out_codes, float* out_scale,
+                                               df8_stream stream) {
     DF8_REQUIRE((kind_a == DF8_E4M3 || kind_a == DF8_E5M2) && (kind_w == DF8_E4M3 || kind_w == DF8_E5M2) &&
                     (out_kind == DF8_E4M3 || out_kind == DF8_E5M2),
                 "df8_gemm_fp8_tn_codes: unknown fp8 kind");
@@ -1433,5 +1540,6 @@ extern "C" df8_status df8_gemm_fp8_tn_codes(const uint8_t* a_codes, df8_kind kin
     args.out_codes = out_codes;
     args.q_amax = amax_in;
     args.out_scale = out_scale;
-    return run_gemm(out_kind == DF8_E4M3 ? kOutE4M3 : kOutE5M2, a_codes, kind_a, w_codes, kind_w, args, as_stream(stream));
+    return run_gemm(out_kind == DF8_E4M3 ? kOutE4M3 : kOutE5M2, a_codes, kind_a, w_codes, kind_w, args, as_stream(stream),
+                    nullptr, a_slabs);
 }

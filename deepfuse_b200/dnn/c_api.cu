@@ -201,6 +201,29 @@ extern "C" int dnn_gpt2_forward_logits_host(dnn_gpt2* m, const int32_t* ids_h, i
     });
 }
 
+extern "C" int dnn_gpt2_forward_logits_pitched(dnn_gpt2* m, const int32_t* ids, int ids_on_host, int B, int T,
+                                               int check_ids, float** logits_d, int* pitch_h) {
+    return guarded([&] {
+        stage_ids(m, ids, B, T, ids_on_host ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice);
+        m->last.reset();
+        m->last = std::make_unique<dnn::tensor<float>>(m->model->forward_logits_pitched(*m->ids, check_ids != 0));
+        *logits_d = m->last->data();
+        if (pitch_h) *pitch_h = m->model->logits_pitch();
+    });
+}
+
+extern "C" int dnn_gpt2_copy_logits_host(dnn_gpt2* m, float* dst_h) {
+    return guarded([&] {
+        if (!m->last || m->last->shape().size() != 2) throw std::runtime_error("dnn_gpt2_copy_logits_host: no logits to copy");
+        const int rows = m->last->shape()[0], pitch = m->last->shape()[1];
+        const int vocab = m->model->vocab_size();
+        if (pitch < vocab) throw std::runtime_error("dnn_gpt2_copy_logits_host: the last result is not a logits tensor");
+        dnn::utils::CHECK_CUDA_EX(cudaMemcpy2DAsync(dst_h, size_t(vocab) * sizeof(float), m->last->data(),
+                                                    size_t(pitch) * sizeof(float), size_t(vocab) * sizeof(float),
+                                                    size_t(rows), cudaMemcpyDeviceToHost, dnn::Cuda::stream()));
+    });
+}
+
 extern "C" int dnn_gpt2_forward_hidden(dnn_gpt2* m, const int32_t* ids_d, int B, int T, float** hidden_d) {
     return guarded([&] {
         stage_ids(m, ids_d, B, T, cudaMemcpyDeviceToDevice);

@@ -44,9 +44,10 @@ public:
     // Per-tensor quantised weights, refreshed if the fp32 weights changed since the last call.
     const fp8::Quantized& quantized_weights();
     // out[M,out] = epilogue(codes . Wq^T); a_codes is [M, padded_in()]; `flags` are DF8_EPI_* bits;
-    // out_amax may be null.
+    // out_amax may be null.  ldc: row pitch of `out` and `residual` in floats (0 = out_features); a_slabs: the
+    // columns of a_codes are stored as that many [M, padded_in() / a_slabs] slabs (see df8_gemm_fp8_tn_ex).
     void forward_codes(const uint8_t* a_codes, df8_kind a_kind, const float* a_scale, int M, int flags,
-                       const float* residual, float* out, float* out_amax);
+                       const float* residual, float* out, float* out_amax, int ldc = 0, int a_slabs = 1);
 
     // q <- per-tensor quantisation (kind out_kind) of epilogue(codes . Wq^T), `flags` = 0 or DF8_EPI_GELU.
     // Uses the two-pass GEMM that never writes the fp32 result when out_features % 32 == 0.

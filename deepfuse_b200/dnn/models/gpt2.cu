@@ -108,6 +108,19 @@ tensor<T> Gpt2<T>::forward_logits(const tensor<int>& ids, bool check_ids) {
 }
 
 template <typename T>
+tensor<T> Gpt2<T>::forward_logits_pitched(const tensor<int>& ids, bool check_ids) {
+    fp8::PassScope amax_slots;
+    tensor<T> x = forward_hidden(ids, check_ids);
+    const int M = int(x.numel() / size_t(hidden_dim_));
+    fp8::quantize(x.data(), x.numel(), fp8::policy().activation_kind, head_q_);
+    const int pitch = logits_pitch();
+    tensor<T> logits({M, pitch});
+    final_fc_->forward_codes(head_q_.codes.data(), head_q_.kind, head_q_.scale.data(), M, 0, nullptr, logits.data(),
+                             nullptr, pitch);
+    return logits;
+}
+
+template <typename T>
 Gpt2<T>::~Gpt2() {
     if (streamer_) df8_streamer_destroy(streamer_);
 }

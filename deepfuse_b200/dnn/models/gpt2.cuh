@@ -55,6 +55,12 @@ public:
     // ---- batched fp8 inference ----
     tensor<T> forward_hidden(const tensor<int>& ids, bool check_ids = true);
     tensor<T> forward_logits(const tensor<int>& ids, bool check_ids = true);
+    // The same logits in a row-pitched buffer: a tensor [B*T, logits_pitch()] whose first vocab_size() columns
+    // of every row are the logits (the rest is padding with unspecified contents).  Rows of 50257 floats do not
+    // start on 16-byte boundaries, which costs the head GEMM one 4-byte store per element; with the pitch
+    // rounded up to a multiple of 32 floats its epilogue leaves through TMA stores.
+    tensor<T> forward_logits_pitched(const tensor<int>& ids, bool check_ids = true);
+    int logits_pitch() const { return (vocab_size_ + 31) / 32 * 32; }
     void set_mlp_gelu(bool on);
     void set_causal(bool causal);
 

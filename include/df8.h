@@ -101,6 +101,21 @@ df8_status df8_gemm_fp8_tn(const uint8_t* a_codes, df8_kind kind_a, const float*
                            const float* bias, const float* residual, int M, int N, int K, int flags,
                            float* out, float* out_amax, df8_stream stream);
 
+/* The same call with two more degrees of freedom (df8_gemm_fp8_tn is this with a_slabs = 1 and ldc = N):
+ *   ldc      row pitch, in floats, of `out` (and of `residual`), ldc >= N.  A pitch that is a multiple of 4 floats
+ *            lets rows of any N start on 16-byte boundaries: the epilogue then writes 128 bits at a time, and
+ *            without a residual it leaves through TMA stores.  Columns N .. ldc-1 of a row belong to the caller;
+ *            up to three of them (N rounded up to a multiple of 4) may be overwritten with unspecified values.
+ *            A vocabulary of 50257 is the case: dense rows are not 16-byte aligned and cost one 4-byte store per
+ *            element (upstream's kernel writes `output[row * out + col]`, fully_connected_layer.cu:39).
+ *   a_slabs  A's K columns are stored as a_slabs row-major [M, K / a_slabs] matrices, M * K / a_slabs bytes apart
+ *            — the layout an all-gather of per-rank [M, K / world] column slices leaves — and are read in place
+ *            (K / a_slabs must be a multiple of 128 when a_slabs > 1). */
+df8_status df8_gemm_fp8_tn_ex(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a, int a_slabs,
+                              const uint8_t* w_codes, df8_kind kind_w, const float* scale_w, const float* bias,
+                              const float* residual, int M, int N, int K, int flags, float* out, int ldc,
+                              float* out_amax, df8_stream stream);
+
 /* Same product with per-tensor-quantised fp8 OUTPUT and no fp32 intermediate in memory:
  *     out_codes[m,n] = fp8_out_kind( epi(acc*dq_a*dq_w + bias[n]) * q ),  q = FP8_MAX / max|epi(...)|
  * The kernel runs twice — a first pass that only reduces max|.| into out_amax, a second that
@@ -123,6 +138,15 @@ df8_status df8_gemm_fp8_tn_codes(const uint8_t* a_codes, df8_kind kind_a, const 
                                  const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
                                  const float* bias, int M, int N, int K, int flags, df8_kind out_kind,
                                  const float* amax_in, uint8_t* out_codes, float* out_scale, df8_stream stream);
+
+/* ... and with A read from a_slabs column slabs (see df8_gemm_fp8_tn_ex) */
+df8_status df8_gemm_fp8_tn_amax_ex(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a, int a_slabs,
+                                   const uint8_t* w_codes, df8_kind kind_w, const float* scale_w, const float* bias,
+                                   int M, int N, int K, int flags, float* out_amax, df8_stream stream);
+df8_status df8_gemm_fp8_tn_codes_ex(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a, int a_slabs,
+                                    const uint8_t* w_codes, df8_kind kind_w, const float* scale_w, const float* bias,
+                                    int M, int N, int K, int flags, df8_kind out_kind, const float* amax_in,
+                                    uint8_t* out_codes, float* out_scale, df8_stream stream);
 
 /* ---- fp8 attention -------------------------------------------------------------------------
  * Replaces, inside MultiHeadAttentionLayer::forward (dnn/layers/multi_head_attention.cu:204-308), the

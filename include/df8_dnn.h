@@ -46,6 +46,13 @@ int dnn_gpt2_prepare(dnn_gpt2* m);
  * ids are int32 on the device (ids_d) or on the host (ids_h, uploaded inside the call). */
 int dnn_gpt2_forward_logits(dnn_gpt2* m, const int32_t* ids_d, int B, int T, int check_ids, float** logits_d);
 int dnn_gpt2_forward_logits_host(dnn_gpt2* m, const int32_t* ids_h, int B, int T, float** logits_d);
+/* Gpt2::forward_logits_pitched: logits [B*T, *pitch_h] fp32 with the first `vocab` columns of every row valid
+ * (pitch = vocab rounded up to a multiple of 32 floats); ids on the device, or on the host when ids_on_host. */
+int dnn_gpt2_forward_logits_pitched(dnn_gpt2* m, const int32_t* ids, int ids_on_host, int B, int T, int check_ids,
+                                    float** logits_d, int* pitch_h);
+/* Enqueues the copy of the last logits (dense or pitched) to a dense HOST array [rows, vocab] on the thread's
+ * stream (pinned memory makes it asynchronous); the caller synchronises before reading dst_h. */
+int dnn_gpt2_copy_logits_host(dnn_gpt2* m, float* dst_h);
 /* hidden states [B,T,E] of Gpt2::forward_hidden, device pointer owned by the handle */
 int dnn_gpt2_forward_hidden(dnn_gpt2* m, const int32_t* ids_d, int B, int T, float** hidden_d);
 /* the model's own public batch-1 entry point, Gpt2::forward(std::vector<int>): hidden [1,T,E] to host */

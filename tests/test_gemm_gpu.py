@@ -316,3 +316,113 @@ def test_gemm_cta_pair_quantised_output(df8, oracle, cuda, monkeypatch):
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
     assert outs[0][2].item() == outs[1][2].item()
     assert df8.status_word() == (0, 0)
+
+
+@pytest.mark.parametrize("M,N,K,flags,pair", [(512, 768, 256, 0, "0"), (300, 1000, 256, 4, "0"), (129, 2304, 768, 5, "0"),
+                                               (1024, 3072, 768, 1, "0"), (203, 516, 128, 4, "0"),
+                                               (512, 768, 1024, 0, "1"), (300, 1000, 256, 5, "1"), (1000, 2048, 2048, 4, "auto")])
+def test_gemm_tma_store_epilogue_equals_st_global(df8, oracle, cuda, monkeypatch, M, N, K, flags, pair):
+    """fp32 output without a residual leaves through TMA stores when rows start on 16-byte boundaries
+    (DF8_GEMM_TMA_STORE=0 keeps the transpose + st.global epilogue): the two must agree bit for bit, max|out|
+    included, on ragged M, on N that ends inside a 32-column chunk, with GELU, and in the CTA-pair kernel; and
+    nothing may be written past the output."""
+    import torch
+
+    if pair != "auto":
+        monkeypatch.setenv("DF8_GEMM_PAIR", pair)
+    xc, sx = oracle.quantize(oracle.fill_normal(M * K, seed=M + 1).reshape(M, K), 0)
+    wc, sw = oracle.quantize(oracle.fill_normal(N * K, seed=N + 2, std=0.05).reshape(N, K), 0)
+    b = oracle.fill_normal(N, seed=3, std=0.1)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+    xcd, wcd, sxd, swd, bd = t(xc), t(wc), t(sx), t(sw), t(b)
+    outs = []
+    for tma in ("1", "0"):
+        monkeypatch.setenv("DF8_GEMM_TMA_STORE", tma)
+        buf = torch.full((M * N + 256,), 777.0, device=cuda)
+        amax = torch.full((1,), -1.0, device=cuda)
+        df8.gemm_fp8_tn(xcd, 0, sxd, wcd, 0, swd, bd, None, M, N, K, flags, buf, amax)
+        torch.cuda.synchronize()
+        assert bool((buf[M * N:] == 777.0).all())
+        outs.append((buf[: M * N].clone(), amax.item()))
+    assert torch.equal(outs[0][0], outs[1][0]), f"{(outs[0][0] != outs[1][0]).sum().item()} elements differ"
+    assert outs[0][1] == outs[1][1]
+    y = outs[0][0].cpu().numpy().reshape(M, N)
+    ref = oracle.fc_forward_fp8(xc, 0, sx[1], wc, 0, sw[1], b, None, flags & 1)
+    tol = 2e-3 if flags & 1 else TIGHT
+    assert rel_err(y, ref) <= tol, describe_mismatch(y, ref, tol)
+    if flags & 4:
+        assert outs[0][1] == np.abs(y).max()
+    assert df8.status_word() == (0, 0)
+
+
+@pytest.mark.parametrize("N,ldc", [(1001, 1024), (1003, 1004), (50257 // 8, 6304), (770, 772)])
+@pytest.mark.parametrize("flags", [0, 4, 6])
+def test_gemm_pitched_output_rows(df8, oracle, cuda, flags, N, ldc):
+    """df8_gemm_fp8_tn_ex with a row pitch that is a multiple of 4 floats: rows of any N then start on 16-byte
+    boundaries (TMA stores without a residual, 128-bit stores with one).  The N valid columns of every row must
+    equal the dense call's output bit for bit; columns from N rounded up to 4 onwards are never written."""
+    import torch
+
+    M, K = 300, 256
+    xc, sx = oracle.quantize(oracle.fill_normal(M * K, seed=N).reshape(M, K), 0)
+    wc, sw = oracle.quantize(oracle.fill_normal(N * K, seed=N + 1, std=0.05).reshape(N, K), 0)
+    b = oracle.fill_normal(N, seed=N + 2, std=0.1)
+    res = oracle.fill_normal(M * N, seed=N + 3).reshape(M, N) if flags & 2 else None
+    t = lambda a: None if a is None else torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+    xcd, wcd, sxd, swd = t(xc), t(wc), t(sx), t(sw)
+    bd = torch.full((N + 16,), 1e30, device=cuda)  # poison after the bias: a read past N would show in the output
+    bd[:N] = t(b)
+    dense = torch.empty((M, N), device=cuda)
+    a0 = torch.zeros(1, device=cuda)
+    df8.gemm_fp8_tn(xcd, 0, sxd, wcd, 0, swd, bd, t(res), M, N, K, flags, dense, a0)
+    pitched = torch.full((M, ldc), 777.0, device=cuda)
+    res_p = None
+    if res is not None:
+        res_p = torch.zeros((M, ldc), device=cuda)
+        res_p[:, :N] = t(res)
+    a1 = torch.zeros(1, device=cuda)
+    df8.gemm_fp8_tn_ex(xcd, 0, sxd, 1, wcd, 0, swd, bd, res_p, M, N, K, flags, pitched, ldc, a1)
+    torch.cuda.synchronize()
+    assert torch.equal(pitched[:, :N], dense)
+    n4 = (N + 3) // 4 * 4
+    assert bool((pitched[:, n4:] == 777.0).all())
+    if flags & 4:
+        assert a0.item() == a1.item() == dense.abs().max().item()
+    ref = oracle.fc_forward_fp8(xc, 0, sx[1], wc, 0, sw[1], b, res, flags & 3)
+    assert rel_err(dense.cpu().numpy(), ref) <= TIGHT
+    assert df8.status_word() == (0, 0)
+
+
+@pytest.mark.parametrize("slabs,K,pair", [(2, 256, "0"), (4, 1024, "0"), (8, 1024, "1"), (2, 2048, "auto")])
+def test_gemm_reads_a_stored_as_column_slabs(df8, oracle, cuda, monkeypatch, slabs, K, pair):
+    """A given as `slabs` row-major [M, K/slabs] matrices one after the other (what an all-gather of per-rank column
+    slices leaves) must give exactly the product of the ordinary [M, K] matrix: fp32 output and both passes of
+    the fp8-codes output."""
+    import torch
+
+    if pair != "auto":
+        monkeypatch.setenv("DF8_GEMM_PAIR", pair)
+    M, N = 515, 768
+    xc, sx = oracle.quantize(oracle.fill_normal(M * K, seed=K + slabs).reshape(M, K), 0)
+    wc, sw = oracle.quantize(oracle.fill_normal(N * K, seed=9, std=0.05).reshape(N, K), 0)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+    xcd, wcd, sxd, swd = t(xc), t(wc), t(sx), t(sw)
+    slabbed = xcd.reshape(M, slabs, K // slabs).permute(1, 0, 2).contiguous()
+    want = torch.empty((M, N), device=cuda)
+    df8.gemm_fp8_tn(xcd, 0, sxd, wcd, 0, swd, None, None, M, N, K, 0, want)
+    got = torch.empty((M, N), device=cuda)
+    df8.gemm_fp8_tn_ex(slabbed, 0, sxd, slabs, wcd, 0, swd, None, None, M, N, K, 0, got, N)
+    assert torch.equal(got, want)
+    lib = df8.lib()
+    am = [torch.zeros(1, device=cuda) for _ in range(2)]
+    codes = [torch.zeros((M, N), dtype=torch.uint8, device=cuda) for _ in range(2)]
+    sc = [torch.zeros(2, device=cuda) for _ in range(2)]
+    for i, (a, s) in enumerate(((xcd, 1), (slabbed, slabs))):
+        df8.check(lib.df8_gemm_fp8_tn_amax_ex(df8.ptr(a), 0, df8.ptr(sxd), s, df8.ptr(wcd), 0, df8.ptr(swd), None, M, N, K,
+                                              1, df8.ptr(am[i]), df8.stream_ptr()))
+        df8.check(lib.df8_gemm_fp8_tn_codes_ex(df8.ptr(a), 0, df8.ptr(sxd), s, df8.ptr(wcd), 0, df8.ptr(swd), None, M, N, K,
+                                               1, 0, df8.ptr(am[i]), df8.ptr(codes[i]), df8.ptr(sc[i]), df8.stream_ptr()))
+    assert am[0].item() == am[1].item() and torch.equal(codes[0], codes[1]) and torch.equal(sc[0], sc[1])
+    with pytest.raises(df8.Df8Error, match="slabs"):
+        df8.gemm_fp8_tn_ex(slabbed, 0, sxd, 3, wcd, 0, swd, None, None, M, N, K, 0, got, N)
+    assert df8.status_word() == (0, 0)

@@ -52,6 +52,10 @@ _SIGNATURES = {
     "df8_softmax_masked_f32": [_vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "df8_gemm_fp8_tn_q": [_vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     "df8_streamer_create": [_sz, _i, _i, _vp],
+    "df8_streamer_create_sharded": [_sz, _i, _i, _vp, _vp],
+    "df8_streamer_resize": [_vp, _i],
+    "df8_streamer_traffic": [_vp, _vp, _vp],
+    "df8_streamer_time_uploads": [_vp, _vp],
     "df8_streamer_destroy": [_vp],
     "df8_streamer_host_ptr": [_vp, _i, _vp],
     "df8_streamer_prefetch": [_vp, _i],
@@ -218,6 +222,9 @@ _DNN_SIGNATURES = {
     "dnn_gpt2_param_upload": [_vp, _i, _vp],
     "dnn_gpt2_param_download": [_vp, _i, _vp],
     "dnn_gpt2_prepare": [_vp],
+    "dnn_gpt2_set_stage_timing": [_vp, _i],
+    "dnn_gpt2_last_head_ms": [_vp, _vp],
+    "dnn_gpt2_initialize_on_device": [_vp, C.c_ulonglong, _f],
     "dnn_gpt2_forward_logits": [_vp, _vp, _i, _i, _i, _vp],
     "dnn_gpt2_forward_logits_host": [_vp, _vp, _i, _i, _vp],
     "dnn_gpt2_forward_hidden": [_vp, _vp, _i, _i, _vp],
@@ -227,6 +234,10 @@ _DNN_SIGNATURES = {
     "dnn_gpt2_save": [_vp, C.c_char_p],
     "dnn_gpt2_enable_streaming": [_vp, _i, _i],
     "dnn_gpt2_disable_streaming": [_vp],
+    "dnn_gpt2_enable_streaming_sharded": [_vp, _i, _i, _vp],
+    "dnn_gpt2_resize_streaming_slots": [_vp, _i],
+    "dnn_gpt2_streaming_traffic": [_vp, _vp, _vp],
+    "dnn_gpt2_time_layer_uploads": [_vp, _vp],
     "dnn_fc_forward": [_i, _i, _vp, _vp, _vp, _i, _vp],
     "dnn_layernorm_forward": [_i, _i, _vp, _vp, _f, _vp, _vp],
     "dnn_softmax_forward": [_i, _i, _i, _vp, _vp, _i, _vp],
@@ -330,11 +341,45 @@ class Gpt2:
             dnn_check(d.dnn_gpt2_param_upload(self.h, i, a.ctypes.data_as(C.c_void_p)), "dnn_gpt2_param_upload")
         dnn_check(d.dnn_gpt2_prepare(self.h), "dnn_gpt2_prepare")
 
+    def initialize_on_device(self, seed: int, std: float = 0.02):
+        dnn_check(dnn_lib().dnn_gpt2_initialize_on_device(self.h, seed, std), "dnn_gpt2_initialize_on_device")
+        dnn_check(dnn_lib().dnn_gpt2_prepare(self.h), "dnn_gpt2_prepare")
+
+    def set_stage_timing(self, on: bool):
+        dnn_check(dnn_lib().dnn_gpt2_set_stage_timing(self.h, int(on)), "dnn_gpt2_set_stage_timing")
+
+    def last_head_ms(self) -> float:
+        ms = C.c_float(0)
+        dnn_check(dnn_lib().dnn_gpt2_last_head_ms(self.h, C.byref(ms)), "dnn_gpt2_last_head_ms")
+        return ms.value
+
     def set_options(self, gelu=True, causal=False):
         dnn_check(dnn_lib().dnn_gpt2_set_options(self.h, int(gelu), int(causal)), "dnn_gpt2_set_options")
 
-    def enable_streaming(self, slots=2, release_fp32=False):
-        dnn_check(dnn_lib().dnn_gpt2_enable_streaming(self.h, slots, int(release_fp32)), "dnn_gpt2_enable_streaming")
+    def enable_streaming(self, slots=2, release_fp32=False, comm=None):
+        """comm: a Comm of more than one rank -> every rank uploads 1/world of each layer and an all-gather over
+        NVLink completes the slot (all ranks then run the same sequence of forwards)."""
+        if comm is not None and comm.h:
+            dnn_check(dnn_lib().dnn_gpt2_enable_streaming_sharded(self.h, slots, int(release_fp32), comm.h),
+                      "dnn_gpt2_enable_streaming_sharded")
+        else:
+            dnn_check(dnn_lib().dnn_gpt2_enable_streaming(self.h, slots, int(release_fp32)), "dnn_gpt2_enable_streaming")
+        self._streaming = True
+
+    def resize_streaming_slots(self, slots: int):
+        dnn_check(dnn_lib().dnn_gpt2_resize_streaming_slots(self.h, slots), "dnn_gpt2_resize_streaming_slots")
+
+    def streaming_traffic(self) -> tuple[int, int]:
+        """(bytes this rank copied from host memory, bytes it received from its peers) since streaming began."""
+        a, b = C.c_ulonglong(0), C.c_ulonglong(0)
+        dnn_check(dnn_lib().dnn_gpt2_streaming_traffic(self.h, C.byref(a), C.byref(b)), "dnn_gpt2_streaming_traffic")
+        return a.value, b.value
+
+    def time_uploads(self) -> float:
+        """Device time (ms) of uploading every layer once with nothing else running."""
+        ms = C.c_float(0)
+        dnn_check(dnn_lib().dnn_gpt2_time_layer_uploads(self.h, C.byref(ms)), "dnn_gpt2_time_layer_uploads")
+        return ms.value
 
     def disable_streaming(self):
         dnn_check(dnn_lib().dnn_gpt2_disable_streaming(self.h), "dnn_gpt2_disable_streaming")

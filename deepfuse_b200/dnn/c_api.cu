@@ -160,6 +160,21 @@ extern "C" int dnn_gpt2_param_download(dnn_gpt2* m, int index, float* data_h) {
     return guarded([&] { m->params.at(size_t(index)).t->download(data_h); });
 }
 
+extern "C" int dnn_gpt2_initialize_on_device(dnn_gpt2* m, unsigned long long seed, float std) {
+    return guarded([&] {
+        m->model->initialize_on_device(seed, std);
+        sync_stream();
+    });
+}
+
+extern "C" int dnn_gpt2_set_stage_timing(dnn_gpt2* m, int on) {
+    return guarded([&] { m->model->set_stage_timing(on != 0); });
+}
+
+extern "C" int dnn_gpt2_last_head_ms(dnn_gpt2* m, float* ms_h) {
+    return guarded([&] { *ms_h = m->model->last_head_ms(); });
+}
+
 extern "C" int dnn_gpt2_prepare(dnn_gpt2* m) {
     return guarded([&] {
         for (int i = 0; i < m->model->num_layers(); ++i) {
@@ -370,6 +385,25 @@ extern "C" int dnn_gpt2_enable_streaming(dnn_gpt2* m, int slots, int release_fp3
         m->model->enable_layer_streaming(slots, release_fp32 != 0);
         sync_stream();
     });
+}
+
+extern "C" int dnn_gpt2_enable_streaming_sharded(dnn_gpt2* m, int slots, int release_fp32, void* comm) {
+    return guarded([&] {
+        m->model->enable_layer_streaming(slots, release_fp32 != 0, static_cast<df8_comm*>(comm));
+        sync_stream();
+    });
+}
+
+extern "C" int dnn_gpt2_resize_streaming_slots(dnn_gpt2* m, int slots) {
+    return guarded([&] { m->model->resize_streaming_slots(slots); });
+}
+
+extern "C" int dnn_gpt2_streaming_traffic(dnn_gpt2* m, unsigned long long* h2d_bytes_h, unsigned long long* gathered_bytes_h) {
+    return guarded([&] { m->model->streaming_traffic(h2d_bytes_h, gathered_bytes_h); });
+}
+
+extern "C" int dnn_gpt2_time_layer_uploads(dnn_gpt2* m, float* ms_h) {
+    return guarded([&] { *ms_h = m->model->time_layer_uploads(); });
 }
 
 extern "C" int dnn_gpt2_disable_streaming(dnn_gpt2* m) {

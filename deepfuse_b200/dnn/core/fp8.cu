@@ -20,7 +20,29 @@ __global__ void fill_uniform_kernel(float* w, size_t n, float limit, uint64_t se
         w[i] = (2.0f * u - 1.0f) * limit;
     }
 }
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+__device__ __forceinline__ float u01(uint64_t bits) { return (float(bits >> 40) + 0.5f) * (1.0f / 16777216.0f); }
+
+__global__ void fill_normal_kernel(float* w, size_t n, float mean, float stddev, uint64_t seed, uint64_t offset) {
+    const uint64_t base = seed * 0xD1342543DE82EF95ull;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
+        const uint64_t idx = uint64_t(i) + offset;
+        const float r = sqrtf(-2.0f * logf(u01(mix64(base + 2 * idx))));
+        w[i] = mean + stddev * (r * cosf(6.28318530718f * u01(mix64(base + 2 * idx + 1))));
+    }
+}
 }  // namespace
+
+void fill_normal(float* p, size_t n, float mean, float std, uint64_t seed, uint64_t index_offset) {
+    if (n == 0) return;
+    fill_normal_kernel<<<1184, 256, 0, Cuda::stream()>>>(p, n, mean, std, seed, index_offset);
+    utils::CHECK_CUDA_EX(cudaGetLastError());
+}
 
 void fill_uniform(float* p, size_t n, float limit, uint64_t seed, uint64_t index_offset) {
     if (n == 0) return;

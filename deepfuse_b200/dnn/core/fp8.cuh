@@ -29,6 +29,11 @@ struct Policy {
 // p[i] = uniform in (-limit, limit) from a counter hash of (seed, i + index_offset), generated on the device
 void fill_uniform(float* p, size_t n, float limit, uint64_t seed, uint64_t index_offset = 0);
 
+// p[i] = mean + std * z, z ~ N(0,1) from the counter-based stream `seed` at index i + index_offset (splitmix64 ->
+// two uniforms -> Box-Muller in fp32), generated on the device.  Any slice of a tensor can be generated on its
+// own, so every rank of a sharded model fills exactly its rows of one global tensor.
+void fill_normal(float* p, size_t n, float mean, float std, uint64_t seed, uint64_t index_offset = 0);
+
 // Process-wide policy read by layers at forward time.
 Policy& policy();
 

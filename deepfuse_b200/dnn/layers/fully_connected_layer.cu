@@ -59,6 +59,21 @@ void FullyConnectedLayer<TT>::initialize_weights_on_device(float limit, uint64_t
     }
 }
 
+template <typename TT>
+void FullyConnectedLayer<TT>::initialize_rows_normal_on_device(float std, uint64_t seed, uint64_t index_offset,
+                                                               int row_begin, int rows) {
+    if constexpr (std::is_same<TT, float>::value) {
+        if (row_begin < 0 || rows < 0 || row_begin + rows > out_features_)
+            throw std::invalid_argument("initialize_rows_normal_on_device: row range outside the weights");
+        fp8::fill_normal(this->weights_.data() + size_t(row_begin) * size_t(in_features_),
+                         size_t(rows) * size_t(in_features_), 0.f, std, seed, index_offset);
+        this->weights_.bump_version();
+        this->bias_.zero();
+    } else {
+        throw std::runtime_error("initialize_rows_normal_on_device: float layers only");
+    }
+}
+
 namespace {
 // rows x cols fp32 -> rows x cols_padded, the new columns zero (zero is the fp8 code 0x00 as well)
 tensor<float> pad_columns(const float* src, int rows, int cols, int cols_padded) {

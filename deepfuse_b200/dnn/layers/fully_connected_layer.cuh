@@ -76,6 +76,9 @@ public:
     // Replaces the weights by uniform values in (-limit, +limit) generated on the device from a counter hash
     // of (seed, element index + index_offset); for models too large to initialise through the host.
     void initialize_weights_on_device(float limit, uint64_t seed, uint64_t index_offset = 0);
+    // Rows [row_begin, row_begin + rows) of this layer's weights <- N(0, std) values of the stream `seed` starting at
+    // element index_offset (fp8::fill_normal): a shard fills its rows of the global tensor; bias <- 0.
+    void initialize_rows_normal_on_device(float std, uint64_t seed, uint64_t index_offset, int row_begin, int rows);
 
 private:
     const uint8_t* external_codes_ = nullptr;

@@ -14,7 +14,8 @@ Gpt2<T>::Gpt2(std::shared_ptr<Tokenizer> tokenizer, int vocab_size, int max_seq_
       max_seq_len_(max_seq_len),
       hidden_dim_(hidden_dim) {
     token_embedding_ = std::make_unique<TokenEmbedding<T>>(vocab_size, hidden_dim, max_seq_len, training_enabled);
-    initialize_weights(token_embedding_->weights(), static_cast<T>(0.02f));
+    // (with fp8::policy().host_init off the weights stay zero until initialize_on_device() or an upload fills them)
+    if (fp8::policy().host_init) initialize_weights(token_embedding_->weights(), static_cast<T>(0.02f));
     positional_encoding_ = std::make_unique<PositionalEncoding<T>>(hidden_dim, max_seq_len, training_enabled);
     for (int i = 0; i < num_layers; ++i) {
         auto block = std::make_unique<TransformerBlock<T>>(hidden_dim, num_heads, intermediate_dim, training_enabled);
@@ -22,7 +23,7 @@ Gpt2<T>::Gpt2(std::shared_ptr<Tokenizer> tokenizer, int vocab_size, int max_seq_
         transformer_blocks_.push_back(std::move(block));
     }
     final_fc_ = std::make_unique<FullyConnectedLayer<T>>(hidden_dim, vocab_size, training_enabled);
-    initialize_weights(final_fc_->weights(), static_cast<T>(0.02f));
+    if (fp8::policy().host_init) initialize_weights(final_fc_->weights(), static_cast<T>(0.02f));
 }
 
 template <typename T>
@@ -39,6 +40,20 @@ void Gpt2<T>::initialize_weights(tensor<T>* weights, T scale) {
     for (auto& v : host) v = static_cast<T>(dist(gen));
     weights->upload(host.data());
     utils::CHECK_CUDA_EX(cudaStreamSynchronize(Cuda::stream()));
+}
+
+template <typename T>
+void Gpt2<T>::initialize_on_device(uint64_t seed, float std) {
+    uint64_t k = seed * 1000ull;
+    tensor<T>* emb = token_embedding_->weights();
+    fp8::fill_normal(emb->data(), emb->numel(), 0.f, std, ++k);
+    emb->bump_version();
+    for (auto& b : transformer_blocks_) {
+        FullyConnectedLayer<T>* fcs[4] = {&b->attention().qkv_projection(), &b->attention().out_projection(),
+                                          &b->mlp_fc1(), &b->mlp_fc2()};
+        for (FullyConnectedLayer<T>* fc : fcs) fc->initialize_rows_normal_on_device(std, ++k, 0, 0, fc->out_features());
+    }
+    final_fc_->initialize_rows_normal_on_device(std, ++k, 0, 0, final_fc_->out_features());
 }
 
 template <typename T>
@@ -102,9 +117,32 @@ tensor<T> Gpt2<T>::forward_logits(const tensor<int>& ids, bool check_ids) {
     const int M = int(x.numel() / size_t(hidden_dim_));
     fp8::quantize(x.data(), x.numel(), fp8::policy().activation_kind, head_q_);
     tensor<T> logits({M, vocab_size_});
-    final_fc_->forward_codes(head_q_.codes.data(), head_q_.kind, head_q_.scale.data(), M, 0, nullptr, logits.data(),
-                             nullptr);
+    head_gemm(M, logits.data(), vocab_size_);
     return logits;
+}
+
+template <typename T>
+void Gpt2<T>::head_gemm(int M, float* logits, int pitch) {
+    if (stage_timing_) utils::CHECK_CUDA_EX(cudaEventRecord(head_ev_[0], Cuda::stream()));
+    final_fc_->forward_codes(head_q_.codes.data(), head_q_.kind, head_q_.scale.data(), M, 0, nullptr, logits, nullptr,
+                             pitch);
+    if (stage_timing_) utils::CHECK_CUDA_EX(cudaEventRecord(head_ev_[1], Cuda::stream()));
+}
+
+template <typename T>
+void Gpt2<T>::set_stage_timing(bool on) {
+    if (on && !head_ev_[0])
+        for (cudaEvent_t& ev : head_ev_) utils::CHECK_CUDA_EX(cudaEventCreate(&ev));
+    stage_timing_ = on;
+}
+
+template <typename T>
+float Gpt2<T>::last_head_ms() const {
+    if (!head_ev_[0]) throw std::runtime_error("Gpt2::last_head_ms: stage timing was never switched on");
+    utils::CHECK_CUDA_EX(cudaEventSynchronize(head_ev_[1]));
+    float ms = 0.f;
+    utils::CHECK_CUDA_EX(cudaEventElapsedTime(&ms, head_ev_[0], head_ev_[1]));
+    return ms;
 }
 
 template <typename T>
@@ -115,18 +153,19 @@ tensor<T> Gpt2<T>::forward_logits_pitched(const tensor<int>& ids, bool check_ids
     fp8::quantize(x.data(), x.numel(), fp8::policy().activation_kind, head_q_);
     const int pitch = logits_pitch();
     tensor<T> logits({M, pitch});
-    final_fc_->forward_codes(head_q_.codes.data(), head_q_.kind, head_q_.scale.data(), M, 0, nullptr, logits.data(),
-                             nullptr, pitch);
+    head_gemm(M, logits.data(), pitch);
     return logits;
 }
 
 template <typename T>
 Gpt2<T>::~Gpt2() {
+    for (cudaEvent_t ev : head_ev_)
+        if (ev) cudaEventDestroy(ev);
     if (streamer_) df8_streamer_destroy(streamer_);
 }
 
 template <typename T>
-void Gpt2<T>::enable_layer_streaming(int slots, bool release_fp32) {
+void Gpt2<T>::enable_layer_streaming(int slots, bool release_fp32, df8_comm* comm) {
     if (streamer_ || transformer_blocks_.empty()) return;
     const int L = int(transformer_blocks_.size());
     auto fcs_of = [](TransformerBlock<T>& blk) {
@@ -135,7 +174,7 @@ void Gpt2<T>::enable_layer_streaming(int slots, bool release_fp32) {
     };
     size_t layer_bytes = 0;
     for (FullyConnectedLayer<T>* fc : fcs_of(*transformer_blocks_[0])) layer_bytes += (fc->weight_code_bytes() + 255) & ~size_t(255);
-    utils::CHECK_DF8(df8_streamer_create(layer_bytes, slots, L, &streamer_));
+    utils::CHECK_DF8(df8_streamer_create_sharded(layer_bytes, slots, L, comm, &streamer_));
     int n_slots = 0;
     utils::CHECK_DF8(df8_streamer_stats(streamer_, nullptr, nullptr, &n_slots));
     stream_slots_ = n_slots;
@@ -171,6 +210,31 @@ void Gpt2<T>::disable_layer_streaming() {
     }
     df8_streamer_destroy(streamer_);
     streamer_ = nullptr;
+}
+
+template <typename T>
+void Gpt2<T>::resize_streaming_slots(int slots) {
+    if (!streamer_) throw std::runtime_error("Gpt2::resize_streaming_slots: layer streaming is off");
+    utils::CHECK_DF8(df8_streamer_resize(streamer_, slots));
+    int n_slots = 0;
+    utils::CHECK_DF8(df8_streamer_stats(streamer_, nullptr, nullptr, &n_slots));
+    stream_slots_ = n_slots;
+    for (int l = 0; l < stream_slots_; ++l) utils::CHECK_DF8(df8_streamer_prefetch(streamer_, l));
+}
+
+template <typename T>
+void Gpt2<T>::streaming_traffic(unsigned long long* h2d_bytes, unsigned long long* gathered_bytes) const {
+    if (h2d_bytes) *h2d_bytes = 0;
+    if (gathered_bytes) *gathered_bytes = 0;
+    if (streamer_) utils::CHECK_DF8(df8_streamer_traffic(streamer_, h2d_bytes, gathered_bytes));
+}
+
+template <typename T>
+float Gpt2<T>::time_layer_uploads() {
+    if (!streamer_) throw std::runtime_error("Gpt2::time_layer_uploads: layer streaming is off");
+    float ms = 0.f;
+    utils::CHECK_DF8(df8_streamer_time_uploads(streamer_, &ms));
+    return ms;
 }
 
 template <typename T>

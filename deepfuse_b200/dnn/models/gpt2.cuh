@@ -61,8 +61,16 @@ public:
     // rounded up to a multiple of 32 floats its epilogue leaves through TMA stores.
     tensor<T> forward_logits_pitched(const tensor<int>& ids, bool check_ids = true);
     int logits_pitch() const { return (vocab_size_ + 31) / 32 * 32; }
+    // Measurement aid: with stage timing on, forward_logits / forward_logits_pitched bracket the vocabulary-head
+    // GEMM (the longest single launch of a forward) with two events on the stream; last_head_ms() waits for the
+    // second one and returns the launch's duration inside the forward, with the cache state the blocks leave.
+    void set_stage_timing(bool on);
+    float last_head_ms() const;
     void set_mlp_gelu(bool on);
     void set_causal(bool causal);
+    // Every weight matrix <- N(0, std) generated on the device (fp8::fill_normal), biases <- 0; stream numbers
+    // seed*1000 + 1, 2, ... in the order embedding, then per block qkv, out, fc1, fc2, then the head.
+    void initialize_on_device(uint64_t seed, float std = 0.02f);
 
     // Layer streaming (README.md:212-220 sketches `layer->load_weights_to_gpu()`; no such code exists
     // upstream).  The e4m3 codes of every block's four weight matrices move to pinned host memory; the
@@ -70,10 +78,19 @@ public:
     // stream while layer l computes.  Scales, biases and LayerNorm parameters stay resident.
     // release_fp32 also frees the blocks' fp32 master weights on the device (weights() then returns
     // empty tensors; re-uploading them requires disabling streaming first).
-    void enable_layer_streaming(int slots = 2, bool release_fp32 = false);
+    // With `comm` (ranks that work on shares of one batch, one process per GPU) each rank uploads 1/world of a
+    // layer and an all-gather over NVLink on the copy stream completes the slot; every rank must then run the
+    // same sequence of forwards.
+    void enable_layer_streaming(int slots = 2, bool release_fp32 = false, df8_comm* comm = nullptr);
     void disable_layer_streaming();
     bool layer_streaming() const { return streamer_ != nullptr; }
     unsigned long long streamed_bytes() const;
+    // measurement aids: another number of device slots (all layers resident when slots >= layers), the bytes
+    // this rank copied from the host / received from its peers, and the device time of uploading every layer
+    // once with nothing else running
+    void resize_streaming_slots(int slots);
+    void streaming_traffic(unsigned long long* h2d_bytes, unsigned long long* gathered_bytes) const;
+    float time_layer_uploads();
 
     int vocab_size() const { return vocab_size_; }
     int hidden_dim() const { return hidden_dim_; }
@@ -96,6 +113,9 @@ private:
     fp8::Quantized head_q_;
     df8_streamer* streamer_ = nullptr;
     int stream_slots_ = 0;
+    bool stage_timing_ = false;
+    cudaEvent_t head_ev_[2] = {nullptr, nullptr};
+    void head_gemm(int M, float* logits, int pitch);
 
 public:
     ~Gpt2() override;

@@ -76,20 +76,27 @@ Gpt2ColumnSharded<T>::Gpt2ColumnSharded(df8_comm* comm, int vocab_size, int max_
     if (world_ > 1) final_fc_->set_shard_comm(comm_);
 }
 
+// The shards of the model dnn::Gpt2::initialize_on_device(seed, std) makes: every rank fills its rows of each
+// global weight matrix from the same counter-based streams (qkv: the rows of this rank's heads inside the Q, the
+// K and the V block of the fused [3E, E] matrix).
 template <typename T>
-void Gpt2ColumnSharded<T>::initialize_on_device(uint64_t seed) {
-    const float limit = 0.02f * 1.7320508f;  // uniform with the standard deviation of N(0, 0.02)
-    uint64_t tag = seed * 1000003ull;
+void Gpt2ColumnSharded<T>::initialize_on_device(uint64_t seed, float std) {
+    uint64_t k = seed * 1000ull;
+    const uint64_t E = uint64_t(hidden_dim_), F = uint64_t(ffn_dim_);
+    const int Eg = hidden_dim_ / world_, Fg = ffn_dim_ / world_;
+    tensor<T>* emb = token_embedding_->weights();  // replicated
+    fp8::fill_normal(emb->data(), emb->numel(), 0.f, std, ++k);
+    emb->bump_version();
     for (auto& bp : blocks_) {
         Block& b = *bp;
-        FullyConnectedLayer<T>* fcs[4] = {&b.qkv, &b.out, &b.fc1, &b.fc2};
-        for (FullyConnectedLayer<T>* fc : fcs)
-            fc->initialize_weights_on_device(limit, ++tag, uint64_t(rank_) * fc->weights()->numel());
+        ++k;
+        for (int part = 0; part < 3; ++part)  // Q, K, V
+            b.qkv.initialize_rows_normal_on_device(std, k, (uint64_t(part) * E + uint64_t(rank_) * Eg) * E, part * Eg, Eg);
+        b.out.initialize_rows_normal_on_device(std, ++k, uint64_t(rank_) * Eg * E, 0, Eg);
+        b.fc1.initialize_rows_normal_on_device(std, ++k, uint64_t(rank_) * Fg * E, 0, Fg);
+        b.fc2.initialize_rows_normal_on_device(std, ++k, uint64_t(rank_) * Eg * F, 0, Eg);
     }
-    final_fc_->initialize_weights_on_device(limit, ++tag, uint64_t(vocab_begin_) * uint64_t(hidden_dim_));
-    // the (replicated) embedding table: the same values on every rank
-    fp8::fill_uniform(token_embedding_->weights()->data(), token_embedding_->weights()->numel(), limit, ++tag, 0);
-    token_embedding_->weights()->bump_version();
+    final_fc_->initialize_rows_normal_on_device(std, ++k, uint64_t(vocab_begin_) * E, 0, vocab_rows_);
 }
 
 template <typename T>

@@ -61,7 +61,7 @@ public:
     void set_causal(bool causal) { causal_ = causal; }
     // Device-side random initialisation of this rank's shards (uniform, the N(0, 0.02) standard deviation),
     // for shapes too large to initialise through the host.
-    void initialize_on_device(uint64_t seed);
+    void initialize_on_device(uint64_t seed, float std = 0.02f);
 
     int rank() const { return rank_; }
     int world() const { return world_; }

@@ -226,10 +226,28 @@ df8_status df8_embed_pe_f32(const int32_t* ids, int B, int T, int E, int V, cons
  *     ... launch the layer's kernels on the compute stream ...
  *     release(l, compute)  -> the slot may be overwritten once those kernels are done
  *     prefetch((l + n_slots) % n_layers)   -> upload of a later layer overlaps the following compute
+ * Slots are filled in the order of the uploads (a ring), so with this loop the slot refilled is the one just
+ * released, for any ratio of layers to slots.
  * create allocates (cudaHostAlloc, cudaMalloc, stream, events); destroy frees.  The other calls
- * neither allocate nor synchronise.  Not thread-safe: one streamer per model per host thread. */
+ * neither allocate nor synchronise, except resize and time_uploads (both wait for the device).
+ * Not thread-safe: one streamer per model per host thread. */
 typedef struct df8_streamer df8_streamer;
+typedef struct df8_comm df8_comm;
 df8_status df8_streamer_create(size_t slot_bytes, int n_slots, int n_layers, df8_streamer** out);
+/* The same for ranks that work on shares of one batch with replicated weights (one process per GPU, the same
+ * layer loop on every rank): each upload copies only this rank's 1/world share of the layer from ITS pinned
+ * arena and an all-gather over `comm` on the copy stream completes the slot, so host->device bytes per rank fall
+ * world-fold.  prefetch / acquire are then collectives: every rank must issue the same sequence.  comm == NULL
+ * (or a single rank) is df8_streamer_create.  The communicator is borrowed, not owned. */
+df8_status df8_streamer_create_sharded(size_t slot_bytes, int n_slots, int n_layers, df8_comm* comm,
+                                       df8_streamer** out);
+/* Replaces the ring of device slots by one of n_slots (waits for the device; every layer becomes non-resident). */
+df8_status df8_streamer_resize(df8_streamer* s, int n_slots);
+/* bytes this rank has copied from host memory / received from its peers so far */
+df8_status df8_streamer_traffic(df8_streamer* s, unsigned long long* h2d_bytes_h, unsigned long long* gathered_bytes_h);
+/* Uploads every layer once, back to back, with nothing else running, and returns the device time in ms
+ * (measurement aid: the upload time a forward has to hide; waits for the device; collective when sharded). */
+df8_status df8_streamer_time_uploads(df8_streamer* s, float* ms_h);
 df8_status df8_streamer_destroy(df8_streamer* s);
 /* host_ptr_h receives the pinned HOST address where layer `layer`'s slot_bytes bytes are kept */
 df8_status df8_streamer_host_ptr(df8_streamer* s, int layer, void** host_ptr_h);
@@ -247,7 +265,6 @@ df8_status df8_streamer_stats(df8_streamer* s, unsigned long long* bytes_uploade
  * any host channel; df8_comm_init_rank is collective and allocates; the data calls are enqueued on
  * `stream` and neither allocate nor synchronise.  df8_comm_abort ends outstanding collectives with an
  * error when a peer has gone away (host-side failure handling; never on the data path). */
-typedef struct df8_comm df8_comm;
 df8_status df8_comm_available(int* version_h);
 df8_status df8_comm_unique_id(void* id_h);
 df8_status df8_comm_init_rank(const void* id_h, int world, int rank, df8_comm** out);

@@ -40,6 +40,13 @@ int dnn_gpt2_num_params(dnn_gpt2* m);
 int dnn_gpt2_param_info(dnn_gpt2* m, int index, char* name_h, int name_cap, int* shape_h, int* ndim_h);
 int dnn_gpt2_param_upload(dnn_gpt2* m, int index, const float* data_h);
 int dnn_gpt2_param_download(dnn_gpt2* m, int index, float* data_h);
+/* Every weight matrix <- N(0, std) generated on the device from counter-based streams numbered seed*1000 + 1, 2, ...
+ * (embedding; per block qkv, out, fc1, fc2; head), biases <- 0: the values of deepfuse_b200/synthetic.py
+ * make_gpt2_params(cfg, seed, std) up to the last bit of fp32 log / cos, without the trip through the host. */
+int dnn_gpt2_initialize_on_device(dnn_gpt2* m, unsigned long long seed, float std);
+/* Gpt2::set_stage_timing / last_head_ms: events around the vocabulary-head GEMM inside the forward. */
+int dnn_gpt2_set_stage_timing(dnn_gpt2* m, int on);
+int dnn_gpt2_last_head_ms(dnn_gpt2* m, float* ms_h);
 /* Quantises every weight now (otherwise it happens lazily in the first forward). */
 int dnn_gpt2_prepare(dnn_gpt2* m);
 /* logits [B*T, vocab] fp32 stay on the device, owned by the handle until the next forward;
@@ -60,6 +67,13 @@ int dnn_gpt2_forward_ids(dnn_gpt2* m, const int32_t* ids_h, int T, float* hidden
 /* Gpt2::enable_layer_streaming: block weight codes move to pinned host memory and are uploaded per layer
  * through `slots` device buffers on a side stream; release_fp32 also frees the fp32 block weights. */
 int dnn_gpt2_enable_streaming(dnn_gpt2* m, int slots, int release_fp32);
+/* the same with each rank of `comm` (a df8_comm*, see include/df8.h) uploading 1/world of every layer and an all-gather
+ * completing the slot; every rank then runs the same sequence of forwards */
+int dnn_gpt2_enable_streaming_sharded(dnn_gpt2* m, int slots, int release_fp32, void* comm);
+/* measurement aids (Gpt2::resize_streaming_slots, streaming_traffic, time_layer_uploads) */
+int dnn_gpt2_resize_streaming_slots(dnn_gpt2* m, int slots);
+int dnn_gpt2_streaming_traffic(dnn_gpt2* m, unsigned long long* h2d_bytes_h, unsigned long long* gathered_bytes_h);
+int dnn_gpt2_time_layer_uploads(dnn_gpt2* m, float* ms_h);
 int dnn_gpt2_disable_streaming(dnn_gpt2* m);
 unsigned long long dnn_gpt2_streamed_bytes(dnn_gpt2* m);
 int dnn_gpt2_save(dnn_gpt2* m, const char* path);

@@ -278,9 +278,57 @@ def test_gpt2_layer_streaming_is_bit_identical(df8, dnn, oracle, cuda, slots, re
     model.set_stream(torch.cuda.current_stream())
     layer_bytes = (3 * 128 * 128 + 128 * 128 + 2 * 128 * 512)
     assert model.streamed_bytes() >= 3 * 5 * layer_bytes
+    # the slots form a ring over the execution order, so a forward uploads every layer exactly once whatever
+    # the ratio of layers (5) to slots (2, 3, 1): no layer that is still to be used is ever evicted
+    before = model.streamed_bytes()
+    with torch.cuda.stream(side):
+        model.set_stream(side)
+        model.forward_logits(ids)
+        side.synchronize()
+    model.set_stream(torch.cuda.current_stream())
+    assert model.streamed_bytes() - before == 5 * layer_bytes
+    h2d, gathered = model.streaming_traffic()
+    assert gathered == 0 and h2d == model.streamed_bytes()  # a single rank copies everything itself
     if not release:
         model.disable_streaming()
         again = df8.device_view(torch, model.forward_logits(ids), (3 * 64, 300)).clone()
         assert torch.equal(again, want)
     assert df8.status_word() == (0, 0)
+    model.close()
+
+
+def test_gpt2_device_init_equals_host_generated_params(df8, dnn, oracle, cuda):
+    """Gpt2::initialize_on_device(seed) draws every weight matrix on the device from the counter-based streams
+    that deepfuse_b200.synthetic.make_gpt2_params (numpy) and the oracle's generator (C) use: the same model, up
+    to the last bit of fp32 log / cos."""
+    import torch
+    from deepfuse_b200 import synthetic
+
+    cfg = dict(vocab=300, max_seq_len=64, layers=2, heads=2, hidden=128, ffn=256)
+    want = synthetic.make_gpt2_params(cfg, seed=9, std=0.02)
+    df8.dnn_check(dnn.dnn_set_host_init(0))
+    try:
+        model = df8.Gpt2(**cfg)
+    finally:
+        df8.dnn_check(dnn.dnn_set_host_init(1))
+    model.initialize_on_device(9, 0.02)
+    for i, (name, shape) in enumerate(model.param_names()):
+        got = np.zeros(int(np.prod(shape)), np.float32)
+        df8.dnn_check(dnn.dnn_gpt2_param_download(model.h, i, p(got)))
+        if name.endswith("gamma") or name.endswith("beta"):
+            continue
+        assert np.allclose(got, want[name].ravel(), rtol=0, atol=1e-7), name
+    ids = torch.from_numpy(oracle.fill_token_ids(2 * 64, seed=1, vocab=300).reshape(2, 64)).to(cuda)
+    ptr, pitch = model.forward_logits_pitched(ids)
+    assert pitch == 320
+    pitched = df8.device_view(torch, ptr, (128, pitch))[:, :300].clone()
+    dense = df8.device_view(torch, model.forward_logits(ids), (128, 300)).clone()
+    assert torch.equal(pitched, dense)
+    host = torch.empty((128, 300), dtype=torch.float32).pin_memory()
+    model.copy_logits_host(host)
+    torch.cuda.synchronize()
+    assert torch.equal(host, dense.cpu())
+    model.set_stage_timing(True)
+    model.forward_logits_pitched(ids)
+    assert 0.0 < model.last_head_ms() < 50.0
     model.close()

@@ -770,16 +770,16 @@ class Gpt2ShardedWorkload(Gpt2Workload):
             self.comm.close()
 
     def step(self):
-        self.logits_ptr = self.model.forward_logits_shard(self.ids, check_ids=False)
+        self.logits_ptr, self.pitch = self.model.forward_logits_shard_pitched(self.ids, check_ids=False)
 
     def e2e_setup(self, torch, dev, full=True):
         pass
 
     def e2e_step(self):
         torch = self.torch
-        ptr = self.model.forward_logits_shard_host(self.ids_host)
-        logits = self.df8.device_view(torch, ptr, (self.B, self.T, self.model.vocab_rows))
-        self.last_logits.copy_(logits[:, -1, :], non_blocking=True)
+        ptr, pitch = self.model.forward_logits_shard_pitched(self.ids_host, check_ids=False)
+        logits = self.df8.device_view(torch, ptr, (self.B, self.T, pitch))
+        self.last_logits.copy_(logits[:, -1, :self.model.vocab_rows], non_blocking=True)
 
     e2e_step_next_token = e2e_step
 
@@ -1043,6 +1043,15 @@ def secondary_forward(torch, df8, dev, rank, world, comm, make, timed, barrier, 
                "scaling": "strong", "config": wl.config(world), "dtype": wl.dtype, "clocks": clocks,
                "model_flops_per_token": gpt2_flops_per_token(wl.c, wl.T)}
         rec["model_tflops"] = round(rec["value"] * rec["model_flops_per_token"] / 1e12, 1)
+        if hasattr(wl.model, "bytes_pushed"):
+            b0 = wl.model.bytes_pushed()
+            wl.step()
+            torch.cuda.synchronize()
+            pushed = wl.model.bytes_pushed() - b0
+            rec["exchange"] = {"bytes_pushed_per_forward_per_rank": pushed,
+                               "transport": "peer-mapped buffers + copy engines" if pushed > 0 else
+                               ("none (single rank)" if world == 1 else "NCCL fallback"),
+                               "nvlink_gbs_if_fully_exposed": round(pushed / (ms / steps) / 1e6, 1)}
         if getattr(wl.model, "_streaming", False):
             rec["streaming"] = streaming_report(torch, wl, steps + warmup, ms / steps, timed, max_over_ranks)
         rec["device_wait_status"] = list(df8.status_word())

@@ -47,6 +47,9 @@ _SIGNATURES = {
     "df8_layernorm_f32": [_vp, _i, _i, _vp, _vp, _f, _vp, _vp, _vp],
     "df8_layernorm_quantize_f32": [_vp, _i, _i, _vp, _vp, _f, _i, _vp, _vp, _vp, _vp, _vp],
     "df8_layernorm_quantize_f32_noalloc": [_vp, _i, _i, _vp, _vp, _f, _i, _vp, _vp, _vp, _vp],
+    "df8_layernorm_shard_stats_f32": [_vp, _i, _i, _vp, _vp],
+    "df8_layernorm_shard_amax_f32": [_vp, _i, _i, _vp, _i, _vp, _vp, _f, _vp, _vp, _vp],
+    "df8_layernorm_shard_quantize_f32": [_vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp],
     "df8_embed_pe_f32": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
     "df8_attention_fp8": [_vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp, _vp],
     "df8_softmax_masked_f32": [_vp, _vp, _i, _i, _i, _i, _vp, _vp],
@@ -69,6 +72,11 @@ _SIGNATURES = {
     "df8_comm_abort": [_vp],
     "df8_comm_rank": [_vp, _vp, _vp],
     "df8_comm_allgather_u8": [_vp, _vp, _vp, _sz, _vp],
+    "df8_comm_symm_alloc": [_vp, _sz, _vp],
+    "df8_comm_p2p_enabled": [_vp, _vp],
+    "df8_comm_allgather_symm": [_vp, _vp, _sz, _sz, _vp],
+    "df8_comm_allreduce_max_p2p": [_vp, _vp, _vp],
+    "df8_comm_bytes_pushed": [_vp, _vp],
     "df8_comm_allreduce_max_f32": [_vp, _vp, _sz, _vp],
     "df8_gemm_fp8_tn_amax": [_vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "df8_gemm_fp8_tn_codes": [_vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
@@ -259,6 +267,8 @@ _DNN_SIGNATURES = {
     "dnn_gpt2cs_prepare": [_vp],
     "dnn_gpt2cs_forward_logits_shard": [_vp, _vp, _i, _i, _i, _vp],
     "dnn_gpt2cs_forward_logits_shard_host": [_vp, _vp, _i, _i, _vp],
+    "dnn_gpt2cs_forward_logits_shard_pitched": [_vp, _vp, _i, _i, _i, _i, _vp, _vp],
+    "dnn_gpt2cs_forward_hidden": [_vp, _vp, _i, _i, _vp],
 }
 
 
@@ -279,6 +289,8 @@ def dnn_lib() -> C.CDLL:
         handle.dnn_gpt2_streamed_bytes.argtypes = [_vp]
         handle.dnn_gpt2_load.restype = C.c_void_p
         handle.dnn_gpt2_load.argtypes = [C.c_char_p]
+        handle.dnn_gpt2cs_bytes_pushed.restype = C.c_ulonglong
+        handle.dnn_gpt2cs_bytes_pushed.argtypes = [_vp]
         handle.dnn_gpt2cs_create.restype = C.c_void_p
         handle.dnn_gpt2cs_create.argtypes = [_vp] + [_i] * 6
         for name, args in _DNN_SIGNATURES.items():
@@ -555,6 +567,24 @@ class Gpt2ColumnSharded:
         dnn_check(dnn_lib().dnn_gpt2cs_forward_logits_shard(self.h, ptr(ids_dev), B, T, int(check_ids), C.byref(out)),
                   "dnn_gpt2cs_forward_logits_shard")
         return out.value
+
+    def forward_logits_shard_pitched(self, ids, check_ids=True) -> tuple[int, int]:
+        """ids on the device or pinned on the host; returns (device pointer, pitch) of fp32 logits [B*T, pitch]."""
+        out, pitch = C.c_void_p(0), C.c_int(0)
+        B, T = ids.shape
+        dnn_check(dnn_lib().dnn_gpt2cs_forward_logits_shard_pitched(self.h, ids.data_ptr(), 0 if ids.is_cuda else 1, B, T,
+                                                                    int(check_ids), C.byref(out), C.byref(pitch)),
+                  "dnn_gpt2cs_forward_logits_shard_pitched")
+        return out.value, pitch.value
+
+    def forward_hidden(self, ids_dev) -> int:
+        out = C.c_void_p(0)
+        B, T = ids_dev.shape
+        dnn_check(dnn_lib().dnn_gpt2cs_forward_hidden(self.h, ptr(ids_dev), B, T, C.byref(out)), "dnn_gpt2cs_forward_hidden")
+        return out.value
+
+    def bytes_pushed(self) -> int:
+        return int(dnn_lib().dnn_gpt2cs_bytes_pushed(self.h))
 
     def forward_logits_shard_host(self, ids_host) -> int:
         out = C.c_void_p(0)

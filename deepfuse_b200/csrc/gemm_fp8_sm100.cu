@@ -1214,10 +1214,16 @@ df8_status launch_gemm_bn(bool wide, const CUtensorMap& ta, const CUtensorMap& t
 
 // DF8_GEMM_PAIR=0 / 1 in the environment (read at every call) forces the choice for profiling and tests;
 // otherwise the pair kernel takes problems that give every CTA pair at least one full 256 x 256 tile.
-bool use_pair_kernel(int M, int N, int K, int sms) {
+bool use_pair_kernel(int M, int N, int K, int sms, int mode) {
     const char* e = getenv("DF8_GEMM_PAIR");
     if (e && e[0] == '0') return false;
     if (e && e[0] == '1') return M > 0 && N > 0;
+    // Outputs far larger than L2 written through TMA stores (the vocabulary head: 1.6 GB of logits): the tile's
+    // stores are the longest phase and slow the operand loads of the next tile down; a pair loads half of W per
+    // CTA and hides more of them.  Measured at 8192 x 50257 x 768 into rows of 50272 floats: 462 us with pairs,
+    // 598 us without (and 578 us for dense rows of 50257 floats through 4-byte stores); at 8192 x 2304 x 768 the
+    // single-CTA kernel stays ahead (30 against 33 us).
+    if (mode == kOutF32Tma && M >= 256 && N >= 256 && double(M) * double(N) * 4.0 >= 512e6) return true;
     // measured on B200 (M = 8192): 8192 x 8192 x 8192 runs at 2547 TFLOP/s with CTA pairs against 2245 without;
     // at K = 768 the epilogue dominates and the pairs' coupled accumulator hand-back costs a few per cent
     const long tiles2 = long((M + 255) / 256) * ((N + 255) / 256);
@@ -1258,7 +1264,7 @@ df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uin
         return make_tmap_2d_f32(&to, args.out, uint64_t(M), uint64_t(N), uint64_t(args.ldc) * sizeof(float), 32, 32, 128);
     };
     // CTA pairs on 256 x 256 tiles when the problem fills them (see gemm_fp8_tn_pair_kernel)
-    if (use_pair_kernel(M, N, K, sms)) {
+    if (use_pair_kernel(M, N, K, sms, mode)) {
         if (want_fused) return DF8_OK;
         // Tile width of the fp32 modes, by the measured per-K-block and per-chunk costs (cycles): a K block is
         // bound by the tensor core (2 BN) or by the CTA's operand bytes arriving at ~50 bytes per cycle while the

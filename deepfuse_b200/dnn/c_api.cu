@@ -535,6 +535,32 @@ extern "C" int dnn_gpt2cs_forward_logits_shard(dnn_gpt2cs* m, const int32_t* ids
     });
 }
 
+extern "C" int dnn_gpt2cs_forward_logits_shard_pitched(dnn_gpt2cs* m, const int32_t* ids, int ids_on_host, int B, int T,
+                                                       int check_ids, float** logits_d, int* pitch_h) {
+    return guarded([&] {
+        m->stage_ids(ids, B, T, ids_on_host ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice);
+        m->last.reset();
+        m->last = std::make_unique<dnn::tensor<float>>(m->model->forward_logits_shard_pitched(*m->ids, check_ids != 0));
+        *logits_d = m->last->data();
+        if (pitch_h) *pitch_h = m->model->logits_pitch();
+    });
+}
+
+extern "C" int dnn_gpt2cs_forward_hidden(dnn_gpt2cs* m, const int32_t* ids_d, int B, int T, float** hidden_d) {
+    return guarded([&] {
+        m->stage_ids(ids_d, B, T, cudaMemcpyDeviceToDevice);
+        m->last.reset();
+        m->last = std::make_unique<dnn::tensor<float>>(m->model->forward_hidden(*m->ids, true));
+        *hidden_d = m->last->data();
+    });
+}
+
+extern "C" unsigned long long dnn_gpt2cs_bytes_pushed(dnn_gpt2cs* m) {
+    unsigned long long b = 0;
+    guarded([&] { b = m->model->bytes_pushed(); });
+    return b;
+}
+
 extern "C" int dnn_gpt2cs_forward_logits_shard_host(dnn_gpt2cs* m, const int32_t* ids_h, int B, int T,
                                                     float** logits_d) {
     return guarded([&] {

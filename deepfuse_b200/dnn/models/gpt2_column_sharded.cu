@@ -7,24 +7,6 @@ namespace dnn {
 
 namespace {
 
-__global__ void add_kernel_f32(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
-                               size_t n4) {
-    const float4* a4 = reinterpret_cast<const float4*>(a);
-    const float4* b4 = reinterpret_cast<const float4*>(b);
-    float4* o4 = reinterpret_cast<float4*>(out);
-    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += size_t(gridDim.x) * blockDim.x) {
-        const float4 x = a4[i], y = b4[i];
-        o4[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
-    }
-}
-
-// out = a + b, n a multiple of 4 and the pointers 16-byte aligned (rows of E floats, E % 16 == 0)
-void add_f32(const float* a, const float* b, float* out, size_t n) {
-    if (n == 0) return;
-    add_kernel_f32<<<1184, 256, 0, Cuda::stream()>>>(a, b, out, n / 4);
-    utils::CHECK_CUDA_EX(cudaGetLastError());
-}
-
 template <typename TensorT>
 void ensure(TensorT& t, size_t n) {
     if (t.numel() != n) t = TensorT({int(n)});
@@ -54,6 +36,10 @@ Gpt2ColumnSharded<T>::Gpt2ColumnSharded(df8_comm* comm, int vocab_size, int max_
         (3 * hidden_dim / world_) % 32 != 0)
         throw std::invalid_argument("Gpt2ColumnSharded: heads, hidden_dim / 16 and intermediate_dim / 32 must be "
                                     "divisible by the number of ranks (" + std::to_string(world_) + ")");
+    // the gathered codes are read in place as one K slab per rank; a slab is whole 128-column K blocks
+    if (world_ > 1 && ((hidden_dim / world_) % 128 != 0 || (intermediate_dim / world_) % 128 != 0))
+        throw std::invalid_argument("Gpt2ColumnSharded: hidden_dim and intermediate_dim must be multiples of 128 x the "
+                                    "number of ranks (" + std::to_string(world_) + ")");
     const int Eg = hidden_dim / world_, Fg = intermediate_dim / world_;
     const int per_rank = (vocab_size + world_ - 1) / world_;
     vocab_begin_ = std::min(rank_ * per_rank, vocab_size);
@@ -99,91 +85,162 @@ void Gpt2ColumnSharded<T>::initialize_on_device(uint64_t seed, float std) {
     final_fc_->initialize_rows_normal_on_device(std, ++k, uint64_t(vocab_begin_) * E, 0, vocab_rows_);
 }
 
-template <typename T>
-void Gpt2ColumnSharded<T>::gather_columns(const void* local, int M, int bytes_per_row, void* full) {
-    const size_t bytes = size_t(M) * size_t(bytes_per_row);
-    if (world_ == 1) {
-        utils::CHECK_CUDA_EX(cudaMemcpyAsync(full, local, bytes, cudaMemcpyDeviceToDevice, Cuda::stream()));
-        return;
-    }
-    if (gathered_.numel() < bytes * size_t(world_)) throw std::runtime_error("Gpt2ColumnSharded: gather buffer too small");
-    utils::CHECK_DF8(df8_comm_allgather_u8(comm_, static_cast<const uint8_t*>(local), gathered_.data(), bytes,
-                                           fp8::stream()));
-    utils::CHECK_DF8(df8_interleave_gathered_u8(gathered_.data(), M, bytes_per_row, world_,
-                                                static_cast<uint8_t*>(full), fp8::stream()));
-}
+// ---- single rank ----------------------------------------------------------------------------------
 
 template <typename T>
-void Gpt2ColumnSharded<T>::block_forward(Block& b, float* x, int B, int T_len) {
+void Gpt2ColumnSharded<T>::block_forward_single(Block& b, float* x, int B, int T_len) {
     const int M = B * T_len, E = hidden_dim_, F = ffn_dim_;
-    const int Eg = E / world_, Fg = F / world_, Hg = num_heads_ / world_, D = E / num_heads_;
     const df8_kind act = fp8::policy().activation_kind;
     const df8_stream st = fp8::stream();
     fp8::PassScope amax_slots;
-    auto all_max = [&](float* am) {
-        if (world_ > 1) utils::CHECK_DF8(df8_comm_allreduce_max_f32(comm_, am, 1, st));
-    };
-    ensure(qkvq_.codes, size_t(M) * 3 * Eg);
-    ensure(attn_f32_, size_t(M) * Eg);
-    ensure(attnq_.codes, size_t(M) * E);
-    ensure(y_local_, size_t(M) * Eg);
-    ensure(y_full_, size_t(M) * E);
     ensure(x1_, size_t(M) * E);
-    ensure(hidden_q_.codes, size_t(M) * F);
-    ensure(slice_, size_t(M) * Fg);
-    ensure(gathered_, size_t(M) * std::max(size_t(F), size_t(E) * 4));
+    ensure(attn_f32_, size_t(M) * E);
+    b.norm1.forward_quantized(x, M, act, ln_q_);
+    b.qkv.forward_codes_quantized(ln_q_.codes.data(), ln_q_.kind, ln_q_.scale.data(), M, 0, act, qkvq_);
+    float* am = fp8::amax_slot(amax_.data());
+    utils::CHECK_DF8(df8_attention_fp8(qkvq_.codes.data(), qkvq_.kind, qkvq_.scale.data(), B, T_len, num_heads_,
+                                       E / num_heads_, causal_ ? DF8_MASK_CAUSAL : DF8_MASK_NONE, nullptr, 0,
+                                       attn_f32_.data(), am, st));
+    fp8::quantize_with_amax(attn_f32_.data(), size_t(M) * E, act, am, attnq_);
+    b.out.forward_codes(attnq_.codes.data(), attnq_.kind, attnq_.scale.data(), M, DF8_EPI_RESIDUAL, x, x1_.data(), nullptr);
+    b.norm2.forward_quantized(x1_.data(), M, act, ln_q_);
+    b.fc1.forward_codes_quantized(ln_q_.codes.data(), ln_q_.kind, ln_q_.scale.data(), M, mlp_gelu_ ? DF8_EPI_GELU : 0, act,
+                                  hidden_q_);
+    b.fc2.forward_codes(hidden_q_.codes.data(), hidden_q_.kind, hidden_q_.scale.data(), M, DF8_EPI_RESIDUAL, x1_.data(), x,
+                        nullptr);
+    (void)F;
+}
+
+// ---- several ranks --------------------------------------------------------------------------------
+
+template <typename T>
+void Gpt2ColumnSharded<T>::all_max(float* amax) {
+    utils::CHECK_DF8(df8_comm_allreduce_max_p2p(comm_, amax, fp8::stream()));
+}
+
+// The buffers every peer writes into are allocated collectively, for the largest M seen so far (a buffer of the
+// communicator lives as long as the communicator).
+template <typename T>
+void Gpt2ColumnSharded<T>::ensure_work_space(int M) {
+    const size_t E = size_t(hidden_dim_), F = size_t(ffn_dim_), g = size_t(world_);
+    if (M > work_rows_) {
+        void* p = nullptr;
+        utils::CHECK_DF8(df8_comm_symm_alloc(comm_, size_t(M) * E, &p));
+        sym_ln_ = static_cast<uint8_t*>(p);
+        utils::CHECK_DF8(df8_comm_symm_alloc(comm_, size_t(M) * E, &p));
+        sym_attn_ = static_cast<uint8_t*>(p);
+        utils::CHECK_DF8(df8_comm_symm_alloc(comm_, size_t(M) * F, &p));
+        sym_hidden_ = static_cast<uint8_t*>(p);
+        utils::CHECK_DF8(df8_comm_symm_alloc(comm_, 2 * g * size_t(M) * 2 * sizeof(float), &p));
+        sym_stats_ = static_cast<float*>(p);
+        work_rows_ = M;
+    }
+    ensure(x_shard_, size_t(M) * E / g);
+    ensure(x1_shard_, size_t(M) * E / g);
+    ensure(attn_f32_, size_t(M) * E / g);
+    ensure(row_stats_, size_t(M) * 2);
+    ensure(qkvq_.codes, size_t(M) * 3 * E / g);
+}
+
+template <typename T>
+void Gpt2ColumnSharded<T>::layernorm_quantize_sharded(LayerNormLayer<T>& norm, const float* x, int M, int which) {
+    const int Eg = hidden_dim_ / world_;
+    const df8_kind act = fp8::policy().activation_kind;
+    const df8_stream st = fp8::stream();
+    auto params = norm.parameters();  // {gamma, beta}, replicated
+    const float* gamma = params.size() > 0 ? params[0]->data() + size_t(rank_) * Eg : nullptr;
+    const float* beta = params.size() > 1 ? params[1]->data() + size_t(rank_) * Eg : nullptr;
+    // statistics of the row pieces: this rank's [M][2] goes straight into its slot of the gathered array
+    float* stats_all = sym_stats_ + size_t(which) * size_t(world_) * size_t(work_rows_) * 2;
+    const size_t slot_bytes = size_t(M) * 2 * sizeof(float);
+    float* mine = stats_all + size_t(rank_) * size_t(M) * 2;
+    utils::CHECK_DF8(df8_layernorm_shard_stats_f32(x, M, Eg, mine, st));
+    utils::CHECK_DF8(df8_comm_allgather_symm(comm_, stats_all, 0, slot_bytes, st));
+    float* am = fp8::amax_slot(amax_.data());
+    utils::CHECK_DF8(df8_layernorm_shard_amax_f32(x, M, Eg, stats_all, world_, gamma, beta, norm.epsilon(),
+                                                  row_stats_.data(), am, st));
+    all_max(am);
+    utils::CHECK_DF8(df8_layernorm_shard_quantize_f32(x, M, Eg, row_stats_.data(), gamma, beta, act, am,
+                                                      sym_ln_ + size_t(rank_) * size_t(M) * Eg, ln_scale_.data(), st));
+    utils::CHECK_DF8(df8_comm_allgather_symm(comm_, sym_ln_, 0, size_t(M) * Eg, st));
+}
+
+template <typename T>
+void Gpt2ColumnSharded<T>::quantize_gather_sharded(const float* x, int M, float* amax, uint8_t* sym, float* scale) {
+    const int Eg = hidden_dim_ / world_;
+    const df8_kind act = fp8::policy().activation_kind;
+    const df8_stream st = fp8::stream();
+    all_max(amax);
+    utils::CHECK_DF8(df8_quantize_f32(x, size_t(M) * Eg, act, amax, sym + size_t(rank_) * size_t(M) * Eg, scale, st));
+    utils::CHECK_DF8(df8_comm_allgather_symm(comm_, sym, 0, size_t(M) * Eg, st));
+}
+
+template <typename T>
+void Gpt2ColumnSharded<T>::block_forward_sharded(Block& b, int B, int T_len) {
+    const int M = B * T_len, E = hidden_dim_, F = ffn_dim_, g = world_;
+    const int Eg = E / g, Fg = F / g, Hg = num_heads_ / g, D = E / num_heads_;
+    const df8_kind act = fp8::policy().activation_kind;
+    const df8_stream st = fp8::stream();
+    fp8::PassScope amax_slots;
+    float* x = x_shard_.data();
+    float* x1 = x1_shard_.data();
 
     // ---- x1 = x + out_proj(attention(QKV(LN1(x)))) ----
-    b.norm1.forward_quantized(x, M, act, ln_q_);
+    layernorm_quantize_sharded(b.norm1, x, M, 0);
     {   // QKV of this rank's heads: max|out| over all ranks, then the codes
         const fp8::Quantized& w = b.qkv.quantized_weights();
         float* am = fp8::amax_slot(amax_.data());
-        utils::CHECK_DF8(df8_gemm_fp8_tn_amax(ln_q_.codes.data(), ln_q_.kind, ln_q_.scale.data(), w.codes.data(), w.kind,
-                                              w.scale.data(), b.qkv.bias()->data(), M, 3 * Eg, E, 0, am, st));
+        utils::CHECK_DF8(df8_gemm_fp8_tn_amax_ex(sym_ln_, act, ln_scale_.data(), g, w.codes.data(), w.kind,
+                                                 w.scale.data(), b.qkv.bias()->data(), M, 3 * Eg, E, 0, am, st));
         all_max(am);
         qkvq_.kind = act;
-        utils::CHECK_DF8(df8_gemm_fp8_tn_codes(ln_q_.codes.data(), ln_q_.kind, ln_q_.scale.data(), w.codes.data(), w.kind,
-                                               w.scale.data(), b.qkv.bias()->data(), M, 3 * Eg, E, 0, act, am,
-                                               qkvq_.codes.data(), qkvq_.scale.data(), st));
+        utils::CHECK_DF8(df8_gemm_fp8_tn_codes_ex(sym_ln_, act, ln_scale_.data(), g, w.codes.data(), w.kind,
+                                                  w.scale.data(), b.qkv.bias()->data(), M, 3 * Eg, E, 0, act, am,
+                                                  qkvq_.codes.data(), qkvq_.scale.data(), st));
     }
     {   // attention of the local heads; its output is quantised with the maximum over all heads
         float* am = fp8::amax_slot(amax_.data());
         utils::CHECK_DF8(df8_attention_fp8(qkvq_.codes.data(), qkvq_.kind, qkvq_.scale.data(), B, T_len, Hg, D,
                                            causal_ ? DF8_MASK_CAUSAL : DF8_MASK_NONE, nullptr, 0, attn_f32_.data(), am,
                                            st));
-        all_max(am);
-        fp8::quantize_with_amax(attn_f32_.data(), size_t(M) * Eg, act, am, attnq_local_);
-        gather_columns(attnq_local_.codes.data(), M, Eg, attnq_.codes.data());
-        attnq_.kind = act;
+        quantize_gather_sharded(attn_f32_.data(), M, am, sym_attn_, attn_scale_.data());
     }
-    b.out.forward_codes(attnq_.codes.data(), attnq_.kind, attnq_local_.scale.data(), M, 0, nullptr, y_local_.data(),
-                        nullptr);
-    gather_columns(y_local_.data(), M, Eg * int(sizeof(float)), y_full_.data());
-    add_f32(x, y_full_.data(), x1_.data(), size_t(M) * E);
+    b.out.forward_codes(sym_attn_, act, attn_scale_.data(), M, DF8_EPI_RESIDUAL, x, x1, nullptr, Eg, g);
 
     // ---- x = x1 + FC2(act(FC1(LN2(x1)))) ----
-    b.norm2.forward_quantized(x1_.data(), M, act, ln_q_);
+    layernorm_quantize_sharded(b.norm2, x1, M, 1);
     {
         const fp8::Quantized& w = b.fc1.quantized_weights();
         float* am = fp8::amax_slot(amax_.data());
-        hidden_q_.kind = act;
-        if (world_ > 1) {
-            utils::CHECK_DF8(df8_fc_fp8_column_sharded(comm_, ln_q_.codes.data(), ln_q_.kind, ln_q_.scale.data(),
-                                                       w.codes.data(), w.kind, w.scale.data(), b.fc1.bias()->data(), M,
-                                                       F, E, mlp_gelu_ ? DF8_EPI_GELU : 0, act, slice_.data(),
-                                                       gathered_.data(), hidden_q_.codes.data(),
-                                                       hidden_q_.scale.data(), am, st));
-        } else {
-            utils::CHECK_DF8(df8_gemm_fp8_tn_q(ln_q_.codes.data(), ln_q_.kind, ln_q_.scale.data(), w.codes.data(), w.kind,
-                                               w.scale.data(), b.fc1.bias()->data(), M, F, E,
-                                               mlp_gelu_ ? DF8_EPI_GELU : 0, act, hidden_q_.codes.data(),
-                                               hidden_q_.scale.data(), am, st));
-        }
+        const int flags = mlp_gelu_ ? DF8_EPI_GELU : 0;
+        utils::CHECK_DF8(df8_gemm_fp8_tn_amax_ex(sym_ln_, act, ln_scale_.data(), g, w.codes.data(), w.kind,
+                                                 w.scale.data(), b.fc1.bias()->data(), M, Fg, E, flags, am, st));
+        all_max(am);
+        // the codes go straight into this rank's slab of the buffer the peers gather into
+        utils::CHECK_DF8(df8_gemm_fp8_tn_codes_ex(sym_ln_, act, ln_scale_.data(), g, w.codes.data(), w.kind,
+                                                  w.scale.data(), b.fc1.bias()->data(), M, Fg, E, flags, act, am,
+                                                  sym_hidden_ + size_t(rank_) * size_t(M) * Fg, hidden_scale_.data(),
+                                                  st));
+        utils::CHECK_DF8(df8_comm_allgather_symm(comm_, sym_hidden_, 0, size_t(M) * Fg, st));
     }
-    b.fc2.forward_codes(hidden_q_.codes.data(), hidden_q_.kind, hidden_q_.scale.data(), M, 0, nullptr, y_local_.data(),
-                        nullptr);
-    gather_columns(y_local_.data(), M, Eg * int(sizeof(float)), y_full_.data());
-    add_f32(x1_.data(), y_full_.data(), x, size_t(M) * E);
+    b.fc2.forward_codes(sym_hidden_, act, hidden_scale_.data(), M, DF8_EPI_RESIDUAL, x1, x, nullptr, Eg, g);
+}
+
+// Embedding (replicated table) -> this rank's columns -> the blocks.  The hidden states stay in x_shard_.
+template <typename T>
+void Gpt2ColumnSharded<T>::run_blocks_sharded(const tensor<int>& ids, bool check_ids, int* M_out) {
+    const auto& s = ids.shape();
+    const int B = s[0], T_len = s[1], M = B * T_len, E = hidden_dim_, Eg = E / world_;
+    ensure_work_space(M);
+    {
+        tensor<T> full = token_embedding_->forward_with_positions(ids, positional_encoding_->table().data(), check_ids);
+        utils::CHECK_CUDA_EX(cudaMemcpy2DAsync(x_shard_.data(), size_t(Eg) * sizeof(float),
+                                               full.data() + size_t(rank_) * Eg, size_t(E) * sizeof(float),
+                                               size_t(Eg) * sizeof(float), size_t(M), cudaMemcpyDeviceToDevice,
+                                               Cuda::stream()));
+    }
+    for (auto& b : blocks_) block_forward_sharded(*b, B, T_len);
+    *M_out = M;
 }
 
 template <typename T>
@@ -194,21 +251,88 @@ tensor<T> Gpt2ColumnSharded<T>::forward_hidden(const tensor<int>& ids, bool chec
     if (T_len > positional_encoding_->max_seq_len())
         throw std::runtime_error("Input sequence length exceeds maximum allowed length");
     fp8::PassScope amax_slots;
-    tensor<T> x = token_embedding_->forward_with_positions(ids, positional_encoding_->table().data(), check_ids);
-    for (auto& b : blocks_) block_forward(*b, x.data(), B, T_len);
+    if (world_ == 1) {
+        tensor<T> x = token_embedding_->forward_with_positions(ids, positional_encoding_->table().data(), check_ids);
+        for (auto& b : blocks_) block_forward_single(*b, x.data(), B, T_len);
+        return x;
+    }
+    int M = 0;
+    run_blocks_sharded(ids, check_ids, &M);
+    // gather the fp32 column slices (NCCL; not on the path of forward_logits_shard) and put them side by side
+    const size_t E = size_t(hidden_dim_), Eg = E / size_t(world_);
+    tensor<uint8_t> gathered({int(size_t(M) * E * sizeof(float))});
+    utils::CHECK_DF8(df8_comm_allgather_u8(comm_, reinterpret_cast<const uint8_t*>(x_shard_.data()), gathered.data(),
+                                           size_t(M) * Eg * sizeof(float), fp8::stream()));
+    tensor<T> x({B, T_len, hidden_dim_});
+    utils::CHECK_DF8(df8_interleave_gathered_u8(gathered.data(), M, int(Eg * sizeof(float)), world_,
+                                                reinterpret_cast<uint8_t*>(x.data()), fp8::stream()));
     return x;
+}
+
+// logits [M, pitch] of this rank's vocabulary rows from the hidden states of the last forward
+template <typename T>
+void Gpt2ColumnSharded<T>::head(int M, float* logits, int pitch) {
+    const df8_kind act = fp8::policy().activation_kind;
+    if (world_ == 1) throw std::logic_error("Gpt2ColumnSharded::head: sharded path only");
+    float* am = fp8::amax_slot(amax_.data());
+    const int Eg = hidden_dim_ / world_;
+    utils::CHECK_DF8(df8_amax_f32(x_shard_.data(), size_t(M) * Eg, am, fp8::stream()));
+    quantize_gather_sharded(x_shard_.data(), M, am, sym_ln_, ln_scale_.data());
+    final_fc_->forward_codes(sym_ln_, act, ln_scale_.data(), M, 0, nullptr, logits, nullptr, pitch, world_);
+}
+
+template <typename T>
+tensor<T> Gpt2ColumnSharded<T>::forward_logits_shard_pitched(const tensor<int>& ids, bool check_ids) {
+    const auto& s = ids.shape();
+    if (s.size() != 2) throw std::runtime_error("Gpt2ColumnSharded expects token ids shaped [B, T]");
+    if (s[1] > positional_encoding_->max_seq_len())
+        throw std::runtime_error("Input sequence length exceeds maximum allowed length");
+    fp8::PassScope amax_slots;
+    const int pitch = logits_pitch();
+    if (world_ == 1) {
+        tensor<T> x = forward_hidden(ids, check_ids);
+        const int M = int(x.numel() / size_t(hidden_dim_));
+        fp8::quantize(x.data(), x.numel(), fp8::policy().activation_kind, head_q_);
+        tensor<T> logits({M, pitch});
+        final_fc_->forward_codes(head_q_.codes.data(), head_q_.kind, head_q_.scale.data(), M, 0, nullptr, logits.data(),
+                                 nullptr, pitch);
+        return logits;
+    }
+    int M = 0;
+    run_blocks_sharded(ids, check_ids, &M);
+    tensor<T> logits({M, pitch});
+    head(M, logits.data(), pitch);
+    return logits;
 }
 
 template <typename T>
 tensor<T> Gpt2ColumnSharded<T>::forward_logits_shard(const tensor<int>& ids, bool check_ids) {
+    const auto& s = ids.shape();
+    if (s.size() != 2) throw std::runtime_error("Gpt2ColumnSharded expects token ids shaped [B, T]");
+    if (s[1] > positional_encoding_->max_seq_len())
+        throw std::runtime_error("Input sequence length exceeds maximum allowed length");
     fp8::PassScope amax_slots;
-    tensor<T> x = forward_hidden(ids, check_ids);
-    const int M = int(x.numel() / size_t(hidden_dim_));
-    fp8::quantize(x.data(), x.numel(), fp8::policy().activation_kind, head_q_);
+    if (world_ == 1) {
+        tensor<T> x = forward_hidden(ids, check_ids);
+        const int M = int(x.numel() / size_t(hidden_dim_));
+        fp8::quantize(x.data(), x.numel(), fp8::policy().activation_kind, head_q_);
+        tensor<T> logits({M, vocab_rows_});
+        final_fc_->forward_codes(head_q_.codes.data(), head_q_.kind, head_q_.scale.data(), M, 0, nullptr, logits.data(),
+                                 nullptr);
+        return logits;
+    }
+    int M = 0;
+    run_blocks_sharded(ids, check_ids, &M);
     tensor<T> logits({M, vocab_rows_});
-    final_fc_->forward_codes(head_q_.codes.data(), head_q_.kind, head_q_.scale.data(), M, 0, nullptr, logits.data(),
-                             nullptr);
+    head(M, logits.data(), vocab_rows_);
     return logits;
+}
+
+template <typename T>
+unsigned long long Gpt2ColumnSharded<T>::bytes_pushed() const {
+    unsigned long long b = 0;
+    if (comm_ && world_ > 1) utils::CHECK_DF8(df8_comm_bytes_pushed(comm_, &b));
+    return b;
 }
 
 template class Gpt2ColumnSharded<float>;

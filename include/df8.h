@@ -207,6 +207,27 @@ df8_status df8_layernorm_quantize_f32_noalloc(const float* x, int rows, int cols
                                               uint8_t* codes_out, float* scale_out, float* amax_out,
                                               df8_stream stream);
 
+/* LayerNorm + per-tensor quantisation of a tensor whose COLUMNS are split across ranks (the column-sharded forward
+ * keeps the fp32 residual stream sharded).  Same formula as df8_layernorm_f32 (layer_norm_layer.cu:40-62); the
+ * ranks exchange two floats per row instead of the fp32 rows:
+ *   _stats     partial_out[rows][2] = {mean, sum of squared deviations} of this rank's [rows, cols_shard] piece
+ *   (caller: all-gather the partial arrays of all ranks into partial_all [world][rows][2])
+ *   _amax      combines them in rank order, writes row_stats_out[rows][2] = {mean, rstd} of the whole rows and
+ *              reduces max|y| over this rank's columns into amax_out (cleared by the call)
+ *   (caller: maximum of amax_out over the ranks)
+ *   _quantize  codes_shard_out [rows, cols_shard] = fp8(y * q), q from amax_in[0]; writes scale_out = {q, dq}
+ * gamma_shard / beta_shard are this rank's slices ([cols_shard]) or NULL.  cols_shard % 4 == 0.  Sums are taken
+ * in another order than a single GPU's row sum: results agree with df8_layernorm_quantize_f32 to fp32 rounding. */
+df8_status df8_layernorm_shard_stats_f32(const float* x_shard, int rows, int cols_shard, float* partial_out,
+                                         df8_stream stream);
+df8_status df8_layernorm_shard_amax_f32(const float* x_shard, int rows, int cols_shard, const float* partial_all,
+                                        int world, const float* gamma_shard, const float* beta_shard, float eps,
+                                        float* row_stats_out, float* amax_out, df8_stream stream);
+df8_status df8_layernorm_shard_quantize_f32(const float* x_shard, int rows, int cols_shard, const float* row_stats,
+                                            const float* gamma_shard, const float* beta_shard, df8_kind kind,
+                                            const float* amax_in, uint8_t* codes_shard_out, float* scale_out,
+                                            df8_stream stream);
+
 /* ---- token embedding + positional encoding -----------------------------------------------
  * Replaces embedding_forward_kernel (dnn/tokens/token_embedding.cu:31-45, launched at :146-154) and
  * add_positional_encodings_kernel (dnn/tokens/positional_encoding.cu:31-48, launched at :94-104):
@@ -276,6 +297,25 @@ df8_status df8_comm_allgather_u8(df8_comm* c, const uint8_t* send_d, uint8_t* re
                                  df8_stream stream);
 /* in place: buf_d[i] = max over ranks (the per-tensor amax of a tensor whose columns are sharded) */
 df8_status df8_comm_allreduce_max_f32(df8_comm* c, float* buf_d, size_t count, df8_stream stream);
+
+/* Exchanges of the column-sharded forward without NCCL kernels on the data path (no upstream counterpart).  Buffers
+ * from df8_comm_symm_alloc exist on every rank and are mapped into every other rank (cudaMalloc + CUDA IPC; the
+ * call is collective, allocates and synchronises; buffers live until df8_comm_destroy).  Where the mapping is not
+ * possible (or with DF8_COMM_P2P=0 in the environment) the calls below fall back to NCCL on the same buffers.
+ *   df8_comm_allgather_symm   every rank's slice — bytes_per_rank bytes at local_d + offset + rank*bytes_per_rank of
+ *                             ITS copy, produced by work already on `stream` — is copied by the copy engines into
+ *                             the same position of every peer's copy over NVLink; later work on `stream` sees all
+ *                             world slices.  The wait for the peers is a bounded poll (2 s, then status word).
+ *   df8_comm_allreduce_max_p2p  value_d[0] <- max over ranks, one small kernel per rank (the value travels inside
+ *                             the flag word the peers poll).
+ * Every rank must issue the same sequence of these calls.  Neither allocates or synchronises the host. */
+df8_status df8_comm_symm_alloc(df8_comm* c, size_t bytes, void** local_d_h);
+df8_status df8_comm_p2p_enabled(df8_comm* c, int* enabled_h);
+df8_status df8_comm_allgather_symm(df8_comm* c, void* local_d, size_t offset, size_t bytes_per_rank,
+                                   df8_stream stream);
+df8_status df8_comm_allreduce_max_p2p(df8_comm* c, float* value_d, df8_stream stream);
+/* bytes this rank has sent to its peers through df8_comm_allgather_symm */
+df8_status df8_comm_bytes_pushed(df8_comm* c, unsigned long long* bytes_h);
 
 /* Column-sharded fully-connected layer (no upstream counterpart: upstream's layer always holds the full
  * [out,in] weight, dnn/layers/fully_connected_layer.cu:112-116).  Every rank passes the full quantised input

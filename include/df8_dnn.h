@@ -100,6 +100,13 @@ int dnn_gpt2cs_prepare(dnn_gpt2cs* m);
 int dnn_gpt2cs_forward_logits_shard(dnn_gpt2cs* m, const int32_t* ids_d, int B, int T, int check_ids,
                                     float** logits_d);
 int dnn_gpt2cs_forward_logits_shard_host(dnn_gpt2cs* m, const int32_t* ids_h, int B, int T, float** logits_d);
+/* the same in a row-pitched buffer [B*T, *pitch_h] (pitch = vocab_rows rounded up to a multiple of 32 floats) */
+int dnn_gpt2cs_forward_logits_shard_pitched(dnn_gpt2cs* m, const int32_t* ids, int ids_on_host, int B, int T,
+                                            int check_ids, float** logits_d, int* pitch_h);
+/* collective: hidden states after the last block, gathered onto every rank, [B,T,E] fp32 */
+int dnn_gpt2cs_forward_hidden(dnn_gpt2cs* m, const int32_t* ids_d, int B, int T, float** hidden_d);
+/* bytes this rank has pushed to its peers' buffers since the model was made (0 for a single rank) */
+unsigned long long dnn_gpt2cs_bytes_pushed(dnn_gpt2cs* m);
 
 /* ---- single layers through their public forward(), host buffers in and out ---- */
 int dnn_fc_forward(int in_features, int out_features, const float* w_h, const float* b_h, const float* x_h, int M,

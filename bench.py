@@ -1053,7 +1053,7 @@ def secondary_forward(torch, df8, dev, rank, world, comm, make, timed, barrier, 
                                ("none (single rank)" if world == 1 else "NCCL fallback"),
                                "nvlink_gbs_if_fully_exposed": round(pushed / (ms / steps) / 1e6, 1)}
         if getattr(wl.model, "_streaming", False):
-            rec["streaming"] = streaming_report(torch, wl, steps + warmup, ms / steps, timed, max_over_ranks)
+            rec["streaming"] = streaming_report(torch, wl, steps + warmup, ms / steps, timed, max_over_ranks, barrier)
         rec["device_wait_status"] = list(df8.status_word())
         return rec
     except Exception as e:
@@ -1067,7 +1067,7 @@ def secondary_forward(torch, df8, dev, rank, world, comm, make, timed, barrier, 
         barrier()
 
 
-def streaming_report(torch, wl, passes, ms_streamed, timed, max_over_ranks):
+def streaming_report(torch, wl, passes, ms_streamed, timed, max_over_ranks, barrier):
     """Host->device and NVLink bytes per rank and forward of the layer streamer, the rate of the uploads when they
     run alone, and how much of that upload time a forward hides under its compute:
     overlap = (upload alone - (streamed forward - forward with every layer resident)) / upload alone."""
@@ -1077,6 +1077,7 @@ def streaming_report(torch, wl, passes, ms_streamed, timed, max_over_ranks):
         rep["h2d_bytes_per_forward_per_rank"] = h2d // max(1, passes)
         rep["gathered_bytes_per_forward_per_rank"] = gathered // max(1, passes)
         h0, g0 = wl.model.streaming_traffic()
+        barrier()  # the ranks enter together: a sharded upload waits for its slowest peer
         up_ms = max_over_ranks(wl.model.time_uploads())[0]
         h1, g1 = wl.model.streaming_traffic()
         wl.model.resize_streaming_slots(wl.c["layers"])  # every layer resident after one pass

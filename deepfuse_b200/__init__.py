@@ -256,6 +256,10 @@ _DNN_SIGNATURES = {
     "dnn_selftest_context": [_vp, _i],
     "dnn_selftest_errors": [_vp, _i],
     "dnn_selftest_bounded_wait": [_vp, _i],
+    "dnn_selftest_tokenizer": [C.c_char_p, _vp, _i],
+    "dnn_tokenizer_encode": [C.c_char_p, C.c_char_p, C.c_char_p, _i, _vp, _i],
+    "dnn_tokenizer_decode": [C.c_char_p, C.c_char_p, _vp, _i, _i, _vp, _i],
+    "dnn_tokenizer_save": [C.c_char_p, C.c_char_p],
     "dnn_set_host_init": [_i],
     "dnn_gpt2cs_destroy": [_vp],
     "dnn_gpt2cs_set_options": [_vp, _i, _i],

@@ -63,7 +63,10 @@ def _compile(src: Path, obj: Path, extra: list[str], force: bool, hdr_mtime: flo
 
 def _link(objs: list[Path], out: Path, extra: list[str]) -> None:
     out.parent.mkdir(parents=True, exist_ok=True)
-    _run([NVCC, *ARCH_FLAGS, "-shared", "-o", str(out), *map(str, objs), *extra])
+    # link beside the target and rename: a reader never sees a half-written library
+    tmp = out.with_name(out.name + ".linking")
+    _run([NVCC, *ARCH_FLAGS, "-shared", "-o", str(tmp), *map(str, objs), *extra])
+    os.replace(tmp, out)
 
 
 def _build_lib(name: str, sources: list[Path], extra_cc: list[str], extra_ld: list[str], force: bool) -> Path:

@@ -17,8 +17,12 @@
 #include "dnn/layers/transformer_block.cuh"
 #include "dnn/models/gpt2.cuh"
 #include "dnn/models/gpt2_column_sharded.cuh"
+#include "dnn/tokens/bpe_tokenizer.cuh"
 #include "dnn/tokens/positional_encoding.cuh"
 #include "dnn/tokens/token_embedding.cuh"
+#include "dnn/tokens/vocab_loader.cuh"
+
+#include <fstream>
 
 namespace {
 
@@ -568,5 +572,59 @@ extern "C" int dnn_gpt2cs_forward_logits_shard_host(dnn_gpt2cs* m, const int32_t
         m->last.reset();
         m->last = std::make_unique<dnn::tensor<float>>(m->model->forward_logits_shard(*m->ids, false));
         *logits_d = m->last->data();
+    });
+}
+
+// ---- the text front end (host-only) ---------------------------------------------------------------------
+
+namespace {
+// vocabulary from a JSON file (merges.txt beside it is picked up), or from a binary state stream when
+// `state_path` is given instead
+std::shared_ptr<dnn::BpeTokenizer> make_tokenizer(const char* vocab_json_path, const char* state_path) {
+    auto loader = std::make_shared<dnn::VocabLoader>();
+    auto tok = std::make_shared<dnn::BpeTokenizer>(loader);
+    if (state_path && state_path[0]) {
+        std::ifstream in(state_path, std::ios::binary);
+        if (!in) throw std::runtime_error(std::string("cannot open tokenizer state ") + state_path);
+        tok->load(in);
+    } else {
+        loader->load_from_file(vocab_json_path);
+    }
+    return tok;
+}
+}  // namespace
+
+extern "C" int dnn_tokenizer_encode(const char* vocab_json_path, const char* state_path, const char* text, int add_special,
+                                    int* ids_out, int cap) {
+    int n = -1;
+    guarded([&] {
+        auto tok = make_tokenizer(vocab_json_path, state_path);
+        std::vector<int> ids = tok->encode(text, add_special != 0);
+        for (int i = 0; i < int(ids.size()) && i < cap; ++i) ids_out[i] = ids[size_t(i)];
+        n = int(ids.size());
+    });
+    return n;
+}
+
+extern "C" int dnn_tokenizer_decode(const char* vocab_json_path, const char* state_path, const int* ids, int n,
+                                    int skip_special, char* out, int cap) {
+    int len = -1;
+    guarded([&] {
+        auto tok = make_tokenizer(vocab_json_path, state_path);
+        std::string s = tok->decode(std::vector<int>(ids, ids + n), skip_special != 0);
+        if (int(s.size()) + 1 > cap) throw std::runtime_error("dnn_tokenizer_decode: output buffer too small");
+        std::memcpy(out, s.data(), s.size());
+        out[s.size()] = 0;
+        len = int(s.size());
+    });
+    return len;
+}
+
+extern "C" int dnn_tokenizer_save(const char* vocab_json_path, const char* out_path) {
+    return guarded([&] {
+        auto tok = make_tokenizer(vocab_json_path, nullptr);
+        std::ofstream out(out_path, std::ios::binary);
+        if (!out) throw std::runtime_error(std::string("cannot write ") + out_path);
+        tok->save(out);
     });
 }

@@ -7,6 +7,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <fstream>
 #include <functional>
 #include <sstream>
 #include <string>
@@ -21,7 +22,9 @@
 #include "dnn/layers/transformer_block.cuh"
 #include "dnn/models/gpt2.cuh"
 #include "dnn/tokens/positional_encoding.cuh"
+#include "dnn/tokens/bpe_tokenizer.cuh"
 #include "dnn/tokens/token_embedding.cuh"
+#include "dnn/tokens/vocab_loader.cuh"
 #include "df8_internal.cuh"
 #include "sm100_ptx.cuh"
 
@@ -456,6 +459,121 @@ extern "C" int dnn_selftest_bounded_wait(char* report_h, int cap) {
         CHECK(r, df8_status_word_read(&got_code, &count) == DF8_OK && got_code == 0 && count == 0);
     } catch (const std::exception& e) {
         df8_status_word_reset();
+        r.check(false, e.what(), __LINE__);
+    }
+    return r.finish(report_h, cap);
+}
+
+// The text front end (host-only code: runs without a GPU).  The cases are those of upstream's
+// tests/tokens/vocab_loader_test.cu:60-163 and tests/tokens/bpe_tokenizer_test.cu:83-190, on vocabulary and merge
+// files written into `dir`.
+extern "C" int dnn_selftest_tokenizer(const char* dir, char* report_h, int cap) {
+    Report r;
+    try {
+        using namespace dnn;
+        const std::string d = std::string(dir) + "/";
+        {   // vocabulary file of the loader cases: 7 tokens, 8 merge rules beside it
+            std::ofstream v(d + "vocab.json");
+            v << "{\n  \"<|endoftext|>\": 0,\n  \"<|unk|>\": 1,\n  \"<|pad|>\": 2,\n  \"hello\": 3,\n  \"world\": 4,\n"
+                 "  \"test\": 5,\n  \"token\": 6\n}\n";
+            std::ofstream m(d + "merges.txt");
+            m << "#version: 0.2\nh e\nhe l\nhel l\nhell o\nw o\nwo r\nwor l\nworl d\n";
+        }
+        {
+            VocabLoader fresh;
+            CHECK(r, fresh.size() == 0 && fresh.get_bpe_merges().empty());
+            CHECK(r, fresh.bytes_to_unicode().size() == 256 && fresh.unicode_to_bytes().size() == 256);
+            fresh.add_token("test_token");
+            CHECK(r, fresh.size() == 1 && fresh.token_to_id("test_token") == 0);
+            fresh.add_token("test_token");
+            CHECK(r, fresh.size() == 1);
+            fresh.add_token("far", 9);
+            CHECK(r, fresh.size() == 10 && fresh.id_to_token(9) == "far" && fresh.id_to_token(5).empty());
+        }
+        VocabLoader vocab;
+        vocab.load_from_file(d + "vocab.json");
+        CHECK(r, vocab.size() == 7);
+        CHECK(r, vocab.token_to_id("<|endoftext|>") == 0 && vocab.token_to_id("<|unk|>") == 1 && vocab.token_to_id("<|pad|>") == 2);
+        CHECK(r, vocab.token_to_id("hello") == 3 && vocab.token_to_id("world") == 4);
+        CHECK(r, vocab.token_to_id("test") == 5 && vocab.token_to_id("token") == 6);
+        CHECK(r, vocab.token_to_id("unknown") == vocab.get_unk_token_id());
+        CHECK(r, vocab.id_to_token(0) == "<|endoftext|>" && vocab.id_to_token(3) == "hello" && vocab.id_to_token(4) == "world");
+        CHECK(r, vocab.id_to_token(-1) == "<|endoftext|>" && vocab.id_to_token(100) == "<|endoftext|>");
+        CHECK(r, vocab.get_bos_token_id() == 0 && vocab.get_eos_token_id() == 0 && vocab.get_unk_token_id() == 1 && vocab.get_pad_token_id() == 2);
+        const auto& merges = vocab.get_bpe_merges();
+        CHECK(r, merges.size() == 8);
+        CHECK(r, merges.size() == 8 && merges[0].first == "h e" && merges[0].second == "he");
+        CHECK(r, merges.size() == 8 && merges[3].first == "hell o" && merges[3].second == "hello");
+        CHECK(r, merges.size() == 8 && merges[7].first == "worl d" && merges[7].second == "world");
+        {   // binary round trip of the loader's state
+            std::stringstream blob;
+            vocab.save(blob);
+            VocabLoader back;
+            back.load(blob);
+            CHECK(r, back.size() == 7 && back.token_to_id("token") == 6 && back.id_to_token(5) == "test");
+            CHECK(r, back.get_bpe_merges() == vocab.get_bpe_merges());
+            CHECK(r, back.bytes_to_unicode() == vocab.bytes_to_unicode() && back.unicode_to_bytes() == vocab.unicode_to_bytes());
+            std::stringstream cut(blob.str().substr(0, 40));
+            CHECK(r, throws<std::runtime_error>([&] { VocabLoader v2; v2.load(cut); }));
+        }
+        {
+            VocabLoader copy;
+            copy.load_from_file(d + "vocab.json");
+            copy.clear();
+            CHECK(r, copy.size() == 0 && copy.get_bpe_merges().empty());
+            CHECK(r, throws<std::runtime_error>([&] { copy.load_from_file(d + "nonexistent_file.json"); }));
+            std::ofstream(d + "invalid.json") << "invalid json content";
+            CHECK(r, throws<std::runtime_error>([&] { copy.load_from_file(d + "invalid.json"); }));
+            // escapes and values that are not numbers
+            std::ofstream(d + "escapes.json") << "{\"a\\\"b\": 3, \"\\u0120the\": 4, \"skip\": [1, {\"x\": 2}], \"<|unk|>\": 1}";
+            copy.load_from_file(d + "escapes.json");
+            CHECK(r, copy.token_to_id("a\"b") == 3 && copy.token_to_id("\xC4\xA0the") == 4 && copy.token_to_id("skip") == 1);
+        }
+        {   // the tokenizer cases: a vocabulary with single letters, pairs and two whole words (no merges.txt beside it)
+            std::ofstream v(d + "tok_vocab.json");
+            v << "{\"<|endoftext|>\": 0, \"<|unk|>\": 1, \"<|pad|>\": 2, \"h\": 3, \"e\": 4, \"l\": 5, \"o\": 6, \"w\": 7, "
+                 "\"r\": 8, \"d\": 9, \"he\": 10, \"ll\": 11, \"lo\": 12, \"wo\": 13, \"rl\": 14, \"ld\": 15, "
+                 "\"hello\": 16, \"world\": 17}";
+        }
+        auto tv = std::make_shared<VocabLoader>();
+        tv->load_from_file(d + "tok_vocab.json");
+        CHECK(r, throws<std::invalid_argument>([] { BpeTokenizer bad(nullptr); }));
+        BpeTokenizer tok(tv);
+        using Ids = std::vector<int>;
+        CHECK(r, tok.encode("hello world") == Ids({16, 17}));
+        CHECK(r, tok.encode("hello world", true) == Ids({0, 16, 17, 0}));
+        CHECK(r, tok.decode({16, 17}) == "helloworld");
+        CHECK(r, tok.decode({0, 16, 17, 0}, true) == "helloworld");
+        CHECK(r, tok.encode("xyz") == Ids({1, 1, 1}));
+        CHECK(r, tok.encode("  hello  world  ") == Ids({16, 17}));
+        CHECK(r, tok.decode(tok.encode("  hello  world  ")) == "helloworld");
+        CHECK(r, tok.get_bos_token_id() == 0 && tok.get_eos_token_id() == 0 && tok.get_unk_token_id() == 1 && tok.get_pad_token_id() == 2);
+        CHECK(r, tok.vocab_size() == tv->size() && tok.vocab_size() == 18);
+        CHECK(r, tok.unicode_to_text(tok.text_to_unicode("hello")) == "hello");
+        CHECK(r, tok.encode("helo") == Ids({3, 4, 5, 6}));  // spelt out: the merge rules are not applied by encode
+        CHECK(r, tok.encode("hello\x01world") == Ids({16, 17}));
+        CHECK(r, tok.encode("hello\tworld\nhello") == Ids({16, 17, 16}));
+        CHECK(r, tok.encode("") == Ids() && tok.encode("   ", true) == Ids({0, 0}));
+        CHECK(r, tok.encode("caf\xC3\xA9 hello") == Ids({1, 1, 1, 16}));  // bytes above 0x7E separate words
+        {   // every byte survives the two byte tables
+            std::string all;
+            for (int b = 1; b < 256; ++b) all += char(b);
+            CHECK(r, tok.unicode_to_text(tok.text_to_unicode(all)) == all);
+        }
+        {   // save / load of the tokenizer state through the Tokenizer interface
+            std::stringstream blob;
+            tok.save(blob);
+            BpeTokenizer other(std::make_shared<VocabLoader>());
+            other.load(blob);
+            CHECK(r, other.encode("hello xyz world", true) == tok.encode("hello xyz world", true));
+        }
+        {   // the merge rules themselves (an addition): applied in file order until none matches
+            BpeTokenizer with_merges(std::make_shared<VocabLoader>(vocab));
+            CHECK(r, with_merges.merge_word("hello") == std::vector<std::string>({"hello"}));
+            CHECK(r, with_merges.merge_word("helo") == std::vector<std::string>({"hel", "o"}));
+            CHECK(r, with_merges.merge_word("x") == std::vector<std::string>({"x"}));
+        }
+    } catch (const std::exception& e) {
         r.check(false, e.what(), __LINE__);
     }
     return r.finish(report_h, cap);

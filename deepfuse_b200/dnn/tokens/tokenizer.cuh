@@ -1,6 +1,5 @@
 // Tokenizer: the abstract text <-> token-id interface the language models hold (upstream
-// dnn/tokens/tokenizer.cuh).  Only the interface is part of this build; upstream's BPE implementation
-// and vocabulary loader are CPU-side text processing outside the fp8 forward path.
+// dnn/tokens/tokenizer.cuh).  The implementation that ships with it is BpeTokenizer (bpe_tokenizer.cuh).
 #pragma once
 
 #include <iostream>

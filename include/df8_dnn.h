@@ -123,6 +123,15 @@ int dnn_block_forward(int B, int T, int E, int H, int F, const float* const* par
 int dnn_embedding_forward(int V, int E, int max_len, const float* table_h, const float* bias_h, const int32_t* ids_h,
                           int B, int T, int add_positions, float* y_h);
 
+/* ---- the text front end: dnn::BpeTokenizer over a dnn::VocabLoader (host-only).  The vocabulary comes from a JSON
+ * file (a merges.txt beside it is picked up) or, when state_path_h is a non-empty string, from a binary state stream
+ * as Tokenizer::save writes it.  encode returns the number of ids (-1 on error), decode the length of the text. ---- */
+int dnn_tokenizer_encode(const char* vocab_json_path_h, const char* state_path_h, const char* text_h, int add_special,
+                         int* ids_out_h, int cap);
+int dnn_tokenizer_decode(const char* vocab_json_path_h, const char* state_path_h, const int* ids_h, int n, int skip_special,
+                         char* out_h, int cap);
+int dnn_tokenizer_save(const char* vocab_json_path_h, const char* out_path_h);
+
 /* ---- self tests written in C++ against the class API (tensor, Cuda/StreamGuard, error behaviour);
  * return the number of failed checks and write a report to report_h. ---- */
 int dnn_selftest_tensor(char* report_h, int cap);
@@ -131,6 +140,9 @@ int dnn_selftest_errors(char* report_h, int cap);
 /* makes a bounded device-side wait run out (a 1 ms limit on a barrier nobody arrives at; nothing faults or hangs)
  * and follows the failure to the caller: status word, DF8_ERR_TIMEOUT, std::runtime_error, reset, normal work */
 int dnn_selftest_bounded_wait(char* report_h, int cap);
+/* the text front end (dnn::VocabLoader, dnn::BpeTokenizer; host-only, needs no GPU): upstream's own test cases on
+ * vocabulary files written into the directory dir_h */
+int dnn_selftest_tokenizer(const char* dir_h, char* report_h, int cap);
 
 #ifdef __cplusplus
 }

@@ -105,3 +105,58 @@ extern "C" int ref_embedding_forward(int V, int E, int max_len, const float* tab
         x.download(y);
     });
 }
+
+// ---- files written by upstream's own save() code (for the import tests) ---------------------------------
+
+#include <fstream>
+
+extern "C" int ref_tensor_save_f32(const char* path, int ndim, const int* shape, const float* data) {
+    return guarded([&] {
+        ensure_ctx();
+        dnn::tensor<float> t(std::vector<int>(shape, shape + ndim));
+        t.upload(data);
+        std::ofstream out(path, std::ios::binary);
+        t.save(out);
+    });
+}
+
+extern "C" int ref_fc_save(const char* path, int in_f, int out_f, const float* w, const float* b) {
+    return guarded([&] {
+        ensure_ctx();
+        dnn::FullyConnectedLayer<float> layer(in_f, out_f, false);
+        layer.weights()->upload(w);
+        layer.bias()->upload(b);
+        std::ofstream out(path, std::ios::binary);
+        layer.save(out);
+    });
+}
+
+extern "C" int ref_layernorm_save(const char* path, int n, const float* gamma, const float* beta) {
+    return guarded([&] {
+        ensure_ctx();
+        dnn::LayerNormLayer<float> layer(n, 1e-5f, true, false);
+        auto p = layer.parameters();
+        p[0]->upload(gamma);
+        p[1]->upload(beta);
+        std::ofstream out(path, std::ios::binary);
+        layer.save(out);
+    });
+}
+
+extern "C" int ref_embedding_save(const char* path, int V, int E, int max_len, const float* table, const float* bias) {
+    return guarded([&] {
+        ensure_ctx();
+        dnn::TokenEmbedding<float> emb(V, E, max_len, false);
+        emb.weights()->upload(table);
+        emb.bias()->upload(bias);
+        std::ofstream out(path, std::ios::binary);
+        emb.save(out);
+    });
+}
+
+// Upstream's TransformerBlock, Gpt2 and tokenizer are not wrapped: every translation unit that includes
+// dnn/tokens/bpe_tokenizer.cuh (gpt2.cuh does) carries the class-static `control_chars_regex`
+// (bpe_tokenizer.cuh:56, "[\x00-\x1f\x7f-\x9f]"), whose construction throws std::regex_error under libstdc++ (with
+// signed char the range \x7f-\x9f runs backwards) during static initialisation, i.e. a library that contains it
+// aborts the process that loads it.  Their on-disk layouts are taken from the source instead
+// (transformer_block.cuh:37-56, models/gpt2.cu:144-166).

@@ -44,6 +44,9 @@ _SIGNATURES = {
     "df8_gemm_fp8_tn_ex": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp],
     "df8_gemm_fp8_tn_amax_ex": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "df8_gemm_fp8_tn_codes_ex": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
+    "df8_gemv_fp8_tn": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp],
+    "df8_kv_cache_append": [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
+    "df8_attention_decode_fp8": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp],
     "df8_layernorm_f32": [_vp, _i, _i, _vp, _vp, _f, _vp, _vp, _vp],
     "df8_layernorm_quantize_f32": [_vp, _i, _i, _vp, _vp, _f, _i, _vp, _vp, _vp, _vp, _vp],
     "df8_layernorm_quantize_f32_noalloc": [_vp, _i, _i, _vp, _vp, _f, _i, _vp, _vp, _vp, _vp],
@@ -260,6 +263,13 @@ _DNN_SIGNATURES = {
     "dnn_tokenizer_encode": [C.c_char_p, C.c_char_p, C.c_char_p, _i, _vp, _i],
     "dnn_tokenizer_decode": [C.c_char_p, C.c_char_p, _vp, _i, _i, _vp, _i],
     "dnn_tokenizer_save": [C.c_char_p, C.c_char_p],
+    "dnn_gpt2_prefill": [_vp, _vp, _i, _i, _i, _vp],
+    "dnn_gpt2_decode_step": [_vp, _vp, _i, _i, _vp],
+    "dnn_gpt2_end_decode": [_vp],
+    "dnn_gpt2_save_upstream": [_vp, C.c_char_p],
+    "dnn_gpt2_save_quantized": [_vp, C.c_char_p],
+    "dnn_gpt2_forward_text": [_vp, C.c_char_p, _vp, _i, _vp],
+    "dnn_file_roundtrip": [_i, C.c_char_p, C.c_char_p, _vp, _i, _vp],
     "dnn_set_host_init": [_i],
     "dnn_gpt2cs_destroy": [_vp],
     "dnn_gpt2cs_set_options": [_vp, _i, _i],
@@ -293,6 +303,11 @@ def dnn_lib() -> C.CDLL:
         handle.dnn_gpt2_streamed_bytes.argtypes = [_vp]
         handle.dnn_gpt2_load.restype = C.c_void_p
         handle.dnn_gpt2_load.argtypes = [C.c_char_p]
+        for fn in ("dnn_gpt2_load_upstream", "dnn_gpt2_load_quantized"):
+            getattr(handle, fn).restype = C.c_void_p
+            getattr(handle, fn).argtypes = [C.c_char_p]
+        handle.dnn_gpt2_create_with_tokenizer.restype = C.c_void_p
+        handle.dnn_gpt2_create_with_tokenizer.argtypes = [C.c_char_p] + [_i] * 6
         handle.dnn_gpt2cs_bytes_pushed.restype = C.c_ulonglong
         handle.dnn_gpt2cs_bytes_pushed.argtypes = [_vp]
         handle.dnn_gpt2cs_create.restype = C.c_void_p
@@ -313,13 +328,50 @@ def dnn_check(rc: int, what: str = "dnn call") -> None:
 class Gpt2:
     """dnn::Gpt2<float> driven through the C harness (tests and bench.py)."""
 
-    def __init__(self, vocab, max_seq_len, layers, heads, hidden, ffn, device: int = 0):
+    def __init__(self, vocab, max_seq_len, layers, heads, hidden, ffn, device: int = 0, vocab_json: str | None = None):
         d = dnn_lib()
         dnn_check(d.dnn_init(device), "dnn_init")
         self.cfg = dict(vocab=vocab, max_seq_len=max_seq_len, layers=layers, heads=heads, hidden=hidden, ffn=ffn)
-        self.h = d.dnn_gpt2_create(vocab, max_seq_len, layers, heads, hidden, ffn)
+        if vocab_json is not None:  # with a BpeTokenizer over that vocabulary file
+            self.h = d.dnn_gpt2_create_with_tokenizer(vocab_json.encode(), vocab, max_seq_len, layers, heads, hidden, ffn)
+        else:
+            self.h = d.dnn_gpt2_create(vocab, max_seq_len, layers, heads, hidden, ffn)
         if not self.h:
             raise Df8Error("dnn_gpt2_create failed: " + d.dnn_last_error().decode())
+
+    @classmethod
+    def from_file(cls, path: str, layout: str = "upstream", device: int = 0) -> "Gpt2":
+        """A model read from a file: layout 'upstream' (what upstream's Gpt2::save writes), 'quantized' (the
+        quantise-once cache of save_quantized) or 'native' (Gpt2::save of this build)."""
+        d = dnn_lib()
+        dnn_check(d.dnn_init(device), "dnn_init")
+        fn = {"upstream": d.dnn_gpt2_load_upstream, "quantized": d.dnn_gpt2_load_quantized, "native": d.dnn_gpt2_load}[layout]
+        h = fn(path.encode())
+        if not h:
+            raise Df8Error(f"loading {path} failed: " + d.dnn_last_error().decode())
+        self = cls.__new__(cls)
+        self.h = h
+        self.cfg = None
+        return self
+
+    def save_file(self, path: str, layout: str = "upstream"):
+        d = dnn_lib()
+        fn = {"upstream": d.dnn_gpt2_save_upstream, "quantized": d.dnn_gpt2_save_quantized, "native": d.dnn_gpt2_save}[layout]
+        dnn_check(fn(self.h, path.encode()), f"saving {path}")
+
+    def forward_text(self, text: str):
+        """Gpt2::forward_from_text: numpy hidden states [T, E] of the tokenised text."""
+        import numpy as np
+
+        cap = 1 << 24
+        out = np.empty(cap, np.float32)
+        t = C.c_int(0)
+        dnn_check(dnn_lib().dnn_gpt2_forward_text(self.h, text.encode(), out.ctypes.data_as(C.c_void_p), cap, C.byref(t)),
+                  "dnn_gpt2_forward_text")
+        hidden = self.cfg["hidden"] if self.cfg else None
+        if hidden is None:
+            raise Df8Error("forward_text needs the model's configuration (models made by from_file: use the harness call)")
+        return out[: t.value * hidden].reshape(t.value, hidden).copy()
 
     def close(self):
         if self.h:
@@ -443,6 +495,23 @@ class Gpt2:
         dnn_check(dnn_lib().dnn_gpt2_forward_hidden(self.h, ptr(ids_dev), B, T, C.byref(out)),
                   "dnn_gpt2_forward_hidden")
         return out.value
+
+    def prefill(self, ids_dev, max_len: int = 0) -> int:
+        """Prompt [B,T] (int32, device) -> device pointer of the last position's logits [B, vocab]; fills the KV cache."""
+        out = C.c_void_p(0)
+        B, T = ids_dev.shape
+        dnn_check(dnn_lib().dnn_gpt2_prefill(self.h, ptr(ids_dev), B, T, max_len, C.byref(out)), "dnn_gpt2_prefill")
+        return out.value
+
+    def decode_step(self, next_ids_dev, check_ids=True) -> int:
+        """One new token id per sequence [B] (int32, device) -> device pointer of its logits [B, vocab]."""
+        out = C.c_void_p(0)
+        dnn_check(dnn_lib().dnn_gpt2_decode_step(self.h, ptr(next_ids_dev), next_ids_dev.numel(), int(check_ids),
+                                                 C.byref(out)), "dnn_gpt2_decode_step")
+        return out.value
+
+    def end_decode(self):
+        dnn_check(dnn_lib().dnn_gpt2_end_decode(self.h), "dnn_gpt2_end_decode")
 
 
 class Comm:

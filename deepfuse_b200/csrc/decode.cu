@@ -1,0 +1,197 @@
+// The autoregressive decode step after a prefill: a cache of the keys and values of every earlier position, and
+// the attention of ONE new query per sequence and head against it.
+//
+// Upstream's Gpt2::forward recomputes the whole sequence for every call (dnn/models/gpt2.cu:126-142) and has no
+// cache; its attention semantics (dnn/layers/multi_head_attention.cu:225-301, softmax_layer.cu:26-81:
+// p = exp(s - max) / (sum + 1e-6)) are kept.  New here:
+//   * the cache holds the fp8 CODES the QKV projection produced, [B, H, T_max, D] per layer for K and for V, plus
+//     one dequantisation factor per cached position: the 8-bit path quantises every QKV tensor per tensor, so the
+//     positions of a prefill share one scale and every later step brings its own;
+//   * a step's attention is bound by reading the cache once from HBM (2 * t * D bytes per sequence and head):
+//     no tensor cores, one CTA per (sequence, head), its warps taking keys in turn with an online softmax each
+//     and a combine through shared memory.
+#include "df8_internal.cuh"
+
+namespace df8 {
+namespace {
+
+constexpr int kDecodeWarps = 8;
+
+// qkv [B*Tn, 3E] codes of Tn new positions per sequence -> rows t0 .. t0+Tn-1 of the K and V caches [B,H,Tmax,D]
+__global__ void __launch_bounds__(256)
+kv_append_kernel(const uint8_t* __restrict__ qkv, int B, int Tn, int H, int D, int t0, int Tmax,
+                 uint8_t* __restrict__ kc, uint8_t* __restrict__ vc, const float* __restrict__ scale,
+                 float* __restrict__ row_dq) {
+    griddep_launch_dependents();
+    griddep_wait();
+    const int E = H * D, d16 = D / 16;
+    const size_t total = size_t(B) * Tn * H * d16;  // 16-byte pieces per cache
+    for (size_t i = blockIdx.x * size_t(256) + threadIdx.x; i < total; i += size_t(gridDim.x) * 256) {
+        const int c = int(i % d16);
+        size_t r = i / d16;
+        const int h = int(r % H);
+        r /= H;
+        const int t = int(r % Tn), b = int(r / Tn);
+        const uint8_t* src = qkv + (size_t(b) * Tn + t) * 3 * E + h * D + c * 16;
+        const size_t dst = ((size_t(b) * H + h) * Tmax + t0 + t) * D + c * 16;
+        *reinterpret_cast<uint4*>(kc + dst) = *reinterpret_cast<const uint4*>(src + E);
+        *reinterpret_cast<uint4*>(vc + dst) = *reinterpret_cast<const uint4*>(src + 2 * E);
+    }
+    if (blockIdx.x == 0)
+        for (int t = threadIdx.x; t < Tn; t += 256) row_dq[t0 + t] = scale[1];
+}
+
+template <int KIND>
+__device__ __forceinline__ float dot16(const uint4& k, const float* __restrict__ q) {
+    const uint32_t w[4] = {k.x, k.y, k.z, k.w};
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 a = cvt_fp8x2_to_f32x2<KIND>(uint16_t(w[i] & 0xFFFFu));
+        const float2 b = cvt_fp8x2_to_f32x2<KIND>(uint16_t(w[i] >> 16));
+        s = fmaf(a.x, q[4 * i], s);
+        s = fmaf(a.y, q[4 * i + 1], s);
+        s = fmaf(b.x, q[4 * i + 2], s);
+        s = fmaf(b.y, q[4 * i + 3], s);
+    }
+    return s;
+}
+
+// One CTA per (sequence, head): out[b, h*D : (h+1)*D] = softmax(q . K^T / sqrt(D)) . V over the n_keys cached positions.
+template <int D, int KIND>
+__global__ void __launch_bounds__(32 * kDecodeWarps)
+attention_decode_kernel(const uint8_t* __restrict__ q_codes, const float* __restrict__ q_scale,
+                        const uint8_t* __restrict__ kc, const uint8_t* __restrict__ vc,
+                        const float* __restrict__ row_dq, int H, int n_keys, int Tmax, float* __restrict__ out,
+                        float* __restrict__ out_amax) {
+    griddep_launch_dependents();
+    griddep_wait();
+    constexpr int DPL = D / 32;  // output dimensions per lane
+    const int b = blockIdx.x / H, h = blockIdx.x % H;
+    const int E = H * D;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __shared__ float sq[D];
+    __shared__ float sm[kDecodeWarps], sl[kDecodeWarps], sacc[kDecodeWarps][D];
+    const float dq_q = q_scale[1];
+    // scores are kept in the log2 domain: s * log2(e) / sqrt(D), the query's scale folded in
+    const float qs = dq_q * rsqrtf(float(D)) * 1.4426950408889634f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const uint8_t c = q_codes[size_t(b) * 3 * E + h * D + d];
+        sq[d] = cvt_fp8x2_to_f32x2<KIND>(uint16_t(c)).x * qs;
+    }
+    __syncthreads();
+    const uint8_t* kbase = kc + (size_t(b) * H + h) * size_t(Tmax) * D;
+    const uint8_t* vbase = vc + (size_t(b) * H + h) * size_t(Tmax) * D;
+    float m = -INFINITY, l = 0.f, acc[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+    for (int j0 = warp * 32; j0 < n_keys; j0 += kDecodeWarps * 32) {
+        const int j = j0 + lane;
+        float s = -INFINITY, dqj = 0.f;
+        if (j < n_keys) {
+            dqj = row_dq[j];
+            float dot = 0.f;
+            const uint4* krow = reinterpret_cast<const uint4*>(kbase + size_t(j) * D);
+#pragma unroll
+            for (int c = 0; c < D / 16; ++c) dot += dot16<KIND>(krow[c], sq + 16 * c);
+            s = dot * dqj;
+        }
+        const float mb = warp_max(s);
+        const float m_new = fmaxf(m, mb);
+        const float alpha = exp2f(m - m_new);  // 0 for the first block (m = -inf)
+        const float p = (j < n_keys) ? exp2f(s - m_new) : 0.f;
+        l = l * alpha + warp_sum(p);
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[i] *= alpha;
+        m = m_new;
+        const float pv = p * dqj;  // the value row's scale
+        const int nk = min(32, n_keys - j0);
+        for (int k = 0; k < nk; ++k) {
+            const float pk = __shfl_sync(0xffffffffu, pv, k);
+            const uint8_t* vrow = vbase + size_t(j0 + k) * D;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i)
+                acc[i] = fmaf(pk, cvt_fp8x2_to_f32x2<KIND>(uint16_t(vrow[lane + 32 * i])).x, acc[i]);
+        }
+    }
+    if (lane == 0) {
+        sm[warp] = m;
+        sl[warp] = l;
+    }
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) sacc[warp][lane + 32 * i] = acc[i];
+    __syncthreads();
+    if (warp == 0) {
+        float mt = -INFINITY;
+        for (int w = 0; w < kDecodeWarps; ++w) mt = fmaxf(mt, sm[w]);
+        float lt = 0.f, o[DPL];
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) o[i] = 0.f;
+        for (int w = 0; w < kDecodeWarps; ++w) {
+            const float f = (sm[w] == -INFINITY) ? 0.f : exp2f(sm[w] - mt);
+            lt += sl[w] * f;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) o[i] = fmaf(sacc[w][lane + 32 * i], f, o[i]);
+        }
+        // p = exp(s - max) / (sum + 1e-6), as upstream's softmax
+        const float inv = 1.f / (lt + 1e-6f);
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const float v = (n_keys > 0) ? o[i] * inv : 0.f;
+            out[size_t(b) * E + h * D + lane + 32 * i] = v;
+            amax = fmaxf(amax, fabsf(v));
+        }
+        if (out_amax) {
+            amax = warp_max(amax);
+            if (lane == 0 && amax > 0.f) atomic_max_nonneg(out_amax, amax);
+        }
+    }
+}
+
+}  // namespace
+}  // namespace df8
+
+using namespace df8;
+
+extern "C" df8_status df8_kv_cache_append(const uint8_t* qkv_codes, const float* scale, int B, int Tn, int H, int D,
+                                          int t0, int Tmax, uint8_t* k_cache, uint8_t* v_cache, float* row_dq,
+                                          df8_stream stream) {
+    DF8_REQUIRE(B >= 0 && Tn >= 0 && H > 0 && D > 0 && D % 16 == 0, "df8_kv_cache_append: bad shape");
+    DF8_REQUIRE(t0 >= 0 && t0 + Tn <= Tmax, "df8_kv_cache_append: positions %d..%d do not fit a cache of %d", t0, t0 + Tn, Tmax);
+    if (B == 0 || Tn == 0) return DF8_OK;
+    DF8_REQUIRE(qkv_codes && scale && k_cache && v_cache && row_dq, "df8_kv_cache_append: null buffer");
+    DF8_REQUIRE(aligned16(qkv_codes) && aligned16(k_cache) && aligned16(v_cache), "df8_kv_cache_append: buffers must be 16-byte aligned");
+    const size_t total = size_t(B) * Tn * H * (D / 16);
+    size_t blocks = (total + 255) / 256;
+    const size_t cap = size_t(sm_count()) * 8;
+    if (blocks > cap) blocks = cap;
+    DF8_LAUNCH("kv_append_kernel", kv_append_kernel, dim3(unsigned(blocks)), dim3(256), 0, as_stream(stream), qkv_codes, B, Tn,
+               H, D, t0, Tmax, k_cache, v_cache, scale, row_dq);
+    return DF8_OK;
+}
+
+extern "C" df8_status df8_attention_decode_fp8(const uint8_t* qkv_codes, df8_kind kind, const float* scale,
+                                               const uint8_t* k_cache, const uint8_t* v_cache, const float* row_dq,
+                                               int B, int H, int D, int n_keys, int Tmax, float* out, float* out_amax,
+                                               df8_stream stream) {
+    DF8_REQUIRE(kind == DF8_E4M3 || kind == DF8_E5M2, "df8_attention_decode_fp8: unknown fp8 kind %d", int(kind));
+    DF8_REQUIRE(B >= 0 && H > 0 && n_keys >= 0 && n_keys <= Tmax, "df8_attention_decode_fp8: bad shape");
+    if (D != 64 && D != 128)
+        return fail(DF8_ERR_UNSUPPORTED, "df8_attention_decode_fp8: head dimension %d not supported (64 or 128)", D);
+    cudaStream_t st = as_stream(stream);
+    DF8_CLEAR_AMAX(out_amax, st);
+    if (B == 0) return DF8_OK;
+    DF8_REQUIRE(qkv_codes && scale && k_cache && v_cache && row_dq && out, "df8_attention_decode_fp8: null buffer");
+    DF8_REQUIRE(aligned16(k_cache) && aligned16(v_cache), "df8_attention_decode_fp8: the caches must be 16-byte aligned");
+    const dim3 grid(unsigned(B * H)), block(32 * kDecodeWarps);
+#define DF8_DECODE(DD, KK)                                                                                              \
+    DF8_LAUNCH("attention_decode_kernel", (attention_decode_kernel<DD, KK>), grid, block, 0, st, qkv_codes, scale, k_cache,  \
+               v_cache, row_dq, H, n_keys, Tmax, out, out_amax)
+    if (D == 64 && kind == DF8_E4M3) DF8_DECODE(64, DF8_E4M3);
+    else if (D == 64) DF8_DECODE(64, DF8_E5M2);
+    else if (kind == DF8_E4M3) DF8_DECODE(128, DF8_E4M3);
+    else DF8_DECODE(128, DF8_E5M2);
+#undef DF8_DECODE
+    return DF8_OK;
+}

@@ -55,6 +55,8 @@ constexpr int kOutE4M3 = 2;     // fp8 codes, N % 16 == 0
 constexpr int kOutE5M2 = 3;
 constexpr int kOutNone = 4;     // max|out| only
 constexpr int kOutF32Tma = 5;   // fp32 through TMA stores: row pitch a multiple of 4 floats, no residual, 256-column tiles
+constexpr int kOutF32T = 6;     // fp32, TRANSPOSED: out[n * ldc + m], bias indexed by m (the skinny products of a decode step,
+                                // computed as W . X^T so that the weight rows fill the 128-row tile)
 
 // the modes whose epilogue works thread = row straight from registers (fp8 codes, max|out| only)
 __host__ __device__ constexpr bool is_direct(int mode) { return mode == kOutE4M3 || mode == kOutE5M2 || mode == kOutNone; }
@@ -418,6 +420,59 @@ __device__ __forceinline__ bool epilogue_tile_f32_tma(const CUtensorMap* tma_out
     return true;
 }
 
+// ---- fp32 output, transposed (kOutF32T) ------------------------------------------------------------------
+//
+// A decode step multiplies a handful of token rows (the batch) with a whole weight matrix: the product is bound by
+// streaming the weights from HBM, and with the tokens as the M dimension a 128-row tile would be almost empty.  So
+// the operands swap roles: the kernel's A is the WEIGHT matrix [rows = output features, K] and its "W" operand the
+// activations [batch, K]; the accumulator tile is [128 features, batch] and leaves transposed, out[b * ldc + f].
+// thread = feature row, so for a fixed batch column the 32 lanes of a warp write 32 consecutive floats.  bias is
+// indexed by the feature (row), the residual is read at the output's position.
+template <typename ReleaseFn>
+__device__ __forceinline__ bool epilogue_tile_f32_transposed(const GemmArgs& args, uint32_t tfull_bar, uint32_t acc_phase,
+                                                             uint32_t taddr, int row0, int n0, int half, int lane,
+                                                             float alpha, float& amax, ReleaseFn release) {
+    constexpr int kChunks = 2;  // BN = 128: chunks half, half + 2
+    const int grow = row0 + lane;
+    const bool row_ok = grow < args.M;
+    const float b = (args.bias && row_ok) ? __ldg(args.bias + grow) : 0.f;
+    if (!mbar_wait_bounded(tfull_bar, acc_phase)) return false;
+    tc_fence_after_sync();
+    int nvalid = 0;
+#pragma unroll
+    for (int j = 0; j < kChunks; ++j)
+        if (n0 + 32 * (half + 2 * j) < args.N) nvalid = j + 1;
+    for (int j = 0; j < nvalid; ++j) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + 32 * (half + 2 * j), r);
+        tmem_ld_wait();
+        if (j + 1 == nvalid) {
+            tc_fence_before_sync();
+            __syncwarp();
+            release();
+        }
+        const int col0 = n0 + 32 * (half + 2 * j);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const int col = col0 + i;  // batch row
+            if (col < args.N && row_ok) {
+                float v = fmaf(__uint_as_float(r[i]), alpha, b);
+                if (args.flags & 1) v = gelu_tanh(v);
+                const size_t at = size_t(col) * args.ldc + grow;
+                if (args.flags & 2) v += args.residual[at];
+                amax = fmaxf(amax, fabsf(v));
+                args.out[at] = v;
+            }
+        }
+    }
+    if (nvalid == 0) {
+        tc_fence_before_sync();
+        __syncwarp();
+        release();
+    }
+    return true;
+}
+
 // FUSED (fp8 modes only): the one-launch max|out| + codes form, an instantiation of its own so that the plain
 // kernels carry none of its code or registers.
 template <int BN, int STAGES, int MODE, bool FUSED = false>
@@ -694,6 +749,17 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
             const int n0 = (tile / num_m) * BN;
             const int row0 = m0 + q * 32;
             const uint32_t taddr = tmem_base + buf * BN + lane_addr;
+            if constexpr (MODE == kOutF32T) {
+                auto release = [&] {
+                    if (lane == 0) mbar_arrive(smem_u32(tempty + buf));
+                };
+                if (!epilogue_tile_f32_transposed(args, smem_u32(tfull + buf), acc_phase, taddr, row0, n0, half, lane, alpha,
+                                                  amax, release)) {
+                    if (lane == 0) record_timeout(args.status, 0x400u + buf);
+                    break;
+                }
+                continue;
+            }
             if constexpr (MODE == kOutF32Tma) {
                 uint8_t* boxes = reinterpret_cast<uint8_t*>(staging) + e * (2 * kTmaBoxBytes);
                 float* sbias = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(staging) + kEpiWarps * 2 * kTmaBoxBytes) +
@@ -1208,6 +1274,8 @@ df8_status launch_gemm_bn(bool wide, const CUtensorMap& ta, const CUtensorMap& t
         return wide ? launch_gemm<256, 4, MODE>(ta, tw, to, args, grid, st) : launch_gemm<128, 6, MODE>(ta, tw, to, args, grid, st);
     else if constexpr (MODE == kOutF32Tma)  // 256-column tiles only (run_gemm falls back to the st.global modes otherwise)
         return launch_gemm<256, 3, MODE>(ta, tw, to, args, grid, st);
+    else if constexpr (MODE == kOutF32T)  // the batch is the N dimension: one 128-column tile at most
+        return launch_gemm<128, 5, MODE>(ta, tw, to, args, grid, st);
     else
         return wide ? launch_gemm<256, 3, MODE>(ta, tw, to, args, grid, st) : launch_gemm<128, 5, MODE>(ta, tw, to, args, grid, st);
 }
@@ -1264,7 +1332,7 @@ df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uin
         return make_tmap_2d_f32(&to, args.out, uint64_t(M), uint64_t(N), uint64_t(args.ldc) * sizeof(float), 32, 32, 128);
     };
     // CTA pairs on 256 x 256 tiles when the problem fills them (see gemm_fp8_tn_pair_kernel)
-    if (use_pair_kernel(M, N, K, sms, mode)) {
+    if (mode != kOutF32T && use_pair_kernel(M, N, K, sms, mode)) {
         if (want_fused) return DF8_OK;
         // Tile width of the fp32 modes, by the measured per-K-block and per-chunk costs (cycles): a K block is
         // bound by the tensor core (2 BN) or by the CTA's operand bytes arriving at ~50 bytes per cycle while the
@@ -1320,7 +1388,7 @@ df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uin
         const double epilogue = (cost_mode == kOutF32Vec || cost_mode == kOutF32) ? 31.0 * bn : 0.0;
         return main_loop > epilogue ? main_loop : epilogue;
     };
-    const bool wide = N > 128 && rounds(256) * tile_cycles(256) <= rounds(128) * tile_cycles(128);
+    const bool wide = mode != kOutF32T && N > 128 && rounds(256) * tile_cycles(256) <= rounds(128) * tile_cycles(128);
     if (mode == kOutF32Tma && !wide) mode = tma_fallback;  // the TMA-store epilogue exists for 256-column tiles
     const int bn = wide ? 256 : 128;
     const long tiles = long((M + BM - 1) / BM) * ((N + bn - 1) / bn);
@@ -1350,6 +1418,7 @@ df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uin
         case kOutF32Vec: return launch_gemm_bn<kOutF32Vec>(wide, ta, tw, to, args, grid, st);
         case kOutF32: return launch_gemm_bn<kOutF32>(wide, ta, tw, to, args, grid, st);
         case kOutF32Tma: return launch_gemm_bn<kOutF32Tma>(wide, ta, tw, to, args, grid, st);
+        case kOutF32T: return launch_gemm_bn<kOutF32T>(wide, ta, tw, to, args, grid, st);
         case kOutE4M3: return launch_gemm_bn<kOutE4M3>(wide, ta, tw, to, args, grid, st);
         case kOutE5M2: return launch_gemm_bn<kOutE5M2>(wide, ta, tw, to, args, grid, st);
         default: return launch_gemm_bn<kOutNone>(wide, ta, tw, to, args, grid, st);
@@ -1548,4 +1617,40 @@ extern "C" df8_status df8_gemm_fp8_tn_codes_ex(const uint8_t* a_codes, df8_kind 
     args.out_scale = out_scale;
     return run_gemm(out_kind == DF8_E4M3 ? kOutE4M3 : kOutE5M2, a_codes, kind_a, w_codes, kind_w, args, as_stream(stream),
                     nullptr, a_slabs);
+}
+
+// The skinny product of a decode step: out[B, N] = epi(X[B, K] . W[N, K]^T * dq + bias), B <= 128 token rows against a
+// whole weight matrix.  Bound by streaming W from HBM; computed as W . X^T (the weight rows fill the 128-row
+// tensor-core tile, the batch is the tile's N) and written back transposed.
+extern "C" df8_status df8_gemv_fp8_tn(const uint8_t* x_codes, df8_kind kind_x, const float* scale_x,
+                                      const uint8_t* w_codes, df8_kind kind_w, const float* scale_w, const float* bias,
+                                      const float* residual, int B, int N, int K, int flags, float* out, float* out_amax,
+                                      df8_stream stream) {
+    DF8_REQUIRE((kind_x == DF8_E4M3 || kind_x == DF8_E5M2) && (kind_w == DF8_E4M3 || kind_w == DF8_E5M2),
+                "df8_gemv_fp8_tn: unknown fp8 kind");
+    DF8_REQUIRE(B >= 0 && N >= 0 && K > 0, "df8_gemv_fp8_tn: bad shape B=%d N=%d K=%d", B, N, K);
+    DF8_REQUIRE((flags & ~7) == 0, "df8_gemv_fp8_tn: unknown flags 0x%x", flags);
+    cudaStream_t st = as_stream(stream);
+    if (flags & DF8_EPI_AMAX) {
+        DF8_REQUIRE(out_amax != nullptr, "df8_gemv_fp8_tn: DF8_EPI_AMAX needs out_amax");
+        DF8_CLEAR_AMAX(out_amax, st);
+    }
+    if (B == 0 || N == 0) return DF8_OK;
+    if (B > 128) return fail(DF8_ERR_UNSUPPORTED, "df8_gemv_fp8_tn: at most 128 token rows (got %d); use df8_gemm_fp8_tn", B);
+    if (K % 16 != 0) return fail(DF8_ERR_UNSUPPORTED, "df8_gemv_fp8_tn: K=%d must be a multiple of 16 (TMA row pitch)", K);
+    DF8_REQUIRE(x_codes && w_codes && scale_x && scale_w && out, "df8_gemv_fp8_tn: null buffer");
+    DF8_REQUIRE(!(flags & DF8_EPI_RESIDUAL) || residual != nullptr, "df8_gemv_fp8_tn: DF8_EPI_RESIDUAL needs residual");
+    GemmArgs args{};
+    args.scale_a = scale_w;  // the roles are swapped: the kernel's A operand is the weight matrix
+    args.scale_w = scale_x;
+    args.bias = bias;
+    args.residual = residual;
+    args.out = out;
+    args.out_amax = out_amax;
+    args.M = N;
+    args.N = B;
+    args.K = K;
+    args.ldc = N;
+    args.flags = flags;
+    return run_gemm(kOutF32T, w_codes, kind_w, x_codes, kind_x, args, st);
 }

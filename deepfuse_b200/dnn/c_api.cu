@@ -628,3 +628,137 @@ extern "C" int dnn_tokenizer_save(const char* vocab_json_path, const char* out_p
         tok->save(out);
     });
 }
+
+// ---- checkpoint files -----------------------------------------------------------------------------------
+
+namespace {
+dnn_gpt2* wrap_model(std::unique_ptr<dnn::Gpt2<float>> model) {
+    auto handle = std::make_unique<dnn_gpt2>();
+    handle->model = std::move(model);
+    handle->index_params();
+    return handle.release();
+}
+}  // namespace
+
+extern "C" dnn_gpt2* dnn_gpt2_create_with_tokenizer(const char* vocab_json_path, int vocab, int max_seq_len, int layers,
+                                                    int heads, int hidden, int ffn) {
+    dnn_gpt2* h = nullptr;
+    guarded([&] {
+        h = wrap_model(std::make_unique<dnn::Gpt2<float>>(make_tokenizer(vocab_json_path, nullptr), vocab, max_seq_len,
+                                                          layers, heads, hidden, ffn));
+    });
+    return h;
+}
+
+extern "C" int dnn_gpt2_save_upstream(dnn_gpt2* m, const char* path) {
+    return guarded([&] { m->model->save_upstream(path); });
+}
+
+extern "C" dnn_gpt2* dnn_gpt2_load_upstream(const char* path) {
+    dnn_gpt2* h = nullptr;
+    guarded([&] { h = wrap_model(dnn::Gpt2<float>::load_upstream(path, false)); });
+    return h;
+}
+
+extern "C" int dnn_gpt2_save_quantized(dnn_gpt2* m, const char* path) {
+    return guarded([&] { m->model->save_quantized(path); });
+}
+
+extern "C" dnn_gpt2* dnn_gpt2_load_quantized(const char* path) {
+    dnn_gpt2* h = nullptr;
+    guarded([&] { h = wrap_model(dnn::Gpt2<float>::load_quantized(path)); });
+    return h;
+}
+
+extern "C" int dnn_gpt2_forward_text(dnn_gpt2* m, const char* text, float* hidden_h, int cap_floats, int* tokens_h) {
+    return guarded([&] {
+        dnn::tensor<float> hidden = m->model->forward_from_text(text);
+        if (tokens_h) *tokens_h = hidden.size(1);
+        if (hidden.size() > cap_floats) throw std::runtime_error("dnn_gpt2_forward_text: output buffer too small");
+        hidden.download(hidden_h);
+    });
+}
+
+// Reads one record with the class's own load(), hands the parameters back and writes the record again with the
+// class's own save(): what = 0 tensor<float>, 1 FullyConnectedLayer, 2 LayerNormLayer (gamma, beta), 3 TokenEmbedding,
+// 4 TransformerBlock (its 12 parameter tensors in the order of dnn_block_forward).  params_h receives the
+// parameter tensors one after the other (at most cap_floats floats), *count_h their total length.
+extern "C" int dnn_file_roundtrip(int what, const char* in_path, const char* out_path, float* params_h, int cap_floats,
+                                  int* count_h) {
+    return guarded([&] {
+        std::ifstream in(in_path, std::ios::binary);
+        if (!in) throw std::runtime_error(std::string("cannot open ") + in_path);
+        std::ofstream out(out_path, std::ios::binary);
+        if (!out) throw std::runtime_error(std::string("cannot write ") + out_path);
+        int used = 0;
+        auto take = [&](const dnn::tensor<float>& t) {
+            if (used + t.size() > cap_floats) throw std::runtime_error("dnn_file_roundtrip: params_h too small");
+            t.download(params_h + used);
+            used += t.size();
+        };
+        dnn::fp8::Policy& pol = dnn::fp8::policy();
+        const bool prev = pol.host_init;
+        pol.host_init = false;
+        try {
+            if (what == 0) {
+                dnn::tensor<float> t({1});
+                t.load(in);
+                take(t);
+                t.save(out);
+            } else if (what == 1) {
+                dnn::FullyConnectedLayer<float> fc(1, 1);
+                fc.load(in);
+                take(*fc.weights());
+                take(*fc.bias());
+                fc.save(out);
+            } else if (what == 2) {
+                dnn::LayerNormLayer<float> ln(1);
+                ln.load(in);
+                for (auto* p : ln.parameters()) take(*p);
+                ln.save(out);
+            } else if (what == 3) {
+                dnn::TokenEmbedding<float> emb(1, 1, 1);
+                emb.load(in);
+                take(*emb.weights());
+                take(*emb.bias());
+                emb.save(out);
+            } else if (what == 4) {
+                dnn::TransformerBlock<float> blk(1, 1, 1);
+                blk.load(in);
+                for (auto* p : blk.parameters()) take(*p);
+                blk.save(out);
+            } else {
+                throw std::invalid_argument("dnn_file_roundtrip: unknown record kind");
+            }
+        } catch (...) {
+            pol.host_init = prev;
+            throw;
+        }
+        pol.host_init = prev;
+        if (count_h) *count_h = used;
+    });
+}
+
+// ---- autoregressive decoding ----------------------------------------------------------------------------
+
+extern "C" int dnn_gpt2_prefill(dnn_gpt2* m, const int32_t* ids_d, int B, int T, int max_len, float** logits_d) {
+    return guarded([&] {
+        stage_ids(m, ids_d, B, T, cudaMemcpyDeviceToDevice);
+        m->last.reset();
+        m->last = std::make_unique<dnn::tensor<float>>(m->model->prefill(*m->ids, max_len, true));
+        *logits_d = m->last->data();
+    });
+}
+
+extern "C" int dnn_gpt2_decode_step(dnn_gpt2* m, const int32_t* next_ids_d, int B, int check_ids, float** logits_d) {
+    return guarded([&] {
+        stage_ids(m, next_ids_d, B, 1, cudaMemcpyDeviceToDevice);
+        m->last.reset();
+        m->last = std::make_unique<dnn::tensor<float>>(m->model->decode_step(*m->ids, check_ids != 0));
+        *logits_d = m->last->data();
+    });
+}
+
+extern "C" int dnn_gpt2_end_decode(dnn_gpt2* m) {
+    return guarded([&] { m->model->end_decode(); });
+}

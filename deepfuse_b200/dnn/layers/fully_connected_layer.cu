@@ -124,6 +124,54 @@ void FullyConnectedLayer<TT>::export_weight_codes(uint8_t* dst_h) {
     utils::CHECK_CUDA_EX(cudaStreamSynchronize(Cuda::stream()));
 }
 
+// record: int in, out, padded_in, kind; float scale[2], amax; codes [out * padded_in] bytes; bias [out] floats
+template <typename TT>
+void FullyConnectedLayer<TT>::export_quantized(std::ostream& out) {
+    const fp8::Quantized& w = quantized_weights();
+    if (w.codes.numel() != weight_code_bytes())
+        throw std::runtime_error("FullyConnectedLayer::export_quantized: the weight codes are not resident (layer streaming)");
+    const int hdr[4] = {in_features_, out_features_, padded_in(), int(w.kind)};
+    out.write(reinterpret_cast<const char*>(hdr), sizeof(hdr));
+    float meta[3] = {0.f, 0.f, 0.f};
+    utils::CHECK_CUDA_EX(cudaMemcpyAsync(meta, w.scale.data(), 2 * sizeof(float), cudaMemcpyDeviceToHost, Cuda::stream()));
+    utils::CHECK_CUDA_EX(cudaMemcpyAsync(meta + 2, w.amax.data(), sizeof(float), cudaMemcpyDeviceToHost, Cuda::stream()));
+    std::vector<uint8_t> codes(weight_code_bytes());
+    export_weight_codes(codes.data());  // synchronises the stream
+    out.write(reinterpret_cast<const char*>(meta), sizeof(meta));
+    out.write(reinterpret_cast<const char*>(codes.data()), std::streamsize(codes.size()));
+    std::vector<float> bias(static_cast<size_t>(out_features_));
+    this->bias_.download(bias.data());
+    out.write(reinterpret_cast<const char*>(bias.data()), std::streamsize(bias.size() * sizeof(float)));
+}
+
+template <typename TT>
+void FullyConnectedLayer<TT>::import_quantized(std::istream& in) {
+    if constexpr (!std::is_same<TT, float>::value) {
+        throw std::runtime_error("FullyConnectedLayer::import_quantized: float layers only");
+    } else {
+        int hdr[4] = {0, 0, 0, 0};
+        in.read(reinterpret_cast<char*>(hdr), sizeof(hdr));
+        if (!in || hdr[0] != in_features_ || hdr[1] != out_features_ || hdr[2] != padded_in() || (hdr[3] != 0 && hdr[3] != 1))
+            throw std::runtime_error("FullyConnectedLayer::import_quantized: the record does not match this layer");
+        float meta[3];
+        in.read(reinterpret_cast<char*>(meta), sizeof(meta));
+        std::vector<uint8_t> codes(weight_code_bytes());
+        in.read(reinterpret_cast<char*>(codes.data()), std::streamsize(codes.size()));
+        std::vector<float> bias(static_cast<size_t>(out_features_));
+        in.read(reinterpret_cast<char*>(bias.data()), std::streamsize(bias.size() * sizeof(float)));
+        if (!in) throw std::runtime_error("FullyConnectedLayer::import_quantized: truncated record");
+        wq_.codes = tensor<uint8_t>({int(codes.size())});
+        wq_.codes.upload(codes.data());
+        wq_.kind = df8_kind(hdr[3]);
+        utils::CHECK_CUDA_EX(cudaMemcpyAsync(wq_.scale.data(), meta, 2 * sizeof(float), cudaMemcpyHostToDevice, Cuda::stream()));
+        utils::CHECK_CUDA_EX(cudaMemcpyAsync(wq_.amax.data(), meta + 2, sizeof(float), cudaMemcpyHostToDevice, Cuda::stream()));
+        this->bias_.upload(bias.data());
+        utils::CHECK_CUDA_EX(cudaStreamSynchronize(Cuda::stream()));  // the host buffers die at scope exit
+        this->weights_ = tensor<TT>({0, in_features_});  // no fp32 master copy; keep version(): the codes are current
+        mark_weights_quantized();
+    }
+}
+
 template <typename TT>
 void FullyConnectedLayer<TT>::drop_cached_codes() {
     quantized_weights();  // make sure the scale is current before the codes go away
@@ -139,6 +187,15 @@ void FullyConnectedLayer<TT>::forward_codes(const uint8_t* a_codes, df8_kind a_k
     utils::CHECK_DF8(df8_gemm_fp8_tn_ex(a_codes, a_kind, a_scale, a_slabs, w_codes, w.kind, w.scale.data(),
                                         this->bias_.data(), residual, M, out_features_, padded_in(), flags, out,
                                         ldc > 0 ? ldc : out_features_, out_amax, fp8::stream()));
+}
+
+template <typename TT>
+void FullyConnectedLayer<TT>::forward_codes_skinny(const uint8_t* a_codes, df8_kind a_kind, const float* a_scale, int B,
+                                                   int flags, const float* residual, float* out, float* out_amax) {
+    const fp8::Quantized& w = quantized_weights();
+    const uint8_t* w_codes = external_codes_ ? external_codes_ : w.codes.data();
+    utils::CHECK_DF8(df8_gemv_fp8_tn(a_codes, a_kind, a_scale, w_codes, w.kind, w.scale.data(), this->bias_.data(), residual,
+                                     B, out_features_, padded_in(), flags, out, out_amax, fp8::stream()));
 }
 
 template <typename TT>

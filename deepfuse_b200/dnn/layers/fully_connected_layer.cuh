@@ -49,6 +49,11 @@ public:
     void forward_codes(const uint8_t* a_codes, df8_kind a_kind, const float* a_scale, int M, int flags,
                        const float* residual, float* out, float* out_amax, int ldc = 0, int a_slabs = 1);
 
+    // The same product for the few token rows of a decode step (B <= 128): bound by streaming the weights
+    // (df8_gemv_fp8_tn).
+    void forward_codes_skinny(const uint8_t* a_codes, df8_kind a_kind, const float* a_scale, int B, int flags,
+                              const float* residual, float* out, float* out_amax);
+
     // q <- per-tensor quantisation (kind out_kind) of epilogue(codes . Wq^T), `flags` = 0 or DF8_EPI_GELU.
     // Uses the two-pass GEMM that never writes the fp32 result when out_features % 32 == 0.
     void forward_codes_quantized(const uint8_t* a_codes, df8_kind a_kind, const float* a_scale, int M, int flags,
@@ -63,6 +68,11 @@ public:
     void export_weight_codes(uint8_t* dst_h);
     // Frees the device copy of the weight codes (streaming mode keeps them in pinned host memory).
     void drop_cached_codes();
+    // The quantise-once cache: this layer's weight codes [out, padded_in()], their {q, dq} scale, the amax they were
+    // derived from and the fp32 bias as one binary record; import installs them without the fp32 weights ever
+    // being on the device (weights() is then an empty [0, in] tensor, as after release_fp32 in layer streaming).
+    void export_quantized(std::ostream& out);
+    void import_quantized(std::istream& in);
     // Declares the cached scale current for the present weights tensor / forces a re-quantisation.
     void mark_weights_quantized() { wq_version_ = this->weights_.version(); }
     void invalidate_quantized_weights() { wq_version_ = ~0ull; }

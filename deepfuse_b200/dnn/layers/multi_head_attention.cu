@@ -49,6 +49,12 @@ void MultiHeadAttentionLayer<TT>::forward_quantized(const fp8::Quantized& xq, in
     // QKV projection straight to per-tensor-quantised codes (the fp32 [M,3E] tensor is never written)
     qkv_proj_.forward_codes_quantized(xq.codes.data(), xq.kind, xq.scale.data(), M, 0, act, qkvq_);
 
+    if (kv_) {  // a prefill: keep the keys and values of these positions for the decode steps
+        if (B != kv_->batch || kv_len_ + T > kv_->max_len)
+            throw std::runtime_error("MultiHeadAttentionLayer: the attached KV cache does not fit this batch / length");
+        utils::CHECK_DF8(df8_kv_cache_append(qkvq_.codes.data(), qkvq_.scale.data(), B, T, num_heads_, head_dim_, kv_len_,
+                                             kv_->max_len, kv_->k.data(), kv_->v.data(), kv_->row_dq.data(), fp8::stream()));
+    }
     int mode = causal_ ? DF8_MASK_CAUSAL : DF8_MASK_NONE;
     const float* mask_ptr = nullptr;
     int mask_b = 0;
@@ -66,6 +72,30 @@ void MultiHeadAttentionLayer<TT>::forward_quantized(const fp8::Quantized& xq, in
     fp8::quantize_with_amax(attn_f32_.data(), attn_f32_.numel(), act, am, attnq_);
     out_proj_.forward_codes(attnq_.codes.data(), attnq_.kind, attnq_.scale.data(), M,
                             residual ? DF8_EPI_RESIDUAL : 0, residual, out, nullptr);
+}
+
+template <typename TT>
+void MultiHeadAttentionLayer<TT>::decode_quantized(const fp8::Quantized& xq, int B, const float* residual, float* out) {
+    if (!kv_) throw std::runtime_error("MultiHeadAttentionLayer::decode_quantized: no KV cache attached");
+    if (B != kv_->batch || kv_len_ + 1 > kv_->max_len)
+        throw std::runtime_error("MultiHeadAttentionLayer::decode_quantized: the KV cache is full or of another batch size");
+    const int E = embed_dim_;
+    const df8_kind act = fp8::policy().activation_kind;
+    if (qkv_f32_.numel() != size_t(B) * 3 * E) qkv_f32_ = tensor<float>({B, 3 * E});
+    if (attn_f32_.numel() != size_t(B) * E) attn_f32_ = tensor<float>({B, E});
+    // the new token's QKV, quantised per tensor like every QKV tensor of the 8-bit path
+    float* am = fp8::amax_slot(amax_.data());
+    qkv_proj_.forward_codes_skinny(xq.codes.data(), xq.kind, xq.scale.data(), B, DF8_EPI_AMAX, nullptr, qkv_f32_.data(), am);
+    fp8::quantize_with_amax(qkv_f32_.data(), qkv_f32_.numel(), act, am, qkvq_);
+    utils::CHECK_DF8(df8_kv_cache_append(qkvq_.codes.data(), qkvq_.scale.data(), B, 1, num_heads_, head_dim_, kv_len_,
+                                         kv_->max_len, kv_->k.data(), kv_->v.data(), kv_->row_dq.data(), fp8::stream()));
+    float* am2 = fp8::amax_slot(amax_.data());
+    utils::CHECK_DF8(df8_attention_decode_fp8(qkvq_.codes.data(), qkvq_.kind, qkvq_.scale.data(), kv_->k.data(),
+                                              kv_->v.data(), kv_->row_dq.data(), B, num_heads_, head_dim_, kv_len_ + 1,
+                                              kv_->max_len, attn_f32_.data(), am2, fp8::stream()));
+    fp8::quantize_with_amax(attn_f32_.data(), attn_f32_.numel(), act, am2, attnq_);
+    out_proj_.forward_codes_skinny(attnq_.codes.data(), attnq_.kind, attnq_.scale.data(), B,
+                                   residual ? DF8_EPI_RESIDUAL : 0, residual, out, nullptr);
 }
 
 template <typename TT>

@@ -58,6 +58,21 @@ public:
     // out[B*T, E] = out_proj(attention(qkv_proj(xq))) (+ residual when given), fp32.
     void forward_quantized(const fp8::Quantized& xq, int B, int T, const float* residual, float* out);
 
+    // ---- autoregressive decoding (no upstream counterpart: its forward recomputes the whole sequence) ----
+    // A cache of this layer's key and value codes, [B, H, max_len, D] each, with one dequantisation factor per
+    // position.  While a cache is attached, forward_quantized() also stores the K / V codes of the positions it
+    // sees at rows `kv_len` .. (a prefill), and decode_quantized() runs one step: the new token's QKV (a skinny
+    // product), its K / V appended at row `kv_len`, the query against all kv_len + 1 cached positions, the output
+    // projection.  The owner (the model) advances kv_len after every layer has seen the positions.
+    struct KvCache {
+        tensor<uint8_t> k{{0}}, v{{0}};
+        tensor<float> row_dq{{0}};
+        int batch = 0, max_len = 0;
+    };
+    void attach_kv_cache(KvCache* cache) { kv_ = cache; }
+    void set_kv_len(int len) { kv_len_ = len; }
+    void decode_quantized(const fp8::Quantized& xq, int B, const float* residual, float* out);
+
 private:
     int embed_dim_;
     int num_heads_;
@@ -73,6 +88,9 @@ private:
     tensor<float> attn_f32_;
     tensor<float> amax_;
     fp8::Quantized xq_, qkvq_, attnq_;
+    KvCache* kv_ = nullptr;
+    int kv_len_ = 0;
+    tensor<float> qkv_f32_{{0}};
 };
 
 }  // namespace dnn

@@ -58,6 +58,8 @@ public:
 
     // In-place variant used by the model loop: x [B*T, E] fp32 is replaced by the block output.
     void forward_inplace(float* x, int B, int T_len);
+    // One decode step on x [B, E] (one new token per sequence) against the attention layer's attached KV cache.
+    void decode_inplace(float* x, int B);
 
 private:
     int embed_dim_;
@@ -73,6 +75,7 @@ private:
     // reused work buffers
     fp8::Quantized ln_q_, hidden_q_;
     tensor<float> x1_;
+    tensor<float> hidden_f32_{{0}}, amax_{{1}};
 };
 
 }  // namespace dnn

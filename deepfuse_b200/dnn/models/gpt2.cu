@@ -1,7 +1,11 @@
 #include "dnn/models/gpt2.cuh"
 
+#include <algorithm>
 #include <fstream>
 #include <random>
+
+#include "dnn/tokens/bpe_tokenizer.cuh"
+#include "dnn/tokens/vocab_loader.cuh"
 
 namespace dnn {
 
@@ -157,6 +161,83 @@ tensor<T> Gpt2<T>::forward_logits_pitched(const tensor<int>& ids, bool check_ids
     return logits;
 }
 
+// logits [B, V] of the last position of every sequence of x [B, T_len, E]
+template <typename T>
+tensor<T> Gpt2<T>::last_rows_logits(const float* x, int B, int T_len) {
+    const int E = hidden_dim_;
+    tensor<T> last({B, E});
+    utils::CHECK_CUDA_EX(cudaMemcpy2DAsync(last.data(), size_t(E) * sizeof(float), x + size_t(T_len - 1) * E,
+                                           size_t(T_len) * E * sizeof(float), size_t(E) * sizeof(float), size_t(B),
+                                           cudaMemcpyDeviceToDevice, Cuda::stream()));
+    fp8::quantize(last.data(), last.numel(), fp8::policy().activation_kind, head_q_);
+    tensor<T> logits({B, vocab_size_});
+    final_fc_->forward_codes_skinny(head_q_.codes.data(), head_q_.kind, head_q_.scale.data(), B, 0, nullptr, logits.data(),
+                                    nullptr);
+    return logits;
+}
+
+template <typename T>
+tensor<T> Gpt2<T>::prefill(const tensor<int>& ids, int max_len, bool check_ids) {
+    const auto& s = ids.shape();
+    if (s.size() != 2) throw std::runtime_error("Gpt2 expects token ids shaped [B, T]");
+    const int B = s[0], T_len = s[1];
+    if (max_len <= 0) max_len = max_seq_len_;
+    if (T_len < 1 || T_len > max_len || max_len > max_seq_len_ || B < 1 || B > 128)
+        throw std::runtime_error("Gpt2::prefill: needs 1 <= T <= max_len <= max_seq_len and 1 <= B <= 128");
+    if (streamer_) throw std::runtime_error("Gpt2::prefill: decoding with streamed weights is not supported");
+    end_decode();
+    for (auto& blk : transformer_blocks_) {
+        auto cache = std::make_unique<typename MultiHeadAttentionLayer<T>::KvCache>();
+        const int H = blk->attention().num_heads(), D = blk->attention().head_dim();
+        cache->k = tensor<uint8_t>({B, H, max_len, D});
+        cache->v = tensor<uint8_t>({B, H, max_len, D});
+        cache->row_dq = tensor<float>({max_len});
+        cache->batch = B;
+        cache->max_len = max_len;
+        blk->attention().attach_kv_cache(cache.get());
+        blk->attention().set_kv_len(0);
+        blk->attention().set_causal(true);
+        kv_.push_back(std::move(cache));
+    }
+    fp8::PassScope amax_slots;
+    tensor<T> x = token_embedding_->forward_with_positions(ids, positional_encoding_->table().data(), check_ids);
+    for (auto& blk : transformer_blocks_) blk->forward_inplace(x.data(), B, T_len);
+    kv_len_ = T_len;
+    return last_rows_logits(x.data(), B, T_len);
+}
+
+template <typename T>
+tensor<T> Gpt2<T>::decode_step(const tensor<int>& next_ids, bool check_ids) {
+    if (kv_.empty()) throw std::runtime_error("Gpt2::decode_step: call prefill first");
+    const int B = kv_[0]->batch;
+    if (next_ids.numel() != size_t(B)) throw std::runtime_error("Gpt2::decode_step: one token id per sequence of the prefill");
+    if (kv_len_ + 1 > kv_[0]->max_len) throw std::runtime_error("Gpt2::decode_step: the KV cache is full");
+    tensor<int> ids({B, 1});
+    utils::CHECK_CUDA_EX(cudaMemcpyAsync(ids.data(), next_ids.data(), size_t(B) * sizeof(int), cudaMemcpyDeviceToDevice,
+                                         Cuda::stream()));
+    fp8::PassScope amax_slots;
+    // position kv_len_: its row of the sinusoidal table
+    tensor<T> x = token_embedding_->forward_with_positions(
+        ids, positional_encoding_->table().data() + size_t(kv_len_) * hidden_dim_, check_ids);
+    for (auto& blk : transformer_blocks_) {
+        blk->attention().set_kv_len(kv_len_);
+        blk->decode_inplace(x.data(), B);
+    }
+    ++kv_len_;
+    return last_rows_logits(x.data(), B, 1);
+}
+
+template <typename T>
+void Gpt2<T>::end_decode() {
+    for (auto& blk : transformer_blocks_) {
+        blk->attention().attach_kv_cache(nullptr);
+        blk->attention().set_kv_len(0);
+    }
+    if (!kv_.empty()) utils::CHECK_CUDA_EX(cudaStreamSynchronize(Cuda::stream()));  // the caches may still be read
+    kv_.clear();
+    kv_len_ = 0;
+}
+
 template <typename T>
 Gpt2<T>::~Gpt2() {
     for (cudaEvent_t ev : head_ev_)
@@ -300,6 +381,171 @@ std::unique_ptr<Gpt2<T>> Gpt2<T>::load(const std::string& path, bool training_en
     for (auto& b : model->transformer_blocks_) b->load(in);
     model->final_fc_->load(in);
     return model;
+}
+
+namespace {
+
+void put_i(std::ostream& out, int v) { out.write(reinterpret_cast<const char*>(&v), sizeof(v)); }
+int get_i(std::istream& in, const char* what) {
+    int v = 0;
+    in.read(reinterpret_cast<char*>(&v), sizeof(v));
+    if (!in) throw std::runtime_error(std::string("Gpt2: truncated file while reading ") + what);
+    return v;
+}
+// the raw bytes of a layer's name, as upstream writes them in front of each layer (no length)
+void put_name(std::ostream& out, const std::string& name) { out.write(name.data(), std::streamsize(name.size())); }
+void expect_name(std::istream& in, const std::string& name) {
+    std::string got(name.size(), '\0');
+    in.read(&got[0], std::streamsize(got.size()));
+    if (!in || got != name) throw std::runtime_error("Gpt2::load_upstream: expected the layer name '" + name + "'");
+}
+// skips one tensor record (int ndim, int shape[ndim], elements of elem_bytes each)
+void skip_tensor(std::istream& in, size_t elem_bytes) {
+    const int ndim = get_i(in, "a tensor header");
+    if (ndim < 0 || ndim > 8) throw std::runtime_error("Gpt2::load_upstream: bad tensor header");
+    size_t n = 1;
+    for (int d = 0; d < ndim; ++d) n *= size_t(std::max(0, get_i(in, "a tensor shape")));
+    in.seekg(std::streamoff(n * elem_bytes), std::ios::cur);
+    if (!in) throw std::runtime_error("Gpt2::load_upstream: truncated tensor");
+}
+struct HostInitOff {  // constructors leave the weights alone while this lives: they are about to be loaded
+    bool prev;
+    HostInitOff() : prev(fp8::policy().host_init) { fp8::policy().host_init = false; }
+    ~HostInitOff() { fp8::policy().host_init = prev; }
+};
+
+}  // namespace
+
+template <typename T>
+void Gpt2<T>::save_upstream(const std::string& path) const {
+    if (!this->tokenizer_) throw std::runtime_error("Gpt2::save_upstream: the model has no tokenizer (its state is part of the file)");
+    std::ofstream out(path, std::ios::binary);
+    if (!out) throw std::runtime_error("Failed to open file for saving Gpt2");
+    put_i(out, vocab_size_);
+    put_i(out, max_seq_len_);
+    put_i(out, int(transformer_blocks_.size()));
+    put_i(out, hidden_dim_);
+    this->tokenizer_->save(out);
+    put_name(out, token_embedding_->name());
+    token_embedding_->save(out);
+    put_name(out, positional_encoding_->name());
+    positional_encoding_->save(out);
+    for (const auto& b : transformer_blocks_) {
+        put_name(out, b->name());
+        b->save(out);
+    }
+    put_name(out, final_fc_->name());
+    final_fc_->save(out);
+}
+
+template <typename T>
+std::unique_ptr<Gpt2<T>> Gpt2<T>::load_upstream(const std::string& path, bool training_enabled) {
+    std::ifstream in(path, std::ios::binary);
+    if (!in) throw std::runtime_error("Failed to open file for loading Gpt2");
+    const int vocab = get_i(in, "the header"), max_seq = get_i(in, "the header");
+    const int layers = get_i(in, "the header"), hidden = get_i(in, "the header");
+    if (vocab <= 0 || max_seq <= 0 || layers < 0 || hidden <= 0) throw std::runtime_error("Gpt2::load_upstream: bad header");
+    auto tokenizer = std::make_shared<BpeTokenizer>(std::make_shared<VocabLoader>());
+    tokenizer->load(in);
+    // look ahead to the first block's header for the head count and the MLP width
+    const std::streampos body = in.tellg();
+    expect_name(in, "TokenEmbedding");
+    for (int k = 0; k < 3; ++k) get_i(in, "the embedding header");
+    skip_tensor(in, sizeof(T));
+    skip_tensor(in, sizeof(T));
+    expect_name(in, "PositionalEncoding");
+    int heads = 1, ffn = hidden;
+    if (layers > 0) {
+        expect_name(in, "TransformerBlock");
+        const int e = get_i(in, "a block header");
+        heads = get_i(in, "a block header");
+        ffn = get_i(in, "a block header");
+        if (e != hidden || heads <= 0 || ffn <= 0 || hidden % heads != 0)
+            throw std::runtime_error("Gpt2::load_upstream: the first block does not match the model header");
+    }
+    in.seekg(body);
+    std::unique_ptr<Gpt2<T>> model;
+    {
+        HostInitOff quiet;
+        model = std::make_unique<Gpt2<T>>(tokenizer, vocab, max_seq, layers, heads, hidden, ffn, static_cast<T>(1e-4),
+                                          static_cast<T>(0.9), static_cast<T>(0.98), static_cast<T>(1e-8), training_enabled);
+    }
+    expect_name(in, model->token_embedding_->name());
+    model->token_embedding_->load(in);
+    expect_name(in, model->positional_encoding_->name());
+    model->positional_encoding_->load(in);
+    for (auto& b : model->transformer_blocks_) {
+        expect_name(in, b->name());
+        b->load(in);
+    }
+    expect_name(in, model->final_fc_->name());
+    model->final_fc_->load(in);
+    return model;
+}
+
+// "DF8Q" 1 | vocab max_seq layers heads hidden ffn | embedding (weights, bias) | per block: ln1, ln2 parameters,
+// qkv, out, fc1, fc2 records | head record
+template <typename T>
+void Gpt2<T>::save_quantized(const std::string& path) {
+    std::ofstream out(path, std::ios::binary);
+    if (!out) throw std::runtime_error("Failed to open file for saving the quantised Gpt2");
+    out.write("DF8Q", 4);
+    put_i(out, 1);
+    put_i(out, vocab_size_);
+    put_i(out, max_seq_len_);
+    put_i(out, int(transformer_blocks_.size()));
+    put_i(out, transformer_blocks_.empty() ? 1 : transformer_blocks_[0]->attention().num_heads());
+    put_i(out, hidden_dim_);
+    put_i(out, transformer_blocks_.empty() ? hidden_dim_ : transformer_blocks_[0]->mlp_fc1().out_features());
+    token_embedding_->weights()->save(out);
+    token_embedding_->bias()->save(out);
+    for (auto& b : transformer_blocks_) {
+        for (tensor<T>* p : b->norm1().parameters()) p->save(out);
+        for (tensor<T>* p : b->norm2().parameters()) p->save(out);
+        b->attention().qkv_projection().export_quantized(out);
+        b->attention().out_projection().export_quantized(out);
+        b->mlp_fc1().export_quantized(out);
+        b->mlp_fc2().export_quantized(out);
+    }
+    final_fc_->export_quantized(out);
+    if (!out) throw std::runtime_error("Gpt2::save_quantized: write failed");
+}
+
+template <typename T>
+std::unique_ptr<Gpt2<T>> Gpt2<T>::load_quantized(const std::string& path) {
+    std::ifstream in(path, std::ios::binary);
+    if (!in) throw std::runtime_error("Failed to open file for loading the quantised Gpt2");
+    char magic[4] = {0, 0, 0, 0};
+    in.read(magic, 4);
+    if (!in || std::string(magic, 4) != "DF8Q" || get_i(in, "the version") != 1)
+        throw std::runtime_error("Gpt2::load_quantized: not a quantised Gpt2 file of version 1");
+    int cfg[6];
+    for (int& v : cfg) v = get_i(in, "the header");
+    if (cfg[0] <= 0 || cfg[1] <= 0 || cfg[2] < 0 || cfg[3] <= 0 || cfg[4] <= 0 || cfg[5] <= 0)
+        throw std::runtime_error("Gpt2::load_quantized: bad header");
+    std::unique_ptr<Gpt2<T>> model;
+    {
+        HostInitOff quiet;
+        model = std::make_unique<Gpt2<T>>(nullptr, cfg[0], cfg[1], cfg[2], cfg[3], cfg[4], cfg[5]);
+    }
+    model->token_embedding_->weights()->load(in);
+    model->token_embedding_->bias()->load(in);
+    for (auto& b : model->transformer_blocks_) {
+        for (tensor<T>* p : b->norm1().parameters()) p->load(in);
+        for (tensor<T>* p : b->norm2().parameters()) p->load(in);
+        b->attention().qkv_projection().import_quantized(in);
+        b->attention().out_projection().import_quantized(in);
+        b->mlp_fc1().import_quantized(in);
+        b->mlp_fc2().import_quantized(in);
+    }
+    model->final_fc_->import_quantized(in);
+    return model;
+}
+
+template <typename T>
+tensor<T> Gpt2<T>::forward_from_text(const std::string& text) {
+    if (!this->tokenizer_) throw std::runtime_error("Gpt2::forward_from_text: the model has no tokenizer");
+    return forward(this->tokenizer_->encode(text, true));
 }
 
 template class Gpt2<float>;

@@ -49,6 +49,22 @@ public:
 
     void save(const std::string& path) const override;
     static std::unique_ptr<Gpt2<T>> load(const std::string& path, bool training_enabled);
+    // Files in the layout upstream's Gpt2::save writes (dnn/models/gpt2.cu:144-166): vocab, max_seq_len, block
+    // count, hidden; the tokenizer's state; then, each preceded by the raw bytes of its name(), the token
+    // embedding, the (empty) positional encoding, every transformer block and the head.  Upstream's own loader
+    // cannot read these files back (:168-192 expects length-prefixed names, reads num_layers - 2 blocks and
+    // hard-codes 12 heads / 3072); load_upstream reads what save writes and takes heads and MLP width from the
+    // first block's header.  save_upstream needs a tokenizer (its state is part of the file).
+    static std::unique_ptr<Gpt2<T>> load_upstream(const std::string& path, bool training_enabled = false);
+    void save_upstream(const std::string& path) const;
+    // The quantise-once cache: every fully-connected layer as e4m3 codes + scale + bias, the embedding table and
+    // the LayerNorm parameters in fp32.  A model loaded from it never holds fp32 weight matrices on the device
+    // and computes bit for bit what the model that wrote it computes.
+    void save_quantized(const std::string& path);
+    static std::unique_ptr<Gpt2<T>> load_quantized(const std::string& path);
+    // Token ids of `text` (tokenizer's encode with BOS / EOS) through the token-based forward: hidden states
+    // [1,T,E].  (Upstream's NaturalLanguageModel::forward_from_text ends in Gpt2::forward(tensor), which throws.)
+    tensor<T> forward_from_text(const std::string& text);
 
     std::vector<BaseLayer*> layers() override;
 
@@ -71,6 +87,17 @@ public:
     // Every weight matrix <- N(0, std) generated on the device (fp8::fill_normal), biases <- 0; stream numbers
     // seed*1000 + 1, 2, ... in the order embedding, then per block qkv, out, fc1, fc2, then the head.
     void initialize_on_device(uint64_t seed, float std = 0.02f);
+
+    // ---- autoregressive decoding ----
+    // prefill(ids [B,T]) runs the forward on a prompt, keeps every layer's key / value codes in a cache sized for
+    // `max_len` positions (default: max_seq_len) and returns the logits of the LAST position, [B, V];
+    // decode_step(ids [B]) feeds one new token per sequence at the next position and returns its logits [B, V].
+    // The blocks' attention is causal from the prefill on (a cached key never sees a later query).  Every tensor
+    // that feeds a product is quantised per tensor, as in the batched forward: a step's tensors are [B, .].
+    tensor<T> prefill(const tensor<int>& ids, int max_len = 0, bool check_ids = true);
+    tensor<T> decode_step(const tensor<int>& next_ids, bool check_ids = true);
+    int decode_position() const { return kv_len_; }
+    void end_decode();
 
     // Layer streaming (README.md:212-220 sketches `layer->load_weights_to_gpu()`; no such code exists
     // upstream).  The e4m3 codes of every block's four weight matrices move to pinned host memory; the
@@ -113,6 +140,9 @@ private:
     fp8::Quantized head_q_;
     df8_streamer* streamer_ = nullptr;
     int stream_slots_ = 0;
+    std::vector<std::unique_ptr<typename MultiHeadAttentionLayer<T>::KvCache>> kv_;
+    int kv_len_ = 0;
+    tensor<T> last_rows_logits(const float* x, int B, int T_len);
     bool stage_timing_ = false;
     cudaEvent_t head_ev_[2] = {nullptr, nullptr};
     void head_gemm(int M, float* logits, int pitch);

@@ -167,6 +167,27 @@ df8_status df8_attention_fp8(const uint8_t* qkv_codes, df8_kind kind, const floa
                              int H, int D, int mask_mode, const float* mask, int mask_b, float* out,
                              float* out_amax, df8_stream stream);
 
+/* ---- autoregressive decode step ---------------------------------------------------------------
+ * Upstream's Gpt2::forward recomputes the whole sequence on every call (dnn/models/gpt2.cu:126-142); these calls
+ * add the step after a prefill, with upstream's attention semantics (multi_head_attention.cu:225-301; softmax
+ * p = exp(s - max) / (sum + 1e-6), softmax_layer.cu:26-81) restricted to the keys that exist.
+ *   df8_gemv_fp8_tn          out[B,N] = epi(X[B,K] . W[N,K]^T * dq + bias) for B <= 128 token rows: the product is
+ *                            bound by streaming W from HBM; flags as df8_gemm_fp8_tn (GELU, RESIDUAL, AMAX)
+ *   df8_kv_cache_append      the K and V codes of Tn new positions per sequence, taken from a QKV code buffer
+ *                            [B*Tn, 3E], go to rows t0 .. t0+Tn-1 of the caches [B, H, Tmax, D]; row_dq[t0 ..] receives
+ *                            the buffer's dequantisation factor (scale[1]): every QKV tensor has its own per-tensor
+ *                            scale, so the cache keeps one factor per position
+ *   df8_attention_decode_fp8 one query per sequence and head (the Q part of qkv_codes [B, 3E]) against the first
+ *                            n_keys cached positions -> out [B, E] fp32 (+ max|out|).  D = 64 or 128. */
+df8_status df8_gemv_fp8_tn(const uint8_t* x_codes, df8_kind kind_x, const float* scale_x, const uint8_t* w_codes,
+                           df8_kind kind_w, const float* scale_w, const float* bias, const float* residual, int B, int N,
+                           int K, int flags, float* out, float* out_amax, df8_stream stream);
+df8_status df8_kv_cache_append(const uint8_t* qkv_codes, const float* scale, int B, int Tn, int H, int D, int t0, int Tmax,
+                               uint8_t* k_cache, uint8_t* v_cache, float* row_dq, df8_stream stream);
+df8_status df8_attention_decode_fp8(const uint8_t* qkv_codes, df8_kind kind, const float* scale, const uint8_t* k_cache,
+                                    const uint8_t* v_cache, const float* row_dq, int B, int H, int D, int n_keys, int Tmax,
+                                    float* out, float* out_amax, df8_stream stream);
+
 /* ---- stand-alone masked softmax ------------------------------------------------------------
  * Replaces the launch of softmax_masked_kernel (dnn/layers/softmax_layer.cu:26-81, launched at
  * :154-167) for SoftmaxLayer::forward: x [B,H,T,T] fp32, optional additive mask [mask_b,1,T,T]

@@ -123,6 +123,33 @@ int dnn_block_forward(int B, int T, int E, int H, int F, const float* const* par
 int dnn_embedding_forward(int V, int E, int max_len, const float* table_h, const float* bias_h, const int32_t* ids_h,
                           int B, int T, int add_positions, float* y_h);
 
+/* ---- autoregressive decoding: Gpt2::prefill (prompt [B,T] -> logits of the last position [B, vocab], KV cache for
+ * max_len positions, 0 = max_seq_len), Gpt2::decode_step (one new token id per sequence -> logits [B, vocab]),
+ * Gpt2::end_decode.  Device pointers owned by the handle until its next call. ---- */
+int dnn_gpt2_prefill(dnn_gpt2* m, const int32_t* ids_d, int B, int T, int max_len, float** logits_d);
+int dnn_gpt2_decode_step(dnn_gpt2* m, const int32_t* next_ids_d, int B, int check_ids, float** logits_d);
+int dnn_gpt2_end_decode(dnn_gpt2* m);
+
+/* ---- checkpoint files ----
+ * save_upstream / load_upstream: the layout upstream's Gpt2::save writes (header, tokenizer state, then every layer
+ * preceded by the raw bytes of its name); a model needs a tokenizer to be saved that way
+ * (dnn_gpt2_create_with_tokenizer builds one from a vocabulary JSON file).
+ * save_quantized / load_quantized: the quantise-once cache (e4m3 codes + scales of every fully-connected layer, fp32
+ * embedding and LayerNorm parameters); a model loaded from it holds no fp32 weight matrices.
+ * forward_text: Gpt2::forward_from_text, hidden states [1,T,E] to the host, *tokens_h = T. */
+dnn_gpt2* dnn_gpt2_create_with_tokenizer(const char* vocab_json_path_h, int vocab, int max_seq_len, int layers, int heads,
+                                         int hidden, int ffn);
+int dnn_gpt2_save_upstream(dnn_gpt2* m, const char* path_h);
+dnn_gpt2* dnn_gpt2_load_upstream(const char* path_h);
+int dnn_gpt2_save_quantized(dnn_gpt2* m, const char* path_h);
+dnn_gpt2* dnn_gpt2_load_quantized(const char* path_h);
+int dnn_gpt2_forward_text(dnn_gpt2* m, const char* text_h, float* hidden_h, int cap_floats, int* tokens_h);
+/* Reads one record with the class's own load(), hands the parameter tensors back one after the other and writes
+ * the record again with the class's own save(): what = 0 tensor<float>, 1 FullyConnectedLayer, 2 LayerNormLayer,
+ * 3 TokenEmbedding, 4 TransformerBlock. */
+int dnn_file_roundtrip(int what, const char* in_path_h, const char* out_path_h, float* params_h, int cap_floats,
+                       int* count_h);
+
 /* ---- the text front end: dnn::BpeTokenizer over a dnn::VocabLoader (host-only).  The vocabulary comes from a JSON
  * file (a merges.txt beside it is picked up) or, when state_path_h is a non-empty string, from a binary state stream
  * as Tokenizer::save writes it.  encode returns the number of ids (-1 on error), decode the length of the text. ---- */

@@ -143,3 +143,64 @@ def gpt2_forward(p: dict, ids: np.ndarray, cfg: dict, act_kind: int = O.E4M3, w_
     if return_hidden:
         return x
     return _fc(x, p["final_fc.weight"], p["final_fc.bias"], act_kind, w_kind)
+
+
+# ---- autoregressive decoding with a key / value cache ---------------------------------------------------------
+#
+# The step after a prefill, restated with the same per-kernel oracle functions.  Upstream has no cache (its
+# Gpt2::forward recomputes the sequence, dnn/models/gpt2.cu:126-142); the semantics are those of its causal
+# attention (multi_head_attention.cu:225-301 with the -1e9 mask of its tests, softmax_layer.cu:26-81) on the keys
+# that exist.  Quantisation follows the 8-bit path: every tensor that feeds a product is quantised per tensor, so
+# the keys / values of a prefill share one scale and every later step has its own; the cache keeps codes and one
+# dequantisation factor per position.
+
+def _attend_cached(q, k, v, heads):
+    """q [B,E]; k, v [B,n,E] dequantised floats -> [B,E]: softmax(q.k/sqrt(D)) v per head, p = exp(s-max)/(sum+1e-6)."""
+    B, E = q.shape
+    D = E // heads
+    out = np.zeros((B, E), np.float64)
+    for b in range(B):
+        for h in range(heads):
+            sl = slice(h * D, (h + 1) * D)
+            s = (k[b, :, sl].astype(np.float64) @ q[b, sl].astype(np.float64)).astype(np.float32) / np.float32(np.sqrt(D))
+            p = np.exp(s - s.max()).astype(np.float32)
+            p = p / (p.sum(dtype=np.float32) + np.float32(1e-6))
+            out[b, sl] = p.astype(np.float64) @ v[b, :, sl].astype(np.float64)
+    return out.astype(np.float32)
+
+
+def decode_reference(p: dict, cfg: dict, ids: np.ndarray, next_ids: list, act_kind: int = O.E4M3, w_kind: int = O.E4M3,
+                     gelu: bool = True):
+    """Prefill on ids [B,T] (causal), then one decode step per entry of next_ids (each [B]).  Returns the list of
+    logits [B,V]: after the prefill (last position) and after every step."""
+    B, T = ids.shape
+    E, H, L = cfg["hidden"], cfg["heads"], cfg["layers"]
+    pe = O.pe_table(cfg["max_seq_len"], E)
+    x = O.embed_pe(ids, p["embedding.weight"], p["embedding.bias"], pe).reshape(B * T, E)
+    caches = []  # per layer: list of (codes [B, n, 3E], dq) pieces
+    for i in range(L):
+        t = block_trace(p, f"block{i}", x, B, T, H, act_kind, w_kind, gelu, O.MASK_CAUSAL)
+        caches.append([(t["qkv_q"][0].reshape(B, T, 3 * E), float(t["qkv_q"][1][1]))])
+        x = t["y"]
+    outs = [_fc(x.reshape(B, T, E)[:, -1, :], p["final_fc.weight"], p["final_fc.bias"], act_kind, w_kind)]
+    lut = np.array([O.code_value(c, act_kind) for c in range(256)], np.float32)
+    pos = T
+    for nxt in next_ids:
+        idn = np.asarray(nxt, np.int32).reshape(B, 1)
+        x = (p["embedding.weight"][idn[:, 0]] + p["embedding.bias"] + pe[pos]).astype(np.float32)
+        for i in range(L):
+            pre = f"block{i}"
+            h1 = O.layernorm(x, p[f"{pre}.ln1.gamma"], p[f"{pre}.ln1.beta"], 1e-5)
+            qkv = _fc(h1, p[f"{pre}.qkv.weight"], p[f"{pre}.qkv.bias"], act_kind, w_kind)
+            qc, qs = O.quantize(qkv, act_kind)
+            caches[i].append((qc.reshape(B, 1, 3 * E), float(qs[1])))
+            k = np.concatenate([lut[c[:, :, E:2 * E]] * np.float32(dq) for c, dq in caches[i]], axis=1)
+            v = np.concatenate([lut[c[:, :, 2 * E:]] * np.float32(dq) for c, dq in caches[i]], axis=1)
+            a = _attend_cached(lut[qc[:, :E]] * qs[1], k, v, H)
+            x1 = _fc(a, p[f"{pre}.out.weight"], p[f"{pre}.out.bias"], act_kind, w_kind, residual=x)
+            h2 = O.layernorm(x1, p[f"{pre}.ln2.gamma"], p[f"{pre}.ln2.beta"], 1e-5)
+            f = _fc(h2, p[f"{pre}.fc1.weight"], p[f"{pre}.fc1.bias"], act_kind, w_kind, gelu=gelu)
+            x = _fc(f, p[f"{pre}.fc2.weight"], p[f"{pre}.fc2.bias"], act_kind, w_kind, residual=x1)
+        outs.append(_fc(x, p["final_fc.weight"], p["final_fc.bias"], act_kind, w_kind))
+        pos += 1
+    return outs

@@ -1,0 +1,137 @@
+"""The autoregressive decode step: the skinny weight-streaming product (df8_gemv_fp8_tn), the key / value cache and
+the one-query attention against it, and Gpt2::prefill / decode_step against the oracle's restatement
+(oracle.gpt2_ref.decode_reference: the same per-tensor quantisation points, causal attention over the cached
+positions with upstream's softmax).  Bounds: one kernel on identical inputs within 1e-2 of the oracle (observed
+~1e-6 for the products, ~1e-5 for the attention); the chain of a small model within 5e-2."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(y, ref):
+    return float(np.abs(np.asarray(y, np.float64) - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+@pytest.mark.parametrize("B,N,K,flags,kinds", [(1, 768, 768, 0, (0, 0)), (8, 2304, 768, 4, (0, 0)), (5, 3072, 768, 5, (1, 0)),
+                                               (64, 768, 3072, 2, (0, 0)), (128, 1000, 256, 6, (0, 1)), (3, 50257, 768, 0, (0, 0)),
+                                               (16, 4096, 4096, 4, (0, 0))])
+def test_skinny_product_matches_the_gemm_and_the_oracle(df8, oracle, cuda, B, N, K, flags, kinds):
+    import torch
+
+    kx, kw = kinds
+    x = oracle.fill_normal(B * K, seed=B + N).reshape(B, K)
+    w = oracle.fill_normal(N * K, seed=N + K, std=0.03).reshape(N, K)
+    b = oracle.fill_normal(N, seed=3, std=0.1)
+    res = oracle.fill_normal(B * N, seed=4).reshape(B, N) if flags & 2 else None
+    xc, sx = oracle.quantize(x, kx)
+    wc, sw = oracle.quantize(w, kw)
+    t = lambda a: None if a is None else torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+    xcd, wcd, sxd, swd, bd, rd = t(xc), t(wc), t(sx), t(sw), t(b), t(res)
+    buf = torch.full((B * N + 64,), 777.0, device=cuda)
+    amax = torch.full((1,), -1.0, device=cuda)
+    df8.check(df8.lib().df8_gemv_fp8_tn(df8.ptr(xcd), kx, df8.ptr(sxd), df8.ptr(wcd), kw, df8.ptr(swd), df8.ptr(bd),
+                                        df8.ptr(rd), B, N, K, flags, df8.ptr(buf), df8.ptr(amax), df8.stream_ptr()))
+    want = torch.empty((B, N), device=cuda)
+    a2 = torch.zeros(1, device=cuda)
+    df8.gemm_fp8_tn(xcd, kx, sxd, wcd, kw, swd, bd, rd, B, N, K, flags, want, a2)
+    torch.cuda.synchronize()
+    got = buf[: B * N].reshape(B, N)
+    assert bool((buf[B * N:] == 777.0).all())
+    ref = oracle.fc_forward_fp8(xc, kx, sx[1], wc, kw, sw[1], b, res, flags & 3)
+    tol = 2e-3 if flags & 1 else 2e-4
+    assert rel_err(got.cpu().numpy(), ref) <= tol
+    assert rel_err(got.cpu().numpy(), want.cpu().numpy()) <= 1e-5  # the same products with the operands' roles swapped
+    if flags & 4:
+        assert amax.item() == got.abs().max().item()
+    else:
+        assert amax.item() == -1.0
+    assert df8.status_word() == (0, 0)
+
+
+@pytest.mark.parametrize("B,H,D,n_prefill,steps,kind", [(2, 3, 64, 37, 4, 0), (1, 2, 128, 300, 2, 0), (3, 2, 64, 1, 5, 1),
+                                                        (2, 12, 64, 1024, 1, 0)])
+def test_cache_and_one_query_attention(df8, oracle, cuda, B, H, D, n_prefill, steps, kind):
+    """Fill the cache from a prefill-sized QKV buffer, then append one position per step (each with its own scale)
+    and attend: against a float64 restatement with upstream's softmax on the dequantised rows."""
+    import torch
+
+    E, Tmax = H * D, n_prefill + steps
+    lib, st = df8.lib(), df8.stream_ptr()
+    lut = np.array([oracle.code_value(c, kind) for c in range(256)], np.float32)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+    kc = torch.zeros((B, H, Tmax, D), dtype=torch.uint8, device=cuda)
+    vc = torch.zeros_like(kc)
+    row_dq = torch.zeros(Tmax, device=cuda)
+    qkv0 = oracle.fill_normal(B * n_prefill * 3 * E, seed=1).reshape(B * n_prefill, 3 * E)
+    c0, s0 = oracle.quantize(qkv0, kind)
+    df8.check(lib.df8_kv_cache_append(df8.ptr(t(c0)), df8.ptr(t(s0)), B, n_prefill, H, D, 0, Tmax, df8.ptr(kc), df8.ptr(vc),
+                                      df8.ptr(row_dq), st))
+    pieces = [(c0.reshape(B, n_prefill, 3 * E), float(s0[1]))]
+    for step in range(steps):
+        n = n_prefill + step
+        qkv = oracle.fill_normal(B * 3 * E, seed=10 + step, std=1.0 + step).reshape(B, 3 * E)  # another scale each step
+        c, s = oracle.quantize(qkv, kind)
+        cd, sd = t(c), t(s)
+        df8.check(lib.df8_kv_cache_append(df8.ptr(cd), df8.ptr(sd), B, 1, H, D, n, Tmax, df8.ptr(kc), df8.ptr(vc),
+                                          df8.ptr(row_dq), st))
+        out = torch.full((B, E), float("nan"), device=cuda)
+        amax = torch.zeros(1, device=cuda)
+        df8.check(lib.df8_attention_decode_fp8(df8.ptr(cd), kind, df8.ptr(sd), df8.ptr(kc), df8.ptr(vc), df8.ptr(row_dq), B, H,
+                                               D, n + 1, Tmax, df8.ptr(out), df8.ptr(amax), st))
+        torch.cuda.synchronize()
+        pieces.append((c.reshape(B, 1, 3 * E), float(s[1])))
+        k = np.concatenate([lut[p[:, :, E:2 * E]] * np.float32(dq) for p, dq in pieces], axis=1)
+        v = np.concatenate([lut[p[:, :, 2 * E:]] * np.float32(dq) for p, dq in pieces], axis=1)
+        from oracle import gpt2_ref
+
+        ref = gpt2_ref._attend_cached(lut[c[:, :E]] * s[1], k, v, H)
+        y = out.cpu().numpy()
+        assert rel_err(y, ref) <= 1e-2 and rel_err(y, ref) <= 1e-4, rel_err(y, ref)
+        assert amax.item() == np.abs(y).max()
+    # the cache layout: position j of sequence b, head h
+    got_k = kc.cpu().numpy()
+    assert np.array_equal(got_k[:, :, :n_prefill, :],
+                          c0.reshape(B, n_prefill, 3, H, D)[:, :, 1].transpose(0, 2, 1, 3))
+    assert df8.status_word() == (0, 0)
+
+
+@pytest.mark.parametrize("act_kind", [0, 1])
+def test_prefill_and_decode_steps_against_the_oracle(df8, oracle, cuda, act_kind):
+    import torch
+    from oracle import gpt2_ref
+
+    cfg = dict(vocab=500, max_seq_len=64, layers=2, heads=2, hidden=128, ffn=256)
+    B, T, steps = 3, 20, 4
+    prm = gpt2_ref.make_params(cfg, seed=31, std=0.05)
+    ids = oracle.fill_token_ids(B * T, seed=5, vocab=500).reshape(B, T)
+    nxt = [oracle.fill_token_ids(B, seed=50 + i, vocab=500) for i in range(steps)]
+    lib = df8.dnn_lib()
+    df8.dnn_check(lib.dnn_init(0))
+    df8.dnn_check(lib.dnn_set_fp8_policy(0, act_kind))
+    try:
+        model = df8.Gpt2(**cfg)
+        model.load_params(prm)
+        got = [df8.device_view(torch, model.prefill(torch.from_numpy(ids).to(cuda)), (B, 500)).cpu().numpy()]
+        for n in nxt:
+            got.append(df8.device_view(torch, model.decode_step(torch.from_numpy(n).to(cuda)), (B, 500)).cpu().numpy())
+        # the cache is full after max_seq_len positions; a second prefill starts over
+        model.end_decode()
+        again = df8.device_view(torch, model.prefill(torch.from_numpy(ids).to(cuda), max_len=T + 1), (B, 500)).cpu().numpy()
+        model.decode_step(torch.from_numpy(nxt[0]).to(cuda))
+        with pytest.raises(df8.Df8Error, match="full"):
+            model.decode_step(torch.from_numpy(nxt[1]).to(cuda))
+        model.end_decode()
+        with pytest.raises(df8.Df8Error, match="prefill"):
+            model.decode_step(torch.from_numpy(nxt[0]).to(cuda))
+    finally:
+        df8.dnn_check(lib.dnn_set_fp8_policy(0, 0))
+    want = gpt2_ref.decode_reference(prm, cfg, ids, nxt, act_kind=act_kind)
+    f32 = gpt2_ref.decode_reference(prm, cfg, ids, nxt, act_kind=None, w_kind=None) if False else None
+    bound = 5e-2 if act_kind == 0 else 1.5e-1  # e5m2 keeps 2 mantissa bits: a flipped code is a 25 % step
+    for i, (g, w) in enumerate(zip(got, want)):
+        assert np.isfinite(g).all()
+        assert rel_err(g, w) <= bound, (i, rel_err(g, w))
+    assert np.array_equal(again, got[0])
+    assert df8.status_word() == (0, 0)
+    model.close()

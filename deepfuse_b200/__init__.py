@@ -565,6 +565,13 @@ class Comm:
             check(lib().df8_comm_destroy(self.h), "df8_comm_destroy")
             self.h = C.c_void_p(0)
 
+    def abort(self):
+        """df8_comm_abort: give the communicator up without talking to the peers (one of them is gone).  Close every
+        model built on it first; nothing of this rank may be in flight on it."""
+        if self.h:
+            h, self.h = self.h, C.c_void_p(0)
+            check(lib().df8_comm_abort(h), "df8_comm_abort")
+
 
 class Gpt2ColumnSharded:
     """dnn::Gpt2ColumnSharded<float> through the C harness: this rank's shard of a GPT-2 whose fully-connected

@@ -109,7 +109,7 @@ def test_gpt2_upstream_layout_round_trip(df8, dnn, oracle, cuda, tmp_path):
 
     vocab = {"<|endoftext|>": 0, "<|unk|>": 1, "<|pad|>": 2, "hello": 3, "world": 4, "h": 5, "i": 6}
     (tmp_path / "vocab.json").write_text(json.dumps(vocab))
-    cfg = dict(vocab=64, max_seq_len=32, layers=2, heads=2, hidden=64, ffn=128)
+    cfg = dict(vocab=64, max_seq_len=32, layers=2, heads=1, hidden=64, ffn=128)
     model = df8.Gpt2(**cfg, vocab_json=str(tmp_path / "vocab.json"))
     path = str(tmp_path / "gpt2_upstream.bin")
     model.save_file(path, "upstream")

@@ -95,14 +95,15 @@ struct GemmArgs {
 constexpr int kFusedCounters = 64;
 __device__ unsigned int g_gemm_grid_counter[kFusedCounters] = {};
 
-// TMA-store mode: two 32 x 32 fp32 boxes (4 KB each, 1024-byte aligned) per epilogue warp, then each warp's bias
-// slice (its four chunks of a 256-column tile)
+// TMA-store mode: two 128 x 32 fp32 boxes (16 KB each) per group of four epilogue warps, a 4 KB quarter per warp,
+// then each warp's bias slice (its four chunks of a 256-column tile)
 constexpr int kTmaBoxBytes = 32 * 32 * 4;
 constexpr int kTmaBiasFloatsPerWarp = 128;
 __host__ __device__ constexpr int tma_staging_bytes() { return kEpiWarps * (2 * kTmaBoxBytes + kTmaBiasFloatsPerWarp * 4); }
 
 __host__ __device__ constexpr int pair_staging_bytes(int mode) {
     return mode == kOutF32Tma ? tma_staging_bytes()
+           : mode == kOutF32T ? 0
            : is_direct(mode)  ? epi_warps(mode) * direct_staging_bytes(mode)
                               : kEpiWarps * kStagingFloatsPerWarp * 4;
 }
@@ -200,36 +201,55 @@ __device__ __forceinline__ void store_chunk_f32(const float* stg, int lane, int 
             const int rl = it * 4 + (lane >> 3);
             v[it] = *reinterpret_cast<const float4*>(stg + rl * 36 + cq);
         }
+        // flag tests outside the per-element loops (a uniform branch per group costs more than the group's arithmetic)
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
-            const int grow = row0 + it * 4 + (lane >> 3);
-            float4 o = v[it];
-            o.x = fmaf(o.x, alpha, b4.x);
-            o.y = fmaf(o.y, alpha, b4.y);
-            o.z = fmaf(o.z, alpha, b4.z);
-            o.w = fmaf(o.w, alpha, b4.w);
-            if (a.flags & 1) {
-                o.x = gelu_tanh(o.x);
-                o.y = gelu_tanh(o.y);
-                o.z = gelu_tanh(o.z);
-                o.w = gelu_tanh(o.w);
+            v[it].x = fmaf(v[it].x, alpha, b4.x);
+            v[it].y = fmaf(v[it].y, alpha, b4.y);
+            v[it].z = fmaf(v[it].z, alpha, b4.z);
+            v[it].w = fmaf(v[it].w, alpha, b4.w);
+        }
+        if (a.flags & 1) {
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                v[it].x = gelu_tanh(v[it].x);
+                v[it].y = gelu_tanh(v[it].y);
+                v[it].z = gelu_tanh(v[it].z);
+                v[it].w = gelu_tanh(v[it].w);
             }
-            if (a.flags & 2) {  // not unconditionally: x + 0 would turn -0 into +0
-                o.x += rs[it].x;
-                o.y += rs[it].y;
-                o.z += rs[it].z;
-                o.w += rs[it].w;
+        }
+        if (a.flags & 2) {  // not unconditionally: x + 0 would turn -0 into +0
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                v[it].x += rs[it].x;
+                v[it].y += rs[it].y;
+                v[it].z += rs[it].z;
+                v[it].w += rs[it].w;
             }
-            if (grow < a.M && col_ok) {
+        }
+        if (col_ok) {
+            const int row_first = row0 + (lane >> 3);
+            if (a.flags & 4) {
                 if (whole) {
-                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w))));
+#pragma unroll
+                    for (int it = 0; it < 8; ++it)
+                        if (row_first + it * 4 < a.M)
+                            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[it].x), fabsf(v[it].y)), fmaxf(fabsf(v[it].z), fabsf(v[it].w))));
                 } else {
-                    amax = fmaxf(amax, fabsf(o.x));
-                    if (gcol + 1 < a.N) amax = fmaxf(amax, fabsf(o.y));
-                    if (gcol + 2 < a.N) amax = fmaxf(amax, fabsf(o.z));
+#pragma unroll
+                    for (int it = 0; it < 8; ++it)
+                        if (row_first + it * 4 < a.M) {
+                            amax = fmaxf(amax, fabsf(v[it].x));
+                            if (gcol + 1 < a.N) amax = fmaxf(amax, fabsf(v[it].y));
+                            if (gcol + 2 < a.N) amax = fmaxf(amax, fabsf(v[it].z));
+                        }
                 }
-                *reinterpret_cast<float4*>(a.out + size_t(grow) * a.ldc + gcol) = o;
             }
+            float* dst = a.out + size_t(row_first) * a.ldc + gcol;
+            const size_t step = size_t(4) * a.ldc;
+#pragma unroll
+            for (int it = 0; it < 8; ++it)
+                if (row_first + it * 4 < a.M) *reinterpret_cast<float4*>(dst + it * step) = v[it];
         }
     } else {
         // any N (e.g. a vocabulary of 50257): 4-byte accesses, a warp covers 128 contiguous bytes of one row;
@@ -274,33 +294,61 @@ __device__ __forceinline__ void store_chunk_f32(const float* stg, int lane, int 
 // staging tile `stg` ([32 rows][PP pieces of 16 bytes], pieces XOR-swizzled so that neither these writes nor the
 // row-segment reads of store_staged_codes conflict); storing them from here, 16 bytes per row and instruction,
 // cost 6-10 us per pass (measured): the stores must leave as whole row segments.
+// One variant per (GELU, where the bias comes from): the flags are uniform over the launch, and tested inside the
+// per-element loop each test is a branch that costs more than the four elements' arithmetic.  Elements are reduced
+// or converted four at a time as before (sixteen epilogue warps leave no registers for a whole chunk of results).
+// BIAS: 0 none, 1 the warp's slice in shared memory, 2 global memory.
+template <int KIND, bool GELU, int BIAS>
+__device__ __forceinline__ void direct_chunk_body(const uint32_t (&r)[32], bool row_ok, int col0, const GemmArgs& a,
+                                                  float alpha, float out_q, float& amax, const float* sbias,
+                                                  uint32_t (&w)[8]) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float4 bq[4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {  // four reads in flight at a time
+            if constexpr (BIAS == 1) bq[g] = *reinterpret_cast<const float4*>(sbias + 16 * h + 4 * g);  // broadcast read
+            else if constexpr (BIAS == 2) bq[g] = __ldg(reinterpret_cast<const float4*>(a.bias + col0 + 16 * h + 4 * g));
+            else bq[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const int i = 16 * h + 4 * g;
+            float v0 = fmaf(__uint_as_float(r[i]), alpha, bq[g].x);
+            float v1 = fmaf(__uint_as_float(r[i + 1]), alpha, bq[g].y);
+            float v2 = fmaf(__uint_as_float(r[i + 2]), alpha, bq[g].z);
+            float v3 = fmaf(__uint_as_float(r[i + 3]), alpha, bq[g].w);
+            if constexpr (GELU) {
+                v0 = gelu_tanh(v0);
+                v1 = gelu_tanh(v1);
+                v2 = gelu_tanh(v2);
+                v3 = gelu_tanh(v3);
+            }
+            if constexpr (KIND < 0) {
+                if (row_ok) amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3))));
+            } else {
+                w[4 * h + g] = cvt_f32x4_to_fp8x4<KIND>(__fmul_rn(v0, out_q), __fmul_rn(v1, out_q), __fmul_rn(v2, out_q),
+                                                        __fmul_rn(v3, out_q));
+            }
+        }
+    }
+}
+
 template <int KIND, int PP = 2>
 __device__ __forceinline__ void direct_chunk(const uint32_t (&r)[32], int grow, int col0, const GemmArgs& a,
                                              float alpha, float out_q, float& amax, const float* sbias = nullptr,
                                              uint8_t* stg = nullptr, int j = 0) {
     const bool row_ok = grow < a.M;
     uint32_t w[8];
-#pragma unroll
-    for (int g = 0; g < 8; ++g) {
-        float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (sbias) b4 = *reinterpret_cast<const float4*>(sbias + 4 * g);  // broadcast read
-        else if (a.bias) b4 = __ldg(reinterpret_cast<const float4*>(a.bias + col0 + 4 * g));  // same address in every lane
-        float v0 = fmaf(__uint_as_float(r[4 * g]), alpha, b4.x);
-        float v1 = fmaf(__uint_as_float(r[4 * g + 1]), alpha, b4.y);
-        float v2 = fmaf(__uint_as_float(r[4 * g + 2]), alpha, b4.z);
-        float v3 = fmaf(__uint_as_float(r[4 * g + 3]), alpha, b4.w);
-        if (a.flags & 1) {
-            v0 = gelu_tanh(v0);
-            v1 = gelu_tanh(v1);
-            v2 = gelu_tanh(v2);
-            v3 = gelu_tanh(v3);
-        }
-        if constexpr (KIND < 0) {
-            if (row_ok) amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3))));
-        } else {
-            w[g] = cvt_f32x4_to_fp8x4<KIND>(__fmul_rn(v0, out_q), __fmul_rn(v1, out_q), __fmul_rn(v2, out_q),
-                                            __fmul_rn(v3, out_q));
-        }
+    const int bias_mode = sbias ? 1 : (a.bias ? 2 : 0);
+    if (a.flags & 1) {
+        if (bias_mode == 1) direct_chunk_body<KIND, true, 1>(r, row_ok, col0, a, alpha, out_q, amax, sbias, w);
+        else if (bias_mode == 2) direct_chunk_body<KIND, true, 2>(r, row_ok, col0, a, alpha, out_q, amax, sbias, w);
+        else direct_chunk_body<KIND, true, 0>(r, row_ok, col0, a, alpha, out_q, amax, sbias, w);
+    } else {
+        if (bias_mode == 1) direct_chunk_body<KIND, false, 1>(r, row_ok, col0, a, alpha, out_q, amax, sbias, w);
+        else if (bias_mode == 2) direct_chunk_body<KIND, false, 2>(r, row_ok, col0, a, alpha, out_q, amax, sbias, w);
+        else direct_chunk_body<KIND, false, 0>(r, row_ok, col0, a, alpha, out_q, amax, sbias, w);
     }
     if constexpr (KIND >= 0) {
         const int lane = threadIdx.x & 31;
@@ -330,21 +378,35 @@ __device__ __forceinline__ void store_staged_codes(const uint8_t* stg, int lane,
 
 // ---- fp32 output through TMA stores (kOutF32Tma) ----------------------------------------------------
 //
-// thread = row.  A 32 x 32 chunk is scaled, biased (and GELU'd) in registers and parked in one of the warp's two
-// 4 KB boxes in the 128-byte-swizzled layout of the output tensor map (16-byte piece c of row r at piece c ^ (r & 7):
-// neither these writes nor the copy engine's reads conflict); one cp.async.bulk.tensor store then takes the box
-// to global memory while the warp works on the next chunk.  The store clips rows >= M and columns >= N itself,
-// so edge tiles need no predication and the pitch padding of a row is never written.  Against the transpose
-// through shared memory + 128-bit st.global of the other fp32 modes this takes the global stores (and the
-// second pass over shared memory) off the warps: the vocabulary head, whose 1.6 GB of logits make the epilogue
-// the longest phase of a tile, is the case it is for.
-// `box_it` counts the warp's stores over the whole kernel (box box_it & 1 is the next one to fill).  Returns
-// false when the wait for the accumulators gave up.
+// thread = row.  A 32 x 32 chunk is scaled, biased (and GELU'd) in registers and parked in shared memory in the
+// 128-byte-swizzled layout of the output tensor map (16-byte piece c of row r at piece c ^ (r & 7): neither these
+// writes nor the copy engine's reads conflict); a cp.async.bulk.tensor store then takes it to global memory while
+// the warps work on the next chunk.  The store clips rows >= M and columns >= N itself, so edge tiles need no
+// predication and the pitch padding of a row is never written.  Against the transpose through shared memory +
+// 128-bit st.global of the other fp32 modes this takes the global stores (and the second pass over shared memory)
+// off the warps: the vocabulary head, whose 1.6 GB of logits make the epilogue the longest phase of a tile, is the
+// case it is for.
+// ONE store per 128 x 32 piece of the tile: the four warps that share a chunk index (one per TMEM lane quarter)
+// fill the four 4 KB quarters of one 16 KB box (the swizzle pattern repeats every 8 rows, so a quarter is laid out
+// like a box of its own), meet at a named barrier, and warp 0 of the group issues the store.  Before it arrives at
+// that barrier the issuing lane has waited for the group's previous store to be done READING its box, so every
+// warp that leaves the barrier may fill the other box at once: one barrier per chunk.  `box_it` counts the group's
+// stores over the whole kernel (box box_it & 1 is the next one to fill).  Returns false when the wait for the
+// accumulators gave up.
+// What the clock stamps of this epilogue showed on the vocabulary head (8192 x 50257 x 768, CTA pairs), and what
+// the code keeps from them: (1) every flag test inside the per-element loops is a uniform branch that costs more
+// than the arithmetic it guards (30 branches per chunk, ~1000 cycles against ~100 for the multiply-adds), so the
+// flags are tested once per chunk around whole loops, here and in the other epilogues; (2) the bias values are
+// read into registers in one go before the accumulators are waited for: read one by one between the stores they
+// cannot be moved up by the compiler (the stores might alias them) and each costs a shared-memory round trip of
+// ~150 cycles while the operand ring is busy; (3) the size of the store (4 KB per warp or 16 KB per group) made
+// no difference to the head, 16 KB helps at K = 4096 (1570 -> 1390 us for 8192 x 50257 x 4096).
 template <int BN, typename ReleaseFn>
-__device__ __forceinline__ bool epilogue_tile_f32_tma(const CUtensorMap* tma_out, const GemmArgs& args, uint8_t* boxes,
-                                                      float* sbias, uint32_t tfull_bar, uint32_t acc_phase,
-                                                      uint32_t taddr, int row0, int n0, int half, int lane,
-                                                      float alpha, float& amax, uint32_t& box_it, ReleaseFn release) {
+__device__ __forceinline__ bool epilogue_tile_f32_tma_group(const CUtensorMap* tma_out, const GemmArgs& args,
+                                                            uint8_t* group_boxes, float* sbias, uint32_t tfull_bar,
+                                                            uint32_t acc_phase, uint32_t taddr, int tile_row0, int q,
+                                                            int n0, int half, int lane, float alpha, float& amax,
+                                                            uint32_t& box_it, ReleaseFn release) {
     constexpr int kChunks = BN / 64;
     static_assert(kChunks * 32 <= kTmaBiasFloatsPerWarp, "bias slice");
 #pragma unroll
@@ -355,61 +417,73 @@ __device__ __forceinline__ bool epilogue_tile_f32_tma(const CUtensorMap* tma_out
     __syncwarp();
     if (!mbar_wait_bounded(tfull_bar, acc_phase)) return false;
     tc_fence_after_sync();
-    int nvalid = 0;
+    int nvalid = 0;  // the same for the four warps of a group
 #pragma unroll
     for (int j = 0; j < kChunks; ++j)
         if (n0 + 32 * (half + 2 * j) < args.N) nvalid = j + 1;
     uint32_t r[32];
     if (nvalid > 0) tmem_ld_32x32(taddr + 32 * half, r);
-    const bool row_ok = row0 + lane < args.M;
+    const bool row_ok = tile_row0 + q * 32 + lane < args.M;
     for (int j = 0; j < nvalid; ++j) {
         const int col0 = n0 + 32 * (half + 2 * j);
-        uint8_t* box = boxes + (box_it & 1u) * kTmaBoxBytes;
-        // the store that last read this box (two stores ago) must be done reading it
-        if (lane == 0) tma_store_wait_read<1>();
-        __syncwarp();
+        uint8_t* box = group_boxes + (box_it & 1u) * (4 * kTmaBoxBytes);
+        uint8_t* mine = box + q * kTmaBoxBytes;
+        // the chunk's bias values, all eight reads in flight at once and before the accumulators are waited for:
+        // read one by one between the stores below they cannot be moved up by the compiler (the stores might
+        // alias them) and each costs a full shared-memory round trip, ~150 cycles while the operand ring is busy
+        float4 bq[8];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) bq[g] = *reinterpret_cast<const float4*>(sbias + j * 32 + 4 * g);  // broadcast reads
         tmem_ld_wait();
-        const float* sb = sbias + j * 32;
-        const bool full = col0 + 32 <= args.N;
+        // flag tests stay outside the per-element loops: a uniform branch per four elements cost more than the
+        // arithmetic (30 branches per chunk, ~1000 cycles against ~100 for the multiply-adds)
+        float o[32];
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
-            const float4 b4 = *reinterpret_cast<const float4*>(sb + 4 * g);  // broadcast read
-            float4 o;
-            o.x = fmaf(__uint_as_float(r[4 * g]), alpha, b4.x);
-            o.y = fmaf(__uint_as_float(r[4 * g + 1]), alpha, b4.y);
-            o.z = fmaf(__uint_as_float(r[4 * g + 2]), alpha, b4.z);
-            o.w = fmaf(__uint_as_float(r[4 * g + 3]), alpha, b4.w);
-            if (args.flags & 1) {
-                o.x = gelu_tanh(o.x);
-                o.y = gelu_tanh(o.y);
-                o.z = gelu_tanh(o.z);
-                o.w = gelu_tanh(o.w);
-            }
-            if ((args.flags & 4) && row_ok) {
-                if (full) {
-                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w))));
-                } else {
-                    const int c = col0 + 4 * g;
-                    if (c < args.N) amax = fmaxf(amax, fabsf(o.x));
-                    if (c + 1 < args.N) amax = fmaxf(amax, fabsf(o.y));
-                    if (c + 2 < args.N) amax = fmaxf(amax, fabsf(o.z));
-                    if (c + 3 < args.N) amax = fmaxf(amax, fabsf(o.w));
-                }
-            }
-            *reinterpret_cast<float4*>(box + lane * 128 + ((g ^ (lane & 7)) << 4)) = o;
+            o[4 * g] = fmaf(__uint_as_float(r[4 * g]), alpha, bq[g].x);
+            o[4 * g + 1] = fmaf(__uint_as_float(r[4 * g + 1]), alpha, bq[g].y);
+            o[4 * g + 2] = fmaf(__uint_as_float(r[4 * g + 2]), alpha, bq[g].z);
+            o[4 * g + 3] = fmaf(__uint_as_float(r[4 * g + 3]), alpha, bq[g].w);
         }
+        if (args.flags & 1) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = gelu_tanh(o[i]);
+        }
+        if ((args.flags & 4) && row_ok) {
+            if (col0 + 32 <= args.N) {
+                float m0 = 0.f, m1 = 0.f;
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    m0 = fmaxf(m0, fabsf(o[i]));
+                    m1 = fmaxf(m1, fabsf(o[i + 1]));
+                }
+                amax = fmaxf(amax, fmaxf(m0, m1));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (col0 + i < args.N) amax = fmaxf(amax, fabsf(o[i]));
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+            *reinterpret_cast<float4*>(mine + lane * 128 + ((g ^ (lane & 7)) << 4)) =
+                make_float4(o[4 * g], o[4 * g + 1], o[4 * g + 2], o[4 * g + 3]);
         fence_proxy_async_smem();  // each lane's writes become visible to the copy engine
-        __syncwarp();
         if (j + 1 < nvalid) {
-            tmem_ld_32x32(taddr + 32 * (half + 2 * (j + 1)), r);  // in flight while the store is issued
+            tmem_ld_32x32(taddr + 32 * (half + 2 * (j + 1)), r);  // in flight across the barrier and the store
         } else {
             tc_fence_before_sync();  // the tile's last chunk is out of TMEM: hand the buffer back
+            __syncwarp();
             release();
         }
-        if (lane == 0) {
-            tma_store_2d(tma_out, smem_u32(box), col0, row0);
+        // the other box (filled next) was read by the store before last; the issuing lane alone knows its bulk groups
+        if (q == 0 && lane == 0) tma_store_wait_read<0>();
+        asm volatile("bar.sync %0, 128;" ::"r"(2 + half) : "memory");
+        if (q == 0 && lane == 0) {
+            tma_store_2d(tma_out, smem_u32(box), col0, tile_row0);
             tma_store_commit();
         }
+
         ++box_it;
     }
     if (nvalid == 0) {
@@ -428,11 +502,57 @@ __device__ __forceinline__ bool epilogue_tile_f32_tma(const CUtensorMap* tma_out
 // activations [batch, K]; the accumulator tile is [128 features, batch] and leaves transposed, out[b * ldc + f].
 // thread = feature row, so for a fixed batch column the 32 lanes of a warp write 32 consecutive floats.  bias is
 // indexed by the feature (row), the residual is read at the output's position.
-template <typename ReleaseFn>
+// One chunk: this lane's feature row, 32 consecutive token columns col0 .. col0 + 31.  Flag tests stay outside the
+// per-element loops (a uniform branch per element costs more than its arithmetic).
+__device__ __forceinline__ void store_chunk_transposed(const uint32_t (&r)[32], const GemmArgs& args, int grow, int col0,
+                                                       float alpha, float b, float& amax) {
+    float o[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) o[i] = fmaf(__uint_as_float(r[i]), alpha, b);
+    if (args.flags & 1) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = gelu_tanh(o[i]);
+    }
+    const size_t ldc = size_t(args.ldc);
+    float* dst = args.out + size_t(col0) * ldc + grow;
+    if (col0 + 32 <= args.N) {
+        if (args.flags & 2) {
+            const float* res = args.residual + size_t(col0) * ldc + grow;
+            float rs[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) rs[i] = res[i * ldc];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] += rs[i];
+        }
+        if (args.flags & 4) {
+            float m0 = 0.f, m1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                m0 = fmaxf(m0, fabsf(o[i]));
+                m1 = fmaxf(m1, fabsf(o[i + 1]));
+            }
+            amax = fmaxf(amax, fmaxf(m0, m1));
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) dst[i * ldc] = o[i];
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (col0 + i < args.N) {
+                float v = o[i];
+                if (args.flags & 2) v += args.residual[size_t(col0 + i) * ldc + grow];
+                if (args.flags & 4) amax = fmaxf(amax, fabsf(v));
+                dst[i * ldc] = v;
+            }
+        }
+    }
+}
+
+template <int BN, typename ReleaseFn>
 __device__ __forceinline__ bool epilogue_tile_f32_transposed(const GemmArgs& args, uint32_t tfull_bar, uint32_t acc_phase,
                                                              uint32_t taddr, int row0, int n0, int half, int lane,
                                                              float alpha, float& amax, ReleaseFn release) {
-    constexpr int kChunks = 2;  // BN = 128: chunks half, half + 2
+    constexpr int kChunks = BN / 64;  // this warp's chunks: half, half + 2, ...
     const int grow = row0 + lane;
     const bool row_ok = grow < args.M;
     const float b = (args.bias && row_ok) ? __ldg(args.bias + grow) : 0.f;
@@ -442,26 +562,24 @@ __device__ __forceinline__ bool epilogue_tile_f32_transposed(const GemmArgs& arg
 #pragma unroll
     for (int j = 0; j < kChunks; ++j)
         if (n0 + 32 * (half + 2 * j) < args.N) nvalid = j + 1;
-    for (int j = 0; j < nvalid; ++j) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + 32 * (half + 2 * j), r);
-        tmem_ld_wait();
-        if (j + 1 == nvalid) {
-            tc_fence_before_sync();
-            __syncwarp();
-            release();
-        }
-        const int col0 = n0 + 32 * (half + 2 * j);
+    // two register sets: the next chunk's accumulators are on their way while this one is stored
+    uint32_t ra[32], rb[32];
+    if (nvalid > 0) tmem_ld_32x32(taddr + 32 * half, ra);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const int col = col0 + i;  // batch row
-            if (col < args.N && row_ok) {
-                float v = fmaf(__uint_as_float(r[i]), alpha, b);
-                if (args.flags & 1) v = gelu_tanh(v);
-                const size_t at = size_t(col) * args.ldc + grow;
-                if (args.flags & 2) v += args.residual[at];
-                amax = fmaxf(amax, fabsf(v));
-                args.out[at] = v;
+    for (int j = 0; j < kChunks; ++j) {
+        if (j < nvalid) {
+            tmem_ld_wait();
+            if (j + 1 < nvalid) {
+                if (j & 1) tmem_ld_32x32(taddr + 32 * (half + 2 * (j + 1)), ra);
+                else tmem_ld_32x32(taddr + 32 * (half + 2 * (j + 1)), rb);
+            } else {
+                tc_fence_before_sync();
+                __syncwarp();
+                release();
+            }
+            if (row_ok) {
+                if (j & 1) store_chunk_transposed(rb, args, grow, n0 + 32 * (half + 2 * j), alpha, b, amax);
+                else store_chunk_transposed(ra, args, grow, n0 + 32 * (half + 2 * j), alpha, b, amax);
             }
         }
     }
@@ -753,22 +871,23 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
                 auto release = [&] {
                     if (lane == 0) mbar_arrive(smem_u32(tempty + buf));
                 };
-                if (!epilogue_tile_f32_transposed(args, smem_u32(tfull + buf), acc_phase, taddr, row0, n0, half, lane, alpha,
-                                                  amax, release)) {
+                if (!epilogue_tile_f32_transposed<BN>(args, smem_u32(tfull + buf), acc_phase, taddr, row0, n0, half, lane,
+                                                      alpha, amax, release)) {
                     if (lane == 0) record_timeout(args.status, 0x400u + buf);
                     break;
                 }
                 continue;
             }
             if constexpr (MODE == kOutF32Tma) {
-                uint8_t* boxes = reinterpret_cast<uint8_t*>(staging) + e * (2 * kTmaBoxBytes);
+                uint8_t* group_boxes = reinterpret_cast<uint8_t*>(staging) + half * (8 * kTmaBoxBytes);
                 float* sbias = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(staging) + kEpiWarps * 2 * kTmaBoxBytes) +
                                e * kTmaBiasFloatsPerWarp;
                 auto release = [&] {
                     if (lane == 0) mbar_arrive(smem_u32(tempty + buf));
                 };
-                if (!epilogue_tile_f32_tma<BN>(&tma_out, args, boxes, sbias, smem_u32(tfull + buf), acc_phase, taddr, row0,
-                                               n0, half, lane, alpha, amax, box_it, release)) {
+                const bool ok = epilogue_tile_f32_tma_group<BN>(&tma_out, args, group_boxes, sbias, smem_u32(tfull + buf), acc_phase,
+                                                                taddr, m0, q, n0, half, lane, alpha, amax, box_it, release);
+                if (!ok) {
                     if (lane == 0) record_timeout(args.status, 0x400u + buf);
                     break;
                 }
@@ -1060,13 +1179,23 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
             const int n0 = (tile / num_m) * BN;
             const int row0 = m0 + q * 32;
             const uint32_t taddr = tmem_base + buf * BN + lane_addr;
+            if constexpr (MODE == kOutF32T) {
+                auto release_buf = [&] { release(buf); };
+                if (!epilogue_tile_f32_transposed<BN>(args, smem_u32(tfull + buf), acc_phase, taddr, row0, n0, half, lane,
+                                                      alpha, amax, release_buf)) {
+                    if (lane == 0) record_timeout(args.status, 0x2400u + (rank << 4) + buf);
+                    break;
+                }
+                continue;
+            }
             if constexpr (MODE == kOutF32Tma) {  // as in the single-CTA kernel
-                uint8_t* boxes = reinterpret_cast<uint8_t*>(staging) + e * (2 * kTmaBoxBytes);
+                uint8_t* group_boxes = reinterpret_cast<uint8_t*>(staging) + half * (8 * kTmaBoxBytes);
                 float* sbias = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(staging) + kEpiWarps * 2 * kTmaBoxBytes) +
                                e * kTmaBiasFloatsPerWarp;
                 auto release_buf = [&] { release(buf); };
-                if (!epilogue_tile_f32_tma<BN>(&tma_out, args, boxes, sbias, smem_u32(tfull + buf), acc_phase, taddr, row0,
-                                               n0, half, lane, alpha, amax, box_it, release_buf)) {
+                const bool ok = epilogue_tile_f32_tma_group<BN>(&tma_out, args, group_boxes, sbias, smem_u32(tfull + buf), acc_phase,
+                                                                taddr, m0, q, n0, half, lane, alpha, amax, box_it, release_buf);
+                if (!ok) {
                     if (lane == 0) record_timeout(args.status, 0x2400u + (rank << 4) + buf);
                     break;
                 }
@@ -1181,7 +1310,7 @@ template <int BN, int MODE>
 struct PairCfg {
     // ring depth: the operand loads are latency-bound (~2.4 k cycles from issue to arrival with every SM loading),
     // so as many stages as fit beside the epilogue's staging
-    static constexpr int kStages = MODE == kOutF32Tma ? 4 : ((BN == 192 || MODE == kOutNone) ? 6 : 5);
+    static constexpr int kStages = MODE == kOutF32Tma ? 4 : ((BN == 192 || MODE == kOutNone || MODE == kOutF32T) ? 6 : 5);
     static constexpr int kSmemBytes = kStages * (BM * BK + (BN / 2) * BK) + pair_staging_bytes(MODE) + 256 + 1024;
     static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
@@ -1274,8 +1403,8 @@ df8_status launch_gemm_bn(bool wide, const CUtensorMap& ta, const CUtensorMap& t
         return wide ? launch_gemm<256, 4, MODE>(ta, tw, to, args, grid, st) : launch_gemm<128, 6, MODE>(ta, tw, to, args, grid, st);
     else if constexpr (MODE == kOutF32Tma)  // 256-column tiles only (run_gemm falls back to the st.global modes otherwise)
         return launch_gemm<256, 3, MODE>(ta, tw, to, args, grid, st);
-    else if constexpr (MODE == kOutF32T)  // the batch is the N dimension: one 128-column tile at most
-        return launch_gemm<128, 5, MODE>(ta, tw, to, args, grid, st);
+    else if constexpr (MODE == kOutF32T)  // no staging: the whole of shared memory is operand ring
+        return wide ? launch_gemm<256, 4, MODE>(ta, tw, to, args, grid, st) : launch_gemm<128, 6, MODE>(ta, tw, to, args, grid, st);
     else
         return wide ? launch_gemm<256, 3, MODE>(ta, tw, to, args, grid, st) : launch_gemm<128, 5, MODE>(ta, tw, to, args, grid, st);
 }
@@ -1291,7 +1420,7 @@ bool use_pair_kernel(int M, int N, int K, int sms, int mode) {
     // CTA and hides more of them.  Measured at 8192 x 50257 x 768 into rows of 50272 floats: 462 us with pairs,
     // 598 us without (and 578 us for dense rows of 50257 floats through 4-byte stores); at 8192 x 2304 x 768 the
     // single-CTA kernel stays ahead (30 against 33 us).
-    if (mode == kOutF32Tma && M >= 256 && N >= 256 && double(M) * double(N) * 4.0 >= 512e6) return true;
+    if ((mode == kOutF32Tma || mode == kOutF32T) && M >= 256 && N >= 256 && double(M) * double(N) * 4.0 >= 512e6) return true;
     // measured on B200 (M = 8192): 8192 x 8192 x 8192 runs at 2547 TFLOP/s with CTA pairs against 2245 without;
     // at K = 768 the epilogue dominates and the pairs' coupled accumulator hand-back costs a few per cent
     const long tiles2 = long((M + 255) / 256) * ((N + 255) / 256);
@@ -1329,10 +1458,10 @@ df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uin
                                     uint64_t(M) * uint64_t(slab_cols), BM, BK, 128);
     if (rc != DF8_OK) return rc;
     auto make_out_map = [&]() {
-        return make_tmap_2d_f32(&to, args.out, uint64_t(M), uint64_t(N), uint64_t(args.ldc) * sizeof(float), 32, 32, 128);
+        return make_tmap_2d_f32(&to, args.out, uint64_t(M), uint64_t(N), uint64_t(args.ldc) * sizeof(float), 128, 32, 128);
     };
     // CTA pairs on 256 x 256 tiles when the problem fills them (see gemm_fp8_tn_pair_kernel)
-    if (mode != kOutF32T && use_pair_kernel(M, N, K, sms, mode)) {
+    if (use_pair_kernel(M, N, K, sms, mode)) {
         if (want_fused) return DF8_OK;
         // Tile width of the fp32 modes, by the measured per-K-block and per-chunk costs (cycles): a K block is
         // bound by the tensor core (2 BN) or by the CTA's operand bytes arriving at ~50 bytes per cycle while the
@@ -1365,6 +1494,7 @@ df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uin
                 return bn2 == 192 ? launch_gemm_pair<192, kOutF32>(ta, tw, to, args, grid2, st)
                                   : launch_gemm_pair<256, kOutF32>(ta, tw, to, args, grid2, st);
             case kOutF32Tma: return launch_gemm_pair<256, kOutF32Tma>(ta, tw, to, args, grid2, st);
+            case kOutF32T: return launch_gemm_pair<256, kOutF32T>(ta, tw, to, args, grid2, st);
             case kOutE4M3: return launch_gemm_pair<256, kOutE4M3>(ta, tw, to, args, grid2, st);
             case kOutE5M2: return launch_gemm_pair<256, kOutE5M2>(ta, tw, to, args, grid2, st);
             default: return launch_gemm_pair<256, kOutNone>(ta, tw, to, args, grid2, st);
@@ -1388,7 +1518,7 @@ df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uin
         const double epilogue = (cost_mode == kOutF32Vec || cost_mode == kOutF32) ? 31.0 * bn : 0.0;
         return main_loop > epilogue ? main_loop : epilogue;
     };
-    const bool wide = mode != kOutF32T && N > 128 && rounds(256) * tile_cycles(256) <= rounds(128) * tile_cycles(128);
+    const bool wide = N > 128 && rounds(256) * tile_cycles(256) <= rounds(128) * tile_cycles(128);
     if (mode == kOutF32Tma && !wide) mode = tma_fallback;  // the TMA-store epilogue exists for 256-column tiles
     const int bn = wide ? 256 : 128;
     const long tiles = long((M + BM - 1) / BM) * ((N + bn - 1) / bn);
@@ -1470,6 +1600,26 @@ extern "C" df8_status df8_gemm_fp8_tn_ex(const uint8_t* a_codes, df8_kind kind_a
     args.K = K;
     args.ldc = ldc;
     args.flags = flags;
+    // Operands swapped (the kernel's A = the weight matrix, accumulator tile = [128 features, tokens], see kOutF32T):
+    // a lane then owns one output COLUMN and a warp's store instruction covers 128 contiguous bytes of one output row
+    // straight from registers, with no staging in shared memory and no alignment rule for N or ldc; results are bit
+    // for bit those of the other epilogues (tested).  Measured at M = 8192 (us, unswapped -> swapped): fp32 output
+    // with GELU 8192 x 3072 x 768: 66 -> 42; the out-projection and FC2 shapes within 1 us of each other; the
+    // vocabulary head into pitched rows 402 -> 430 (the TMA-store epilogue stays ahead there).  So: GELU outputs.
+    // DF8_GEMM_SWAP=0 / 1 in the environment forces the choice (profiling and tests).
+    {
+        const char* e = getenv("DF8_GEMM_SWAP");
+        bool swap = a_slabs == 1 && (flags & DF8_EPI_GELU) && M >= 256 && N >= 256;
+        if (e && e[0] == '0') swap = false;
+        if (e && e[0] == '1') swap = a_slabs == 1;
+        if (swap) {
+            args.scale_a = scale_w;
+            args.scale_w = scale_a;
+            args.M = N;
+            args.N = M;
+            return run_gemm(kOutF32T, w_codes, kind_w, a_codes, kind_a, args, st);
+        }
+    }
     // 128-bit accesses need rows that start on 16-byte boundaries (a pitch that is a multiple of 4 floats; N itself
     // may be anything: the last group of a row then reaches into the pitch padding)
     const bool pitch4 = ldc % 4 == 0 && ldc >= (N + 3) / 4 * 4;
@@ -1654,3 +1804,4 @@ extern "C" df8_status df8_gemv_fp8_tn(const uint8_t* x_codes, df8_kind kind_x, c
     args.flags = flags;
     return run_gemm(kOutF32T, w_codes, kind_w, x_codes, kind_x, args, st);
 }
+

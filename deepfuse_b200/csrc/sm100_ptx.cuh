@@ -213,9 +213,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_
 }
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-// arrive on an mbarrier that lives in another CTA of the cluster (address from map_to_cta)
+// arrive on an mbarrier that lives in another CTA of the cluster (address from map_to_cta).  CTA-scope release, as
+// for a local arrive: what the waiting thread needs from the arriving one here is that its tcgen05.ld have
+// completed (tcgen05.wait::ld + tcgen05.fence::before_thread_sync order those), not its global stores.  With
+// .release.cluster the arrive waited until every earlier store of the thread had been acknowledged, 1.5-5 k cycles
+// per tile in the epilogue warps of a pair's second CTA, and that CTA's epilogue set the pace of the kernel.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 // 2-D tiled load into THIS CTA's shared memory whose completion bytes are credited to an mbarrier that
 // may live in the pair's other CTA (`cluster_bar` from map_to_cta)

@@ -355,6 +355,48 @@ def test_gemm_tma_store_epilogue_equals_st_global(df8, oracle, cuda, monkeypatch
     assert df8.status_word() == (0, 0)
 
 
+@pytest.mark.parametrize("M,N,K,flags,ldc,pair", [(300, 1001, 256, 0, 1001, "auto"), (1000, 770, 768, 7, 772, "auto"),
+                                                  (513, 2304, 768, 5, 2304, "auto"), (640, 515, 1024, 6, 515, "1"),
+                                                  (2048, 3072, 768, 5, 3072, "1"), (100, 50, 64, 3, 50, "0")])
+def test_gemm_swapped_operands_equal_the_plain_form(df8, oracle, cuda, monkeypatch, M, N, K, flags, ldc, pair):
+    """DF8_GEMM_SWAP=1 computes the product with the operands' roles exchanged (weight rows on the accumulator's
+    lanes; a lane stores one output column straight from registers) and must give the plain form's output bit for
+    bit, with bias, GELU, residual and max|out|, on ragged shapes, dense and pitched rows, single CTAs and pairs;
+    and nothing may be written past the output or into the pitch padding."""
+    import torch
+
+    if pair != "auto":
+        monkeypatch.setenv("DF8_GEMM_PAIR", pair)
+    xc, sx = oracle.quantize(oracle.fill_normal(M * K, seed=M + 1).reshape(M, K), 0)
+    wc, sw = oracle.quantize(oracle.fill_normal(N * K, seed=N + 2, std=0.05).reshape(N, K), 1 if flags & 2 else 0)
+    kw = 1 if flags & 2 else 0
+    b = oracle.fill_normal(N, seed=3, std=0.1)
+    res = np.zeros((M, ldc), np.float32)
+    res[:, :N] = oracle.fill_normal(M * N, seed=4).reshape(M, N)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+    xcd, wcd, sxd, swd, bd, rd = t(xc), t(wc), t(sx), t(sw), t(b), (t(res) if flags & 2 else None)
+    outs = []
+    for swap in ("0", "1"):
+        monkeypatch.setenv("DF8_GEMM_SWAP", swap)
+        buf = torch.full((M * ldc + 256,), 777.0, device=cuda)
+        amax = torch.full((1,), -1.0, device=cuda)
+        df8.gemm_fp8_tn_ex(xcd, 0, sxd, 1, wcd, kw, swd, bd, rd, M, N, K, flags, buf, ldc, amax)
+        torch.cuda.synchronize()
+        full = buf[: M * ldc].reshape(M, ldc)
+        assert bool((buf[M * ldc:] == 777.0).all())
+        assert bool((full[:, (N + 3) // 4 * 4:] == 777.0).all())
+        outs.append((full[:, :N].clone(), amax.item()))
+    assert torch.equal(outs[0][0], outs[1][0]), f"{(outs[0][0] != outs[1][0]).sum().item()} elements differ"
+    assert outs[0][1] == outs[1][1]
+    y = outs[1][0].cpu().numpy()
+    ref = oracle.fc_forward_fp8(xc, 0, sx[1], wc, kw, sw[1], b, res[:, :N] if flags & 2 else None, flags & 3)
+    tol = 2e-3 if flags & 1 else TIGHT
+    assert rel_err(y, ref) <= tol, describe_mismatch(y, ref, tol)
+    if flags & 4:
+        assert outs[1][1] == np.abs(y).max()
+    assert df8.status_word() == (0, 0)
+
+
 @pytest.mark.parametrize("N,ldc", [(1001, 1024), (1003, 1004), (50257 // 8, 6304), (770, 772)])
 @pytest.mark.parametrize("flags", [0, 4, 6])
 def test_gemm_pitched_output_rows(df8, oracle, cuda, flags, N, ldc):

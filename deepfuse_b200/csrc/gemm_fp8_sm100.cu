@@ -294,61 +294,33 @@ __device__ __forceinline__ void store_chunk_f32(const float* stg, int lane, int 
 // staging tile `stg` ([32 rows][PP pieces of 16 bytes], pieces XOR-swizzled so that neither these writes nor the
 // row-segment reads of store_staged_codes conflict); storing them from here, 16 bytes per row and instruction,
 // cost 6-10 us per pass (measured): the stores must leave as whole row segments.
-// One variant per (GELU, where the bias comes from): the flags are uniform over the launch, and tested inside the
-// per-element loop each test is a branch that costs more than the four elements' arithmetic.  Elements are reduced
-// or converted four at a time as before (sixteen epilogue warps leave no registers for a whole chunk of results).
-// BIAS: 0 none, 1 the warp's slice in shared memory, 2 global memory.
-template <int KIND, bool GELU, int BIAS>
-__device__ __forceinline__ void direct_chunk_body(const uint32_t (&r)[32], bool row_ok, int col0, const GemmArgs& a,
-                                                  float alpha, float out_q, float& amax, const float* sbias,
-                                                  uint32_t (&w)[8]) {
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        float4 bq[4];
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {  // four reads in flight at a time
-            if constexpr (BIAS == 1) bq[g] = *reinterpret_cast<const float4*>(sbias + 16 * h + 4 * g);  // broadcast read
-            else if constexpr (BIAS == 2) bq[g] = __ldg(reinterpret_cast<const float4*>(a.bias + col0 + 16 * h + 4 * g));
-            else bq[g] = make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-            const int i = 16 * h + 4 * g;
-            float v0 = fmaf(__uint_as_float(r[i]), alpha, bq[g].x);
-            float v1 = fmaf(__uint_as_float(r[i + 1]), alpha, bq[g].y);
-            float v2 = fmaf(__uint_as_float(r[i + 2]), alpha, bq[g].z);
-            float v3 = fmaf(__uint_as_float(r[i + 3]), alpha, bq[g].w);
-            if constexpr (GELU) {
-                v0 = gelu_tanh(v0);
-                v1 = gelu_tanh(v1);
-                v2 = gelu_tanh(v2);
-                v3 = gelu_tanh(v3);
-            }
-            if constexpr (KIND < 0) {
-                if (row_ok) amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3))));
-            } else {
-                w[4 * h + g] = cvt_f32x4_to_fp8x4<KIND>(__fmul_rn(v0, out_q), __fmul_rn(v1, out_q), __fmul_rn(v2, out_q),
-                                                        __fmul_rn(v3, out_q));
-            }
-        }
-    }
-}
-
 template <int KIND, int PP = 2>
 __device__ __forceinline__ void direct_chunk(const uint32_t (&r)[32], int grow, int col0, const GemmArgs& a,
                                              float alpha, float out_q, float& amax, const float* sbias = nullptr,
                                              uint8_t* stg = nullptr, int j = 0) {
     const bool row_ok = grow < a.M;
     uint32_t w[8];
-    const int bias_mode = sbias ? 1 : (a.bias ? 2 : 0);
-    if (a.flags & 1) {
-        if (bias_mode == 1) direct_chunk_body<KIND, true, 1>(r, row_ok, col0, a, alpha, out_q, amax, sbias, w);
-        else if (bias_mode == 2) direct_chunk_body<KIND, true, 2>(r, row_ok, col0, a, alpha, out_q, amax, sbias, w);
-        else direct_chunk_body<KIND, true, 0>(r, row_ok, col0, a, alpha, out_q, amax, sbias, w);
-    } else {
-        if (bias_mode == 1) direct_chunk_body<KIND, false, 1>(r, row_ok, col0, a, alpha, out_q, amax, sbias, w);
-        else if (bias_mode == 2) direct_chunk_body<KIND, false, 2>(r, row_ok, col0, a, alpha, out_q, amax, sbias, w);
-        else direct_chunk_body<KIND, false, 0>(r, row_ok, col0, a, alpha, out_q, amax, sbias, w);
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (sbias) b4 = *reinterpret_cast<const float4*>(sbias + 4 * g);  // broadcast read
+        else if (a.bias) b4 = __ldg(reinterpret_cast<const float4*>(a.bias + col0 + 4 * g));  // same address in every lane
+        float v0 = fmaf(__uint_as_float(r[4 * g]), alpha, b4.x);
+        float v1 = fmaf(__uint_as_float(r[4 * g + 1]), alpha, b4.y);
+        float v2 = fmaf(__uint_as_float(r[4 * g + 2]), alpha, b4.z);
+        float v3 = fmaf(__uint_as_float(r[4 * g + 3]), alpha, b4.w);
+        if (a.flags & 1) {
+            v0 = gelu_tanh(v0);
+            v1 = gelu_tanh(v1);
+            v2 = gelu_tanh(v2);
+            v3 = gelu_tanh(v3);
+        }
+        if constexpr (KIND < 0) {
+            if (row_ok) amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3))));
+        } else {
+            w[g] = cvt_f32x4_to_fp8x4<KIND>(__fmul_rn(v0, out_q), __fmul_rn(v1, out_q), __fmul_rn(v2, out_q),
+                                            __fmul_rn(v3, out_q));
+        }
     }
     if constexpr (KIND >= 0) {
         const int lane = threadIdx.x & 31;
@@ -1600,16 +1572,27 @@ extern "C" df8_status df8_gemm_fp8_tn_ex(const uint8_t* a_codes, df8_kind kind_a
     args.K = K;
     args.ldc = ldc;
     args.flags = flags;
+    // 128-bit accesses need rows that start on 16-byte boundaries (a pitch that is a multiple of 4 floats; N itself
+    // may be anything: the last group of a row then reaches into the pitch padding)
+    const bool pitch4 = ldc % 4 == 0 && ldc >= (N + 3) / 4 * 4;
+    const bool vec4 = pitch4 && aligned16(out) && (!bias || aligned16(bias)) &&
+                      (!(flags & DF8_EPI_RESIDUAL) || aligned16(residual));
+    const int st_mode = vec4 ? kOutF32Vec : kOutF32;
+    // without a residual to read, rows that start on 16-byte boundaries leave through TMA stores
+    const bool tma = pitch4 && aligned16(out) && !(flags & DF8_EPI_RESIDUAL);
     // Operands swapped (the kernel's A = the weight matrix, accumulator tile = [128 features, tokens], see kOutF32T):
     // a lane then owns one output COLUMN and a warp's store instruction covers 128 contiguous bytes of one output row
     // straight from registers, with no staging in shared memory and no alignment rule for N or ldc; results are bit
-    // for bit those of the other epilogues (tested).  Measured at M = 8192 (us, unswapped -> swapped): fp32 output
-    // with GELU 8192 x 3072 x 768: 66 -> 42; the out-projection and FC2 shapes within 1 us of each other; the
-    // vocabulary head into pitched rows 402 -> 430 (the TMA-store epilogue stays ahead there).  So: GELU outputs.
+    // for bit those of the other epilogues (tested).  Measured at M = 8192, each shape alone (us, plain -> swapped):
+    // fp32 output with GELU 8192 x 3072 x 768: 68 -> 40; out-projection 768 x 768 with residual 17.6 -> 15.7; FC2
+    // 768 x 3072: 35.8 -> 35.0; 8192 x 8192 x 8192: 450 -> 413; QKV-shaped 2304 x 768: the same; the vocabulary head
+    // into pitched rows (TMA stores) 394 -> 417, into dense rows of 50257 floats 565 -> 615.  Inside the GPT-2 small
+    // forward, though, the swapped out-projection and FC2 made the pass SLOWER (3.435 against 3.346 ms, two runs
+    // each), so only the case with the large margin takes this path by itself: GELU outputs.
     // DF8_GEMM_SWAP=0 / 1 in the environment forces the choice (profiling and tests).
     {
         const char* e = getenv("DF8_GEMM_SWAP");
-        bool swap = a_slabs == 1 && (flags & DF8_EPI_GELU) && M >= 256 && N >= 256;
+        bool swap = a_slabs == 1 && (flags & DF8_EPI_GELU) && M >= 256 && N >= 256 && double(M) * double(N) * 4.0 < 512e6;
         if (e && e[0] == '0') swap = false;
         if (e && e[0] == '1') swap = a_slabs == 1;
         if (swap) {
@@ -1620,14 +1603,6 @@ extern "C" df8_status df8_gemm_fp8_tn_ex(const uint8_t* a_codes, df8_kind kind_a
             return run_gemm(kOutF32T, w_codes, kind_w, a_codes, kind_a, args, st);
         }
     }
-    // 128-bit accesses need rows that start on 16-byte boundaries (a pitch that is a multiple of 4 floats; N itself
-    // may be anything: the last group of a row then reaches into the pitch padding)
-    const bool pitch4 = ldc % 4 == 0 && ldc >= (N + 3) / 4 * 4;
-    const bool vec4 = pitch4 && aligned16(out) && (!bias || aligned16(bias)) &&
-                      (!(flags & DF8_EPI_RESIDUAL) || aligned16(residual));
-    const int st_mode = vec4 ? kOutF32Vec : kOutF32;
-    // without a residual to read, rows that start on 16-byte boundaries leave through TMA stores
-    const bool tma = pitch4 && aligned16(out) && !(flags & DF8_EPI_RESIDUAL);
     return run_gemm(tma ? kOutF32Tma : st_mode, a_codes, kind_a, w_codes, kind_w, args, st, nullptr, a_slabs, st_mode);
 }
 

@@ -664,7 +664,7 @@ class Gpt2Workload:
         peak = 2.0 * peaks["bf16_tflops"]
         wbytes = M * N * 4
         write_roof_ms = wbytes / (peaks["hbm_gbs"] * 1e9) * 1e3
-        return {"kernel": "gemm_fp8_tn_kernel (vocabulary head)", "bound": "tensor", "achieved": round(tf, 1),
+        return {"kernel": "gemm_fp8_tn_pair_kernel (vocabulary head, CTA pairs, TMA-store epilogue)", "bound": "tensor", "achieved": round(tf, 1),
                 "peak": peak, "peak_source": peaks["source"] + " bf16 burst x2 (fp8 dense); the launch runs at full clock "
                                                                 "inside a forward of a few ms",
                 "unit": "TFLOP/s", "frac": round(tf / peak, 4),
@@ -675,8 +675,8 @@ class Gpt2Workload:
                 "hbm_write_roof": {"bytes": wbytes, "ms_at_peak": round(write_roof_ms, 4), "peak_gbs": peaks["hbm_gbs"],
                                    "achieved_gbs": round(wbytes / ms / 1e6, 1), "frac": round(write_roof_ms / ms, 4)},
                 # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this launch at batch 8 x 1024
-                # (profiles/gemm_fp8_tn_kernel_head_8192x50257x768.md), scaled by the rows
-                "traffic": round((68.0e6 + 1.605e9) * M / 8192) if c["hidden"] == 768 else None,
+                # (profiles/gemm_fp8_tn_pair_kernel_head_8192x50257x768.md), scaled by the rows
+                "traffic": round((61.2e6 + 1.588e9) * M / 8192) if c["hidden"] == 768 else None,
                 "model_flops_per_token": gpt2_flops_per_token(c, self.T)}
 
     def cpu_sample(self, orc, step=0):

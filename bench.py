@@ -993,7 +993,8 @@ def run_ours(args, rank, world, local_rank):
         if rank == 0:
             for key, fn in (("gemm_tflops", lambda: gemm_sweep(torch, df8, dev, peaks)),
                             ("quant_gbs", lambda: quant_sweep(torch, df8, dev, peaks)),
-                            ("decode", lambda: decode_report(torch, df8, dev, peaks))):
+                            ("decode", lambda: decode_report(torch, df8, dev, peaks)),
+                            ("cross_entropy", lambda: cross_entropy_report(torch, df8, dev, peaks))):
                 try:
                     sec[key] = fn()
                 except Exception as e:  # a secondary figure must not take the line down
@@ -1089,6 +1090,49 @@ def decode_report(torch, df8, dev, peaks, batch=32, prompt=128, steps=64):
                 "device_wait_status": list(df8.status_word())}
     finally:
         model.close()
+
+
+def cross_entropy_report(torch, df8, dev, peaks, rows=8192, classes=50257):
+    """Softmax cross-entropy on the head's logits (df8_cross_entropy_f32 / _grad_f32): per-row loss from pitched
+    fp32 logits and class indices, and the gradient.  HBM-bound: the logits cross HBM once per call (the second and
+    third pass over a row find it in L2), the gradient is written once."""
+    import ctypes as C
+
+    from deepfuse_b200 import synthetic
+
+    pitch = (classes + 31) // 32 * 32
+    logits = torch.randn((rows, pitch), device=dev)
+    idx = torch.from_numpy(synthetic.fill_token_ids(rows, seed=3, vocab=classes)).to(dev)
+    row_loss = torch.empty(rows, device=dev)
+    grad = torch.empty((rows, classes), device=dev)
+    lib, st = df8.lib(), df8.stream_ptr()
+
+    def timeit(fn, iters=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    ms_loss = timeit(lambda: df8.check(lib.df8_cross_entropy_f32(df8.ptr(logits), pitch, None, 0, df8.ptr(idx), rows, classes,
+                                                                 df8.ptr(row_loss), st)))
+    ms_grad = timeit(lambda: df8.check(lib.df8_cross_entropy_grad_f32(df8.ptr(logits), pitch, None, 0, df8.ptr(idx), rows,
+                                                                      classes, df8.ptr(grad), classes, st)))
+    bad = C.c_uint(0)
+    df8.check(lib.df8_cross_entropy_bad_indices(C.byref(bad), 1))
+    b_loss, b_grad = rows * classes * 4, 2 * rows * classes * 4
+    return {"unit": "GB/s", "peak": peaks["hbm_gbs"], "peak_source": peaks["source"] + " copy bandwidth",
+            "shape": [rows, classes], "row_pitch": pitch, "targets": "class indices",
+            "loss": {"ms": round(ms_loss, 4), "algorithmic_bytes": b_loss, "gbs": round(b_loss / ms_loss / 1e6, 1),
+                     "frac": round(b_loss / ms_loss / 1e6 / peaks["hbm_gbs"], 4)},
+            "gradient": {"ms": round(ms_grad, 4), "algorithmic_bytes": b_grad, "gbs": round(b_grad / ms_grad / 1e6, 1),
+                         "frac": round(b_grad / ms_grad / 1e6 / peaks["hbm_gbs"], 4)},
+            "mean_row_loss": round(float(row_loss.mean().item()), 4), "bad_indices": bad.value}
 
 
 def secondary_forward(torch, df8, dev, rank, world, comm, make, timed, barrier, max_over_ranks, steps=5, warmup=3):

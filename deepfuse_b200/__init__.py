@@ -45,6 +45,9 @@ _SIGNATURES = {
     "df8_gemm_fp8_tn_amax_ex": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "df8_gemm_fp8_tn_codes_ex": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     "df8_gemv_fp8_tn": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp],
+    "df8_cross_entropy_f32": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp],
+    "df8_cross_entropy_grad_f32": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _i, _vp],
+    "df8_cross_entropy_bad_indices": [_vp, _i],
     "df8_kv_cache_append": [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     "df8_attention_decode_fp8": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp],
     "df8_layernorm_f32": [_vp, _i, _i, _vp, _vp, _f, _vp, _vp, _vp],
@@ -263,6 +266,7 @@ _DNN_SIGNATURES = {
     "dnn_tokenizer_encode": [C.c_char_p, C.c_char_p, C.c_char_p, _i, _vp, _i],
     "dnn_tokenizer_decode": [C.c_char_p, C.c_char_p, _vp, _i, _i, _vp, _i],
     "dnn_tokenizer_save": [C.c_char_p, C.c_char_p],
+    "dnn_cross_entropy": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp],
     "dnn_gpt2_prefill": [_vp, _vp, _i, _i, _i, _vp],
     "dnn_gpt2_decode_step": [_vp, _vp, _i, _i, _vp],
     "dnn_gpt2_end_decode": [_vp],

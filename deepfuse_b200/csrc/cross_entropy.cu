@@ -1,0 +1,172 @@
+// Softmax cross-entropy on fp32 logits: per-row loss and the gradient with respect to the logits.
+//
+// Replaces the launches of cross_entropy_log_softmax_kernel and cross_entropy_gradient_logit_kernel
+// (dnn/losses/cross_entropy.cu:12-74, :77-139, launched at :147-153 and :181-187), same math:
+//   loss_i  = -sum_j t_ij * (x_ij - max_i - log(sum_j exp(x_ij - max_i) + 1e-7))
+//   grad_ij = exp(x_ij - max_i) / (sum_j exp(x_ij - max_i) + 1e-7) - t_ij
+// Upstream gives one THREAD a whole row (three serial loops over the classes, 50257 for the GPT-2 head) and wants
+// the targets as a dense one-hot matrix the size of the logits.  Here one CTA owns a row: maximum, then the sum of
+// exponentials, then the target term, each a strided pass with warp-shuffle + shared-memory reductions; the second and
+// third pass find the row (200 KB at 50257 classes) in L2, so the logits cross HBM once.  Targets come either as
+// upstream's dense matrix or as one class index per row (no one-hot matrix is ever built: that alone is as many
+// bytes as the logits).  Rows may be pitched (the row pitch of Gpt2::forward_logits_pitched).
+// HBM-bound: 4 B per logit for the loss, 8 B per logit (+4 with dense targets) for the gradient.
+#include "df8_internal.cuh"
+
+namespace df8 {
+namespace {
+
+constexpr int kCeThreads = 256;
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+    v = warp_max(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = red[lane < kCeThreads / 32 ? lane : 0];
+    r = warp_max(r);
+    __syncthreads();
+    return r;
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = lane < kCeThreads / 32 ? red[lane] : 0.f;
+    r = warp_sum(r);
+    __syncthreads();
+    return r;
+}
+
+// VEC: rows start on 16-byte boundaries (base aligned, pitch a multiple of 4 floats): 128-bit loads over the whole
+// groups of a row, the up-to-three loose floats at its end one by one.
+template <bool GRAD, bool VEC>
+__global__ void __launch_bounds__(kCeThreads)
+cross_entropy_kernel(const float* __restrict__ logits, long ld, const float* __restrict__ targets, long ldt,
+                     const int* __restrict__ target_idx, int rows, int C, float* __restrict__ row_loss,
+                     float* __restrict__ grad, long ldg, unsigned int* __restrict__ bad_index) {
+    __shared__ float red[kCeThreads / 32];
+    griddep_launch_dependents();
+    griddep_wait();
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float* x = logits + size_t(row) * ld;
+        const int c4 = VEC ? C >> 2 : 0;
+        // ---- maximum ----
+        float mx = -INFINITY;
+        if (VEC) {
+            const float4* x4 = reinterpret_cast<const float4*>(x);
+            for (int i = threadIdx.x; i < c4; i += kCeThreads) {
+                const float4 v = x4[i];
+                mx = fmaxf(mx, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+            }
+        }
+        for (int i = 4 * c4 + threadIdx.x; i < C; i += kCeThreads) mx = fmaxf(mx, x[i]);
+        mx = block_max(mx, red);
+        // ---- sum of exponentials (the row comes from L2 now) ----
+        float s = 0.f;
+        if (VEC) {
+            const float4* x4 = reinterpret_cast<const float4*>(x);
+            for (int i = threadIdx.x; i < c4; i += kCeThreads) {
+                const float4 v = x4[i];
+                s += (expf(v.x - mx) + expf(v.y - mx)) + (expf(v.z - mx) + expf(v.w - mx));
+            }
+        }
+        for (int i = 4 * c4 + threadIdx.x; i < C; i += kCeThreads) s += expf(x[i] - mx);
+        s = block_sum(s, red);
+        int t = -1;
+        if (target_idx) {
+            t = target_idx[row];
+            if (t < 0 || t >= C) {  // recorded for the host (upstream's one-hot helper would write out of bounds)
+                if (threadIdx.x == 0 && bad_index) atomicAdd(bad_index, 1u);
+                t = -1;
+            }
+        }
+        if (!GRAD) {
+            const float lse = logf(s + 1e-7f);
+            float total = 0.f;
+            if (target_idx) {
+                if (threadIdx.x == 0 && t >= 0) total = x[t] - mx - lse;
+            } else {
+                const float* tr = targets + size_t(row) * ldt;
+                for (int i = threadIdx.x; i < C; i += kCeThreads) {
+                    const float tv = tr[i];
+                    if (tv != 0.f) total += tv * (x[i] - mx - lse);
+                }
+                total = block_sum(total, red);
+            }
+            if (threadIdx.x == 0) row_loss[row] = -total;
+        } else {
+            const float denom = s + 1e-7f;
+            float* g = grad + size_t(row) * ldg;
+            const float* tr = targets ? targets + size_t(row) * ldt : nullptr;
+            for (int i = threadIdx.x; i < C; i += kCeThreads) {
+                const float p = expf(x[i] - mx) / denom;
+                const float tv = tr ? tr[i] : (i == t ? 1.f : 0.f);
+                g[i] = p - tv;
+            }
+        }
+    }
+}
+
+__device__ unsigned int g_ce_bad_index = 0;
+
+df8_status run_ce(bool want_grad, const float* logits, int ld, const float* targets, int ldt, const int* target_idx, int rows,
+                  int classes, float* row_loss, float* grad, int ldg, cudaStream_t st) {
+    unsigned int* bad = nullptr;
+    DF8_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&bad), g_ce_bad_index));
+    const bool vec = aligned16(logits) && ld % 4 == 0;
+    const int sms = sm_count();
+    const int grid = rows < sms * 8 ? rows : sms * 8;
+    const dim3 g{unsigned(grid)}, b{kCeThreads};
+    if (want_grad) {
+        if (vec) (void)launch_kernel((cross_entropy_kernel<true, true>), g, b, 0, st, logits, long(ld), targets, long(ldt), target_idx, rows, classes, row_loss, grad, long(ldg), bad);
+        else (void)launch_kernel((cross_entropy_kernel<true, false>), g, b, 0, st, logits, long(ld), targets, long(ldt), target_idx, rows, classes, row_loss, grad, long(ldg), bad);
+    } else {
+        if (vec) (void)launch_kernel((cross_entropy_kernel<false, true>), g, b, 0, st, logits, long(ld), targets, long(ldt), target_idx, rows, classes, row_loss, grad, long(ldg), bad);
+        else (void)launch_kernel((cross_entropy_kernel<false, false>), g, b, 0, st, logits, long(ld), targets, long(ldt), target_idx, rows, classes, row_loss, grad, long(ldg), bad);
+    }
+    DF8_LAUNCH_CHECK("cross_entropy_kernel");
+    return DF8_OK;
+}
+
+}  // namespace
+}  // namespace df8
+
+using namespace df8;
+
+extern "C" df8_status df8_cross_entropy_f32(const float* logits_d, int ld, const float* targets_d, int ldt,
+                                            const int* target_idx_d, int rows, int classes, float* row_loss_d,
+                                            df8_stream stream) {
+    DF8_REQUIRE(rows >= 0 && classes > 0 && ld >= classes, "df8_cross_entropy_f32: bad shape rows=%d classes=%d ld=%d", rows,
+                classes, ld);
+    DF8_REQUIRE((targets_d != nullptr) != (target_idx_d != nullptr),
+                "df8_cross_entropy_f32: give dense targets or class indices, one of the two");
+    DF8_REQUIRE(!targets_d || ldt >= classes, "df8_cross_entropy_f32: ldt=%d is smaller than classes=%d", ldt, classes);
+    if (rows == 0) return DF8_OK;
+    DF8_REQUIRE(logits_d && row_loss_d, "df8_cross_entropy_f32: null buffer");
+    return run_ce(false, logits_d, ld, targets_d, ldt, target_idx_d, rows, classes, row_loss_d, nullptr, 0, as_stream(stream));
+}
+
+extern "C" df8_status df8_cross_entropy_grad_f32(const float* logits_d, int ld, const float* targets_d, int ldt,
+                                                 const int* target_idx_d, int rows, int classes, float* grad_d, int ldg,
+                                                 df8_stream stream) {
+    DF8_REQUIRE(rows >= 0 && classes > 0 && ld >= classes && ldg >= classes,
+                "df8_cross_entropy_grad_f32: bad shape rows=%d classes=%d ld=%d ldg=%d", rows, classes, ld, ldg);
+    DF8_REQUIRE((targets_d != nullptr) != (target_idx_d != nullptr),
+                "df8_cross_entropy_grad_f32: give dense targets or class indices, one of the two");
+    DF8_REQUIRE(!targets_d || ldt >= classes, "df8_cross_entropy_grad_f32: ldt=%d is smaller than classes=%d", ldt, classes);
+    if (rows == 0) return DF8_OK;
+    DF8_REQUIRE(logits_d && grad_d, "df8_cross_entropy_grad_f32: null buffer");
+    return run_ce(true, logits_d, ld, targets_d, ldt, target_idx_d, rows, classes, nullptr, grad_d, ldg, as_stream(stream));
+}
+
+extern "C" df8_status df8_cross_entropy_bad_indices(unsigned int* count_h, int reset) {
+    DF8_REQUIRE(count_h != nullptr, "df8_cross_entropy_bad_indices: null argument");
+    unsigned int* bad = nullptr;
+    DF8_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&bad), g_ce_bad_index));
+    DF8_CUDA_TRY(cudaMemcpy(count_h, bad, sizeof(unsigned int), cudaMemcpyDeviceToHost));
+    if (reset) DF8_CUDA_TRY(cudaMemset(bad, 0, sizeof(unsigned int)));
+    return DF8_OK;
+}

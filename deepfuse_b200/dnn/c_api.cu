@@ -15,6 +15,7 @@
 #include "dnn/layers/multi_head_attention.cuh"
 #include "dnn/layers/softmax_layer.cuh"
 #include "dnn/layers/transformer_block.cuh"
+#include "dnn/losses/cross_entropy.cuh"
 #include "dnn/models/gpt2.cuh"
 #include "dnn/models/gpt2_column_sharded.cuh"
 #include "dnn/tokens/bpe_tokenizer.cuh"
@@ -761,4 +762,43 @@ extern "C" int dnn_gpt2_decode_step(dnn_gpt2* m, const int32_t* next_ids_d, int 
 
 extern "C" int dnn_gpt2_end_decode(dnn_gpt2* m) {
     return guarded([&] { m->model->end_decode(); });
+}
+
+// ---- CrossEntropyLoss ---------------------------------------------------------------------------------------
+
+// logits_d [rows, pitch] (pitch == classes: dense); dense targets [rows, classes] or class indices [rows], one of the
+// two; mean loss to *loss_h and / or the gradient [rows, classes] to grad_d (either may be null)
+extern "C" int dnn_cross_entropy(const float* logits_d, int rows, int classes, int pitch, const float* targets_d,
+                                 const int32_t* idx_d, float* loss_h, float* grad_d) {
+    return guarded([&] {
+        dnn::CrossEntropyLoss<float> ce;
+        dnn::tensor<float> logits({rows, pitch});
+        dnn::utils::CHECK_CUDA_EX(cudaMemcpyAsync(logits.data(), logits_d, size_t(rows) * pitch * sizeof(float),
+                                             cudaMemcpyDeviceToDevice, dnn::Cuda::stream()));
+        std::unique_ptr<dnn::tensor<float>> tg;
+        std::unique_ptr<dnn::tensor<int>> idx;
+        if (targets_d) {
+            if (pitch != classes) throw std::runtime_error("dnn_cross_entropy: dense targets go with dense logits");
+            tg = std::make_unique<dnn::tensor<float>>(std::vector<int>{rows, classes});
+            dnn::utils::CHECK_CUDA_EX(cudaMemcpyAsync(tg->data(), targets_d, size_t(rows) * classes * sizeof(float),
+                                                 cudaMemcpyDeviceToDevice, dnn::Cuda::stream()));
+        } else {
+            idx = std::make_unique<dnn::tensor<int>>(std::vector<int>{rows});
+            dnn::utils::CHECK_CUDA_EX(cudaMemcpyAsync(idx->data(), idx_d, size_t(rows) * sizeof(int), cudaMemcpyDeviceToDevice,
+                                                 dnn::Cuda::stream()));
+        }
+        if (loss_h) {
+            if (tg) *loss_h = ce.compute(logits, *tg);
+            else if (pitch == classes) *loss_h = ce.compute(logits, *idx);
+            else *loss_h = ce.compute_pitched(logits, classes, *idx);
+        }
+        if (grad_d) {
+            dnn::tensor<float> g = tg ? ce.compute_gradient(logits, *tg)
+                                      : (pitch == classes ? ce.compute_gradient(logits, *idx)
+                                                          : ce.compute_gradient_pitched(logits, classes, *idx));
+            dnn::utils::CHECK_CUDA_EX(cudaMemcpyAsync(grad_d, g.data(), size_t(rows) * classes * sizeof(float),
+                                                 cudaMemcpyDeviceToDevice, dnn::Cuda::stream()));
+            dnn::utils::CHECK_CUDA_EX(cudaStreamSynchronize(dnn::Cuda::stream()));
+        }
+    });
 }

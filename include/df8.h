@@ -299,6 +299,23 @@ df8_status df8_streamer_release(df8_streamer* s, int layer, df8_stream compute_s
 df8_status df8_streamer_stats(df8_streamer* s, unsigned long long* bytes_uploaded_h, size_t* slot_bytes_h,
                               int* n_slots_h);
 
+/* ---- softmax cross-entropy on fp32 logits (training-side neighbour of the vocabulary head) -----------------
+ * Replaces cross_entropy_log_softmax_kernel / cross_entropy_gradient_logit_kernel
+ * (dnn/losses/cross_entropy.cu:12-74, 77-139; launches :147-153, :181-187) with upstream's arithmetic:
+ *   loss_i  = -sum_j t_ij (x_ij - max_i - log(sum_j exp(x_ij - max_i) + 1e-7))
+ *   grad_ij = exp(x_ij - max_i) / (sum_j exp(x_ij - max_i) + 1e-7) - t_ij
+ * Targets: either upstream's dense [rows, ldt] matrix (targets_d) or one class index per row (target_idx_d);
+ * exactly one of the two.  ld / ldt / ldg: row pitches in floats (>= classes), so the pitched logits of the head
+ * GEMM are read in place.  An index outside [0, classes) contributes nothing and is counted
+ * (df8_cross_entropy_bad_indices; the reduction of the row losses to their mean is the caller's, as upstream does
+ * it on the host, cross_entropy.cu:155-168). */
+df8_status df8_cross_entropy_f32(const float* logits_d, int ld, const float* targets_d, int ldt,
+                                 const int* target_idx_d, int rows, int classes, float* row_loss_d, df8_stream stream);
+df8_status df8_cross_entropy_grad_f32(const float* logits_d, int ld, const float* targets_d, int ldt,
+                                      const int* target_idx_d, int rows, int classes, float* grad_d, int ldg,
+                                      df8_stream stream);
+df8_status df8_cross_entropy_bad_indices(unsigned int* count_h, int reset);
+
 /* ---- collectives for the column-sharded fully-connected path --------------------------------------
  * Upstream has no communication backend: its multi-GPU mode runs independent replicas under a
  * tbb::parallel_for (apps/host-multi/main.cpp:157-181).  These calls wrap NCCL (bound at run time with

@@ -130,6 +130,12 @@ int dnn_gpt2_prefill(dnn_gpt2* m, const int32_t* ids_d, int B, int T, int max_le
 int dnn_gpt2_decode_step(dnn_gpt2* m, const int32_t* next_ids_d, int B, int check_ids, float** logits_d);
 int dnn_gpt2_end_decode(dnn_gpt2* m);
 
+/* ---- CrossEntropyLoss<float> (dnn/losses/cross_entropy.cuh:8-20): logits_d [rows, pitch] (pitch == classes: dense),
+ * dense targets [rows, classes] or class indices [rows] (one of the two); the mean loss goes to *loss_h, the
+ * gradient [rows, classes] to grad_d; either output may be null ---- */
+int dnn_cross_entropy(const float* logits_d, int rows, int classes, int pitch, const float* targets_d,
+                      const int32_t* idx_d, float* loss_h, float* grad_d);
+
 /* ---- checkpoint files ----
  * save_upstream / load_upstream: the layout upstream's Gpt2::save writes (header, tokenizer state, then every layer
  * preceded by the raw bytes of its name); a model needs a tokenizer to be saved that way

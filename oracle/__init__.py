@@ -147,6 +147,40 @@ def softmax_masked(x, mask=None) -> np.ndarray:
     return out
 
 
+def cross_entropy(logits, targets=None, target_idx=None):
+    """Upstream's softmax cross-entropy (dnn/losses/cross_entropy.cu:12-74 loss, :77-139 gradient, :142-170 the mean),
+    restated in float32 with its order of operations: per row the maximum, the sum of expf(x - max) accumulated class
+    by class, log(sum + 1e-7); loss_i = -sum_j t_ij (x_ij - max - lse); the mean is a float accumulated row by row;
+    grad_ij = expf(x_ij - max) / (sum + 1e-7) - t_ij.  Targets: dense [rows, C] or class indices [rows]
+    (upstream turns indices into a one-hot matrix first, utils/common.cuh:123).  Returns (mean loss, row losses, grad)."""
+    x = _f32(logits)
+    rows, Cn = x.shape
+    if (targets is None) == (target_idx is None):
+        raise ValueError("give dense targets or class indices, one of the two")
+    if targets is None:
+        t = np.zeros((rows, Cn), np.float32)
+        t[np.arange(rows), np.asarray(target_idx, np.int64)] = 1.0
+    else:
+        t = _f32(targets)
+    mx = x.max(axis=1, keepdims=True)
+    e = np.exp((x - mx).astype(np.float32)).astype(np.float32)
+    s = np.zeros(rows, np.float32)
+    for j in range(Cn):  # class by class, as the kernel's loop
+        s = (s + e[:, j]).astype(np.float32)
+    lse = np.log((s + np.float32(1e-7)).astype(np.float32)).astype(np.float32)
+    term = (t * ((x - mx).astype(np.float32) - lse[:, None]).astype(np.float32)).astype(np.float32)
+    total = np.zeros(rows, np.float32)
+    for j in range(Cn):
+        total = (total + term[:, j]).astype(np.float32)
+    row_loss = (-total).astype(np.float32)
+    acc = np.float32(0.0)
+    for v in row_loss:
+        acc = np.float32(acc + v)
+    mean = np.float32(acc / np.float32(rows))
+    grad = (e / (s + np.float32(1e-7))[:, None]).astype(np.float32) - t
+    return float(mean), row_loss, grad.astype(np.float32)
+
+
 def layernorm(x, gamma=None, beta=None, eps: float = 1e-5) -> np.ndarray:
     x = _f32(x)
     cols = x.shape[-1]

@@ -20,7 +20,7 @@ fi
 SRCS=(
     "$REF/dnn/core/tensor.cu" "$REF/dnn/core/tensor_transpose.cu" "$REF/dnn/core/cuda.cu" "$REF/dnn/core/device.cu"
     "$REF/dnn/layers/fully_connected_layer.cu" "$REF/dnn/layers/softmax_layer.cu" "$REF/dnn/layers/layer_norm_layer.cu"
-    "$REF/dnn/tokens/token_embedding.cu" "$REF/dnn/tokens/positional_encoding.cu"
+    "$REF/dnn/tokens/token_embedding.cu" "$REF/dnn/tokens/positional_encoding.cu" "$REF/dnn/losses/cross_entropy.cu"
     "$REF/dnn/utils/convert.cu" "$REF/dnn/utils/scalar.cu" "$REF/dnn/utils/infinity.cu"
     "$HERE/ref_wrap.cu"
 )

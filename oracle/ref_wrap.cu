@@ -2,13 +2,15 @@
 // (see ref_build.sh; nothing of upstream is copied into this repository).  TEST INFRASTRUCTURE ONLY: it lets a
 // GPU test check the CPU oracle against outputs of the reference implementation itself, for the layers whose
 // reference kernels are numerically sound: FullyConnectedLayer<float>::forward, SoftmaxLayer<float>::forward
-// (T <= 1024), LayerNormLayer<float>::forward on 2-D [rows, C <= 1024] inputs, TokenEmbedding + PositionalEncoding.
+// (T <= 1024), LayerNormLayer<float>::forward on 2-D [rows, C <= 1024] inputs, TokenEmbedding + PositionalEncoding,
+// CrossEntropyLoss<float> (dense targets and class indices).
 // Upstream's MultiHeadAttention / TransformerBlock / Gpt2 forward are not wrapped: they compute batch-head 0 only.
 #include <dnn/core/cuda.cuh>
 #include <dnn/core/tensor.cuh>
 #include <dnn/layers/fully_connected_layer.cuh>
 #include <dnn/layers/layer_norm_layer.cuh>
 #include <dnn/layers/softmax_layer.cuh>
+#include <dnn/losses/cross_entropy.cuh>
 #include <dnn/tokens/positional_encoding.cuh>
 #include <dnn/tokens/token_embedding.cuh>
 
@@ -160,3 +162,34 @@ extern "C" int ref_embedding_save(const char* path, int V, int E, int max_len, c
 // signed char the range \x7f-\x9f runs backwards) during static initialisation, i.e. a library that contains it
 // aborts the process that loads it.  Their on-disk layouts are taken from the source instead
 // (transformer_block.cuh:37-56, models/gpt2.cu:144-166).
+
+// CrossEntropyLoss<float>: host logits [B,C]; dense targets [B,C] or class indices [B] (one of the two);
+// mean loss to *loss and / or the gradient [B,C] to grad
+extern "C" int ref_cross_entropy(int B, int C, const float* logits, const float* targets, const int* idx, float* loss,
+                                 float* grad) {
+    return guarded([&] {
+        ensure_ctx();
+        dnn::CrossEntropyLoss<float> ce;
+        dnn::tensor<float> x({B, C});
+        x.upload(logits);
+        if (targets) {
+            dnn::tensor<float> t({B, C});
+            t.upload(targets);
+            if (loss) *loss = ce.compute(x, t);
+            if (grad) {
+                dnn::tensor<float> g = ce.compute_gradient(x, t);
+                cudaDeviceSynchronize();
+                g.download(grad);
+            }
+        } else {
+            dnn::tensor<int> t({B});
+            t.upload(idx);
+            if (loss) *loss = ce.compute(x, t);
+            if (grad) {
+                dnn::tensor<float> g = ce.compute_gradient(x, t);
+                cudaDeviceSynchronize();
+                g.download(grad);
+            }
+        }
+    });
+}

@@ -45,6 +45,10 @@ _SIGNATURES = {
     "df8_gemm_fp8_tn_amax_ex": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "df8_gemm_fp8_tn_codes_ex": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     "df8_gemv_fp8_tn": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp],
+    "df8_quantize_transpose_f32": [_vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp],
+    "df8_transpose_u8": [_vp, _i, _i, _i, _vp, _i, _vp],
+    "df8_colsum_f32": [_vp, _i, _i, _i, _vp, _vp, _vp],
+    "df8_colsum_partial_floats": [_i],
     "df8_cross_entropy_f32": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp],
     "df8_cross_entropy_grad_f32": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _i, _vp],
     "df8_cross_entropy_bad_indices": [_vp, _i],
@@ -253,6 +257,7 @@ _DNN_SIGNATURES = {
     "dnn_gpt2_streaming_traffic": [_vp, _vp, _vp],
     "dnn_gpt2_time_layer_uploads": [_vp, _vp],
     "dnn_fc_forward": [_i, _i, _vp, _vp, _vp, _i, _vp],
+    "dnn_fc_backward": [_i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp],
     "dnn_layernorm_forward": [_i, _i, _vp, _vp, _f, _vp, _vp],
     "dnn_softmax_forward": [_i, _i, _i, _vp, _vp, _i, _vp],
     "dnn_mha_forward": [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp],

@@ -292,6 +292,27 @@ extern "C" int dnn_fc_forward(int in_features, int out_features, const float* w_
     });
 }
 
+// FullyConnectedLayer with training enabled: forward on x_h, then backward on dy_h; all arrays on the host
+extern "C" int dnn_fc_backward(int in_features, int out_features, const float* w_h, const float* b_h, const float* x_h,
+                               int M, const float* dy_h, float* dx_h, float* dw_h, float* db_h) {
+    return guarded([&] {
+        dnn::FullyConnectedLayer<float> layer(in_features, out_features, true);
+        auto params = layer.parameters();
+        if (w_h) params[0]->upload(w_h);
+        if (b_h) params[1]->upload(b_h);
+        dnn::tensor<float> x({M, in_features});
+        x.upload(x_h);
+        (void)layer.forward(x);
+        dnn::tensor<float> dy({M, out_features});
+        dy.upload(dy_h);
+        dnn::tensor<float> dx = layer.backward(dy);
+        if (dx_h) dx.download(dx_h);
+        auto grads = layer.gradients();
+        if (dw_h) grads[0]->download(dw_h);
+        if (db_h) grads[1]->download(db_h);
+    });
+}
+
 extern "C" int dnn_layernorm_forward(int rows, int cols, const float* gamma_h, const float* beta_h, float eps,
                                      const float* x_h, float* y_h) {
     return guarded([&] {

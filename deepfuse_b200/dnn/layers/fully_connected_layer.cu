@@ -239,13 +239,66 @@ tensor<TT> FullyConnectedLayer<TT>::forward(const tensor<TT>& input) {
     return output;
 }
 
-// The backward pass (upstream fc_backward_* kernels, fully_connected_layer.cu:43-107) is training-side
-// and outside this build; the error upstream raises when no forward input was cached is kept.
+// Backward pass: upstream's dX = dY W, dW = dY^T X, db = sum_n dY (fc_backward_* kernels,
+// fully_connected_layer.cu:43-107, launched at :317-353) as two fp8 products and a column sum.  dY is quantised per
+// tensor to e5m2 (gradients want the range), X as in the forward pass (the policy's activation kind), W's cached e4m3
+// codes are used transposed; products accumulate in fp32; db is summed in fp32 from the unquantised dY.  Like
+// upstream the gradients overwrite grad_weights() / grad_bias(), and the cached forward input is required.
+// The contraction lengths (out_features for dX, the row count N for dW) are padded to a multiple of 16 with zero
+// codes.
 template <typename TT>
-tensor<TT> FullyConnectedLayer<TT>::backward(const tensor<TT>& /*grad_output*/) {
-    if (!input_cache_.has_value())
-        throw std::runtime_error("FullyConnectedLayer::backward: no cached input (training disabled or forward not run)");
-    throw std::runtime_error("FullyConnectedLayer::backward: the fp8 inference build has no backward pass");
+tensor<TT> FullyConnectedLayer<TT>::backward(const tensor<TT>& grad_output) {
+    if (!this->training_enabled_)
+        throw std::runtime_error("FullyConnectedLayer: backward called without input argument in stateless mode");
+    if (!input_cache_.has_value()) throw std::runtime_error("FullyConnectedLayer: input_cache_ not set for backward");
+    const tensor<TT>& x = *input_cache_;
+    const int in_f = in_features_, out_f = out_features_;
+    const int N = int(x.numel() / size_t(in_f));
+    if (grad_output.numel() != size_t(N) * size_t(out_f))
+        throw std::runtime_error("FullyConnectedLayer::backward: grad_output must be [N, out_features] for the cached input");
+    if (external_codes_) throw std::runtime_error("FullyConnectedLayer::backward: the weights of this layer are streamed codes");
+    std::vector<int> in_shape = x.shape();
+    tensor<TT> grad_input(in_shape);
+    if (N == 0) return grad_input;
+    const df8_stream st = fp8::stream();
+    const df8_kind gk = DF8_E5M2, ak = fp8::policy().activation_kind;
+    const int Kd = (out_f + 15) / 16 * 16;  // contraction length of dX
+    const int Kw = (N + 15) / 16 * 16;      // contraction length of dW
+    fp8::PassScope amax_slots;
+
+    // dY: one maximum, two layouts of the same codes
+    tensor<float> amax({2});
+    float* am_dy = fp8::amax_slot(amax.data());
+    utils::CHECK_DF8(df8_amax_f32(grad_output.data(), grad_output.numel(), am_dy, st));
+    tensor<float> dy_scale({2}), x_scale({2});
+    tensor<uint8_t> dy_t({out_f, Kw});  // dY^T [out, N]
+    utils::CHECK_DF8(df8_quantize_transpose_f32(grad_output.data(), N, out_f, gk, am_dy, dy_t.data(), Kw, dy_scale.data(), st));
+    tensor<uint8_t> dy_c({N, Kd});      // dY   [N, out] with the K padding
+    if (Kd == out_f) {
+        utils::CHECK_DF8(df8_quantize_f32(grad_output.data(), grad_output.numel(), gk, am_dy, dy_c.data(), dy_scale.data(), st));
+    } else {  // transposing the transposed codes back pads the rows with zero codes
+        utils::CHECK_DF8(df8_transpose_u8(dy_t.data(), out_f, N, Kw, dy_c.data(), Kd, st));
+    }
+
+    // dX = dY W: the weight codes transposed, [in, out]
+    const fp8::Quantized& w = quantized_weights();
+    tensor<uint8_t> w_t({in_f, Kd});
+    utils::CHECK_DF8(df8_transpose_u8(w.codes.data(), out_f, in_f, padded_in(), w_t.data(), Kd, st));
+    utils::CHECK_DF8(df8_gemm_fp8_tn(dy_c.data(), gk, dy_scale.data(), w_t.data(), w.kind, w.scale.data(), nullptr, nullptr, N,
+                                     in_f, Kd, 0, grad_input.data(), nullptr, st));
+
+    // dW = dY^T X
+    float* am_x = fp8::amax_slot(amax.data() + 1);
+    utils::CHECK_DF8(df8_amax_f32(x.data(), x.numel(), am_x, st));
+    tensor<uint8_t> x_t({in_f, Kw});
+    utils::CHECK_DF8(df8_quantize_transpose_f32(x.data(), N, in_f, ak, am_x, x_t.data(), Kw, x_scale.data(), st));
+    utils::CHECK_DF8(df8_gemm_fp8_tn(dy_t.data(), gk, dy_scale.data(), x_t.data(), ak, x_scale.data(), nullptr, nullptr, out_f,
+                                     in_f, Kw, 0, this->grad_weights_.data(), nullptr, st));
+
+    // db
+    tensor<float> partial({df8_colsum_partial_floats(out_f)});
+    utils::CHECK_DF8(df8_colsum_f32(grad_output.data(), N, out_f, out_f, partial.data(), this->grad_bias_.data(), st));
+    return grad_input;
 }
 
 // Stream layout shared with upstream (fully_connected_layer.cu:387-401): in, out, weights, bias.

@@ -299,6 +299,25 @@ df8_status df8_streamer_release(df8_streamer* s, int layer, df8_stream compute_s
 df8_status df8_streamer_stats(df8_streamer* s, unsigned long long* bytes_uploaded_h, size_t* slot_bytes_h,
                               int* n_slots_h);
 
+/* ---- operands of the fully-connected backward pass as fp8 products --------------------------------------
+ * Upstream: fc_backward_input / fc_backward_weights / fc_backward_bias (dnn/layers/fully_connected_layer.cu:43-107,
+ * launches :317-353): dX = dY W, dW = dY^T X, db = sum_n dY.  The two products run through df8_gemm_fp8_tn, which
+ * contracts over the contiguous dimension of both operands, so they need W^T [in, out], dY^T [out, N] and
+ * X^T [in, N] as codes:
+ *   df8_quantize_transpose_f32  fp32 [rows, cols] -> codes [cols, ld_t] (ld_t >= rows; columns rows .. ld_t-1 are
+ *                               written as zero codes: padding of the K dimension), scale from amax_in_d as in
+ *                               df8_quantize_f32, so the codes equal those of the untransposed tensor
+ *   df8_transpose_u8            codes [rows, ld_in] (cols used) -> [cols, ld_out], zero beyond `rows`
+ *   df8_colsum_f32              out_d[c] = sum_r x_d[r * ld + c]; partial_d: df8_colsum_partial_floats(cols) floats
+ *                               of scratch; fixed summation order (no atomics) */
+df8_status df8_quantize_transpose_f32(const float* x_d, int rows, int cols, df8_kind kind, const float* amax_in_d,
+                                      uint8_t* codes_t_d, int ld_t, float* scale_out_d, df8_stream stream);
+df8_status df8_transpose_u8(const uint8_t* in_d, int rows, int cols, int ld_in, uint8_t* out_d, int ld_out,
+                            df8_stream stream);
+df8_status df8_colsum_f32(const float* x_d, int rows, int cols, int ld, float* partial_d, float* out_d,
+                          df8_stream stream);
+int df8_colsum_partial_floats(int cols);
+
 /* ---- softmax cross-entropy on fp32 logits (training-side neighbour of the vocabulary head) -----------------
  * Replaces cross_entropy_log_softmax_kernel / cross_entropy_gradient_logit_kernel
  * (dnn/losses/cross_entropy.cu:12-74, 77-139; launches :147-153, :181-187) with upstream's arithmetic:

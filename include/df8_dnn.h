@@ -111,6 +111,10 @@ unsigned long long dnn_gpt2cs_bytes_pushed(dnn_gpt2cs* m);
 /* ---- single layers through their public forward(), host buffers in and out ---- */
 int dnn_fc_forward(int in_features, int out_features, const float* w_h, const float* b_h, const float* x_h, int M,
                    float* y_h);
+/* FullyConnectedLayer<float>(in, out, training_enabled = true): forward(x) then backward(dy)
+ * (fully_connected_layer.cu:216-356); dx [M, in], dw [out, in], db [out]; host arrays, outputs may be null */
+int dnn_fc_backward(int in_features, int out_features, const float* w_h, const float* b_h, const float* x_h, int M,
+                    const float* dy_h, float* dx_h, float* dw_h, float* db_h);
 int dnn_layernorm_forward(int rows, int cols, const float* gamma_h, const float* beta_h, float eps, const float* x_h,
                           float* y_h);
 int dnn_softmax_forward(int B, int H, int T, const float* x_h, const float* mask_h, int mask_b, float* y_h);

@@ -147,6 +147,30 @@ def softmax_masked(x, mask=None) -> np.ndarray:
     return out
 
 
+def fc_backward_f32(dy, x, w):
+    """Upstream's fully-connected backward in fp32 (dnn/layers/fully_connected_layer.cu:43-107): dX = dY W,
+    dW = dY^T X, db = sum_n dY, each a sequential fp32 sum in upstream; float64 accumulation here (the comparison
+    tolerances are far above the difference)."""
+    dy, x, w = _f32(dy), _f32(x), _f32(w)
+    dx = (dy.astype(np.float64) @ w.astype(np.float64)).astype(np.float32)
+    dw = (dy.astype(np.float64).T @ x.astype(np.float64)).astype(np.float32)
+    db = dy.astype(np.float64).sum(axis=0).astype(np.float32)
+    return dx, dw, db
+
+
+def fc_backward_fp8(dy, x, w, act_kind: int = E4M3, grad_kind: int = E5M2, w_kind: int = E4M3):
+    """The same through the 8-bit path: dY quantised per tensor to e5m2, X to the activation kind, W to e4m3; products of
+    the dequantised codes accumulated exactly; db from the unquantised dY."""
+    dy, x, w = _f32(dy), _f32(x), _f32(w)
+    dyc, dys = quantize(dy, grad_kind)
+    xc, xs = quantize(x, act_kind)
+    wc, ws = quantize(w, w_kind)
+    dyq = dequantize(dyc, grad_kind, dys[1]).astype(np.float64)
+    xq = dequantize(xc, act_kind, xs[1]).astype(np.float64)
+    wq = dequantize(wc, w_kind, ws[1]).astype(np.float64)
+    return (dyq @ wq).astype(np.float32), (dyq.T @ xq).astype(np.float32), dy.astype(np.float64).sum(axis=0).astype(np.float32)
+
+
 def cross_entropy(logits, targets=None, target_idx=None):
     """Upstream's softmax cross-entropy (dnn/losses/cross_entropy.cu:12-74 loss, :77-139 gradient, :142-170 the mean),
     restated in float32 with its order of operations: per row the maximum, the sum of expf(x - max) accumulated class

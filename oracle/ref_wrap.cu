@@ -193,3 +193,27 @@ extern "C" int ref_cross_entropy(int B, int C, const float* logits, const float*
         }
     });
 }
+
+
+// FullyConnectedLayer<float> with training enabled: forward(x), backward(dy); host arrays, outputs may be null
+extern "C" int ref_fc_backward(int in_f, int out_f, const float* w, const float* b, const float* x, int M, const float* dy,
+                               float* dx, float* dw, float* db) {
+    return guarded([&] {
+        ensure_ctx();
+        dnn::FullyConnectedLayer<float> layer(in_f, out_f, true);
+        auto p = layer.parameters();
+        p[0]->upload(w);
+        p[1]->upload(b);
+        dnn::tensor<float> in({M, in_f});
+        in.upload(x);
+        (void)layer.forward(in);
+        dnn::tensor<float> g({M, out_f});
+        g.upload(dy);
+        dnn::tensor<float> gi = layer.backward(g);
+        cudaDeviceSynchronize();
+        if (dx) gi.download(dx);
+        auto grads = layer.gradients();
+        if (dw) grads[0]->download(dw);
+        if (db) grads[1]->download(db);
+    });
+}

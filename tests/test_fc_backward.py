@@ -1,0 +1,126 @@
+"""Fully-connected backward as fp8 products: dX = dY W, dW = dY^T X, db = sum_n dY
+(upstream: fc_backward_input / _weights / _bias, dnn/layers/fully_connected_layer.cu:43-107).
+
+CPU: the fp32 restatement on a hand-checked case (upstream's tests hold no known answer for the backward beyond
+shapes: tests/layers/fully_connected_layer_test.cu:152-197 checks that gradients exist and are finite).
+GPU: the operand kernels (quantise + transpose, transpose of codes, column sums) bit for bit against numpy;
+FullyConnectedLayer::backward against the 8-bit oracle on identical inputs (<= 2e-4 of the tensor maximum for the
+products; db <= 1e-6) and against the fp32 backward (<= 5e-2); upstream's own layer, compiled from its sources,
+against the fp32 restatement."""
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+REF_LIB = Path(__file__).resolve().parent.parent / "oracle" / "_ref" / "libdnn_ref.so"
+p = lambda a: a.ctypes.data_as(C.c_void_p)
+
+
+def rel(y, ref):
+    return float(np.abs(np.asarray(y, np.float64) - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+def test_fp32_restatement_on_a_small_case(oracle):
+    dy = np.array([[1.0, -2.0], [0.5, 4.0]], np.float32)  # [N=2, out=2]
+    x = np.array([[1.0, 2.0, 3.5], [-1.0, 0.0, 2.0]], np.float32)  # [N, in=3]
+    w = np.array([[1.0, 0.0, -1.0], [1.75, 1.0, 0.5]], np.float32)  # [out, in]
+    dx, dw, db = oracle.fc_backward_f32(dy, x, w)
+    assert np.array_equal(dx, np.array([[-2.5, -2.0, -2.0], [7.5, 4.0, 1.5]], np.float32))
+    assert np.array_equal(dw, np.array([[0.5, 2.0, 4.5], [-6.0, -4.0, 1.0]], np.float32))
+    assert np.array_equal(db, np.array([1.5, 2.0], np.float32))
+    # the 8-bit form of values that the codes hold exactly (maxima 4, 3.5, 1.75: power-of-two scales) is the fp32 result
+    dx8, dw8, db8 = oracle.fc_backward_fp8(dy, x, w)
+    assert rel(dx8, dx) <= 1e-6 and rel(dw8, dw) <= 1e-6 and np.array_equal(db8, db)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,cols,ld,kind", [(64, 64, 64, 0), (100, 37, 112, 1), (1000, 768, 1008, 0), (33, 300, 48, 1)])
+def test_quantize_transpose_and_code_transpose(df8, oracle, cuda, rows, cols, ld, kind):
+    import torch
+
+    x = oracle.fill_normal_outliers(rows * cols, seed=rows + cols).reshape(rows, cols)
+    codes, scale = oracle.quantize(x, kind)
+    xd = torch.from_numpy(x).to(cuda)
+    amax = torch.zeros(1, device=cuda)
+    df8.amax_f32(xd, amax)
+    out = torch.full((cols * ld + 64,), 0xAB, dtype=torch.uint8, device=cuda)
+    sc = torch.zeros(2, device=cuda)
+    df8.check(df8.lib().df8_quantize_transpose_f32(df8.ptr(xd), rows, cols, kind, df8.ptr(amax), df8.ptr(out), ld, df8.ptr(sc),
+                                                   df8.stream_ptr()))
+    torch.cuda.synchronize()
+    got = out[: cols * ld].reshape(cols, ld).cpu().numpy()
+    assert np.array_equal(got[:, :rows], codes.reshape(rows, cols).T)
+    assert not got[:, rows:].any()  # the K padding is zero codes
+    assert bool((out[cols * ld:] == 0xAB).all())
+    assert np.array_equal(sc.cpu().numpy(), scale)
+    # codes -> transposed codes
+    cd = torch.from_numpy(codes.reshape(rows, cols)).to(cuda)
+    out2 = torch.full((cols * ld + 64,), 0xCD, dtype=torch.uint8, device=cuda)
+    df8.check(df8.lib().df8_transpose_u8(df8.ptr(cd), rows, cols, cols, df8.ptr(out2), ld, df8.stream_ptr()))
+    torch.cuda.synchronize()
+    assert torch.equal(out2[: cols * ld], out[: cols * ld]) and bool((out2[cols * ld:] == 0xCD).all())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,cols,ld", [(1, 1, 1), (777, 100, 104), (8192, 768, 768), (5, 3072, 3072)])
+def test_column_sums_are_exact_for_integers_and_repeatable(df8, cuda, rows, cols, ld):
+    import torch
+
+    g = torch.Generator(device="cpu").manual_seed(rows)
+    xi = torch.randint(-8, 9, (rows, ld), generator=g).float()
+    x = xi.to(cuda)
+    lib = df8.lib()
+    partial = torch.zeros(lib.df8_colsum_partial_floats(cols), device=cuda)
+    outs = []
+    for _ in range(2):
+        out = torch.full((cols + 8,), 55.0, device=cuda)
+        df8.check(lib.df8_colsum_f32(df8.ptr(x), rows, cols, ld, df8.ptr(partial), df8.ptr(out), df8.stream_ptr()))
+        torch.cuda.synchronize()
+        outs.append(out.clone())
+    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0][:cols].cpu(), xi[:, :cols].sum(dim=0)) and bool((outs[0][cols:] == 55.0).all())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K,N,act", [(64, 768, 3072, 0), (100, 100, 40, 0), (256, 3072, 768, 1), (1024, 768, 768, 0)])
+def test_fc_backward_matches_the_oracle(df8, oracle, cuda, M, K, N, act):
+    lib = df8.dnn_lib()
+    df8.dnn_check(lib.dnn_init(0))
+    df8.dnn_check(lib.dnn_set_fp8_policy(0, act))
+    try:
+        x = oracle.fill_normal(M * K, seed=M + 1).reshape(M, K)
+        w = oracle.fill_normal(N * K, seed=N + 2, std=0.05).reshape(N, K)
+        b = oracle.fill_normal(N, seed=3, std=0.1)
+        dy = oracle.fill_normal(M * N, seed=5, std=1e-3).reshape(M, N)  # gradients are small numbers
+        dx = np.zeros((M, K), np.float32)
+        dw = np.zeros((N, K), np.float32)
+        db = np.zeros(N, np.float32)
+        df8.dnn_check(lib.dnn_fc_backward(K, N, p(w), p(b), p(x), M, p(dy), p(dx), p(dw), p(db)), "dnn_fc_backward")
+    finally:
+        df8.dnn_check(lib.dnn_set_fp8_policy(0, 0))
+    qx, qw, qb = oracle.fc_backward_fp8(dy, x, w, act_kind=act)
+    fx, fw, fb = oracle.fc_backward_f32(dy, x, w)
+    assert rel(dx, qx) <= 2e-4 and rel(dw, qw) <= 2e-4, (rel(dx, qx), rel(dw, qw))
+    assert rel(db, qb) <= 1e-6
+    # against the unquantised backward: the bound stated for the fp32 comparison of the forward path
+    assert rel(dx, fx) <= 5e-2 and rel(dw, fw) <= 5e-2, (rel(dx, fx), rel(dw, fw))
+    assert df8.status_word() == (0, 0)
+
+
+@pytest.mark.gpu
+def test_fp32_restatement_matches_upstreams_backward(oracle, cuda):
+    if not REF_LIB.exists():
+        pytest.skip("oracle/_ref/libdnn_ref.so not built (needs the upstream sources at build time)")
+    ref = C.CDLL(str(REF_LIB))
+    if not hasattr(ref, "ref_fc_backward"):
+        pytest.skip("oracle/_ref/libdnn_ref.so predates the backward wrapper")
+    for M, K, N in ((8, 16, 4), (64, 300, 100)):
+        x = oracle.fill_normal(M * K, seed=M).reshape(M, K)
+        w = oracle.fill_normal(N * K, seed=N, std=0.05).reshape(N, K)
+        b = oracle.fill_normal(N, seed=3, std=0.1)
+        dy = oracle.fill_normal(M * N, seed=5).reshape(M, N)
+        dx, dw, db = np.zeros((M, K), np.float32), np.zeros((N, K), np.float32), np.zeros(N, np.float32)
+        assert ref.ref_fc_backward(K, N, p(w), p(b), p(x), M, p(dy), p(dx), p(dw), p(db)) == 0
+        fx, fw, fb = oracle.fc_backward_f32(dy, x, w)
+        assert rel(dx, fx) <= 1e-5 and rel(dw, fw) <= 1e-5 and rel(db, fb) <= 1e-5

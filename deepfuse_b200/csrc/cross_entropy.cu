@@ -16,15 +16,48 @@
 namespace df8 {
 namespace {
 
-constexpr int kCeThreads = 256;
+constexpr int kCeThreads = 1024;  // one CTA per row; few rows in flight (see run_ce)
 
-__device__ __forceinline__ float block_max(float v, float* red) {
-    v = warp_max(v);
+// running (maximum, sum of exp(x - maximum)) of the elements seen so far
+struct MaxSum {
+    float m, s;
+};
+__device__ __forceinline__ MaxSum merge(MaxSum a, MaxSum b) {
+    const float m = fmaxf(a.m, b.m);
+    if (m == -INFINITY) return MaxSum{m, 0.f};
+    return MaxSum{m, a.s * __expf(a.m - m) + b.s * __expf(b.m - m)};
+}
+__device__ __forceinline__ void absorb4(MaxSum& r, float4 v) {
+    const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+    if (m4 > r.m) {  // rare after the first few elements: rescale what has been summed
+        r.s *= __expf(r.m - m4);
+        r.m = m4;
+    }
+    r.s += (__expf(v.x - r.m) + __expf(v.y - r.m)) + (__expf(v.z - r.m) + __expf(v.w - r.m));
+}
+__device__ __forceinline__ void absorb1(MaxSum& r, float v) {
+    if (v > r.m) {
+        r.s *= __expf(r.m - v);
+        r.m = v;
+    }
+    r.s += __expf(v - r.m);
+}
+
+__device__ __forceinline__ MaxSum block_merge(MaxSum v, MaxSum* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        MaxSum other{__shfl_xor_sync(0xffffffffu, v.m, o), __shfl_xor_sync(0xffffffffu, v.s, o)};
+        v = merge(v, other);
+    }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) red[warp] = v;
     __syncthreads();
-    float r = red[lane < kCeThreads / 32 ? lane : 0];
-    r = warp_max(r);
+    MaxSum r = lane < kCeThreads / 32 ? red[lane] : MaxSum{-INFINITY, 0.f};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        MaxSum other{__shfl_xor_sync(0xffffffffu, r.m, o), __shfl_xor_sync(0xffffffffu, r.s, o)};
+        r = merge(r, other);
+    }
     __syncthreads();
     return r;
 }
@@ -40,41 +73,33 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return r;
 }
 
-// VEC: rows start on 16-byte boundaries (base aligned, pitch a multiple of 4 floats): 128-bit loads over the whole
-// groups of a row, the up-to-three loose floats at its end one by one.
+// One pass over the row gives the maximum and the sum of exponentials together (each thread keeps a running pair and
+// rescales its sum when its maximum grows; pairs are merged across the block): the logits cross HBM once for the
+// loss.  The gradient reads the row a second time, from L2: run_ce keeps the rows in flight (2 CTAs per SM) well
+// inside L2, where a grid of one CTA per row had 240 MB of rows in flight and read every row from HBM twice.
+// VEC: rows start on 16-byte boundaries (base aligned, pitch a multiple of 4 floats): 128-bit accesses over the
+// whole groups of a row, the up-to-three loose floats at its end one by one.
 template <bool GRAD, bool VEC>
 __global__ void __launch_bounds__(kCeThreads)
 cross_entropy_kernel(const float* __restrict__ logits, long ld, const float* __restrict__ targets, long ldt,
                      const int* __restrict__ target_idx, int rows, int C, float* __restrict__ row_loss,
                      float* __restrict__ grad, long ldg, unsigned int* __restrict__ bad_index) {
+    __shared__ MaxSum red_ms[kCeThreads / 32];
     __shared__ float red[kCeThreads / 32];
     griddep_launch_dependents();
     griddep_wait();
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const float* x = logits + size_t(row) * ld;
         const int c4 = VEC ? C >> 2 : 0;
-        // ---- maximum ----
-        float mx = -INFINITY;
+        MaxSum r{-INFINITY, 0.f};
         if (VEC) {
             const float4* x4 = reinterpret_cast<const float4*>(x);
-            for (int i = threadIdx.x; i < c4; i += kCeThreads) {
-                const float4 v = x4[i];
-                mx = fmaxf(mx, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
-            }
+#pragma unroll 4
+            for (int i = threadIdx.x; i < c4; i += kCeThreads) absorb4(r, ld_stream_f4(x4 + i));
         }
-        for (int i = 4 * c4 + threadIdx.x; i < C; i += kCeThreads) mx = fmaxf(mx, x[i]);
-        mx = block_max(mx, red);
-        // ---- sum of exponentials (the row comes from L2 now) ----
-        float s = 0.f;
-        if (VEC) {
-            const float4* x4 = reinterpret_cast<const float4*>(x);
-            for (int i = threadIdx.x; i < c4; i += kCeThreads) {
-                const float4 v = x4[i];
-                s += (expf(v.x - mx) + expf(v.y - mx)) + (expf(v.z - mx) + expf(v.w - mx));
-            }
-        }
-        for (int i = 4 * c4 + threadIdx.x; i < C; i += kCeThreads) s += expf(x[i] - mx);
-        s = block_sum(s, red);
+        for (int i = 4 * c4 + threadIdx.x; i < C; i += kCeThreads) absorb1(r, x[i]);
+        r = block_merge(r, red_ms);
+        const float mx = r.m, s = r.s;
         int t = -1;
         if (target_idx) {
             t = target_idx[row];
@@ -98,13 +123,35 @@ cross_entropy_kernel(const float* __restrict__ logits, long ld, const float* __r
             }
             if (threadIdx.x == 0) row_loss[row] = -total;
         } else {
-            const float denom = s + 1e-7f;
+            const float inv = 1.f / (s + 1e-7f);
             float* g = grad + size_t(row) * ldg;
             const float* tr = targets ? targets + size_t(row) * ldt : nullptr;
-            for (int i = threadIdx.x; i < C; i += kCeThreads) {
-                const float p = expf(x[i] - mx) / denom;
-                const float tv = tr ? tr[i] : (i == t ? 1.f : 0.f);
-                g[i] = p - tv;
+            const bool gvec = VEC && !tr && (ldg & 3) == 0 && (reinterpret_cast<uintptr_t>(grad) & 15u) == 0;
+            if (gvec) {
+                const float4* x4 = reinterpret_cast<const float4*>(x);
+                float4* g4 = reinterpret_cast<float4*>(g);
+#pragma unroll 4
+                for (int i = threadIdx.x; i < c4; i += kCeThreads) {
+                    const float4 v = ld_stream_f4(x4 + i);
+                    float4 o;
+                    o.x = expf(v.x - mx) * inv;
+                    o.y = expf(v.y - mx) * inv;
+                    o.z = expf(v.z - mx) * inv;
+                    o.w = expf(v.w - mx) * inv;
+                    const int d = t - 4 * i;  // the target class, if it lies in this group
+                    if (d == 0) o.x -= 1.f;
+                    else if (d == 1) o.y -= 1.f;
+                    else if (d == 2) o.z -= 1.f;
+                    else if (d == 3) o.w -= 1.f;
+                    st_stream_f4(g4 + i, o);
+                }
+                for (int i = 4 * c4 + threadIdx.x; i < C; i += kCeThreads) g[i] = expf(x[i] - mx) * inv - (i == t ? 1.f : 0.f);
+            } else {
+                for (int i = threadIdx.x; i < C; i += kCeThreads) {
+                    const float p = expf(x[i] - mx) * inv;
+                    const float tv = tr ? tr[i] : (i == t ? 1.f : 0.f);
+                    g[i] = p - tv;
+                }
             }
         }
     }
@@ -118,7 +165,7 @@ df8_status run_ce(bool want_grad, const float* logits, int ld, const float* targ
     DF8_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&bad), g_ce_bad_index));
     const bool vec = aligned16(logits) && ld % 4 == 0;
     const int sms = sm_count();
-    const int grid = rows < sms * 8 ? rows : sms * 8;
+    const int grid = rows < sms * 2 ? rows : sms * 2;  // rows in flight: 2 per SM (60 MB at 50257 classes, inside L2)
     const dim3 g{unsigned(grid)}, b{kCeThreads};
     if (want_grad) {
         if (vec) (void)launch_kernel((cross_entropy_kernel<true, true>), g, b, 0, st, logits, long(ld), targets, long(ldt), target_idx, rows, classes, row_loss, grad, long(ldg), bad);

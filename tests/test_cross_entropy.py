@@ -92,7 +92,7 @@ def test_cross_entropy_matches_the_oracle(df8, oracle, cuda, rows, Cn, pitch):
         t = np.zeros((rows, Cn), np.float32)
         t[np.arange(rows), idx] = 1.0
         loss_d, grad_d = _gpu_ce(df8, torch, cuda, x, t=t)
-        assert loss_d == loss and np.array_equal(grad_d, grad)
+        assert abs(loss_d - loss) <= 1e-6 * max(1.0, abs(loss)) and np.abs(grad_d - grad).max() <= 1e-7
         rng = np.random.default_rng(3)
         soft = rng.dirichlet(np.ones(Cn), rows).astype(np.float32)
         want_loss, _, want_grad = oracle.cross_entropy(x, targets=soft)

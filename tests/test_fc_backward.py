@@ -5,7 +5,7 @@ CPU: the fp32 restatement on a hand-checked case (upstream's tests hold no known
 shapes: tests/layers/fully_connected_layer_test.cu:152-197 checks that gradients exist and are finite).
 GPU: the operand kernels (quantise + transpose, transpose of codes, column sums) bit for bit against numpy;
 FullyConnectedLayer::backward against the 8-bit oracle on identical inputs (<= 2e-4 of the tensor maximum for the
-products; db <= 1e-6) and against the fp32 backward (<= 5e-2); upstream's own layer, compiled from its sources,
+products; db <= 1e-6) and against the fp32 backward (the oracle's own distance, below 1e-1: dY is e5m2); upstream's own layer, compiled from its sources,
 against the fp32 restatement."""
 import ctypes as C
 from pathlib import Path
@@ -103,8 +103,10 @@ def test_fc_backward_matches_the_oracle(df8, oracle, cuda, M, K, N, act):
     fx, fw, fb = oracle.fc_backward_f32(dy, x, w)
     assert rel(dx, qx) <= 2e-4 and rel(dw, qw) <= 2e-4, (rel(dx, qx), rel(dw, qw))
     assert rel(db, qb) <= 1e-6
-    # against the unquantised backward: the bound stated for the fp32 comparison of the forward path
-    assert rel(dx, fx) <= 5e-2 and rel(dw, fw) <= 5e-2, (rel(dx, fx), rel(dw, fw))
+    # against the unquantised backward: dY carries two mantissa bits (e5m2, up to 6 % per element), so the 5e-2 of
+    # the e4m3 forward path does not apply; the distance must be the 8-bit oracle's own (+25 %) and below 1e-1
+    for ours, q8, f32 in ((dx, qx, fx), (dw, qw, fw)):
+        assert rel(ours, f32) <= 1.25 * rel(q8, f32) + 2e-3 and rel(ours, f32) <= 1e-1, (rel(ours, f32), rel(q8, f32))
     assert df8.status_word() == (0, 0)
 
 

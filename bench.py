@@ -994,7 +994,8 @@ def run_ours(args, rank, world, local_rank):
             for key, fn in (("gemm_tflops", lambda: gemm_sweep(torch, df8, dev, peaks)),
                             ("quant_gbs", lambda: quant_sweep(torch, df8, dev, peaks)),
                             ("decode", lambda: decode_report(torch, df8, dev, peaks)),
-                            ("cross_entropy", lambda: cross_entropy_report(torch, df8, dev, peaks))):
+                            ("cross_entropy", lambda: cross_entropy_report(torch, df8, dev, peaks)),
+                            ("fc_backward", lambda: fc_backward_report(torch, df8, dev, peaks))):
                 try:
                     sec[key] = fn()
                 except Exception as e:  # a secondary figure must not take the line down
@@ -1133,6 +1134,59 @@ def cross_entropy_report(torch, df8, dev, peaks, rows=8192, classes=50257):
             "gradient": {"ms": round(ms_grad, 4), "algorithmic_bytes": b_grad, "gbs": round(b_grad / ms_grad / 1e6, 1),
                          "frac": round(b_grad / ms_grad / 1e6 / peaks["hbm_gbs"], 4)},
             "mean_row_loss": round(float(row_loss.mean().item()), 4), "bad_indices": bad.value}
+
+
+def fc_backward_report(torch, df8, dev, peaks, M=8192):
+    """Backward of GPT-2 small's FC1 and FC2 at M tokens as the layer runs it (FullyConnectedLayer::backward): max|dY|,
+    dY quantised to e5m2 in both layouts, the weight codes transposed, dX = dY W, max|X|, X quantised transposed,
+    dW = dY^T X, db = column sums.  TFLOP/s counts the two products (4 M N K)."""
+    lib, st = df8.lib(), df8.stream_ptr()
+    out = {"unit": "TFLOP/s", "peak": 2.0 * peaks["bf16_tflops"], "peak_source": peaks["source"] + " bf16 burst x2 (fp8 dense)",
+           "tokens": M, "kinds": "dY e5m2, X e4m3, W e4m3 -> f32 accumulate", "layers": {}}
+    for name, K, N in (("fc1", 768, 3072), ("fc2", 3072, 768)):  # in_features K, out_features N
+        x = torch.randn((M, K), device=dev)
+        dy = torch.randn((M, N), device=dev) * 1e-3
+        w_codes = torch.randint(0, 120, (N, K), dtype=torch.uint8, device=dev)
+        w_scale = torch.tensor([448.0, 1.0 / 448.0], device=dev)
+        amax = torch.zeros(2, device=dev)
+        dy_scale, x_scale = torch.zeros(2, device=dev), torch.zeros(2, device=dev)
+        dy_t = torch.empty((N, M), dtype=torch.uint8, device=dev)
+        dy_c = torch.empty((M, N), dtype=torch.uint8, device=dev)
+        w_t = torch.empty((K, N), dtype=torch.uint8, device=dev)
+        x_t = torch.empty((K, M), dtype=torch.uint8, device=dev)
+        dx = torch.empty((M, K), device=dev)
+        dw = torch.empty((N, K), device=dev)
+        db = torch.empty(N, device=dev)
+        partial = torch.empty(lib.df8_colsum_partial_floats(N), device=dev)
+
+        def step():
+            c = df8.check
+            c(lib.df8_amax_f32(df8.ptr(dy), dy.numel(), df8.ptr(amax), st))
+            c(lib.df8_quantize_transpose_f32(df8.ptr(dy), M, N, 1, df8.ptr(amax), df8.ptr(dy_t), M, df8.ptr(dy_scale), st))
+            c(lib.df8_quantize_f32(df8.ptr(dy), dy.numel(), 1, df8.ptr(amax), df8.ptr(dy_c), df8.ptr(dy_scale), st))
+            c(lib.df8_transpose_u8(df8.ptr(w_codes), N, K, K, df8.ptr(w_t), N, st))
+            c(lib.df8_gemm_fp8_tn(df8.ptr(dy_c), 1, df8.ptr(dy_scale), df8.ptr(w_t), 0, df8.ptr(w_scale), None, None, M, K, N, 0,
+                                  df8.ptr(dx), None, st))
+            c(lib.df8_amax_f32(df8.ptr(x), x.numel(), df8.ptr(amax[1:]), st))
+            c(lib.df8_quantize_transpose_f32(df8.ptr(x), M, K, 0, df8.ptr(amax[1:]), df8.ptr(x_t), M, df8.ptr(x_scale), st))
+            c(lib.df8_gemm_fp8_tn(df8.ptr(dy_t), 1, df8.ptr(dy_scale), df8.ptr(x_t), 0, df8.ptr(x_scale), None, None, N, K, M, 0,
+                                  df8.ptr(dw), None, st))
+            c(lib.df8_colsum_f32(df8.ptr(dy), M, N, N, df8.ptr(partial), df8.ptr(db), st))
+
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 10
+        tf = 4.0 * M * N * K / ms / 1e9
+        out["layers"][name] = {"shape_in_out": [K, N], "ms": round(ms, 4), "tflops": round(tf, 1), "frac": round(tf / out["peak"], 4),
+                               "launches": 9}
+    return out
 
 
 def secondary_forward(torch, df8, dev, rank, world, comm, make, timed, barrier, max_over_ranks, steps=5, warmup=3):

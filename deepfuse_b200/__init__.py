@@ -46,6 +46,7 @@ _SIGNATURES = {
     "df8_gemm_fp8_tn_codes_ex": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     "df8_gemv_fp8_tn": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp],
     "df8_quantize_transpose_f32": [_vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp],
+    "df8_quantize_both_layouts_f32": [_vp, _i, _i, _i, _vp, _vp, _i, _vp, _i, _vp, _vp],
     "df8_transpose_u8": [_vp, _i, _i, _i, _vp, _i, _vp],
     "df8_colsum_f32": [_vp, _i, _i, _i, _vp, _vp, _vp],
     "df8_colsum_partial_floats": [_i],

@@ -22,7 +22,8 @@ constexpr int kTile = 64;
 template <int KIND, bool QUANT>
 __global__ void __launch_bounds__(256)
 transpose_kernel(const void* __restrict__ in, long ld_in, int rows, int cols, const float* __restrict__ amax_in,
-                 uint8_t* __restrict__ out, long ld_out, float* __restrict__ scale_out) {
+                 uint8_t* __restrict__ out, long ld_out, float* __restrict__ scale_out, uint8_t* __restrict__ plain,
+                 long ld_plain) {
     __shared__ __align__(16) uint8_t tile[kTile][kTile + 16];
     griddep_launch_dependents();
     griddep_wait();
@@ -37,23 +38,49 @@ transpose_kernel(const void* __restrict__ in, long ld_in, int rows, int cols, co
     }
     const int r0 = blockIdx.y * kTile, c0 = blockIdx.x * kTile;
     const int tc = (threadIdx.x & 15) * 4, tr = threadIdx.x >> 4;  // 16 threads across a row piece, 16 rows per pass
+    // 128-bit loads / 32-bit stores of a thread's four consecutive elements where the layout allows
+    const bool in_vec = QUANT && (ld_in & 3) == 0 && (reinterpret_cast<uintptr_t>(in) & 15u) == 0;
+    const bool plain_vec = plain && (ld_plain & 3) == 0 && (reinterpret_cast<uintptr_t>(plain) & 3u) == 0;
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
         const int r = r0 + tr + 16 * p;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int c = c0 + tc + k;
-            uint8_t code = 0;
-            if (r < rows && c < cols) {
-                if (QUANT) {
-                    const float v = static_cast<const float*>(in)[size_t(r) * ld_in + c];
-                    code = uint8_t(cvt_f32x2_to_fp8x2<KIND>(__fmul_rn(v, q), 0.f) & 0xFFu);
+        const int c = c0 + tc;
+        uint8_t code[4] = {0, 0, 0, 0};
+        if (r < rows && c < cols) {
+            if (QUANT) {
+                const float* src = static_cast<const float*>(in) + size_t(r) * ld_in + c;
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
+                if (in_vec && c + 3 < cols) {
+                    const float4 f = *reinterpret_cast<const float4*>(src);
+                    v[0] = f.x, v[1] = f.y, v[2] = f.z, v[3] = f.w;
                 } else {
-                    code = static_cast<const uint8_t*>(in)[size_t(r) * ld_in + c];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        if (c + k < cols) v[k] = src[k];
                 }
+                const uint32_t packed = cvt_f32x4_to_fp8x4<KIND>(__fmul_rn(v[0], q), __fmul_rn(v[1], q), __fmul_rn(v[2], q),
+                                                                 __fmul_rn(v[3], q));
+#pragma unroll
+                for (int k = 0; k < 4; ++k) code[k] = (c + k < cols) ? uint8_t(packed >> (8 * k)) : uint8_t(0);
+                if (plain) {  // the same codes in the tensor's own layout
+                    uint8_t* dst = plain + size_t(r) * ld_plain + c;
+                    if (plain_vec && c + 3 < cols) {
+                        *reinterpret_cast<uint32_t*>(dst) = packed;
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            if (c + k < cols) dst[k] = code[k];
+                    }
+                }
+            } else {
+                const uint8_t* src = static_cast<const uint8_t*>(in) + size_t(r) * ld_in + c;
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (c + k < cols) code[k] = src[k];
             }
-            tile[tc + k][tr + 16 * p] = code;
         }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) tile[tc + k][tr + 16 * p] = code[k];
     }
     __syncthreads();
     // output row = input column c0 + oc; its bytes r0 .. r0 + 63 (zero beyond `rows`: they pad the K dimension)
@@ -113,6 +140,13 @@ using namespace df8;
 
 extern "C" df8_status df8_quantize_transpose_f32(const float* x_d, int rows, int cols, df8_kind kind, const float* amax_in_d,
                                                  uint8_t* codes_t_d, int ld_t, float* scale_out_d, df8_stream stream) {
+    return df8_quantize_both_layouts_f32(x_d, rows, cols, kind, amax_in_d, codes_t_d, ld_t, nullptr, 0, scale_out_d, stream);
+}
+
+extern "C" df8_status df8_quantize_both_layouts_f32(const float* x_d, int rows, int cols, df8_kind kind, const float* amax_in_d,
+                                                    uint8_t* codes_t_d, int ld_t, uint8_t* codes_d, int ld_c,
+                                                    float* scale_out_d, df8_stream stream) {
+    DF8_REQUIRE(!codes_d || ld_c >= cols, "df8_quantize_both_layouts_f32: ld_c=%d is smaller than cols=%d", ld_c, cols);
     DF8_REQUIRE(kind == DF8_E4M3 || kind == DF8_E5M2, "df8_quantize_transpose_f32: unknown fp8 kind");
     DF8_REQUIRE(rows >= 0 && cols >= 0 && ld_t >= rows, "df8_quantize_transpose_f32: bad shape rows=%d cols=%d ld_t=%d", rows,
                 cols, ld_t);
@@ -123,10 +157,10 @@ extern "C" df8_status df8_quantize_transpose_f32(const float* x_d, int rows, int
     cudaStream_t st = as_stream(stream);
     if (kind == DF8_E4M3)
         (void)launch_kernel((transpose_kernel<int(DF8_E4M3), true>), grid, block, 0, st, static_cast<const void*>(x_d), long(cols),
-                            rows, cols, amax_in_d, codes_t_d, long(ld_t), scale_out_d);
+                            rows, cols, amax_in_d, codes_t_d, long(ld_t), scale_out_d, codes_d, long(ld_c));
     else
         (void)launch_kernel((transpose_kernel<int(DF8_E5M2), true>), grid, block, 0, st, static_cast<const void*>(x_d), long(cols),
-                            rows, cols, amax_in_d, codes_t_d, long(ld_t), scale_out_d);
+                            rows, cols, amax_in_d, codes_t_d, long(ld_t), scale_out_d, codes_d, long(ld_c));
     DF8_LAUNCH_CHECK("transpose_kernel (quantise)");
     return DF8_OK;
 }
@@ -140,7 +174,7 @@ extern "C" df8_status df8_transpose_u8(const uint8_t* in_d, int rows, int cols, 
     const dim3 grid{unsigned((cols + kTile - 1) / kTile), unsigned((ld_out + kTile - 1) / kTile)}, block{256};
     (void)launch_kernel((transpose_kernel<0, false>), grid, block, 0, as_stream(stream), static_cast<const void*>(in_d),
                         long(ld_in), rows, cols, static_cast<const float*>(nullptr), out_d, long(ld_out),
-                        static_cast<float*>(nullptr));
+                        static_cast<float*>(nullptr), static_cast<uint8_t*>(nullptr), 0L);
     DF8_LAUNCH_CHECK("transpose_kernel");
     return DF8_OK;
 }

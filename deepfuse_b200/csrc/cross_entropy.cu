@@ -13,6 +13,8 @@
 // HBM-bound: 4 B per logit for the loss, 8 B per logit (+4 with dense targets) for the gradient.
 #include "df8_internal.cuh"
 
+#include <atomic>
+
 namespace df8 {
 namespace {
 
@@ -157,6 +159,70 @@ cross_entropy_kernel(const float* __restrict__ logits, long ld, const float* __r
     }
 }
 
+// Gradient with the row held in shared memory between the two passes (rows of up to ~56 K classes: the GPT-2
+// vocabulary's 50257 floats are 196 KB): the logits cross HBM once and the gradient once, whatever L2 does with 1.65 GB
+// of gradient stores streaming through it.  One CTA per SM; class-index targets, rows on 16-byte boundaries.
+__global__ void __launch_bounds__(kCeThreads, 1)
+cross_entropy_grad_smem_kernel(const float* __restrict__ logits, long ld, const int* __restrict__ target_idx, int rows,
+                               int C, float* __restrict__ grad, long ldg, unsigned int* __restrict__ bad_index) {
+    extern __shared__ float4 row4[];  // ceil(C / 4) groups
+    __shared__ MaxSum red_ms[kCeThreads / 32];
+    griddep_launch_dependents();
+    griddep_wait();
+    const int c4 = C >> 2;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float* x = logits + size_t(row) * ld;
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        MaxSum r{-INFINITY, 0.f};
+#pragma unroll 4
+        for (int i = threadIdx.x; i < c4; i += kCeThreads) {
+            const float4 v = ld_stream_f4(x4 + i);
+            row4[i] = v;
+            absorb4(r, v);
+        }
+        float* tail = reinterpret_cast<float*>(row4 + c4);
+        for (int i = 4 * c4 + threadIdx.x; i < C; i += kCeThreads) {
+            const float v = x[i];
+            tail[i - 4 * c4] = v;
+            absorb1(r, v);
+        }
+        r = block_merge(r, red_ms);  // its barriers also make the row visible to every thread
+        const float mx = r.m, inv = 1.f / (r.s + 1e-7f);
+        int t = target_idx[row];
+        if (t < 0 || t >= C) {
+            if (threadIdx.x == 0 && bad_index) atomicAdd(bad_index, 1u);
+            t = -1;
+        }
+        float* g = grad + size_t(row) * ldg;
+        const bool gvec = (ldg & 3) == 0 && (reinterpret_cast<uintptr_t>(grad) & 15u) == 0;
+        if (gvec) {
+            float4* g4 = reinterpret_cast<float4*>(g);
+#pragma unroll 4
+            for (int i = threadIdx.x; i < c4; i += kCeThreads) {
+                const float4 v = row4[i];
+                float4 o;
+                o.x = expf(v.x - mx) * inv;
+                o.y = expf(v.y - mx) * inv;
+                o.z = expf(v.z - mx) * inv;
+                o.w = expf(v.w - mx) * inv;
+                const int d = t - 4 * i;
+                if (d == 0) o.x -= 1.f;
+                else if (d == 1) o.y -= 1.f;
+                else if (d == 2) o.z -= 1.f;
+                else if (d == 3) o.w -= 1.f;
+                st_stream_f4(g4 + i, o);
+            }
+        } else {
+            const float* rowf = reinterpret_cast<const float*>(row4);
+            for (int i = threadIdx.x; i < 4 * c4; i += kCeThreads) g[i] = expf(rowf[i] - mx) * inv - (i == t ? 1.f : 0.f);
+        }
+        for (int i = 4 * c4 + threadIdx.x; i < C; i += kCeThreads) g[i] = expf(tail[i - 4 * c4] - mx) * inv - (i == t ? 1.f : 0.f);
+        __syncthreads();  // the next row overwrites the buffer
+    }
+}
+
+constexpr int kCeSmemCap = 224 * 1024;
+
 __device__ unsigned int g_ce_bad_index = 0;
 
 df8_status run_ce(bool want_grad, const float* logits, int ld, const float* targets, int ldt, const int* target_idx, int rows,
@@ -167,6 +233,20 @@ df8_status run_ce(bool want_grad, const float* logits, int ld, const float* targ
     const int sms = sm_count();
     const int grid = rows < sms * 2 ? rows : sms * 2;  // rows in flight: 2 per SM (60 MB at 50257 classes, inside L2)
     const dim3 g{unsigned(grid)}, b{kCeThreads};
+    if (want_grad && vec && target_idx && !targets && size_t((classes + 3) / 4) * 16 <= size_t(kCeSmemCap)) {
+        static std::atomic<bool> configured[64] = {};
+        int dev = 0;
+        DF8_CUDA_TRY(cudaGetDevice(&dev));
+        if (dev >= 0 && dev < 64 && !configured[dev].load()) {
+            DF8_CUDA_TRY(cudaFuncSetAttribute(cross_entropy_grad_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCeSmemCap));
+            configured[dev].store(true);
+        }
+        const size_t smem = size_t((classes + 3) / 4) * 16;
+        (void)launch_kernel(cross_entropy_grad_smem_kernel, dim3(unsigned(rows < sms ? rows : sms)), b, smem, st, logits, long(ld),
+                            target_idx, rows, classes, grad, long(ldg), bad);
+        DF8_LAUNCH_CHECK("cross_entropy_grad_smem_kernel");
+        return DF8_OK;
+    }
     if (want_grad) {
         if (vec) (void)launch_kernel((cross_entropy_kernel<true, true>), g, b, 0, st, logits, long(ld), targets, long(ldt), target_idx, rows, classes, row_loss, grad, long(ldg), bad);
         else (void)launch_kernel((cross_entropy_kernel<true, false>), g, b, 0, st, logits, long(ld), targets, long(ldt), target_idx, rows, classes, row_loss, grad, long(ldg), bad);

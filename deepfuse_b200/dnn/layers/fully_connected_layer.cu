@@ -272,11 +272,12 @@ tensor<TT> FullyConnectedLayer<TT>::backward(const tensor<TT>& grad_output) {
     utils::CHECK_DF8(df8_amax_f32(grad_output.data(), grad_output.numel(), am_dy, st));
     tensor<float> dy_scale({2}), x_scale({2});
     tensor<uint8_t> dy_t({out_f, Kw});  // dY^T [out, N]
-    utils::CHECK_DF8(df8_quantize_transpose_f32(grad_output.data(), N, out_f, gk, am_dy, dy_t.data(), Kw, dy_scale.data(), st));
     tensor<uint8_t> dy_c({N, Kd});      // dY   [N, out] with the K padding
-    if (Kd == out_f) {
-        utils::CHECK_DF8(df8_quantize_f32(grad_output.data(), grad_output.numel(), gk, am_dy, dy_c.data(), dy_scale.data(), st));
+    if (Kd == out_f) {  // one read of dY for both layouts
+        utils::CHECK_DF8(df8_quantize_both_layouts_f32(grad_output.data(), N, out_f, gk, am_dy, dy_t.data(), Kw, dy_c.data(), Kd,
+                                                       dy_scale.data(), st));
     } else {  // transposing the transposed codes back pads the rows with zero codes
+        utils::CHECK_DF8(df8_quantize_transpose_f32(grad_output.data(), N, out_f, gk, am_dy, dy_t.data(), Kw, dy_scale.data(), st));
         utils::CHECK_DF8(df8_transpose_u8(dy_t.data(), out_f, N, Kw, dy_c.data(), Kd, st));
     }
 

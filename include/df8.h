@@ -312,6 +312,11 @@ df8_status df8_streamer_stats(df8_streamer* s, unsigned long long* bytes_uploade
  *                               of scratch; fixed summation order (no atomics) */
 df8_status df8_quantize_transpose_f32(const float* x_d, int rows, int cols, df8_kind kind, const float* amax_in_d,
                                       uint8_t* codes_t_d, int ld_t, float* scale_out_d, df8_stream stream);
+/* one read of x for both layouts: codes_t_d as above, and the same codes untransposed in codes_d [rows, ld_c]
+ * (ld_c >= cols; bytes cols .. ld_c-1 of a row are left alone); codes_d may be null */
+df8_status df8_quantize_both_layouts_f32(const float* x_d, int rows, int cols, df8_kind kind, const float* amax_in_d,
+                                         uint8_t* codes_t_d, int ld_t, uint8_t* codes_d, int ld_c, float* scale_out_d,
+                                         df8_stream stream);
 df8_status df8_transpose_u8(const uint8_t* in_d, int rows, int cols, int ld_in, uint8_t* out_d, int ld_out,
                             df8_stream stream);
 df8_status df8_colsum_f32(const float* x_d, int rows, int cols, int ld, float* partial_d, float* out_d,

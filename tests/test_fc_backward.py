@@ -54,6 +54,15 @@ def test_quantize_transpose_and_code_transpose(df8, oracle, cuda, rows, cols, ld
     assert not got[:, rows:].any()  # the K padding is zero codes
     assert bool((out[cols * ld:] == 0xAB).all())
     assert np.array_equal(sc.cpu().numpy(), scale)
+    # both layouts from one read: the transposed codes again, and the tensor's own layout with a row pitch
+    ldc = cols + 12
+    out_t = torch.full((cols * ld,), 0x11, dtype=torch.uint8, device=cuda)
+    out_p = torch.full((rows, ldc), 0x22, dtype=torch.uint8, device=cuda)
+    df8.check(df8.lib().df8_quantize_both_layouts_f32(df8.ptr(xd), rows, cols, kind, df8.ptr(amax), df8.ptr(out_t), ld,
+                                                      df8.ptr(out_p), ldc, df8.ptr(sc), df8.stream_ptr()))
+    torch.cuda.synchronize()
+    assert torch.equal(out_t, out[: cols * ld])
+    assert np.array_equal(out_p[:, :cols].cpu().numpy(), codes.reshape(rows, cols)) and bool((out_p[:, cols:] == 0x22).all())
     # codes -> transposed codes
     cd = torch.from_numpy(codes.reshape(rows, cols)).to(cuda)
     out2 = torch.full((cols * ld + 64,), 0xCD, dtype=torch.uint8, device=cuda)

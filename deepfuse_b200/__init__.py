@@ -621,8 +621,9 @@ class Gpt2ColumnSharded:
             out.append((buf.value.decode(), tuple(shape[k] for k in range(ndim.value))))
         return out
 
-    def load_full_params(self, params: dict):
-        """Slices this rank's shards out of a full parameter dictionary and uploads them (collective)."""
+    def load_full_params(self, params: dict, prepare: bool = True):
+        """Slices this rank's shards out of a full parameter dictionary and uploads them (collective).  prepare=False
+        leaves the re-quantisation of the weights to the next forward (what a C++ caller that only uploads gets)."""
         import numpy as np
 
         from .sharding import shard_gpt2_params
@@ -637,7 +638,8 @@ class Gpt2ColumnSharded:
             if a.size != n:
                 raise ValueError(f"{name}: expected {shape}, got {a.shape}")
             dnn_check(d.dnn_gpt2cs_param_upload(self.h, i, a.ctypes.data_as(C.c_void_p)), "dnn_gpt2cs_param_upload")
-        dnn_check(d.dnn_gpt2cs_prepare(self.h), "dnn_gpt2cs_prepare")
+        if prepare:
+            dnn_check(d.dnn_gpt2cs_prepare(self.h), "dnn_gpt2cs_prepare")
 
     def initialize_on_device(self, seed: int):
         dnn_check(dnn_lib().dnn_gpt2cs_initialize_on_device(self.h, seed), "dnn_gpt2cs_initialize_on_device")

@@ -6,7 +6,10 @@ and the LayerNorm row sums are combined from the ranks' pieces, i.e. taken in an
 activation on a rounding boundary may take the neighbouring fp8 code and the logits agree with the unsharded model
 the way two roundings of the same 8-bit pipeline do: the maximum and RMS differences are held against the model's
 own distance to the UNQUANTISED fp32 pipeline.  What must be exact: every rank computes the same hidden states, and
-the exchange through peer-mapped buffers + copy engines gives bit for bit what the NCCL fallback gives."""
+the exchange through peer-mapped buffers + copy engines gives bit for bit what the NCCL fallback gives.  Both
+cases also upload a second, smaller set of weights WITHOUT asking for a re-quantisation and compare the next forward:
+the per-tensor maxima of the sharded weights must be taken afresh (a maximum left from the first set would lose three
+bits of every code)."""
 import numpy as np
 import pytest
 
@@ -66,13 +69,33 @@ def _compare(rank, world, id_path, act_kind, causal):
                 if world == 1 and not torch.equal(got, want):
                     return False
             hidden = df8.device_view(torch, model.forward_hidden(ids), (B * T, CFG["hidden"])).clone()
-            results.append((got, hidden, model.bytes_pushed()))
+            pushed = model.bytes_pushed()
+            # a weight update that is NOT followed by an explicit re-quantisation: smaller weights, so a per-tensor
+            # maximum left over from the first set would cost three bits of every code
+            small = {k: (v * np.float32(0.125) if k.endswith("weight") and "embedding" not in k else v) for k, v in params.items()}
+            model.load_full_params(small, prepare=False)
+            full.load_params(small)
+            ref_small = df8.device_view(torch, full.forward_hidden(ids), (B * T, CFG["hidden"])).clone()
+            got_small = df8.device_view(torch, model.forward_hidden(ids), (B * T, CFG["hidden"])).clone()
+            full.load_params(params)
+            torch.cuda.synchronize()
+            if world == 1:
+                if not torch.equal(got_small, ref_small):
+                    print("re-upload: single rank differs from the unsharded model", flush=True)
+                    return False
+            else:
+                f32s = torch.from_numpy(gpt2_ref.gpt2_forward(small, ids_h, CFG, act_kind=None, w_kind=None, causal=causal,
+                                                              return_hidden=True)).to(dev)
+                if _rel(got_small, ref_small) > 1.5 * _rel(ref_small, f32s) or _rms(got_small, ref_small) > 1.5 * _rms(ref_small, f32s):
+                    print("re-upload", _rel(got_small, ref_small), _rel(ref_small, f32s), flush=True)
+                    return False
+            results.append((got, hidden, pushed, got_small))
             model.close()
         finally:
             comm.close()
     if world > 1:
-        (g_p2p, h_p2p, pushed), (g_nccl, h_nccl, pushed_nccl) = results
-        if not (torch.equal(g_p2p, g_nccl) and torch.equal(h_p2p, h_nccl)):
+        (g_p2p, h_p2p, pushed, s_p2p), (g_nccl, h_nccl, pushed_nccl, s_nccl) = results
+        if not (torch.equal(g_p2p, g_nccl) and torch.equal(h_p2p, h_nccl) and torch.equal(s_p2p, s_nccl)):
             return False
         if pushed <= 0 or pushed_nccl != 0:
             return False

@@ -44,6 +44,9 @@ _SIGNATURES = {
     "df8_gemm_fp8_tn_ex": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp],
     "df8_gemm_fp8_tn_amax_ex": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "df8_gemm_fp8_tn_codes_ex": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
+    "df8_gemm_fp8_tn_part": [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp],
+    "df8_gemm_fp8_tn_amax_part": [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
+    "df8_gemm_fp8_tn_codes_part": [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     "df8_gemv_fp8_tn": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp],
     "df8_quantize_transpose_f32": [_vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp],
     "df8_quantize_both_layouts_f32": [_vp, _i, _i, _i, _vp, _vp, _i, _vp, _i, _vp, _vp],
@@ -86,6 +89,8 @@ _SIGNATURES = {
     "df8_comm_symm_alloc": [_vp, _sz, _vp],
     "df8_comm_p2p_enabled": [_vp, _vp],
     "df8_comm_allgather_symm": [_vp, _vp, _sz, _sz, _vp],
+    "df8_comm_push_symm": [_vp, _vp, _sz, _sz, _vp, _vp],
+    "df8_comm_wait_symm": [_vp, C.c_uint, _i, _vp],
     "df8_comm_allreduce_max_p2p": [_vp, _vp, _vp],
     "df8_comm_bytes_pushed": [_vp, _vp],
     "df8_comm_allreduce_max_f32": [_vp, _vp, _sz, _vp],

@@ -473,6 +473,55 @@ extern "C" df8_status df8_comm_allgather_symm(df8_comm* c, void* local_d, size_t
     return DF8_OK;
 }
 
+// The two halves of df8_comm_allgather_symm for callers that pipeline a gather in pieces: push one piece of this
+// rank's slab (the bytes [local_d + offset, + bytes), to the same place in every peer's copy of the buffer) as soon
+// as it is produced; wait for the peers' matching piece only where it is consumed.  Every rank must issue the same
+// sequence of pushes.  Pieces of one stream of pushes arrive in order, so waiting for a ticket also covers every
+// earlier push of the peers.
+extern "C" df8_status df8_comm_push_symm(df8_comm* c, void* local_d, size_t offset, size_t bytes, df8_stream stream,
+                                         unsigned int* ticket_h) {
+    DF8_REQUIRE(c && c->comm && local_d && ticket_h, "df8_comm_push_symm: null argument");
+    DF8_REQUIRE(c->p2p_ok, "df8_comm_push_symm: needs the peer-mapped transport (df8_comm_p2p_enabled)");
+    uint8_t* base = static_cast<uint8_t*>(local_d) + offset;
+    const Df8SymmBuf* b = find_symm(c, base, bytes);
+    DF8_REQUIRE(b != nullptr, "df8_comm_push_symm: the region is not inside a buffer of df8_comm_symm_alloc");
+    cudaStream_t st = as_stream(stream);
+    const uint32_t seq = ++c->seq;
+    *ticket_h = seq;
+    if (bytes == 0) return DF8_OK;
+    const size_t rel = size_t(base - b->local);
+    DF8_CUDA_TRY(cudaEventRecord(c->ev_ready, st));
+    DF8_CUDA_TRY(cudaStreamWaitEvent(c->copy_stream, c->ev_ready, 0));
+    for (int k = 1; k < c->world; ++k) {
+        const int p = (c->rank + k) % c->world;
+        DF8_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(b->peer[p]) + rel, base, bytes, cudaMemcpyDeviceToDevice,
+                                     c->copy_stream));
+    }
+    signal_peers_kernel<<<1, 32, 0, c->copy_stream>>>(ctrl_ptrs(c), c->rank, c->world, seq);
+    DF8_LAUNCH_CHECK("signal_peers_kernel");
+    DF8_CUDA_TRY(cudaEventRecord(c->ev_sent, c->copy_stream));
+    c->bytes_pushed += bytes * size_t(c->world - 1);
+    return DF8_OK;
+}
+
+// `stream` waits (bounded, status word) until every peer's push with this ticket has landed; with own_too != 0 it
+// also waits for this rank's own pushes issued so far, after which its slab may be overwritten again.
+extern "C" df8_status df8_comm_wait_symm(df8_comm* c, unsigned int ticket, int own_too, df8_stream stream) {
+    DF8_REQUIRE(c && c->comm, "df8_comm_wait_symm: null communicator");
+    DF8_REQUIRE(c->p2p_ok, "df8_comm_wait_symm: needs the peer-mapped transport (df8_comm_p2p_enabled)");
+    DF8_REQUIRE(ticket != 0 && c->seq - ticket < uint32_t(kFlagRing), "df8_comm_wait_symm: ticket %u is not one of the last %d pushes",
+                ticket, kFlagRing);
+    unsigned int* status = nullptr;
+    df8_status src = status_word_device_ptr(&status);
+    if (src != DF8_OK) return src;
+    cudaStream_t st = as_stream(stream);
+    wait_peers_kernel<<<1, 32, 0, st>>>(reinterpret_cast<const uint32_t*>(c->symm[size_t(c->ctrl)].local), c->rank, c->world,
+                                        ticket, status);
+    DF8_LAUNCH_CHECK("wait_peers_kernel");
+    if (own_too) DF8_CUDA_TRY(cudaStreamWaitEvent(st, c->ev_sent, 0));
+    return DF8_OK;
+}
+
 extern "C" df8_status df8_comm_allreduce_max_p2p(df8_comm* c, float* value_d, df8_stream stream) {
     DF8_REQUIRE(c && c->comm && value_d, "df8_comm_allreduce_max_p2p: null argument");
     df8_status rc = ensure_p2p(c);

@@ -1408,7 +1408,7 @@ bool use_pair_kernel(int M, int N, int K, int sms, int mode) {
 // runs the two passes.
 df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uint8_t* w_codes, df8_kind kind_w,
                     GemmArgs args, cudaStream_t st, bool* fused = nullptr, int a_slabs = 1,
-                    int tma_fallback = kOutF32) {
+                    int tma_fallback = kOutF32, int a_slab_rows = 0) {
     const int M = args.M, N = args.N, K = args.K;
     df8_status src = status_word_device_ptr(&args.status);
     if (src != DF8_OK) return src;
@@ -1426,8 +1426,12 @@ df8_status run_gemm(int mode, const uint8_t* a_codes, df8_kind kind_a, const uin
     const int sms = sm_count();
     // A: coordinates (column inside the slab, row, slab)
     CUtensorMap ta, tw, to = {};
+    // a_slab_rows: the slabs hold that many rows each (M of them are used): a row range of a gathered tensor
+    if (a_slab_rows != 0 && a_slab_rows < M)
+        return fail(DF8_ERR_INVALID, "fp8 GEMM: a_slab_rows=%d is smaller than M=%d", a_slab_rows, M);
+    const uint64_t slab_rows = a_slab_rows ? uint64_t(a_slab_rows) : uint64_t(M);
     df8_status rc = make_tmap_3d_u8(&ta, a_codes, uint64_t(M), uint64_t(slab_cols), uint64_t(a_slabs), uint64_t(slab_cols),
-                                    uint64_t(M) * uint64_t(slab_cols), BM, BK, 128);
+                                    slab_rows * uint64_t(slab_cols), BM, BK, 128);
     if (rc != DF8_OK) return rc;
     auto make_out_map = [&]() {
         return make_tmap_2d_f32(&to, args.out, uint64_t(M), uint64_t(N), uint64_t(args.ldc) * sizeof(float), 128, 32, 128);
@@ -1544,6 +1548,14 @@ extern "C" df8_status df8_gemm_fp8_tn_ex(const uint8_t* a_codes, df8_kind kind_a
                                          const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
                                          const float* bias, const float* residual, int M, int N, int K, int flags,
                                          float* out, int ldc, float* out_amax, df8_stream stream) {
+    return df8_gemm_fp8_tn_part(a_codes, kind_a, scale_a, a_slabs, M, w_codes, kind_w, scale_w, bias, residual, M, N, K, flags,
+                                out, ldc, out_amax, stream);
+}
+
+extern "C" df8_status df8_gemm_fp8_tn_part(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a, int a_slabs,
+                                           int a_slab_rows, const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
+                                           const float* bias, const float* residual, int M, int N, int K, int flags,
+                                           float* out, int ldc, float* out_amax, df8_stream stream) {
     DF8_REQUIRE((kind_a == DF8_E4M3 || kind_a == DF8_E5M2) && (kind_w == DF8_E4M3 || kind_w == DF8_E5M2),
                 "df8_gemm_fp8_tn: unknown fp8 kind");
     DF8_REQUIRE(ldc >= N, "df8_gemm_fp8_tn: ldc=%d is smaller than N=%d", ldc, N);
@@ -1603,7 +1615,8 @@ extern "C" df8_status df8_gemm_fp8_tn_ex(const uint8_t* a_codes, df8_kind kind_a
             return run_gemm(kOutF32T, w_codes, kind_w, a_codes, kind_a, args, st);
         }
     }
-    return run_gemm(tma ? kOutF32Tma : st_mode, a_codes, kind_a, w_codes, kind_w, args, st, nullptr, a_slabs, st_mode);
+    return run_gemm(tma ? kOutF32Tma : st_mode, a_codes, kind_a, w_codes, kind_w, args, st, nullptr, a_slabs, st_mode,
+                    a_slab_rows);
 }
 
 extern "C" df8_status df8_gemm_fp8_tn_q(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a,
@@ -1679,6 +1692,14 @@ extern "C" df8_status df8_gemm_fp8_tn_amax_ex(const uint8_t* a_codes, df8_kind k
                                               const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
                                               const float* bias, int M, int N, int K, int flags, float* out_amax,
                                               df8_stream stream) {
+    return df8_gemm_fp8_tn_amax_part(a_codes, kind_a, scale_a, a_slabs, M, w_codes, kind_w, scale_w, bias, M, N, K, flags,
+                                     out_amax, stream);
+}
+
+extern "C" df8_status df8_gemm_fp8_tn_amax_part(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a, int a_slabs,
+                                                int a_slab_rows, const uint8_t* w_codes, df8_kind kind_w,
+                                                const float* scale_w, const float* bias, int M, int N, int K, int flags,
+                                                float* out_amax, df8_stream stream) {
     DF8_REQUIRE((kind_a == DF8_E4M3 || kind_a == DF8_E5M2) && (kind_w == DF8_E4M3 || kind_w == DF8_E5M2),
                 "df8_gemm_fp8_tn_amax: unknown fp8 kind");
     DF8_REQUIRE(M >= 0 && N >= 0 && K > 0, "df8_gemm_fp8_tn_amax: bad shape M=%d N=%d K=%d", M, N, K);
@@ -1700,7 +1721,7 @@ extern "C" df8_status df8_gemm_fp8_tn_amax_ex(const uint8_t* a_codes, df8_kind k
     args.N = N;
     args.K = K;
     args.flags = flags | DF8_EPI_AMAX;
-    return run_gemm(kOutNone, a_codes, kind_a, w_codes, kind_w, args, st, nullptr, a_slabs);
+    return run_gemm(kOutNone, a_codes, kind_a, w_codes, kind_w, args, st, nullptr, a_slabs, kOutF32, a_slab_rows);
 }
 
 extern "C" df8_status df8_gemm_fp8_tn_codes(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a,
@@ -1717,6 +1738,15 @@ extern "C" df8_status df8_gemm_fp8_tn_codes_ex(const uint8_t* a_codes, df8_kind 
                                                const float* bias, int M, int N, int K, int flags, df8_kind out_kind,
                                                const float* amax_in, uint8_t* out_codes, float* out_scale,
                                                df8_stream stream) {
+    return df8_gemm_fp8_tn_codes_part(a_codes, kind_a, scale_a, a_slabs, M, w_codes, kind_w, scale_w, bias, M, N, K, flags,
+                                      out_kind, amax_in, out_codes, out_scale, stream);
+}
+
+extern "C" df8_status df8_gemm_fp8_tn_codes_part(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a, int a_slabs,
+                                                 int a_slab_rows, const uint8_t* w_codes, df8_kind kind_w,
+                                                 const float* scale_w, const float* bias, int M, int N, int K, int flags,
+                                                 df8_kind out_kind, const float* amax_in, uint8_t* out_codes,
+                                                 float* out_scale, df8_stream stream) {
     DF8_REQUIRE((kind_a == DF8_E4M3 || kind_a == DF8_E5M2) && (kind_w == DF8_E4M3 || kind_w == DF8_E5M2) &&
                     (out_kind == DF8_E4M3 || out_kind == DF8_E5M2),
                 "df8_gemm_fp8_tn_codes: unknown fp8 kind");
@@ -1741,7 +1771,7 @@ extern "C" df8_status df8_gemm_fp8_tn_codes_ex(const uint8_t* a_codes, df8_kind 
     args.q_amax = amax_in;
     args.out_scale = out_scale;
     return run_gemm(out_kind == DF8_E4M3 ? kOutE4M3 : kOutE5M2, a_codes, kind_a, w_codes, kind_w, args, as_stream(stream),
-                    nullptr, a_slabs);
+                    nullptr, a_slabs, kOutF32, a_slab_rows);
 }
 
 // The skinny product of a decode step: out[B, N] = epi(X[B, K] . W[N, K]^T * dq + bias), B <= 128 token rows against a

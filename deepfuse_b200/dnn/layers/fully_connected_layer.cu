@@ -181,12 +181,12 @@ void FullyConnectedLayer<TT>::drop_cached_codes() {
 template <typename TT>
 void FullyConnectedLayer<TT>::forward_codes(const uint8_t* a_codes, df8_kind a_kind, const float* a_scale, int M,
                                             int flags, const float* residual, float* out, float* out_amax, int ldc,
-                                            int a_slabs) {
+                                            int a_slabs, int a_slab_rows) {
     const fp8::Quantized& w = quantized_weights();
     const uint8_t* w_codes = external_codes_ ? external_codes_ : w.codes.data();
-    utils::CHECK_DF8(df8_gemm_fp8_tn_ex(a_codes, a_kind, a_scale, a_slabs, w_codes, w.kind, w.scale.data(),
-                                        this->bias_.data(), residual, M, out_features_, padded_in(), flags, out,
-                                        ldc > 0 ? ldc : out_features_, out_amax, fp8::stream()));
+    utils::CHECK_DF8(df8_gemm_fp8_tn_part(a_codes, a_kind, a_scale, a_slabs, a_slab_rows > 0 ? a_slab_rows : M, w_codes, w.kind,
+                                          w.scale.data(), this->bias_.data(), residual, M, out_features_, padded_in(), flags,
+                                          out, ldc > 0 ? ldc : out_features_, out_amax, fp8::stream()));
 }
 
 template <typename TT>

@@ -45,9 +45,11 @@ public:
     const fp8::Quantized& quantized_weights();
     // out[M,out] = epilogue(codes . Wq^T); a_codes is [M, padded_in()]; `flags` are DF8_EPI_* bits;
     // out_amax may be null.  ldc: row pitch of `out` and `residual` in floats (0 = out_features); a_slabs: the
-    // columns of a_codes are stored as that many [M, padded_in() / a_slabs] slabs (see df8_gemm_fp8_tn_ex).
+    // columns of a_codes are stored as that many [M, padded_in() / a_slabs] slabs (see df8_gemm_fp8_tn_ex);
+    // a_slab_rows: rows per slab when M is only a row range of them (0 = M; see df8_gemm_fp8_tn_part).
     void forward_codes(const uint8_t* a_codes, df8_kind a_kind, const float* a_scale, int M, int flags,
-                       const float* residual, float* out, float* out_amax, int ldc = 0, int a_slabs = 1);
+                       const float* residual, float* out, float* out_amax, int ldc = 0, int a_slabs = 1,
+                       int a_slab_rows = 0);
 
     // The same product for the few token rows of a decode step (B <= 128): bound by streaming the weights
     // (df8_gemv_fp8_tn).

@@ -1,5 +1,7 @@
 #include "dnn/models/gpt2_column_sharded.cuh"
 
+#include <cstdlib>
+
 #include <stdexcept>
 #include <string>
 
@@ -134,6 +136,17 @@ void Gpt2ColumnSharded<T>::ensure_work_space(int M) {
         utils::CHECK_DF8(df8_comm_symm_alloc(comm_, 2 * g * size_t(M) * 2 * sizeof(float), &p));
         sym_stats_ = static_cast<float*>(p);
         work_rows_ = M;
+        int enabled = 0;
+        utils::CHECK_DF8(df8_comm_p2p_enabled(comm_, &enabled));
+        p2p_ = enabled != 0;
+        if (const char* e = getenv("DF8_SHARD_CHUNKS")) {  // profiling and tests
+            const int n = atoi(e);
+            if (n == 1 || n == 2 || n == 4 || n == 8) chunks_ = n;
+        }
+        if (const char* e = getenv("DF8_SHARD_CHUNK_MIN_ROWS")) {  // tests: small models still exercise the pipeline
+            const int n = atoi(e);
+            if (n >= 128) chunk_min_rows_ = n;
+        }
     }
     ensure(x_shard_, size_t(M) * E / g);
     ensure(x1_shard_, size_t(M) * E / g);
@@ -160,9 +173,32 @@ void Gpt2ColumnSharded<T>::layernorm_quantize_sharded(LayerNormLayer<T>& norm, c
     utils::CHECK_DF8(df8_layernorm_shard_amax_f32(x, M, Eg, stats_all, world_, gamma, beta, norm.epsilon(),
                                                   row_stats_.data(), am, st));
     all_max(am);
-    utils::CHECK_DF8(df8_layernorm_shard_quantize_f32(x, M, Eg, row_stats_.data(), gamma, beta, act, am,
-                                                      sym_ln_ + size_t(rank_) * size_t(M) * Eg, ln_scale_.data(), st));
-    utils::CHECK_DF8(df8_comm_allgather_symm(comm_, sym_ln_, 0, size_t(M) * Eg, st));
+    const int nc = chunks_for(M);
+    if (nc == 1) {
+        utils::CHECK_DF8(df8_layernorm_shard_quantize_f32(x, M, Eg, row_stats_.data(), gamma, beta, act, am,
+                                                          sym_ln_ + size_t(rank_) * size_t(M) * Eg, ln_scale_.data(), st));
+        utils::CHECK_DF8(df8_comm_allgather_symm(comm_, sym_ln_, 0, size_t(M) * Eg, st));
+        return;
+    }
+    // row chunks: a chunk is on its way to the peers while the next one is quantised; the consumer (a GEMM over the
+    // same row chunk) waits for its ticket
+    const int Mc = M / nc;
+    for (int c = 0; c < nc; ++c) {
+        const size_t off = size_t(rank_) * size_t(M) * Eg + size_t(c) * Mc * Eg;
+        utils::CHECK_DF8(df8_layernorm_shard_quantize_f32(x + size_t(c) * Mc * Eg, Mc, Eg, row_stats_.data() + size_t(c) * Mc * 2,
+                                                          gamma, beta, act, am, sym_ln_ + off, ln_scale_.data(), st));
+        utils::CHECK_DF8(df8_comm_push_symm(comm_, sym_ln_, off, size_t(Mc) * Eg, st, &tickets_ln_[c]));
+    }
+}
+
+// Row chunks of a pipelined gather: only over the peer-mapped transport, and only when the chunks stay whole GEMM
+// tiles (128 rows) and large enough to fill the GPU.
+template <typename T>
+int Gpt2ColumnSharded<T>::chunks_for(int M) const {
+    if (world_ == 1 || !p2p_ || chunks_ <= 1) return 1;
+    int nc = chunks_;
+    while (nc > 1 && (M % (nc * 128) != 0 || M / nc < chunk_min_rows_)) nc >>= 1;
+    return nc;
 }
 
 template <typename T>
@@ -171,8 +207,18 @@ void Gpt2ColumnSharded<T>::quantize_gather_sharded(const float* x, int M, float*
     const df8_kind act = fp8::policy().activation_kind;
     const df8_stream st = fp8::stream();
     all_max(amax);
-    utils::CHECK_DF8(df8_quantize_f32(x, size_t(M) * Eg, act, amax, sym + size_t(rank_) * size_t(M) * Eg, scale, st));
-    utils::CHECK_DF8(df8_comm_allgather_symm(comm_, sym, 0, size_t(M) * Eg, st));
+    const int nc = chunks_for(M);
+    if (nc == 1) {
+        utils::CHECK_DF8(df8_quantize_f32(x, size_t(M) * Eg, act, amax, sym + size_t(rank_) * size_t(M) * Eg, scale, st));
+        utils::CHECK_DF8(df8_comm_allgather_symm(comm_, sym, 0, size_t(M) * Eg, st));
+        return;
+    }
+    const int Mc = M / nc;
+    for (int c = 0; c < nc; ++c) {
+        const size_t off = size_t(rank_) * size_t(M) * Eg + size_t(c) * Mc * Eg;
+        utils::CHECK_DF8(df8_quantize_f32(x + size_t(c) * Mc * Eg, size_t(Mc) * Eg, act, amax, sym + off, scale, st));
+        utils::CHECK_DF8(df8_comm_push_symm(comm_, sym, off, size_t(Mc) * Eg, st, &tickets_attn_[c]));
+    }
 }
 
 template <typename T>
@@ -185,13 +231,23 @@ void Gpt2ColumnSharded<T>::block_forward_sharded(Block& b, int B, int T_len) {
     float* x = x_shard_.data();
     float* x1 = x1_shard_.data();
 
+    const int nc = chunks_for(M), Mc = M / nc;
+    // consumers of a chunked gather: wait for the chunk's ticket (the last one also for this rank's own pushes, after
+    // which its slab may be rewritten), then work on that row range of the gathered slabs
+    auto wait_chunk = [&](const unsigned int* tickets, int c) {
+        if (nc > 1) utils::CHECK_DF8(df8_comm_wait_symm(comm_, tickets[c], c == nc - 1 ? 1 : 0, st));
+    };
+
     // ---- x1 = x + out_proj(attention(QKV(LN1(x)))) ----
     layernorm_quantize_sharded(b.norm1, x, M, 0);
     {   // QKV of this rank's heads: max|out| over all ranks, then the codes
         const fp8::Quantized& w = b.qkv.quantized_weights();
         float* am = fp8::amax_slot(amax_.data());
-        utils::CHECK_DF8(df8_gemm_fp8_tn_amax_ex(sym_ln_, act, ln_scale_.data(), g, w.codes.data(), w.kind,
-                                                 w.scale.data(), b.qkv.bias()->data(), M, 3 * Eg, E, 0, am, st));
+        for (int c = 0; c < nc; ++c) {
+            wait_chunk(tickets_ln_, c);
+            utils::CHECK_DF8(df8_gemm_fp8_tn_amax_part(sym_ln_ + size_t(c) * Mc * Eg, act, ln_scale_.data(), g, M, w.codes.data(),
+                                                       w.kind, w.scale.data(), b.qkv.bias()->data(), Mc, 3 * Eg, E, 0, am, st));
+        }
         all_max(am);
         qkvq_.kind = act;
         utils::CHECK_DF8(df8_gemm_fp8_tn_codes_ex(sym_ln_, act, ln_scale_.data(), g, w.codes.data(), w.kind,
@@ -205,7 +261,11 @@ void Gpt2ColumnSharded<T>::block_forward_sharded(Block& b, int B, int T_len) {
                                            st));
         quantize_gather_sharded(attn_f32_.data(), M, am, sym_attn_, attn_scale_.data());
     }
-    b.out.forward_codes(sym_attn_, act, attn_scale_.data(), M, DF8_EPI_RESIDUAL, x, x1, nullptr, Eg, g);
+    for (int c = 0; c < nc; ++c) {
+        wait_chunk(tickets_attn_, c);
+        const size_t r = size_t(c) * Mc * Eg;
+        b.out.forward_codes(sym_attn_ + r, act, attn_scale_.data(), Mc, DF8_EPI_RESIDUAL, x + r, x1 + r, nullptr, Eg, g, M);
+    }
 
     // ---- x = x1 + FC2(act(FC1(LN2(x1)))) ----
     layernorm_quantize_sharded(b.norm2, x1, M, 1);
@@ -213,17 +273,27 @@ void Gpt2ColumnSharded<T>::block_forward_sharded(Block& b, int B, int T_len) {
         const fp8::Quantized& w = b.fc1.quantized_weights();
         float* am = fp8::amax_slot(amax_.data());
         const int flags = mlp_gelu_ ? DF8_EPI_GELU : 0;
-        utils::CHECK_DF8(df8_gemm_fp8_tn_amax_ex(sym_ln_, act, ln_scale_.data(), g, w.codes.data(), w.kind,
-                                                 w.scale.data(), b.fc1.bias()->data(), M, Fg, E, flags, am, st));
+        for (int c = 0; c < nc; ++c) {
+            wait_chunk(tickets_ln_, c);
+            utils::CHECK_DF8(df8_gemm_fp8_tn_amax_part(sym_ln_ + size_t(c) * Mc * Eg, act, ln_scale_.data(), g, M, w.codes.data(),
+                                                       w.kind, w.scale.data(), b.fc1.bias()->data(), Mc, Fg, E, flags, am, st));
+        }
         all_max(am);
-        // the codes go straight into this rank's slab of the buffer the peers gather into
-        utils::CHECK_DF8(df8_gemm_fp8_tn_codes_ex(sym_ln_, act, ln_scale_.data(), g, w.codes.data(), w.kind,
-                                                  w.scale.data(), b.fc1.bias()->data(), M, Fg, E, flags, act, am,
-                                                  sym_hidden_ + size_t(rank_) * size_t(M) * Fg, hidden_scale_.data(),
-                                                  st));
-        utils::CHECK_DF8(df8_comm_allgather_symm(comm_, sym_hidden_, 0, size_t(M) * Fg, st));
+        // the codes go straight into this rank's slab of the buffer the peers gather into, a row chunk at a time
+        for (int c = 0; c < nc; ++c) {
+            const size_t off = size_t(rank_) * size_t(M) * Fg + size_t(c) * Mc * Fg;
+            utils::CHECK_DF8(df8_gemm_fp8_tn_codes_part(sym_ln_ + size_t(c) * Mc * Eg, act, ln_scale_.data(), g, M, w.codes.data(),
+                                                        w.kind, w.scale.data(), b.fc1.bias()->data(), Mc, Fg, E, flags, act, am,
+                                                        sym_hidden_ + off, hidden_scale_.data(), st));
+            if (nc > 1) utils::CHECK_DF8(df8_comm_push_symm(comm_, sym_hidden_, off, size_t(Mc) * Fg, st, &tickets_hidden_[c]));
+        }
+        if (nc == 1) utils::CHECK_DF8(df8_comm_allgather_symm(comm_, sym_hidden_, 0, size_t(M) * Fg, st));
     }
-    b.fc2.forward_codes(sym_hidden_, act, hidden_scale_.data(), M, DF8_EPI_RESIDUAL, x1, x, nullptr, Eg, g);
+    for (int c = 0; c < nc; ++c) {
+        wait_chunk(tickets_hidden_, c);
+        b.fc2.forward_codes(sym_hidden_ + size_t(c) * Mc * Fg, act, hidden_scale_.data(), Mc, DF8_EPI_RESIDUAL,
+                            x1 + size_t(c) * Mc * Eg, x + size_t(c) * Mc * Eg, nullptr, Eg, g, M);
+    }
 }
 
 // Embedding (replicated table) -> this rank's columns -> the blocks.  The hidden states stay in x_shard_.

@@ -100,6 +100,7 @@ private:
     // per-tensor quantisation of a sharded fp32 tensor [M, E/g] into this rank's slab of `sym`, then gather
     void quantize_gather_sharded(const float* x, int M, float* amax, uint8_t* sym, float* scale);
     void all_max(float* amax);
+    int chunks_for(int M) const;
     void head(int M, float* logits, int pitch);
 
     df8_comm* comm_;
@@ -117,6 +118,12 @@ private:
     tensor<float> amax_, ln_scale_{{2}}, attn_scale_{{2}}, hidden_scale_{{2}};
     // buffers mapped into every peer (df8_comm_symm_alloc; owned by the communicator): fp8 codes of all columns as
     // g slabs [g][M, cols/g], and the LayerNorm row statistics [2][g][M][2]
+    // pipelined gathers (several ranks, peer-mapped transport): a gathered tensor travels in row chunks; the producer
+    // pushes a chunk as soon as it is quantised and the consuming GEMM runs chunk by chunk behind the tickets
+    bool p2p_ = false;
+    int chunks_ = 4;  // DF8_SHARD_CHUNKS in the environment; 1 = whole-tensor gathers
+    int chunk_min_rows_ = 2048;  // smaller chunks do not fill the GPU (DF8_SHARD_CHUNK_MIN_ROWS)
+    unsigned int tickets_ln_[8] = {}, tickets_attn_[8] = {}, tickets_hidden_[8] = {};
     int work_rows_ = 0;
     uint8_t *sym_ln_ = nullptr, *sym_attn_ = nullptr, *sym_hidden_ = nullptr;
     float* sym_stats_ = nullptr;

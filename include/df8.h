@@ -148,6 +148,22 @@ df8_status df8_gemm_fp8_tn_codes_ex(const uint8_t* a_codes, df8_kind kind_a, con
                                     int M, int N, int K, int flags, df8_kind out_kind, const float* amax_in,
                                     uint8_t* out_codes, float* out_scale, df8_stream stream);
 
+/* Row ranges of a slab-stored A (the "_ex" forms with one more argument): the slabs hold a_slab_rows rows each, of
+ * which this call multiplies M starting at a_codes (a_codes points at the range's first row inside slab 0).  Lets a
+ * caller whose A operand arrives over NVLink in row chunks start on the chunks that have landed. */
+df8_status df8_gemm_fp8_tn_part(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a, int a_slabs,
+                                int a_slab_rows, const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
+                                const float* bias, const float* residual, int M, int N, int K, int flags, float* out,
+                                int ldc, float* out_amax, df8_stream stream);
+df8_status df8_gemm_fp8_tn_amax_part(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a, int a_slabs,
+                                     int a_slab_rows, const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
+                                     const float* bias, int M, int N, int K, int flags, float* out_amax,
+                                     df8_stream stream);
+df8_status df8_gemm_fp8_tn_codes_part(const uint8_t* a_codes, df8_kind kind_a, const float* scale_a, int a_slabs,
+                                      int a_slab_rows, const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
+                                      const float* bias, int M, int N, int K, int flags, df8_kind out_kind,
+                                      const float* amax_in, uint8_t* out_codes, float* out_scale, df8_stream stream);
+
 /* ---- fp8 attention -------------------------------------------------------------------------
  * Replaces, inside MultiHeadAttentionLayer::forward (dnn/layers/multi_head_attention.cu:204-308), the
  * Q/K/V slice + head-split copies (:231-260), both matmul_kernel launches (:266-270, :283-287),
@@ -375,6 +391,14 @@ df8_status df8_comm_symm_alloc(df8_comm* c, size_t bytes, void** local_d_h);
 df8_status df8_comm_p2p_enabled(df8_comm* c, int* enabled_h);
 df8_status df8_comm_allgather_symm(df8_comm* c, void* local_d, size_t offset, size_t bytes_per_rank,
                                    df8_stream stream);
+/* df8_comm_allgather_symm in two halves, for a gather that is pipelined in pieces: push [local_d + offset, + bytes)
+ * to the same place in every peer's copy as soon as it is produced (returns a ticket), and make a stream wait for the
+ * peers' push with that ticket only where the piece is consumed (own_too: also for this rank's own pushes so far,
+ * after which its slab may be rewritten).  Needs the peer-mapped transport; every rank issues the same pushes in
+ * the same order; a ticket stays valid for 64 further pushes. */
+df8_status df8_comm_push_symm(df8_comm* c, void* local_d, size_t offset, size_t bytes, df8_stream stream,
+                              unsigned int* ticket_h);
+df8_status df8_comm_wait_symm(df8_comm* c, unsigned int ticket, int own_too, df8_stream stream);
 df8_status df8_comm_allreduce_max_p2p(df8_comm* c, float* value_d, df8_stream stream);
 /* bytes this rank has sent to its peers through df8_comm_allgather_symm */
 df8_status df8_comm_bytes_pushed(df8_comm* c, unsigned long long* bytes_h);

@@ -467,4 +467,33 @@ def test_gemm_reads_a_stored_as_column_slabs(df8, oracle, cuda, monkeypatch, sla
     assert am[0].item() == am[1].item() and torch.equal(codes[0], codes[1]) and torch.equal(sc[0], sc[1])
     with pytest.raises(df8.Df8Error, match="slabs"):
         df8.gemm_fp8_tn_ex(slabbed, 0, sxd, 3, wcd, 0, swd, None, None, M, N, K, 0, got, N)
+    # row ranges of the slabbed operand (the "_part" forms): rows [r0, r0 + Mp) of every slab, slabs M rows apart;
+    # fp32 output, max|out| accumulated over the ranges (no clearing in between), codes
+    st = df8.stream_ptr()
+    sk = K // slabs
+    got2 = torch.full((M, N), 5.0, device=cuda)
+    am2 = torch.zeros(1, device=cuda)
+    codes2 = torch.zeros((M, N), dtype=torch.uint8, device=cuda)
+    sc2 = torch.zeros(2, device=cuda)
+    ranges = [(0, 128), (128, 256), (384, M - 384)]
+    before = lib.df8_set_amax_preclear(0)  # returns the previous setting
+    try:
+        for r0, mp in ranges:
+            a = df8.ptr(slabbed) + r0 * sk
+            df8.check(lib.df8_gemm_fp8_tn_part(a, 0, df8.ptr(sxd), slabs, M, df8.ptr(wcd), 0, df8.ptr(swd), None, None, mp, N, K,
+                                               0, df8.ptr(got2) + r0 * N * 4, N, None, st))
+            df8.check(lib.df8_gemm_fp8_tn_amax_part(a, 0, df8.ptr(sxd), slabs, M, df8.ptr(wcd), 0, df8.ptr(swd), None, mp, N, K,
+                                                    1, df8.ptr(am2), st))
+        for r0, mp in ranges:
+            a = df8.ptr(slabbed) + r0 * sk
+            df8.check(lib.df8_gemm_fp8_tn_codes_part(a, 0, df8.ptr(sxd), slabs, M, df8.ptr(wcd), 0, df8.ptr(swd), None, mp, N, K,
+                                                     1, 0, df8.ptr(am2), df8.ptr(codes2) + r0 * N, df8.ptr(sc2), st))
+    finally:
+        lib.df8_set_amax_preclear(before)
+    torch.cuda.synchronize()
+    assert torch.equal(got2, want)
+    assert am2.item() == am[0].item() and torch.equal(codes2, codes[0]) and torch.equal(sc2, sc[0])
+    with pytest.raises(df8.Df8Error, match="a_slab_rows"):
+        df8.check(lib.df8_gemm_fp8_tn_part(df8.ptr(slabbed), 0, df8.ptr(sxd), slabs, M - 1, df8.ptr(wcd), 0, df8.ptr(swd), None,
+                                           None, M, N, K, 0, df8.ptr(got2), N, None, st))
     assert df8.status_word() == (0, 0)

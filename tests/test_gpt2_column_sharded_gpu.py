@@ -6,7 +6,9 @@ and the LayerNorm row sums are combined from the ranks' pieces, i.e. taken in an
 activation on a rounding boundary may take the neighbouring fp8 code and the logits agree with the unsharded model
 the way two roundings of the same 8-bit pipeline do: the maximum and RMS differences are held against the model's
 own distance to the UNQUANTISED fp32 pipeline.  What must be exact: every rank computes the same hidden states, and
-the exchange through peer-mapped buffers + copy engines gives bit for bit what the NCCL fallback gives.  Both
+the exchange through peer-mapped buffers + copy engines (gathers pipelined in four row chunks: producer pushes a
+chunk, the consuming GEMM runs chunk by chunk behind the tickets) gives bit for bit what the NCCL fallback (whole-tensor
+gathers) gives.  Both
 cases also upload a second, smaller set of weights WITHOUT asking for a re-quantisation and compare the next forward:
 the per-tensor maxima of the sharded weights must be taken afresh (a maximum left from the first set would lose three
 bits of every code)."""
@@ -16,7 +18,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 CFG = dict(vocab=1000, max_seq_len=128, layers=2, heads=4, hidden=256, ffn=512)
-B, T = 2, 128
+B, T = 4, 128  # 512 token rows: four row chunks of 128 for the pipelined gathers
 
 
 def _rel(a, b):
@@ -38,6 +40,7 @@ def _compare(rank, world, id_path, act_kind, causal):
 
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
+    os.environ["DF8_SHARD_CHUNK_MIN_ROWS"] = "128"  # the peer-mapped arm gathers in four row chunks, the NCCL arm whole
     df8.dnn_check(df8.dnn_lib().dnn_init(rank), "dnn_init")
     df8.dnn_check(df8.dnn_lib().dnn_set_fp8_policy(0, act_kind))
     params = gpt2_ref.make_params(CFG, seed=11)

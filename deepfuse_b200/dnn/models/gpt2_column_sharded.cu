@@ -347,8 +347,13 @@ void Gpt2ColumnSharded<T>::head(int M, float* logits, int pitch) {
     float* am = fp8::amax_slot(amax_.data());
     const int Eg = hidden_dim_ / world_;
     utils::CHECK_DF8(df8_amax_f32(x_shard_.data(), size_t(M) * Eg, am, fp8::stream()));
-    quantize_gather_sharded(x_shard_.data(), M, am, sym_ln_, ln_scale_.data());
-    final_fc_->forward_codes(sym_ln_, act, ln_scale_.data(), M, 0, nullptr, logits, nullptr, pitch, world_);
+    quantize_gather_sharded(x_shard_.data(), M, am, sym_ln_, ln_scale_.data());  // tickets in tickets_attn_ when chunked
+    const int nc = chunks_for(M), Mc = M / nc;
+    for (int c = 0; c < nc; ++c) {
+        if (nc > 1) utils::CHECK_DF8(df8_comm_wait_symm(comm_, tickets_attn_[c], c == nc - 1 ? 1 : 0, fp8::stream()));
+        final_fc_->forward_codes(sym_ln_ + size_t(c) * Mc * Eg, act, ln_scale_.data(), Mc, 0, nullptr,
+                                 logits + size_t(c) * Mc * pitch, nullptr, pitch, world_, M);
+    }
 }
 
 template <typename T>

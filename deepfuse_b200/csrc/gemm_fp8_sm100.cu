@@ -476,8 +476,25 @@ __device__ __forceinline__ bool epilogue_tile_f32_tma_group(const CUtensorMap* t
 // indexed by the feature (row), the residual is read at the output's position.
 // One chunk: this lane's feature row, 32 consecutive token columns col0 .. col0 + 31.  Flag tests stay outside the
 // per-element loops (a uniform branch per element costs more than its arithmetic).
+// The residual values of one chunk (this lane's feature row, token columns col0 .. col0 + 31), zero outside the
+// output.  They do not depend on the accumulators: the epilogue asks for a chunk's values one chunk ahead (for a
+// tile's first chunk before it waits for the MMAs), so their global-memory latency stays off the per-chunk chain.
+__device__ __forceinline__ void load_residual_transposed(float (&rs)[32], const GemmArgs& args, int grow, bool row_ok, int col0) {
+    const size_t ldc = size_t(args.ldc);
+    const float* res = args.residual + size_t(col0) * ldc + grow;
+    if (row_ok && col0 + 32 <= args.N) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) rs[i] = res[i * ldc];
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) rs[i] = (row_ok && col0 + i < args.N) ? res[i * ldc] : 0.f;
+    }
+}
+
+// `rs`: the chunk's residual values on entry; refilled with those of the chunk at next_col0 (>= 0) once they have been
+// added, before the stores are issued.
 __device__ __forceinline__ void store_chunk_transposed(const uint32_t (&r)[32], const GemmArgs& args, int grow, int col0,
-                                                       float alpha, float b, float& amax) {
+                                                       float alpha, float b, float& amax, float (&rs)[32], int next_col0) {
     float o[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) o[i] = fmaf(__uint_as_float(r[i]), alpha, b);
@@ -485,17 +502,14 @@ __device__ __forceinline__ void store_chunk_transposed(const uint32_t (&r)[32], 
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[i] = gelu_tanh(o[i]);
     }
+    if (args.flags & 2) {  // not unconditionally: x + 0 would turn -0 into +0
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] += rs[i];
+        if (next_col0 >= 0) load_residual_transposed(rs, args, grow, true, next_col0);
+    }
     const size_t ldc = size_t(args.ldc);
     float* dst = args.out + size_t(col0) * ldc + grow;
     if (col0 + 32 <= args.N) {
-        if (args.flags & 2) {
-            const float* res = args.residual + size_t(col0) * ldc + grow;
-            float rs[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) rs[i] = res[i * ldc];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] += rs[i];
-        }
         if (args.flags & 4) {
             float m0 = 0.f, m1 = 0.f;
 #pragma unroll
@@ -511,10 +525,8 @@ __device__ __forceinline__ void store_chunk_transposed(const uint32_t (&r)[32], 
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
             if (col0 + i < args.N) {
-                float v = o[i];
-                if (args.flags & 2) v += args.residual[size_t(col0 + i) * ldc + grow];
-                if (args.flags & 4) amax = fmaxf(amax, fabsf(v));
-                dst[i * ldc] = v;
+                if (args.flags & 4) amax = fmaxf(amax, fabsf(o[i]));
+                dst[i * ldc] = o[i];
             }
         }
     }
@@ -528,6 +540,9 @@ __device__ __forceinline__ bool epilogue_tile_f32_transposed(const GemmArgs& arg
     const int grow = row0 + lane;
     const bool row_ok = grow < args.M;
     const float b = (args.bias && row_ok) ? __ldg(args.bias + grow) : 0.f;
+    const bool with_res = (args.flags & 2) != 0;
+    float rs[32];
+    if (with_res && n0 + 32 * half < args.N) load_residual_transposed(rs, args, grow, row_ok, n0 + 32 * half);
     if (!mbar_wait_bounded(tfull_bar, acc_phase)) return false;
     tc_fence_after_sync();
     int nvalid = 0;
@@ -550,8 +565,9 @@ __device__ __forceinline__ bool epilogue_tile_f32_transposed(const GemmArgs& arg
                 release();
             }
             if (row_ok) {
-                if (j & 1) store_chunk_transposed(rb, args, grow, n0 + 32 * (half + 2 * j), alpha, b, amax);
-                else store_chunk_transposed(ra, args, grow, n0 + 32 * (half + 2 * j), alpha, b, amax);
+                const int next_col0 = (with_res && j + 1 < nvalid) ? n0 + 32 * (half + 2 * (j + 1)) : -1;
+                if (j & 1) store_chunk_transposed(rb, args, grow, n0 + 32 * (half + 2 * j), alpha, b, amax, rs, next_col0);
+                else store_chunk_transposed(ra, args, grow, n0 + 32 * (half + 2 * j), alpha, b, amax, rs, next_col0);
             }
         }
     }
@@ -1395,8 +1411,11 @@ bool use_pair_kernel(int M, int N, int K, int sms, int mode) {
     if ((mode == kOutF32Tma || mode == kOutF32T) && M >= 256 && N >= 256 && double(M) * double(N) * 4.0 >= 512e6) return true;
     // measured on B200 (M = 8192): 8192 x 8192 x 8192 runs at 2547 TFLOP/s with CTA pairs against 2245 without;
     // at K = 768 the epilogue dominates and the pairs' coupled accumulator hand-back costs a few per cent
+    // the max|out| / codes passes at K = 1024 stay ahead on single CTAs (8192 x 3072 x 1024, both passes: 51.5 against
+    // 55.3 us; 8192 x 4096 x 1024: 67.0 against 69.8), the fp32 outputs at K = 3072 on pairs (27.1 against 31.2 us)
     const long tiles2 = long((M + 255) / 256) * ((N + 255) / 256);
-    return K >= 1024 && M >= 256 && N >= 256 && tiles2 >= sms / 2;
+    const int k_min = is_direct(mode) ? 2048 : 1024;
+    return K >= k_min && M >= 256 && N >= 256 && tiles2 >= sms / 2;
 }
 
 // Shared host path of the entry points: picks the tile width, encodes the tensor maps, launches `mode`.
@@ -1601,12 +1620,14 @@ extern "C" df8_status df8_gemm_fp8_tn_part(const uint8_t* a_codes, df8_kind kind
     // into pitched rows (TMA stores) 394 -> 417, into dense rows of 50257 floats 565 -> 615.  Inside the GPT-2 small
     // forward, though, the swapped out-projection and FC2 made the pass SLOWER (3.435 against 3.346 ms, two runs
     // each), so only the case with the large margin takes this path by itself: GELU outputs.
-    // DF8_GEMM_SWAP=0 / 1 in the environment forces the choice (profiling and tests).
+    // DF8_GEMM_SWAP=0 / 1 in the environment forces the choice, 2 = every output that is not far larger than L2
+    // (profiling and tests).
     {
         const char* e = getenv("DF8_GEMM_SWAP");
         bool swap = a_slabs == 1 && (flags & DF8_EPI_GELU) && M >= 256 && N >= 256 && double(M) * double(N) * 4.0 < 512e6;
         if (e && e[0] == '0') swap = false;
         if (e && e[0] == '1') swap = a_slabs == 1;
+        if (e && e[0] == '2') swap = a_slabs == 1 && M >= 256 && N >= 256 && double(M) * double(N) * 4.0 < 512e6;
         if (swap) {
             args.scale_a = scale_w;
             args.scale_w = scale_a;

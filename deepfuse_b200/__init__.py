@@ -52,6 +52,7 @@ _SIGNATURES = {
     "df8_quantize_both_layouts_f32": [_vp, _i, _i, _i, _vp, _vp, _i, _vp, _i, _vp, _vp],
     "df8_transpose_u8": [_vp, _i, _i, _i, _vp, _i, _vp],
     "df8_colsum_f32": [_vp, _i, _i, _i, _vp, _vp, _vp],
+    "df8_colsum_amax_f32": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp],
     "df8_colsum_partial_floats": [_i],
     "df8_cross_entropy_f32": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp],
     "df8_cross_entropy_grad_f32": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _i, _vp],

@@ -101,7 +101,8 @@ constexpr int kSumChunks = 32;
 
 // stage 1: grid (cols / 32, kSumChunks); a warp-wide row piece of 32 columns, 8 warps take rows in turn
 __global__ void __launch_bounds__(256)
-colsum_partial_kernel(const float* __restrict__ x, long ld, int rows, int cols, float* __restrict__ partial) {
+colsum_partial_kernel(const float* __restrict__ x, long ld, int rows, int cols, float* __restrict__ partial,
+                      float* __restrict__ amax_out) {
     __shared__ float red[8][32];
     griddep_launch_dependents();
     griddep_wait();
@@ -109,9 +110,17 @@ colsum_partial_kernel(const float* __restrict__ x, long ld, int rows, int cols, 
     const int c = blockIdx.x * 32 + lane;
     const int per = (rows + kSumChunks - 1) / kSumChunks;
     const int r_begin = blockIdx.y * per, r_end = min(rows, r_begin + per);
-    float s = 0.f;
+    float s = 0.f, m = 0.f;
     if (c < cols)
-        for (int r = r_begin + warp; r < r_end; r += 8) s += x[size_t(r) * ld + c];
+        for (int r = r_begin + warp; r < r_end; r += 8) {
+            const float v = x[size_t(r) * ld + c];
+            s += v;
+            m = fmaxf(m, fabsf(v));
+        }
+    if (amax_out) {  // the same pass also gives max|x| (the tensor is about to be quantised)
+        m = warp_max(m);
+        if (lane == 0 && m > 0.f) atomic_max_nonneg(amax_out, m);
+    }
     red[warp][lane] = s;
     __syncthreads();
     if (warp == 0 && c < cols) {
@@ -181,12 +190,18 @@ extern "C" df8_status df8_transpose_u8(const uint8_t* in_d, int rows, int cols, 
 
 extern "C" df8_status df8_colsum_f32(const float* x_d, int rows, int cols, int ld, float* partial_d, float* out_d,
                                      df8_stream stream) {
+    return df8_colsum_amax_f32(x_d, rows, cols, ld, partial_d, out_d, nullptr, stream);
+}
+
+extern "C" df8_status df8_colsum_amax_f32(const float* x_d, int rows, int cols, int ld, float* partial_d, float* out_d,
+                                          float* amax_out_d, df8_stream stream) {
     DF8_REQUIRE(rows >= 0 && cols >= 0 && ld >= cols, "df8_colsum_f32: bad shape rows=%d cols=%d ld=%d", rows, cols, ld);
+    cudaStream_t st = as_stream(stream);
+    if (amax_out_d) DF8_CLEAR_AMAX(amax_out_d, st);
     if (cols == 0) return DF8_OK;
     DF8_REQUIRE(x_d && partial_d && out_d, "df8_colsum_f32: null buffer");
-    cudaStream_t st = as_stream(stream);
     (void)launch_kernel(colsum_partial_kernel, dim3(unsigned((cols + 31) / 32), kSumChunks), dim3(256), 0, st, x_d, long(ld), rows,
-                        cols, partial_d);
+                        cols, partial_d, amax_out_d);
     DF8_LAUNCH_CHECK("colsum_partial_kernel");
     (void)launch_kernel(colsum_final_kernel, dim3(unsigned((cols + 255) / 256)), dim3(256), 0, st,
                         static_cast<const float*>(partial_d), cols, out_d);

@@ -266,10 +266,11 @@ tensor<TT> FullyConnectedLayer<TT>::backward(const tensor<TT>& grad_output) {
     const int Kw = (N + 15) / 16 * 16;      // contraction length of dW
     fp8::PassScope amax_slots;
 
-    // dY: one maximum, two layouts of the same codes
+    // dY: one pass for db and max|dY|, then two layouts of the same codes
     tensor<float> amax({2});
     float* am_dy = fp8::amax_slot(amax.data());
-    utils::CHECK_DF8(df8_amax_f32(grad_output.data(), grad_output.numel(), am_dy, st));
+    tensor<float> partial({df8_colsum_partial_floats(out_f)});
+    utils::CHECK_DF8(df8_colsum_amax_f32(grad_output.data(), N, out_f, out_f, partial.data(), this->grad_bias_.data(), am_dy, st));
     tensor<float> dy_scale({2}), x_scale({2});
     tensor<uint8_t> dy_t({out_f, Kw});  // dY^T [out, N]
     tensor<uint8_t> dy_c({N, Kd});      // dY   [N, out] with the K padding
@@ -296,9 +297,6 @@ tensor<TT> FullyConnectedLayer<TT>::backward(const tensor<TT>& grad_output) {
     utils::CHECK_DF8(df8_gemm_fp8_tn(dy_t.data(), gk, dy_scale.data(), x_t.data(), ak, x_scale.data(), nullptr, nullptr, out_f,
                                      in_f, Kw, 0, this->grad_weights_.data(), nullptr, st));
 
-    // db
-    tensor<float> partial({df8_colsum_partial_floats(out_f)});
-    utils::CHECK_DF8(df8_colsum_f32(grad_output.data(), N, out_f, out_f, partial.data(), this->grad_bias_.data(), st));
     return grad_input;
 }
 

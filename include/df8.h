@@ -337,6 +337,9 @@ df8_status df8_transpose_u8(const uint8_t* in_d, int rows, int cols, int ld_in, 
                             df8_stream stream);
 df8_status df8_colsum_f32(const float* x_d, int rows, int cols, int ld, float* partial_d, float* out_d,
                           df8_stream stream);
+/* the same pass also reducing max|x| into amax_out_d (cleared first, like df8_amax_f32), or null */
+df8_status df8_colsum_amax_f32(const float* x_d, int rows, int cols, int ld, float* partial_d, float* out_d,
+                               float* amax_out_d, df8_stream stream);
 int df8_colsum_partial_floats(int cols);
 
 /* ---- softmax cross-entropy on fp32 logits (training-side neighbour of the vocabulary head) -----------------

@@ -89,6 +89,12 @@ def test_column_sums_are_exact_for_integers_and_repeatable(df8, cuda, rows, cols
         outs.append(out.clone())
     assert torch.equal(outs[0], outs[1])
     assert torch.equal(outs[0][:cols].cpu(), xi[:, :cols].sum(dim=0)) and bool((outs[0][cols:] == 55.0).all())
+    # the same pass with max|x|
+    out = torch.zeros(cols, device=cuda)
+    amax = torch.full((1,), 123.0, device=cuda)
+    df8.check(lib.df8_colsum_amax_f32(df8.ptr(x), rows, cols, ld, df8.ptr(partial), df8.ptr(out), df8.ptr(amax), df8.stream_ptr()))
+    torch.cuda.synchronize()
+    assert torch.equal(out, outs[0][:cols]) and amax.item() == xi[:, :cols].abs().max().item()
 
 
 @pytest.mark.gpu

@@ -1055,8 +1055,12 @@ def decode_report(torch, df8, dev, peaks, batch=32, prompt=128, steps=64):
         model = df8.Gpt2(**cfg, device=dev.index)
     finally:
         df8.dnn_check(d.dnn_set_host_init(1))
+    side = torch.cuda.Stream(device=dev)  # a stream of its own: the model replays a step from a CUDA graph there
+    side.wait_stream(torch.cuda.current_stream())
+    ctx = torch.cuda.stream(side)
+    ctx.__enter__()
     try:
-        model.set_stream(torch.cuda.current_stream())
+        model.set_stream(side)
         model.initialize_on_device(c["seed"], 0.02)
         model.set_options(gelu=True, causal=True)
         ids = torch.from_numpy(synthetic.fill_token_ids(batch * prompt, seed=7, vocab=c["vocab"]).reshape(batch, prompt)).to(dev)
@@ -1085,6 +1089,7 @@ def decode_report(torch, df8, dev, peaks, batch=32, prompt=128, steps=64):
         logits_bytes = batch * V * 4
         algo = weight_bytes + kv_bytes + logits_bytes
         gbs = algo / (ms * 1e6)
+        graph = model.decode_graph_active()
         model.end_decode()
         return {"metric": "GPT-2 small fp8 decode tokens/s", "value": round(batch / (ms / 1e3), 1), "unit": "tokens/s",
                 "ms_per_step": round(ms, 4), "steps": steps, "batch": batch, "prompt": prompt, "prefill_ms": round(prefill_ms, 3),
@@ -1093,8 +1098,10 @@ def decode_report(torch, df8, dev, peaks, batch=32, prompt=128, steps=64):
                              "frac": round(gbs / peaks["hbm_gbs"], 4), "peak_source": "measured copy bandwidth"},
                 "config": {"workload": f"GPT-2 small, {batch} sequences, prompt {prompt}, one token per sequence and step, "
                                        "KV cache of fp8 codes with one scale per position, causal"},
-                "device_wait_status": list(df8.status_word())}
+                "cuda_graph": graph, "device_wait_status": list(df8.status_word())}
     finally:
+        ctx.__exit__(None, None, None)
+        torch.cuda.current_stream().wait_stream(side)
         model.close()
 
 

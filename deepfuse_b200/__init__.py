@@ -48,6 +48,11 @@ _SIGNATURES = {
     "df8_gemm_fp8_tn_amax_part": [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "df8_gemm_fp8_tn_codes_part": [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     "df8_gemv_fp8_tn": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp],
+    "df8_embed_pe_pos_f32": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
+    "df8_kv_cache_append_pos": [_vp, _vp, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _vp],
+    "df8_attention_decode_fp8_pos": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp, _vp],
+    "df8_attention_decode_fused_f32": [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp, _vp],
+    "df8_position_advance": [_vp, _vp],
     "df8_quantize_transpose_f32": [_vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp],
     "df8_quantize_both_layouts_f32": [_vp, _i, _i, _i, _vp, _vp, _i, _vp, _i, _vp, _vp],
     "df8_transpose_u8": [_vp, _i, _i, _i, _vp, _i, _vp],
@@ -282,6 +287,7 @@ _DNN_SIGNATURES = {
     "dnn_gpt2_prefill": [_vp, _vp, _i, _i, _i, _vp],
     "dnn_gpt2_decode_step": [_vp, _vp, _i, _i, _vp],
     "dnn_gpt2_end_decode": [_vp],
+    "dnn_gpt2_decode_graph_active": [_vp, _vp],
     "dnn_gpt2_save_upstream": [_vp, C.c_char_p],
     "dnn_gpt2_save_quantized": [_vp, C.c_char_p],
     "dnn_gpt2_forward_text": [_vp, C.c_char_p, _vp, _i, _vp],
@@ -528,6 +534,12 @@ class Gpt2:
 
     def end_decode(self):
         dnn_check(dnn_lib().dnn_gpt2_end_decode(self.h), "dnn_gpt2_end_decode")
+
+    def decode_graph_active(self):
+        """True once decode steps are replayed from a CUDA graph (never on the legacy default stream)."""
+        v = C.c_int(0)
+        dnn_check(dnn_lib().dnn_gpt2_decode_graph_active(self.h, C.byref(v)), "dnn_gpt2_decode_graph_active")
+        return bool(v.value)
 
 
 class Comm:

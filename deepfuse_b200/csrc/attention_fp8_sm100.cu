@@ -325,7 +325,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnArgs
         const int q = warp & 3;            // TMEM lane quarter (warps w and w+4 share it)
         constexpr int HC = BKV;            // score columns per thread and block: the whole row
         const int row = q * 32 + lane;
-        const float dq = args.scale[1];
+        const float dq = ld_l2_f32(args.scale + 1);
         const float cs = dq * dq * rsqrtf(float(D)) * kLog2e;  // raw score -> log2 domain
         const uint32_t lane_addr = uint32_t(q * 32) << 16;
 
@@ -903,7 +903,7 @@ attention_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_qkv, const Att
         const int q = warp & 3;         // TMEM lane quarter
         const int t = sw >> 2;          // query tile
         const int row = q * 32 + lane;  // query row within the tile
-        const float dq = args.scale[1];
+        const float dq = ld_l2_f32(args.scale + 1);
         const float cs = dq * dq * rsqrtf(float(D)) * kLog2e;
         const uint32_t lane_addr = uint32_t(q * 32) << 16;
         const uint32_t tmem_s = tmem_base + 256 * t;

@@ -29,7 +29,7 @@ transpose_kernel(const void* __restrict__ in, long ld_in, int rows, int cols, co
     griddep_wait();
     float q = 1.f;
     if (QUANT) {
-        const float2 sc = scales_from_amax(*amax_in, fp8_max(KIND));
+        const float2 sc = scales_from_amax(ld_l2_f32(amax_in), fp8_max(KIND));
         q = sc.x;
         if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && scale_out) {
             scale_out[0] = sc.x;

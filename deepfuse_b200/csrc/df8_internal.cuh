@@ -153,17 +153,33 @@ __device__ __forceinline__ void atomic_max_nonneg(float* addr, float v) {
     atomicMax(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
 }
 
-// 128-bit streaming global accesses (data touched once: keep it out of L1).
+// A scalar that an earlier kernel of the stream produced (a max|.|, a scale pair, the decode position), read at L2.
+// Kernels launched with the programmatic attribute become resident while their predecessors still run; an L1 line
+// that a co-resident kernel filled before the producer's write (neighbouring slots of the max|.| pool share a line)
+// would otherwise serve a stale value: L1 is only invalidated when a kernel is launched, not at griddepcontrol.wait.
+__device__ __forceinline__ float ld_l2_f32(const float* p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ int ld_l2_s32(const int* p) {
+    int v;
+    asm volatile("ld.global.cg.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// 128-bit streaming global loads of data touched once, served at L2: never from an L1 line, which may predate the
+// producing kernel's write when kernels overlap (see ld_l2_f32).
 __device__ __forceinline__ float4 ld_stream_f4(const float4* p) {
     float4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];"
                  : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
                  : "l"(p));
     return v;
 }
 __device__ __forceinline__ uint4 ld_stream_u4(const uint4* p) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(p));
     return v;

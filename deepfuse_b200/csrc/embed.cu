@@ -18,9 +18,10 @@ template <bool VEC4>
 __global__ void __launch_bounds__(kEmbThreads)
 embed_pe_kernel(const int* __restrict__ ids, int rows, int T, int E, int V, const float* __restrict__ table,
                 const float* __restrict__ bias, const float* __restrict__ pe, float* __restrict__ out,
-                int* __restrict__ bad_ids) {
+                int* __restrict__ bad_ids, const int* __restrict__ pos0) {
     griddep_launch_dependents();
     griddep_wait();
+    if (pos0 && pe) pe += size_t(ld_l2_s32(pos0)) * E;  // the sequence's first position, read on the device (decode steps in a graph)
     const int warps_per_block = kEmbThreads / 32;
     const int lane = threadIdx.x & 31;
     for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
@@ -79,9 +80,29 @@ extern "C" df8_status df8_embed_pe_f32(const int32_t* ids, int B, int T, int E, 
     const bool vec4 = (E % 4 == 0) && aligned16(table) && aligned16(out) && aligned16(bias) && aligned16(pe);
     if (vec4)
         DF8_LAUNCH("embed_pe_kernel", embed_pe_kernel<true>, dim3(unsigned(blocks)), dim3(kEmbThreads), 0, st, ids, int(rows), T,
-                   E, V, table, bias, pe, out, bad_ids);
+                   E, V, table, bias, pe, out, bad_ids, static_cast<const int*>(nullptr));
     else
         DF8_LAUNCH("embed_pe_kernel", embed_pe_kernel<false>, dim3(unsigned(blocks)), dim3(kEmbThreads), 0, st, ids, int(rows), T,
-                   E, V, table, bias, pe, out, bad_ids);
+                   E, V, table, bias, pe, out, bad_ids, static_cast<const int*>(nullptr));
+    return DF8_OK;
+}
+
+// One new token per sequence at the position stored in device memory: out[b] = table[ids[b]] + bias + pe_table[*pos_d].
+// For a decode step whose launches are replayed from a CUDA graph (the position cannot be a launch argument then).
+extern "C" df8_status df8_embed_pe_pos_f32(const int32_t* ids, int B, int E, int V, const float* table, const float* bias,
+                                           const float* pe_table, const int32_t* pos_d, float* out, df8_stream stream) {
+    DF8_REQUIRE(B >= 0 && E > 0 && V > 0, "df8_embed_pe_pos_f32: bad shape B=%d E=%d V=%d", B, E, V);
+    if (B == 0) return DF8_OK;
+    DF8_REQUIRE(ids && table && out && pe_table && pos_d, "df8_embed_pe_pos_f32: null buffer");
+    const int warps_per_block = kEmbThreads / 32;
+    const long blocks = (long(B) + warps_per_block - 1) / warps_per_block;
+    const bool vec4 = (E % 4 == 0) && aligned16(table) && aligned16(out) && aligned16(bias) && aligned16(pe_table);
+    cudaStream_t st = as_stream(stream);
+    if (vec4)
+        DF8_LAUNCH("embed_pe_kernel", embed_pe_kernel<true>, dim3(unsigned(blocks)), dim3(kEmbThreads), 0, st, ids, B, 1, E, V, table,
+                   bias, pe_table, out, static_cast<int*>(nullptr), pos_d);
+    else
+        DF8_LAUNCH("embed_pe_kernel", embed_pe_kernel<false>, dim3(unsigned(blocks)), dim3(kEmbThreads), 0, st, ids, B, 1, E, V, table,
+                   bias, pe_table, out, static_cast<int*>(nullptr), pos_d);
     return DF8_OK;
 }

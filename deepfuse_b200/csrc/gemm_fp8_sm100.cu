@@ -168,7 +168,7 @@ __device__ __forceinline__ void load_residual_vec4(float4 (&rs)[8], int lane, in
     for (int it = 0; it < 8; ++it) {
         const int rl = it * 4 + (lane >> 3);
         if ((a.flags & 2) && row0 + rl < a.M && gcol < a.N)
-            rs[it] = *reinterpret_cast<const float4*>(a.residual + size_t(row0 + rl) * a.ldc + gcol);
+            rs[it] = __ldcg(reinterpret_cast<const float4*>(a.residual + size_t(row0 + rl) * a.ldc + gcol));
         else
             rs[it] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
@@ -274,7 +274,7 @@ __device__ __forceinline__ void store_chunk_f32(const float* stg, int lane, int 
                     float v = fmaf(stg[rl * 33 + lane], alpha, b);
                     if (gelu) v = gelu_tanh(v);
                     if (res) {
-                        v += *res;
+                        v += __ldcg(res);
                         res += a.ldc;
                     }
                     amax = fmaxf(amax, fabsf(v));
@@ -484,10 +484,10 @@ __device__ __forceinline__ void load_residual_transposed(float (&rs)[32], const 
     const float* res = args.residual + size_t(col0) * ldc + grow;
     if (row_ok && col0 + 32 <= args.N) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) rs[i] = res[i * ldc];
+        for (int i = 0; i < 32; ++i) rs[i] = __ldcg(res + i * ldc);
     } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) rs[i] = (row_ok && col0 + i < args.N) ? res[i * ldc] : 0.f;
+        for (int i = 0; i < 32; ++i) rs[i] = (row_ok && col0 + i < args.N) ? __ldcg(res + i * ldc) : 0.f;
     }
 }
 
@@ -730,11 +730,11 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
         const int half = e >> 2;   // which of the quarter's two warps: takes chunks half, half+2, ...
         constexpr int kChunks = BN / 64;  // 32-column chunks per warp and tile
         float* stg = staging + e * kStagingFloatsPerWarp;
-        const float alpha = args.scale_a[1] * args.scale_w[1];
+        const float alpha = ld_l2_f32(args.scale_a + 1) * ld_l2_f32(args.scale_w + 1);
         float out_q = 1.f;
         if constexpr (MODE == kOutE4M3 || MODE == kOutE5M2) {
             if (!fused) {
-                const float2 sc = scales_from_amax(*args.q_amax, fp8_max(MODE == kOutE4M3 ? DF8_E4M3 : DF8_E5M2));
+                const float2 sc = scales_from_amax(ld_l2_f32(args.q_amax), fp8_max(MODE == kOutE4M3 ? DF8_E4M3 : DF8_E5M2));
                 out_q = sc.x;
                 if (blockIdx.x == 0 && e == 0 && lane == 0 && args.out_scale) {
                     args.out_scale[0] = sc.x;
@@ -1140,10 +1140,10 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
         const int half = e >> 2;
         constexpr int kChunks = BN / 64;
         float* stg = staging + e * kStagingFloatsPerWarp;
-        const float alpha = args.scale_a[1] * args.scale_w[1];
+        const float alpha = ld_l2_f32(args.scale_a + 1) * ld_l2_f32(args.scale_w + 1);
         float out_q = 1.f;
         if constexpr (MODE == kOutE4M3 || MODE == kOutE5M2) {
-            const float2 sc = scales_from_amax(*args.q_amax, fp8_max(MODE == kOutE4M3 ? DF8_E4M3 : DF8_E5M2));
+            const float2 sc = scales_from_amax(ld_l2_f32(args.q_amax), fp8_max(MODE == kOutE4M3 ? DF8_E4M3 : DF8_E5M2));
             out_q = sc.x;
             if (blockIdx.x == 0 && e == 0 && lane == 0 && args.out_scale) {
                 args.out_scale[0] = sc.x;

@@ -59,7 +59,7 @@ layernorm_kernel(const float* __restrict__ x, int rows, int C, const float* __re
     __shared__ float red[kLnThreads / 32];
     float q = 1.f;
     if constexpr (MODE == 2) {
-        const float2 s = scales_from_amax(*amax_in, fp8_max(KIND));
+        const float2 s = scales_from_amax(ld_l2_f32(amax_in), fp8_max(KIND));
         q = s.x;
         if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) {
             scale_out[0] = s.x;
@@ -175,7 +175,7 @@ layernorm_rows_kernel(const float* __restrict__ x, int rows, int C, const float*
     const int c4 = C >> 2;
     float q = 1.f;
     if constexpr (MODE == 2) {
-        const float2 s = scales_from_amax(*amax_in, fp8_max(KIND));
+        const float2 s = scales_from_amax(ld_l2_f32(amax_in), fp8_max(KIND));
         q = s.x;
         if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) {
             scale_out[0] = s.x;
@@ -248,6 +248,100 @@ layernorm_rows_kernel(const float* __restrict__ x, int rows, int C, const float*
             }
         }
     }
+}
+
+// At most 32 rows (a decode step's one token per sequence): ONE CTA, a warp per row with the normalised row kept in
+// registers across the block-wide maximum, so statistics, max|y|, scale and codes take one launch and x is read
+// once.  Same arithmetic, in the same order, as the two passes of layernorm_rows_kernel (MODE 1 then MODE 2).
+template <int KIND, int V4>
+__global__ void __launch_bounds__(1024)
+layernorm_quantize_one_cta_kernel(const float* __restrict__ x, int rows, int C, const float* __restrict__ gamma,
+                                  const float* __restrict__ beta, float eps, float* __restrict__ amax_out,
+                                  uint8_t* __restrict__ codes, float* __restrict__ scale_out) {
+    griddep_launch_dependents();
+    griddep_wait();
+    const int lane = threadIdx.x & 31, row = threadIdx.x >> 5;
+    const int c4 = C >> 2;
+    __shared__ float warp_amax[32];
+    const float before = ld_l2_f32(amax_out);  // normally 0 (cleared by the caller's convention); kept as a lower bound
+    float4 o[V4];
+    float mx = 0.f;
+    if (row < rows) {
+        const float4* xr = reinterpret_cast<const float4*>(x + size_t(row) * C);
+        float4 v[V4];
+#pragma unroll
+        for (int j = 0; j < V4; ++j) {
+            const int i = lane + 32 * j;
+            v[j] = i < c4 ? ld_stream_f4(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < V4; ++j) sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+        const float mean = warp_sum(sum) / float(C);
+        float sq = 0.f;
+#pragma unroll
+        for (int j = 0; j < V4; ++j) {
+            if (lane + 32 * j < c4) {
+                const float a = v[j].x - mean, b = v[j].y - mean, c = v[j].z - mean, d = v[j].w - mean;
+                sq += (a * a + b * b) + (c * c + d * d);
+            }
+        }
+        const float rstd = rsqrtf(warp_sum(sq) / float(C) + eps);
+#pragma unroll
+        for (int j = 0; j < V4; ++j) {
+            const int i = lane + 32 * j;
+            o[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < c4) {
+                float4 g = make_float4(1.f, 1.f, 1.f, 1.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (gamma) g = __ldg(reinterpret_cast<const float4*>(gamma) + i);
+                if (beta) b = __ldg(reinterpret_cast<const float4*>(beta) + i);
+                o[j].x = fmaf((v[j].x - mean) * rstd, g.x, b.x);
+                o[j].y = fmaf((v[j].y - mean) * rstd, g.y, b.y);
+                o[j].z = fmaf((v[j].z - mean) * rstd, g.z, b.z);
+                o[j].w = fmaf((v[j].w - mean) * rstd, g.w, b.w);
+                mx = fmaxf(mx, fmaxf(fmaxf(fabsf(o[j].x), fabsf(o[j].y)), fmaxf(fabsf(o[j].z), fabsf(o[j].w))));
+            }
+        }
+    }
+    mx = warp_max(mx);
+    if (lane == 0) warp_amax[row] = mx;
+    __syncthreads();
+    const float amax = fmaxf(before, warp_max(warp_amax[lane]));
+    const float2 s = scales_from_amax(amax, fp8_max(KIND));
+    if (threadIdx.x == 0) {
+        if (amax > 0.f) atomic_max_nonneg(amax_out, amax);
+        if (scale_out) {
+            scale_out[0] = s.x;
+            scale_out[1] = s.y;
+        }
+    }
+    if (row < rows) {
+        const float q = s.x;
+#pragma unroll
+        for (int j = 0; j < V4; ++j) {
+            const int i = lane + 32 * j;
+            if (i < c4)
+                reinterpret_cast<uint32_t*>(codes + size_t(row) * C)[i] = cvt_f32x4_to_fp8x4<KIND>(
+                    __fmul_rn(o[j].x, q), __fmul_rn(o[j].y, q), __fmul_rn(o[j].z, q), __fmul_rn(o[j].w, q));
+        }
+    }
+}
+
+template <int KIND>
+bool launch_one_cta(const float* x, int rows, int C, const float* gamma, const float* beta, float eps, uint8_t* codes,
+                    float* scale_out, float* amax, cudaStream_t st) {
+    if (rows > 32 || C > 1024) return false;
+    if (const char* e = getenv("DF8_LN_ONE_CTA"))
+        if (e[0] == '0') return false;
+#define DF8_LN_ONE(V4)                                                                                               \
+    (void)launch_kernel((layernorm_quantize_one_cta_kernel<KIND, V4>), dim3(1), dim3(1024), 0, st, x, rows, C, gamma, beta, \
+                        eps, amax, codes, scale_out)
+    if (C <= 256) DF8_LN_ONE(2);
+    else if (C <= 512) DF8_LN_ONE(4);
+    else if (C <= 768) DF8_LN_ONE(6);
+    else DF8_LN_ONE(8);
+#undef DF8_LN_ONE
+    return true;
 }
 
 template <int MODE, int KIND>
@@ -547,6 +641,10 @@ df8_status launch_ln_quant(const float* x, int rows, int cols, const float* gamm
                            uint8_t* codes, float* scale_out, float* amax_out, float2* row_stats, cudaStream_t st) {
     const int grid = ln_grid(rows);
     const bool fast = fast_ok(cols, x, gamma, beta, nullptr) && (reinterpret_cast<uintptr_t>(codes) & 3u) == 0;
+    if (fast && launch_one_cta<KIND>(x, rows, cols, gamma, beta, eps, codes, scale_out, amax_out, st)) {
+        DF8_LAUNCH_CHECK("layernorm_quantize_one_cta_kernel");
+        return DF8_OK;
+    }
     if (fast && launch_resident<KIND>(x, rows, cols, gamma, beta, eps, codes, scale_out, amax_out, st)) return DF8_OK;
     if (fast && cols <= 4096) {
         launch_rows_kernel<1, KIND>(x, rows, cols, gamma, beta, eps, nullptr, amax_out, row_stats, nullptr, nullptr,

@@ -114,7 +114,7 @@ shard_quantize_kernel(const float* __restrict__ x, int rows, int n, const float2
                       uint8_t* __restrict__ codes, float* __restrict__ scale_out) {
     griddep_launch_dependents();
     griddep_wait();
-    const float2 sc = scales_from_amax(*amax_in, fp8_max(KIND));
+    const float2 sc = scales_from_amax(ld_l2_f32(amax_in), fp8_max(KIND));
     if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) {
         scale_out[0] = sc.x;
         scale_out[1] = sc.y;

@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(kThreads) quantize_f32_kernel(const float* __r
                                                                 float* __restrict__ scale_out) {
     griddep_launch_dependents();
     griddep_wait();
-    const float2 s = scales_from_amax(*amax_in, fp8_max(KIND));
+    const float2 s = scales_from_amax(ld_l2_f32(amax_in), fp8_max(KIND));
     if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) {
         scale_out[0] = s.x;
         scale_out[1] = s.y;
@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(kThreads) quantize_f32_kernel(const float* __r
 
 __device__ __forceinline__ uint32_t ld_stream_u32(const uint32_t* p) {
     uint32_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p));
     return v;
 }
 
@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(kThreads) dequantize_f32_kernel(const uint8_t*
                                                                   float* __restrict__ y) {
     griddep_launch_dependents();
     griddep_wait();
-    const float dq = scale[1];
+    const float dq = ld_l2_f32(scale + 1);
     const size_t n4 = n >> 2;
     const uint32_t* c4 = reinterpret_cast<const uint32_t*>(codes);
     float4* y4 = reinterpret_cast<float4*>(y);

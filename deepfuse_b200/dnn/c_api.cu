@@ -785,6 +785,10 @@ extern "C" int dnn_gpt2_end_decode(dnn_gpt2* m) {
     return guarded([&] { m->model->end_decode(); });
 }
 
+extern "C" int dnn_gpt2_decode_graph_active(dnn_gpt2* m, int* active) {
+    return guarded([&] { *active = m->model->decode_graph_active() ? 1 : 0; });
+}
+
 // ---- CrossEntropyLoss ---------------------------------------------------------------------------------------
 
 // logits_d [rows, pitch] (pitch == classes: dense); dense targets [rows, classes] or class indices [rows], one of the

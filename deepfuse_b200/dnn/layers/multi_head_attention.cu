@@ -1,5 +1,7 @@
 #include "dnn/layers/multi_head_attention.cuh"
 
+#include <cstdlib>
+
 #include <stdexcept>
 
 namespace dnn {
@@ -17,7 +19,7 @@ MultiHeadAttentionLayer<TT>::MultiHeadAttentionLayer(int embed_dim, int num_head
       last_q_({1, 1}),
       last_attn_({1, 1}),
       attn_f32_({1}),
-      amax_({1}) {
+      amax_({2}) {
     if (embed_dim <= 0 || num_heads <= 0) throw std::runtime_error("embed_dim and num_heads must be positive");
     if (embed_dim % num_heads != 0) throw std::runtime_error("embed_dim must be divisible by num_heads");
 }
@@ -86,13 +88,25 @@ void MultiHeadAttentionLayer<TT>::decode_quantized(const fp8::Quantized& xq, int
     // the new token's QKV, quantised per tensor like every QKV tensor of the 8-bit path
     float* am = fp8::amax_slot(amax_.data());
     qkv_proj_.forward_codes_skinny(xq.codes.data(), xq.kind, xq.scale.data(), B, DF8_EPI_AMAX, nullptr, qkv_f32_.data(), am);
-    fp8::quantize_with_amax(qkv_f32_.data(), qkv_f32_.numel(), act, am, qkvq_);
-    utils::CHECK_DF8(df8_kv_cache_append(qkvq_.codes.data(), qkvq_.scale.data(), B, 1, num_heads_, head_dim_, kv_len_,
-                                         kv_->max_len, kv_->k.data(), kv_->v.data(), kv_->row_dq.data(), fp8::stream()));
-    float* am2 = fp8::amax_slot(amax_.data());
-    utils::CHECK_DF8(df8_attention_decode_fp8(qkvq_.codes.data(), qkvq_.kind, qkvq_.scale.data(), kv_->k.data(),
-                                              kv_->v.data(), kv_->row_dq.data(), B, num_heads_, head_dim_, kv_len_ + 1,
-                                              kv_->max_len, attn_f32_.data(), am2, fp8::stream()));
+    const char* unfused = getenv("DF8_DECODE_UNFUSED");
+    if (unfused && unfused[0] == '1') {
+        fp8::quantize_with_amax(qkv_f32_.data(), qkv_f32_.numel(), act, am, qkvq_);
+        utils::CHECK_DF8(df8_kv_cache_append_pos(qkvq_.codes.data(), qkvq_.scale.data(), B, num_heads_, head_dim_, pos_d_,
+                                                 kv_->max_len, kv_->k.data(), kv_->v.data(), kv_->row_dq.data(), fp8::stream()));
+        float* amu = fp8::amax_slot(amax_.data() + 1);
+        utils::CHECK_DF8(df8_attention_decode_fp8_pos(qkvq_.codes.data(), qkvq_.kind, qkvq_.scale.data(), kv_->k.data(),
+                                                      kv_->v.data(), kv_->row_dq.data(), B, num_heads_, head_dim_, kv_len_ + 1,
+                                                      pos_d_, kv_->max_len, attn_f32_.data(), amu, fp8::stream()));
+        fp8::quantize_with_amax(attn_f32_.data(), attn_f32_.numel(), act, amu, attnq_);
+        out_proj_.forward_codes_skinny(attnq_.codes.data(), attnq_.kind, attnq_.scale.data(), B,
+                                       residual ? DF8_EPI_RESIDUAL : 0, residual, out, nullptr);
+        return;
+    }
+    // quantise + cache append + attention in one launch (the codes are those of quantize_with_amax)
+    float* am2 = fp8::amax_slot(amax_.data() + 1);  // read and written by the same launch: never the slot of `am`
+    utils::CHECK_DF8(df8_attention_decode_fused_f32(qkv_f32_.data(), am, act, kv_->k.data(), kv_->v.data(),
+                                                    kv_->row_dq.data(), B, num_heads_, head_dim_, kv_len_ + 1, pos_d_,
+                                                    kv_->max_len, attn_f32_.data(), am2, fp8::stream()));
     fp8::quantize_with_amax(attn_f32_.data(), attn_f32_.numel(), act, am2, attnq_);
     out_proj_.forward_codes_skinny(attnq_.codes.data(), attnq_.kind, attnq_.scale.data(), B,
                                    residual ? DF8_EPI_RESIDUAL : 0, residual, out, nullptr);

@@ -71,6 +71,9 @@ public:
     };
     void attach_kv_cache(KvCache* cache) { kv_ = cache; }
     void set_kv_len(int len) { kv_len_ = len; }
+    // decode_quantized reads the position from this device integer instead of kv_len (null = the host value): a
+    // step's launches then do not depend on the position and can be replayed from a CUDA graph
+    void set_decode_position(const int* pos_d) { pos_d_ = pos_d; }
     void decode_quantized(const fp8::Quantized& xq, int B, const float* residual, float* out);
 
 private:
@@ -90,6 +93,7 @@ private:
     fp8::Quantized xq_, qkvq_, attnq_;
     KvCache* kv_ = nullptr;
     int kv_len_ = 0;
+    const int* pos_d_ = nullptr;
     tensor<float> qkv_f32_{{0}};
 };
 

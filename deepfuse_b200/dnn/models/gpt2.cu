@@ -203,7 +203,27 @@ tensor<T> Gpt2<T>::prefill(const tensor<int>& ids, int max_len, bool check_ids) 
     tensor<T> x = token_embedding_->forward_with_positions(ids, positional_encoding_->table().data(), check_ids);
     for (auto& blk : transformer_blocks_) blk->forward_inplace(x.data(), B, T_len);
     kv_len_ = T_len;
+    const int pos = T_len;
+    utils::CHECK_CUDA_EX(cudaMemcpyAsync(dec_pos_.data(), &pos, sizeof(int), cudaMemcpyHostToDevice, Cuda::stream()));
+    utils::CHECK_CUDA_EX(cudaStreamSynchronize(Cuda::stream()));  // `pos` is a local
+    for (auto& blk : transformer_blocks_) blk->attention().set_decode_position(dec_pos_.data());
     return last_rows_logits(x.data(), B, T_len);
+}
+
+// One decode step on the persistent buffers: every launch reads the position from dec_pos_, so the sequence of
+// launches (and every argument) is the same from step to step.
+template <typename T>
+void Gpt2<T>::decode_body(int B) {
+    fp8::PassScope amax_slots;
+    const int E = hidden_dim_;
+    utils::CHECK_DF8(df8_embed_pe_pos_f32(dec_ids_.data(), B, E, vocab_size_, token_embedding_->weights()->data(),
+                                          token_embedding_->bias()->data(), positional_encoding_->table().data(),
+                                          dec_pos_.data(), dec_x_.data(), fp8::stream()));
+    for (auto& blk : transformer_blocks_) blk->decode_inplace(dec_x_.data(), B);
+    fp8::quantize(dec_x_.data(), size_t(B) * E, fp8::policy().activation_kind, head_q_);
+    final_fc_->forward_codes_skinny(head_q_.codes.data(), head_q_.kind, head_q_.scale.data(), B, 0, nullptr,
+                                    dec_logits_.data(), nullptr);
+    utils::CHECK_DF8(df8_position_advance(dec_pos_.data(), fp8::stream()));
 }
 
 template <typename T>
@@ -212,19 +232,51 @@ tensor<T> Gpt2<T>::decode_step(const tensor<int>& next_ids, bool check_ids) {
     const int B = kv_[0]->batch;
     if (next_ids.numel() != size_t(B)) throw std::runtime_error("Gpt2::decode_step: one token id per sequence of the prefill");
     if (kv_len_ + 1 > kv_[0]->max_len) throw std::runtime_error("Gpt2::decode_step: the KV cache is full");
-    tensor<int> ids({B, 1});
-    utils::CHECK_CUDA_EX(cudaMemcpyAsync(ids.data(), next_ids.data(), size_t(B) * sizeof(int), cudaMemcpyDeviceToDevice,
-                                         Cuda::stream()));
-    fp8::PassScope amax_slots;
-    // position kv_len_: its row of the sinusoidal table
-    tensor<T> x = token_embedding_->forward_with_positions(
-        ids, positional_encoding_->table().data() + size_t(kv_len_) * hidden_dim_, check_ids);
-    for (auto& blk : transformer_blocks_) {
-        blk->attention().set_kv_len(kv_len_);
-        blk->decode_inplace(x.data(), B);
+    cudaStream_t st = Cuda::stream();
+    if (check_ids) {  // upstream validates ids on every call (token_embedding.cu:131-138)
+        std::vector<int> h(static_cast<size_t>(B), 0);
+        utils::CHECK_CUDA_EX(cudaMemcpyAsync(h.data(), next_ids.data(), size_t(B) * sizeof(int), cudaMemcpyDeviceToHost, st));
+        utils::CHECK_CUDA_EX(cudaStreamSynchronize(st));
+        int bad = 0;
+        for (int id : h) bad += (id < 0 || id >= vocab_size_) ? 1 : 0;
+        if (bad) throw std::runtime_error("Invalid token ID: " + std::to_string(bad) + " id(s) outside the vocabulary");
     }
+    if (dec_ids_.numel() != size_t(B)) {
+        dec_ids_ = tensor<int>({B, 1});
+        dec_x_ = tensor<T>({B, hidden_dim_});
+        dec_logits_ = tensor<T>({B, vocab_size_});
+    }
+    utils::CHECK_CUDA_EX(cudaMemcpyAsync(dec_ids_.data(), next_ids.data(), size_t(B) * sizeof(int), cudaMemcpyDeviceToDevice, st));
+    for (auto& blk : transformer_blocks_) blk->attention().set_kv_len(kv_len_);  // host mirror (bounds checks)
+
+    const char* env = getenv("DF8_DECODE_GRAPH");
+    const bool want_graph = dec_graph_ok_ && dec_steps_ >= 1 && st != nullptr && !(env && env[0] == '0');
+    if (want_graph && !dec_graph_) {
+        // the first step ran eagerly and sized every buffer; capture the second and replay it from then on
+        cudaGraph_t graph = nullptr;
+        if (cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed) == cudaSuccess) {
+            bool body_ok = true;
+            try {
+                decode_body(B);
+            } catch (...) {
+                body_ok = false;
+            }
+            const cudaError_t end = cudaStreamEndCapture(st, &graph);
+            if (!(body_ok && end == cudaSuccess && graph && cudaGraphInstantiate(&dec_graph_, graph, 0) == cudaSuccess)) {
+                dec_graph_ = nullptr;
+                dec_graph_ok_ = false;  // eager from here on
+            }
+            if (graph) cudaGraphDestroy(graph);
+        } else {
+            dec_graph_ok_ = false;
+        }
+        (void)cudaGetLastError();
+    }
+    if (dec_graph_) utils::CHECK_CUDA_EX(cudaGraphLaunch(dec_graph_, st));
+    else decode_body(B);
+    ++dec_steps_;
     ++kv_len_;
-    return last_rows_logits(x.data(), B, 1);
+    return dec_logits_.clone();
 }
 
 template <typename T>
@@ -232,8 +284,15 @@ void Gpt2<T>::end_decode() {
     for (auto& blk : transformer_blocks_) {
         blk->attention().attach_kv_cache(nullptr);
         blk->attention().set_kv_len(0);
+        blk->attention().set_decode_position(nullptr);
     }
     if (!kv_.empty()) utils::CHECK_CUDA_EX(cudaStreamSynchronize(Cuda::stream()));  // the caches may still be read
+    if (dec_graph_) {
+        cudaGraphExecDestroy(dec_graph_);
+        dec_graph_ = nullptr;
+    }
+    dec_graph_ok_ = true;
+    dec_steps_ = 0;
     kv_.clear();
     kv_len_ = 0;
 }

@@ -97,6 +97,7 @@ public:
     tensor<T> prefill(const tensor<int>& ids, int max_len = 0, bool check_ids = true);
     tensor<T> decode_step(const tensor<int>& next_ids, bool check_ids = true);
     int decode_position() const { return kv_len_; }
+    bool decode_graph_active() const { return dec_graph_ != nullptr; }
     void end_decode();
 
     // Layer streaming (README.md:212-220 sketches `layer->load_weights_to_gpu()`; no such code exists
@@ -142,6 +143,17 @@ private:
     int stream_slots_ = 0;
     std::vector<std::unique_ptr<typename MultiHeadAttentionLayer<T>::KvCache>> kv_;
     int kv_len_ = 0;
+    // decode steps: the position lives in device memory, the step's buffers persist, and from the second step on the
+    // step's launches are replayed from a CUDA graph captured on the model's stream (a step is ~165 kernels of a few
+    // microseconds; issued one by one it is bound by the host).  DF8_DECODE_GRAPH=0 in the environment or the legacy
+    // default stream keep the launches eager.
+    void decode_body(int B);
+    tensor<int> dec_pos_{{1}};
+    tensor<int> dec_ids_{{0}};
+    tensor<T> dec_x_{{0}}, dec_logits_{{0}};
+    cudaGraphExec_t dec_graph_ = nullptr;
+    bool dec_graph_ok_ = true;
+    int dec_steps_ = 0;
     tensor<T> last_rows_logits(const float* x, int B, int T_len);
     bool stage_timing_ = false;
     cudaEvent_t head_ev_[2] = {nullptr, nullptr};

@@ -204,6 +204,31 @@ df8_status df8_attention_decode_fp8(const uint8_t* qkv_codes, df8_kind kind, con
                                     const uint8_t* v_cache, const float* row_dq, int B, int H, int D, int n_keys, int Tmax,
                                     float* out, float* out_amax, df8_stream stream);
 
+/* The decode step's position read from DEVICE memory, for steps whose launches are replayed from a CUDA graph (a
+ * captured launch argument would freeze the position): *pos_d = number of positions already cached.
+ *   df8_embed_pe_pos_f32          out[b] = table[ids[b]] + bias + pe_table[*pos_d]        (one token per sequence)
+ *   df8_kv_cache_append_pos       the new position's K / V codes into row *pos_d of the caches
+ *   df8_attention_decode_fp8_pos  pos_d != null: attends over *pos_d + 1 keys (n_keys ignored); null: as above
+ *   df8_position_advance          *pos_d += 1 */
+df8_status df8_embed_pe_pos_f32(const int32_t* ids, int B, int E, int V, const float* table, const float* bias,
+                                const float* pe_table, const int32_t* pos_d, float* out, df8_stream stream);
+df8_status df8_kv_cache_append_pos(const uint8_t* qkv_codes, const float* scale, int B, int H, int D,
+                                   const int32_t* pos_d, int Tmax, uint8_t* k_cache, uint8_t* v_cache, float* row_dq,
+                                   df8_stream stream);
+df8_status df8_attention_decode_fp8_pos(const uint8_t* qkv_codes, df8_kind kind, const float* scale,
+                                        const uint8_t* k_cache, const uint8_t* v_cache, const float* row_dq, int B,
+                                        int H, int D, int n_keys, const int32_t* pos_d, int Tmax, float* out,
+                                        float* out_amax, df8_stream stream);
+df8_status df8_position_advance(int32_t* pos_d, df8_stream stream);
+
+/* The step's attention straight from the fp32 QKV projection [B, 3E] and its max|.| (device scalar): the kernel
+ * quantises per tensor (the codes df8_quantize_f32 would give with that maximum), writes the new position's key /
+ * value codes and dequantisation factor into row n_keys - 1 of the caches (row *pos_d when pos_d != null) and attends
+ * over all n_keys positions: df8_quantize_f32 + df8_kv_cache_append + df8_attention_decode_fp8 in one launch. */
+df8_status df8_attention_decode_fused_f32(const float* qkv_f32, const float* qkv_amax, df8_kind kind, uint8_t* k_cache,
+                                          uint8_t* v_cache, float* row_dq, int B, int H, int D, int n_keys,
+                                          const int32_t* pos_d, int Tmax, float* out, float* out_amax, df8_stream stream);
+
 /* ---- stand-alone masked softmax ------------------------------------------------------------
  * Replaces the launch of softmax_masked_kernel (dnn/layers/softmax_layer.cu:26-81, launched at
  * :154-167) for SoftmaxLayer::forward: x [B,H,T,T] fp32, optional additive mask [mask_b,1,T,T]

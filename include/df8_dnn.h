@@ -133,6 +133,9 @@ int dnn_embedding_forward(int V, int E, int max_len, const float* table_h, const
 int dnn_gpt2_prefill(dnn_gpt2* m, const int32_t* ids_d, int B, int T, int max_len, float** logits_d);
 int dnn_gpt2_decode_step(dnn_gpt2* m, const int32_t* next_ids_d, int B, int check_ids, float** logits_d);
 int dnn_gpt2_end_decode(dnn_gpt2* m);
+/* 1 once decode steps are replayed from a CUDA graph (from the third step after a prefill when the model's stream is
+ * not the legacy default stream and DF8_DECODE_GRAPH is not 0), else 0 */
+int dnn_gpt2_decode_graph_active(dnn_gpt2* m, int* active);
 
 /* ---- CrossEntropyLoss<float> (dnn/losses/cross_entropy.cuh:8-20): logits_d [rows, pitch] (pitch == classes: dense),
  * dense targets [rows, classes] or class indices [rows] (one of the two); the mean loss goes to *loss_h, the

@@ -74,13 +74,24 @@ def test_cache_and_one_query_attention(df8, oracle, cuda, B, H, D, n_prefill, st
         qkv = oracle.fill_normal(B * 3 * E, seed=10 + step, std=1.0 + step).reshape(B, 3 * E)  # another scale each step
         c, s = oracle.quantize(qkv, kind)
         cd, sd = t(c), t(s)
+        kc2, vc2, dq2 = kc.clone(), vc.clone(), row_dq.clone()  # for the one-launch form below
         df8.check(lib.df8_kv_cache_append(df8.ptr(cd), df8.ptr(sd), B, 1, H, D, n, Tmax, df8.ptr(kc), df8.ptr(vc),
                                           df8.ptr(row_dq), st))
         out = torch.full((B, E), float("nan"), device=cuda)
         amax = torch.zeros(1, device=cuda)
         df8.check(lib.df8_attention_decode_fp8(df8.ptr(cd), kind, df8.ptr(sd), df8.ptr(kc), df8.ptr(vc), df8.ptr(row_dq), B, H,
                                                D, n + 1, Tmax, df8.ptr(out), df8.ptr(amax), st))
+        # quantise + append + attend in one launch from the fp32 QKV rows and their maximum: the same bits everywhere
+        out2 = torch.full((B, E), float("nan"), device=cuda)
+        amax2 = torch.zeros(1, device=cuda)
+        qd, qa = t(qkv), t(np.array([np.abs(qkv).max()], np.float32))
+        pos = torch.tensor([n], dtype=torch.int32, device=cuda) if step % 2 else None
+        df8.check(lib.df8_attention_decode_fused_f32(df8.ptr(qd), df8.ptr(qa), kind, df8.ptr(kc2), df8.ptr(vc2), df8.ptr(dq2),
+                                                     B, H, D, 1 if pos is not None else n + 1, df8.ptr(pos), Tmax,
+                                                     df8.ptr(out2), df8.ptr(amax2), st))
         torch.cuda.synchronize()
+        assert torch.equal(out2, out) and amax2.item() == amax.item()
+        assert torch.equal(kc2, kc) and torch.equal(vc2, vc) and torch.equal(dq2, row_dq)
         pieces.append((c.reshape(B, 1, 3 * E), float(s[1])))
         k = np.concatenate([lut[p[:, :, E:2 * E]] * np.float32(dq) for p, dq in pieces], axis=1)
         v = np.concatenate([lut[p[:, :, 2 * E:]] * np.float32(dq) for p, dq in pieces], axis=1)
@@ -143,3 +154,51 @@ def test_prefill_and_decode_steps_against_the_oracle(df8, oracle, cuda, act_kind
     assert np.array_equal(again, got[0])
     assert df8.status_word() == (0, 0)
     model.close()
+
+
+def test_graph_replayed_steps_equal_eager_steps(df8, oracle, cuda, monkeypatch):
+    """On a stream of its own the model captures the second decode step as a CUDA graph and replays it: same logits,
+    bit for bit, as the eager launches (DF8_DECODE_GRAPH=0), across steps that change the position, and a new prefill
+    drops the graph."""
+    import torch
+    from oracle import gpt2_ref
+
+    cfg = dict(vocab=300, max_seq_len=48, layers=2, heads=2, hidden=128, ffn=256)
+    B, T, steps = 2, 9, 6
+    prm = gpt2_ref.make_params(cfg, seed=77, std=0.05)
+    ids = oracle.fill_token_ids(B * T, seed=6, vocab=300).reshape(B, T)
+    nxt = [oracle.fill_token_ids(B, seed=80 + i, vocab=300) for i in range(steps)]
+    side = torch.cuda.Stream(device=cuda)
+    runs = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("DF8_DECODE_GRAPH", mode)
+        model = df8.Gpt2(**cfg)
+        try:
+            model.load_params(prm)
+            with torch.cuda.stream(side):
+                model.set_stream(side)
+                out = [df8.device_view(torch, model.prefill(torch.from_numpy(ids).to(cuda)), (B, 300)).clone()]
+                active = []
+                for n in nxt:
+                    out.append(df8.device_view(torch, model.decode_step(torch.from_numpy(n).to(cuda), check_ids=False),
+                                               (B, 300)).clone())
+                    active.append(model.decode_graph_active())
+                side.synchronize()
+                if mode == "1":
+                    assert active == [False] + [True] * (steps - 1), active
+                    # a second prompt: the graph of the first is gone, a new one is captured
+                    model.prefill(torch.from_numpy(ids).to(cuda))
+                    assert not model.decode_graph_active()
+                    a = df8.device_view(torch, model.decode_step(torch.from_numpy(nxt[0]).to(cuda)), (B, 300)).clone()
+                    side.synchronize()
+                    assert torch.equal(a, out[1])
+                else:
+                    assert active == [False] * steps
+                model.end_decode()
+            runs[mode] = [o.cpu().numpy() for o in out]
+        finally:
+            model.close()
+    for i, (g, e) in enumerate(zip(runs["1"], runs["0"])):
+        assert np.isfinite(g).all()
+        assert np.array_equal(g, e), i
+    assert df8.status_word() == (0, 0)

@@ -28,11 +28,13 @@ def test_layernorm_vs_oracle(df8, oracle, cuda, rows, cols, affine):
 
 
 @pytest.mark.parametrize("kind", [0, 1])
-@pytest.mark.parametrize("rows,cols", [(64, 768), (130, 1024), (17, 4096), (9, 770)])
+@pytest.mark.parametrize("rows,cols", [(64, 768), (130, 1024), (17, 4096), (9, 770), (32, 768), (5, 768), (1, 256), (17, 1024),
+                                       (32, 520), (33, 768)])
 def test_layernorm_quantize_vs_oracle(df8, oracle, cuda, kind, rows, cols):
     """Fused LN + quantise.  The codes are those of quantising the kernel's own LayerNorm output (bit-exact,
     checked through df8_layernorm_f32 + df8_quantize_f32); against the oracle's LayerNorm, whose row sums
-    run in a different order, codes may differ by one step on a few elements."""
+    run in a different order, codes may differ by one step on a few elements.  Up to 32 rows of at most 1024
+    columns take the one-CTA kernel (a decode step's shape)."""
     import torch
 
     x = oracle.fill_normal(rows * cols, seed=3 * rows + cols, std=1.5).reshape(rows, cols)

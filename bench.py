@@ -1102,6 +1102,7 @@ def decode_report(torch, df8, dev, peaks, batch=32, prompt=128, steps=64):
     finally:
         ctx.__exit__(None, None, None)
         torch.cuda.current_stream().wait_stream(side)
+        model.set_stream(torch.cuda.current_stream())  # the library's stream is process-wide
         model.close()
 
 

@@ -478,6 +478,9 @@ class Gpt2:
         return int(dnn_lib().dnn_gpt2_streamed_bytes(self.h))
 
     def set_stream(self, stream=None):
+        """The stream every dnn:: object of this process launches on from now on (as upstream's Cuda context holds
+        one stream): not a property of this model.  None = torch's current stream.  Hand the default back before the
+        stream is destroyed."""
         dnn_check(dnn_lib().dnn_set_stream(stream_ptr(stream)), "dnn_set_stream")
 
     def forward_logits(self, ids_dev, check_ids=True) -> int:

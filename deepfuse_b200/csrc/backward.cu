@@ -137,7 +137,7 @@ __global__ void colsum_final_kernel(const float* __restrict__ partial, int cols,
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c < cols) {
         float t = 0.f;
-        for (int k = 0; k < kSumChunks; ++k) t += partial[size_t(k) * cols + c];
+        for (int k = 0; k < kSumChunks; ++k) t += __ldcg(partial + size_t(k) * cols + c);
         out[c] = t;
     }
 }

@@ -123,7 +123,7 @@ shard_quantize_kernel(const float* __restrict__ x, int rows, int n, const float2
     const int warps = (gridDim.x * kThreads) >> 5;
     const int n4 = n >> 2;  // n % 4 == 0 (checked by the entry point)
     for (int r = (blockIdx.x * kThreads + threadIdx.x) >> 5; r < rows; r += warps) {
-        const float2 st = row_stats[r];
+        const float2 st = __ldcg(row_stats + r);
         const float4* row = reinterpret_cast<const float4*>(x + size_t(r) * n);
         uint32_t* out = reinterpret_cast<uint32_t*>(codes + size_t(r) * n);
         for (int i = lane; i < n4; i += 32) {

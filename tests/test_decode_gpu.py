@@ -197,6 +197,7 @@ def test_graph_replayed_steps_equal_eager_steps(df8, oracle, cuda, monkeypatch):
                 model.end_decode()
             runs[mode] = [o.cpu().numpy() for o in out]
         finally:
+            model.set_stream(None)  # the library's stream is process-wide: back to torch's current stream
             model.close()
     for i, (g, e) in enumerate(zip(runs["1"], runs["0"])):
         assert np.isfinite(g).all()

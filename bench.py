@@ -554,7 +554,7 @@ class Gpt2Workload:
         if layers:
             self.c["layers"] = layers
         self.n_gpus = n_gpus
-        self.slots = slots
+        self.slots = int(os.environ.get("DF8_BENCH_STREAM_SLOTS", slots))  # device slots of the layer streamer (gpt2m)
         # gpt2s: weak scaling, 8 sequences per GPU; gpt2m: the fixed batch of 32 sharded across the GPUs
         self.strong = name == "gpt2m"
         self.B = batch or (max(1, self.c["batch"] // n_gpus) if self.strong else self.c["batch"])

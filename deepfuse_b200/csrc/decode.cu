@@ -91,7 +91,7 @@ attention_decode_kernel(const uint8_t* __restrict__ q_codes, const float* __rest
                         float* __restrict__ out_amax, const int* __restrict__ pos) {
     griddep_launch_dependents();
     griddep_wait();
-    if (pos) n_keys = min(ld_l2_s32(pos) + 1, Tmax);  // the new position's own key included
+    const int pos_v = pos ? ld_l2_s32(pos) : 0;  // (consumed below, after the other requests are out)
     constexpr int DPL = D / 32;             // output dimensions per lane in the final combine
     constexpr int CH = D / 16, KPI = 32 / CH;  // 16-byte pieces per row, keys per pass of the p . V loop
     const int b = blockIdx.x / H, h = blockIdx.x % H;
@@ -104,15 +104,31 @@ attention_decode_kernel(const uint8_t* __restrict__ q_codes, const float* __rest
     // scores are kept in the log2 domain: s * log2(e) / sqrt(D), the query's scale folded in
     int j_new = -1;
     float dq_new = 0.f;
+    if constexpr (!FUSED)
+        if (pos) n_keys = min(pos_v + 1, Tmax);  // the new position's own key included
     if constexpr (FUSED) {
+        // (the row's values are requested before the maximum is looked at: a warp issues in order, and the scale's
+        // divisions would hold these loads back by a memory round trip)
+        const float* row = qkv_f32 + size_t(b) * 3 * E + h * D;
+        constexpr int kMine = (3 * D + 32 * kDecodeWarps - 1) / (32 * kDecodeWarps);
+        float mine[kMine];
+#pragma unroll
+        for (int u = 0; u < kMine; ++u) {
+            const int i = threadIdx.x + u * 32 * kDecodeWarps;
+            const int part = i / D, d = i - part * D;
+            mine[u] = i < 3 * D ? __ldcg(row + size_t(part) * E + d) : 0.f;
+        }
         const float2 sc = scales_from_amax(ld_l2_f32(qkv_amax), fp8_max(KIND));
+        if (pos) n_keys = min(pos_v + 1, Tmax);  // the new position's own key included
         const float qs = sc.y * rsqrtf(float(D)) * 1.4426950408889634f;
         j_new = n_keys - 1;
         dq_new = sc.y;
-        const float* row = qkv_f32 + size_t(b) * 3 * E + h * D;
-        for (int i = threadIdx.x; i < 3 * D; i += blockDim.x) {
+#pragma unroll
+        for (int u = 0; u < kMine; ++u) {
+            const int i = threadIdx.x + u * 32 * kDecodeWarps;
+            if (i >= 3 * D) break;
             const int part = i / D, d = i - part * D;
-            const uint16_t c = cvt_f32x2_to_fp8x2<KIND>(__fmul_rn(__ldcg(row + size_t(part) * E + d), sc.x), 0.f) & 0xffu;
+            const uint16_t c = cvt_f32x2_to_fp8x2<KIND>(__fmul_rn(mine[u], sc.x), 0.f) & 0xffu;
             if (part == 0) sq[d] = cvt_fp8x2_to_f32x2<KIND>(c).x * qs;
             else if (part == 1) kbase[size_t(j_new) * D + d] = uint8_t(c);
             else vbase[size_t(j_new) * D + d] = uint8_t(c);

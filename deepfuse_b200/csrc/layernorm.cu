@@ -263,17 +263,27 @@ layernorm_quantize_one_cta_kernel(const float* __restrict__ x, int rows, int C, 
     const int lane = threadIdx.x & 31, row = threadIdx.x >> 5;
     const int c4 = C >> 2;
     __shared__ float warp_amax[32];
+    __shared__ float4 sgamma[32 * V4], sbeta[32 * V4];
     const float before = ld_l2_f32(amax_out);  // normally 0 (cleared by the caller's convention); kept as a lower bound
     float4 o[V4];
+    float4 v[V4];
     float mx = 0.f;
     if (row < rows) {
         const float4* xr = reinterpret_cast<const float4*>(x + size_t(row) * C);
-        float4 v[V4];
 #pragma unroll
         for (int j = 0; j < V4; ++j) {
             const int i = lane + 32 * j;
             v[j] = i < c4 ? ld_stream_f4(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
+    }
+    // gamma and beta to shared memory while the rows are on their way: read where they are needed they would put a
+    // memory round trip behind every reduction
+    for (int i = threadIdx.x; i < c4; i += blockDim.x) {
+        sgamma[i] = gamma ? __ldg(reinterpret_cast<const float4*>(gamma) + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+        sbeta[i] = beta ? __ldg(reinterpret_cast<const float4*>(beta) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    __syncthreads();
+    if (row < rows) {
         float sum = 0.f;
 #pragma unroll
         for (int j = 0; j < V4; ++j) sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
@@ -292,9 +302,7 @@ layernorm_quantize_one_cta_kernel(const float* __restrict__ x, int rows, int C, 
             const int i = lane + 32 * j;
             o[j] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (i < c4) {
-                float4 g = make_float4(1.f, 1.f, 1.f, 1.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (gamma) g = __ldg(reinterpret_cast<const float4*>(gamma) + i);
-                if (beta) b = __ldg(reinterpret_cast<const float4*>(beta) + i);
+                const float4 g = sgamma[i], b = sbeta[i];
                 o[j].x = fmaf((v[j].x - mean) * rstd, g.x, b.x);
                 o[j].y = fmaf((v[j].y - mean) * rstd, g.y, b.y);
                 o[j].z = fmaf((v[j].z - mean) * rstd, g.z, b.z);

@@ -68,17 +68,41 @@ __global__ void __launch_bounds__(kThreads) quantize_f32_kernel(const float* __r
                                                                 float* __restrict__ scale_out) {
     griddep_launch_dependents();
     griddep_wait();
+    const size_t n4 = n >> 2;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    uint32_t* c4 = reinterpret_cast<uint32_t*>(codes);
+    const size_t stride = size_t(gridDim.x) * kThreads;
+    size_t i = size_t(blockIdx.x) * kThreads + threadIdx.x;
+    if (n4 <= 4 * stride) {
+        // a small tensor (a decode step's activations): at most four pieces per thread, all requested before the
+        // maximum is looked at -- a warp issues in order, and the scale's divisions would hold the loads back by a
+        // memory round trip
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = i + u * stride < n4 ? ld_stream_f4(x4 + i + u * stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float2 s = scales_from_amax(ld_l2_f32(amax_in), fp8_max(KIND));
+        if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) {
+            scale_out[0] = s.x;
+            scale_out[1] = s.y;
+        }
+        const float q = s.x;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (i + u * stride < n4)
+                c4[i + u * stride] = cvt_f32x4_to_fp8x4<KIND>(__fmul_rn(v[u].x, q), __fmul_rn(v[u].y, q), __fmul_rn(v[u].z, q),
+                                                              __fmul_rn(v[u].w, q));
+        if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
+            const size_t j = (n4 << 2) + threadIdx.x;
+            codes[j] = uint8_t(cvt_f32x2_to_fp8x2<KIND>(__fmul_rn(x[j], q), 0.f) & 0xff);
+        }
+        return;
+    }
     const float2 s = scales_from_amax(ld_l2_f32(amax_in), fp8_max(KIND));
     if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) {
         scale_out[0] = s.x;
         scale_out[1] = s.y;
     }
     const float q = s.x;
-    const size_t n4 = n >> 2;
-    const float4* x4 = reinterpret_cast<const float4*>(x);
-    uint32_t* c4 = reinterpret_cast<uint32_t*>(codes);
-    const size_t stride = size_t(gridDim.x) * kThreads;
-    size_t i = size_t(blockIdx.x) * kThreads + threadIdx.x;
     for (; i + 3 * stride < n4; i += 4 * stride) {
         float4 a = ld_stream_f4(x4 + i);
         float4 b = ld_stream_f4(x4 + i + stride);

@@ -19,6 +19,11 @@
 // communicator uploads only its 1/world share of a layer and completes the slot with an all-gather over
 // NVLink on the copy stream, so host->device traffic per rank falls world-fold; every rank must then issue
 // the same sequence of prefetch / acquire calls (the all-gather is a collective).
+// The slots then live in a buffer that every rank maps into every other (df8_comm_symm_alloc) and the gather is
+// df8_comm_allgather_symm: the copy engines write a rank's share straight into its peers' slots, so no NCCL kernel
+// competes for SMs with the forward's persistent kernels.  The writes are one-sided: before a rank pushes into the
+// peers' copies of a slot, all ranks meet at a barrier on their copy streams (a one-warp kernel), each after the
+// event that says its own readers of the slot's previous occupant are done.
 #include "df8_internal.cuh"
 
 #include <new>
@@ -34,6 +39,8 @@ struct df8_streamer {
     df8_comm* comm = nullptr;       // not owned
     uint8_t* host_arena = nullptr;  // n_layers * slot_bytes, pinned
     uint8_t* dev_slots = nullptr;   // n_slots * slot_bytes
+    bool slots_symm = false;        // dev_slots is a peer-mapped buffer of the communicator (lives as long as it does)
+    float* barrier_value = nullptr; // operand of the barrier in front of the one-sided pushes
     cudaStream_t copy_stream = nullptr;
     std::vector<cudaEvent_t> copied, freed;
     std::vector<int> slot_layer;    // which layer each slot holds or is receiving (-1: none)
@@ -58,7 +65,19 @@ void destroy_events(df8_streamer* s) {
 
 df8_status make_slots(df8_streamer* s, int n_slots) {
     s->n_slots = n_slots < s->n_layers ? n_slots : s->n_layers;
-    DF8_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&s->dev_slots), s->slot_bytes * size_t(s->n_slots)));
+    if (s->comm) {  // collective: every rank makes its slots at the same point
+        void* p = nullptr;
+        df8_status rc = df8_comm_symm_alloc(s->comm, s->slot_bytes * size_t(s->n_slots), &p);
+        if (rc != DF8_OK) return rc;
+        s->dev_slots = static_cast<uint8_t*>(p);
+        s->slots_symm = true;
+        if (!s->barrier_value) {
+            DF8_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&s->barrier_value), sizeof(float)));
+            DF8_CUDA_TRY(cudaMemset(s->barrier_value, 0, sizeof(float)));
+        }
+    } else {
+        DF8_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&s->dev_slots), s->slot_bytes * size_t(s->n_slots)));
+    }
     for (int i = 0; i < s->n_slots; ++i) {
         cudaEvent_t a = nullptr, b = nullptr;
         DF8_CUDA_TRY(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
@@ -86,8 +105,11 @@ df8_status upload(df8_streamer* s, int layer) {
     const size_t off = size_t(s->rank) * s->part_bytes;
     DF8_CUDA_TRY(cudaMemcpyAsync(dst + off, src + off, s->part_bytes, cudaMemcpyHostToDevice, s->copy_stream));
     if (s->world > 1) {  // in place: this rank's share already sits at its position in the slot
-        df8_status rc = df8_comm_allgather_u8(s->comm, dst + off, dst, s->part_bytes,
-                                              reinterpret_cast<df8_stream>(s->copy_stream));
+        const df8_stream cs = reinterpret_cast<df8_stream>(s->copy_stream);
+        // every rank's readers of the slot's previous occupant are done before anybody writes into it
+        df8_status rc = df8_comm_allreduce_max_p2p(s->comm, s->barrier_value, cs);
+        if (rc != DF8_OK) return rc;
+        rc = df8_comm_allgather_symm(s->comm, s->dev_slots, size_t(slot) * s->slot_bytes, s->part_bytes, cs);
         if (rc != DF8_OK) return rc;
     }
     DF8_CUDA_TRY(cudaEventRecord(s->copied[size_t(slot)], s->copy_stream));
@@ -127,7 +149,8 @@ extern "C" df8_status df8_streamer_create_sharded(size_t slot_bytes, int n_slots
     s->n_layers = n_layers;
     auto bail = [&](df8_status rc) {
         if (s->host_arena) cudaFreeHost(s->host_arena);
-        if (s->dev_slots) cudaFree(s->dev_slots);
+        if (s->dev_slots && !s->slots_symm) cudaFree(s->dev_slots);
+        if (s->barrier_value) cudaFree(s->barrier_value);
         if (s->copy_stream) cudaStreamDestroy(s->copy_stream);
         destroy_events(s);
         delete s;
@@ -153,7 +176,8 @@ extern "C" df8_status df8_streamer_destroy(df8_streamer* s) {
     cudaStreamSynchronize(s->copy_stream);
     destroy_events(s);
     cudaStreamDestroy(s->copy_stream);
-    cudaFree(s->dev_slots);
+    if (!s->slots_symm) cudaFree(s->dev_slots);
+    if (s->barrier_value) cudaFree(s->barrier_value);
     cudaFreeHost(s->host_arena);
     delete s;
     return DF8_OK;
@@ -163,7 +187,7 @@ extern "C" df8_status df8_streamer_resize(df8_streamer* s, int n_slots) {
     DF8_REQUIRE(s != nullptr && n_slots >= 1, "df8_streamer_resize: bad argument");
     DF8_CUDA_TRY(cudaDeviceSynchronize());  // nothing may still read or fill the old slots
     destroy_events(s);
-    DF8_CUDA_TRY(cudaFree(s->dev_slots));
+    if (!s->slots_symm) DF8_CUDA_TRY(cudaFree(s->dev_slots));  // (a peer-mapped buffer stays with the communicator)
     s->dev_slots = nullptr;
     return make_slots(s, n_slots);
 }

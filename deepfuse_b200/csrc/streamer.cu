@@ -19,13 +19,16 @@
 // communicator uploads only its 1/world share of a layer and completes the slot with an all-gather over
 // NVLink on the copy stream, so host->device traffic per rank falls world-fold; every rank must then issue
 // the same sequence of prefetch / acquire calls (the all-gather is a collective).
-// The slots then live in a buffer that every rank maps into every other (df8_comm_symm_alloc) and the gather is
-// df8_comm_allgather_symm: the copy engines write a rank's share straight into its peers' slots, so no NCCL kernel
-// competes for SMs with the forward's persistent kernels.  The writes are one-sided: before a rank pushes into the
-// peers' copies of a slot, all ranks meet at a barrier on their copy streams (a one-warp kernel), each after the
-// event that says its own readers of the slot's previous occupant are done.
+// With DF8_STREAM_P2P=1 in the environment (read when the streamer is created; every rank the same) the slots live
+// in a buffer that every rank maps into every other (df8_comm_symm_alloc) and the gather is df8_comm_allgather_symm:
+// the copy engines write a rank's share straight into its peers' slots, so no NCCL kernel competes for SMs with the
+// forward's persistent kernels.  The writes are one-sided: before a rank pushes into the peers' copies of a slot,
+// all ranks meet at a barrier on their copy streams (a one-warp kernel), each after the event that says its own
+// readers of the slot's previous occupant are done.  Off by default: faster on two GPUs, but on eight the bounded
+// waits of the exchange ran out about once per forward (status word 0x5002) for a reason not yet found.
 #include "df8_internal.cuh"
 
+#include <cstdlib>
 #include <new>
 #include <vector>
 
@@ -39,6 +42,7 @@ struct df8_streamer {
     df8_comm* comm = nullptr;       // not owned
     uint8_t* host_arena = nullptr;  // n_layers * slot_bytes, pinned
     uint8_t* dev_slots = nullptr;   // n_slots * slot_bytes
+    bool use_p2p = false;           // DF8_STREAM_P2P=1: peer-mapped slots and copy-engine pushes instead of ncclAllGather
     bool slots_symm = false;        // dev_slots is a peer-mapped buffer of the communicator (lives as long as it does)
     float* barrier_value = nullptr; // operand of the barrier in front of the one-sided pushes
     cudaStream_t copy_stream = nullptr;
@@ -65,7 +69,7 @@ void destroy_events(df8_streamer* s) {
 
 df8_status make_slots(df8_streamer* s, int n_slots) {
     s->n_slots = n_slots < s->n_layers ? n_slots : s->n_layers;
-    if (s->comm) {  // collective: every rank makes its slots at the same point
+    if (s->comm && s->use_p2p) {  // collective: every rank makes its slots at the same point
         void* p = nullptr;
         df8_status rc = df8_comm_symm_alloc(s->comm, s->slot_bytes * size_t(s->n_slots), &p);
         if (rc != DF8_OK) return rc;
@@ -106,10 +110,15 @@ df8_status upload(df8_streamer* s, int layer) {
     DF8_CUDA_TRY(cudaMemcpyAsync(dst + off, src + off, s->part_bytes, cudaMemcpyHostToDevice, s->copy_stream));
     if (s->world > 1) {  // in place: this rank's share already sits at its position in the slot
         const df8_stream cs = reinterpret_cast<df8_stream>(s->copy_stream);
-        // every rank's readers of the slot's previous occupant are done before anybody writes into it
-        df8_status rc = df8_comm_allreduce_max_p2p(s->comm, s->barrier_value, cs);
-        if (rc != DF8_OK) return rc;
-        rc = df8_comm_allgather_symm(s->comm, s->dev_slots, size_t(slot) * s->slot_bytes, s->part_bytes, cs);
+        df8_status rc;
+        if (s->slots_symm) {
+            // every rank's readers of the slot's previous occupant are done before anybody writes into it
+            rc = df8_comm_allreduce_max_p2p(s->comm, s->barrier_value, cs);
+            if (rc != DF8_OK) return rc;
+            rc = df8_comm_allgather_symm(s->comm, s->dev_slots, size_t(slot) * s->slot_bytes, s->part_bytes, cs);
+        } else {
+            rc = df8_comm_allgather_u8(s->comm, dst + off, dst, s->part_bytes, cs);
+        }
         if (rc != DF8_OK) return rc;
     }
     DF8_CUDA_TRY(cudaEventRecord(s->copied[size_t(slot)], s->copy_stream));
@@ -142,6 +151,8 @@ extern "C" df8_status df8_streamer_create_sharded(size_t slot_bytes, int n_slots
             return rc;
         }
         if (s->world > 1) s->comm = comm;
+        const char* e = getenv("DF8_STREAM_P2P");
+        s->use_p2p = s->comm != nullptr && e && e[0] == '1';
     }
     const size_t unit = size_t(256) * size_t(s->world);
     s->slot_bytes = (slot_bytes + unit - 1) / unit * unit;

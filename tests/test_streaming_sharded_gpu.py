@@ -1,16 +1,18 @@
 """Layer streaming across 2 GPUs (skipped on a single-GPU box): every rank holds the whole model and its own share of
 the batch, uploads HALF of each layer's weight codes from its pinned host arena and gets the other half from its
-peer by an all-gather on the copy stream.  Logits must equal the resident-weights forward bit for bit, on repeated
-forwards, and the byte counters must show the split.  One process per GPU; the NCCL id travels through a file."""
+peer by an all-gather on the copy stream (ncclAllGather, or with DF8_STREAM_P2P=1 copy-engine pushes into peer-mapped
+slots behind a barrier).  Logits must equal the resident-weights forward bit for bit, on repeated forwards, and the
+byte counters must show the split.  One process per GPU; the NCCL id travels through a file."""
 import pytest
 
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, tmp, results):
+def _worker(rank, world, tmp, results, p2p):
     import os
 
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    os.environ["DF8_STREAM_P2P"] = p2p
     import torch
 
     import deepfuse_b200 as df8
@@ -50,7 +52,8 @@ def _worker(rank, world, tmp, results):
     comm.close()
 
 
-def test_streaming_with_sharded_uploads_is_bit_identical(tmp_path):
+@pytest.mark.parametrize("p2p", ["0", "1"])
+def test_streaming_with_sharded_uploads_is_bit_identical(tmp_path, p2p):
     import torch
     import torch.multiprocessing as mp
 
@@ -59,10 +62,14 @@ def test_streaming_with_sharded_uploads_is_bit_identical(tmp_path):
     world = 2
     ctx = mp.get_context("spawn")
     results = ctx.Array("i", [0] * world)
-    procs = [ctx.Process(target=_worker, args=(r, world, str(tmp_path), results)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, str(tmp_path), results, p2p)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
-        p.join(timeout=300)
+        p.join(timeout=240)
+    for p in procs:  # a rank that is still there would keep the box busy: end it (its exit code then fails the test)
+        if p.is_alive():
+            p.kill()
+            p.join()
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     assert list(results) == [1] * world

@@ -299,6 +299,7 @@ void Gpt2<T>::end_decode() {
 
 template <typename T>
 Gpt2<T>::~Gpt2() {
+    if (dec_graph_) cudaGraphExecDestroy(dec_graph_);
     for (cudaEvent_t ev : head_ev_)
         if (ev) cudaEventDestroy(ev);
     if (streamer_) df8_streamer_destroy(streamer_);

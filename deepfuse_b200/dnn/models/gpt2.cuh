@@ -94,6 +94,9 @@ public:
     // decode_step(ids [B]) feeds one new token per sequence at the next position and returns its logits [B, V].
     // The blocks' attention is causal from the prefill on (a cached key never sees a later query).  Every tensor
     // that feeds a product is quantised per tensor, as in the batched forward: a step's tensors are [B, .].
+    // A prefill opens a decoding session that lasts until end_decode() or the next prefill: the model's parameters
+    // and options must not change inside it (from the third step on the launches are replayed from a CUDA graph
+    // that holds the buffers' addresses).
     tensor<T> prefill(const tensor<int>& ids, int max_len = 0, bool check_ids = true);
     tensor<T> decode_step(const tensor<int>& next_ids, bool check_ids = true);
     int decode_position() const { return kv_len_; }

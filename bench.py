@@ -820,6 +820,7 @@ DEFAULT_WORKLOAD = "gpt2s"
 
 
 SIDE_REPORTS = {"ce": lambda *a: cross_entropy_report(*a), "decode": lambda *a: decode_report(*a),
+                "decode_128": lambda *a: decode_report(*a, batch=128),
                 "fc_backward": lambda *a: fc_backward_report(*a)}
 WORKLOADS.update({k: None for k in SIDE_REPORTS})
 
@@ -999,6 +1000,7 @@ def run_ours(args, rank, world, local_rank):
             for key, fn in (("gemm_tflops", lambda: gemm_sweep(torch, df8, dev, peaks)),
                             ("quant_gbs", lambda: quant_sweep(torch, df8, dev, peaks)),
                             ("decode", lambda: decode_report(torch, df8, dev, peaks)),
+                            ("decode_128", lambda: decode_report(torch, df8, dev, peaks, batch=128)),
                             ("cross_entropy", lambda: cross_entropy_report(torch, df8, dev, peaks)),
                             ("fc_backward", lambda: fc_backward_report(torch, df8, dev, peaks))):
                 try:

@@ -90,11 +90,23 @@ attention_decode_kernel(const uint8_t* __restrict__ q_codes, const float* __rest
                         float* row_dq, int H, int n_keys, int Tmax, float* __restrict__ out,
                         float* __restrict__ out_amax, const int* __restrict__ pos) {
     griddep_launch_dependents();
+    const int b = blockIdx.x / H, h = blockIdx.x % H;
+    // The cached rows come from DRAM (a step's working set exceeds L2) and their loads can only be issued once the
+    // position is known: ask L2 for them first, before the wait for the preceding kernel -- they were written by earlier
+    // steps, and a prefetch moves nothing the program can see.  n_keys is the host's count (replayed from a graph: the
+    // count at capture, a lower bound).
+    if (threadIdx.x < 2) {
+        const uint8_t* rows = (threadIdx.x == 0 ? kc : vc) + (size_t(b) * H + h) * size_t(Tmax) * D;
+        const unsigned int bytes = unsigned(min(n_keys, Tmax)) * unsigned(D);
+        for (unsigned int off = 0; off < bytes; off += 16384u) {
+            const unsigned int n = min(16384u, bytes - off);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(rows + off), "r"(n) : "memory");
+        }
+    }
     griddep_wait();
     const int pos_v = pos ? ld_l2_s32(pos) : 0;  // (consumed below, after the other requests are out)
     constexpr int DPL = D / 32;             // output dimensions per lane in the final combine
     constexpr int CH = D / 16, KPI = 32 / CH;  // 16-byte pieces per row, keys per pass of the p . V loop
-    const int b = blockIdx.x / H, h = blockIdx.x % H;
     const int E = H * D;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     __shared__ float sq[D];

@@ -48,7 +48,6 @@ _SIGNATURES = {
     "df8_gemm_fp8_tn_amax_part": [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "df8_gemm_fp8_tn_codes_part": [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     "df8_gemv_fp8_tn": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp],
-    "df8_gemv_fp8_tn_prefetch": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _vp],
     "df8_embed_pe_pos_f32": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
     "df8_kv_cache_append_pos": [_vp, _vp, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _vp],
     "df8_attention_decode_fp8_pos": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp, _vp],

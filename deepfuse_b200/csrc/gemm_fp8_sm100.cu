@@ -87,9 +87,6 @@ struct GemmArgs {
     uint32_t idesc;
     unsigned int* status;
     unsigned int* grid_counter;  // fused max|out| + codes launch: arrival counter of the grid-wide barrier, else null
-    // kOutF32T: bytes the launch asks L2 to fetch for a LATER launch (the next product's weight codes), or null
-    const uint8_t* pf_ptr;
-    unsigned long long pf_bytes;
 };
 
 // Arrival counters of the fused launches' grid-wide barrier: each counts up for ever (a launch waits for the next
@@ -604,22 +601,6 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     griddep_launch_dependents();
-    if constexpr (MODE == kOutF32T) {
-        // A decode step re-reads every weight matrix from DRAM (the step's working set exceeds L2), and the first
-        // block's trip from DRAM sits on each product's critical path.  A product therefore asks L2, before anything
-        // else and without waiting for its predecessor (a prefetch moves no data the program can see), for the weight
-        // codes of the product that FOLLOWS it; each CTA takes a share, a lane per 16 KB piece.
-        if (args.pf_ptr != nullptr && warp >= 2 && lane == 0) {
-            const unsigned long long per_cta = ((args.pf_bytes + gridDim.x - 1) / gridDim.x + 15ull) & ~15ull;
-            const unsigned long long beg = (unsigned long long)blockIdx.x * per_cta;
-            const unsigned long long end = beg + per_cta < args.pf_bytes ? beg + per_cta : args.pf_bytes;
-            for (unsigned long long off = beg + (unsigned long long)(warp - 2) * 16384ull; off < end; off += (unsigned long long)EW * 16384ull) {
-                const unsigned long long left = end - off;
-                const uint32_t n = uint32_t(left < 16384ull ? left : 16384ull) & ~15u;
-                if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(args.pf_ptr + off), "r"(n) : "memory");
-            }
-        }
-    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -1821,17 +1802,6 @@ extern "C" df8_status df8_gemv_fp8_tn(const uint8_t* x_codes, df8_kind kind_x, c
                                       const uint8_t* w_codes, df8_kind kind_w, const float* scale_w, const float* bias,
                                       const float* residual, int B, int N, int K, int flags, float* out, float* out_amax,
                                       df8_stream stream) {
-    return df8_gemv_fp8_tn_prefetch(x_codes, kind_x, scale_x, w_codes, kind_w, scale_w, bias, residual, B, N, K, flags, out,
-                                    out_amax, nullptr, 0, stream);
-}
-
-// next_d / next_bytes: device memory a LATER launch will read (the next product's weight codes); the kernel asks L2
-// to fetch it.  No effect on the result; null / 0 for none.  next_d must be 16-byte aligned.
-extern "C" df8_status df8_gemv_fp8_tn_prefetch(const uint8_t* x_codes, df8_kind kind_x, const float* scale_x,
-                                               const uint8_t* w_codes, df8_kind kind_w, const float* scale_w,
-                                               const float* bias, const float* residual, int B, int N, int K, int flags,
-                                               float* out, float* out_amax, const void* next_d, size_t next_bytes,
-                                               df8_stream stream) {
     DF8_REQUIRE((kind_x == DF8_E4M3 || kind_x == DF8_E5M2) && (kind_w == DF8_E4M3 || kind_w == DF8_E5M2),
                 "df8_gemv_fp8_tn: unknown fp8 kind");
     DF8_REQUIRE(B >= 0 && N >= 0 && K > 0, "df8_gemv_fp8_tn: bad shape B=%d N=%d K=%d", B, N, K);
@@ -1858,10 +1828,6 @@ extern "C" df8_status df8_gemv_fp8_tn_prefetch(const uint8_t* x_codes, df8_kind 
     args.K = K;
     args.ldc = N;
     args.flags = flags;
-    if (next_d != nullptr && next_bytes >= 16 && aligned16(next_d)) {
-        args.pf_ptr = static_cast<const uint8_t*>(next_d);
-        args.pf_bytes = next_bytes;
-    }
     return run_gemm(kOutF32T, w_codes, kind_w, x_codes, kind_x, args, st);
 }
 

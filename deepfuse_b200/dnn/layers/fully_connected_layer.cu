@@ -1,7 +1,5 @@
 #include "dnn/layers/fully_connected_layer.cuh"
 
-#include <cstdlib>
-
 #include <cmath>
 #include <random>
 #include <stdexcept>
@@ -192,26 +190,12 @@ void FullyConnectedLayer<TT>::forward_codes(const uint8_t* a_codes, df8_kind a_k
 }
 
 template <typename TT>
-const uint8_t* FullyConnectedLayer<TT>::resident_codes(size_t* bytes) const {
-    *bytes = 0;
-    if (external_codes_ || wq_version_ != this->weights_.version() || wq_.codes.numel() == 0) return nullptr;
-    *bytes = wq_.codes.numel();
-    return wq_.codes.data();
-}
-
-template <typename TT>
 void FullyConnectedLayer<TT>::forward_codes_skinny(const uint8_t* a_codes, df8_kind a_kind, const float* a_scale, int B,
-                                                   int flags, const float* residual, float* out, float* out_amax,
-                                                   const FullyConnectedLayer<TT>* then) {
+                                                   int flags, const float* residual, float* out, float* out_amax) {
     const fp8::Quantized& w = quantized_weights();
     const uint8_t* w_codes = external_codes_ ? external_codes_ : w.codes.data();
-    size_t next_bytes = 0;
-    const uint8_t* next = then ? then->resident_codes(&next_bytes) : nullptr;
-    if (const char* e = getenv("DF8_DECODE_PREFETCH"))
-        if (e[0] == '0') next = nullptr;
-    utils::CHECK_DF8(df8_gemv_fp8_tn_prefetch(a_codes, a_kind, a_scale, w_codes, w.kind, w.scale.data(), this->bias_.data(),
-                                              residual, B, out_features_, padded_in(), flags, out, out_amax, next,
-                                              next ? next_bytes : 0, fp8::stream()));
+    utils::CHECK_DF8(df8_gemv_fp8_tn(a_codes, a_kind, a_scale, w_codes, w.kind, w.scale.data(), this->bias_.data(), residual,
+                                     B, out_features_, padded_in(), flags, out, out_amax, fp8::stream()));
 }
 
 template <typename TT>

@@ -53,13 +53,8 @@ public:
 
     // The same product for the few token rows of a decode step (B <= 128): bound by streaming the weights
     // (df8_gemv_fp8_tn).
-    // `then`: the layer whose skinny product comes next in the step; this launch asks L2 to fetch its weight codes
-    // (a step's working set exceeds L2: every product would otherwise start with a trip to DRAM)
     void forward_codes_skinny(const uint8_t* a_codes, df8_kind a_kind, const float* a_scale, int B, int flags,
-                              const float* residual, float* out, float* out_amax,
-                              const FullyConnectedLayer<TT>* then = nullptr);
-    // the e4m3 / e5m2 weight codes if they are on the device and current (else null, 0)
-    const uint8_t* resident_codes(size_t* bytes) const;
+                              const float* residual, float* out, float* out_amax);
 
     // q <- per-tensor quantisation (kind out_kind) of epilogue(codes . Wq^T), `flags` = 0 or DF8_EPI_GELU.
     // Uses the two-pass GEMM that never writes the fp32 result when out_features % 32 == 0.

@@ -77,8 +77,7 @@ void MultiHeadAttentionLayer<TT>::forward_quantized(const fp8::Quantized& xq, in
 }
 
 template <typename TT>
-void MultiHeadAttentionLayer<TT>::decode_quantized(const fp8::Quantized& xq, int B, const float* residual, float* out,
-                                                   const FullyConnectedLayer<TT>* then) {
+void MultiHeadAttentionLayer<TT>::decode_quantized(const fp8::Quantized& xq, int B, const float* residual, float* out) {
     if (!kv_) throw std::runtime_error("MultiHeadAttentionLayer::decode_quantized: no KV cache attached");
     if (B != kv_->batch || kv_len_ + 1 > kv_->max_len)
         throw std::runtime_error("MultiHeadAttentionLayer::decode_quantized: the KV cache is full or of another batch size");
@@ -88,8 +87,7 @@ void MultiHeadAttentionLayer<TT>::decode_quantized(const fp8::Quantized& xq, int
     if (attn_f32_.numel() != size_t(B) * E) attn_f32_ = tensor<float>({B, E});
     // the new token's QKV, quantised per tensor like every QKV tensor of the 8-bit path
     float* am = fp8::amax_slot(amax_.data());
-    qkv_proj_.forward_codes_skinny(xq.codes.data(), xq.kind, xq.scale.data(), B, DF8_EPI_AMAX, nullptr, qkv_f32_.data(), am,
-                                   &out_proj_);
+    qkv_proj_.forward_codes_skinny(xq.codes.data(), xq.kind, xq.scale.data(), B, DF8_EPI_AMAX, nullptr, qkv_f32_.data(), am);
     const char* unfused = getenv("DF8_DECODE_UNFUSED");
     if (unfused && unfused[0] == '1') {
         fp8::quantize_with_amax(qkv_f32_.data(), qkv_f32_.numel(), act, am, qkvq_);
@@ -101,7 +99,7 @@ void MultiHeadAttentionLayer<TT>::decode_quantized(const fp8::Quantized& xq, int
                                                       pos_d_, kv_->max_len, attn_f32_.data(), amu, fp8::stream()));
         fp8::quantize_with_amax(attn_f32_.data(), attn_f32_.numel(), act, amu, attnq_);
         out_proj_.forward_codes_skinny(attnq_.codes.data(), attnq_.kind, attnq_.scale.data(), B,
-                                       residual ? DF8_EPI_RESIDUAL : 0, residual, out, nullptr, then);
+                                       residual ? DF8_EPI_RESIDUAL : 0, residual, out, nullptr);
         return;
     }
     // quantise + cache append + attention in one launch (the codes are those of quantize_with_amax)
@@ -111,7 +109,7 @@ void MultiHeadAttentionLayer<TT>::decode_quantized(const fp8::Quantized& xq, int
                                                     kv_->max_len, attn_f32_.data(), am2, fp8::stream()));
     fp8::quantize_with_amax(attn_f32_.data(), attn_f32_.numel(), act, am2, attnq_);
     out_proj_.forward_codes_skinny(attnq_.codes.data(), attnq_.kind, attnq_.scale.data(), B,
-                                   residual ? DF8_EPI_RESIDUAL : 0, residual, out, nullptr, then);
+                                   residual ? DF8_EPI_RESIDUAL : 0, residual, out, nullptr);
 }
 
 template <typename TT>

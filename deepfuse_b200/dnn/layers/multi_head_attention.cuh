@@ -74,9 +74,7 @@ public:
     // decode_quantized reads the position from this device integer instead of kv_len (null = the host value): a
     // step's launches then do not depend on the position and can be replayed from a CUDA graph
     void set_decode_position(const int* pos_d) { pos_d_ = pos_d; }
-    // `then`: the layer whose skinny product follows the output projection in the step (its weights are prefetched)
-    void decode_quantized(const fp8::Quantized& xq, int B, const float* residual, float* out,
-                          const FullyConnectedLayer<TT>* then = nullptr);
+    void decode_quantized(const fp8::Quantized& xq, int B, const float* residual, float* out);
 
 private:
     int embed_dim_;

@@ -49,21 +49,21 @@ void TransformerBlock<T>::forward_inplace(float* x, int B, int T_len) {
 }
 
 template <typename T>
-void TransformerBlock<T>::decode_inplace(float* x, int B, const FullyConnectedLayer<T>* then) {
+void TransformerBlock<T>::decode_inplace(float* x, int B) {
     const int E = embed_dim_, F = mlp_hidden_dim_;
     const df8_kind act = fp8::policy().activation_kind;
     if (x1_.numel() != size_t(B) * E) x1_ = tensor<float>({B, E});
     if (hidden_f32_.numel() != size_t(B) * F) hidden_f32_ = tensor<float>({B, F});
     fp8::PassScope amax_slots;
     norm1_.forward_quantized(x, B, act, ln_q_);
-    attn_.decode_quantized(ln_q_, B, x, x1_.data(), &mlp_fc1_);
+    attn_.decode_quantized(ln_q_, B, x, x1_.data());
     norm2_.forward_quantized(x1_.data(), B, act, ln_q_);
     float* am = fp8::amax_slot(amax_.data());
     mlp_fc1_.forward_codes_skinny(ln_q_.codes.data(), ln_q_.kind, ln_q_.scale.data(), B,
-                                  (mlp_gelu_ ? DF8_EPI_GELU : 0) | DF8_EPI_AMAX, nullptr, hidden_f32_.data(), am, &mlp_fc2_);
+                                  (mlp_gelu_ ? DF8_EPI_GELU : 0) | DF8_EPI_AMAX, nullptr, hidden_f32_.data(), am);
     fp8::quantize_with_amax(hidden_f32_.data(), hidden_f32_.numel(), act, am, hidden_q_);
     mlp_fc2_.forward_codes_skinny(hidden_q_.codes.data(), hidden_q_.kind, hidden_q_.scale.data(), B, DF8_EPI_RESIDUAL,
-                                  x1_.data(), x, nullptr, then);
+                                  x1_.data(), x, nullptr);
 }
 
 template <typename T>

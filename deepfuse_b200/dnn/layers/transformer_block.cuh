@@ -59,9 +59,7 @@ public:
     // In-place variant used by the model loop: x [B*T, E] fp32 is replaced by the block output.
     void forward_inplace(float* x, int B, int T_len);
     // One decode step on x [B, E] (one new token per sequence) against the attention layer's attached KV cache.
-    // then: the layer whose skinny product follows this block's last one in the step (the next block's QKV projection, or
-    // the head): its weights are prefetched by this block's last product
-    void decode_inplace(float* x, int B, const FullyConnectedLayer<T>* then = nullptr);
+    void decode_inplace(float* x, int B);
 
 private:
     int embed_dim_;

@@ -219,18 +219,10 @@ void Gpt2<T>::decode_body(int B) {
     utils::CHECK_DF8(df8_embed_pe_pos_f32(dec_ids_.data(), B, E, vocab_size_, token_embedding_->weights()->data(),
                                           token_embedding_->bias()->data(), positional_encoding_->table().data(),
                                           dec_pos_.data(), dec_x_.data(), fp8::stream()));
-    // every product asks L2 for the weights of the product after it: the next block's QKV projection after a block, the
-    // first block's (the next step's first product) after the head.  Not the head's own 38 MB: asked for by the six
-    // CTAs of the last FC2 they made the step slower (0.525 against 0.513 ms).
-    for (size_t l = 0; l < transformer_blocks_.size(); ++l)
-        transformer_blocks_[l]->decode_inplace(dec_x_.data(), B,
-                                               l + 1 < transformer_blocks_.size()
-                                                   ? &transformer_blocks_[l + 1]->attention().qkv_projection()
-                                                   : nullptr);
+    for (auto& blk : transformer_blocks_) blk->decode_inplace(dec_x_.data(), B);
     fp8::quantize(dec_x_.data(), size_t(B) * E, fp8::policy().activation_kind, head_q_);
     final_fc_->forward_codes_skinny(head_q_.codes.data(), head_q_.kind, head_q_.scale.data(), B, 0, nullptr,
-                                    dec_logits_.data(), nullptr,
-                                    transformer_blocks_.empty() ? nullptr : &transformer_blocks_[0]->attention().qkv_projection());
+                                    dec_logits_.data(), nullptr);
     utils::CHECK_DF8(df8_position_advance(dec_pos_.data(), fp8::stream()));
 }
 

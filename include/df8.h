@@ -198,13 +198,6 @@ df8_status df8_attention_fp8(const uint8_t* qkv_codes, df8_kind kind, const floa
 df8_status df8_gemv_fp8_tn(const uint8_t* x_codes, df8_kind kind_x, const float* scale_x, const uint8_t* w_codes,
                            df8_kind kind_w, const float* scale_w, const float* bias, const float* residual, int B, int N,
                            int K, int flags, float* out, float* out_amax, df8_stream stream);
-/* df8_gemv_fp8_tn that also asks L2 to fetch next_bytes bytes at next_d (16-byte aligned device memory), which a
- * LATER launch will read: the weight codes of the product that follows.  A decode step's working set exceeds L2, so
- * every product would otherwise start with a trip to DRAM on its critical path.  No effect on any result. */
-df8_status df8_gemv_fp8_tn_prefetch(const uint8_t* x_codes, df8_kind kind_x, const float* scale_x, const uint8_t* w_codes,
-                                    df8_kind kind_w, const float* scale_w, const float* bias, const float* residual, int B,
-                                    int N, int K, int flags, float* out, float* out_amax, const void* next_d,
-                                    size_t next_bytes, df8_stream stream);
 df8_status df8_kv_cache_append(const uint8_t* qkv_codes, const float* scale, int B, int Tn, int H, int D, int t0, int Tmax,
                                uint8_t* k_cache, uint8_t* v_cache, float* row_dq, df8_stream stream);
 df8_status df8_attention_decode_fp8(const uint8_t* qkv_codes, df8_kind kind, const float* scale, const uint8_t* k_cache,

@@ -36,15 +36,8 @@ def test_skinny_product_matches_the_gemm_and_the_oracle(df8, oracle, cuda, B, N,
     want = torch.empty((B, N), device=cuda)
     a2 = torch.zeros(1, device=cuda)
     df8.gemm_fp8_tn(xcd, kx, sxd, wcd, kw, swd, bd, rd, B, N, K, flags, want, a2)
-    # the same with an L2 prefetch of a later launch's operand (here: the weights themselves): no effect on the result
-    pf = torch.full((B, N), 555.0, device=cuda)
-    a3 = torch.full((1,), -1.0, device=cuda)
-    df8.check(df8.lib().df8_gemv_fp8_tn_prefetch(df8.ptr(xcd), kx, df8.ptr(sxd), df8.ptr(wcd), kw, df8.ptr(swd), df8.ptr(bd),
-                                                 df8.ptr(rd), B, N, K, flags, df8.ptr(pf), df8.ptr(a3), df8.ptr(wcd),
-                                                 wcd.numel(), df8.stream_ptr()))
     torch.cuda.synchronize()
     got = buf[: B * N].reshape(B, N)
-    assert torch.equal(pf, got) and a3.item() == amax.item()
     assert bool((buf[B * N:] == 777.0).all())
     ref = oracle.fc_forward_fp8(xc, kx, sx[1], wc, kw, sw[1], b, res, flags & 3)
     tol = 2e-3 if flags & 1 else 2e-4

@@ -260,6 +260,8 @@ _DNN_SIGNATURES = {
     "dnn_gpt2_forward_hidden": [_vp, _vp, _i, _i, _vp],
     "dnn_gpt2_forward_logits_pitched": [_vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "dnn_gpt2_copy_logits_host": [_vp, _vp],
+    "dnn_gpt2_serve_step": [_vp, _vp, _i, _i, _vp],
+    "dnn_gpt2_serve_flush": [_vp],
     "dnn_gpt2_forward_ids": [_vp, _vp, _i, _vp],
     "dnn_gpt2_save": [_vp, C.c_char_p],
     "dnn_gpt2_enable_streaming": [_vp, _i, _i],
@@ -513,6 +515,17 @@ class Gpt2:
     def copy_logits_host(self, dst_host) -> None:
         """Enqueues the copy of the last logits into the dense (pinned) host tensor [B*T, vocab]."""
         dnn_check(dnn_lib().dnn_gpt2_copy_logits_host(self.h, dst_host.data_ptr()), "dnn_gpt2_copy_logits_host")
+
+    def serve_step(self, ids_host, dst_host) -> None:
+        """One step of a serving loop: pinned host ids [B,T] in, the full logits into the pinned host tensor
+        [B*T, vocab]; the copy back runs on a stream of its own under the next step's forward.  dst_host must not be
+        reused before the next-but-one call (alternate two buffers) or serve_flush()."""
+        B, T = ids_host.shape
+        dnn_check(dnn_lib().dnn_gpt2_serve_step(self.h, ids_host.data_ptr(), B, T, dst_host.data_ptr()), "dnn_gpt2_serve_step")
+
+    def serve_flush(self) -> None:
+        """The current stream waits for every copy serve_step has issued."""
+        dnn_check(dnn_lib().dnn_gpt2_serve_flush(self.h), "dnn_gpt2_serve_flush")
 
     def forward_hidden(self, ids_dev) -> int:
         out = C.c_void_p(0)

@@ -61,6 +61,21 @@ struct dnn_gpt2 {
     std::vector<NamedParam> params;
     std::unique_ptr<dnn::tensor<float>> last;  // result of the last forward, kept alive for the caller
     std::unique_ptr<dnn::tensor<int>> ids;
+    // dnn_gpt2_serve_step: the logits of the step before the last stay alive while the copy stream reads them
+    std::unique_ptr<dnn::tensor<float>> prev;
+    std::unique_ptr<dnn::tensor<int>> serve_ids[2];
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t ev_forward = nullptr, ev_copied[2] = {nullptr, nullptr};
+    unsigned long long serve_steps = 0;
+    ~dnn_gpt2() {
+        if (copy_stream) {
+            cudaStreamSynchronize(copy_stream);
+            cudaStreamDestroy(copy_stream);
+        }
+        if (ev_forward) cudaEventDestroy(ev_forward);
+        for (cudaEvent_t e : ev_copied)
+            if (e) cudaEventDestroy(e);
+    }
 
     void index_params() {
         params.clear();
@@ -241,6 +256,46 @@ extern "C" int dnn_gpt2_copy_logits_host(dnn_gpt2* m, float* dst_h) {
         dnn::utils::CHECK_CUDA_EX(cudaMemcpy2DAsync(dst_h, size_t(vocab) * sizeof(float), m->last->data(),
                                                     size_t(pitch) * sizeof(float), size_t(vocab) * sizeof(float),
                                                     size_t(rows), cudaMemcpyDeviceToHost, dnn::Cuda::stream()));
+    });
+}
+
+// A serving loop's step: host ids in, the full logits out to (pinned) host memory -- with the device-to-host copy
+// of step i on a stream of its own, so that it runs under the forward of step i + 1 (1.65 GB of logits take 29 ms
+// over PCIe, a forward 3.3 ms: issued on one stream the two add up).  Two logits tensors and two id buffers alternate.
+// dst_h must stay untouched until the next-but-one call or dnn_gpt2_serve_flush.
+extern "C" int dnn_gpt2_serve_step(dnn_gpt2* m, const int32_t* ids_h, int B, int T, float* dst_h) {
+    return guarded([&] {
+        cudaStream_t cs = dnn::Cuda::stream();
+        if (!m->copy_stream) {
+            dnn::utils::CHECK_CUDA_EX(cudaStreamCreateWithFlags(&m->copy_stream, cudaStreamNonBlocking));
+            dnn::utils::CHECK_CUDA_EX(cudaEventCreateWithFlags(&m->ev_forward, cudaEventDisableTiming));
+            for (cudaEvent_t& e : m->ev_copied) dnn::utils::CHECK_CUDA_EX(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        }
+        const int slot = int(m->serve_steps & 1);
+        // the tensor that held the logits two steps ago goes back to the pool: its copy must be over (stream order)
+        if (m->serve_steps >= 2) dnn::utils::CHECK_CUDA_EX(cudaStreamWaitEvent(cs, m->ev_copied[slot], 0));
+        m->prev.reset();
+        m->prev = std::move(m->last);
+        auto& ids = m->serve_ids[slot];
+        if (!ids || ids->shape() != std::vector<int>{B, T}) ids = std::make_unique<dnn::tensor<int>>(std::vector<int>{B, T});
+        dnn::utils::CHECK_CUDA_EX(cudaMemcpyAsync(ids->data(), ids_h, sizeof(int32_t) * size_t(B) * size_t(T), cudaMemcpyHostToDevice, cs));
+        m->last = std::make_unique<dnn::tensor<float>>(m->model->forward_logits_pitched(*ids, false));
+        dnn::utils::CHECK_CUDA_EX(cudaEventRecord(m->ev_forward, cs));
+        dnn::utils::CHECK_CUDA_EX(cudaStreamWaitEvent(m->copy_stream, m->ev_forward, 0));
+        const int rows = m->last->shape()[0], pitch = m->last->shape()[1], vocab = m->model->vocab_size();
+        dnn::utils::CHECK_CUDA_EX(cudaMemcpy2DAsync(dst_h, size_t(vocab) * sizeof(float), m->last->data(), size_t(pitch) * sizeof(float),
+                                        size_t(vocab) * sizeof(float), size_t(rows), cudaMemcpyDeviceToHost, m->copy_stream));
+        dnn::utils::CHECK_CUDA_EX(cudaEventRecord(m->ev_copied[slot], m->copy_stream));
+        ++m->serve_steps;
+    });
+}
+
+// The calling thread's stream waits for every copy dnn_gpt2_serve_step has issued (no host synchronisation).
+extern "C" int dnn_gpt2_serve_flush(dnn_gpt2* m) {
+    return guarded([&] {
+        if (!m->copy_stream) return;
+        for (cudaEvent_t e : m->ev_copied)
+            dnn::utils::CHECK_CUDA_EX(cudaStreamWaitEvent(dnn::Cuda::stream(), e, 0));
     });
 }
 

@@ -60,6 +60,11 @@ int dnn_gpt2_forward_logits_pitched(dnn_gpt2* m, const int32_t* ids, int ids_on_
 /* Enqueues the copy of the last logits (dense or pitched) to a dense HOST array [rows, vocab] on the thread's
  * stream (pinned memory makes it asynchronous); the caller synchronises before reading dst_h. */
 int dnn_gpt2_copy_logits_host(dnn_gpt2* m, float* dst_h);
+/* A serving loop's step: ids on the HOST in, the full dense logits [B*T, vocab] out to (pinned) host memory, with the
+ * device-to-host copy on a stream of its own so that it overlaps the next step's forward.  dst_h must stay untouched
+ * until the next-but-one call; dnn_gpt2_serve_flush makes the thread's stream wait for every copy issued so far. */
+int dnn_gpt2_serve_step(dnn_gpt2* m, const int32_t* ids_h, int B, int T, float* dst_h);
+int dnn_gpt2_serve_flush(dnn_gpt2* m);
 /* hidden states [B,T,E] of Gpt2::forward_hidden, device pointer owned by the handle */
 int dnn_gpt2_forward_hidden(dnn_gpt2* m, const int32_t* ids_d, int B, int T, float** hidden_d);
 /* the model's own public batch-1 entry point, Gpt2::forward(std::vector<int>): hidden [1,T,E] to host */

@@ -332,3 +332,42 @@ def test_gpt2_device_init_equals_host_generated_params(df8, dnn, oracle, cuda):
     model.forward_logits_pitched(ids)
     assert 0.0 < model.last_head_ms() < 50.0
     model.close()
+
+
+def test_gpt2_serve_step_equals_forward_then_copy(df8, dnn, oracle, cuda):
+    """Gpt2.serve_step (host ids in, full logits to pinned host memory with the copy on a stream of its own, two
+    buffers alternating) returns the logits of forward_logits_pitched + copy_logits_host, step after step with
+    different ids."""
+    import torch
+    from oracle import gpt2_ref
+
+    cfg = dict(vocab=300, max_seq_len=32, layers=2, heads=2, hidden=128, ffn=256)
+    B, T, steps = 3, 32, 5
+    prm = gpt2_ref.make_params(cfg, seed=12, std=0.05)
+    model = df8.Gpt2(**cfg)
+    try:
+        model.load_params(prm)
+        ids = [torch.from_numpy(oracle.fill_token_ids(B * T, seed=20 + i, vocab=300).reshape(B, T)).pin_memory() for i in range(steps)]
+        want = []
+        for x in ids:
+            dst = torch.empty((B * T, 300), dtype=torch.float32).pin_memory()
+            model.forward_logits_pitched(x, check_ids=False)
+            model.copy_logits_host(dst)
+            torch.cuda.synchronize()
+            want.append(dst.clone())
+        bufs = [torch.full((B * T, 300), float("nan"), dtype=torch.float32).pin_memory() for _ in range(2)]
+        got = []
+        for i, x in enumerate(ids):
+            model.serve_step(x, bufs[i % 2])
+            if i >= 1:  # the copy of step i - 1 is over once step i's forward has been issued and its event waited for
+                model.serve_flush()
+                torch.cuda.synchronize()
+                got.append(bufs[(i - 1) % 2].clone())
+        model.serve_flush()
+        torch.cuda.synchronize()
+        got.append(bufs[(steps - 1) % 2].clone())
+        for i, (g, w) in enumerate(zip(got, want)):
+            assert torch.equal(g, w), i
+        assert df8.status_word() == (0, 0)
+    finally:
+        model.close()

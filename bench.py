@@ -1018,7 +1018,6 @@ def run_ours(args, rank, world, local_rank):
                            "what": "Gpt2.serve_step: pinned host ids in, the full fp32 logits [B*T, vocab] copied back to "
                                    "pinned host memory every step; the copy of step i runs on a stream of its own under "
                                    "the forward of step i + 1, the last copy is waited for inside the timed region"}
-        wl.full_logits_b = None
         for _ in range(2):
             wl.e2e_step_next_token()
         nt_ms, _ = timed(wl.e2e_step_next_token, e_steps)
@@ -1027,7 +1026,7 @@ def run_ours(args, rank, world, local_rank):
                                       "unit": wl.unit, "h2d_bytes_per_step": wl.ids_host.numel() * 4,
                                       "d2h_bytes_per_step": wl.last_logits.numel() * 4, "steps": e_steps,
                                       "what": "pinned host ids in; only the last position's logits [B, vocab] copied back"}
-        wl.full_logits = None  # 1.65 GB of pinned memory
+        wl.full_logits = wl.full_logits_b = None  # 2 x 1.65 GB of pinned memory (released after the timed legs: unpinning stalls the device)
 
     roofline = wl.roofline(torch, peaks)  # every rank runs it (keeps the ranks in step); rank 0 reports
     if rank == 0:

@@ -995,10 +995,6 @@ def run_ours(args, rank, world, local_rank):
                        "host buffers in and out through the C-ABI"}
     if isinstance(wl, Gpt2Workload) and not isinstance(wl, Gpt2ShardedWorkload):
         # the serving call: step i's logits cross PCIe on a stream of their own while step i + 1 computes
-        wl.e2e_setup_pipelined(torch)
-        for _ in range(2):
-            wl.e2e_step_pipelined()
-        wl.e2e_flush_pipelined()
         p_steps = max(e_steps, 6)
         issued = {"n": 0}
 
@@ -1008,8 +1004,20 @@ def run_ours(args, rank, world, local_rank):
             if issued["n"] == p_steps:
                 wl.e2e_flush_pipelined()  # the last copy ends inside the timed region
 
-        pl_ms, _ = timed(pipelined_step, p_steps)
-        if rank == 0:
+        pl_ok = 1
+        try:  # a second 1.65 GB pinned buffer per rank: if the host refuses it, the one-stream figure stays the e2e
+            wl.e2e_setup_pipelined(torch)
+            for _ in range(2):
+                wl.e2e_step_pipelined()
+            wl.e2e_flush_pipelined()
+            torch.cuda.synchronize()
+        except Exception:
+            pl_ok = 0
+        pl_ok = 0 if max_over_ranks(float(1 - pl_ok))[0] > 0 else 1  # every rank or none (the timed legs hold barriers)
+        pl_ms = None
+        if pl_ok:
+            pl_ms, _ = timed(pipelined_step, p_steps)
+        if rank == 0 and pl_ms is not None:
             line["e2e_serial"] = dict(line["e2e"], what="pinned host ids in; forward, then the full fp32 logits [B*T, vocab] "
                                                         "copied back to pinned host memory, on one stream")
             line["e2e"] = {"value": round(wl.e2e_units_per_step() * world * p_steps / (pl_ms / 1e3), 2), "unit": wl.unit,

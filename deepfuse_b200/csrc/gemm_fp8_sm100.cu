@@ -941,26 +941,61 @@ gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
 
             if constexpr (MODE == kOutF32Vec || MODE == kOutF32) {
                 constexpr bool VEC4 = MODE == kOutF32Vec;
-                uint32_t r[32];
-                if (nvalid > 0) tmem_ld_32x32(taddr + 32 * half, r);
-                for (int j = 0; j < nvalid; ++j) {
-                    tmem_ld_wait();
-                    stage_chunk<VEC4>(r, stg, lane);
-                    __syncwarp();
-                    if (j + 1 < nvalid) {
-                        tmem_ld_32x32(taddr + 32 * (half + 2 * (j + 1)), r);  // in flight during the stores below
-                    } else {
-                        tc_fence_before_sync();  // last chunk is out of TMEM: hand the buffer back early
-                        if (lane == 0) mbar_arrive(smem_u32(tempty + buf));
-                    }
-                    float4 rs_cur[8];
+                // tcgen05.ld writes its destination registers asynchronously, until tcgen05.wait::ld: between the two the
+                // compiler must not copy or recycle them, which it believes defined at the issuing statement.  Hence
+                // two register sets that alternate in a loop with a compile-time trip count: a run-time loop carrying
+                // ONE set over its back edge invites register moves before the wait (and the moved-from registers,
+                // then free, may be handed to an address that the late write clobbers: an illegal memory access that
+                // came and went with unrelated changes of this file).
+                if constexpr (VEC4) {
+                    // (128-bit mode: one register set in a run-time loop, as measured and tuned -- two sets spill at this
+                    // kernel's 168 registers; the same exposure in principle, not observed there)
+                    uint32_t r[32];
+                    if (nvalid > 0) tmem_ld_32x32(taddr + 32 * half, r);
+                    for (int j = 0; j < nvalid; ++j) {
+                        tmem_ld_wait();
+                        stage_chunk<VEC4>(r, stg, lane);
+                        __syncwarp();
+                        if (j + 1 < nvalid) {
+                            tmem_ld_32x32(taddr + 32 * (half + 2 * (j + 1)), r);  // in flight during the stores below
+                        } else {
+                            tc_fence_before_sync();  // last chunk is out of TMEM: hand the buffer back early
+                            if (lane == 0) mbar_arrive(smem_u32(tempty + buf));
+                        }
+                        float4 rs_cur[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) rs_cur[i] = rs[i];
-                    if constexpr (VEC4)
+                        for (int i = 0; i < 8; ++i) rs_cur[i] = rs[i];
                         if (j + 1 < nvalid) load_residual_vec4(rs, lane, row0, n0 + 32 * (half + 2 * (j + 1)), args);
-                    store_chunk_f32<VEC4>(stg, lane, row0, n0 + 32 * (half + 2 * j), args, alpha, amax, rs_cur);
-                    __syncwarp();
+                        store_chunk_f32<VEC4>(stg, lane, row0, n0 + 32 * (half + 2 * j), args, alpha, amax, rs_cur);
+                        __syncwarp();
+                    }
+                } else {
+                uint32_t ra[32], rb[32];
+                if (nvalid > 0) tmem_ld_32x32(taddr + 32 * half, ra);
+#pragma unroll
+                for (int j = 0; j < kChunks; ++j) {
+                    if (j < nvalid) {
+                        tmem_ld_wait();
+                        if (j & 1) stage_chunk<VEC4>(rb, stg, lane);
+                        else stage_chunk<VEC4>(ra, stg, lane);
+                        __syncwarp();
+                        if (j + 1 < nvalid) {  // in flight during the stores below
+                            if (j & 1) tmem_ld_32x32(taddr + 32 * (half + 2 * (j + 1)), ra);
+                            else tmem_ld_32x32(taddr + 32 * (half + 2 * (j + 1)), rb);
+                        } else {
+                            tc_fence_before_sync();  // last chunk is out of TMEM: hand the buffer back early
+                            if (lane == 0) mbar_arrive(smem_u32(tempty + buf));
+                        }
+                        float4 rs_cur[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) rs_cur[i] = rs[i];
+                        if constexpr (VEC4)
+                            if (j + 1 < nvalid) load_residual_vec4(rs, lane, row0, n0 + 32 * (half + 2 * (j + 1)), args);
+                        store_chunk_f32<VEC4>(stg, lane, row0, n0 + 32 * (half + 2 * j), args, alpha, amax, rs_cur);
+                        __syncwarp();
+                    }
                 }
+                }  // !VEC4
                 if (nvalid == 0) {
                     tc_fence_before_sync();
                     __syncwarp();
@@ -1246,26 +1281,55 @@ gemm_fp8_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
 
             if constexpr (MODE == kOutF32Vec || MODE == kOutF32) {
                 constexpr bool VEC4 = MODE == kOutF32Vec;
-                uint32_t r[32];
-                if (nvalid > 0) tmem_ld_32x32(taddr + 32 * half, r);
-                for (int j = 0; j < nvalid; ++j) {
-                    tmem_ld_wait();
-                    stage_chunk<VEC4>(r, stg, lane);
-                    __syncwarp();
-                    if (j + 1 < nvalid) {
-                        tmem_ld_32x32(taddr + 32 * (half + 2 * (j + 1)), r);
-                    } else {
-                        tc_fence_before_sync();
-                        release(buf);
-                    }
-                    float4 rs_cur[8];
+                if constexpr (VEC4) {
+                    // (one register set in a run-time loop: see the single-CTA kernel)
+                    uint32_t r[32];
+                    if (nvalid > 0) tmem_ld_32x32(taddr + 32 * half, r);
+                    for (int j = 0; j < nvalid; ++j) {
+                        tmem_ld_wait();
+                        stage_chunk<VEC4>(r, stg, lane);
+                        __syncwarp();
+                        if (j + 1 < nvalid) {
+                            tmem_ld_32x32(taddr + 32 * (half + 2 * (j + 1)), r);
+                        } else {
+                            tc_fence_before_sync();
+                            release(buf);
+                        }
+                        float4 rs_cur[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) rs_cur[i] = rs[i];
-                    if constexpr (VEC4)
+                        for (int i = 0; i < 8; ++i) rs_cur[i] = rs[i];
                         if (j + 1 < nvalid) load_residual_vec4(rs, lane, row0, n0 + 32 * (half + 2 * (j + 1)), args);
-                    store_chunk_f32<VEC4>(stg, lane, row0, n0 + 32 * (half + 2 * j), args, alpha, amax, rs_cur);
-                    __syncwarp();
+                        store_chunk_f32<VEC4>(stg, lane, row0, n0 + 32 * (half + 2 * j), args, alpha, amax, rs_cur);
+                        __syncwarp();
+                    }
+                } else {
+                // (two register sets and a compile-time trip count: see the single-CTA kernel)
+                uint32_t ra[32], rb[32];
+                if (nvalid > 0) tmem_ld_32x32(taddr + 32 * half, ra);
+#pragma unroll
+                for (int j = 0; j < kChunks; ++j) {
+                    if (j < nvalid) {
+                        tmem_ld_wait();
+                        if (j & 1) stage_chunk<VEC4>(rb, stg, lane);
+                        else stage_chunk<VEC4>(ra, stg, lane);
+                        __syncwarp();
+                        if (j + 1 < nvalid) {
+                            if (j & 1) tmem_ld_32x32(taddr + 32 * (half + 2 * (j + 1)), ra);
+                            else tmem_ld_32x32(taddr + 32 * (half + 2 * (j + 1)), rb);
+                        } else {
+                            tc_fence_before_sync();
+                            release(buf);
+                        }
+                        float4 rs_cur[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) rs_cur[i] = rs[i];
+                        if constexpr (VEC4)
+                            if (j + 1 < nvalid) load_residual_vec4(rs, lane, row0, n0 + 32 * (half + 2 * (j + 1)), args);
+                        store_chunk_f32<VEC4>(stg, lane, row0, n0 + 32 * (half + 2 * j), args, alpha, amax, rs_cur);
+                        __syncwarp();
+                    }
                 }
+                }  // !VEC4
                 if (nvalid == 0) {
                     tc_fence_before_sync();
                     __syncwarp();

@@ -70,6 +70,10 @@ __host__ __device__ constexpr int epi_warps(int mode) { return is_direct(mode) ?
 __host__ __device__ constexpr int direct_staging_bytes(int mode) { return mode == kOutNone ? 256 : 256 + 2048; }
 __host__ __device__ constexpr int gemm_threads(int mode) { return 64 + 32 * epi_warps(mode); }
 
+// Keep this struct at or below 128 bytes (a static_assert below checks it): above that size the compiler no longer
+// scalarises the by-value kernel parameter but reads its fields through a register-held parameter address, and the
+// kernels built that way raised an illegal memory access on a test shape (cause not established).  More per-launch
+// data: a separate kernel parameter.
 struct GemmArgs {
     const float* scale_a;   // {q, dq} of A
     const float* scale_w;   // {q, dq} of W
@@ -88,6 +92,8 @@ struct GemmArgs {
     unsigned int* status;
     unsigned int* grid_counter;  // fused max|out| + codes launch: arrival counter of the grid-wide barrier, else null
 };
+
+static_assert(sizeof(GemmArgs) <= 128, "GemmArgs must stay within 128 bytes: see the comment above the struct");
 
 // Arrival counters of the fused launches' grid-wide barrier: each counts up for ever (a launch waits for the next
 // multiple of its grid size), one of them per launch in turn so that launches that overlap in time do not mix.
